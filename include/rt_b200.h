@@ -1,0 +1,277 @@
+/*
+ * rt_b200.h - C ABI of librt_b200.so: hand-written sm_100a kernels for the
+ * DeepSeek-V3.2 partition hot path of racetrack.
+ *
+ * Conventions
+ *   - Every pointer is a DEVICE pointer unless its comment says "host".
+ *   - Row-major 2-D tensors; a `*_stride` argument is the distance between two
+ *     consecutive rows IN ELEMENTS, so a column slice of a wider matrix (the
+ *     q_c / kv_c / k_pe slices of the [T,2112] qkv_a output) needs no copy.
+ *   - `dtype` / `weight_dtype` take an rt_dtype tag.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = legacy default stream).
+ *     Nothing here synchronises, allocates or frees; every call only enqueues
+ *     kernels on `stream`, so all entry points are CUDA-graph capturable unless
+ *     stated otherwise.
+ *   - Return value: RT_OK (0) or a negative rt_status. rt_last_error() returns
+ *     a thread-local, human readable description of the last failure.
+ *
+ * Each entry point names the racetrack interface it stands in for as
+ * `ref: <file>:<lines>` (paths inside the racetrack project).
+ */
+#ifndef RT_B200_H
+#define RT_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum rt_dtype {
+    RT_BF16 = 0,
+    RT_F32 = 1,
+    RT_F16 = 2
+} rt_dtype;
+
+typedef enum rt_status {
+    RT_OK = 0,
+    RT_ERR_BAD_ARG = -1,      /* null pointer, negative size, bad enum */
+    RT_ERR_UNSUPPORTED = -2,  /* shape / dtype / alignment this build does not cover */
+    RT_ERR_CUDA = -3,         /* a CUDA runtime call or launch failed */
+    RT_ERR_TIMEOUT = -4       /* a bounded device-side wait expired */
+} rt_status;
+
+/* Library ABI version (bumped when a signature changes). */
+int rt_version(void);
+
+/* Thread-local description of the last non-zero status returned on this thread. */
+const char* rt_last_error(void);
+
+/* Number of kernels this library has launched since load (all threads).
+ * Lets a harness count launches inside a timed region. */
+int64_t rt_launch_count(void);
+
+/* ------------------------------------------------------------------------ */
+/* Residual add + RMSNorm                                                     */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * hidden = update + residual (fp32); normed = weight * (hidden * rsqrt(mean(hidden^2) + eps)),
+ * computed from the un-rounded fp32 sum; both outputs rounded to `dtype`.
+ * One pass: each input element is read once, each output written once.
+ * `normed` and `hidden` are contiguous [rows, cols]. cols % 8 == 0, cols <= 65536.
+ * ref: racetrack/models/deepseek.py:485-495 (RMSNorm.forward fallback),
+ *      partitions/dsv3_2/a1f6d7e2/kernels/cutedsl/residual_norm.py:47-147 (the op it replaces).
+ */
+int rt_residual_norm(const void* update, const void* residual,
+                     const void* weight, int weight_dtype,
+                     void* normed, void* hidden,
+                     int64_t rows, int64_t cols,
+                     int64_t update_stride, int64_t residual_stride,
+                     float eps, int dtype, void* stream);
+
+/*
+ * out = (x * rsqrt(mean(x^2) + eps)) * weight, fp32 math, rounded to `dtype`.
+ * `out` has row stride `out_stride`. cols % 8 == 0, cols <= 65536.
+ * ref: partitions/_base.py:24-28 (rms_norm), racetrack/models/deepseek.py:478-483.
+ */
+int rt_rms_norm(const void* x, const void* weight, int weight_dtype, void* out,
+                int64_t rows, int64_t cols, int64_t x_stride, int64_t out_stride,
+                float eps, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* MLA prologue: q_a / kv_a RMSNorm fused with RoPE on the k_pe slice         */
+/* ------------------------------------------------------------------------ */
+
+/* RoPE conventions */
+typedef enum rt_rope_mode {
+    RT_ROPE_HALF = 0,        /* [x1*c - x2*s, x2*c + x1*s], x1 = x[:d/2], x2 = x[d/2:];
+                                cos/sin rounded to `dtype` and every product/sum rounded to
+                                `dtype` like torch eager does on tensors of that dtype.
+                                ref: partitions/dsv3_2/model.py:55-81 (apply_rope) */
+    RT_ROPE_INTERLEAVED = 1  /* complex multiply of (x[2i], x[2i+1]) by (cos_i, sin_i) in fp32,
+                                one rounding at the end.
+                                ref: racetrack/models/deepseek.py:604-624 (apply_rotary_emb) */
+} rt_rope_mode;
+
+/*
+ * One launch per token batch:
+ *   q_out  = rms_norm(q_c,  q_weight)   [tokens, q_cols]   contiguous
+ *   kv_out = rms_norm(kv_c, kv_weight)  [tokens, kv_cols]  contiguous
+ *   k_out  = rope(k_pe)                 [tokens, rope_dim] contiguous
+ * Rotation angles:
+ *   RT_ROPE_HALF:        `table` = inv_freq fp32 [rope_dim/2]; the kernel forms
+ *                        angle = float(positions[t]) * inv_freq[i] and evaluates cosf/sinf.
+ *   RT_ROPE_INTERLEAVED: `table` = [table_rows, rope_dim/2] (cos, sin) fp32 pairs, the
+ *                        memory image of the complex64 tensor precompute_freqs_cis returns;
+ *                        row = positions[t], or t % table_rows when positions is NULL.
+ * q_cols % 8 == 0, kv_cols % 8 == 0, rope_dim % 2 == 0, rope_dim <= 512.
+ * ref: partitions/dsv3_2/model.py:84-99 (fused_norm_rope), :333-344 (its call site),
+ *      racetrack/models/deepseek.py:766-776 (q_norm / kv_norm / k_pe rotary in MLA.forward).
+ */
+int rt_norm_rope(const void* q_c, const void* q_weight,
+                 const void* kv_c, const void* kv_weight, int weight_dtype,
+                 const void* k_pe, const int64_t* positions,
+                 const float* table, int64_t table_rows,
+                 void* q_out, void* kv_out, void* k_out,
+                 int64_t tokens, int64_t q_cols, int64_t kv_cols, int64_t rope_dim,
+                 int64_t q_stride, int64_t kv_stride, int64_t k_stride,
+                 float eps, int rope_mode, int dtype, void* stream);
+
+/*
+ * RoPE on a [tokens, heads, rope_dim] view: element (t, h, :) starts at
+ * x + t*token_stride + h*head_stride (elements); `out` uses out_token_stride /
+ * out_head_stride the same way (x == out is allowed: in-place on the q_pe slice of q).
+ * positions / table / table_rows as in rt_norm_rope.
+ * rope_dim % 16 == 0, rope_dim <= 512; all strides % 8 == 0.
+ * ref: racetrack/models/deepseek.py:604-624, :771 (q_pe), racetrack/realistic_bench.py:297-302.
+ */
+int rt_rope(const void* x, const int64_t* positions, const float* table, int64_t table_rows,
+            void* out, int64_t tokens, int64_t heads, int64_t rope_dim,
+            int64_t token_stride, int64_t head_stride,
+            int64_t out_token_stride, int64_t out_head_stride,
+            int rope_mode, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* SwiGLU and activation quantisation                                         */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * out = (silu(gate.float()) * up.float()) rounded to `dtype`; out contiguous [rows, cols].
+ * gate and up may be the two halves of one [rows, 2*cols] gate_up matrix (strides = 2*cols).
+ * cols % 8 == 0.
+ * ref: racetrack/models/deepseek.py:850-851 (MLP fallback), :958-959 (Expert fallback).
+ */
+int rt_swiglu(const void* gate, const void* up, void* out,
+              int64_t rows, int64_t cols, int64_t gate_stride, int64_t up_stride,
+              int dtype, void* stream);
+
+/*
+ * FP8 e4m3 per-row, per-128-column-group quantisation:
+ *   amax = max(|x|) clamped to >= 1e-4; scale = amax / 448 (IEEE division);
+ *   code = e4m3_rne(clamp(x / scale, -448, 448)).
+ * codes: [rows, cols] bytes (e4m3fn), scales: [rows, cols/128] fp32, both contiguous.
+ * cols % 128 == 0.
+ * ref: racetrack/models/deepseek.py:85-107 (act_quant).
+ */
+int rt_act_quant_fp8(const void* x, void* codes, float* scales,
+                     int64_t rows, int64_t cols, int64_t x_stride,
+                     int dtype, void* stream);
+
+/*
+ * h = (silu(gate.float()) * up.float()) rounded to `dtype`, then the FP8 group
+ * quantisation of rt_act_quant_fp8 applied to h; h is never written to memory.
+ * ref: benchmarks/gsm8k/flat_decode.py:132-136 (SwiGLU -> act_quant composite),
+ *      partitions/dsv3_2/3336cdbd/kernels/cutedsl/act_quant.py:96-151 (the op it replaces).
+ */
+int rt_swiglu_quant_fp8(const void* gate, const void* up, void* codes, float* scales,
+                        int64_t rows, int64_t cols, int64_t gate_stride, int64_t up_stride,
+                        int dtype, void* stream);
+
+/*
+ * Tensor-wide max(|x|) (optionally of h = swiglu(gate, up) when `up` is non-NULL,
+ * `x` then being the gate). Writes one fp32 to *amax_out. The kernel clears
+ * *amax_out itself (a first tiny launch), so no host memset is needed.
+ * No counterpart in racetrack: NVFP4 exists there only as a model label.
+ */
+int rt_absmax(const void* x, const void* up, float* amax_out,
+              int64_t rows, int64_t cols, int64_t x_stride, int64_t up_stride,
+              int dtype, void* stream);
+
+/* Block-scale layouts for NVFP4 */
+typedef enum rt_sf_layout {
+    RT_SF_ROWMAJOR = 0,   /* [rows, cols/16] bytes */
+    RT_SF_TILED128x4 = 1  /* the 128-row x 4-block tile the tcgen05 block-scaled MMA reads:
+                             byte offset of (row r, block b) =
+                             ((r/128) * ceil(nblk/4) + b/4) * 512 + (r%32)*16 + ((r%128)/32)*4 + b%4 */
+} rt_sf_layout;
+
+/*
+ * NVFP4 quantisation: 16-element blocks along a row, e2m1 codes (two per byte,
+ * element 2i in the low nibble), e4m3 block scale, fp32 tensor-wide global scale.
+ *   gs   = amax / 2688            (2688 = 448 * 6; gs := 1 when amax == 0), read from *amax_in
+ *   bs   = e4m3_rne(min(block_amax / (6 * gs), 448))
+ *   code = e2m1_rne_sat(x / (gs * float(bs)))   (0 when bs == 0)
+ * `amax_in` is a device fp32 (from rt_absmax or a calibrated constant).
+ * When `up` is non-NULL the quantised tensor is h = bf16(silu(x) * up) (x = gate).
+ * codes: [rows, cols/2] bytes contiguous; block_scales per `sf_layout`.
+ * global_scale_out (device fp32, may be NULL) receives gs.
+ * cols % 16 == 0 (RT_SF_TILED128x4: the scale buffer must hold
+ * ceil(rows/128)*ceil(cols/64)*512 bytes; padding entries are written as 0).
+ * No counterpart in racetrack (see rt_absmax).
+ */
+int rt_nvfp4_quant(const void* x, const void* up, const float* amax_in,
+                   void* codes, void* block_scales, float* global_scale_out,
+                   int64_t rows, int64_t cols, int64_t x_stride, int64_t up_stride,
+                   int sf_layout, int dtype, void* stream);
+
+/* ------------------------------------------------------------------------ */
+/* MoE routing and token permutation                                          */
+/* ------------------------------------------------------------------------ */
+
+typedef enum rt_score_func {
+    RT_SCORE_SIGMOID = 0,
+    RT_SCORE_SOFTMAX = 1
+} rt_score_func;
+
+/*
+ * Grouped top-k routing on fp32 router logits [tokens, n_experts] (row stride
+ * logits_stride): scores = sigmoid|softmax(logits); biased = scores + bias
+ * (bias may be NULL); experts are split into n_groups contiguous groups, a
+ * group's score is the sum of its two largest biased scores (the max when bias
+ * is NULL); only the topk_groups best groups stay eligible; the topk largest
+ * biased scores among them are selected, in descending order (ties: lowest
+ * expert id). weights = unbiased scores of the selected experts, divided by
+ * their sum when score_func is sigmoid, times route_scale.
+ * weights_out: [tokens, topk] fp32; indices_out: [tokens, topk] int64.
+ * n_experts <= 512, n_experts % n_groups == 0, topk <= 32.
+ * ref: racetrack/models/deepseek.py:888-920 (Gate.forward, after the logits GEMM at :898).
+ */
+int rt_moe_route(const float* logits, const float* bias,
+                 float* weights_out, int64_t* indices_out,
+                 int64_t tokens, int64_t n_experts, int64_t logits_stride,
+                 int64_t n_groups, int64_t topk_groups, int64_t topk,
+                 float route_scale, int score_func, void* stream);
+
+/*
+ * Stable counting sort of the tokens*topk (token, slot) pairs by expert id.
+ *   expert_offsets [n_experts + 1] int32: pairs of expert e occupy sorted positions
+ *                   [expert_offsets[e], expert_offsets[e+1])
+ *   sorted_pairs   [tokens*topk] int32: pair id p = token*topk + slot, grouped by expert,
+ *                   ascending p inside an expert (the order torch.where(indices == e) yields)
+ *   pair_pos       [tokens*topk] int32: inverse map, sorted position of pair p
+ * workspace: caller-provided device scratch of rt_moe_permute_workspace_bytes() bytes.
+ * ref: racetrack/models/deepseek.py:1011-1018 (bincount + per-expert torch.where loop).
+ */
+int64_t rt_moe_permute_workspace_bytes(int64_t tokens, int64_t topk, int64_t n_experts);
+int rt_moe_permute(const int64_t* indices, int32_t* expert_offsets,
+                   int32_t* sorted_pairs, int32_t* pair_pos, void* workspace,
+                   int64_t tokens, int64_t topk, int64_t n_experts, void* stream);
+
+/*
+ * Row gather: out[i, :] = x[sorted_pairs[i] / topk, :] for i in [0, n_pairs).
+ * cols % 8 == 0. Used to lay tokens out expert-by-expert for the grouped GEMM.
+ * ref: racetrack/models/deepseek.py:1017 (x[idx] inside the expert loop).
+ */
+int rt_moe_gather(const void* x, const int32_t* sorted_pairs, void* out,
+                  int64_t n_pairs, int64_t topk, int64_t cols, int64_t x_stride,
+                  int dtype, void* stream);
+
+/*
+ * Weighted combine: y[t, :] = sum_s weights[t, s] * expert_out[pair_pos[t*topk + s], :]
+ * (+ shared[t, :] when `shared` is non-NULL), fp32 accumulation in slot order,
+ * rounded to `dtype`. Pairs whose sorted position lies outside
+ * [pos_begin, pos_end) are skipped (expert-parallel ranks own a slice of the
+ * sorted range). cols % 8 == 0.
+ * ref: racetrack/models/deepseek.py:1018-1022 (y[idx] += expert(x[idx]) * weights[idx, top]; y += shared).
+ */
+int rt_moe_combine(const void* expert_out, const int32_t* pair_pos, const float* weights,
+                   const void* shared, void* y,
+                   int64_t tokens, int64_t topk, int64_t cols,
+                   int64_t pos_begin, int64_t pos_end,
+                   int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* RT_B200_H */

@@ -1,0 +1,321 @@
+"""CPU restatement of racetrack's vanilla-torch DeepSeek-V3.2 hot path.
+
+TEST INFRASTRUCTURE ONLY. This module is the checker, never the product: only
+tests/, __graft_entry__.smoke() and bench.py's CPU-baseline / reference legs may import
+it. Nothing under racetrack_b200/ imports it.
+
+Every function restates one reference function and cites it as ``ref: file:lines``
+(paths inside the racetrack project). The restatements are pinned against outputs of
+the reference itself: tests/golden/make_golden.py imports the reference, runs it on
+seeded inputs and stores input/output pairs; tests/test_oracle_golden.py replays them
+through this module and demands exact equality.
+
+The NVFP4 functions have no counterpart in the reference (it has no e2m1 code at
+all), so their parity is UNPINNED: they implement the format as the build's
+configuration states it (16-element blocks, e4m3 block scale, fp32 global scale =
+amax / (448 * 6)) and are checked only against hand-derived known answers.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Tuple
+
+import torch
+import torch.nn.functional as F
+
+FP8_BLOCK = 128
+FP8_MAX = 448.0
+FP4_MAX = 6.0
+NVFP4_BLOCK = 16
+
+
+# ---------------------------------------------------------------------------
+# norms
+# ---------------------------------------------------------------------------
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    """ref: partitions/_base.py:24-28 (same math as racetrack/models/deepseek.py:478-483)."""
+    dtype = x.dtype
+    xf = x.float()
+    scale = torch.rsqrt(xf.square().mean(dim=-1, keepdim=True) + eps)
+    return (xf * scale * weight.float()).to(dtype)
+
+
+def residual_norm(update: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor,
+                  eps: float) -> Tuple[torch.Tensor, torch.Tensor]:
+    """(normed, hidden). ref: racetrack/models/deepseek.py:485-495."""
+    hidden = update.float() + residual.float()
+    var = hidden.pow(2).mean(-1, keepdim=True)
+    normed = hidden * torch.rsqrt(var + eps)
+    return (weight * normed).to(update.dtype), hidden.to(update.dtype)
+
+
+# ---------------------------------------------------------------------------
+# RoPE
+# ---------------------------------------------------------------------------
+
+def rope_cache(positions: torch.Tensor, rotary_dim: int, base: float = 10000.0,
+               dtype: Optional[torch.dtype] = None):
+    """cos/sin tables [T, rotary_dim/2]. ref: partitions/dsv3_2/model.py:27-52."""
+    half = rotary_dim // 2
+    inv_freq = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float32) / max(half, 1)))
+    freqs = positions.float().unsqueeze(-1) * inv_freq.unsqueeze(0)
+    cos, sin = torch.cos(freqs), torch.sin(freqs)
+    if dtype is not None:
+        cos, sin = cos.to(dtype), sin.to(dtype)
+    return cos, sin
+
+
+def apply_rope(x: torch.Tensor, positions: torch.Tensor, base: float = 10000.0) -> torch.Tensor:
+    """Half-split RoPE over the whole last dimension. ref: partitions/dsv3_2/model.py:55-81."""
+    rotary_dim = x.shape[-1]
+    cos, sin = rope_cache(positions, rotary_dim, base=base, dtype=x.dtype)
+    half = rotary_dim // 2
+    x1, x2 = x[..., :half], x[..., half:]
+    while cos.dim() < x1.dim():
+        cos, sin = cos.unsqueeze(-2), sin.unsqueeze(-2)
+    return torch.cat((x1 * cos - x2 * sin, x2 * cos + x1 * sin), dim=-1)
+
+
+def precompute_freqs_cis(rope_dim: int, seqlen: int, theta: float = 10000.0,
+                         original_seq_len: int = 4096, rope_factor: float = 40.0,
+                         beta_fast: int = 32, beta_slow: int = 1) -> torch.Tensor:
+    """complex64 [seqlen, rope_dim/2], YaRN-corrected beyond original_seq_len.
+    ref: racetrack/models/deepseek.py:523-601."""
+    dim = rope_dim
+
+    def corr_dim(num_rot):
+        return dim * math.log(original_seq_len / (num_rot * 2 * math.pi)) / (2 * math.log(theta))
+
+    freqs = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32) / dim))
+    if seqlen > original_seq_len:
+        low = max(math.floor(corr_dim(beta_fast)), 0)
+        high = min(math.ceil(corr_dim(beta_slow)), dim - 1)
+        hi = high + 0.001 if low == high else high
+        ramp = torch.clamp((torch.arange(dim // 2, dtype=torch.float32) - low) / (hi - low), 0, 1)
+        smooth = 1 - ramp
+        freqs = freqs / rope_factor * (1 - smooth) + freqs * smooth
+    t = torch.arange(seqlen)
+    freqs = torch.outer(t, freqs)
+    return torch.polar(torch.ones_like(freqs), freqs)
+
+
+def apply_rotary_emb(x: torch.Tensor, freqs_cis: torch.Tensor,
+                     interleaved: bool = True) -> torch.Tensor:
+    """x [B, S, H, D] rotated by freqs_cis [S, D/2]. ref: racetrack/models/deepseek.py:604-624."""
+    dtype, shape = x.dtype, x.shape
+    if not interleaved:
+        x = x.view(*shape[:-1], 2, -1).transpose(-1, -2).contiguous()
+    xc = torch.view_as_complex(x.float().view(*shape[:-1], -1, 2))
+    fc = freqs_cis.view(1, xc.size(1), 1, xc.size(-1))
+    y = torch.view_as_real(xc * fc).flatten(3)
+    if not interleaved:
+        y = torch.cat([y[..., 0::2], y[..., 1::2]], dim=-1)
+    return y.to(dtype)
+
+
+def fused_norm_rope(q_c, q_weight, kv_c, kv_weight, k_pe, positions, *, eps: float,
+                    rope_base: float):
+    """ref: partitions/dsv3_2/model.py:84-99."""
+    return (rms_norm(q_c, q_weight, eps), rms_norm(kv_c, kv_weight, eps),
+            apply_rope(k_pe, positions, base=rope_base))
+
+
+def mla_prologue(x, residual, w_attn, q_c, w_q, kv_c, w_kv, q_pe, k_pe, freqs_cis, eps: float):
+    """The fused MLA prologue of the CPU-runnable configuration: residual-add + RMSNorm,
+    q_a / kv_a RMSNorm and interleaved RoPE on q_pe [T, H, D] and k_pe [T, 1, D].
+    ref: racetrack/models/deepseek.py:485-495, :478-483, :766-776."""
+    normed, hidden = residual_norm(x, residual, w_attn, eps)
+    qn = rms_norm(q_c, w_q, eps)
+    kvn = rms_norm(kv_c, w_kv, eps)
+    q_rot = apply_rotary_emb(q_pe.unsqueeze(0), freqs_cis).squeeze(0)
+    k_rot = apply_rotary_emb(k_pe.unsqueeze(0), freqs_cis).squeeze(0)
+    return normed, hidden, qn, kvn, q_rot, k_rot
+
+
+# ---------------------------------------------------------------------------
+# SwiGLU and FP8 activation quantisation
+# ---------------------------------------------------------------------------
+
+def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
+    """ref: racetrack/models/deepseek.py:850-851 (MLP), :958-959 (Expert)."""
+    return (F.silu(gate.float()) * up.float()).type_as(gate)
+
+
+def act_quant(x: torch.Tensor, block_size: int = FP8_BLOCK):
+    """(e4m3 codes, fp32 scales [..., N/block]). ref: racetrack/models/deepseek.py:85-107."""
+    x = x.contiguous()
+    n = x.size(-1)
+    assert n % block_size == 0
+    groups = n // block_size
+    shape = x.shape
+    xf = x.float().reshape(-1, groups, block_size)
+    amax = xf.abs().amax(dim=-1).clamp(min=1e-4)
+    scale = amax / FP8_MAX
+    y = (xf / scale.unsqueeze(-1)).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn).view(shape)
+    return y, scale.view(*shape[:-1], groups)
+
+
+def swiglu_quant(gate: torch.Tensor, up: torch.Tensor):
+    """SwiGLU rounded to the activation dtype, then act_quant.
+    ref: benchmarks/gsm8k/flat_decode.py:132-136."""
+    return act_quant(swiglu(gate, up))
+
+
+def block_dequant(weight: torch.Tensor, scale: torch.Tensor, block: int = FP8_BLOCK) -> torch.Tensor:
+    """FP8 weight [out, in] with [out/128, in/128] scales -> bf16.
+    ref: racetrack/models/deepseek.py:148-161."""
+    out_f, in_f = weight.shape
+    s = scale.float().repeat_interleave(block, 0)[:out_f].repeat_interleave(block, 1)[:, :in_f]
+    return (weight.float() * s).to(torch.bfloat16)
+
+
+def fp8_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor) -> torch.Tensor:
+    """Dequantise-then-matmul fallback of the FP8 block-scaled GEMM.
+    ref: racetrack/models/deepseek.py:113-121."""
+    a_s_e = a_s.repeat_interleave(FP8_BLOCK, dim=-1)[..., : a.shape[-1]]
+    a_bf = (a.to(torch.float32) * a_s_e).to(torch.bfloat16)
+    return F.linear(a_bf, block_dequant(b, b_s))
+
+
+# ---------------------------------------------------------------------------
+# NVFP4 (no reference counterpart: parity unpinned)
+# ---------------------------------------------------------------------------
+
+_E2M1_VALUES = torch.tensor([0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0])
+
+
+def e2m1_encode(v: torch.Tensor) -> torch.Tensor:
+    """fp32 -> 4-bit e2m1 code (uint8), round-to-nearest-even, saturating at +-6.
+    A tie between two grid points goes to the even code."""
+    a = v.abs()
+    code = ((a > 0.25).to(torch.uint8) + (a >= 0.75).to(torch.uint8) + (a > 1.25).to(torch.uint8)
+            + (a >= 1.75).to(torch.uint8) + (a > 2.5).to(torch.uint8) + (a >= 3.5).to(torch.uint8)
+            + (a > 5.0).to(torch.uint8))
+    sign = torch.signbit(v).to(torch.uint8) << 3
+    return code | sign
+
+
+def e2m1_decode(code: torch.Tensor) -> torch.Tensor:
+    mag = _E2M1_VALUES[(code & 7).long()]
+    return torch.where((code & 8) != 0, -mag, mag)
+
+
+def nvfp4_quant(x: torch.Tensor, amax: Optional[torch.Tensor] = None):
+    """(codes uint8 [..., N/2], block scales float8_e4m3fn [..., N/16], global scale fp32 scalar).
+
+    gs = amax / 2688 (1 when amax == 0); bs = e4m3_rne(min(block_amax / (6 * gs), 448));
+    code = e2m1(x * (1 / (gs * float(bs)))), all in IEEE fp32; an all-zero block scale gives
+    zero codes. Element 2i sits in the low nibble of byte i.
+    """
+    n = x.shape[-1]
+    assert n % NVFP4_BLOCK == 0
+    xf = x.float()
+    if amax is None:
+        amax = xf.abs().max()
+    amax = amax.float().reshape(())
+    gs = amax / 2688.0 if float(amax) > 0 else torch.tensor(1.0)
+    blocks = xf.reshape(*x.shape[:-1], n // NVFP4_BLOCK, NVFP4_BLOCK)
+    bmax = blocks.abs().amax(dim=-1)
+    t = (bmax / (6.0 * gs)).clamp(max=FP8_MAX)
+    bs = t.to(torch.float8_e4m3fn)
+    denom = gs * bs.float()
+    inv = torch.where(denom > 0, 1.0 / denom, torch.zeros_like(denom))
+    v = blocks * inv.unsqueeze(-1)
+    code = torch.where((denom > 0).unsqueeze(-1), e2m1_encode(v), torch.zeros((), dtype=torch.uint8))
+    code = code.reshape(*x.shape[:-1], n // 2, 2)
+    packed = code[..., 0] | (code[..., 1] << 4)
+    return packed, bs, gs.reshape(1).float()
+
+
+def nvfp4_dequant(codes: torch.Tensor, block_scales: torch.Tensor, gs: torch.Tensor) -> torch.Tensor:
+    """Inverse of nvfp4_quant -> fp32 [..., N]."""
+    lo, hi = codes & 0xF, codes >> 4
+    vals = torch.stack((e2m1_decode(lo), e2m1_decode(hi)), dim=-1).reshape(*codes.shape[:-1], -1)
+    n = vals.shape[-1]
+    scale = (block_scales.float() * gs.float().reshape(())).repeat_interleave(NVFP4_BLOCK, dim=-1)
+    return vals * scale[..., :n]
+
+
+def sf_tiled_offsets(rows: int, nblk: int) -> torch.Tensor:
+    """Byte offsets [rows, nblk] of block scales in the 128-row x 4-block tiled layout."""
+    r = torch.arange(rows).unsqueeze(1)
+    b = torch.arange(nblk).unsqueeze(0)
+    kt = (nblk + 3) // 4
+    return ((r // 128) * kt + b // 4) * 512 + (r % 32) * 16 + ((r % 128) // 32) * 4 + b % 4
+
+
+# ---------------------------------------------------------------------------
+# MoE gate, permutation, experts
+# ---------------------------------------------------------------------------
+
+def gate_route(logits: torch.Tensor, bias: Optional[torch.Tensor], *, n_groups: int,
+               topk_groups: int, topk: int, route_scale: float, score_func: str = "sigmoid"):
+    """Everything in Gate.forward after the logits GEMM. ref: racetrack/models/deepseek.py:899-920."""
+    tokens = logits.size(0)
+    scores = logits.softmax(dim=-1) if score_func == "softmax" else logits.sigmoid()
+    original = scores
+    if bias is not None:
+        scores = scores + bias
+    if n_groups > 1:
+        scores = scores.view(tokens, n_groups, -1)
+        if bias is None:
+            group_scores = scores.amax(dim=-1)
+        else:
+            group_scores = scores.topk(2, dim=-1)[0].sum(dim=-1)
+        idx = group_scores.topk(topk_groups, dim=-1)[1]
+        mask = scores.new_ones(tokens, n_groups, dtype=torch.bool).scatter_(1, idx, False)
+        scores = scores.masked_fill(mask.unsqueeze(-1), float("-inf")).flatten(1)
+    indices = scores.topk(topk, dim=-1)[1]
+    weights = original.gather(1, indices)
+    if score_func == "sigmoid":
+        weights = weights / weights.sum(dim=-1, keepdim=True)
+    weights = weights * route_scale
+    return weights, indices
+
+
+def gate_forward(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], **kw):
+    """ref: racetrack/models/deepseek.py:888-920 (logits GEMM in fp32 at :898)."""
+    return gate_route(F.linear(x.float(), weight.float()), bias, **kw)
+
+
+def moe_permute(indices: torch.Tensor, n_experts: int):
+    """(expert_offsets, sorted_pairs, pair_pos) as the per-expert ``torch.where(indices == e)``
+    loop orders them. ref: racetrack/models/deepseek.py:1011-1017."""
+    tokens, topk = indices.shape
+    counts = torch.bincount(indices.flatten(), minlength=n_experts)
+    offsets = torch.zeros(n_experts + 1, dtype=torch.int32)
+    offsets[1:] = counts.cumsum(0)
+    sorted_pairs = []
+    for e in range(n_experts):
+        idx, top = torch.where(indices == e)
+        sorted_pairs.append(idx * topk + top)
+    sorted_pairs = torch.cat(sorted_pairs).to(torch.int32)
+    pair_pos = torch.empty(tokens * topk, dtype=torch.int32)
+    pair_pos[sorted_pairs.long()] = torch.arange(tokens * topk, dtype=torch.int32)
+    return offsets, sorted_pairs, pair_pos
+
+
+def expert_mlp(x, w1, w2, w3):
+    """One SwiGLU expert with bf16 weights. ref: racetrack/models/deepseek.py:944-962."""
+    h = swiglu(F.linear(x, w1), F.linear(x, w3))
+    return F.linear(h.type_as(x), w2)
+
+
+def moe_forward(x, gate_w, gate_b, experts, shared, *, n_groups, topk_groups, topk, route_scale,
+                score_func="sigmoid", expert_range=None):
+    """x [T, dim]; experts = list of (w1, w2, w3) or None; shared = (w1, w2, w3) or None.
+    ref: racetrack/models/deepseek.py:998-1022."""
+    weights, indices = gate_forward(x, gate_w, gate_b, n_groups=n_groups, topk_groups=topk_groups,
+                                    topk=topk, route_scale=route_scale, score_func=score_func)
+    y = torch.zeros_like(x, dtype=torch.float32)
+    counts = torch.bincount(indices.flatten(), minlength=len(experts)).tolist()
+    lo, hi = expert_range if expert_range is not None else (0, len(experts))
+    for i in range(lo, hi):
+        if counts[i] == 0:
+            continue
+        idx, top = torch.where(indices == i)
+        y[idx] += expert_mlp(x[idx], *experts[i]) * weights[idx, top, None]
+    if shared is not None:
+        y += expert_mlp(x, *shared)
+    return y.type_as(x)

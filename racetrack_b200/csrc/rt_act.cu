@@ -1,0 +1,380 @@
+// SwiGLU and activation quantisation (FP8 e4m3 per-128 group, NVFP4 per-16 block).
+//
+// Streaming kernels over a [rows, cols] matrix, flattened into work items of 16
+// consecutive columns of one row: two 16-byte loads per input per thread, one
+// 16-byte (fp8) or 8-byte (fp4) store of codes. Items of one row are contiguous
+// in the thread index, so a 128-column FP8 group is 8 neighbouring lanes and its
+// amax needs three shuffles. Algorithmic bytes per element (bf16 input):
+//   swiglu            2 + 2 read, 2 written
+//   act_quant_fp8     2 read, 1 + 4/128 written
+//   swiglu_quant_fp8  4 read, 1 + 4/128 written
+//   nvfp4_quant       2 (or 4 with swiglu) read, 1/2 + 1/16 written
+//   absmax            2 (or 4) read
+#include "rt_common.cuh"
+
+namespace rt {
+
+constexpr int kItem = 16;         // columns per work item
+constexpr int kActThreads = 256;  // threads per CTA for the streaming kernels
+
+// Loads the 16 values of one work item. With UP, the values are
+// bf16(silu(gate) * up), i.e. what the unfused torch path would hand to the quantiser.
+template <bool UP>
+__device__ __forceinline__ void load_item(const __nv_bfloat16* __restrict__ x,
+                                          const __nv_bfloat16* __restrict__ up, int64_t row,
+                                          int64_t col, int64_t xstride, int64_t ustride,
+                                          float (&v)[16]) {
+    const uint4* px = reinterpret_cast<const uint4*>(x + row * xstride + col);
+    const uint4 a0 = ld_stream16(px), a1 = ld_stream16(px + 1);
+    float lo[8], hi[8];
+    unpack_bf16x8(a0, lo);
+    unpack_bf16x8(a1, hi);
+    if constexpr (UP) {
+        const uint4* pu = reinterpret_cast<const uint4*>(up + row * ustride + col);
+        const uint4 b0 = ld_stream16(pu), b1 = ld_stream16(pu + 1);
+        float ulo[8], uhi[8];
+        unpack_bf16x8(b0, ulo);
+        unpack_bf16x8(b1, uhi);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            lo[k] = round_bf16(swiglu_f32(lo[k], ulo[k]));
+            hi[k] = round_bf16(swiglu_f32(hi[k], uhi[k]));
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+        v[k] = lo[k];
+        v[8 + k] = hi[k];
+    }
+}
+
+__device__ __forceinline__ float absmax16(const float (&v)[16]) {
+    float m = 0.f;
+#pragma unroll
+    for (int k = 0; k < 16; ++k) m = fmaxf(m, fabsf(v[k]));
+    return m;
+}
+
+// Two fp32 -> two e4m3 (RNE, saturating), `lo` in the low byte.
+__device__ __forceinline__ uint32_t cvt_e4m3x2(float lo, float hi) {
+    uint16_t d;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+    return d;
+}
+
+// e4m3 byte -> fp32 (exact).
+__device__ __forceinline__ float e4m3_to_f32(uint32_t b) {
+    uint32_t h2;
+    asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(h2) : "h"(static_cast<uint16_t>(b)));
+    return __half2float(__ushort_as_half(static_cast<uint16_t>(h2 & 0xffffu)));
+}
+
+// ---------------------------------------------------------------------------
+// SwiGLU
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(kActThreads) swiglu_kernel(
+    const __nv_bfloat16* __restrict__ gate, const __nv_bfloat16* __restrict__ up,
+    __nv_bfloat16* __restrict__ out, uint32_t items, uint32_t items_per_row, int64_t gstride,
+    int64_t ustride, int64_t cols) {
+    const uint32_t id = blockIdx.x * kActThreads + threadIdx.x;
+    if (id >= items) return;
+    const uint32_t row = id / items_per_row;
+    const int64_t col = static_cast<int64_t>(id - row * items_per_row) * 8;
+    const uint4 g = ld_stream16(gate + row * gstride + col);
+    const uint4 u = ld_stream16(up + row * ustride + col);
+    float gf[8], uf[8], o[8];
+    unpack_bf16x8(g, gf);
+    unpack_bf16x8(u, uf);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) o[k] = swiglu_f32(gf[k], uf[k]);
+    st_stream16(out + row * cols + col, pack_bf16x8(o));
+}
+
+// ---------------------------------------------------------------------------
+// FP8 e4m3 per-128-column group quantisation (optionally of swiglu(gate, up))
+// ---------------------------------------------------------------------------
+template <bool UP>
+__global__ void __launch_bounds__(kActThreads) quant_fp8_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
+    uint8_t* __restrict__ codes, float* __restrict__ scales, uint32_t items,
+    uint32_t items_per_row, int64_t xstride, int64_t ustride, int64_t cols) {
+    const uint32_t id = blockIdx.x * kActThreads + threadIdx.x;
+    // items is a multiple of 8 and CTAs start on a multiple of 8, so the eight
+    // lanes of a group are either all in range or all out of range.
+    if (id >= items) return;
+    const uint32_t row = id / items_per_row;
+    const uint32_t item = id - row * items_per_row;
+    const int64_t col = static_cast<int64_t>(item) * kItem;
+    float v[16];
+    load_item<UP>(x, up, row, col, xstride, ustride, v);
+    float amax = absmax16(v);
+    // the 8 lanes of a group share one shuffle mask segment
+    const uint32_t lane = threadIdx.x & 31u;
+    const uint32_t gmask = 0xffu << (lane & 24u);
+    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 1));
+    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 2));
+    amax = fmaxf(amax, __shfl_xor_sync(gmask, amax, 4));
+    amax = fmaxf(amax, 1.0e-4f);
+    const float scale = __fdiv_rn(amax, 448.0f);
+    const float rscale = __frcp_rn(scale);
+    uint32_t w[4];
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float q[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            q[j] = div_shared(v[4 * k + j], scale, rscale);
+            q[j] = fminf(fmaxf(q[j], -448.0f), 448.0f);
+        }
+        w[k] = cvt_e4m3x2(q[0], q[1]) | (cvt_e4m3x2(q[2], q[3]) << 16);
+    }
+    st_stream16(codes + static_cast<int64_t>(row) * cols + col, make_uint4(w[0], w[1], w[2], w[3]));
+    if ((item & 7u) == 0) scales[static_cast<int64_t>(row) * (cols >> 7) + (item >> 3)] = scale;
+}
+
+// ---------------------------------------------------------------------------
+// Tensor-wide abs-max (NVFP4 global scale)
+// ---------------------------------------------------------------------------
+__global__ void absmax_clear_kernel(float* out) { *out = 0.f; }
+
+template <bool UP>
+__global__ void __launch_bounds__(kActThreads) absmax_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
+    float* __restrict__ out, uint32_t items, uint32_t items_per_row, int64_t xstride,
+    int64_t ustride) {
+    __shared__ float scratch[32];
+    float m = 0.f;
+    for (uint32_t id = blockIdx.x * kActThreads + threadIdx.x; id < items;
+         id += gridDim.x * kActThreads) {
+        const uint32_t row = id / items_per_row;
+        const int64_t col = static_cast<int64_t>(id - row * items_per_row) * kItem;
+        float v[16];
+        load_item<UP>(x, up, row, col, xstride, ustride, v);
+        m = fmaxf(m, absmax16(v));
+    }
+    m = warp_max(m);
+    if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+    __syncthreads();
+    if (threadIdx.x < 32) {
+        m = (threadIdx.x < (kActThreads >> 5)) ? scratch[threadIdx.x] : 0.f;
+        m = warp_max(m);
+        // non-negative floats order like their bit patterns
+        if (threadIdx.x == 0) atomicMax(reinterpret_cast<int*>(out), __float_as_int(m));
+    }
+}
+
+// ---------------------------------------------------------------------------
+// NVFP4: e2m1 codes, e4m3 scale per 16-element block, fp32 global scale
+// ---------------------------------------------------------------------------
+
+// Nearest-even rounding of |v| onto the e2m1 grid {0, .5, 1, 1.5, 2, 3, 4, 6}:
+// the code is the number of rounding thresholds passed; a threshold that is a tie
+// belongs to the even code, hence the mix of > and >=.
+__device__ __forceinline__ uint32_t e2m1_code(float v) {
+    const float a = fabsf(v);
+    uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) +
+                 (a >= 3.5f) + (a > 5.0f);
+    return c | ((__float_as_uint(v) >> 28) & 8u);
+}
+
+__device__ __forceinline__ int64_t sf_offset(int layout, int64_t row, int64_t blk,
+                                             int64_t nblk) {
+    if (layout == RT_SF_ROWMAJOR) return row * nblk + blk;
+    const int64_t kt = (nblk + 3) >> 2;
+    return ((row >> 7) * kt + (blk >> 2)) * 512 + (row & 31) * 16 + ((row & 127) >> 5) * 4 +
+           (blk & 3);
+}
+
+template <bool UP>
+__global__ void __launch_bounds__(kActThreads) quant_nvfp4_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
+    const float* __restrict__ amax_in, uint8_t* __restrict__ codes, uint8_t* __restrict__ sf,
+    float* __restrict__ gs_out, uint32_t items, uint32_t items_per_row, int64_t xstride,
+    int64_t ustride, int64_t cols, int layout) {
+    const uint32_t id = blockIdx.x * kActThreads + threadIdx.x;
+    const float amax = __ldg(amax_in);
+    const float gs = amax > 0.f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
+    if (id == 0 && gs_out) *gs_out = gs;
+    if (id >= items) return;
+    const uint32_t row = id / items_per_row;
+    const uint32_t blk = id - row * items_per_row;
+    const int64_t col = static_cast<int64_t>(blk) * kItem;
+    float v[16];
+    load_item<UP>(x, up, row, col, xstride, ustride, v);
+    const float bmax = absmax16(v);
+    const float t = fminf(__fdiv_rn(bmax, __fmul_rn(6.0f, gs)), 448.0f);
+    const uint32_t bs = cvt_e4m3x2(t, 0.f) & 0xffu;
+    const float denom = __fmul_rn(gs, e4m3_to_f32(bs));
+    uint32_t lo = 0, hi = 0;
+    if (denom > 0.f) {
+        const float inv = __frcp_rn(denom);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) {
+            lo |= e2m1_code(__fmul_rn(v[k], inv)) << (4 * k);
+            hi |= e2m1_code(__fmul_rn(v[8 + k], inv)) << (4 * k);
+        }
+    }
+    st_stream8(codes + static_cast<int64_t>(row) * (cols >> 1) + (col >> 1), make_uint2(lo, hi));
+    sf[sf_offset(layout, row, blk, items_per_row)] = static_cast<uint8_t>(bs);
+}
+
+// Zero-fills the padding entries of a 128x4-tiled scale buffer (rows beyond
+// `rows` inside the last 128-row tile, blocks beyond nblk inside the last 4-block tile).
+__global__ void sf_pad_kernel(uint8_t* __restrict__ sf, int64_t rows, int64_t nblk,
+                              int64_t rows_pad, int64_t nblk_pad) {
+    const int64_t total = rows_pad * nblk_pad;
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t r = i / nblk_pad, b = i - r * nblk_pad;
+        if (r >= rows || b >= nblk) sf[sf_offset(RT_SF_TILED128x4, r, b, nblk)] = 0;
+    }
+}
+
+static int check_stream_args(const char* who, const void* x, int64_t rows, int64_t cols,
+                             int64_t xstride, int64_t mult, int dtype, uint32_t& items,
+                             uint32_t& per_row, int64_t item_cols) {
+    RT_REQUIRE(x, RT_ERR_BAD_ARG, "%s: null pointer", who);
+    RT_REQUIRE(rows >= 0 && cols > 0, RT_ERR_BAD_ARG, "%s: bad shape %lld x %lld", who,
+               (long long)rows, (long long)cols);
+    RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "%s: only bf16 activations", who);
+    RT_REQUIRE(cols % mult == 0, RT_ERR_UNSUPPORTED, "%s: cols %lld must be a multiple of %lld",
+               who, (long long)cols, (long long)mult);
+    RT_REQUIRE(xstride % 8 == 0 && aligned16(x), RT_ERR_UNSUPPORTED,
+               "%s: row stride must be a multiple of 8 and pointers 16-byte aligned", who);
+    const int64_t pr = cols / item_cols;
+    const int64_t total = rows * pr;
+    RT_REQUIRE(total < (1LL << 32) - kActThreads, RT_ERR_UNSUPPORTED, "%s: tensor too large", who);
+    items = static_cast<uint32_t>(total);
+    per_row = static_cast<uint32_t>(pr);
+    return RT_OK;
+}
+
+}  // namespace rt
+
+using namespace rt;
+
+extern "C" int rt_swiglu(const void* gate, const void* up, void* out, int64_t rows, int64_t cols,
+                         int64_t gate_stride, int64_t up_stride, int dtype, void* stream) {
+    uint32_t items, per_row;
+    if (int rc = check_stream_args("rt_swiglu", gate, rows, cols, gate_stride, 8, dtype, items,
+                                   per_row, 8))
+        return rc;
+    RT_REQUIRE(up && out, RT_ERR_BAD_ARG, "rt_swiglu: null pointer");
+    RT_REQUIRE(up_stride % 8 == 0 && aligned16(up) && aligned16(out), RT_ERR_UNSUPPORTED,
+               "rt_swiglu: up/out must be 16-byte aligned with stride %% 8 == 0");
+    if (items == 0) return RT_OK;
+    const unsigned grid = (items + kActThreads - 1) / kActThreads;
+    swiglu_kernel<<<grid, kActThreads, 0, as_stream(stream)>>>(
+        (const __nv_bfloat16*)gate, (const __nv_bfloat16*)up, (__nv_bfloat16*)out, items, per_row,
+        gate_stride, up_stride, cols);
+    count_launch();
+    return check_launch("swiglu_kernel");
+}
+
+static int quant_fp8_common(const char* who, const void* x, const void* up, void* codes,
+                            float* scales, int64_t rows, int64_t cols, int64_t x_stride,
+                            int64_t up_stride, int dtype, void* stream) {
+    uint32_t items, per_row;
+    if (int rc = check_stream_args(who, x, rows, cols, x_stride, 128, dtype, items, per_row, kItem))
+        return rc;
+    RT_REQUIRE(codes && scales, RT_ERR_BAD_ARG, "%s: null output pointer", who);
+    RT_REQUIRE(aligned16(codes), RT_ERR_UNSUPPORTED, "%s: codes must be 16-byte aligned", who);
+    if (up) RT_REQUIRE(up_stride % 8 == 0 && aligned16(up), RT_ERR_UNSUPPORTED,
+                       "%s: up must be 16-byte aligned with stride %% 8 == 0", who);
+    if (items == 0) return RT_OK;
+    const unsigned grid = (items + kActThreads - 1) / kActThreads;
+    if (up)
+        quant_fp8_kernel<true><<<grid, kActThreads, 0, as_stream(stream)>>>(
+            (const __nv_bfloat16*)x, (const __nv_bfloat16*)up, (uint8_t*)codes, scales, items,
+            per_row, x_stride, up_stride, cols);
+    else
+        quant_fp8_kernel<false><<<grid, kActThreads, 0, as_stream(stream)>>>(
+            (const __nv_bfloat16*)x, nullptr, (uint8_t*)codes, scales, items, per_row, x_stride, 0,
+            cols);
+    count_launch();
+    return check_launch("quant_fp8_kernel");
+}
+
+extern "C" int rt_act_quant_fp8(const void* x, void* codes, float* scales, int64_t rows,
+                                int64_t cols, int64_t x_stride, int dtype, void* stream) {
+    return quant_fp8_common("rt_act_quant_fp8", x, nullptr, codes, scales, rows, cols, x_stride, 0,
+                            dtype, stream);
+}
+
+extern "C" int rt_swiglu_quant_fp8(const void* gate, const void* up, void* codes, float* scales,
+                                   int64_t rows, int64_t cols, int64_t gate_stride,
+                                   int64_t up_stride, int dtype, void* stream) {
+    RT_REQUIRE(up, RT_ERR_BAD_ARG, "rt_swiglu_quant_fp8: null up pointer");
+    return quant_fp8_common("rt_swiglu_quant_fp8", gate, up, codes, scales, rows, cols,
+                            gate_stride, up_stride, dtype, stream);
+}
+
+extern "C" int rt_absmax(const void* x, const void* up, float* amax_out, int64_t rows,
+                         int64_t cols, int64_t x_stride, int64_t up_stride, int dtype,
+                         void* stream) {
+    uint32_t items, per_row;
+    if (int rc = check_stream_args("rt_absmax", x, rows, cols, x_stride, 16, dtype, items, per_row,
+                                   kItem))
+        return rc;
+    RT_REQUIRE(amax_out, RT_ERR_BAD_ARG, "rt_absmax: null output pointer");
+    if (up) RT_REQUIRE(up_stride % 8 == 0 && aligned16(up), RT_ERR_UNSUPPORTED,
+                       "rt_absmax: up must be 16-byte aligned with stride %% 8 == 0");
+    cudaStream_t st = as_stream(stream);
+    absmax_clear_kernel<<<1, 1, 0, st>>>(amax_out);
+    count_launch();
+    if (items == 0) return check_launch("absmax_clear_kernel");
+    // persistent grid: 148 SMs x 8 resident CTAs, each thread loops over items
+    unsigned grid = (items + kActThreads - 1) / kActThreads;
+    if (grid > 148u * 8u) grid = 148u * 8u;
+    if (up)
+        absmax_kernel<true><<<grid, kActThreads, 0, st>>>((const __nv_bfloat16*)x,
+                                                          (const __nv_bfloat16*)up, amax_out, items,
+                                                          per_row, x_stride, up_stride);
+    else
+        absmax_kernel<false><<<grid, kActThreads, 0, st>>>((const __nv_bfloat16*)x, nullptr,
+                                                           amax_out, items, per_row, x_stride, 0);
+    count_launch();
+    return check_launch("absmax_kernel");
+}
+
+extern "C" int rt_nvfp4_quant(const void* x, const void* up, const float* amax_in, void* codes,
+                              void* block_scales, float* global_scale_out, int64_t rows,
+                              int64_t cols, int64_t x_stride, int64_t up_stride, int sf_layout,
+                              int dtype, void* stream) {
+    uint32_t items, per_row;
+    if (int rc = check_stream_args("rt_nvfp4_quant", x, rows, cols, x_stride, 16, dtype, items,
+                                   per_row, kItem))
+        return rc;
+    RT_REQUIRE(amax_in && codes && block_scales, RT_ERR_BAD_ARG, "rt_nvfp4_quant: null pointer");
+    RT_REQUIRE(sf_layout == RT_SF_ROWMAJOR || sf_layout == RT_SF_TILED128x4, RT_ERR_BAD_ARG,
+               "rt_nvfp4_quant: bad sf_layout %d", sf_layout);
+    RT_REQUIRE((reinterpret_cast<uintptr_t>(codes) & 7u) == 0, RT_ERR_UNSUPPORTED,
+               "rt_nvfp4_quant: codes must be 8-byte aligned");
+    if (up) RT_REQUIRE(up_stride % 8 == 0 && aligned16(up), RT_ERR_UNSUPPORTED,
+                       "rt_nvfp4_quant: up must be 16-byte aligned with stride %% 8 == 0");
+    if (items == 0) return RT_OK;
+    cudaStream_t st = as_stream(stream);
+    const unsigned grid = (items + kActThreads - 1) / kActThreads;
+    if (up)
+        quant_nvfp4_kernel<true><<<grid, kActThreads, 0, st>>>(
+            (const __nv_bfloat16*)x, (const __nv_bfloat16*)up, amax_in, (uint8_t*)codes,
+            (uint8_t*)block_scales, global_scale_out, items, per_row, x_stride, up_stride, cols,
+            sf_layout);
+    else
+        quant_nvfp4_kernel<false><<<grid, kActThreads, 0, st>>>(
+            (const __nv_bfloat16*)x, nullptr, amax_in, (uint8_t*)codes, (uint8_t*)block_scales,
+            global_scale_out, items, per_row, x_stride, 0, cols, sf_layout);
+    count_launch();
+    if (int rc = check_launch("quant_nvfp4_kernel")) return rc;
+    if (sf_layout == RT_SF_TILED128x4) {
+        const int64_t rows_pad = (rows + 127) / 128 * 128, nblk = cols / 16;
+        const int64_t nblk_pad = (nblk + 3) / 4 * 4;
+        if (rows_pad != rows || nblk_pad != nblk) {
+            sf_pad_kernel<<<148, 256, 0, st>>>((uint8_t*)block_scales, rows, nblk, rows_pad,
+                                               nblk_pad);
+            count_launch();
+            return check_launch("sf_pad_kernel");
+        }
+    }
+    return RT_OK;
+}

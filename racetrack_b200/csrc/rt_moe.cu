@@ -1,0 +1,432 @@
+// MoE routing (grouped top-k on router logits), stable token permutation by
+// expert, row gather and weighted combine.
+//
+// Routing: one warp per token, the expert scores live in registers (n_experts/32
+// per lane), every selection step is a warp collective (redux / ballot / shuffle),
+// nothing touches shared memory. Algorithmic bytes per token: 4*n_experts read,
+// 12*topk written.
+// Permutation: counting sort in three small launches (per-block histograms,
+// scan, stable scatter); positions are a pure function of the indices, so the
+// result is deterministic and equal to what a per-expert torch.where loop yields.
+#include "rt_common.cuh"
+
+namespace rt {
+
+constexpr int kRouteWarps = 8;
+constexpr int kPermThreads = 1024;
+
+__device__ __forceinline__ uint32_t orderable(float f) {
+    const uint32_t u = __float_as_uint(f);
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
+}
+
+// EPL experts per lane; lane l owns experts [l*EPL, (l+1)*EPL).
+template <int EPL>
+__global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
+    const float* __restrict__ logits, const float* __restrict__ bias,
+    float* __restrict__ weights_out, int64_t* __restrict__ indices_out, int64_t tokens,
+    int n_experts, int64_t lstride, int n_groups, int topk_groups, int topk, float route_scale,
+    int score_func) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * kRouteWarps + (threadIdx.x >> 5);
+    if (t >= tokens) return;  // whole warp leaves together
+    const float* row = logits + t * lstride;
+    const float ninf = -INFINITY;
+
+    float s[EPL];  // unbiased scores
+    float b[EPL];  // selection scores (biased, masked)
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int e = lane * EPL + j;
+        s[j] = (e < n_experts) ? __ldg(row + e) : ninf;
+    }
+    if (score_func == RT_SCORE_SOFTMAX) {
+        float m = ninf;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) m = fmaxf(m, s[j]);
+        m = warp_max(m);
+        float sum = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            s[j] = (lane * EPL + j < n_experts) ? expf(s[j] - m) : 0.f;
+            sum += s[j];
+        }
+        sum = warp_sum(sum);
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) s[j] = __fdiv_rn(s[j], sum);
+    } else {
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) s[j] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-s[j])));
+    }
+#pragma unroll
+    for (int j = 0; j < EPL; ++j) {
+        const int e = lane * EPL + j;
+        b[j] = (e < n_experts) ? (bias ? __fadd_rn(s[j], __ldg(bias + e)) : s[j]) : ninf;
+    }
+
+    if (n_groups > 1) {
+        // a group covers `lpg` whole consecutive lanes (checked on the host)
+        const int lpg = (n_experts / n_groups) / EPL;
+        float m1 = ninf, m2 = ninf;  // two largest selection scores of the lane
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            const float v = b[j];
+            m2 = fmaxf(m2, fminf(m1, v));
+            m1 = fmaxf(m1, v);
+        }
+        for (int o = 1; o < lpg; o <<= 1) {
+            const float o1 = __shfl_xor_sync(0xffffffffu, m1, o);
+            const float o2 = __shfl_xor_sync(0xffffffffu, m2, o);
+            m2 = fmaxf(fmaxf(m2, o2), fminf(m1, o1));
+            m1 = fmaxf(m1, o1);
+        }
+        const float gscore = bias ? __fadd_rn(m1, m2) : m1;
+        const int my_group = lane / lpg;
+        int rank = 0;
+        for (int g = 0; g < n_groups; ++g) {
+            const float og = __shfl_sync(0xffffffffu, gscore, g * lpg);
+            rank += (og > gscore) || (og == gscore && g < my_group);
+        }
+        const bool keep = (my_group < n_groups) && (rank < topk_groups);
+        if (!keep) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) b[j] = ninf;
+        }
+    }
+
+    float my_w = 0.f;
+    int my_idx = 0;
+    for (int k = 0; k < topk; ++k) {
+        float best = ninf;
+        int bj = 0;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            if (b[j] > best) {
+                best = b[j];
+                bj = j;
+            }
+        }
+        const uint32_t key = orderable(best);
+        const uint32_t top = __reduce_max_sync(0xffffffffu, key);
+        const int owner = __ffs(__ballot_sync(0xffffffffu, key == top)) - 1;
+        float sv = 0.f;
+#pragma unroll
+        for (int j = 0; j < EPL; ++j) {
+            if (j == bj) sv = s[j];
+        }
+        const float w = __shfl_sync(0xffffffffu, sv, owner);
+        const int idx = __shfl_sync(0xffffffffu, lane * EPL + bj, owner);
+        if (lane == owner) {
+#pragma unroll
+            for (int j = 0; j < EPL; ++j) {
+                if (j == bj) b[j] = ninf;
+            }
+        }
+        if (lane == k) {
+            my_w = w;
+            my_idx = idx;
+        }
+    }
+    if (score_func == RT_SCORE_SIGMOID) {
+        const float sum = warp_sum(lane < topk ? my_w : 0.f);
+        my_w = __fdiv_rn(my_w, sum);
+    }
+    my_w = __fmul_rn(my_w, route_scale);
+    if (lane < topk) {
+        weights_out[t * topk + lane] = my_w;
+        indices_out[t * topk + lane] = my_idx;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Stable permutation by expert
+// ---------------------------------------------------------------------------
+
+// Pass 1: per-block histogram of expert ids. counts[b * n_experts + e].
+__global__ void __launch_bounds__(kPermThreads) moe_count_kernel(
+    const int64_t* __restrict__ indices, int32_t* __restrict__ counts, int n_pairs,
+    int n_experts) {
+    extern __shared__ int hist[];
+    for (int e = threadIdx.x; e < n_experts; e += kPermThreads) hist[e] = 0;
+    __syncthreads();
+    const int p = blockIdx.x * kPermThreads + threadIdx.x;
+    if (p < n_pairs) {
+        const int e = static_cast<int>(indices[p]);
+        if (e >= 0 && e < n_experts) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_experts; e += kPermThreads)
+        counts[blockIdx.x * n_experts + e] = hist[e];
+}
+
+// Pass 2 (one CTA): turns per-block counts into per-block bases (exclusive over
+// blocks) and writes the exclusive scan of expert totals to expert_offsets.
+__global__ void __launch_bounds__(1024) moe_scan_kernel(int32_t* __restrict__ counts,
+                                                        int32_t* __restrict__ expert_offsets,
+                                                        int n_blocks, int n_experts) {
+    __shared__ int warp_tot[32];
+    __shared__ int carry_s;
+    if (threadIdx.x == 0) carry_s = 0;
+    __syncthreads();
+    for (int base = 0; base < n_experts; base += blockDim.x) {
+        const int e = base + threadIdx.x;
+        int total = 0;
+        if (e < n_experts) {
+            for (int b = 0; b < n_blocks; ++b) {
+                const int c = counts[b * n_experts + e];
+                counts[b * n_experts + e] = total;
+                total += c;
+            }
+        }
+        // block-wide exclusive scan of `total`
+        const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+        int incl = total;
+#pragma unroll
+        for (int o = 1; o < 32; o <<= 1) {
+            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            if (lane >= o) incl += v;
+        }
+        if (lane == 31) warp_tot[warp] = incl;
+        __syncthreads();
+        if (warp == 0) {
+            int w = (lane < (int)(blockDim.x >> 5)) ? warp_tot[lane] : 0;
+            int wi = w;
+#pragma unroll
+            for (int o = 1; o < 32; o <<= 1) {
+                const int v = __shfl_up_sync(0xffffffffu, wi, o);
+                if (lane >= o) wi += v;
+            }
+            warp_tot[lane] = wi - w;  // exclusive warp offsets
+        }
+        __syncthreads();
+        const int carry = carry_s;
+        const int excl = carry + warp_tot[warp] + incl - total;
+        if (e < n_experts) expert_offsets[e] = excl;
+        __syncthreads();
+        if (threadIdx.x == blockDim.x - 1) carry_s = excl + total;
+        __syncthreads();
+    }
+    if (threadIdx.x == 0) expert_offsets[n_experts] = carry_s;
+}
+
+// Pass 3: stable scatter. Within a block, pairs of one expert keep ascending
+// pair id: rank inside the warp by match_any, warps ordered by a scan in shared memory.
+__global__ void __launch_bounds__(kPermThreads) moe_scatter_kernel(
+    const int64_t* __restrict__ indices, const int32_t* __restrict__ block_base,
+    const int32_t* __restrict__ expert_offsets, int32_t* __restrict__ sorted_pairs,
+    int32_t* __restrict__ pair_pos, int n_pairs, int n_experts) {
+    extern __shared__ unsigned short wc[];  // [32][n_experts]
+    for (int i = threadIdx.x; i < 32 * n_experts; i += kPermThreads) wc[i] = 0;
+    __syncthreads();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int p = blockIdx.x * kPermThreads + threadIdx.x;
+    int e = -1;
+    if (p < n_pairs) {
+        e = static_cast<int>(indices[p]);
+        if (e < 0 || e >= n_experts) e = -1;
+    }
+    // invalid lanes get unique keys so they match nobody
+    const unsigned peers = __match_any_sync(0xffffffffu, e >= 0 ? e : n_experts + lane);
+    const int rank = __popc(peers & ((1u << lane) - 1u));
+    if (e >= 0 && rank == 0) wc[warp * n_experts + e] = static_cast<unsigned short>(__popc(peers));
+    __syncthreads();
+    for (int x = threadIdx.x; x < n_experts; x += kPermThreads) {
+        unsigned run = 0;
+        for (int w = 0; w < 32; ++w) {
+            const unsigned c = wc[w * n_experts + x];
+            wc[w * n_experts + x] = static_cast<unsigned short>(run);
+            run += c;
+        }
+    }
+    __syncthreads();
+    if (e >= 0) {
+        const int dest = expert_offsets[e] + block_base[blockIdx.x * n_experts + e] +
+                         wc[warp * n_experts + e] + rank;
+        sorted_pairs[dest] = p;
+        pair_pos[p] = dest;
+    }
+}
+
+// ---------------------------------------------------------------------------
+// Gather / combine
+// ---------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) moe_gather_kernel(
+    const __nv_bfloat16* __restrict__ x, const int32_t* __restrict__ sorted_pairs,
+    __nv_bfloat16* __restrict__ out, int64_t n_items, int nvec, int topk, int64_t xstride) {
+    const int64_t id = blockIdx.x * 256LL + threadIdx.x;
+    if (id >= n_items) return;
+    const int64_t r = id / nvec;
+    const int v = static_cast<int>(id - r * nvec);
+    const int64_t tok = __ldg(sorted_pairs + r) / topk;
+    const uint4 d = ld_cached16(reinterpret_cast<const uint4*>(x + tok * xstride) + v);
+    st_stream16(reinterpret_cast<uint4*>(out) + r * nvec + v, d);
+}
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(
+    const __nv_bfloat16* __restrict__ expert_out, const int32_t* __restrict__ pair_pos,
+    const float* __restrict__ weights, const __nv_bfloat16* __restrict__ shared,
+    __nv_bfloat16* __restrict__ y, int nvec, int topk, int pos_begin, int pos_end) {
+    const int64_t t = blockIdx.x;
+    for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+        float acc[8];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = 0.f;
+        for (int s = 0; s < topk; ++s) {
+            const int pos = __ldg(pair_pos + t * topk + s);
+            if (pos < pos_begin || pos >= pos_end) continue;
+            const float w = __ldg(weights + t * topk + s);
+            float f[8];
+            unpack_bf16x8(
+                ld_stream16(reinterpret_cast<const uint4*>(expert_out) + (int64_t)pos * nvec + v), f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = __fadd_rn(acc[k], __fmul_rn(f[k], w));
+        }
+        if (shared) {
+            float f[8];
+            unpack_bf16x8(ld_stream16(reinterpret_cast<const uint4*>(shared) + t * nvec + v), f);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = __fadd_rn(acc[k], f[k]);
+        }
+        st_stream16(reinterpret_cast<uint4*>(y) + t * nvec + v, pack_bf16x8(acc));
+    }
+}
+
+}  // namespace rt
+
+using namespace rt;
+
+extern "C" int rt_moe_route(const float* logits, const float* bias, float* weights_out,
+                            int64_t* indices_out, int64_t tokens, int64_t n_experts,
+                            int64_t logits_stride, int64_t n_groups, int64_t topk_groups,
+                            int64_t topk, float route_scale, int score_func, void* stream) {
+    RT_REQUIRE(logits && weights_out && indices_out, RT_ERR_BAD_ARG, "rt_moe_route: null pointer");
+    RT_REQUIRE(tokens >= 0 && n_experts > 0 && topk > 0 && n_groups > 0, RT_ERR_BAD_ARG,
+               "rt_moe_route: bad shape");
+    RT_REQUIRE(score_func == RT_SCORE_SIGMOID || score_func == RT_SCORE_SOFTMAX, RT_ERR_BAD_ARG,
+               "rt_moe_route: bad score_func %d", score_func);
+    RT_REQUIRE(n_experts <= 512 && topk <= 32 && topk <= n_experts, RT_ERR_UNSUPPORTED,
+               "rt_moe_route: needs n_experts <= 512 and topk <= min(32, n_experts)");
+    RT_REQUIRE(n_experts % n_groups == 0, RT_ERR_BAD_ARG,
+               "rt_moe_route: n_experts must be divisible by n_groups");
+    int epl = 1;
+    while (32 * epl < n_experts) epl <<= 1;
+    if (n_groups > 1) {
+        RT_REQUIRE(topk_groups > 0 && topk_groups <= n_groups, RT_ERR_BAD_ARG,
+                   "rt_moe_route: bad topk_groups");
+        const int64_t gsize = n_experts / n_groups;
+        const int64_t lpg = gsize / epl;
+        RT_REQUIRE(gsize % epl == 0 && lpg >= 1 && (lpg & (lpg - 1)) == 0 && lpg * n_groups <= 32,
+                   RT_ERR_UNSUPPORTED,
+                   "rt_moe_route: a group must cover a power-of-two number of whole lanes "
+                   "(n_experts=%lld n_groups=%lld)",
+                   (long long)n_experts, (long long)n_groups);
+        RT_REQUIRE(topk <= topk_groups * gsize, RT_ERR_BAD_ARG,
+                   "rt_moe_route: topk exceeds the experts left after group selection");
+    }
+    if (tokens == 0) return RT_OK;
+    const unsigned grid = static_cast<unsigned>((tokens + kRouteWarps - 1) / kRouteWarps);
+    cudaStream_t st = as_stream(stream);
+#define RT_LAUNCH_ROUTE(E)                                                                       \
+    moe_route_kernel<E><<<grid, kRouteWarps * 32, 0, st>>>(                                      \
+        logits, bias, weights_out, indices_out, tokens, (int)n_experts, logits_stride,           \
+        (int)n_groups, (int)topk_groups, (int)topk, route_scale, score_func)
+    switch (epl) {
+        case 1: RT_LAUNCH_ROUTE(1); break;
+        case 2: RT_LAUNCH_ROUTE(2); break;
+        case 4: RT_LAUNCH_ROUTE(4); break;
+        case 8: RT_LAUNCH_ROUTE(8); break;
+        default: RT_LAUNCH_ROUTE(16); break;
+    }
+#undef RT_LAUNCH_ROUTE
+    count_launch();
+    return check_launch("moe_route_kernel");
+}
+
+extern "C" int64_t rt_moe_permute_workspace_bytes(int64_t tokens, int64_t topk,
+                                                  int64_t n_experts) {
+    if (tokens < 0 || topk <= 0 || n_experts <= 0) return 0;
+    const int64_t blocks = (tokens * topk + kPermThreads - 1) / kPermThreads;
+    return (blocks > 0 ? blocks : 1) * n_experts * static_cast<int64_t>(sizeof(int32_t));
+}
+
+extern "C" int rt_moe_permute(const int64_t* indices, int32_t* expert_offsets,
+                              int32_t* sorted_pairs, int32_t* pair_pos, void* workspace,
+                              int64_t tokens, int64_t topk, int64_t n_experts, void* stream) {
+    RT_REQUIRE(indices && expert_offsets && sorted_pairs && pair_pos && workspace, RT_ERR_BAD_ARG,
+               "rt_moe_permute: null pointer");
+    RT_REQUIRE(tokens >= 0 && topk > 0 && n_experts > 0, RT_ERR_BAD_ARG,
+               "rt_moe_permute: bad shape");
+    RT_REQUIRE(n_experts <= 1024, RT_ERR_UNSUPPORTED, "rt_moe_permute: n_experts above 1024");
+    const int64_t n_pairs = tokens * topk;
+    RT_REQUIRE(n_pairs < (1LL << 30), RT_ERR_UNSUPPORTED, "rt_moe_permute: too many pairs");
+    const int blocks = static_cast<int>((n_pairs + kPermThreads - 1) / kPermThreads);
+    cudaStream_t st = as_stream(stream);
+    int32_t* counts = static_cast<int32_t*>(workspace);
+    const int ne = static_cast<int>(n_experts);
+    if (blocks > 0) {
+        moe_count_kernel<<<blocks, kPermThreads, ne * sizeof(int), st>>>(indices, counts,
+                                                                         (int)n_pairs, ne);
+        count_launch();
+        if (int rc = check_launch("moe_count_kernel")) return rc;
+    }
+    int scan_threads = (ne + 31) / 32 * 32;
+    if (scan_threads > 1024) scan_threads = 1024;
+    moe_scan_kernel<<<1, scan_threads, 0, st>>>(counts, expert_offsets, blocks, ne);
+    count_launch();
+    if (int rc = check_launch("moe_scan_kernel")) return rc;
+    if (blocks > 0) {
+        const size_t smem = 32u * ne * sizeof(unsigned short);
+        if (smem > 48u * 1024u) {
+            cudaError_t e = cudaFuncSetAttribute(
+                moe_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_moe_permute: %s", cudaGetErrorString(e));
+        }
+        moe_scatter_kernel<<<blocks, kPermThreads, smem, st>>>(
+            indices, counts, expert_offsets, sorted_pairs, pair_pos, (int)n_pairs, ne);
+        count_launch();
+        if (int rc = check_launch("moe_scatter_kernel")) return rc;
+    }
+    return RT_OK;
+}
+
+extern "C" int rt_moe_gather(const void* x, const int32_t* sorted_pairs, void* out,
+                             int64_t n_pairs, int64_t topk, int64_t cols, int64_t x_stride,
+                             int dtype, void* stream) {
+    RT_REQUIRE(x && sorted_pairs && out, RT_ERR_BAD_ARG, "rt_moe_gather: null pointer");
+    RT_REQUIRE(n_pairs >= 0 && topk > 0 && cols > 0, RT_ERR_BAD_ARG, "rt_moe_gather: bad shape");
+    RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_moe_gather: only bf16");
+    RT_REQUIRE(cols % 8 == 0 && x_stride % 8 == 0 && aligned16(x) && aligned16(out),
+               RT_ERR_UNSUPPORTED, "rt_moe_gather: cols/stride %% 8 and 16-byte alignment needed");
+    if (n_pairs == 0) return RT_OK;
+    const int64_t nvec = cols / 8, items = n_pairs * nvec;
+    RT_REQUIRE(items / 256 < 0x7fffffffLL, RT_ERR_UNSUPPORTED, "rt_moe_gather: too large");
+    moe_gather_kernel<<<static_cast<unsigned>((items + 255) / 256), 256, 0, as_stream(stream)>>>(
+        (const __nv_bfloat16*)x, sorted_pairs, (__nv_bfloat16*)out, items, (int)nvec, (int)topk,
+        x_stride);
+    count_launch();
+    return check_launch("moe_gather_kernel");
+}
+
+extern "C" int rt_moe_combine(const void* expert_out, const int32_t* pair_pos,
+                              const float* weights, const void* shared, void* y, int64_t tokens,
+                              int64_t topk, int64_t cols, int64_t pos_begin, int64_t pos_end,
+                              int dtype, void* stream) {
+    RT_REQUIRE(expert_out && pair_pos && weights && y, RT_ERR_BAD_ARG,
+               "rt_moe_combine: null pointer");
+    RT_REQUIRE(tokens >= 0 && topk > 0 && cols > 0, RT_ERR_BAD_ARG, "rt_moe_combine: bad shape");
+    RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_moe_combine: only bf16");
+    RT_REQUIRE(cols % 8 == 0 && aligned16(expert_out) && aligned16(y) &&
+                   (!shared || aligned16(shared)),
+               RT_ERR_UNSUPPORTED, "rt_moe_combine: cols %% 8 and 16-byte alignment needed");
+    RT_REQUIRE(tokens <= 0x7fffffffLL && pos_end < (1LL << 31), RT_ERR_UNSUPPORTED,
+               "rt_moe_combine: too large");
+    if (tokens == 0) return RT_OK;
+    const int nvec = static_cast<int>(cols / 8);
+    int threads = (nvec + 31) / 32 * 32;
+    if (threads > 256) threads = 256;
+    moe_combine_kernel<<<static_cast<unsigned>(tokens), threads, 0, as_stream(stream)>>>(
+        (const __nv_bfloat16*)expert_out, pair_pos, weights, (const __nv_bfloat16*)shared,
+        (__nv_bfloat16*)y, nvec, (int)topk, (int)pos_begin, (int)pos_end);
+    count_launch();
+    return check_launch("moe_combine_kernel");
+}

@@ -1,0 +1,153 @@
+"""Per-kernel micro-benchmark: CUDA-event time, achieved GB/s and fraction of the HBM peak.
+
+    python -m racetrack_b200.kernel_bench [--tokens 4096] [--kernel NAME ...] [--json out.json]
+
+Same role as racetrack's scripts/benchmark_kernel.py (shapes + byte formulas + median of
+CUDA-event timings), for the sm_100a kernels of this package. Bytes are ALGORITHMIC bytes:
+every input element read once, every output element written once. L2 (126 MB) is flushed
+between timed iterations by overwriting a 512 MB buffer, so small working sets cannot hide
+in cache.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import statistics
+from pathlib import Path
+from typing import Callable
+
+import torch
+
+from . import _lib, ops
+
+HIDDEN, Q_LORA, KV_LORA, ROPE, HEADS, INTER, EXPERTS, TOPK = 7168, 1536, 512, 64, 128, 18432, 256, 8
+FALLBACK_HBM_GBS = 6650.0
+
+
+def hbm_peak_gbs() -> tuple[float, str]:
+    """Measured copy bandwidth of this pool's B200s when the driver recorded it, else the
+    stated fallback."""
+    p = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return FALLBACK_HBM_GBS, "fallback"
+
+
+class L2Flusher:
+    def __init__(self, nbytes: int = 512 << 20):
+        self.buf = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+
+    def __call__(self) -> None:
+        self.buf.fill_(1)
+
+
+def time_kernel(fn: Callable[[], object], *, warmup: int = 5, iters: int = 20,
+                flush: L2Flusher | None = None) -> dict:
+    """Median / min per-call device time in microseconds."""
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(iters):
+        if flush is not None:
+            flush()
+        start = torch.cuda.Event(enable_timing=True)
+        end = torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        torch.cuda.synchronize()
+        times.append(start.elapsed_time(end) * 1e3)
+    return {"median_us": statistics.median(times), "min_us": min(times)}
+
+
+def _randn(*shape, dtype=torch.bfloat16):
+    return torch.randn(*shape, device="cuda", dtype=torch.float32).to(dtype)
+
+
+def cases(tokens: int) -> dict[str, tuple[Callable[[], object], int]]:
+    """name -> (callable, algorithmic bytes per call)."""
+    T = tokens
+    out: dict[str, tuple[Callable[[], object], int]] = {}
+    u, r = _randn(T, HIDDEN), _randn(T, HIDDEN)
+    w = torch.ones(HIDDEN, device="cuda")
+    out["fused_residual_norm"] = (lambda: ops.fused_residual_norm(u, r, w, eps=1e-6),
+                                  4 * T * HIDDEN * 2 + HIDDEN * 4)
+    out["fused_rms_norm"] = (lambda: ops.fused_rms_norm(u, w, eps=1e-6), 2 * T * HIDDEN * 2 + HIDDEN * 4)
+    qkv = _randn(T, Q_LORA + KV_LORA + ROPE)
+    wq, wkv = torch.ones(Q_LORA, device="cuda"), torch.ones(KV_LORA, device="cuda")
+    pos = torch.arange(T, device="cuda")
+    out["fused_norm_rope"] = (
+        lambda: ops.fused_norm_rope(qkv[:, :Q_LORA], wq, qkv[:, Q_LORA:Q_LORA + KV_LORA], wkv,
+                                    qkv[:, Q_LORA + KV_LORA:], pos, eps=1e-6, rope_base=10000.0),
+        2 * T * (Q_LORA + KV_LORA + ROPE) * 2)
+    q_pe = _randn(T, HEADS, ROPE)
+    freqs = torch.polar(torch.ones(T, ROPE // 2, device="cuda"),
+                        torch.rand(T, ROPE // 2, device="cuda"))
+    out["fused_rope"] = (lambda: ops.fused_rope(q_pe, freqs), 2 * T * HEADS * ROPE * 2)
+    gu = _randn(T, 2 * INTER)
+    g, up = gu[:, :INTER], gu[:, INTER:]
+    out["fused_swiglu"] = (lambda: ops.fused_swiglu(g, up), 3 * T * INTER * 2)
+    x = _randn(T, INTER)
+    q_out = T * INTER + T * (INTER // 128) * 4
+    out["fused_act_quant"] = (lambda: ops.fused_act_quant(x), T * INTER * 2 + q_out)
+    out["fused_swiglu_quant"] = (lambda: ops.fused_swiglu_quant(g, up), 2 * T * INTER * 2 + q_out)
+    amax = ops.tensor_absmax(x)
+    n_out = T * INTER // 2 + T * INTER // 16
+    out["tensor_absmax"] = (lambda: ops.tensor_absmax(x), T * INTER * 2)
+    out["fused_nvfp4_quant"] = (lambda: ops.fused_nvfp4_quant(x, amax=amax), T * INTER * 2 + n_out)
+    amax_h = ops.tensor_absmax(g, up)
+    out["fused_swiglu_nvfp4_quant"] = (lambda: ops.fused_swiglu_nvfp4_quant(g, up, amax=amax_h),
+                                       2 * T * INTER * 2 + n_out)
+    logits = torch.randn(T, EXPERTS, device="cuda")
+    bias = torch.rand(EXPERTS, device="cuda") * 0.2 - 0.1
+    out["fused_moe_route"] = (
+        lambda: ops.fused_moe_route(logits, bias, n_groups=8, topk_groups=4, topk=TOPK,
+                                    route_scale=2.5),
+        T * EXPERTS * 4 + T * TOPK * 12)
+    _, idx = ops.fused_moe_route(logits, bias, n_groups=8, topk_groups=4, topk=TOPK, route_scale=2.5)
+    out["fused_moe_permute"] = (lambda: ops.fused_moe_permute(idx, EXPERTS),
+                                T * TOPK * (8 + 4 + 4))
+    off, sp, pp = ops.fused_moe_permute(idx, EXPERTS)
+    out["fused_moe_gather"] = (lambda: ops.fused_moe_gather(u, sp, TOPK),
+                               T * HIDDEN * 2 + T * TOPK * HIDDEN * 2)
+    eo = _randn(T * TOPK, HIDDEN)
+    wts = torch.rand(T, TOPK, device="cuda")
+    out["fused_moe_combine"] = (lambda: ops.fused_moe_combine(eo, pp, wts, u),
+                                T * TOPK * HIDDEN * 2 + 2 * T * HIDDEN * 2)
+    return out
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--tokens", type=int, default=4096)
+    ap.add_argument("--kernel", action="append", default=None)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--json", type=Path, default=None)
+    args = ap.parse_args()
+    peak, peak_src = hbm_peak_gbs()
+    flush = L2Flusher()
+    rows = []
+    for name, (fn, nbytes) in cases(args.tokens).items():
+        if args.kernel and name not in args.kernel:
+            continue
+        before = _lib.launch_count()
+        fn()
+        launches = _lib.launch_count() - before
+        t = time_kernel(fn, iters=args.iters, flush=flush)
+        gbs = nbytes / (t["median_us"] * 1e-6) / 1e9
+        rows.append({"kernel": name, "tokens": args.tokens, "launches": launches,
+                     "bytes": nbytes, **t, "gbs": gbs, "frac_of_hbm_peak": gbs / peak})
+        print(f"{name:28s} T={args.tokens:<6d} {t['median_us']:9.1f} us  {nbytes/1e6:9.1f} MB  "
+              f"{gbs:8.1f} GB/s  {100*gbs/peak:5.1f}% of {peak_src} {peak:.0f} GB/s  "
+              f"({launches} launch{'es' if launches != 1 else ''})", flush=True)
+    if args.json:
+        args.json.write_text(json.dumps({"hbm_peak_gbs": peak, "peak_source": peak_src,
+                                         "rows": rows}, indent=1) + "\n")
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,466 @@
+"""Tensor-level entry points of the B200 backend.
+
+Every function here takes CUDA tensors, allocates its outputs with torch's caching
+allocator, and enqueues hand-written sm_100a kernels from librt_b200.so on the
+current CUDA stream through the C ABI (include/rt_b200.h). Signatures and argument
+meaning follow racetrack's own kernel contracts (the file:line each one mirrors is
+given in its docstring); the ``fallback`` keyword every racetrack kernel receives is
+accepted and ignored - there is no torch or CPU fallback, unsupported inputs raise.
+"""
+from __future__ import annotations
+
+from typing import Callable, Optional
+
+import torch
+
+from . import _lib
+
+_BF16 = torch.bfloat16
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _require_cuda(*tensors: torch.Tensor) -> None:
+    for t in tensors:
+        if not t.is_cuda:
+            raise RuntimeError("racetrack_b200 ops need CUDA tensors (there is no CPU path)")
+
+
+def _require_bf16(name: str, t: torch.Tensor) -> None:
+    if t.dtype != _BF16:
+        raise RuntimeError(f"{name}: expected a bfloat16 tensor, got {t.dtype}")
+
+
+def _weight_tag(w: torch.Tensor) -> int:
+    if w.dtype == torch.bfloat16:
+        return _lib.RT_BF16
+    if w.dtype == torch.float32:
+        return _lib.RT_F32
+    raise RuntimeError(f"norm weight must be bfloat16 or float32, got {w.dtype}")
+
+
+def _rows_view(x: torch.Tensor) -> torch.Tensor:
+    """2-D [rows, cols] view whose row stride the kernels can take as is.
+
+    Column slices of a wider matrix are passed through untouched; anything whose
+    last dimension is not unit-stride or whose rows are not 16-byte aligned is copied.
+    """
+    cols = x.shape[-1]
+    if x.dim() == 1:
+        x = x.unsqueeze(0)
+    if x.dim() > 2:
+        x = x.reshape(-1, cols)
+    if x.stride(-1) != 1 or x.stride(0) % 8 != 0 or x.data_ptr() % 16 != 0:
+        x = x.contiguous()
+    return x
+
+
+# ---------------------------------------------------------------------------
+# residual add + RMSNorm
+# ---------------------------------------------------------------------------
+
+def fused_residual_norm(update: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, *,
+                        eps: float, fallback: Optional[Callable] = None):
+    """(normed, hidden) with hidden = update + residual, normed = rms_norm(hidden) * weight.
+
+    Contract of racetrack/models/deepseek.py:485-505 (RMSNorm.forward fallback and its
+    ``_kernel_call("fused_residual_norm", ...)``).
+    """
+    del fallback
+    _require_cuda(update, residual, weight)
+    _require_bf16("fused_residual_norm", update)
+    _require_bf16("fused_residual_norm", residual)
+    if update.shape != residual.shape:
+        raise RuntimeError("fused_residual_norm: update and residual shapes differ")
+    cols = update.shape[-1]
+    if weight.numel() != cols:
+        raise RuntimeError("fused_residual_norm: weight length does not match the last dimension")
+    u2, r2 = _rows_view(update), _rows_view(residual)
+    w = weight.contiguous()
+    normed = torch.empty(update.shape, dtype=update.dtype, device=update.device)
+    hidden = torch.empty(update.shape, dtype=update.dtype, device=update.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_residual_norm(u2.data_ptr(), r2.data_ptr(), w.data_ptr(), _weight_tag(w),
+                                    normed.data_ptr(), hidden.data_ptr(), u2.shape[0], cols,
+                                    u2.stride(0), r2.stride(0), float(eps), _lib.RT_BF16,
+                                    _stream()), "rt_residual_norm")
+    return normed, hidden
+
+
+def fused_residual_norm_legacy(residual: torch.Tensor, update: torch.Tensor, weight: torch.Tensor,
+                               *, eps: float, fallback: Optional[Callable] = None):
+    """Legacy argument/return order ``(residual, update, w) -> (hidden, normed)`` of
+    racetrack/runtime/triton_kernels.py:195-233 and racetrack/fx_patterns.py:116-122."""
+    normed, hidden = fused_residual_norm(update, residual, weight, eps=eps, fallback=fallback)
+    return hidden, normed
+
+
+def fused_rms_norm(x: torch.Tensor, weight: torch.Tensor, *, eps: float,
+                   fallback: Optional[Callable] = None) -> torch.Tensor:
+    """rms_norm(x) * weight; partitions/_base.py:24-28, racetrack/models/deepseek.py:478-483."""
+    del fallback
+    _require_cuda(x, weight)
+    _require_bf16("fused_rms_norm", x)
+    cols = x.shape[-1]
+    x2 = _rows_view(x)
+    w = weight.contiguous()
+    out = torch.empty(x.shape, dtype=x.dtype, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_rms_norm(x2.data_ptr(), w.data_ptr(), _weight_tag(w), out.data_ptr(),
+                               x2.shape[0], cols, x2.stride(0), cols, float(eps), _lib.RT_BF16,
+                               _stream()), "rt_rms_norm")
+    return out
+
+
+# ---------------------------------------------------------------------------
+# MLA prologue
+# ---------------------------------------------------------------------------
+
+_INV_FREQ: dict[tuple, torch.Tensor] = {}
+
+
+def _inv_freq(half: int, base: float, device: torch.device) -> torch.Tensor:
+    """1 / base**(i/half), formed with the same torch ops as
+    partitions/dsv3_2/model.py:39-45 so the angles agree bit for bit."""
+    key = (half, float(base), str(device))
+    t = _INV_FREQ.get(key)
+    if t is None:
+        t = 1.0 / (base ** (torch.arange(0, half, device=device, dtype=torch.float32) / max(half, 1)))
+        _INV_FREQ[key] = t.contiguous()
+        t = _INV_FREQ[key]
+    return t
+
+
+def _freqs_table(freqs_cis: torch.Tensor, half: int) -> torch.Tensor:
+    """[rows, half, 2] fp32 view of a complex64 freqs_cis tensor (no copy when contiguous)."""
+    if not freqs_cis.is_complex():
+        raise RuntimeError("freqs_cis must be a complex tensor")
+    table = torch.view_as_real(freqs_cis.reshape(-1, half).contiguous())
+    if table.dtype != torch.float32:
+        table = table.float()
+    return table
+
+
+def _norm_rope(q_c, q_weight, kv_c, kv_weight, k_pe, positions, table, table_rows, eps, mode):
+    _require_cuda(q_c, kv_c, k_pe, q_weight, kv_weight)
+    for name, t in (("q_c", q_c), ("kv_c", kv_c), ("k_pe", k_pe)):
+        _require_bf16(f"fused_norm_rope {name}", t)
+    q2, kv2, k2 = _rows_view(q_c), _rows_view(kv_c), k_pe.reshape(-1, k_pe.shape[-1])
+    if k2.stride(-1) != 1:
+        k2 = k2.contiguous()
+    tokens = q2.shape[0]
+    if kv2.shape[0] != tokens or k2.shape[0] != tokens:
+        raise RuntimeError("fused_norm_rope: q_c, kv_c and k_pe disagree on the token count")
+    qw, kvw = q_weight.contiguous(), kv_weight.contiguous()
+    if qw.dtype != kvw.dtype:
+        kvw = kvw.to(qw.dtype)
+    q_out = torch.empty(q_c.shape, dtype=q_c.dtype, device=q_c.device)
+    kv_out = torch.empty(kv_c.shape, dtype=kv_c.dtype, device=kv_c.device)
+    k_out = torch.empty(k_pe.shape, dtype=k_pe.dtype, device=k_pe.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_norm_rope(q2.data_ptr(), qw.data_ptr(), kv2.data_ptr(), kvw.data_ptr(),
+                                _weight_tag(qw), k2.data_ptr(),
+                                positions.data_ptr() if positions is not None else None,
+                                table.data_ptr(), table_rows,
+                                q_out.data_ptr(), kv_out.data_ptr(), k_out.data_ptr(),
+                                tokens, q2.shape[1], kv2.shape[1], k2.shape[1],
+                                q2.stride(0), kv2.stride(0), k2.stride(0),
+                                float(eps), mode, _lib.RT_BF16, _stream()), "rt_norm_rope")
+    return q_out, kv_out, k_out
+
+
+def fused_norm_rope(q_c, q_weight, kv_c, kv_weight, k_pe, positions, *, eps: float,
+                    rope_base: float, fallback: Optional[Callable] = None):
+    """(rms_norm(q_c), rms_norm(kv_c), apply_rope(k_pe)) with half-split RoPE.
+
+    Contract of partitions/dsv3_2/model.py:84-99 and its call site :333-344; the three
+    inputs are normally column slices of one [T, q_lora+kv_lora+rope] projection output.
+    """
+    del fallback
+    half = k_pe.shape[-1] // 2
+    pos = positions.reshape(-1)
+    if pos.dtype != torch.int64:
+        pos = pos.to(torch.int64)
+    pos = pos.contiguous()
+    table = _inv_freq(half, rope_base, k_pe.device)
+    return _norm_rope(q_c, q_weight, kv_c, kv_weight, k_pe, pos, table, 0, eps, _lib.RT_ROPE_HALF)
+
+
+def fused_norm_rope_interleaved(q_c, q_weight, kv_c, kv_weight, k_pe, freqs_cis, *, eps: float,
+                                fallback: Optional[Callable] = None):
+    """q_norm / kv_norm / interleaved rotary of k_pe as MLA.forward does them
+    (racetrack/models/deepseek.py:766-776). ``freqs_cis`` is the complex64
+    [seqlen, rope_dim/2] slice for the tokens; rows wrap around per batch element."""
+    del fallback
+    half = k_pe.shape[-1] // 2
+    table = _freqs_table(freqs_cis, half)
+    return _norm_rope(q_c, q_weight, kv_c, kv_weight, k_pe, None, table, table.shape[0], eps,
+                      _lib.RT_ROPE_INTERLEAVED)
+
+
+def _rope_heads(x: torch.Tensor, positions, table, table_rows, mode, inplace: bool):
+    _require_cuda(x)
+    _require_bf16("fused_rope", x)
+    if x.dim() < 2:
+        raise RuntimeError("fused_rope: expected [..., heads, rope_dim]")
+    d = x.shape[-1]
+    heads = x.shape[-2]
+    x3 = x.reshape(-1, heads, d) if x.dim() != 3 else x
+    ok = (x3.stride(2) == 1 and x3.stride(0) % 8 == 0 and x3.stride(1) % 8 == 0
+          and x3.data_ptr() % 16 == 0)
+    if not ok:
+        if inplace:
+            raise RuntimeError("fused_rope: in-place rotation needs a 16-byte aligned strided view")
+        x3 = x3.contiguous()
+    out3 = x3 if inplace else torch.empty((x3.shape[0], heads, d), dtype=x.dtype, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_rope(x3.data_ptr(), positions.data_ptr() if positions is not None else None,
+                           table.data_ptr(), table_rows, out3.data_ptr(),
+                           x3.shape[0], heads, d, x3.stride(0), x3.stride(1),
+                           out3.stride(0), out3.stride(1), mode, _lib.RT_BF16, _stream()),
+               "rt_rope")
+    return x if inplace else out3.view(x.shape)
+
+
+def fused_rope(x: torch.Tensor, freqs_cis: torch.Tensor, *, inplace: bool = False,
+               fallback: Optional[Callable] = None) -> torch.Tensor:
+    """Interleaved rotary embedding of x [batch, seq, heads, rope_dim] (or [seq, heads, rope_dim])
+    by freqs_cis [seq, rope_dim/2]; racetrack/models/deepseek.py:604-624 with interleaved=True
+    (kernel name as in partitions/dsv3_2/3336cdbd/kernels/triton/rope.py:57-62)."""
+    del fallback
+    half = x.shape[-1] // 2
+    table = _freqs_table(freqs_cis, half)
+    return _rope_heads(x, None, table, table.shape[0], _lib.RT_ROPE_INTERLEAVED, inplace)
+
+
+def fused_rope_half(x: torch.Tensor, positions: torch.Tensor, *, rope_base: float = 10000.0,
+                    inplace: bool = False, fallback: Optional[Callable] = None) -> torch.Tensor:
+    """Half-split RoPE of x [tokens, heads, rope_dim] at integer positions;
+    partitions/dsv3_2/model.py:55-81 (apply_rope), racetrack/realistic_bench.py:297-302."""
+    del fallback
+    half = x.shape[-1] // 2
+    pos = positions.reshape(-1).to(torch.int64).contiguous()
+    return _rope_heads(x, pos, _inv_freq(half, rope_base, x.device), 0, _lib.RT_ROPE_HALF, inplace)
+
+
+# ---------------------------------------------------------------------------
+# SwiGLU and activation quantisation
+# ---------------------------------------------------------------------------
+
+def _gate_up(gate: torch.Tensor, up: torch.Tensor, who: str):
+    _require_cuda(gate, up)
+    _require_bf16(who, gate)
+    _require_bf16(who, up)
+    if gate.shape != up.shape:
+        raise RuntimeError(f"{who}: gate and up shapes differ")
+    return _rows_view(gate), _rows_view(up)
+
+
+def fused_swiglu(gate: torch.Tensor, up: torch.Tensor, *,
+                 fallback: Optional[Callable] = None) -> torch.Tensor:
+    """(silu(gate.float()) * up.float()).type_as(gate); racetrack/models/deepseek.py:850-853."""
+    del fallback
+    g2, u2 = _gate_up(gate, up, "fused_swiglu")
+    out = torch.empty(gate.shape, dtype=gate.dtype, device=gate.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_swiglu(g2.data_ptr(), u2.data_ptr(), out.data_ptr(), g2.shape[0],
+                             g2.shape[1], g2.stride(0), u2.stride(0), _lib.RT_BF16, _stream()),
+               "rt_swiglu")
+    return out
+
+
+def fused_act_quant(x: torch.Tensor, *, fallback: Optional[Callable] = None):
+    """FP8 e4m3 codes [..., N] and fp32 scales [..., N/128]; racetrack/models/deepseek.py:85-107."""
+    del fallback
+    _require_cuda(x)
+    _require_bf16("fused_act_quant", x)
+    n = x.shape[-1]
+    if n % 128 != 0:
+        raise RuntimeError(f"fused_act_quant: last dim ({n}) must be a multiple of 128")
+    x2 = _rows_view(x)
+    codes = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty(*x.shape[:-1], n // 128, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_act_quant_fp8(x2.data_ptr(), codes.data_ptr(), scales.data_ptr(),
+                                    x2.shape[0], n, x2.stride(0), _lib.RT_BF16, _stream()),
+               "rt_act_quant_fp8")
+    return codes, scales
+
+
+def fused_swiglu_quant(gate: torch.Tensor, up: torch.Tensor, *,
+                       fallback: Optional[Callable] = None):
+    """act_quant(swiglu(gate, up)) without materialising the bf16 product;
+    benchmarks/gsm8k/flat_decode.py:132-136."""
+    del fallback
+    g2, u2 = _gate_up(gate, up, "fused_swiglu_quant")
+    n = gate.shape[-1]
+    if n % 128 != 0:
+        raise RuntimeError(f"fused_swiglu_quant: last dim ({n}) must be a multiple of 128")
+    codes = torch.empty(gate.shape, dtype=torch.float8_e4m3fn, device=gate.device)
+    scales = torch.empty(*gate.shape[:-1], n // 128, dtype=torch.float32, device=gate.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_swiglu_quant_fp8(g2.data_ptr(), u2.data_ptr(), codes.data_ptr(),
+                                       scales.data_ptr(), g2.shape[0], n, g2.stride(0),
+                                       u2.stride(0), _lib.RT_BF16, _stream()),
+               "rt_swiglu_quant_fp8")
+    return codes, scales
+
+
+def tensor_absmax(x: torch.Tensor, up: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """max(|x|) over the whole tensor as a 1-element fp32 CUDA tensor (of swiglu(x, up)
+    when ``up`` is given). Feeds the NVFP4 global scale."""
+    _require_cuda(x)
+    _require_bf16("tensor_absmax", x)
+    if x.shape[-1] % 16 != 0:
+        raise RuntimeError("tensor_absmax: last dim must be a multiple of 16")
+    x2 = _rows_view(x)
+    u2 = _rows_view(up) if up is not None else None
+    out = torch.empty(1, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_absmax(x2.data_ptr(), u2.data_ptr() if u2 is not None else None,
+                             out.data_ptr(), x2.shape[0], x2.shape[1], x2.stride(0),
+                             u2.stride(0) if u2 is not None else 0, _lib.RT_BF16, _stream()),
+               "rt_absmax")
+    return out
+
+
+def sf_tiled_bytes(rows: int, cols: int) -> int:
+    """Size of a 128x4-tiled NVFP4 block-scale buffer for a [rows, cols] tensor."""
+    return ((rows + 127) // 128) * ((cols // 16 + 3) // 4) * 512
+
+
+def fused_nvfp4_quant(x: torch.Tensor, *, up: Optional[torch.Tensor] = None,
+                      amax: Optional[torch.Tensor] = None, tiled_scales: bool = False,
+                      fallback: Optional[Callable] = None):
+    """NVFP4 quantisation -> (codes uint8 [..., N/2], block_scales float8_e4m3fn, global_scale fp32[1]).
+
+    16-element blocks, e2m1 codes (element 2i in the low nibble), e4m3 block scale and
+    one fp32 global scale = amax / (448 * 6). ``amax`` (1-element fp32 CUDA tensor) skips the
+    abs-max pass when the caller already knows it. With ``up`` the quantised tensor is
+    swiglu(x, up). ``tiled_scales`` selects the 128x4-tiled scale layout the block-scaled
+    tensor-core GEMM consumes; otherwise scales are [..., N/16] row-major.
+    racetrack has no NVFP4 arithmetic; the format follows the build's stated configuration.
+    """
+    del fallback
+    _require_cuda(x)
+    _require_bf16("fused_nvfp4_quant", x)
+    n = x.shape[-1]
+    if n % 16 != 0:
+        raise RuntimeError(f"fused_nvfp4_quant: last dim ({n}) must be a multiple of 16")
+    x2 = _rows_view(x)
+    u2 = None
+    if up is not None:
+        x2, u2 = _gate_up(x, up, "fused_nvfp4_quant")
+    if amax is None:
+        amax = tensor_absmax(x, up)
+    rows = x2.shape[0]
+    codes = torch.empty(*x.shape[:-1], n // 2, dtype=torch.uint8, device=x.device)
+    if tiled_scales:
+        sf = torch.empty(sf_tiled_bytes(rows, n), dtype=torch.uint8, device=x.device)
+    else:
+        sf = torch.empty(*x.shape[:-1], n // 16, dtype=torch.uint8, device=x.device)
+    gs = torch.empty(1, dtype=torch.float32, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_nvfp4_quant(x2.data_ptr(), u2.data_ptr() if u2 is not None else None,
+                                  amax.data_ptr(), codes.data_ptr(), sf.data_ptr(), gs.data_ptr(),
+                                  rows, n, x2.stride(0), u2.stride(0) if u2 is not None else 0,
+                                  _lib.RT_SF_TILED128x4 if tiled_scales else _lib.RT_SF_ROWMAJOR,
+                                  _lib.RT_BF16, _stream()), "rt_nvfp4_quant")
+    return codes, sf.view(torch.float8_e4m3fn), gs
+
+
+def fused_swiglu_nvfp4_quant(gate: torch.Tensor, up: torch.Tensor, **kw):
+    """fused_nvfp4_quant of swiglu(gate, up)."""
+    return fused_nvfp4_quant(gate, up=up, **kw)
+
+
+# ---------------------------------------------------------------------------
+# MoE routing / permutation / combine
+# ---------------------------------------------------------------------------
+
+def fused_moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], *, n_groups: int,
+                    topk_groups: int, topk: int, route_scale: float,
+                    score_func: str = "sigmoid", fallback: Optional[Callable] = None):
+    """(weights fp32 [T, topk], indices int64 [T, topk]) from fp32 router logits [T, E];
+    everything in Gate.forward after the logits GEMM (racetrack/models/deepseek.py:899-920)."""
+    del fallback
+    _require_cuda(logits)
+    if logits.dtype != torch.float32 or logits.dim() != 2:
+        raise RuntimeError("fused_moe_route: logits must be a 2-D float32 tensor")
+    if logits.stride(1) != 1:
+        logits = logits.contiguous()
+    if bias is not None:
+        bias = bias.to(torch.float32).contiguous()
+    tokens, n_experts = logits.shape
+    weights = torch.empty(tokens, topk, dtype=torch.float32, device=logits.device)
+    indices = torch.empty(tokens, topk, dtype=torch.int64, device=logits.device)
+    func = {"sigmoid": _lib.RT_SCORE_SIGMOID, "softmax": _lib.RT_SCORE_SOFTMAX}[score_func]
+    lib = _lib.load()
+    _lib.check(lib.rt_moe_route(logits.data_ptr(), bias.data_ptr() if bias is not None else None,
+                                weights.data_ptr(), indices.data_ptr(), tokens, n_experts,
+                                logits.stride(0), n_groups, topk_groups, topk, float(route_scale),
+                                func, _stream()), "rt_moe_route")
+    return weights, indices
+
+
+def fused_moe_permute(indices: torch.Tensor, n_experts: int):
+    """Stable sort of (token, slot) pairs by expert ->
+    (expert_offsets int32 [E+1], sorted_pairs int32 [T*topk], pair_pos int32 [T*topk]);
+    replaces bincount + per-expert torch.where of racetrack/models/deepseek.py:1011-1017."""
+    _require_cuda(indices)
+    if indices.dtype != torch.int64 or indices.dim() != 2:
+        raise RuntimeError("fused_moe_permute: indices must be a 2-D int64 tensor")
+    indices = indices.contiguous()
+    tokens, topk = indices.shape
+    dev = indices.device
+    lib = _lib.load()
+    ws_bytes = int(lib.rt_moe_permute_workspace_bytes(tokens, topk, n_experts))
+    workspace = torch.empty(max(ws_bytes, 4), dtype=torch.uint8, device=dev)
+    offsets = torch.empty(n_experts + 1, dtype=torch.int32, device=dev)
+    sorted_pairs = torch.empty(tokens * topk, dtype=torch.int32, device=dev)
+    pair_pos = torch.empty(tokens * topk, dtype=torch.int32, device=dev)
+    _lib.check(lib.rt_moe_permute(indices.data_ptr(), offsets.data_ptr(), sorted_pairs.data_ptr(),
+                                  pair_pos.data_ptr(), workspace.data_ptr(), tokens, topk,
+                                  n_experts, _stream()), "rt_moe_permute")
+    return offsets, sorted_pairs, pair_pos
+
+
+def fused_moe_gather(x: torch.Tensor, sorted_pairs: torch.Tensor, topk: int) -> torch.Tensor:
+    """x[sorted_pairs // topk] -> [T*topk, cols]; the x[idx] gathers of deepseek.py:1017."""
+    _require_cuda(x, sorted_pairs)
+    _require_bf16("fused_moe_gather", x)
+    x2 = _rows_view(x)
+    n_pairs = sorted_pairs.numel()
+    out = torch.empty(n_pairs, x2.shape[1], dtype=x.dtype, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_moe_gather(x2.data_ptr(), sorted_pairs.data_ptr(), out.data_ptr(), n_pairs,
+                                 topk, x2.shape[1], x2.stride(0), _lib.RT_BF16, _stream()),
+               "rt_moe_gather")
+    return out
+
+
+def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor,
+                      shared: Optional[torch.Tensor] = None, *, pos_begin: int = 0,
+                      pos_end: Optional[int] = None) -> torch.Tensor:
+    """y[t] = sum_s weights[t, s] * expert_out[pair_pos[t, s]] (+ shared[t]);
+    racetrack/models/deepseek.py:1018-1022."""
+    _require_cuda(expert_out, pair_pos, weights)
+    _require_bf16("fused_moe_combine", expert_out)
+    tokens, topk = weights.shape
+    cols = expert_out.shape[-1]
+    expert_out = expert_out.contiguous()
+    weights = weights.to(torch.float32).contiguous()
+    if shared is not None:
+        _require_bf16("fused_moe_combine", shared)
+        shared = shared.reshape(tokens, cols).contiguous()
+    if pos_end is None:
+        pos_end = tokens * topk
+    y = torch.empty(tokens, cols, dtype=expert_out.dtype, device=expert_out.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_moe_combine(expert_out.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(),
+                                  shared.data_ptr() if shared is not None else None, y.data_ptr(),
+                                  tokens, topk, cols, pos_begin, pos_end, _lib.RT_BF16, _stream()),
+               "rt_moe_combine")
+    return y

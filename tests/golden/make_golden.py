@@ -1,0 +1,171 @@
+"""Generates the golden fixtures in this directory by running racetrack itself.
+
+Run where the reference checkout is available:
+
+    python tests/golden/make_golden.py --reference /path/to/racetrack
+
+It imports the reference's own vanilla-torch functions (CPU), feeds them the seeded inputs
+of oracle/inputs.py and writes
+  * golden_small.pt    - input-free output tensors of small cases (inputs are regenerated
+                         from their seeds by the tests), a few hundred KB;
+  * golden_hashes.json - SHA-256 of the reference outputs at full hot-path sizes, plus the
+                         torch version / CPU capability they were produced with.
+The fixtures only ever travel as data: nothing at test time imports the reference.
+"""
+from __future__ import annotations
+
+import argparse
+import hashlib
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+HERE = Path(__file__).resolve().parent
+ROOT = HERE.parent.parent
+sys.path.insert(0, str(ROOT))
+
+from oracle import inputs as I  # noqa: E402
+
+
+def sha(t: torch.Tensor) -> str:
+    t = t.detach().contiguous()
+    if t.dtype in (torch.bfloat16, torch.float8_e4m3fn):
+        raw = t.view(torch.uint8 if t.element_size() == 1 else torch.int16)
+    else:
+        raw = t
+    return hashlib.sha256(raw.numpy().tobytes()).hexdigest()
+
+
+def main() -> None:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--reference", default="/root/reference")
+    args = ap.parse_args()
+    sys.path.insert(0, args.reference)
+
+    from racetrack.models import deepseek as rm          # noqa: E402
+    from partitions import _base as rbase                 # noqa: E402
+    from partitions.dsv3_2 import model as rsyn           # noqa: E402
+
+    torch.manual_seed(0)
+    small: dict[str, torch.Tensor] = {}
+    hashes: dict[str, str] = {}
+
+    # ---- fused MLA prologue, T=128 full width (hashes) and T=8 (tensors) ----
+    for tag, tokens in (("c1", 128), ("c1_small", 4)):
+        d = I.mla_prologue_inputs(tokens)
+        norm = rm.RMSNorm(I.HIDDEN)
+        with torch.no_grad():
+            norm.weight.copy_(d["w_attn"])
+            normed, hidden = norm(d["x"], d["residual"])
+            qn = rbase.rms_norm(d["q_c"], d["w_q"], d["eps"])
+            kvn = rbase.rms_norm(d["kv_c"], d["w_kv"], d["eps"])
+            qn2 = rm.RMSNorm(I.Q_LORA)
+            qn2.weight.copy_(d["w_q"])
+            qn_real = qn2(d["q_c"])
+            margs = rm.ModelArgs(max_seq_len=tokens, qk_rope_head_dim=I.ROPE_DIM,
+                                 rope_theta=d["rope_theta"])
+            freqs = rm.precompute_freqs_cis(margs)
+            q_rot = rm.apply_rotary_emb(d["q_pe"].unsqueeze(0), freqs).squeeze(0)
+            k_rot = rm.apply_rotary_emb(d["k_pe"].unsqueeze(0).unsqueeze(2), freqs).squeeze(0)
+            k_rot_noninter = rm.apply_rotary_emb(d["k_pe"].unsqueeze(0).unsqueeze(2).contiguous(),
+                                                 freqs, False).squeeze(0)
+            fq, fkv, fk = rsyn.fused_norm_rope(d["q_c"], d["w_q"], d["kv_c"], d["w_kv"], d["k_pe"],
+                                               d["positions"], eps=d["eps"],
+                                               rope_base=d["rope_theta"])
+            q_half = rsyn.apply_rope(d["q_pe"], d["positions"], base=d["rope_theta"])
+        outs = {"normed": normed, "hidden": hidden, "q_norm": qn, "kv_norm": kvn,
+                "q_norm_real": qn_real, "freqs_cis": torch.view_as_real(freqs),
+                "q_rot": q_rot, "k_rot": k_rot, "k_rot_noninterleaved": k_rot_noninter,
+                "fused_q": fq, "fused_kv": fkv, "fused_k": fk, "q_half": q_half}
+        for k, v in outs.items():
+            hashes[f"{tag}.{k}"] = sha(v)
+            if tag == "c1_small":
+                small[f"{tag}.{k}"] = v.clone()
+
+    # ---- YaRN table beyond the original sequence length ----
+    margs = rm.ModelArgs(max_seq_len=8192, qk_rope_head_dim=I.ROPE_DIM)
+    freqs = rm.precompute_freqs_cis(margs)
+    hashes["yarn8192.freqs_cis"] = sha(torch.view_as_real(freqs))
+    small["yarn8192.freqs_cis_rows"] = torch.view_as_real(freqs)[[0, 1, 4095, 4096, 8191]].clone()
+
+    # ---- SwiGLU / FP8 quant ----
+    for tag, tokens, inter in (("c2_small", 16, 512), ("c2_mid", 64, I.DENSE_INTER)):
+        d = I.swiglu_quant_inputs(tokens, inter)
+        h = (torch.nn.functional.silu(d["gate"].float()) * d["up"].float()).type_as(d["gate"])
+        codes, scales = rm.act_quant(d["gate"].contiguous())
+        hcodes, hscales = rm.act_quant(h)
+        outs = {"swiglu": h, "codes": codes, "scales": scales, "h_codes": hcodes,
+                "h_scales": hscales}
+        for k, v in outs.items():
+            hashes[f"{tag}.{k}"] = sha(v)
+            if tag == "c2_small":
+                small[f"{tag}.{k}"] = v.clone()
+    # MLP module end to end (bf16 weights) on a tiny shape
+    mlp = rm.MLP(64, 128)
+    w = I.expert_weights(1, 64, 128, seed=I.SEED + 7)[0]
+    with torch.no_grad():
+        mlp.w1.weight.copy_(w[0]); mlp.w2.weight.copy_(w[1]); mlp.w3.weight.copy_(w[2])
+        x = I.randn((8, 64), I.SEED + 8)
+        small["mlp_small.out"] = mlp(x).clone()
+
+    # ---- FP8 block-scaled GEMM fallback ----
+    a = I.randn((16, 256), I.SEED + 31)
+    wfp = I.randn((384, 256), I.SEED + 32, std=0.02, dtype=torch.float32)
+    wq = wfp.clamp(-448, 448).to(torch.float8_e4m3fn)
+    ws = I.uniform((3, 2), I.SEED + 33, 0.5, 1.5)
+    a_q, a_s = rm.act_quant(a)
+    small["fp8_gemm.out"] = rm.fp8_gemm(a_q, a_s, wq, ws).clone()
+    small["fp8_gemm.dequant"] = rm._block_dequant(wq, ws).clone()
+
+    # ---- Gate (dim 7168 -> bias branch), 64 tokens; and a small softmax gate ----
+    d = I.gate_inputs(64)
+    margs = rm.ModelArgs(dim=I.HIDDEN, n_routed_experts=I.N_EXPERTS, n_activated_experts=I.TOPK,
+                         n_expert_groups=I.N_GROUPS, n_limited_groups=I.TOPK_GROUPS,
+                         score_func="sigmoid", route_scale=I.ROUTE_SCALE)
+    gate = rm.Gate(margs)
+    with torch.no_grad():
+        gate.weight.copy_(d["w_gate"])
+        gate.bias.copy_(d["bias"])
+        gw, gi = gate(d["hidden"])
+    small["gate.weights"], small["gate.indices"] = gw.clone(), gi.clone()
+    margs = rm.ModelArgs(dim=64, n_routed_experts=8, n_activated_experts=2, score_func="softmax")
+    gate = rm.Gate(margs)
+    with torch.no_grad():
+        gate.weight.copy_(I.randn((8, 64), I.SEED + 41, std=0.2))
+        gw, gi = gate(I.randn((32, 64), I.SEED + 42))
+    small["gate_softmax.weights"], small["gate_softmax.indices"] = gw.clone(), gi.clone()
+
+    # ---- MoE forward: dim 7168 (bias), 16 experts in 4 groups, top-4, one shared expert ----
+    margs = rm.ModelArgs(dim=I.HIDDEN, moe_inter_dim=64, n_routed_experts=16, n_shared_experts=1,
+                         n_activated_experts=4, n_expert_groups=4, n_limited_groups=2,
+                         score_func="sigmoid", route_scale=I.ROUTE_SCALE)
+    moe = rm.MoE(margs)
+    ew = I.expert_weights(17, I.HIDDEN, 64, seed=I.SEED + 50)
+    with torch.no_grad():
+        moe.gate.weight.copy_(I.randn((16, I.HIDDEN), I.SEED + 51, std=0.02))
+        moe.gate.bias.copy_(I.uniform((16,), I.SEED + 52, -0.1, 0.1))
+        for e in range(16):
+            moe.experts[e].w1.weight.copy_(ew[e][0])
+            moe.experts[e].w2.weight.copy_(ew[e][1])
+            moe.experts[e].w3.weight.copy_(ew[e][2])
+        moe.shared_experts.w1.weight.copy_(ew[16][0])
+        moe.shared_experts.w2.weight.copy_(ew[16][1])
+        moe.shared_experts.w3.weight.copy_(ew[16][2])
+        x = I.randn((32, I.HIDDEN), I.SEED + 53)
+        y = moe(x)
+    small["moe.out_cols0_256"] = y[:, :256].clone()
+    hashes["moe.out"] = sha(y)
+
+    meta = {"torch": torch.__version__, "cpu_capability": torch.backends.cpu.get_cpu_capability(),
+            "threads": torch.get_num_threads()}
+    torch.save(small, HERE / "golden_small.pt")
+    (HERE / "golden_hashes.json").write_text(json.dumps({"meta": meta, "sha256": hashes}, indent=1,
+                                                        sort_keys=True) + "\n")
+    size = (HERE / "golden_small.pt").stat().st_size
+    print(f"wrote {len(small)} tensors ({size/1024:.0f} KiB) and {len(hashes)} hashes; meta={meta}")
+
+
+if __name__ == "__main__":
+    main()
