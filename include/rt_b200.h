@@ -271,6 +271,63 @@ int rt_moe_combine(const void* expert_out, const int32_t* pair_pos, const float*
                    int64_t pos_begin, int64_t pos_end,
                    int dtype, void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* Tensor-core GEMMs (tcgen05 + TMA + tensor memory)                          */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * c[m, n] = a[m, k] * b[n, k]^T, bf16 inputs, fp32 accumulation in tensor memory, bf16
+ * output: y = F.linear(x, weight) with x = a and weight = b. lda / ldb / ldc are row
+ * pitches in elements. k, n and the pitches must be multiples of 8, pointers 16-byte aligned.
+ * ref: racetrack/models/deepseek.py:341-342 (bf16 branch of linear()),
+ *      racetrack/realistic_bench.py:288,295,307,315 (F.linear of the MLA projections).
+ */
+int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
+                 int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+
+/*
+ * Work list of the grouped GEMM, built on the device from the per-expert row offsets
+ * that rt_moe_permute wrote (no host synchronisation). For groups g in [g_begin, g_end),
+ * rows [offsets[g], offsets[g+1]) are cut into m-tiles of 128 rows:
+ *   tile_map   int32 [max_tiles, 4], 16-byte aligned: {g - g_begin, first row, valid rows,
+ *              scale row-tile index}; the scale row-tile index equals the tile's own index,
+ *              so every group starts on a 128-row scale-tile boundary
+ *   tile_base  int32 [g_end - g_begin + 1]: index of each group's first tile; last = total
+ *   tile_count int32 [1]: number of tiles written (clamped to max_tiles)
+ * max_tiles >= ceil(rows/128) + number of groups is always enough.
+ * ref: racetrack/models/deepseek.py:1012-1017 (the per-expert loop bounds this replaces).
+ */
+int rt_moe_tile_map(const int32_t* offsets, int64_t g_begin, int64_t g_end,
+                    int32_t* tile_map, int32_t* tile_base, int32_t* tile_count,
+                    int64_t max_tiles, void* stream);
+
+/*
+ * Block-scaled NVFP4 grouped GEMM on tcgen05 (kind::mxf4nvf4, scale factors in tensor memory):
+ *   c[rows of tile t, :] = a_gs[0] * b_gs[g] * dequant(a)[rows] * dequant(b_g)^T,  g = tile group
+ * a_codes [total_rows, k/2] e2m1 pairs (even element in the low nibble), rows grouped as the
+ * tile map says; a_sf: e4m3 block scales (16 elements) in the RT_SF_TILED128x4 layout, row tile
+ * = the tile map's scale row-tile index; b_codes [groups * n, k/2] and b_sf (each group tiled
+ * on its own, ceil(n/128) row tiles per group) hold the weights; a_gs / b_gs [groups] are the
+ * fp32 global scales (device memory). c is bf16 [total_rows, n] with row pitch ldc.
+ * With groups == 1 and a tile map over [0, m) this is a dense NVFP4 linear layer.
+ * k % 256 == 0, n % 8 == 0 (n % 128 == 0 when groups > 1).
+ * ref: racetrack/models/deepseek.py:1013-1018 (expert(x[idx]) per routed expert),
+ *      racetrack/realistic_bench.py:338-346 (gathered-weight bmm it replaces). The NVFP4
+ *      arithmetic itself has no counterpart in racetrack.
+ */
+int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* a_gs,
+                          const void* b_codes, const void* b_sf, const float* b_gs,
+                          void* c, const int32_t* tile_map, const int32_t* tile_count,
+                          int64_t max_m_tiles, int64_t total_rows, int64_t groups,
+                          int64_t n, int64_t k, int64_t ldc, void* stream);
+
+/*
+ * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when
+ * one of its bounded waits expired. RT_OK when no kernel gave up since the last call,
+ * RT_ERR_TIMEOUT otherwise. Call after synchronising the stream; not graph-capturable.
+ */
+int rt_tc_error_state(void);
+
 #ifdef __cplusplus
 }
 #endif

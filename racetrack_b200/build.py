@@ -26,6 +26,7 @@ SOURCES = {
     "rt_norm.cu": ["-fmad=false"],
     "rt_act.cu": ["-fmad=false"],
     "rt_moe.cu": ["-fmad=false"],
+    "rt_gemm.cu": [],
 }
 
 COMMON = [

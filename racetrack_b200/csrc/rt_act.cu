@@ -123,8 +123,9 @@ __global__ void __launch_bounds__(kActThreads) quant_fp8_kernel(
         float q[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
+            // no explicit clamp: the saturating conversion maps |q| > 448 to +-448,
+            // which is what clamp(-448, 448) followed by a cast yields
             q[j] = div_shared(v[4 * k + j], scale, rscale);
-            q[j] = fminf(fmaxf(q[j], -448.0f), 448.0f);
         }
         w[k] = cvt_e4m3x2(q[0], q[1]) | (cvt_e4m3x2(q[2], q[3]) << 16);
     }
@@ -167,14 +168,14 @@ __global__ void __launch_bounds__(kActThreads) absmax_kernel(
 // NVFP4: e2m1 codes, e4m3 scale per 16-element block, fp32 global scale
 // ---------------------------------------------------------------------------
 
-// Nearest-even rounding of |v| onto the e2m1 grid {0, .5, 1, 1.5, 2, 3, 4, 6}:
-// the code is the number of rounding thresholds passed; a threshold that is a tie
-// belongs to the even code, hence the mix of > and >=.
-__device__ __forceinline__ uint32_t e2m1_code(float v) {
-    const float a = fabsf(v);
-    uint32_t c = (a > 0.25f) + (a >= 0.75f) + (a > 1.25f) + (a >= 1.75f) + (a > 2.5f) +
-                 (a >= 3.5f) + (a > 5.0f);
-    return c | ((__float_as_uint(v) >> 28) & 8u);
+// Two fp32 -> two e2m1 codes in one byte (`lo` in the low nibble): round to nearest
+// even onto {0, .5, 1, 1.5, 2, 3, 4, 6}, saturating, sign kept (also for zero).
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float lo, float hi) {
+    uint16_t d;
+    asm("{ .reg .b8 t; cvt.rn.satfinite.e2m1x2.f32 t, %1, %2; mov.b16 %0, {t, 0}; }"
+        : "=h"(d)
+        : "f"(hi), "f"(lo));
+    return d;
 }
 
 __device__ __forceinline__ int64_t sf_offset(int layout, int64_t row, int64_t blk,
@@ -209,9 +210,9 @@ __global__ void __launch_bounds__(kActThreads) quant_nvfp4_kernel(
     if (denom > 0.f) {
         const float inv = __frcp_rn(denom);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            lo |= e2m1_code(__fmul_rn(v[k], inv)) << (4 * k);
-            hi |= e2m1_code(__fmul_rn(v[8 + k], inv)) << (4 * k);
+        for (int k = 0; k < 4; ++k) {
+            lo |= cvt_e2m1x2(__fmul_rn(v[2 * k], inv), __fmul_rn(v[2 * k + 1], inv)) << (8 * k);
+            hi |= cvt_e2m1x2(__fmul_rn(v[8 + 2 * k], inv), __fmul_rn(v[9 + 2 * k], inv)) << (8 * k);
         }
     }
     st_stream8(codes + static_cast<int64_t>(row) * (cols >> 1) + (col >> 1), make_uint2(lo, hi));
@@ -233,9 +234,9 @@ __global__ void sf_pad_kernel(uint8_t* __restrict__ sf, int64_t rows, int64_t nb
 static int check_stream_args(const char* who, const void* x, int64_t rows, int64_t cols,
                              int64_t xstride, int64_t mult, int dtype, uint32_t& items,
                              uint32_t& per_row, int64_t item_cols) {
-    RT_REQUIRE(x, RT_ERR_BAD_ARG, "%s: null pointer", who);
     RT_REQUIRE(rows >= 0 && cols > 0, RT_ERR_BAD_ARG, "%s: bad shape %lld x %lld", who,
                (long long)rows, (long long)cols);
+    RT_REQUIRE(x || rows == 0, RT_ERR_BAD_ARG, "%s: null pointer", who);
     RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "%s: only bf16 activations", who);
     RT_REQUIRE(cols % mult == 0, RT_ERR_UNSUPPORTED, "%s: cols %lld must be a multiple of %lld",
                who, (long long)cols, (long long)mult);
@@ -259,6 +260,7 @@ extern "C" int rt_swiglu(const void* gate, const void* up, void* out, int64_t ro
     if (int rc = check_stream_args("rt_swiglu", gate, rows, cols, gate_stride, 8, dtype, items,
                                    per_row, 8))
         return rc;
+    if (items == 0) return RT_OK;
     RT_REQUIRE(up && out, RT_ERR_BAD_ARG, "rt_swiglu: null pointer");
     RT_REQUIRE(up_stride % 8 == 0 && aligned16(up) && aligned16(out), RT_ERR_UNSUPPORTED,
                "rt_swiglu: up/out must be 16-byte aligned with stride %% 8 == 0");
@@ -277,6 +279,7 @@ static int quant_fp8_common(const char* who, const void* x, const void* up, void
     uint32_t items, per_row;
     if (int rc = check_stream_args(who, x, rows, cols, x_stride, 128, dtype, items, per_row, kItem))
         return rc;
+    if (items == 0) return RT_OK;
     RT_REQUIRE(codes && scales, RT_ERR_BAD_ARG, "%s: null output pointer", who);
     RT_REQUIRE(aligned16(codes), RT_ERR_UNSUPPORTED, "%s: codes must be 16-byte aligned", who);
     if (up) RT_REQUIRE(up_stride % 8 == 0 && aligned16(up), RT_ERR_UNSUPPORTED,
@@ -345,6 +348,7 @@ extern "C" int rt_nvfp4_quant(const void* x, const void* up, const float* amax_i
     if (int rc = check_stream_args("rt_nvfp4_quant", x, rows, cols, x_stride, 16, dtype, items,
                                    per_row, kItem))
         return rc;
+    if (items == 0) return RT_OK;
     RT_REQUIRE(amax_in && codes && block_scales, RT_ERR_BAD_ARG, "rt_nvfp4_quant: null pointer");
     RT_REQUIRE(sf_layout == RT_SF_ROWMAJOR || sf_layout == RT_SF_TILED128x4, RT_ERR_BAD_ARG,
                "rt_nvfp4_quant: bad sf_layout %d", sf_layout);

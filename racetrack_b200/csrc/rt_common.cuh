@@ -165,10 +165,13 @@ __device__ __forceinline__ float swiglu_f32(float g, float u) {
 // multiplication, an exact remainder and one fused correction give the IEEE
 // quotient (Markstein's division theorem); all operands here stay far away
 // from the underflow/overflow thresholds where the remainder stops being exact.
+// b must be positive: the sign of the quotient is then the sign of a, which is copied
+// onto the result because the correction step would turn a/b = -0 into +0.
 __device__ __forceinline__ float div_shared(float a, float b, float rb) {
     const float q = __fmul_rn(a, rb);
     const float r = __fmaf_rn(-q, b, a);
-    return __fmaf_rn(r, rb, q);
+    const float c = __fmaf_rn(r, rb, q);
+    return __uint_as_float((__float_as_uint(c) & 0x7fffffffu) | (__float_as_uint(a) & 0x80000000u));
 }
 
 #endif  // __CUDACC__

@@ -310,10 +310,11 @@ extern "C" int rt_residual_norm(const void* update, const void* residual, const 
                                 int weight_dtype, void* normed, void* hidden, int64_t rows,
                                 int64_t cols, int64_t update_stride, int64_t residual_stride,
                                 float eps, int dtype, void* stream) {
-    RT_REQUIRE(update && residual && weight && normed && hidden, RT_ERR_BAD_ARG,
-               "rt_residual_norm: null pointer");
     RT_REQUIRE(rows >= 0 && cols > 0, RT_ERR_BAD_ARG, "rt_residual_norm: bad shape %lld x %lld",
                (long long)rows, (long long)cols);
+    if (rows == 0) return RT_OK;
+    RT_REQUIRE(update && residual && weight && normed && hidden, RT_ERR_BAD_ARG,
+               "rt_residual_norm: null pointer");
     RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_residual_norm: only bf16 activations");
     RT_REQUIRE(weight_dtype == RT_BF16 || weight_dtype == RT_F32, RT_ERR_UNSUPPORTED,
                "rt_residual_norm: weight dtype must be bf16 or f32");
@@ -356,8 +357,9 @@ extern "C" int rt_residual_norm(const void* update, const void* residual, const 
 extern "C" int rt_rms_norm(const void* x, const void* weight, int weight_dtype, void* out,
                            int64_t rows, int64_t cols, int64_t x_stride, int64_t out_stride,
                            float eps, int dtype, void* stream) {
-    RT_REQUIRE(x && weight && out, RT_ERR_BAD_ARG, "rt_rms_norm: null pointer");
     RT_REQUIRE(rows >= 0 && cols > 0, RT_ERR_BAD_ARG, "rt_rms_norm: bad shape");
+    if (rows == 0) return RT_OK;
+    RT_REQUIRE(x && weight && out, RT_ERR_BAD_ARG, "rt_rms_norm: null pointer");
     RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_rms_norm: only bf16 activations");
     RT_REQUIRE(weight_dtype == RT_BF16 || weight_dtype == RT_F32, RT_ERR_UNSUPPORTED,
                "rt_rms_norm: weight dtype must be bf16 or f32");
@@ -415,9 +417,10 @@ extern "C" int rt_norm_rope(const void* q_c, const void* q_weight, const void* k
                             void* q_out, void* kv_out, void* k_out, int64_t tokens, int64_t q_cols,
                             int64_t kv_cols, int64_t rope_dim, int64_t q_stride, int64_t kv_stride,
                             int64_t k_stride, float eps, int rope_mode, int dtype, void* stream) {
+    RT_REQUIRE(tokens >= 0 && q_cols > 0 && kv_cols > 0, RT_ERR_BAD_ARG, "rt_norm_rope: bad shape");
+    if (tokens == 0) return RT_OK;
     RT_REQUIRE(q_c && q_weight && kv_c && kv_weight && k_pe && q_out && kv_out && k_out,
                RT_ERR_BAD_ARG, "rt_norm_rope: null pointer");
-    RT_REQUIRE(tokens >= 0 && q_cols > 0 && kv_cols > 0, RT_ERR_BAD_ARG, "rt_norm_rope: bad shape");
     RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_norm_rope: only bf16 activations");
     RT_REQUIRE(weight_dtype == RT_BF16 || weight_dtype == RT_F32, RT_ERR_UNSUPPORTED,
                "rt_norm_rope: weight dtype must be bf16 or f32");
@@ -467,8 +470,9 @@ extern "C" int rt_rope(const void* x, const int64_t* positions, const float* tab
                        int64_t rope_dim, int64_t token_stride, int64_t head_stride,
                        int64_t out_token_stride, int64_t out_head_stride, int rope_mode, int dtype,
                        void* stream) {
-    RT_REQUIRE(x && out, RT_ERR_BAD_ARG, "rt_rope: null pointer");
     RT_REQUIRE(tokens >= 0 && heads > 0, RT_ERR_BAD_ARG, "rt_rope: bad shape");
+    if (tokens == 0) return RT_OK;
+    RT_REQUIRE(x && out, RT_ERR_BAD_ARG, "rt_rope: null pointer");
     RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_rope: only bf16 activations");
     if (int rc = check_rope_args("rt_rope", positions, table, table_rows, rope_dim, rope_mode))
         return rc;

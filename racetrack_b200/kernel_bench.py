@@ -5,7 +5,7 @@
 Same role as racetrack's scripts/benchmark_kernel.py (shapes + byte formulas + median of
 CUDA-event timings), for the sm_100a kernels of this package. Bytes are ALGORITHMIC bytes:
 every input element read once, every output element written once. L2 (126 MB) is flushed
-between timed iterations by overwriting a 512 MB buffer, so small working sets cannot hide
+between timed iterations by reading a 512 MB buffer, so small working sets cannot hide
 in cache.
 """
 from __future__ import annotations
@@ -37,11 +37,14 @@ def hbm_peak_gbs() -> tuple[float, str]:
 
 
 class L2Flusher:
+    """Evicts L2 by READING a buffer four times its size. (Overwriting a buffer instead
+    would leave L2 full of dirty lines whose write-back lands in the next kernel's time.)"""
+
     def __init__(self, nbytes: int = 512 << 20):
-        self.buf = torch.empty(nbytes, dtype=torch.uint8, device="cuda")
+        self.buf = torch.zeros(nbytes // 4, dtype=torch.int32, device="cuda")
 
     def __call__(self) -> None:
-        self.buf.fill_(1)
+        self.buf.sum()
 
 
 def time_kernel(fn: Callable[[], object], *, warmup: int = 5, iters: int = 20,

@@ -123,13 +123,15 @@ _INV_FREQ: dict[tuple, torch.Tensor] = {}
 
 def _inv_freq(half: int, base: float, device: torch.device) -> torch.Tensor:
     """1 / base**(i/half), formed with the same torch ops as
-    partitions/dsv3_2/model.py:39-45 so the angles agree bit for bit."""
+    partitions/dsv3_2/model.py:39-45. The table is evaluated once on the host (powf differs
+    by an ulp between host and device libraries, and a one-ulp frequency error grows with
+    the position) and cached on the device."""
     key = (half, float(base), str(device))
     t = _INV_FREQ.get(key)
     if t is None:
-        t = 1.0 / (base ** (torch.arange(0, half, device=device, dtype=torch.float32) / max(half, 1)))
-        _INV_FREQ[key] = t.contiguous()
-        t = _INV_FREQ[key]
+        host = 1.0 / (base ** (torch.arange(0, half, dtype=torch.float32) / max(half, 1)))
+        t = host.to(device).contiguous()
+        _INV_FREQ[key] = t
     return t
 
 
@@ -464,3 +466,98 @@ def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights:
                                   tokens, topk, cols, pos_begin, pos_end, _lib.RT_BF16, _stream()),
                "rt_moe_combine")
     return y
+
+
+# ---------------------------------------------------------------------------
+# tensor-core GEMMs
+# ---------------------------------------------------------------------------
+
+def tc_error_state() -> None:
+    """Synchronises the device and raises if a tensor-core kernel abandoned a bounded wait."""
+    torch.cuda.synchronize()
+    _lib.check(_lib.load().rt_tc_error_state(), "tensor-core kernel")
+
+
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """F.linear(x, weight) for bf16 x [..., K] and weight [N, K] on the tcgen05 tensor cores
+    (the bf16 branch of racetrack/models/deepseek.py:316-345 `linear`)."""
+    _require_cuda(x, weight)
+    _require_bf16("linear_bf16 x", x)
+    _require_bf16("linear_bf16 weight", weight)
+    k = x.shape[-1]
+    if weight.dim() != 2 or weight.shape[1] != k:
+        raise RuntimeError("linear_bf16: weight must be [N, K] with K matching x")
+    x2 = _rows_view(x)
+    w = weight if (weight.stride(1) == 1 and weight.stride(0) % 8 == 0
+                   and weight.data_ptr() % 16 == 0) else weight.contiguous()
+    n = w.shape[0]
+    out = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_gemm_bf16(x2.data_ptr(), w.data_ptr(), out.data_ptr(), x2.shape[0], n, k,
+                                x2.stride(0), w.stride(0), n, _stream()), "rt_gemm_bf16")
+    return out
+
+
+def moe_tile_map(offsets: torch.Tensor, g_begin: int, g_end: int, max_tiles: int):
+    """Device-side work list of the grouped GEMM for groups [g_begin, g_end) of the row
+    offsets written by fused_moe_permute -> (tile_map int32 [max_tiles, 4], tile_base
+    int32 [groups + 1], tile_count int32 [1]). No host synchronisation."""
+    _require_cuda(offsets)
+    if offsets.dtype != torch.int32:
+        raise RuntimeError("moe_tile_map: offsets must be int32")
+    dev = offsets.device
+    tile_map = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
+    tile_base = torch.empty(g_end - g_begin + 1, dtype=torch.int32, device=dev)
+    tile_count = torch.empty(1, dtype=torch.int32, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.rt_moe_tile_map(offsets.data_ptr(), g_begin, g_end, tile_map.data_ptr(),
+                                   tile_base.data_ptr(), tile_count.data_ptr(), max_tiles,
+                                   _stream()), "rt_moe_tile_map")
+    return tile_map, tile_base, tile_count
+
+
+def gemm_nvfp4_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, a_gs: torch.Tensor,
+                       b_codes: torch.Tensor, b_sf: torch.Tensor, b_gs: torch.Tensor,
+                       tile_map: torch.Tensor, tile_count: torch.Tensor, *, n: int,
+                       groups: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Block-scaled NVFP4 grouped GEMM (see rt_gemm_nvfp4_grouped in include/rt_b200.h).
+
+    a_codes uint8 [rows, K/2]; a_sf tiled e4m3 scales (bytes); a_gs fp32 [1];
+    b_codes uint8 [groups * n, K/2]; b_sf tiled scales per group; b_gs fp32 [groups].
+    Returns bf16 [rows, n]; rows outside every tile are left untouched."""
+    _require_cuda(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, tile_map, tile_count)
+    rows, kh = a_codes.shape
+    if b_codes.shape != (groups * n, kh):
+        raise RuntimeError("gemm_nvfp4_grouped: b_codes must be [groups * n, K/2]")
+    if not (a_codes.is_contiguous() and b_codes.is_contiguous()):
+        raise RuntimeError("gemm_nvfp4_grouped: code tensors must be contiguous")
+    if out is None:
+        out = torch.empty(rows, n, dtype=torch.bfloat16, device=a_codes.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_gemm_nvfp4_grouped(a_codes.data_ptr(), a_sf.data_ptr(), a_gs.data_ptr(),
+                                         b_codes.data_ptr(), b_sf.data_ptr(), b_gs.data_ptr(),
+                                         out.data_ptr(), tile_map.data_ptr(),
+                                         tile_count.data_ptr(), tile_map.shape[0], rows, groups,
+                                         n, 2 * kh, out.stride(0), _stream()),
+               "rt_gemm_nvfp4_grouped")
+    return out
+
+
+_DENSE_TILES: dict[tuple, tuple] = {}
+
+
+def linear_nvfp4(x_codes: torch.Tensor, x_sf: torch.Tensor, x_gs: torch.Tensor,
+                 w_codes: torch.Tensor, w_sf: torch.Tensor, w_gs: torch.Tensor) -> torch.Tensor:
+    """Dense NVFP4 linear layer: operands as fused_nvfp4_quant(..., tiled_scales=True) returns
+    them (x [M, K], weight [N, K]) -> bf16 [M, N]."""
+    m = x_codes.shape[0]
+    key = (m, str(x_codes.device))
+    tiles = _DENSE_TILES.get(key)
+    if tiles is None:
+        offsets = torch.tensor([0, m], dtype=torch.int32, device=x_codes.device)
+        tm, _, tc = moe_tile_map(offsets, 0, 1, (m + 127) // 128 + 1)
+        tiles = (tm, tc)
+        _DENSE_TILES[key] = tiles
+    return gemm_nvfp4_grouped(x_codes, x_sf.view(torch.uint8), x_gs, w_codes,
+                              w_sf.view(torch.uint8), w_gs.reshape(1), tiles[0], tiles[1],
+                              n=w_codes.shape[0], groups=1)

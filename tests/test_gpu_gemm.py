@@ -1,0 +1,143 @@
+"""GPU parity tests of the tcgen05 GEMMs against an fp32 torch matmul of the same operands."""
+from __future__ import annotations
+
+import pytest
+import torch
+
+from oracle import inputs as I
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from racetrack_b200 import ops as _ops
+    return _ops
+
+
+def _ref(x, w):
+    return x.float() @ w.float().t()
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 64),        # one tile, one K block
+    (128, 256, 256),       # one wide tile
+    (256, 512, 512),       # 2 x 2 tiles
+    (1, 2112, 7168),       # decode row, ragged N
+    (100, 136, 72),        # ragged everywhere (multiples of 8)
+    (4096, 2112, 7168),    # qkv_a projection
+    (2048, 24576, 1536),   # q_b projection, all 128 heads
+    (1000, 7168, 2048),    # expert down projection
+])
+def test_linear_bf16(ops, m, n, k):
+    x = I.randn((m, k), 100 + m).cuda()
+    w = I.randn((n, k), 200 + n, std=0.05).cuda()
+    out = ops.linear_bf16(x, w)
+    ops.tc_error_state()
+    ref = _ref(x, w)
+    assert out.shape == (m, n)
+    err = rel_err(out, ref)
+    assert err <= 1e-2, f"relative error {err}"
+    # element-wise: bf16 rounding of an fp32 accumulation, allow 1 ulp + accumulation noise
+    diff = (out.float() - ref).abs()
+    tol = 2.0 ** -7 * ref.abs() + 2e-3 * ref.abs().max()
+    assert bool((diff <= tol).all()), f"worst {float(diff.max())}"
+
+
+def test_linear_bf16_strided_inputs_and_linearity(ops):
+    big = I.randn((300, 1024), 5).cuda()
+    w = I.randn((512, 512), 6, std=0.05).cuda()
+    x = big[:, 256:768]                      # column slice: row pitch 1024
+    out = ops.linear_bf16(x, w)
+    ops.tc_error_state()
+    assert rel_err(out, _ref(x, w)) <= 1e-2
+    # exact linearity in powers of two: (2x) W^T == 2 (x W^T) bit for bit
+    out2 = ops.linear_bf16((x * 2).contiguous(), w)
+    assert torch.equal(out2, out * 2)
+    # leading dims
+    out3 = ops.linear_bf16(x.contiguous().view(3, 100, 512), w)
+    assert out3.shape == (3, 100, 512) and torch.equal(out3.view(300, 512), out)
+
+
+# ---------------------------------------------------------------------------
+# NVFP4 block-scaled GEMM
+# ---------------------------------------------------------------------------
+
+def _dequant_gpu(ops, x):
+    """fp64 dequantisation (on the GPU) of what fused_nvfp4_quant makes of x."""
+    from oracle import ref_ops as R
+    codes, sf, gs = ops.fused_nvfp4_quant(x)
+    return R.nvfp4_dequant(codes.cpu(), sf.cpu(), gs.cpu()).cuda().double()
+
+
+def _check_nvfp4(out, ref64):
+    ref = ref64.float()
+    err = rel_err(out, ref)
+    assert err <= 1e-2, f"relative error {err}"
+    diff = (out.float() - ref).abs()
+    tol = 2.0 ** -7 * ref.abs() + 1e-3 * ref.abs().max()
+    assert bool((diff <= tol).all()), f"worst {float(diff.max())} (max |ref| {float(ref.abs().max())})"
+
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 128, 256),       # one tile, one K stage
+    (128, 128, 1024),      # one tile, several stages (scale buffers alternate)
+    (256, 256, 512),       # 2 x 2 tiles
+    (100, 2112, 7168),     # ragged M, N not a multiple of the tile
+    (1, 4096, 7168),       # decode row
+    (2048, 4096, 7168),    # expert up-projection shape, many tiles per CTA
+])
+def test_linear_nvfp4_dense(ops, m, n, k):
+    x = I.randn((m, k), 300 + m).cuda()
+    w = I.randn((n, k), 400 + n, std=0.05).cuda()
+    xq = ops.fused_nvfp4_quant(x, tiled_scales=True)
+    wq = ops.fused_nvfp4_quant(w, tiled_scales=True)
+    out = ops.linear_nvfp4(*xq, *wq)
+    ops.tc_error_state()
+    assert out.shape == (m, n)
+    ref = _dequant_gpu(ops, x) @ _dequant_gpu(ops, w).t()
+    _check_nvfp4(out, ref)
+
+
+def test_gemm_nvfp4_grouped_ragged(ops):
+    """Five groups of 130, 0, 5, 256 and 1 rows: tiles never straddle groups, every group
+    uses its own weights and global scale, empty groups cost nothing."""
+    sizes = [130, 0, 5, 256, 1]
+    n, k = 256, 512
+    offsets = torch.tensor([0] + list(torch.tensor(sizes).cumsum(0)), dtype=torch.int32).cuda()
+    rows = sum(sizes)
+    x = I.randn((rows, k), 7).cuda()
+    ws = [(I.randn((n, k), 50 + g, std=0.05) * (g + 1)).to(torch.bfloat16).cuda() for g in range(len(sizes))]
+    amax = ops.tensor_absmax(x)
+    a_codes = torch.empty(rows, k // 2, dtype=torch.uint8, device="cuda")
+    sf_parts, r0 = [], 0
+    for s in sizes:
+        if s:
+            c, sf, a_gs = ops.fused_nvfp4_quant(x[r0:r0 + s], amax=amax, tiled_scales=True)
+            a_codes[r0:r0 + s] = c
+            sf_parts.append(sf.view(torch.uint8))
+        r0 += s
+    a_sf = torch.cat(sf_parts)
+    wq = [ops.fused_nvfp4_quant(w, tiled_scales=True) for w in ws]
+    b_codes = torch.cat([q[0] for q in wq])
+    b_sf = torch.cat([q[1].view(torch.uint8) for q in wq])
+    b_gs = torch.cat([q[2] for q in wq])
+    tile_map, tile_base, tile_count = ops.moe_tile_map(offsets, 0, len(sizes), rows // 128 + len(sizes) + 1)
+    assert tile_base.cpu().tolist() == [0, 2, 2, 3, 5, 6] and int(tile_count) == 6
+    assert tile_map.cpu()[:6].tolist() == [[0, 0, 128, 0], [0, 128, 2, 1], [2, 130, 5, 2],
+                                           [3, 135, 128, 3], [3, 263, 128, 4], [4, 391, 1, 5]]
+    out = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
+    ops.gemm_nvfp4_grouped(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, tile_map, tile_count,
+                           n=n, groups=len(sizes), out=out)
+    ops.tc_error_state()
+    assert not bool(out.isnan().any())
+    xd = _dequant_gpu(ops, x)          # same global amax as the per-group calls
+    r0 = 0
+    for g, s in enumerate(sizes):
+        if s:
+            _check_nvfp4(out[r0:r0 + s], xd[r0:r0 + s] @ _dequant_gpu(ops, ws[g]).t())
+        r0 += s
+    # a sub-range of groups (an expert-parallel rank owning groups 2..4)
+    tm2, tb2, tc2 = ops.moe_tile_map(offsets, 2, 5, 8)
+    assert int(tc2) == 4 and tm2.cpu()[0].tolist() == [0, 130, 5, 0]

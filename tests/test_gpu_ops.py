@@ -168,8 +168,11 @@ def test_rope_variants(ops):
     xh = I.randn((tokens, heads, 64), 14)
     ref_h = R.apply_rope(xh, pos)
     got_h = ops.fused_rope_half(cu(xh), cu(pos))
+    # positions up to ~7800: host and device cos/sin differ in the last fp32 ulp, which can
+    # flip the bf16 rounding of a table entry; cancellation in x1*c - x2*s then rules out a
+    # per-element ulp bound, so the check is relative to the tensor's magnitude
     assert rel_err(got_h, ref_h) <= REL_TOL
-    assert_close_bf16(got_h, ref_h, "half-split", ulps=2, max_frac=5e-2)
+    assert mismatch_fraction(got_h, ref_h) <= 5e-2
 
 
 # ---------------------------------------------------------------------------
@@ -205,6 +208,8 @@ def test_act_quant_fp8_bit_exact(ops, tokens, cols, golden_small):
 
 def test_act_quant_fp8_edge_values(ops):
     x = torch.zeros(4, 256, dtype=torch.bfloat16)
+    x[0, 3] = -0.0                         # the sign of a zero survives (code 0x80)
+    x[3, 200] = -0.0
     x[1, :128] = 1e-6                      # below the 1e-4 amax clamp
     x[2, 5] = 3.0e38                       # near bf16 max
     x[2, 130] = -448.0
@@ -417,10 +422,18 @@ def test_full_size_swiglu_quant_properties(ops):
     assert torch.equal(scales, s2)
     amax = h.float().view(tokens, inter // 128, 128).abs().amax(-1).clamp(min=1e-4)
     assert torch.equal(scales, (amax.double() / 448.0).float())      # correctly rounded quotient
-    # torch on the same GPU, same formula with a tensor divisor (IEEE division)
-    ref_codes = (h.float().view(tokens, -1, 128) / scales.unsqueeze(-1)).clamp(-448, 448) \
+    # codes: x / scale evaluated in float64 and rounded once to fp32 is the IEEE fp32 quotient
+    # (a 53-bit quotient of 24-bit operands never lands on an fp32 rounding boundary)
+    q = (h.double().view(tokens, -1, 128) / scales.double().unsqueeze(-1)).float()
+    ref_codes = q.clamp(-448, 448).to(torch.float8_e4m3fn).view(tokens, inter)
+    bad = int((codes.view(torch.uint8) != ref_codes.view(torch.uint8)).sum())
+    assert bad == 0, f"{bad} of {codes.numel()} FP8 codes differ from the exact quotient"
+    # informative: torch's own fp32 tensor/tensor division on this GPU
+    gpu_codes = (h.float().view(tokens, -1, 128) / scales.unsqueeze(-1)).clamp(-448, 448) \
         .to(torch.float8_e4m3fn).view(tokens, inter)
-    assert torch.equal(codes.view(torch.uint8), ref_codes.view(torch.uint8))
+    frac = float((codes.view(torch.uint8) != gpu_codes.view(torch.uint8)).float().mean())
+    print(f"FP8 codes differing from torch-on-GPU fp32 division: {frac:.3e}")
+    assert frac < 1e-3
     # NVFP4 at the same size: decode error bound and fused == two-step
     n1 = ops.fused_swiglu_nvfp4_quant(g, u)
     n2 = ops.fused_nvfp4_quant(h)
