@@ -249,6 +249,30 @@ int rt_moe_permute(const int64_t* indices, int32_t* expert_offsets,
                    int64_t tokens, int64_t topk, int64_t n_experts, void* stream);
 
 /*
+ * rt_moe_permute for callers that have no scratch memory to hand over and must not trigger
+ * an allocation: a host that pre-sized one device arena at start-up and gives plugins no
+ * allocator, or an operator signature that carries inputs and outputs only. Same inputs,
+ * outputs and results as rt_moe_permute; the per-block histogram lives in a fixed 256 KiB
+ * array inside the library image (every GPU that loads the library holds it until exit).
+ * This entry point has no counterpart in racetrack.
+ *   - Limit: ceil(tokens*topk / 1024) * n_experts <= rt_moe_permute_static_max_ints() (65536),
+ *     e.g. 32 768 pairs with 256 experts. Larger problems are refused with RT_ERR_UNSUPPORTED;
+ *     use rt_moe_permute with a workspace for them.
+ *   - It calls no cudaMalloc / cudaFree and no allocating library routine.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call before any
+ *     stream capture begins.
+ *   - All calls on a device share the one array, which keeps the previous call's contents.
+ *     Nothing in it has to be cleared (each call overwrites the region it reads), but two
+ *     calls whose kernels overlap on the GPU (different streams, or concurrent host threads)
+ *     race on it: serialise them.
+ */
+int64_t rt_moe_permute_static_max_ints(void);
+int rt_moe_permute_static(const int64_t* indices, int32_t* expert_offsets,
+                          int32_t* sorted_pairs, int32_t* pair_pos,
+                          int64_t tokens, int64_t topk, int64_t n_experts, void* stream);
+
+/*
  * Row gather: out[i, :] = x[sorted_pairs[i] / topk, :] for i in [0, n_pairs).
  * cols % 8 == 0. Used to lay tokens out expert-by-expert for the grouped GEMM.
  * ref: racetrack/models/deepseek.py:1017 (x[idx] inside the expert loop).

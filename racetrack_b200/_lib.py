@@ -36,6 +36,8 @@ SIGNATURES: dict[str, tuple] = {
     "rt_moe_route": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _F, _I, _P]),
     "rt_moe_permute_workspace_bytes": (_L, [_L, _L, _L]),
     "rt_moe_permute": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _P]),
+    "rt_moe_permute_static_max_ints": (_L, []),
+    "rt_moe_permute_static": (_I, [_P, _P, _P, _P, _L, _L, _L, _P]),
     "rt_moe_gather": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "rt_moe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _P]),
     "rt_gemm_bf16": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),

@@ -8,6 +8,8 @@
 // Permutation: counting sort in three small launches (per-block histograms,
 // scan, stable scatter); positions are a pure function of the indices, so the
 // result is deterministic and equal to what a per-expert torch.where loop yields.
+#include <mutex>
+
 #include "rt_common.cuh"
 
 namespace rt {
@@ -380,6 +382,96 @@ extern "C" int rt_moe_permute(const int64_t* indices, int32_t* expert_offsets,
             cudaError_t e = cudaFuncSetAttribute(
                 moe_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_moe_permute: %s", cudaGetErrorString(e));
+        }
+        moe_scatter_kernel<<<blocks, kPermThreads, smem, st>>>(
+            indices, counts, expert_offsets, sorted_pairs, pair_pos, (int)n_pairs, ne);
+        count_launch();
+        if (int rc = check_launch("moe_scatter_kernel")) return rc;
+    }
+    return RT_OK;
+}
+
+// ---------------------------------------------------------------------------
+// rt_moe_permute without a caller-provided workspace
+// ---------------------------------------------------------------------------
+// Some hosts cannot give this library scratch memory: an inference runtime that carved all
+// device memory into a fixed arena at start-up and offers plugins no allocator, or a
+// caller bound to a fixed operator signature that carries inputs and outputs only. For them
+// the per-block histogram of the counting sort lives in a fixed array inside the library
+// image. Every GPU that loads the library holds these 256 KiB until the process exits.
+constexpr int64_t kStaticScratchInts = 65536;  // ceil(pairs / 1024) * n_experts must fit
+static __device__ __align__(256) int32_t g_permute_scratch[kStaticScratchInts];
+
+namespace {
+constexpr int kMaxDevices = 64;
+std::mutex g_scratch_mutex;
+int32_t* g_scratch_ptr[kMaxDevices] = {nullptr};
+
+// Device address of g_permute_scratch on the current device. In host code the array's name
+// only stands for the symbol; the address a kernel can use has to be asked for, once per
+// device, with that device current.
+int static_scratch(int32_t** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_moe_permute_static: cudaGetDevice: %s",
+               cudaGetErrorString(e));
+    RT_REQUIRE(dev >= 0 && dev < kMaxDevices, RT_ERR_UNSUPPORTED,
+               "rt_moe_permute_static: device index %d above the supported %d", dev, kMaxDevices);
+    std::lock_guard<std::mutex> lock(g_scratch_mutex);
+    if (g_scratch_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_permute_scratch);
+        RT_REQUIRE(e == cudaSuccess && p != nullptr, RT_ERR_CUDA,
+                   "rt_moe_permute_static: cudaGetSymbolAddress: %s", cudaGetErrorString(e));
+        g_scratch_ptr[dev] = static_cast<int32_t*>(p);
+    }
+    *out = g_scratch_ptr[dev];
+    return RT_OK;
+}
+}  // namespace
+
+extern "C" int64_t rt_moe_permute_static_max_ints(void) { return kStaticScratchInts; }
+
+extern "C" int rt_moe_permute_static(const int64_t* indices, int32_t* expert_offsets,
+                                     int32_t* sorted_pairs, int32_t* pair_pos, int64_t tokens,
+                                     int64_t topk, int64_t n_experts, void* stream) {
+    RT_REQUIRE(indices && expert_offsets && sorted_pairs && pair_pos, RT_ERR_BAD_ARG,
+               "rt_moe_permute_static: null pointer");
+    RT_REQUIRE(tokens >= 0 && topk > 0 && n_experts > 0, RT_ERR_BAD_ARG,
+               "rt_moe_permute_static: bad shape");
+    RT_REQUIRE(n_experts <= 1024, RT_ERR_UNSUPPORTED, "rt_moe_permute_static: n_experts above 1024");
+    const int64_t n_pairs = tokens * topk;
+    const int64_t blocks64 = (n_pairs + kPermThreads - 1) / kPermThreads;
+    RT_REQUIRE(blocks64 * n_experts <= kStaticScratchInts, RT_ERR_UNSUPPORTED,
+               "rt_moe_permute_static: %lld pairs x %lld experts need %lld scratch entries, the "
+               "built-in array holds %lld; use rt_moe_permute with a caller workspace",
+               (long long)n_pairs, (long long)n_experts, (long long)(blocks64 * n_experts),
+               (long long)kStaticScratchInts);
+    int32_t* counts = nullptr;
+    if (int rc = static_scratch(&counts)) return rc;
+    const int blocks = static_cast<int>(blocks64);
+    const int ne = static_cast<int>(n_experts);
+    cudaStream_t st = as_stream(stream);
+    // Nothing in the array has to start at zero: the count kernel writes every entry of the
+    // blocks x n_experts region before the scan and scatter kernels read it.
+    if (blocks > 0) {
+        moe_count_kernel<<<blocks, kPermThreads, ne * sizeof(int), st>>>(indices, counts,
+                                                                         (int)n_pairs, ne);
+        count_launch();
+        if (int rc = check_launch("moe_count_kernel")) return rc;
+    }
+    int scan_threads = (ne + 31) / 32 * 32;
+    if (scan_threads > 1024) scan_threads = 1024;
+    moe_scan_kernel<<<1, scan_threads, 0, st>>>(counts, expert_offsets, blocks, ne);
+    count_launch();
+    if (int rc = check_launch("moe_scan_kernel")) return rc;
+    if (blocks > 0) {
+        const size_t smem = 32u * ne * sizeof(unsigned short);
+        if (smem > 48u * 1024u) {
+            cudaError_t e = cudaFuncSetAttribute(
+                moe_scatter_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+            RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_moe_permute_static: %s",
+                       cudaGetErrorString(e));
         }
         moe_scatter_kernel<<<blocks, kPermThreads, smem, st>>>(
             indices, counts, expert_offsets, sorted_pairs, pair_pos, (int)n_pairs, ne);
