@@ -178,6 +178,15 @@ int rt_absmax(const void* x, const void* up, float* amax_out,
               int64_t rows, int64_t cols, int64_t x_stride, int64_t up_stride,
               int dtype, void* stream);
 
+/*
+ * rt_absmax restricted to rows [*row_begin, *row_end) (device int32 values, NULL = no bound):
+ * the rows of the sorted MoE buffer that an expert-parallel rank actually wrote.
+ * No counterpart in racetrack.
+ */
+int rt_absmax_rows(const void* x, const void* up, float* amax_out,
+                   int64_t rows, int64_t cols, int64_t x_stride, int64_t up_stride,
+                   const int32_t* row_begin, const int32_t* row_end, int dtype, void* stream);
+
 /* Block-scale layouts for NVFP4 */
 typedef enum rt_sf_layout {
     RT_SF_ROWMAJOR = 0,   /* [rows, cols/16] bytes */
@@ -205,13 +214,34 @@ int rt_nvfp4_quant(const void* x, const void* up, const float* amax_in,
                    int64_t rows, int64_t cols, int64_t x_stride, int64_t up_stride,
                    int sf_layout, int dtype, void* stream);
 
+/*
+ * NVFP4 quantisation of the rows a grouped-GEMM tile map covers (see rt_moe_tile_map):
+ * codes [*, cols/2] are written at the tiles' (compact) rows, block scales into the
+ * RT_SF_TILED128x4 layout with row tile = the tile map's scale row-tile index, so each expert
+ * segment starts on a scale-tile boundary; rows of a tile beyond its valid rows get zero scales.
+ * With sorted_pairs != NULL the source row of destination row r is sorted_pairs[r] / topk:
+ * the token gather of the MoE dispatch is fused into the quantiser (x is the un-permuted
+ * [tokens, cols] activation). With up != NULL the quantised values are swiglu(x, up) and rows
+ * are taken as they are. block_scales must hold max_tiles * (cols/64) * 512 bytes.
+ * cols % 64 == 0. Arithmetic as rt_nvfp4_quant.
+ * ref: racetrack/models/deepseek.py:1017 (x[idx] gather); NVFP4 has no counterpart in racetrack.
+ */
+int rt_moe_quant_nvfp4(const void* x, const void* up, const int32_t* sorted_pairs, int64_t topk,
+                       const float* amax_in, void* codes, void* block_scales,
+                       float* global_scale_out, const int32_t* tile_map,
+                       const int32_t* tile_count, int64_t max_tiles, int64_t cols,
+                       int64_t x_stride, int64_t up_stride, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* MoE routing and token permutation                                          */
 /* ------------------------------------------------------------------------ */
 
 typedef enum rt_score_func {
     RT_SCORE_SIGMOID = 0,
-    RT_SCORE_SOFTMAX = 1
+    RT_SCORE_SOFTMAX = 1,
+    RT_SCORE_TOPK_SOFTMAX = 2  /* top-k on the raw logits, weights = softmax over the selected
+                                  logits rounded to bf16 (no bias, no groups);
+                                  ref: racetrack/realistic_bench.py:321-327 */
 } rt_score_func;
 
 /*
@@ -286,13 +316,16 @@ int rt_moe_gather(const void* x, const int32_t* sorted_pairs, void* out,
  * (+ shared[t, :] when `shared` is non-NULL), fp32 accumulation in slot order,
  * rounded to `dtype`. Pairs whose sorted position lies outside
  * [pos_begin, pos_end) are skipped (expert-parallel ranks own a slice of the
- * sorted range). cols % 8 == 0.
+ * sorted range); pos_begin_ptr / pos_end_ptr, when non-NULL, are device int32 values that
+ * override the host ones (entries of expert_offsets, so no host read-back is needed).
+ * cols % 8 == 0.
  * ref: racetrack/models/deepseek.py:1018-1022 (y[idx] += expert(x[idx]) * weights[idx, top]; y += shared).
  */
 int rt_moe_combine(const void* expert_out, const int32_t* pair_pos, const float* weights,
                    const void* shared, void* y,
                    int64_t tokens, int64_t topk, int64_t cols,
                    int64_t pos_begin, int64_t pos_end,
+                   const int32_t* pos_begin_ptr, const int32_t* pos_end_ptr,
                    int dtype, void* stream);
 
 /* ------------------------------------------------------------------------ */

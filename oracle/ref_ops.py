@@ -319,3 +319,42 @@ def moe_forward(x, gate_w, gate_b, experts, shared, *, n_groups, topk_groups, to
     if shared is not None:
         y += expert_mlp(x, *shared)
     return y.type_as(x)
+
+
+def nvfp4_roundtrip(x: torch.Tensor, amax: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """dequant(quant(x)) in fp32: the values an NVFP4 tensor-core GEMM actually multiplies."""
+    return nvfp4_dequant(*nvfp4_quant(x, amax))
+
+
+def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_range=None):
+    """MoE.forward's expert loop (ref: racetrack/models/deepseek.py:1011-1022) with NVFP4
+    operands: x and swiglu(h) quantised with one tensor-wide global scale each (over the rows
+    routed to the experts in `expert_range`), every expert's w13 [2I, H] / w2 [H, I] with its own;
+    products of dequantised operands accumulate in fp32, GEMM outputs round to bf16.
+    NVFP4 itself has no reference counterpart (parity unpinned); the control flow follows the
+    reference. Returns bf16 [T, H]."""
+    tokens, hidden = x.shape
+    n_experts = w13.shape[0]
+    inter = w13.shape[1] // 2
+    lo, hi = expert_range if expert_range is not None else (0, n_experts)
+    xq = nvfp4_roundtrip(x)                       # global amax over the un-permuted activations
+    rows = {}
+    for e in range(lo, hi):
+        idx, top = torch.where(indices == e)
+        if idx.numel() == 0:
+            continue
+        gate_up = (xq[idx] @ nvfp4_roundtrip(w13[e]).t()).to(torch.bfloat16)
+        rows[e] = (idx, top, swiglu(gate_up[:, :inter], gate_up[:, inter:]))
+    y = torch.zeros(tokens, hidden, dtype=torch.float32)
+    if rows:
+        h_amax = torch.stack([h.float().abs().max() for (_, _, h) in rows.values()]).max()
+        # fp32 accumulation in slot order, as the combine kernel does
+        outs = torch.zeros(tokens, indices.shape[1], hidden, dtype=torch.float32)
+        for e, (idx, top, h) in rows.items():
+            out = (nvfp4_roundtrip(h, h_amax) @ nvfp4_roundtrip(w2[e]).t()).to(torch.bfloat16)
+            outs[idx, top] = out.float() * weights[idx, top, None]
+        for s in range(indices.shape[1]):
+            y = y + outs[:, s]
+    if shared_out is not None:
+        y = y + shared_out.float()
+    return y.to(torch.bfloat16)

@@ -14,7 +14,7 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "librt_b200.so"
 RT_BF16, RT_F32, RT_F16 = 0, 1, 2
 RT_ROPE_HALF, RT_ROPE_INTERLEAVED = 0, 1
 RT_SF_ROWMAJOR, RT_SF_TILED128x4 = 0, 1
-RT_SCORE_SIGMOID, RT_SCORE_SOFTMAX = 0, 1
+RT_SCORE_SIGMOID, RT_SCORE_SOFTMAX, RT_SCORE_TOPK_SOFTMAX = 0, 1, 2
 
 _P, _I, _L, _F = c_void_p, c_int, c_int64, c_float
 
@@ -39,7 +39,9 @@ SIGNATURES: dict[str, tuple] = {
     "rt_moe_permute_static_max_ints": (_L, []),
     "rt_moe_permute_static": (_I, [_P, _P, _P, _P, _L, _L, _L, _P]),
     "rt_moe_gather": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _P]),
-    "rt_moe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _I, _P]),
+    "rt_moe_combine": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _P, _P, _I, _P]),
+    "rt_absmax_rows": (_I, [_P, _P, _P, _L, _L, _L, _L, _P, _P, _I, _P]),
+    "rt_moe_quant_nvfp4": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "rt_gemm_bf16": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
     "rt_tc_error_state": (_I, []),
     "rt_moe_tile_map": (_I, [_P, _L, _L, _P, _P, _P, _L, _P]),

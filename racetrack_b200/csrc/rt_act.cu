@@ -142,12 +142,16 @@ template <bool UP>
 __global__ void __launch_bounds__(kActThreads) absmax_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
     float* __restrict__ out, uint32_t items, uint32_t items_per_row, int64_t xstride,
-    int64_t ustride) {
+    int64_t ustride, const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end) {
     __shared__ float scratch[32];
     float m = 0.f;
+    // optional row window read from device memory (the rows an expert-parallel rank owns)
+    const uint32_t r_lo = row_begin ? static_cast<uint32_t>(__ldg(row_begin)) : 0u;
+    const uint32_t r_hi = row_end ? static_cast<uint32_t>(__ldg(row_end)) : 0xffffffffu;
     for (uint32_t id = blockIdx.x * kActThreads + threadIdx.x; id < items;
          id += gridDim.x * kActThreads) {
         const uint32_t row = id / items_per_row;
+        if (row < r_lo || row >= r_hi) continue;
         const int64_t col = static_cast<int64_t>(id - row * items_per_row) * kItem;
         float v[16];
         load_item<UP>(x, up, row, col, xstride, ustride, v);
@@ -217,6 +221,61 @@ __global__ void __launch_bounds__(kActThreads) quant_nvfp4_kernel(
     }
     st_stream8(codes + static_cast<int64_t>(row) * (cols >> 1) + (col >> 1), make_uint2(lo, hi));
     sf[sf_offset(layout, row, blk, items_per_row)] = static_cast<uint8_t>(bs);
+}
+
+// NVFP4 quantisation of the rows a grouped-GEMM tile map covers. Tile t = {group, first
+// row, valid rows, scale row tile}: codes go to the (compact) destination row, scales to the
+// tile's own 128-row scale tiles, rows of the tile beyond `valid rows` get zero scales.
+// With sorted_pairs the source row of destination row r is sorted_pairs[r] / topk (the
+// token gather of the MoE dispatch fused into the quantiser); otherwise source = destination.
+// Grid: 16 CTAs per tile, each doing 8 rows.
+template <bool UP>
+__global__ void __launch_bounds__(kActThreads) quant_nvfp4_tiles_kernel(
+    const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
+    const int32_t* __restrict__ sorted_pairs, int topk, const float* __restrict__ amax_in,
+    uint8_t* __restrict__ codes, uint8_t* __restrict__ sf, float* __restrict__ gs_out,
+    const int4* __restrict__ tile_map, const int32_t* __restrict__ tile_count,
+    uint32_t items_per_row, int64_t xstride, int64_t ustride, int64_t cols) {
+    const int tile = blockIdx.x >> 4, sub = blockIdx.x & 15;
+    const float amax = __ldg(amax_in);
+    const float gs = amax > 0.f ? __fdiv_rn(amax, 2688.0f) : 1.0f;
+    if (blockIdx.x == 0 && threadIdx.x == 0 && gs_out) *gs_out = gs;
+    if (tile >= __ldg(tile_count)) return;
+    const int4 tm = __ldg(tile_map + tile);
+    const float six_gs = __fmul_rn(6.0f, gs);
+    const uint32_t kt = items_per_row >> 2;
+    uint8_t* sf_tile = sf + static_cast<int64_t>(tm.w) * kt * 512;
+    for (uint32_t it = threadIdx.x; it < 8u * items_per_row; it += kActThreads) {
+        const uint32_t rr = it / items_per_row;
+        const uint32_t blk = it - rr * items_per_row;
+        const uint32_t r_local = sub * 8u + rr;
+        uint8_t* sf_dst = sf_tile + static_cast<int64_t>(blk >> 2) * 512 + (r_local & 31u) * 16u +
+                          (r_local >> 5) * 4u + (blk & 3u);
+        if (static_cast<int>(r_local) >= tm.z) {
+            *sf_dst = 0;
+            continue;
+        }
+        const int64_t dst_row = tm.y + r_local;
+        const int64_t src_row = sorted_pairs ? (__ldg(sorted_pairs + dst_row) / topk) : dst_row;
+        const int64_t col = static_cast<int64_t>(blk) * kItem;
+        float v[16];
+        load_item<UP>(x, up, src_row, col, xstride, ustride, v);
+        const float bmax = absmax16(v);
+        const float t = fminf(__fdiv_rn(bmax, six_gs), 448.0f);
+        const uint32_t bs = cvt_e4m3x2(t, 0.f) & 0xffu;
+        const float denom = __fmul_rn(gs, e4m3_to_f32(bs));
+        uint32_t lo = 0, hi = 0;
+        if (denom > 0.f) {
+            const float inv = __frcp_rn(denom);
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+                lo |= cvt_e2m1x2(__fmul_rn(v[2 * k], inv), __fmul_rn(v[2 * k + 1], inv)) << (8 * k);
+                hi |= cvt_e2m1x2(__fmul_rn(v[8 + 2 * k], inv), __fmul_rn(v[9 + 2 * k], inv)) << (8 * k);
+            }
+        }
+        st_stream8(codes + dst_row * (cols >> 1) + (col >> 1), make_uint2(lo, hi));
+        *sf_dst = static_cast<uint8_t>(bs);
+    }
 }
 
 // Zero-fills the padding entries of a 128x4-tiled scale buffer (rows beyond
@@ -312,8 +371,9 @@ extern "C" int rt_swiglu_quant_fp8(const void* gate, const void* up, void* codes
                             gate_stride, up_stride, dtype, stream);
 }
 
-extern "C" int rt_absmax(const void* x, const void* up, float* amax_out, int64_t rows,
-                         int64_t cols, int64_t x_stride, int64_t up_stride, int dtype,
+static int absmax_common(const void* x, const void* up, float* amax_out, int64_t rows,
+                         int64_t cols, int64_t x_stride, int64_t up_stride,
+                         const int32_t* row_begin, const int32_t* row_end, int dtype,
                          void* stream) {
     uint32_t items, per_row;
     if (int rc = check_stream_args("rt_absmax", x, rows, cols, x_stride, 16, dtype, items, per_row,
@@ -332,12 +392,64 @@ extern "C" int rt_absmax(const void* x, const void* up, float* amax_out, int64_t
     if (up)
         absmax_kernel<true><<<grid, kActThreads, 0, st>>>((const __nv_bfloat16*)x,
                                                           (const __nv_bfloat16*)up, amax_out, items,
-                                                          per_row, x_stride, up_stride);
+                                                          per_row, x_stride, up_stride, row_begin,
+                                                          row_end);
     else
         absmax_kernel<false><<<grid, kActThreads, 0, st>>>((const __nv_bfloat16*)x, nullptr,
-                                                           amax_out, items, per_row, x_stride, 0);
+                                                           amax_out, items, per_row, x_stride, 0,
+                                                           row_begin, row_end);
     count_launch();
     return check_launch("absmax_kernel");
+}
+
+extern "C" int rt_absmax(const void* x, const void* up, float* amax_out, int64_t rows,
+                         int64_t cols, int64_t x_stride, int64_t up_stride, int dtype,
+                         void* stream) {
+    return absmax_common(x, up, amax_out, rows, cols, x_stride, up_stride, nullptr, nullptr, dtype,
+                         stream);
+}
+
+extern "C" int rt_absmax_rows(const void* x, const void* up, float* amax_out, int64_t rows,
+                              int64_t cols, int64_t x_stride, int64_t up_stride,
+                              const int32_t* row_begin, const int32_t* row_end, int dtype,
+                              void* stream) {
+    return absmax_common(x, up, amax_out, rows, cols, x_stride, up_stride, row_begin, row_end,
+                         dtype, stream);
+}
+
+extern "C" int rt_moe_quant_nvfp4(const void* x, const void* up, const int32_t* sorted_pairs,
+                                  int64_t topk, const float* amax_in, void* codes,
+                                  void* block_scales, float* global_scale_out,
+                                  const int32_t* tile_map, const int32_t* tile_count,
+                                  int64_t max_tiles, int64_t cols, int64_t x_stride,
+                                  int64_t up_stride, int dtype, void* stream) {
+    RT_REQUIRE(max_tiles >= 0 && cols > 0 && topk > 0, RT_ERR_BAD_ARG,
+               "rt_moe_quant_nvfp4: bad shape");
+    if (max_tiles == 0) return RT_OK;
+    RT_REQUIRE(x && amax_in && codes && block_scales && tile_map && tile_count, RT_ERR_BAD_ARG,
+               "rt_moe_quant_nvfp4: null pointer");
+    RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_moe_quant_nvfp4: only bf16 activations");
+    RT_REQUIRE(cols % 64 == 0, RT_ERR_UNSUPPORTED,
+               "rt_moe_quant_nvfp4: cols must be a multiple of 64 (whole scale tiles)");
+    RT_REQUIRE(x_stride % 8 == 0 && aligned16(x) && (!up || (up_stride % 8 == 0 && aligned16(up))) &&
+                   aligned16(tile_map) && (reinterpret_cast<uintptr_t>(codes) & 7u) == 0,
+               RT_ERR_UNSUPPORTED, "rt_moe_quant_nvfp4: alignment (16-byte inputs, stride %% 8)");
+    RT_REQUIRE(max_tiles < (1LL << 27), RT_ERR_UNSUPPORTED, "rt_moe_quant_nvfp4: too many tiles");
+    const unsigned grid = static_cast<unsigned>(max_tiles * 16);
+    const uint32_t per_row = static_cast<uint32_t>(cols / kItem);
+    cudaStream_t st = as_stream(stream);
+    if (up)
+        quant_nvfp4_tiles_kernel<true><<<grid, kActThreads, 0, st>>>(
+            (const __nv_bfloat16*)x, (const __nv_bfloat16*)up, sorted_pairs, (int)topk, amax_in,
+            (uint8_t*)codes, (uint8_t*)block_scales, global_scale_out, (const int4*)tile_map,
+            tile_count, per_row, x_stride, up_stride, cols);
+    else
+        quant_nvfp4_tiles_kernel<false><<<grid, kActThreads, 0, st>>>(
+            (const __nv_bfloat16*)x, nullptr, sorted_pairs, (int)topk, amax_in, (uint8_t*)codes,
+            (uint8_t*)block_scales, global_scale_out, (const int4*)tile_map, tile_count, per_row,
+            x_stride, 0, cols);
+    count_launch();
+    return check_launch("quant_nvfp4_tiles_kernel");
 }
 
 extern "C" int rt_nvfp4_quant(const void* x, const void* up, const float* amax_in, void* codes,

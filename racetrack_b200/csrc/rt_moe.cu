@@ -56,6 +56,8 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
         sum = warp_sum(sum);
 #pragma unroll
         for (int j = 0; j < EPL; ++j) s[j] = __fdiv_rn(s[j], sum);
+    } else if (score_func == RT_SCORE_TOPK_SOFTMAX) {
+        // selection happens on the raw logits; the softmax comes after it
     } else {
 #pragma unroll
         for (int j = 0; j < EPL; ++j) s[j] = __fdiv_rn(1.0f, __fadd_rn(1.0f, expf(-s[j])));
@@ -132,6 +134,12 @@ __global__ void __launch_bounds__(kRouteWarps * 32) moe_route_kernel(
     if (score_func == RT_SCORE_SIGMOID) {
         const float sum = warp_sum(lane < topk ? my_w : 0.f);
         my_w = __fdiv_rn(my_w, sum);
+    } else if (score_func == RT_SCORE_TOPK_SOFTMAX) {
+        // softmax over the selected logits, rounded to bf16 like the activations it scales
+        const float m = warp_max(lane < topk ? my_w : ninf);
+        const float e = lane < topk ? expf(my_w - m) : 0.f;
+        const float sum = warp_sum(e);
+        my_w = round_bf16(__fdiv_rn(e, sum));
     }
     my_w = __fmul_rn(my_w, route_scale);
     if (lane < topk) {
@@ -267,8 +275,12 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(
 __global__ void __launch_bounds__(256) moe_combine_kernel(
     const __nv_bfloat16* __restrict__ expert_out, const int32_t* __restrict__ pair_pos,
     const float* __restrict__ weights, const __nv_bfloat16* __restrict__ shared,
-    __nv_bfloat16* __restrict__ y, int nvec, int topk, int pos_begin, int pos_end) {
+    __nv_bfloat16* __restrict__ y, int nvec, int topk, int pos_begin, int pos_end,
+    const int32_t* __restrict__ pos_begin_ptr, const int32_t* __restrict__ pos_end_ptr) {
     const int64_t t = blockIdx.x;
+    // a window given in device memory (expert offsets of this rank) overrides the host values
+    if (pos_begin_ptr) pos_begin = __ldg(pos_begin_ptr);
+    if (pos_end_ptr) pos_end = __ldg(pos_end_ptr);
     for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
         float acc[8];
 #pragma unroll
@@ -304,8 +316,9 @@ extern "C" int rt_moe_route(const float* logits, const float* bias, float* weigh
     RT_REQUIRE(logits && weights_out && indices_out, RT_ERR_BAD_ARG, "rt_moe_route: null pointer");
     RT_REQUIRE(tokens >= 0 && n_experts > 0 && topk > 0 && n_groups > 0, RT_ERR_BAD_ARG,
                "rt_moe_route: bad shape");
-    RT_REQUIRE(score_func == RT_SCORE_SIGMOID || score_func == RT_SCORE_SOFTMAX, RT_ERR_BAD_ARG,
-               "rt_moe_route: bad score_func %d", score_func);
+    RT_REQUIRE(score_func == RT_SCORE_SIGMOID || score_func == RT_SCORE_SOFTMAX ||
+                   score_func == RT_SCORE_TOPK_SOFTMAX,
+               RT_ERR_BAD_ARG, "rt_moe_route: bad score_func %d", score_func);
     RT_REQUIRE(n_experts <= 512 && topk <= 32 && topk <= n_experts, RT_ERR_UNSUPPORTED,
                "rt_moe_route: needs n_experts <= 512 and topk <= min(32, n_experts)");
     RT_REQUIRE(n_experts % n_groups == 0, RT_ERR_BAD_ARG,
@@ -502,6 +515,7 @@ extern "C" int rt_moe_gather(const void* x, const int32_t* sorted_pairs, void* o
 extern "C" int rt_moe_combine(const void* expert_out, const int32_t* pair_pos,
                               const float* weights, const void* shared, void* y, int64_t tokens,
                               int64_t topk, int64_t cols, int64_t pos_begin, int64_t pos_end,
+                              const int32_t* pos_begin_ptr, const int32_t* pos_end_ptr,
                               int dtype, void* stream) {
     RT_REQUIRE(expert_out && pair_pos && weights && y, RT_ERR_BAD_ARG,
                "rt_moe_combine: null pointer");
@@ -518,7 +532,8 @@ extern "C" int rt_moe_combine(const void* expert_out, const int32_t* pair_pos,
     if (threads > 256) threads = 256;
     moe_combine_kernel<<<static_cast<unsigned>(tokens), threads, 0, as_stream(stream)>>>(
         (const __nv_bfloat16*)expert_out, pair_pos, weights, (const __nv_bfloat16*)shared,
-        (__nv_bfloat16*)y, nvec, (int)topk, (int)pos_begin, (int)pos_end);
+        (__nv_bfloat16*)y, nvec, (int)topk, (int)pos_begin, (int)pos_end, pos_begin_ptr,
+        pos_end_ptr);
     count_launch();
     return check_launch("moe_combine_kernel");
 }

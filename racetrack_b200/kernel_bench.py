@@ -124,11 +124,52 @@ def cases(tokens: int) -> dict[str, tuple[Callable[[], object], int]]:
     return out
 
 
+def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, str]]:
+    """name -> (callable, flops, bytes, kind) for the tensor-core GEMMs."""
+    T = tokens
+    out = {}
+    for name, n, k in (("qkv_a", Q_LORA + KV_LORA + ROPE, HIDDEN), ("q_b", HEADS * 192, Q_LORA),
+                       ("kv_b", HEADS * 256, KV_LORA), ("w_o", HIDDEN, HEADS * 128)):
+        x, w = _randn(T, k), _randn(n, k)
+        out[f"linear_bf16[{name} {T}x{n}x{k}]"] = (
+            (lambda x=x, w=w: ops.linear_bf16(x, w)), 2 * T * n * k, (T * k + n * k + T * n) * 2, "bf16")
+    for name, n, k in (("w13", 4096, HIDDEN), ("w2", HIDDEN, 2048)):
+        x, w = _randn(T, k), _randn(n, k)
+        xq = ops.fused_nvfp4_quant(x, tiled_scales=True)
+        wq = ops.fused_nvfp4_quant(w, tiled_scales=True)
+        out[f"linear_nvfp4[{name} {T}x{n}x{k}]"] = (
+            (lambda xq=xq, wq=wq: ops.linear_nvfp4(*xq, *wq)), 2 * T * n * k,
+            (T * k + n * k) * 9 // 16 + T * n * 2, "nvfp4")
+    return out
+
+
+def run_gemms(tokens: int, iters: int, flush: "L2Flusher") -> list[dict]:
+    peaks = {}
+    p = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
+    if p.exists():
+        peaks = json.loads(p.read_text())
+    bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
+    rows = []
+    for name, (fn, flops, nbytes, kind) in gemm_cases(tokens).items():
+        t = time_kernel(fn, iters=iters, flush=flush)
+        tf = flops / (t["median_us"] * 1e-6) / 1e12
+        # dense NVFP4 has no measured peak on this pool: quoted against the nominal 9 PFLOP/s
+        peak = bf16_peak if kind == "bf16" else 9000.0
+        rows.append({"kernel": name, **t, "tflops": tf, "frac_of_peak": tf / peak, "peak_tflops": peak,
+                     "gbs": nbytes / (t["median_us"] * 1e-6) / 1e9})
+        print(f"{name:40s} {t['median_us']:9.1f} us  {tf:8.1f} TFLOP/s  {100*tf/peak:5.1f}% of "
+              f"{peak:.0f} ({'measured bf16' if kind == 'bf16' else 'nominal nvfp4'})  "
+              f"{rows[-1]['gbs']:7.1f} GB/s", flush=True)
+    ops.tc_error_state()
+    return rows
+
+
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--tokens", type=int, default=4096)
     ap.add_argument("--kernel", action="append", default=None)
     ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--gemm", action="store_true", help="also time the tensor-core GEMMs")
     ap.add_argument("--json", type=Path, default=None)
     args = ap.parse_args()
     peak, peak_src = hbm_peak_gbs()
@@ -147,9 +188,12 @@ def main() -> None:
         print(f"{name:28s} T={args.tokens:<6d} {t['median_us']:9.1f} us  {nbytes/1e6:9.1f} MB  "
               f"{gbs:8.1f} GB/s  {100*gbs/peak:5.1f}% of {peak_src} {peak:.0f} GB/s  "
               f"({launches} launch{'es' if launches != 1 else ''})", flush=True)
+    gemm_rows = []
+    if args.gemm:
+        gemm_rows = run_gemms(args.tokens, args.iters, flush)
     if args.json:
         args.json.write_text(json.dumps({"hbm_peak_gbs": peak, "peak_source": peak_src,
-                                         "rows": rows}, indent=1) + "\n")
+                                         "rows": rows, "gemm_rows": gemm_rows}, indent=1) + "\n")
 
 
 if __name__ == "__main__":

@@ -1,0 +1,202 @@
+"""Synthetic full-size DeepSeek-V3.2 layer on the B200 kernels: the counterpart of
+racetrack/realistic_bench.py:118-427 (ShardedRealisticBlock / ShardedRealisticModel).
+
+Same structure and sharding as the reference runner: one layer's weights reused for every layer
+of the stack; attention heads tensor-parallel (w_q_b / w_kv_b column-sharded, w_o row-sharded,
+all-reduce after w_o); routed experts expert-parallel (each rank owns a contiguous slice, tokens
+replicated, all-reduce after the combine); router replicated. Per layer:
+
+    rms_norm -> qkv_a GEMM -> fused q_a/kv_a RMSNorm + k_pe RoPE -> q_b GEMM -> q_pe RoPE (in place)
+    -> kv_b GEMM -> causal attention over the local heads -> w_o GEMM -> all-reduce
+    -> fused residual-add + rms_norm -> router GEMM (fp32) -> routing kernel -> NVFP4 grouped
+    expert GEMMs with SwiGLU -> weighted combine -> all-reduce -> residual add (fused with the
+    next layer's first rms_norm)
+
+Dense projections run on the bf16 tcgen05 GEMM, experts on the NVFP4 block-scaled grouped GEMM,
+everything element-wise on the fused kernels of ops.py. The attention core (QK^T, softmax, PV) is
+torch's scaled_dot_product_attention: it is not one of this backend's kernels.
+
+Unlike the reference, which seeds each rank's weights with seed + rank (so a 2-rank model is a
+different model from a 1-rank one), weights here are defined per shard unit (one eighth of the
+heads, one expert) and a rank draws the units it owns: every world size computes the same layer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, replace
+from typing import Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import moe, ops
+
+
+@dataclass(frozen=True)
+class LayerShape:
+    """Dimensions of racetrack/realistic_bench.py:62-82 (realistic_shape("dsv3_2"))."""
+    name: str = "dsv3_2"
+    hidden: int = 7168
+    heads: int = 128
+    q_lora: int = 1536
+    kv_lora: int = 512
+    nope: int = 128
+    rope: int = 64
+    v_dim: int = 128
+    moe_inter: int = 2048
+    n_experts: int = 256
+    topk: int = 8
+    dense_inter: int = 18432
+    eps: float = 1.0e-6
+    rope_base: float = 10000.0
+    seed: int = 38595
+    units: int = 8           # shard granularity of heads and of the dense FFN
+
+    @property
+    def qk_dim(self) -> int:
+        return self.nope + self.rope
+
+    def scaled(self, **kw) -> "LayerShape":
+        return replace(self, **kw)
+
+
+DSV32 = LayerShape()
+
+
+def _draw(shape, seed: int, std: float, device, dtype) -> torch.Tensor:
+    g = torch.Generator(device=device)
+    g.manual_seed(seed)
+    w = torch.empty(shape, device=device, dtype=torch.float32 if str(device) == "cpu" else dtype)
+    w.normal_(mean=0.0, std=std, generator=g)
+    return w.to(dtype)
+
+
+def make_weights(shape: LayerShape, rank: int, world: int, device, *, ffn: str = "moe",
+                 std: float = 0.02, dtype: torch.dtype = torch.bfloat16) -> dict:
+    """The weights rank `rank` of `world` owns, drawn unit by unit (see the module docstring).
+    Keys: w_qkv_a [q+kv+rope, H]; w_q_b [h_loc*(nope+rope), q]; w_kv_b [h_loc*(nope+v), kv];
+    w_o [H, h_loc*v]; w_gate [E, H]; w13 [E_loc, 2I, H], w2 [E_loc, H, I] (ffn == "moe") or
+    w1, w3 [I_loc, H], w2d [H, I_loc] (ffn == "dense")."""
+    if shape.units % world or shape.n_experts % world:
+        raise ValueError("world size must divide the shard units and the expert count")
+    s = shape
+    hpu = s.heads // s.units                     # heads per unit
+    units = range(rank * s.units // world, (rank + 1) * s.units // world)
+    seed = s.seed
+    w = {"w_qkv_a": _draw((s.q_lora + s.kv_lora + s.rope, s.hidden), seed + 1, std, device, dtype),
+         "w_gate": _draw((s.n_experts, s.hidden), seed + 100000, std, device, dtype)}
+    w["w_q_b"] = torch.cat([_draw((hpu * s.qk_dim, s.q_lora), seed + 100 + u, std, device, dtype)
+                            for u in units])
+    w["w_kv_b"] = torch.cat([_draw((hpu * (s.nope + s.v_dim), s.kv_lora), seed + 200 + u, std, device, dtype)
+                             for u in units])
+    w["w_o"] = torch.cat([_draw((s.hidden, hpu * s.v_dim), seed + 300 + u, std, device, dtype)
+                          for u in units], dim=1)
+    if ffn == "moe":
+        e_loc = s.n_experts // world
+        experts = range(rank * e_loc, (rank + 1) * e_loc)
+        w["w13"] = torch.stack([_draw((2 * s.moe_inter, s.hidden), seed + 10000 + 2 * e, std, device, dtype)
+                                for e in experts])
+        w["w2"] = torch.stack([_draw((s.hidden, s.moe_inter), seed + 10001 + 2 * e, std, device, dtype)
+                               for e in experts])
+    else:
+        ipu = s.dense_inter // s.units
+        w["w1"] = torch.cat([_draw((ipu, s.hidden), seed + 400 + u, std, device, dtype) for u in units])
+        w["w3"] = torch.cat([_draw((ipu, s.hidden), seed + 500 + u, std, device, dtype) for u in units])
+        w["w2d"] = torch.cat([_draw((s.hidden, ipu), seed + 600 + u, std, device, dtype) for u in units], dim=1)
+    return w
+
+
+def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """Causal softmax(q k^T / sqrt(d)) v over [T, H, D] tensors -> [T, H, Dv]
+    (racetrack/runtime/torch_ops.py:97-110). torch SDPA; when the value width differs from the
+    query width and the fused kernels refuse that, v is zero-padded to the query width."""
+    qt, kt, vt = (t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
+    try:
+        out = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
+    except RuntimeError:
+        pad = q.shape[-1] - v.shape[-1]
+        out = F.scaled_dot_product_attention(qt, kt, F.pad(vt, (0, pad)), is_causal=True)[..., :v.shape[-1]]
+    return out.squeeze(0).transpose(0, 1)
+
+
+class RealisticLayer:
+    """One rank's shard of the synthetic layer; `forward_stack` applies it `layers` times."""
+
+    def __init__(self, shape: LayerShape, weights: dict, rank: int = 0, world: int = 1, *,
+                 ffn: str = "moe", route: str = "topk_softmax", process_group=None):
+        self.shape, self.rank, self.world, self.ffn, self.route = shape, rank, world, ffn, route
+        self.group = process_group
+        self.local_heads = shape.heads // world
+        dev = weights["w_qkv_a"].device
+        self.w_qkv_a = weights["w_qkv_a"].contiguous()
+        self.w_q_b = weights["w_q_b"].contiguous()
+        self.w_kv_b = weights["w_kv_b"].contiguous()
+        self.w_o = weights["w_o"].contiguous()
+        self.w_gate_f32 = weights["w_gate"].float().contiguous()
+        self.ones_h = torch.ones(shape.hidden, device=dev, dtype=torch.bfloat16)
+        self.q_norm = torch.ones(shape.q_lora, device=dev, dtype=torch.bfloat16)
+        self.kv_norm = torch.ones(shape.kv_lora, device=dev, dtype=torch.bfloat16)
+        if ffn == "moe":
+            self.local_experts = shape.n_experts // world
+            self.experts = moe.quantize_experts(weights["w13"], weights["w2"])
+        else:
+            self.w13d = torch.cat([weights["w1"], weights["w3"]]).contiguous()
+            self.w2d = weights["w2d"].contiguous()
+
+    # -- pieces ---------------------------------------------------------------------------
+    reduce = True   # set False to get this rank's partial sums (single-process checks)
+
+    def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
+        if self.world > 1 and self.reduce:
+            import torch.distributed as dist
+            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+        return t
+
+    def attention(self, normed: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """racetrack/realistic_bench.py:286-317."""
+        s, h = self.shape, self.local_heads
+        tokens = normed.shape[0]
+        qkv = ops.linear_bf16(normed, self.w_qkv_a)
+        q_c, kv_c, k_pe = ops.fused_norm_rope(
+            qkv[:, :s.q_lora], self.q_norm, qkv[:, s.q_lora:s.q_lora + s.kv_lora], self.kv_norm,
+            qkv[:, s.q_lora + s.kv_lora:], positions, eps=s.eps, rope_base=s.rope_base)
+        q = ops.linear_bf16(q_c, self.w_q_b).view(tokens, h, s.qk_dim)
+        ops.fused_rope_half(q[..., s.nope:], positions, rope_base=s.rope_base, inplace=True)
+        kv = ops.linear_bf16(kv_c, self.w_kv_b).view(tokens, h, s.nope + s.v_dim)
+        k = torch.cat((kv[..., :s.nope], k_pe.unsqueeze(1).expand(-1, h, -1)), dim=-1)
+        local = attention_core(q, k, kv[..., s.nope:])
+        out = ops.linear_bf16(local.reshape(tokens, h * s.v_dim), self.w_o)
+        return self._all_reduce(out)
+
+    def ffn_forward(self, normed: torch.Tensor) -> torch.Tensor:
+        """racetrack/realistic_bench.py:319-352 (routed experts) or a dense SwiGLU FFN."""
+        s = self.shape
+        if self.ffn == "moe":
+            logits = F.linear(normed.float(), self.w_gate_f32)
+            if self.route == "topk_softmax":
+                weights, indices = ops.fused_moe_route(logits, None, n_groups=1, topk_groups=1,
+                                                       topk=s.topk, route_scale=1.0,
+                                                       score_func="topk_softmax")
+            else:
+                raise ValueError(f"unknown route {self.route!r}")
+            out = moe.fused_moe_experts(normed, weights, indices, self.experts,
+                                        n_experts=s.n_experts,
+                                        expert_begin=self.rank * self.local_experts)
+        else:
+            gate_up = ops.linear_bf16(normed, self.w13d)
+            inter = gate_up.shape[1] // 2
+            out = ops.linear_bf16(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]), self.w2d)
+        return self._all_reduce(out)
+
+    # -- the stack ----------------------------------------------------------------------------
+    def forward_stack(self, hidden: torch.Tensor, positions: torch.Tensor, layers: int) -> torch.Tensor:
+        """hidden [T, H] bf16 -> hidden after `layers` applications of the layer
+        (racetrack/realistic_bench.py:354-389,420-423)."""
+        s = self.shape
+        normed = ops.fused_rms_norm(hidden, self.ones_h, eps=s.eps)
+        for layer in range(layers):
+            attn = self.attention(normed, positions)
+            normed, hidden = ops.fused_residual_norm(attn, hidden, self.ones_h, eps=s.eps)
+            ffn = self.ffn_forward(normed)
+            # the add closing this layer and the rms_norm opening the next one, in one pass
+            normed, hidden = ops.fused_residual_norm(ffn, hidden, self.ones_h, eps=s.eps)
+        return hidden

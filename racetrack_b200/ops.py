@@ -398,7 +398,8 @@ def fused_moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], *, n_gro
     tokens, n_experts = logits.shape
     weights = torch.empty(tokens, topk, dtype=torch.float32, device=logits.device)
     indices = torch.empty(tokens, topk, dtype=torch.int64, device=logits.device)
-    func = {"sigmoid": _lib.RT_SCORE_SIGMOID, "softmax": _lib.RT_SCORE_SOFTMAX}[score_func]
+    func = {"sigmoid": _lib.RT_SCORE_SIGMOID, "softmax": _lib.RT_SCORE_SOFTMAX,
+            "topk_softmax": _lib.RT_SCORE_TOPK_SOFTMAX}[score_func]
     lib = _lib.load()
     _lib.check(lib.rt_moe_route(logits.data_ptr(), bias.data_ptr() if bias is not None else None,
                                 weights.data_ptr(), indices.data_ptr(), tokens, n_experts,
@@ -445,9 +446,12 @@ def fused_moe_gather(x: torch.Tensor, sorted_pairs: torch.Tensor, topk: int) -> 
 
 def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor,
                       shared: Optional[torch.Tensor] = None, *, pos_begin: int = 0,
-                      pos_end: Optional[int] = None) -> torch.Tensor:
+                      pos_end: Optional[int] = None,
+                      pos_window: Optional[tuple] = None) -> torch.Tensor:
     """y[t] = sum_s weights[t, s] * expert_out[pair_pos[t, s]] (+ shared[t]);
-    racetrack/models/deepseek.py:1018-1022."""
+    racetrack/models/deepseek.py:1018-1022. ``pos_window`` = (begin, end) as 1-element int32
+    CUDA tensors (entries of expert_offsets) restricts the sum to an expert-parallel rank's
+    slice of the sorted range without a host read-back."""
     _require_cuda(expert_out, pair_pos, weights)
     _require_bf16("fused_moe_combine", expert_out)
     tokens, topk = weights.shape
@@ -463,7 +467,10 @@ def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights:
     lib = _lib.load()
     _lib.check(lib.rt_moe_combine(expert_out.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(),
                                   shared.data_ptr() if shared is not None else None, y.data_ptr(),
-                                  tokens, topk, cols, pos_begin, pos_end, _lib.RT_BF16, _stream()),
+                                  tokens, topk, cols, pos_begin, pos_end,
+                                  pos_window[0].data_ptr() if pos_window is not None else None,
+                                  pos_window[1].data_ptr() if pos_window is not None else None,
+                                  _lib.RT_BF16, _stream()),
                "rt_moe_combine")
     return y
 
