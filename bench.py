@@ -2,15 +2,17 @@
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload NAME]
 
-One JSON line on stdout (rank 0). A "step" is one pass of the hot path over one batch of
-synthetic, seeded input. `value` is whole-job tokens/s with inputs resident in HBM; `e2e` is
-the same metric through the public op API with HOST buffers (pinned host -> device copy of
-the step's input and device -> host read of its result inside the timed region).
-`--impl reference` times racetrack's own vanilla-torch CPU path (restated in oracle/) on the
-host cores, on a bounded sample of the same workload.
+One JSON line on stdout (rank 0). Default workload `dsv3_2_prefill_stack`: the realistic prefill
+stack of racetrack/realistic_bench.py at T = 8192 tokens, hidden 7168, one synthetic
+DeepSeek-V3.2 layer (MLA attention + 256-expert top-8 MoE, NVFP4 experts) reused for 61 layers;
+a step is one forward of the whole stack. Metric: tokens * layers / second, the reference
+runner's own figure (racetrack/realistic_bench.py:557). `value` has the input resident in HBM;
+`e2e` moves the step's hidden states from pinned host memory and reads the result back inside
+the timed region. Under torchrun (N > 1) attention heads are tensor-parallel and experts
+expert-parallel with NCCL all-reduces, tokens replicated: total work is fixed (strong scaling).
 
-Under torchrun (N > 1) every rank processes its own batch of the same shape (weak scaling,
-no data-path collective: the workload is a row-partitioned stream); time is the max over ranks.
+`--impl reference` times racetrack's own vanilla-torch CPU path (restated in oracle/) on the
+host cores, on a bounded sample (a few tokens, one layer) of the same workload.
 """
 from __future__ import annotations
 
@@ -29,14 +31,10 @@ ROOT = Path(__file__).resolve().parent
 if str(ROOT) not in sys.path:
     sys.path.insert(0, str(ROOT))
 
-METRIC = "dsv3_2_hot_path_tokens_per_s"
-UNIT = "tokens/s"
+UNIT = "tokens*layers/s"
 FALLBACK_HBM_GBS = 6650.0
+CPU_SAMPLE_TOKENS = 8
 
-
-# ---------------------------------------------------------------------------
-# helpers
-# ---------------------------------------------------------------------------
 
 def measured_peaks() -> tuple[float, str]:
     p = ROOT / "MEASURED_PEAKS.json"
@@ -105,31 +103,151 @@ class ClockSampler(threading.Thread):
 
 
 # ---------------------------------------------------------------------------
+# workload: realistic prefill stack (default)
+# ---------------------------------------------------------------------------
+
+class PrefillStackWorkload:
+    """T tokens through `layers` applications of one synthetic DeepSeek-V3.2 layer."""
+    name = "dsv3_2_prefill_stack"
+    metric = "dsv3_2_layer_tokens_per_s"
+    scaling = "strong"
+    dominant = "gemm_nvfp4_kernel[experts w13]"
+
+    def __init__(self, device, rank: int, world: int, args):
+        from racetrack_b200 import layer, moe, ops
+        self.layer_mod, self.moe, self.ops = layer, moe, ops
+        self.device, self.rank, self.world = device, rank, world
+        self.tokens, self.layers = args.tokens, args.layers
+        self.shape = layer.DSV32
+        w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02)
+        w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
+        self.model = layer.RealisticLayer(self.shape, w, rank, world)
+        gen = torch.Generator(device=device)
+        gen.manual_seed(self.shape.seed)
+        self.hidden = torch.empty(self.tokens, self.shape.hidden, device=device, dtype=torch.bfloat16)
+        self.hidden.normal_(mean=0.0, std=0.01, generator=gen)
+        self.positions = torch.arange(self.tokens, device=device, dtype=torch.int64)
+        self.dom_events = []
+        self._wrap_dominant()
+
+    def _wrap_dominant(self):
+        """CUDA events around every first expert GEMM (w13) of the timed region."""
+        ops, inter2 = self.ops, 2 * self.shape.moe_inter
+        inner = ops.gemm_nvfp4_grouped
+        wl = self
+
+        def timed(*a, **kw):
+            if wl.recording and kw.get("n") == inter2:
+                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s.record()
+                out = inner(*a, **kw)
+                e.record()
+                wl.dom_events.append((s, e))
+                return out
+            return inner(*a, **kw)
+
+        self.recording = False
+        ops.gemm_nvfp4_grouped = timed
+
+    @property
+    def units_per_step(self) -> int:
+        return self.tokens * self.layers
+
+    @property
+    def dominant_bytes(self) -> int:
+        s = self.shape
+        e_loc = s.n_experts // self.world
+        pairs_local = self.tokens * s.topk // self.world       # expected rows of this rank
+        weights = e_loc * 2 * s.moe_inter * s.hidden * 9 // 16   # e2m1 codes + e4m3 scales
+        acts = pairs_local * s.hidden * 9 // 16
+        out = pairs_local * 2 * s.moe_inter * 2
+        return weights + acts + out
+
+    def config(self) -> dict:
+        s = self.shape
+        return {"workload": self.name, "tokens": self.tokens, "layers": self.layers,
+                "hidden": s.hidden, "heads": s.heads, "experts": s.n_experts, "topk": s.topk,
+                "moe_inter": s.moe_inter, "experts_dtype": "nvfp4", "projections_dtype": "bf16",
+                "attention_core": "torch sdpa (not a kernel of this backend)",
+                "routing": "topk_softmax (racetrack/realistic_bench.py:321-327)",
+                "l2_policy": "inputs_exceed_l2 (6.3 GB of expert weights + 117 MB of hidden "
+                             "states stream through the 126 MB L2 every layer)"}
+
+    def step(self, record: bool = False):
+        self.recording = record
+        out = self.model.forward_stack(self.hidden, self.positions, self.layers)
+        self.recording = False
+        return out
+
+    def e2e_setup(self):
+        self.host_in = torch.empty(self.hidden.shape, dtype=torch.bfloat16, pin_memory=True)
+        self.host_in.copy_(self.hidden)
+        self.dev_in = torch.empty_like(self.hidden)
+        self.host_out = torch.empty(self.hidden.shape, dtype=torch.bfloat16, pin_memory=True)
+
+    def e2e_step(self):
+        self.dev_in.copy_(self.host_in, non_blocking=True)
+        out = self.model.forward_stack(self.dev_in, self.positions, self.layers)
+        self.host_out.copy_(out, non_blocking=True)
+        return out
+
+    def e2e_bytes(self):
+        n = self.host_in.numel() * self.host_in.element_size()
+        return n, n
+
+    @staticmethod
+    def cpu_runner(sample_tokens: int):
+        """The reference's vanilla-torch layer (oracle/ref_layer.py) on `sample_tokens` tokens,
+        one layer, full width. Only the experts the sample routes to are materialised."""
+        from oracle import ref_layer, ref_ops as R
+        from racetrack_b200 import layer
+        shape = layer.DSV32
+        w = layer.make_weights(shape, 0, 1, "cpu", ffn="none", std=0.02)
+        g = torch.Generator().manual_seed(shape.seed)
+        hidden = (torch.randn(sample_tokens, shape.hidden, generator=g) * 0.01).to(torch.bfloat16)
+        pos = torch.arange(sample_tokens, dtype=torch.int64)
+        ones = torch.ones(shape.hidden, dtype=torch.bfloat16)
+        # routing of the sample decides which experts need weights
+        h = R.rms_norm(hidden, ones, shape.eps)
+        mid = hidden + ref_layer.attention(h, pos, w, shape, shape.heads)
+        logits = torch.nn.functional.linear(R.rms_norm(mid, ones, shape.eps).float(), w["w_gate"].float())
+        used = sorted(set(torch.topk(logits, shape.topk, dim=-1)[1].flatten().tolist()))
+        w["w13"] = torch.empty(shape.n_experts, 2 * shape.moe_inter, shape.hidden, dtype=torch.bfloat16)
+        w["w2"] = torch.empty(shape.n_experts, shape.hidden, shape.moe_inter, dtype=torch.bfloat16)
+        for e in used:
+            w["w13"][e], w["w2"][e] = layer.draw_expert(shape, e, "cpu", std=0.02)
+
+        def run():
+            return ref_layer.forward_stack(hidden, pos, [w], shape, 1)
+        return run, sample_tokens * 1
+
+
+# ---------------------------------------------------------------------------
 # workload: SwiGLU + activation quantisation at T=4096 (gate_up [T, 2*18432] bf16)
 # ---------------------------------------------------------------------------
 
 class SwigluQuantWorkload:
-    """silu(gate)*up -> FP8 e4m3 per-128 codes+scales and NVFP4 codes+block scales+global scale.
-
-    Per step (T tokens): one fused SwiGLU+FP8-quant launch, one abs-max launch pair and one
-    fused SwiGLU+NVFP4-quant launch. Algorithmic bytes of the dominant kernel
-    (swiglu_quant_fp8): 2*T*I*2 read + T*I + T*(I/128)*4 written.
-    """
+    """silu(gate)*up -> FP8 e4m3 per-128 codes+scales and NVFP4 codes+block scales+global scale."""
     name = "swiglu_act_quant_T4096_I18432"
-    tokens = 4096
-    inter = 18432
+    metric = "dsv3_2_swiglu_quant_tokens_per_s"
+    scaling = "weak"
     dominant = "quant_fp8_kernel<swiglu>"
+    tokens_default = 4096
+    inter = 18432
 
-    def __init__(self, device: torch.device, seed: int):
+    def __init__(self, device, rank: int, world: int, args):
         from racetrack_b200 import ops
         self.ops = ops
-        self.device = device
+        self.tokens, self.layers = self.tokens_default, 1
         gen = torch.Generator(device=device)
-        gen.manual_seed(seed)
+        gen.manual_seed(38595 + rank)
         self.gate_up = torch.empty(self.tokens, 2 * self.inter, device=device, dtype=torch.bfloat16)
         self.gate_up.normal_(generator=gen)
-        self.dom_events: list[tuple[torch.cuda.Event, torch.cuda.Event]] = []
-        self.host_in = None
+        self.dom_events = []
+
+    @property
+    def units_per_step(self) -> int:
+        return self.tokens
 
     @property
     def dominant_bytes(self) -> int:
@@ -137,11 +255,11 @@ class SwigluQuantWorkload:
         return 2 * t * i * 2 + t * i + t * (i // 128) * 4
 
     def config(self) -> dict:
-        return {"workload": self.name, "tokens_per_step": self.tokens, "inter": self.inter,
+        return {"workload": self.name, "tokens": self.tokens, "inter": self.inter,
                 "outputs": "fp8_e4m3_per128+nvfp4_block16",
                 "l2_policy": "inputs_exceed_l2 (302 MB gate_up per step vs 126 MB L2)"}
 
-    def _run(self, gate_up: torch.Tensor, record: bool):
+    def _run(self, gate_up, record):
         ops, i = self.ops, self.inter
         g, u = gate_up[:, :i], gate_up[:, i:]
         if record:
@@ -157,13 +275,11 @@ class SwigluQuantWorkload:
     def step(self, record: bool = False):
         return self._run(self.gate_up, record)
 
-    # end to end: pinned host input -> device, kernels, results back to pinned host
     def e2e_setup(self):
         self.host_in = torch.empty(self.gate_up.shape, dtype=torch.bfloat16, pin_memory=True)
         self.host_in.copy_(self.gate_up)
         self.dev_in = torch.empty_like(self.gate_up)
-        outs = self.step()
-        self.host_out = [torch.empty(o.shape, dtype=o.dtype, pin_memory=True) for o in outs]
+        self.host_out = [torch.empty(o.shape, dtype=o.dtype, pin_memory=True) for o in self.step()]
 
     def e2e_step(self):
         self.dev_in.copy_(self.host_in, non_blocking=True)
@@ -172,71 +288,54 @@ class SwigluQuantWorkload:
             h.copy_(o, non_blocking=True)
         return outs
 
-    def e2e_bytes(self) -> tuple[int, int]:
-        h2d = self.host_in.numel() * self.host_in.element_size()
-        d2h = sum(h.numel() * h.element_size() for h in self.host_out)
-        return h2d, d2h
+    def e2e_bytes(self):
+        return (self.host_in.numel() * 2,
+                sum(h.numel() * h.element_size() for h in self.host_out))
 
-    # CPU legs (oracle = restated reference torch path)
     @staticmethod
-    def cpu_step(sample_tokens: int, inter: int, seed: int):
+    def cpu_runner(sample_tokens: int):
         from oracle import inputs as I, ref_ops as R
-        d = I.swiglu_quant_inputs(sample_tokens, inter, seed=seed)
+        sample_tokens = 256
+        d = I.swiglu_quant_inputs(sample_tokens, SwigluQuantWorkload.inter)
 
         def run():
             R.swiglu_quant(d["gate"], d["up"])
-            h = R.swiglu(d["gate"], d["up"])
-            R.nvfp4_quant(h)
-        return run
+            R.nvfp4_quant(R.swiglu(d["gate"], d["up"]))
+        return run, sample_tokens
 
 
-WORKLOADS = {SwigluQuantWorkload.name: SwigluQuantWorkload}
-DEFAULT_WORKLOAD = SwigluQuantWorkload.name
+WORKLOADS = {w.name: w for w in (PrefillStackWorkload, SwigluQuantWorkload)}
+DEFAULT_WORKLOAD = PrefillStackWorkload.name
 
 
-def time_cpu(run, sample_tokens: int, min_seconds: float = 3.0, max_iters: int = 50):
-    run()  # warm-up
-    n, t0 = 0, time.perf_counter()
-    while True:
+def cpu_line(wl_cls, steps: int, warmup: int) -> dict:
+    run, units = wl_cls.cpu_runner(CPU_SAMPLE_TOKENS)
+    for _ in range(max(warmup, 1)):
         run()
-        n += 1
-        dt = time.perf_counter() - t0
-        if dt >= min_seconds or n >= max_iters:
-            break
-    return sample_tokens * n / dt, dt / n
-
-
-# ---------------------------------------------------------------------------
-# arms
-# ---------------------------------------------------------------------------
-
-def run_reference(args) -> None:
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
-        return
-    wl = WORKLOADS[args.workload]
-    sample = 256
-    run = wl.cpu_step(sample, wl.inter, 38595)
-    for _ in range(max(args.warmup, 1) - 1):
-        run()
-    run()
     t0 = time.perf_counter()
-    for _ in range(args.steps):
+    for _ in range(steps):
         run()
     dt = time.perf_counter() - t0
-    value = sample * args.steps / dt
     cores = torch.get_num_threads()
+    return {"value": units * steps / dt, "unit": UNIT, "cores": cores, "kind": "port",
+            "ms_per_step": 1e3 * dt / steps,
+            "sample": f"{units} token(s) x 1 layer per step at full width, torch CPU "
+                      f"(oracle/ref_layer.py), {cores} threads of {os.cpu_count()} logical cores"}
+
+
+def run_reference(args) -> None:
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    wl = WORKLOADS[args.workload]
+    cpu = cpu_line(wl, args.steps, args.warmup)
     line = {
-        "impl": "reference", "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * dt / args.steps,
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
-        "data": "synthetic",
-        "config": {"workload": wl.name, "tokens_per_step": sample, "inter": wl.inter,
-                   "device": "host CPU"},
-        "cpu_baseline": {"value": value, "unit": UNIT, "cores": cores, "kind": "port",
-                         "sample": f"{sample} of {wl.tokens} tokens per step, torch CPU, "
-                                   f"{cores} threads of {os.cpu_count()} logical cores"},
-        "e2e": {"value": value, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": wl.metric, "value": cpu["value"], "unit": UNIT,
+        "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": cpu.pop("ms_per_step"), "higher_is_better": True, "scaling": wl.scaling,
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": wl.name, "device": "host CPU", "sample": cpu["sample"]},
+        "cpu_baseline": cpu,
+        "e2e": {"value": cpu["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
     }
     print(json.dumps(line), flush=True)
@@ -269,10 +368,9 @@ def run_ours(args) -> None:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
-    wl = WORKLOADS[args.workload](device, 38595 + rank)
     _lib.load()
+    wl = WORKLOADS[args.workload](device, rank, world, args)
 
-    # ---- device-resident timing -------------------------------------------------
     for _ in range(args.warmup):
         wl.step()
     barrier()
@@ -289,12 +387,11 @@ def run_ours(args) -> None:
     ms_total = max_over_ranks(start.elapsed_time(end))
     dom_us = statistics.mean(s.elapsed_time(e) for s, e in wl.dom_events) * 1e3
 
-    # ---- end to end (host buffers) ------------------------------------------------
     wl.e2e_setup()
-    for _ in range(min(args.warmup, 3)):
+    for _ in range(min(args.warmup, 2)):
         wl.e2e_step()
     barrier()
-    e2e_steps = max(3, min(args.steps, 20))
+    e2e_steps = max(2, min(args.steps, 5))
     s2, e2 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     s2.record()
     for _ in range(e2e_steps):
@@ -304,35 +401,37 @@ def run_ours(args) -> None:
     e2e_ms = max_over_ranks(s2.elapsed_time(e2))
     clocks = sampler.stop()
     h2d, d2h = wl.e2e_bytes()
+    from racetrack_b200 import ops
+    ops.tc_error_state()
 
     if rank == 0:
         peak, peak_src = measured_peaks()
         achieved = wl.dominant_bytes / (dom_us * 1e-6) / 1e9
         line = {
-            "metric": METRIC,
-            "value": world * wl.tokens * args.steps / (ms_total * 1e-3),
+            "metric": wl.metric,
+            "value": wl.units_per_step * args.steps / (ms_total * 1e-3)
+                     * (world if wl.scaling == "weak" else 1),
             "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": args.warmup,
-            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": "weak",
+            "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": wl.scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {**wl.config(), "parallelism": f"replicated-stream x{world}"},
+            "config": {**wl.config(),
+                       "parallelism": f"tp{world}(heads)+ep{world}(experts)" if wl.scaling == "strong"
+                       else f"replicated-stream x{world}"},
             "roofline": {"bound": "hbm", "kernel": wl.dominant, "achieved": achieved, "peak": peak,
                          "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-                         "traffic": None, "avg_launch_us": dom_us,
+                         "traffic": None, "avg_launch_us": dom_us, "launches_timed": len(wl.dom_events),
                          "algorithmic_bytes": wl.dominant_bytes},
-            "e2e": {"value": world * wl.tokens * e2e_steps / (e2e_ms * 1e-3), "unit": UNIT,
-                    "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h, "steps": e2e_steps},
+            "e2e": {"value": wl.units_per_step * e2e_steps / (e2e_ms * 1e-3)
+                             * (world if wl.scaling == "weak" else 1),
+                    "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "steps": e2e_steps},
             "gpu_launches": launches,
             "clocks": clocks,
         }
-        if world == 1:
-            sample = 256
-            run = wl.cpu_step(sample, wl.inter, 38595)
-            cpu_value, _ = time_cpu(run, sample)
-            cores = torch.get_num_threads()
-            line["cpu_baseline"] = {
-                "value": cpu_value, "unit": UNIT, "cores": cores, "kind": "port",
-                "sample": f"{sample} of {wl.tokens} tokens per step, torch CPU, {cores} threads "
-                          f"of {os.cpu_count()} logical cores"}
+        if world == 1 and not args.no_cpu:
+            cpu = cpu_line(type(wl), 3, 1)
+            cpu.pop("ms_per_step")
+            line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
     if distributed:
         dist.destroy_process_group()
@@ -341,10 +440,13 @@ def run_ours(args) -> None:
 def main() -> None:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=50)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=("ours", "reference"))
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--layers", type=int, default=61)
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -74,13 +74,31 @@ def moe(hidden, w, shape, rank, local_experts):
     return local
 
 
+def moe_nvfp4(hidden, w, shape, rank, local_experts):
+    """Same routing as `moe`, experts evaluated on NVFP4-quantised operands
+    (ref_ops.moe_experts_nvfp4): what the B200 layer computes, for tight comparisons. The
+    NVFP4 arithmetic has no reference counterpart (parity unpinned)."""
+    s = shape
+    logits = F.linear(hidden.float(), w["w_gate"].float())
+    topk_logits, topk_ids = torch.topk(logits, s.topk, dim=-1)
+    topk_weights = torch.softmax(topk_logits, dim=-1).to(hidden.dtype).float()
+    n = s.n_experts
+    w13 = torch.zeros(n, *w["w13"].shape[1:], dtype=w["w13"].dtype)
+    w2 = torch.zeros(n, *w["w2"].shape[1:], dtype=w["w2"].dtype)
+    lo, hi = rank * local_experts, (rank + 1) * local_experts
+    w13[lo:hi], w2[lo:hi] = w["w13"], w["w2"]
+    return R.moe_experts_nvfp4(hidden, topk_weights, topk_ids, w13, w2, expert_range=(lo, hi))
+
+
 def dense_ffn(hidden, w):
     """Dense SwiGLU FFN shard (the first-layers variant): w2(silu(w1 x) * w3 x)."""
     return F.linear(F.silu(F.linear(hidden, w["w1"])) * F.linear(hidden, w["w3"]), w["w2d"])
 
 
-def forward_stack(hidden, positions, rank_weights, shape, layers, ffn="moe"):
-    """ref: racetrack/realistic_bench.py:375-389 (hc_mult == 1 branch) applied `layers` times."""
+def forward_stack(hidden, positions, rank_weights, shape, layers, ffn="moe", experts="bf16"):
+    """ref: racetrack/realistic_bench.py:375-389 (hc_mult == 1 branch) applied `layers` times.
+    experts="nvfp4" swaps the bf16 expert matmuls for their NVFP4-quantised evaluation."""
+    moe_fn = moe if experts == "bf16" else moe_nvfp4
     world = len(rank_weights)
     ones = torch.ones(shape.hidden, dtype=hidden.dtype)
     local_heads = shape.heads // world
@@ -93,7 +111,7 @@ def forward_stack(hidden, positions, rank_weights, shape, layers, ffn="moe"):
         residual = hidden
         h = R.rms_norm(hidden, ones, shape.eps)
         if ffn == "moe":
-            out = _all_reduce([moe(h, w, shape, r, local_experts) for r, w in enumerate(rank_weights)])
+            out = _all_reduce([moe_fn(h, w, shape, r, local_experts) for r, w in enumerate(rank_weights)])
         else:
             out = _all_reduce([dense_ffn(h, w) for w in rank_weights])
         hidden = residual + out

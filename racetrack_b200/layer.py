@@ -70,6 +70,14 @@ def _draw(shape, seed: int, std: float, device, dtype) -> torch.Tensor:
     return w.to(dtype)
 
 
+def draw_expert(shape: LayerShape, e: int, device, *, std: float = 0.02,
+                dtype: torch.dtype = torch.bfloat16):
+    """(w13 [2I, H], w2 [H, I]) of routed expert `e`; the same values whatever rank draws them."""
+    s = shape
+    return (_draw((2 * s.moe_inter, s.hidden), s.seed + 10000 + 2 * e, std, device, dtype),
+            _draw((s.hidden, s.moe_inter), s.seed + 10001 + 2 * e, std, device, dtype))
+
+
 def make_weights(shape: LayerShape, rank: int, world: int, device, *, ffn: str = "moe",
                  std: float = 0.02, dtype: torch.dtype = torch.bfloat16) -> dict:
     """The weights rank `rank` of `world` owns, drawn unit by unit (see the module docstring).
@@ -92,17 +100,36 @@ def make_weights(shape: LayerShape, rank: int, world: int, device, *, ffn: str =
                           for u in units], dim=1)
     if ffn == "moe":
         e_loc = s.n_experts // world
-        experts = range(rank * e_loc, (rank + 1) * e_loc)
-        w["w13"] = torch.stack([_draw((2 * s.moe_inter, s.hidden), seed + 10000 + 2 * e, std, device, dtype)
-                                for e in experts])
-        w["w2"] = torch.stack([_draw((s.hidden, s.moe_inter), seed + 10001 + 2 * e, std, device, dtype)
-                               for e in experts])
-    else:
+        experts = [draw_expert(s, e, device, std=std, dtype=dtype)
+                   for e in range(rank * e_loc, (rank + 1) * e_loc)]
+        w["w13"] = torch.stack([e[0] for e in experts])
+        w["w2"] = torch.stack([e[1] for e in experts])
+    elif ffn == "dense":
         ipu = s.dense_inter // s.units
         w["w1"] = torch.cat([_draw((ipu, s.hidden), seed + 400 + u, std, device, dtype) for u in units])
         w["w3"] = torch.cat([_draw((ipu, s.hidden), seed + 500 + u, std, device, dtype) for u in units])
         w["w2d"] = torch.cat([_draw((s.hidden, ipu), seed + 600 + u, std, device, dtype) for u in units], dim=1)
     return w
+
+
+def make_nvfp4_experts(shape: LayerShape, rank: int, world: int, device, *,
+                       std: float = 0.02) -> "moe.NVFP4Experts":
+    """The rank's routed experts drawn and quantised one at a time, so that the bf16 weights of
+    only one expert exist at any moment (all 256 experts in bf16 would take 22.5 GB)."""
+    s = shape
+    e_loc = s.n_experts // world
+    parts13, parts2 = [], []
+    for e in range(rank * e_loc, (rank + 1) * e_loc):
+        w13, w2 = draw_expert(s, e, device, std=std)
+        parts13.append(ops.fused_nvfp4_quant(w13, tiled_scales=True))
+        parts2.append(ops.fused_nvfp4_quant(w2, tiled_scales=True))
+    cat = torch.cat
+    return moe.NVFP4Experts(
+        e_loc, s.hidden, s.moe_inter,
+        cat([p[0] for p in parts13]), cat([p[1].view(torch.uint8) for p in parts13]),
+        cat([p[2] for p in parts13]),
+        cat([p[0] for p in parts2]), cat([p[1].view(torch.uint8) for p in parts2]),
+        cat([p[2] for p in parts2]))
 
 
 def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
@@ -137,7 +164,8 @@ class RealisticLayer:
         self.kv_norm = torch.ones(shape.kv_lora, device=dev, dtype=torch.bfloat16)
         if ffn == "moe":
             self.local_experts = shape.n_experts // world
-            self.experts = moe.quantize_experts(weights["w13"], weights["w2"])
+            self.experts = weights["experts"] if "experts" in weights else \
+                moe.quantize_experts(weights["w13"], weights["w2"])
         else:
             self.w13d = torch.cat([weights["w1"], weights["w3"]]).contiguous()
             self.w2d = weights["w2d"].contiguous()

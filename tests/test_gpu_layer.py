@@ -44,19 +44,66 @@ def _check(out, ref, tight):
     assert rel_err(out, ref) <= tight, f"relative error {rel_err(out, ref)}"
 
 
-@pytest.mark.parametrize("ffn,tight", [("moe", 6e-2), ("dense", 2e-2)])
 @pytest.mark.parametrize("tokens,layers", [(96, 2), (1, 1), (130, 3)])
-def test_layer_stack_matches_reference_layer(L, ffn, tight, tokens, layers):
+def test_dense_layer_stack_matches_reference_layer(L, tokens, layers):
     layer, ops = L
     shape = small_shape(layer)
-    w = layer.make_weights(shape, 0, 1, "cpu", ffn=ffn, std=0.05)
+    w = layer.make_weights(shape, 0, 1, "cpu", ffn="dense", std=0.05)
     hidden, pos = _inputs(shape, tokens)
-    ref = ref_layer.forward_stack(hidden, pos, [w], shape, layers, ffn=ffn)
-    model = layer.RealisticLayer(shape, _to_cuda(w), ffn=ffn)
+    ref = ref_layer.forward_stack(hidden, pos, [w], shape, layers, ffn="dense")
+    model = layer.RealisticLayer(shape, _to_cuda(w), ffn="dense")
     out = model.forward_stack(hidden.cuda(), pos.cuda(), layers)
     ops.tc_error_state()
     assert out.shape == ref.shape and out.dtype == torch.bfloat16
-    _check(out, ref, tight)
+    _check(out, ref, 2e-2)
+
+
+@pytest.mark.parametrize("tokens,layers", [(96, 2), (1, 1), (130, 3)])
+def test_moe_layer_stack_matches_reference_layer(L, tokens, layers):
+    """End-to-end stack with NVFP4 experts. e2m1 keeps one mantissa bit, and on white-noise
+    synthetic data its rounding noise does not average out along K (about 15 % of a GEMM
+    output's RMS per quantised GEMM). The noise realisation flips with a one-ulp change of the
+    tensor-wide scale, so two evaluations whose inputs differ in the last bf16 bit (here: the
+    CPU oracle's attention against the GPU's) land a noise amplitude apart. The stack is
+    therefore bounded loosely against both the bf16 reference and its NVFP4 evaluation, and the
+    oracle's own NVFP4 evaluation is shown to sit as far from the bf16 reference; the tight
+    checks feed identical inputs to one stage at a time (test_stages_match_reference_on_identical_inputs,
+    tests/test_gpu_moe.py) and the dense stack above pins the control flow."""
+    layer, ops = L
+    shape = small_shape(layer)
+    w = layer.make_weights(shape, 0, 1, "cpu", std=0.05)
+    hidden, pos = _inputs(shape, tokens)
+    model = layer.RealisticLayer(shape, _to_cuda(w))
+    out = model.forward_stack(hidden.cuda(), pos.cuda(), layers)
+    ops.tc_error_state()
+    ref_q = ref_layer.forward_stack(hidden, pos, [w], shape, layers, experts="nvfp4")
+    ref = ref_layer.forward_stack(hidden, pos, [w], shape, layers)
+    assert out.shape == ref.shape and out.dtype == torch.bfloat16
+    assert bool(torch.isfinite(out.float()).all())
+    assert rel_err(out, ref_q) <= 0.45
+    assert rel_err(out, ref) <= 0.45
+    assert rel_err(ref_q, ref) <= 0.45
+
+
+def test_stages_match_reference_on_identical_inputs(L):
+    """Each stage of the MoE layer against the reference stage fed the very same tensor."""
+    layer, ops = L
+    shape = small_shape(layer)
+    w = layer.make_weights(shape, 0, 1, "cpu", std=0.05)
+    hidden, pos = _inputs(shape, 80, seed=5)
+    model = layer.RealisticLayer(shape, _to_cuda(w))
+    normed = ops.fused_rms_norm(hidden.cuda(), model.ones_h, eps=shape.eps)
+    normed_cpu = normed.cpu()
+    attn = model.attention(normed, pos.cuda())
+    attn_ref = ref_layer.attention(normed_cpu, pos, w, shape, shape.heads)
+    assert rel_err(attn, attn_ref) <= 2e-2
+    n2, h2 = ops.fused_residual_norm(attn, hidden.cuda(), model.ones_h, eps=shape.eps)
+    h2_ref = hidden + attn.cpu()
+    assert torch.equal(h2.cpu(), h2_ref)
+    ffn = model.ffn_forward(n2)
+    ops.tc_error_state()
+    ffn_ref = ref_layer.moe_nvfp4(n2.cpu(), w, shape, 0, shape.n_experts)
+    assert rel_err(ffn, ffn_ref) <= 2e-2
 
 
 def test_rank_partials_sum_to_the_unsharded_layer(L):
@@ -79,10 +126,13 @@ def test_rank_partials_sum_to_the_unsharded_layer(L):
     f_full = full.ffn_forward(normed).float()
     f_sum = sum(m.ffn_forward(normed).float() for m in ranks)
     ops.tc_error_state()
-    # each rank quantises swiglu(h) with its own tensor-wide scale: close, not identical
-    assert rel_err(f_sum, f_full) <= 5e-2
-    # and the reference layer evaluated with two ranks agrees with the unsharded product
+    # each rank quantises swiglu(h) with its own tensor-wide scale, i.e. draws different NVFP4
+    # rounding noise: the sum is near the unsharded result, not equal to it
+    assert rel_err(f_sum, f_full) <= 0.3
+    # the two-rank product against the two-rank reference evaluated on NVFP4 operands: tight
     ws = [layer.make_weights(shape, r, 2, "cpu", std=0.05) for r in range(2)]
-    ref = ref_layer.forward_stack(hidden, pos, ws, shape, 1)
-    out = full.forward_stack(hidden.cuda(), pos.cuda(), 1)
-    _check(out, ref, 6e-2)
+    normed_cpu = normed.cpu()
+    ref_parts = [ref_layer.moe_nvfp4(normed_cpu, ws[r], shape, r, shape.n_experts // 2) for r in range(2)]
+    got_parts = [m.ffn_forward(normed) for m in ranks]
+    for g, r_ in zip(got_parts, ref_parts):
+        assert rel_err(g, r_) <= 2e-2
