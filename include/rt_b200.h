@@ -336,11 +336,14 @@ int rt_moe_combine(const void* expert_out, const int32_t* pair_pos, const float*
  * c[m, n] = a[m, k] * b[n, k]^T, bf16 inputs, fp32 accumulation in tensor memory, bf16
  * output: y = F.linear(x, weight) with x = a and weight = b. lda / ldb / ldc are row
  * pitches in elements. k, n and the pitches must be multiples of 8, pointers 16-byte aligned.
- * ref: racetrack/models/deepseek.py:341-342 (bf16 branch of linear()),
- *      racetrack/realistic_bench.py:288,295,307,315 (F.linear of the MLA projections).
+ * out_dtype RT_BF16 rounds the result to bf16; RT_F32 stores the fp32 accumulators, which is
+ * how the router logits x.float() @ W.float()^T of bf16-valued operands are formed (every
+ * product is exact in fp32, only the summation order differs from an fp32 GEMM).
+ * ref: racetrack/models/deepseek.py:341-342 (bf16 branch of linear()), :898 (Gate logits),
+ *      racetrack/realistic_bench.py:288,295,307,315,321 (F.linear of the MLA projections, router).
  */
 int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                 int64_t lda, int64_t ldb, int64_t ldc, void* stream);
+                 int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, void* stream);
 
 /*
  * Work list of the grouped GEMM, built on the device from the per-expert row offsets

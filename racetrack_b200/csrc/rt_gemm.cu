@@ -45,10 +45,11 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
     tn = local / rows;
 }
 
-template <int BN>
+// F32OUT: c is fp32 (the router logits), otherwise bf16.
+template <int BN, bool F32OUT>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-    __nv_bfloat16* __restrict__ c, int M, int N, int K, int64_t ldc) {
+    void* __restrict__ c_out, int M, int N, int K, int64_t ldc) {
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -162,7 +163,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
             if (!(ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4))) break;
             tc_fence_after();
             const int row = tm * kBM + quad * 32 + lane;
-            __nv_bfloat16* crow = c + static_cast<int64_t>(row) * ldc;
+            __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(c_out) + static_cast<int64_t>(row) * ldc;
+            float* crow_f = static_cast<float*>(c_out) + static_cast<int64_t>(row) * ldc;
 #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; ++chunk) {
                 uint32_t r[32];
@@ -176,6 +178,13 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
                     for (int v = 0; v < 4; ++v) {
                         const int col = col0 + v * 8;
                         if (col < N) {  // N % 8 == 0, so a started vector is complete
+                            if constexpr (F32OUT) {
+                                *reinterpret_cast<uint4*>(crow_f + col) =
+                                    make_uint4(r[8 * v], r[8 * v + 1], r[8 * v + 2], r[8 * v + 3]);
+                                *reinterpret_cast<uint4*>(crow_f + col + 4) =
+                                    make_uint4(r[8 * v + 4], r[8 * v + 5], r[8 * v + 6], r[8 * v + 7]);
+                                continue;
+                            }
                             uint4 o;
                             o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
                             o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
@@ -217,33 +226,28 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
 // routing kernels and this one.
 // Stage = 256 elements of K: 128-byte rows for A and B (128-byte swizzle) plus 4 scale tiles
 // each. tcgen05.mma kind::mxf4nvf4 consumes 64 elements of K per instruction and reads its
-// scale factors from tensor memory, where tcgen05.cp puts them.
+// scale factors from tensor memory. Four extra warps (one per 32-lane quarter of tensor memory)
+// move each stage's scale tiles shared memory -> registers -> tensor memory with one
+// tcgen05.st per warp and stage; every smem stage owns 32 scale columns, so the copy of stage
+// s+1 runs while the MMAs of stage s execute. (Issuing the eight tcgen05.cp per stage from the
+// MMA thread instead serialised with the MMAs and cost a third of the kernel time.)
+// Warps: 0 TMA producer, 1 MMA issuer, 2-5 epilogue, 6-9 scale loaders.
 constexpr int kFBN = 128;                          // tile columns
 constexpr int kFBK = 256;                          // K elements per stage
 constexpr int kFStages = 6;
+constexpr int kFThreads = 320;
 constexpr uint32_t kFTileBytes = 128 * 128;        // A or B codes of a stage
 constexpr uint32_t kFSfBytes = 4 * 512;            // scale tiles of a stage, per operand
 constexpr uint32_t kFStageBytes = 2 * kFTileBytes + 2 * kFSfBytes;
 constexpr uint32_t kFBarOffset = kFStages * kFStageBytes;
-constexpr uint32_t kFSmemBytes = kFBarOffset + (2 * kFStages + 4) * 8 + 16 + 1024;
-constexpr uint32_t kFTmemCols = 512;               // 2 x 128 accumulator + 2 x 32 scale columns
+constexpr uint32_t kFSmemBytes = kFBarOffset + (3 * kFStages + 4) * 8 + 16 + 1024;
+constexpr uint32_t kFTmemCols = 512;               // 2 x 128 accumulator + 6 x 32 scale columns
 constexpr uint32_t kFTmemSf = 256;                 // first scale column
 // block-scaled instruction descriptor: e2m1 x e2m1, e4m3 scales, K-major, N = 128, M = 128
 constexpr uint32_t kFIdesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(kFBN >> 3) << 17) |
                              (static_cast<uint32_t>(kBM >> 4) << 24);
 
-// Shared-memory descriptor of one 512-byte scale tile: 32 rows of 16 bytes, no swizzle,
-// 8-row core matrices 128 bytes apart.
-__device__ __forceinline__ uint64_t smem_desc_sf(uint32_t addr) {
-    uint64_t d = 0;
-    d |= static_cast<uint64_t>((addr & 0x3ffffu) >> 4);
-    d |= static_cast<uint64_t>(1) << 16;
-    d |= static_cast<uint64_t>(128 >> 4) << 32;
-    d |= static_cast<uint64_t>(1) << 46;
-    return d;
-}
-
-__global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(
+__global__ void __launch_bounds__(kFThreads, 1) gemm_nvfp4_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     const uint8_t* __restrict__ sfa, const uint8_t* __restrict__ sfb,
     const float* __restrict__ a_gs, const float* __restrict__ b_gs, __nv_bfloat16* __restrict__ c,
@@ -255,11 +259,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(
     const uint32_t bars = base + kFBarOffset;
     auto full_bar = [&](int s) { return bars + 8u * s; };
     auto empty_bar = [&](int s) { return bars + 8u * (kFStages + s); };
-    auto tfull_bar = [&](int a) { return bars + 8u * (2 * kFStages + a); };
-    auto tempty_bar = [&](int a) { return bars + 8u * (2 * kFStages + 2 + a); };
-    const uint32_t slot = bars + 8u * (2 * kFStages + 4);
+    auto sf_bar = [&](int s) { return bars + 8u * (2 * kFStages + s); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (3 * kFStages + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (3 * kFStages + 2 + a); };
+    const uint32_t slot = bars + 8u * (3 * kFStages + 4);
     volatile uint32_t* slot_ptr =
-        reinterpret_cast<volatile uint32_t*>(base_ptr + kFBarOffset + 8 * (2 * kFStages + 4));
+        reinterpret_cast<volatile uint32_t*>(base_ptr + kFBarOffset + 8 * (3 * kFStages + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -275,6 +280,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(
         for (int s = 0; s < kFStages; ++s) {
             mbar_init(full_bar(s), 1);
             mbar_init(empty_bar(s), 1);
+            mbar_init(sf_bar(s), 4);     // one arrival per scale-loader warp
         }
         for (int a = 0; a < 2; ++a) {
             mbar_init(tfull_bar(a), 1);
@@ -330,24 +336,19 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(
             uint32_t phase = 0;
             int acc = 0;
             uint32_t acc_phase = 0;
-            uint32_t sfbuf = 0;
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 if (!(ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 12))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * kFBN);
                 for (int kb = 0; kb < num_kb; ++kb) {
+                    // codes landed in shared memory, scales landed in tensor memory
                     if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, 13))) break;
+                    if (!(ok = mbar_wait(sf_bar(stage), phase, abort_flag, 15))) break;
                     tc_fence_after();
                     const uint32_t sa = base + stage * kFStageBytes;
-                    const uint32_t t_sfa = tmem_base + kFTmemSf + 32u * sfbuf;
+                    const uint32_t t_sfa = tmem_base + kFTmemSf + 32u * stage;
                     const uint32_t t_sfb = t_sfa + 16u;
-#pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        tmem_cp_32x128b_warpx4(t_sfa + 4u * j, smem_desc_sf(sa + 2 * kFTileBytes + 512u * j));
-                        tmem_cp_32x128b_warpx4(t_sfb + 4u * j,
-                                               smem_desc_sf(sa + 2 * kFTileBytes + kFSfBytes + 512u * j));
-                    }
                     const uint64_t adesc = smem_desc_sw128(sa);
                     const uint64_t bdesc = smem_desc_sw128(sa + kFTileBytes);
 #pragma unroll
@@ -357,7 +358,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(
                                   t_sfb + 4u * j, (kb | j) != 0 ? 1u : 0u);
                     }
                     mma_commit(empty_bar(stage));
-                    sfbuf ^= 1u;
                     if (++stage == kFStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -372,6 +372,36 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_nvfp4_kernel(
             }
         }
         __syncwarp();
+    } else if (warp >= 6) {
+        // Scale loaders: warp w serves the tensor-memory lanes [32*(w%4), +32). A 512-byte scale
+        // tile holds, for lane l, the 16 bytes of rows l, l+32, l+64, l+96 (4 scales each):
+        // exactly the 4 columns the MMA of that 64-element K block reads at lane l.
+        const int quad = warp & 3;
+        int stage = 0;
+        uint32_t phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            for (int kb = 0; kb < num_kb; ++kb) {
+                if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, 16))) break;
+                const uint8_t* sf_smem = base_ptr + stage * kFStageBytes + 2 * kFTileBytes;
+                uint32_t r[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {   // 4 tiles of A scales, then 4 of B scales
+                    const uint4 v = *reinterpret_cast<const uint4*>(sf_smem + j * 512 + lane * 16);
+                    r[4 * j] = v.x; r[4 * j + 1] = v.y; r[4 * j + 2] = v.z; r[4 * j + 3] = v.w;
+                }
+                tmem_st_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kFTmemSf +
+                                  32u * stage, r);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sf_bar(stage));
+                if (++stage == kFStages) {
+                    stage = 0;
+                    phase ^= 1u;
+                }
+            }
+        }
     } else {
         const int quad = warp & 3;
         int acc = 0;
@@ -536,7 +566,7 @@ int sm_count() {
     return n;
 }
 
-template <int BN>
+template <int BN, bool F32OUT>
 static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
                        int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t st) {
     using Cfg = GemmCfg<BN>;
@@ -547,7 +577,7 @@ static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t
         return rc;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN>,
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, F32OUT>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(Cfg::kSmemBytes));
         RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_bf16: %s", cudaGetErrorString(e));
@@ -555,9 +585,8 @@ static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t
     }
     const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    gemm_bf16_kernel<BN><<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(
-        ta, tb, static_cast<__nv_bfloat16*>(c), static_cast<int>(M), static_cast<int>(N),
-        static_cast<int>(K), ldc);
+    gemm_bf16_kernel<BN, F32OUT><<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(
+        ta, tb, c, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldc);
     count_launch();
     return check_launch("gemm_bf16_kernel");
 }
@@ -584,7 +613,7 @@ static int launch_nvfp4(const void* a_codes, const void* a_sf, const float* a_gs
     }
     const int64_t tiles = max_m_tiles * ((N + kFBN - 1) / kFBN);
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
-    gemm_nvfp4_kernel<<<grid, kGemmThreads, kFSmemBytes, st>>>(
+    gemm_nvfp4_kernel<<<grid, kFThreads, kFSmemBytes, st>>>(
         ta, tb, static_cast<const uint8_t*>(a_sf), static_cast<const uint8_t*>(b_sf), a_gs, b_gs,
         static_cast<__nv_bfloat16*>(c), reinterpret_cast<const int4*>(tile_map), tile_count,
         static_cast<int>(N), static_cast<int>(K), ldc);
@@ -639,7 +668,9 @@ extern "C" int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, cons
 }
 
 extern "C" int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,
-                            int64_t lda, int64_t ldb, int64_t ldc, void* stream) {
+                            int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, void* stream) {
+    RT_REQUIRE(out_dtype == RT_BF16 || out_dtype == RT_F32, RT_ERR_UNSUPPORTED,
+               "rt_gemm_bf16: output dtype must be bf16 or f32");
     RT_REQUIRE(m >= 0 && n > 0 && k > 0, RT_ERR_BAD_ARG, "rt_gemm_bf16: bad shape");
     if (m == 0) return RT_OK;
     RT_REQUIRE(a && b && c, RT_ERR_BAD_ARG, "rt_gemm_bf16: null pointer");
@@ -649,8 +680,13 @@ extern "C" int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, in
                "rt_gemm_bf16: pointers must be 16-byte aligned");
     RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_bf16: dimension too large");
-    if (n <= 128) return tc::launch_bf16<128>(a, b, c, m, n, k, lda, ldb, ldc, as_stream(stream));
-    return tc::launch_bf16<256>(a, b, c, m, n, k, lda, ldb, ldc, as_stream(stream));
+    cudaStream_t st = as_stream(stream);
+    if (out_dtype == RT_F32) {
+        if (n <= 128) return tc::launch_bf16<128, true>(a, b, c, m, n, k, lda, ldb, ldc, st);
+        return tc::launch_bf16<256, true>(a, b, c, m, n, k, lda, ldb, ldc, st);
+    }
+    if (n <= 128) return tc::launch_bf16<128, false>(a, b, c, m, n, k, lda, ldb, ldc, st);
+    return tc::launch_bf16<256, false>(a, b, c, m, n, k, lda, ldb, ldc, st);
 }
 
 extern "C" int rt_tc_error_state(void) {

@@ -158,7 +158,7 @@ class RealisticLayer:
         self.w_q_b = weights["w_q_b"].contiguous()
         self.w_kv_b = weights["w_kv_b"].contiguous()
         self.w_o = weights["w_o"].contiguous()
-        self.w_gate_f32 = weights["w_gate"].float().contiguous()
+        self.w_gate = weights["w_gate"].contiguous()
         self.ones_h = torch.ones(shape.hidden, device=dev, dtype=torch.bfloat16)
         self.q_norm = torch.ones(shape.q_lora, device=dev, dtype=torch.bfloat16)
         self.kv_norm = torch.ones(shape.kv_lora, device=dev, dtype=torch.bfloat16)
@@ -199,7 +199,8 @@ class RealisticLayer:
         """racetrack/realistic_bench.py:319-352 (routed experts) or a dense SwiGLU FFN."""
         s = self.shape
         if self.ffn == "moe":
-            logits = F.linear(normed.float(), self.w_gate_f32)
+            # fp32 router logits of bf16 operands: tensor cores with the fp32 accumulators kept
+            logits = ops.linear_bf16(normed, self.w_gate, out_dtype=torch.float32)
             if self.route == "topk_softmax":
                 weights, indices = ops.fused_moe_route(logits, None, n_groups=1, topk_groups=1,
                                                        topk=s.topk, route_scale=1.0,

@@ -138,8 +138,9 @@ def fused_moe_forward(x: torch.Tensor, gate_weight: torch.Tensor, gate_bias: Opt
                       experts: NVFP4Experts, *, n_experts: int, n_groups: int, topk_groups: int,
                       topk: int, route_scale: float, score_func: str = "sigmoid",
                       expert_begin: int = 0, shared: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Gate (fp32 logits GEMM as in racetrack/models/deepseek.py:898) + routing kernel + experts."""
-    logits = torch.nn.functional.linear(x.float(), gate_weight.float())
+    """Gate (fp32 logits as in racetrack/models/deepseek.py:898, formed on the tensor cores from
+    the bf16 operands with the fp32 accumulators kept) + routing kernel + experts."""
+    logits = ops.linear_bf16(x, gate_weight.to(torch.bfloat16), out_dtype=torch.float32)
     weights, indices = ops.fused_moe_route(logits, gate_bias, n_groups=n_groups,
                                            topk_groups=topk_groups, topk=topk,
                                            route_scale=route_scale, score_func=score_func)

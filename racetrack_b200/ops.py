@@ -485,9 +485,11 @@ def tc_error_state() -> None:
     _lib.check(_lib.load().rt_tc_error_state(), "tensor-core kernel")
 
 
-def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
+                out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """F.linear(x, weight) for bf16 x [..., K] and weight [N, K] on the tcgen05 tensor cores
-    (the bf16 branch of racetrack/models/deepseek.py:316-345 `linear`)."""
+    (the bf16 branch of racetrack/models/deepseek.py:316-345 `linear`). out_dtype=torch.float32
+    returns the fp32 accumulators (router logits, racetrack/models/deepseek.py:898)."""
     _require_cuda(x, weight)
     _require_bf16("linear_bf16 x", x)
     _require_bf16("linear_bf16 weight", weight)
@@ -498,10 +500,14 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     w = weight if (weight.stride(1) == 1 and weight.stride(0) % 8 == 0
                    and weight.data_ptr() % 16 == 0) else weight.contiguous()
     n = w.shape[0]
-    out = torch.empty(*x.shape[:-1], n, dtype=x.dtype, device=x.device)
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise RuntimeError("linear_bf16: out_dtype must be bfloat16 or float32")
+    out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
     lib = _lib.load()
     _lib.check(lib.rt_gemm_bf16(x2.data_ptr(), w.data_ptr(), out.data_ptr(), x2.shape[0], n, k,
-                                x2.stride(0), w.stride(0), n, _stream()), "rt_gemm_bf16")
+                                x2.stride(0), w.stride(0), n,
+                                _lib.RT_F32 if out_dtype == torch.float32 else _lib.RT_BF16,
+                                _stream()), "rt_gemm_bf16")
     return out
 
 

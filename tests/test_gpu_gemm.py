@@ -60,6 +60,25 @@ def test_linear_bf16_strided_inputs_and_linearity(ops):
     assert out3.shape == (3, 100, 512) and torch.equal(out3.view(300, 512), out)
 
 
+@pytest.mark.parametrize("m", [4096, 1, 77])
+def test_router_logits_fp32_output(ops, m):
+    """fp32 logits of bf16 hidden states and gate weights ([256, 7168]): every product is exact
+    in fp32; the tensor-core accumulator aligns addends with a few bits less than an IEEE fp32
+    sum, which shows as ~1e-5 of the largest logit."""
+    x = I.randn((m, I.HIDDEN), 9).cuda()
+    w = I.randn((I.N_EXPERTS, I.HIDDEN), 10, std=0.02).cuda()
+    out = ops.linear_bf16(x, w, out_dtype=torch.float32)
+    ops.tc_error_state()
+    assert out.dtype == torch.float32 and out.shape == (m, I.N_EXPERTS)
+    ref = (x.double() @ w.double().t())
+    err = float((out.double() - ref).abs().max() / ref.abs().max())
+    assert err <= 3e-5, f"relative error {err}"
+    # same top-8 as the fp32 reference GEMM except on near-ties
+    ref32 = torch.nn.functional.linear(x.float(), w.float())
+    same = (out.topk(8, dim=-1)[1] == ref32.topk(8, dim=-1)[1]).all(dim=-1).float().mean()
+    assert float(same) >= 0.99
+
+
 # ---------------------------------------------------------------------------
 # NVFP4 block-scaled GEMM
 # ---------------------------------------------------------------------------
