@@ -378,11 +378,15 @@ def run_ours(args) -> None:
     sampler.start()
     launches0 = _lib.launch_count()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if args.profiler_range:      # lets `ncu --profile-from-start off` see the timed steps only
+        torch.cuda.profiler.start()
     start.record()
     for _ in range(args.steps):
         wl.step(record=True)
     end.record()
     barrier()
+    if args.profiler_range:
+        torch.cuda.profiler.stop()
     launches = _lib.launch_count() - launches0
     ms_total = max_over_ranks(start.elapsed_time(end))
     dom_us = statistics.mean(s.elapsed_time(e) for s, e in wl.dom_events) * 1e3
@@ -447,6 +451,8 @@ def main() -> None:
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=61)
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--profiler-range", action="store_true",
+                    help="bracket the timed steps with cudaProfilerStart/Stop")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -1,0 +1,141 @@
+"""The shipped dsv3_2 partition swapped into the synthetic baseline model on a GPU: dispatcher
+path, torch.compile path (FX rewrite to the custom op) and the module patchers, all ending in
+the CUDA kernels."""
+from __future__ import annotations
+
+import pytest
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture
+def cuda_backend(monkeypatch):
+    monkeypatch.setenv("RACETRACK_KERNEL_BACKEND", "cuda")
+
+
+@pytest.fixture(scope="module")
+def spec():
+    from racetrack_b200.partition_spec import discover_partitions
+    return discover_partitions("dsv3_2")[0]
+
+
+def test_baseline_model_with_partition_matches_torch_baseline(spec, cuda_backend):
+    """The reference's smoke criterion: max-abs-diff <= 5e-2 against the torch baseline
+    (racetrack/bench.py:266-268,409)."""
+    from racetrack_b200 import _lib
+    from racetrack_b200.partitions.dsv3_2 import model as syn
+    cfg = syn.DSV3_2_CONFIG
+    base = syn.FlattenedDeepSeekModel(cfg).cuda().to(torch.bfloat16)
+    part = syn.FlattenedDeepSeekModel(cfg, partition_root=spec.partition_dir).cuda().to(torch.bfloat16)
+    part.load_state_dict(base.state_dict())
+    tokens = torch.randint(0, cfg.vocab_size, (128,), device="cuda")
+    with torch.no_grad():
+        want = base(tokens)
+        before = _lib.launch_count()
+        got = part(tokens)
+    assert _lib.launch_count() - before == cfg.num_layers      # one fused_norm_rope launch per layer
+    assert float((got.float() - want.float()).abs().max()) <= 5e-2
+    assert part.backend_status["cuda"] == "native"
+
+
+class Block(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.w1, self.w3, self.w2 = (nn.Linear(512, 1024, bias=False), nn.Linear(512, 1024, bias=False),
+                                     nn.Linear(1024, 512, bias=False))
+
+    def forward(self, x):
+        gate, up = self.w1(x), self.w3(x)
+        return self.w2((F.silu(gate.float()) * up.float()).type_as(gate))
+
+
+def test_torch_compile_rewrites_swiglu_to_the_cuda_kernel(spec, cuda_backend):
+    from racetrack_b200 import _lib, compile_backend
+    model = Block().cuda().to(torch.bfloat16)
+    x = torch.randn(64, 512, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        want = model(x)
+        compiled, originals = compile_backend.compile_with_partition(model, spec, backend_override="cuda")
+        before = _lib.launch_count()
+        got = compiled(x)
+        launches = _lib.launch_count() - before
+    compile_backend.cleanup_compile_state()
+    assert launches == 1, "the silu*mul pair should have become one swiglu kernel launch"
+    assert rel_err(got, want) <= 1e-2
+    assert hasattr(torch.ops.racetrack_b200, "fused_swiglu")
+    assert hasattr(torch.ops.racetrack_b200, "fused_residual_norm")
+    assert hasattr(torch.ops.racetrack_b200, "fused_act_quant")
+    n, h = torch.ops.racetrack_b200.fused_residual_norm(x, x, torch.ones(512, device="cuda"), 1e-6)
+    assert torch.equal(h, x + x)
+    codes, scales = torch.ops.racetrack_b200.fused_act_quant(x)
+    assert codes.dtype == torch.float8_e4m3fn and scales.shape == (64, 4)
+
+
+class Expert(nn.Module):
+    def __init__(self, dim, inter):
+        super().__init__()
+        self.w1, self.w2, self.w3 = (nn.Linear(dim, inter, bias=False), nn.Linear(inter, dim, bias=False),
+                                     nn.Linear(dim, inter, bias=False))
+
+    def forward(self, x):
+        return self.w2((F.silu(self.w1(x).float()) * self.w3(x).float()).type_as(x))
+
+
+class Gate(nn.Module):
+    def __init__(self, dim, n_experts):
+        super().__init__()
+        self.topk, self.n_groups, self.topk_groups = 4, 4, 2
+        self.score_func, self.route_scale = "sigmoid", 2.5
+        self.weight = nn.Parameter(torch.randn(n_experts, dim) * 0.05)
+        self.bias = nn.Parameter(torch.rand(n_experts) * 0.2 - 0.1)
+
+
+class MoE(nn.Module):
+    """Same attributes and control flow as racetrack/models/deepseek.py:965-1022."""
+
+    def __init__(self, dim=512, inter=256, n_experts=16):
+        super().__init__()
+        self.dim, self.n_routed_experts, self.experts_start_idx = dim, n_experts, 0
+        self.gate = Gate(dim, n_experts)
+        self.experts = nn.ModuleList(Expert(dim, inter) for _ in range(n_experts))
+        self.shared_experts = Expert(dim, inter)
+
+    def forward(self, x):
+        from oracle import ref_ops as R
+        shape = x.size()
+        x = x.view(-1, self.dim)
+        weights, indices = R.gate_forward(x, self.gate.weight, self.gate.bias, n_groups=4,
+                                          topk_groups=2, topk=4, route_scale=2.5)
+        y = torch.zeros_like(x, dtype=torch.float32)
+        for i, expert in enumerate(self.experts):
+            idx, top = torch.where(indices == i)
+            if idx.numel():
+                y[idx] += expert(x[idx]) * weights[idx, top, None]
+        y += self.shared_experts(x)
+        return y.type_as(x).view(shape)
+
+
+def test_moe_patcher_runs_the_nvfp4_expert_path(spec, cuda_backend):
+    from racetrack_b200 import ops, pre_trace
+    from racetrack_b200.dispatch import KernelDispatcher
+    torch.manual_seed(1)
+    moe = MoE().cuda().to(torch.bfloat16)
+    moe.gate.bias.data = moe.gate.bias.data.float()
+    x = torch.randn(2, 48, 512, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        want = moe(x)
+        originals = pre_trace.apply_pre_trace_patches(moe, spec, KernelDispatcher(spec.kernel_root))
+        got = moe(x)
+        ops.tc_error_state()
+        pre_trace.rollback_patches(originals)
+        again = moe(x)
+    assert got.shape == want.shape
+    assert torch.equal(again, want)
+    # bf16 experts against NVFP4 experts: the format's rounding noise, not a wiring error
+    assert rel_err(got, want) <= 0.35
+    assert hasattr(moe, "_rt_nvfp4_experts")
