@@ -132,6 +132,18 @@ int rt_rope(const void* x, const int64_t* positions, const float* table, int64_t
             int64_t out_token_stride, int64_t out_head_stride,
             int rope_mode, int dtype, void* stream);
 
+/*
+ * dst[t, h, 0:dim] = src[t, 0:dim] for h in [0, heads): element (t, h, 0) of dst is at
+ * dst + t*dst_token_stride + h*dst_head_stride. Writes the rotated k_pe of each token next to
+ * every head's k_nope inside the kv_b projection output, so K = [k_nope | k_pe] needs no
+ * concatenation. dim % 8 == 0, strides % 8 == 0.
+ * ref: racetrack/realistic_bench.py:311, racetrack/models/deepseek.py:785
+ *      (k_pe.expand(..., n_local_heads, ...) inside torch.cat).
+ */
+int rt_head_broadcast(const void* src, void* dst, int64_t tokens, int64_t heads, int64_t dim,
+                      int64_t src_stride, int64_t dst_token_stride, int64_t dst_head_stride,
+                      int dtype, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* SwiGLU and activation quantisation                                         */
 /* ------------------------------------------------------------------------ */

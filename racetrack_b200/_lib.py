@@ -28,6 +28,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_norm_rope": (_I, [_P, _P, _P, _P, _I, _P, _P, _P, _L, _P, _P, _P,
                           _L, _L, _L, _L, _L, _L, _L, _F, _I, _I, _P]),
     "rt_rope": (_I, [_P, _P, _P, _L, _P, _L, _L, _L, _L, _L, _L, _L, _I, _I, _P]),
+    "rt_head_broadcast": (_I, [_P, _P, _L, _L, _L, _L, _L, _L, _I, _P]),
     "rt_swiglu": (_I, [_P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "rt_act_quant_fp8": (_I, [_P, _P, _P, _L, _L, _L, _I, _P]),
     "rt_swiglu_quant_fp8": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),

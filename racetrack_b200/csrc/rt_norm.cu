@@ -493,3 +493,37 @@ extern "C" int rt_rope(const void* x, const int64_t* positions, const float* tab
     count_launch();
     return check_launch("rope_kernel");
 }
+
+namespace rt {
+// dst[t, h, 0:dim] = src[t, 0:dim] for every head h: the rotated k_pe row of a token copied
+// next to each head's k_nope, so that K = [k_nope | k_pe] exists without a concatenation.
+__global__ void __launch_bounds__(256) head_broadcast_kernel(
+    const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int heads, int nvec,
+    int64_t sstride, int64_t tstride, int64_t hstride) {
+    const int64_t t = blockIdx.x;
+    const uint4* s = reinterpret_cast<const uint4*>(src + t * sstride);
+    for (int it = threadIdx.x; it < heads * nvec; it += blockDim.x) {
+        const int h = it / nvec, v = it - h * nvec;
+        reinterpret_cast<uint4*>(dst + t * tstride + h * hstride)[v] = __ldg(s + v);
+    }
+}
+}  // namespace rt
+
+extern "C" int rt_head_broadcast(const void* src, void* dst, int64_t tokens, int64_t heads,
+                                 int64_t dim, int64_t src_stride, int64_t dst_token_stride,
+                                 int64_t dst_head_stride, int dtype, void* stream) {
+    RT_REQUIRE(tokens >= 0 && heads > 0 && dim > 0, RT_ERR_BAD_ARG, "rt_head_broadcast: bad shape");
+    if (tokens == 0) return RT_OK;
+    RT_REQUIRE(src && dst, RT_ERR_BAD_ARG, "rt_head_broadcast: null pointer");
+    RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_head_broadcast: only bf16");
+    RT_REQUIRE(dim % 8 == 0 && src_stride % 8 == 0 && dst_token_stride % 8 == 0 &&
+                   dst_head_stride % 8 == 0 && aligned16(src) && aligned16(dst),
+               RT_ERR_UNSUPPORTED, "rt_head_broadcast: dim/strides %% 8 and 16-byte alignment needed");
+    RT_REQUIRE(tokens <= 0x7fffffffLL && heads * dim < (1LL << 30), RT_ERR_UNSUPPORTED,
+               "rt_head_broadcast: shape too large");
+    rt::head_broadcast_kernel<<<static_cast<unsigned>(tokens), 256, 0, as_stream(stream)>>>(
+        (const __nv_bfloat16*)src, (__nv_bfloat16*)dst, (int)heads, (int)(dim / 8), src_stride,
+        dst_token_stride, dst_head_stride);
+    count_launch();
+    return check_launch("head_broadcast_kernel");
+}

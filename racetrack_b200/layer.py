@@ -156,7 +156,13 @@ class RealisticLayer:
         dev = weights["w_qkv_a"].device
         self.w_qkv_a = weights["w_qkv_a"].contiguous()
         self.w_q_b = weights["w_q_b"].contiguous()
-        self.w_kv_b = weights["w_kv_b"].contiguous()
+        # kv_b rows regrouped per head as [k_nope | rope-wide gap (zero rows) | v]: the GEMM then
+        # leaves room for k_pe right behind k_nope and K / V are strided views of its output
+        s = shape
+        wkv = weights["w_kv_b"].view(self.local_heads, s.nope + s.v_dim, s.kv_lora)
+        gap = torch.zeros(self.local_heads, s.rope, s.kv_lora, device=dev, dtype=wkv.dtype)
+        self.w_kv_b = torch.cat((wkv[:, :s.nope], gap, wkv[:, s.nope:]), dim=1) \
+            .reshape(self.local_heads * (s.nope + s.rope + s.v_dim), s.kv_lora).contiguous()
         self.w_o = weights["w_o"].contiguous()
         self.w_gate = weights["w_gate"].contiguous()
         self.ones_h = torch.ones(shape.hidden, device=dev, dtype=torch.bfloat16)
@@ -189,9 +195,9 @@ class RealisticLayer:
             qkv[:, s.q_lora + s.kv_lora:], positions, eps=s.eps, rope_base=s.rope_base)
         q = ops.linear_bf16(q_c, self.w_q_b).view(tokens, h, s.qk_dim)
         ops.fused_rope_half(q[..., s.nope:], positions, rope_base=s.rope_base, inplace=True)
-        kv = ops.linear_bf16(kv_c, self.w_kv_b).view(tokens, h, s.nope + s.v_dim)
-        k = torch.cat((kv[..., :s.nope], k_pe.unsqueeze(1).expand(-1, h, -1)), dim=-1)
-        local = attention_core(q, k, kv[..., s.nope:])
+        kv = ops.linear_bf16(kv_c, self.w_kv_b).view(tokens, h, s.qk_dim + s.v_dim)
+        ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
+        local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
         out = ops.linear_bf16(local.reshape(tokens, h * s.v_dim), self.w_o)
         return self._all_reduce(out)
 

@@ -247,6 +247,23 @@ def fused_rope_half(x: torch.Tensor, positions: torch.Tensor, *, rope_base: floa
     return _rope_heads(x, pos, _inv_freq(half, rope_base, x.device), 0, _lib.RT_ROPE_HALF, inplace)
 
 
+def head_broadcast_(dst: torch.Tensor, src: torch.Tensor) -> torch.Tensor:
+    """dst[t, h, :] = src[t, :] in place; dst is a [tokens, heads, dim] view (typically a column
+    slice of the kv_b projection output), src is [tokens, dim]. The k_pe broadcast of
+    racetrack/realistic_bench.py:311 without the torch.cat."""
+    _require_cuda(dst, src)
+    _require_bf16("head_broadcast_", dst)
+    _require_bf16("head_broadcast_", src)
+    tokens, heads, dim = dst.shape
+    if src.shape != (tokens, dim) or dst.stride(2) != 1 or src.stride(1) != 1:
+        raise RuntimeError("head_broadcast_: expected dst [T, H, D] and src [T, D], unit inner stride")
+    lib = _lib.load()
+    _lib.check(lib.rt_head_broadcast(src.data_ptr(), dst.data_ptr(), tokens, heads, dim,
+                                     src.stride(0), dst.stride(0), dst.stride(1), _lib.RT_BF16,
+                                     _stream()), "rt_head_broadcast")
+    return dst
+
+
 # ---------------------------------------------------------------------------
 # SwiGLU and activation quantisation
 # ---------------------------------------------------------------------------
