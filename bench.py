@@ -121,7 +121,8 @@ class PrefillStackWorkload:
         self.shape = layer.DSV32
         w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02)
         w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
-        self.model = layer.RealisticLayer(self.shape, w, rank, world)
+        self.proj = args.proj
+        self.model = layer.RealisticLayer(self.shape, w, rank, world, proj=args.proj)
         gen = torch.Generator(device=device)
         gen.manual_seed(self.shape.seed)
         self.hidden = torch.empty(self.tokens, self.shape.hidden, device=device, dtype=torch.bfloat16)
@@ -167,7 +168,7 @@ class PrefillStackWorkload:
         s = self.shape
         return {"workload": self.name, "tokens": self.tokens, "layers": self.layers,
                 "hidden": s.hidden, "heads": s.heads, "experts": s.n_experts, "topk": s.topk,
-                "moe_inter": s.moe_inter, "experts_dtype": "nvfp4", "projections_dtype": "bf16",
+                "moe_inter": s.moe_inter, "experts_dtype": "nvfp4", "projections_dtype": self.proj,
                 "attention_core": "torch sdpa (not a kernel of this backend)",
                 "routing": "topk_softmax (racetrack/realistic_bench.py:321-327)",
                 "l2_policy": "inputs_exceed_l2 (6.3 GB of expert weights + 117 MB of hidden "
@@ -450,6 +451,8 @@ def main() -> None:
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=61)
+    ap.add_argument("--proj", default="fp8", choices=("fp8", "bf16"),
+                    help="arithmetic of the dense projections (FP8 e4m3 block-scaled or bf16)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop")

@@ -358,6 +358,20 @@ int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, in
                  int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, void* stream);
 
 /*
+ * FP8 e4m3 GEMM with DeepSeek block scales, bf16 output:
+ *   c[m, n] = sum_kb (a[m, kb] . b[n, kb]) * a_scales[m, kb] * b_scales[n / 128, kb]
+ * a [m, k] and b [n, k] are e4m3fn bytes (row pitches lda / ldb in bytes = elements);
+ * a_scales fp32 [m, k/128] (what rt_act_quant_fp8 writes), b_scales fp32 [ceil(n/128), k/128]
+ * (one scale per 128 x 128 weight block). Products are summed per 128-wide K block on
+ * tcgen05 (kind::f8f6f4) and folded, scaled, into fp32 accumulators.
+ * k % 128 == 0, n % 8 == 0, lda / ldb % 16 == 0, ldc % 8 == 0.
+ * ref: racetrack/models/deepseek.py:30-82 (_fp8_gemm_kernel), :110-145 (fp8_gemm), :316-345 (linear).
+ */
+int rt_gemm_fp8(const void* a, const float* a_scales, const void* b, const float* b_scales,
+                void* c, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldc,
+                void* stream);
+
+/*
  * Work list of the grouped GEMM, built on the device from the per-expert row offsets
  * that rt_moe_permute wrote (no host synchronisation). For groups g in [g_begin, g_end),
  * rows [offsets[g], offsets[g+1]) are cut into m-tiles of 128 rows:

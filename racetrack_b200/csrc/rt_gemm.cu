@@ -171,7 +171,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                        static_cast<uint32_t>(acc * BN + chunk * 32);
                 tmem_ld_32x32(taddr, r);
-                tmem_ld_wait();
+                tmem_ld_wait(r);
                 if (row < M) {
                     const int col0 = tn * BN + chunk * 32;
 #pragma unroll
@@ -422,7 +422,7 @@ __global__ void __launch_bounds__(kFThreads, 1) gemm_nvfp4_kernel(
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                        static_cast<uint32_t>(acc * kFBN + chunk * 32);
                 tmem_ld_32x32(taddr, r);
-                tmem_ld_wait();
+                tmem_ld_wait(r);
                 if (lrow < tm.z) {
                     const int col0 = tn * kFBN + chunk * 32;
 #pragma unroll
@@ -517,6 +517,208 @@ __global__ void __launch_bounds__(1024) moe_tile_map_kernel(const int32_t* __res
 }
 
 // ---------------------------------------------------------------------------
+// FP8 e4m3 GEMM with DeepSeek block scales
+// ---------------------------------------------------------------------------
+// C[m, n] = sum over 128-wide K blocks kb of
+//           (A_fp8[m, kb] . B_fp8[n, kb]) * a_s[m, kb] * b_s[n / 128, kb]         -> bf16
+// (activation scales per row and K block, weight scales per 128 x 128 block). The scales are
+// arbitrary fp32 numbers, so they cannot ride along inside the MMA: every K block is
+// multiplied on its own into a fresh tensor-memory buffer (4 x tcgen05.mma kind::f8f6f4,
+// K = 32 each) and eight epilogue warps fold it, scaled, into fp32 register accumulators while
+// the tensor core works on the next K block (two 256-column buffers alternate).
+// Tile 128 x 256, stage = one K block: 16 KB of A + 32 KB of B, 4 stages.
+// Warps: 0 TMA producer, 1 MMA issuer, 2-9 epilogue (warp w: lane quarter w % 4, column half
+// (w - 2) / 4).
+constexpr int kQBN = 256;
+constexpr int kQBK = 128;
+constexpr int kQStages = 4;
+constexpr int kQThreads = 320;
+constexpr uint32_t kQABytes = kBM * kQBK;
+constexpr uint32_t kQBBytes = kQBN * kQBK;
+constexpr uint32_t kQStageBytes = kQABytes + kQBBytes;
+constexpr uint32_t kQBarOffset = kQStages * kQStageBytes;
+constexpr uint32_t kQSmemBytes = kQBarOffset + (2 * kQStages + 4) * 8 + 16 + 1024;
+constexpr uint32_t kQTmemCols = 512;
+// fp32 accumulate, e4m3 x e4m3 (format code 0), K-major, N = 256, M = 128
+constexpr uint32_t kQIdesc = (1u << 4) | (static_cast<uint32_t>(kQBN >> 3) << 17) |
+                             (static_cast<uint32_t>(kBM >> 4) << 24);
+
+__global__ void __launch_bounds__(kQThreads, 1) gemm_fp8_kernel(
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    const float* __restrict__ a_s, const float* __restrict__ b_s, __nv_bfloat16* __restrict__ c,
+    int M, int N, int K, int64_t ldc) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + kQBarOffset;
+    auto full_bar = [&](int s) { return bars + 8u * s; };
+    auto empty_bar = [&](int s) { return bars + 8u * (kQStages + s); };
+    auto pfull_bar = [&](int a) { return bars + 8u * (2 * kQStages + a); };
+    auto pempty_bar = [&](int a) { return bars + 8u * (2 * kQStages + 2 + a); };
+    const uint32_t slot = bars + 8u * (2 * kQStages + 4);
+    volatile uint32_t* slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(base_ptr + kQBarOffset + 8 * (2 * kQStages + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_m = (M + kBM - 1) / kBM, num_n = (N + kQBN - 1) / kQBN;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = K / kQBK;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int s = 0; s < kQStages; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(pfull_bar(a), 1);
+            mbar_init(pempty_bar(a), 256);
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc(slot, kQTmemCols);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                int tm, tn;
+                tile_coords(tile, num_m, num_n, tm, tn);
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 21))) break;
+                    const uint32_t sa = base + stage * kQStageBytes;
+                    mbar_arrive_expect_tx(full_bar(stage), kQStageBytes);
+                    tma_load_2d(sa, &tmap_a, kb * kQBK, tm * kBM, full_bar(stage));
+                    tma_load_2d(sa + kQABytes, &tmap_b, kb * kQBK, tn * kQBN, full_bar(stage));
+                    if (++stage == kQStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int buf = 0;
+            uint32_t buf_phase = 0;
+            bool ok = true;
+            for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!(ok = mbar_wait(pempty_bar(buf), buf_phase ^ 1u, abort_flag, 22))) break;
+                    if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, 23))) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + stage * kQStageBytes;
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * kQBN);
+                    const uint64_t adesc = smem_desc_sw128(sa);
+                    const uint64_t bdesc = smem_desc_sw128(sa + kQABytes);
+#pragma unroll
+                    for (int j = 0; j < kQBK / 32; ++j) {
+                        // 32 e4m3 = 32 bytes along K: +2 in the 16-byte-unit address field
+                        mma_f8f6f4(d_tmem, adesc + 2u * j, bdesc + 2u * j, kQIdesc, j != 0 ? 1u : 0u);
+                    }
+                    mma_commit(empty_bar(stage));   // smem stage reusable
+                    mma_commit(pfull_bar(buf));     // partial product of this K block complete
+                    if (++stage == kQStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                    if (++buf == 2) {
+                        buf = 0;
+                        buf_phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;       // which 128 columns of the tile
+        const int kbs = num_kb;                 // scales per row of A / per block row of B
+        int buf = 0;
+        uint32_t buf_phase = 0;
+        bool ok = true;
+        for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
+            int tm, tn;
+            tile_coords(tile, num_m, num_n, tm, tn);
+            const int row = tm * kBM + quad * 32 + lane;
+            const int col_base = tn * kQBN + half * 128;
+            const bool live = col_base < N;                       // whole half outside the matrix?
+            const float* as_row = a_s + static_cast<int64_t>(row < M ? row : 0) * kbs;
+            const float* bs_row = b_s + static_cast<int64_t>(live ? col_base >> 7 : 0) * kbs;
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const float scale = __ldg(as_row + kb) * __ldg(bs_row + kb);
+                if (!(ok = mbar_wait(pfull_bar(buf), buf_phase, abort_flag, 24))) break;
+                tc_fence_after();
+                // two register buffers: the load of chunk c+1 is in flight while chunk c is folded in
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                                       static_cast<uint32_t>(buf * kQBN + half * 128);
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(taddr, r0);
+                tmem_ld_wait(r0);
+                tmem_ld_32x32(taddr + 32, r1);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), scale, acc[i]);
+                tmem_ld_wait(r1);
+                tmem_ld_32x32(taddr + 64, r0);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[32 + i]);
+                tmem_ld_wait(r0);
+                tmem_ld_32x32(taddr + 96, r1);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), scale, acc[64 + i]);
+                tmem_ld_wait(r1);
+                // every column of the buffer has been read: hand it back before the last fold
+                tc_fence_before();
+                mbar_arrive(pempty_bar(buf));
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[96 + i]);
+                if (++buf == 2) {
+                    buf = 0;
+                    buf_phase ^= 1u;
+                }
+            }
+            if (!ok) break;
+            if (row < M && live) {
+                __nv_bfloat16* crow = c + static_cast<int64_t>(row) * ldc + col_base;
+#pragma unroll
+                for (int v = 0; v < 16; ++v) {
+                    if (col_base + v * 8 < N) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = acc[v * 8 + i];
+                        *reinterpret_cast<uint4*>(crow + v * 8) = pack_bf16x8(f);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, kQTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // host side
 // ---------------------------------------------------------------------------
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*,
@@ -591,6 +793,29 @@ static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t
     return check_launch("gemm_bf16_kernel");
 }
 
+static int launch_fp8(const void* a, const float* a_s, const void* b, const float* b_s, void* c,
+                      int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                      cudaStream_t st) {
+    CUtensorMap ta, tb;
+    if (int rc = make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, a, K, M, lda, kQBK, kBM)) return rc;
+    if (int rc = make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, b, K, N, ldb, kQBK, kQBN)) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kQSmemBytes));
+        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_fp8: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + kQBN - 1) / kQBN);
+    const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+    gemm_fp8_kernel<<<grid, kQThreads, kQSmemBytes, st>>>(
+        ta, tb, a_s, b_s, static_cast<__nv_bfloat16*>(c), static_cast<int>(M), static_cast<int>(N),
+        static_cast<int>(K), ldc);
+    count_launch();
+    return check_launch("gemm_fp8_kernel");
+}
+
 static int launch_nvfp4(const void* a_codes, const void* a_sf, const float* a_gs,
                         const void* b_codes, const void* b_sf, const float* b_gs, void* c,
                         const int32_t* tile_map, const int32_t* tile_count, int64_t max_m_tiles,
@@ -625,6 +850,22 @@ static int launch_nvfp4(const void* a_codes, const void* a_sf, const float* a_gs
 }  // namespace rt
 
 using namespace rt;
+
+extern "C" int rt_gemm_fp8(const void* a, const float* a_scales, const void* b,
+                           const float* b_scales, void* c, int64_t m, int64_t n, int64_t k,
+                           int64_t lda, int64_t ldb, int64_t ldc, void* stream) {
+    RT_REQUIRE(m >= 0 && n > 0 && k > 0, RT_ERR_BAD_ARG, "rt_gemm_fp8: bad shape");
+    if (m == 0) return RT_OK;
+    RT_REQUIRE(a && a_scales && b && b_scales && c, RT_ERR_BAD_ARG, "rt_gemm_fp8: null pointer");
+    RT_REQUIRE(k % 128 == 0, RT_ERR_UNSUPPORTED, "rt_gemm_fp8: k must be a multiple of 128");
+    RT_REQUIRE(n % 8 == 0 && lda % 16 == 0 && ldb % 16 == 0 && ldc % 8 == 0, RT_ERR_UNSUPPORTED,
+               "rt_gemm_fp8: n %% 8, lda/ldb %% 16 and ldc %% 8 are required");
+    RT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c), RT_ERR_UNSUPPORTED,
+               "rt_gemm_fp8: pointers must be 16-byte aligned");
+    RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
+               "rt_gemm_fp8: dimension too large");
+    return tc::launch_fp8(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc, as_stream(stream));
+}
 
 extern "C" int rt_moe_tile_map(const int32_t* offsets, int64_t g_begin, int64_t g_end,
                                int32_t* tile_map, int32_t* tile_base, int32_t* tile_count,

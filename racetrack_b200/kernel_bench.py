@@ -133,6 +133,11 @@ def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, s
         x, w = _randn(T, k), _randn(n, k)
         out[f"linear_bf16[{name} {T}x{n}x{k}]"] = (
             (lambda x=x, w=w: ops.linear_bf16(x, w)), 2 * T * n * k, (T * k + n * k + T * n) * 2, "bf16")
+        wc, ws = ops.quantize_weight_fp8(w)
+        xc, xs = ops.fused_act_quant(x)
+        out[f"linear_fp8[{name} {T}x{n}x{k}]"] = (
+            (lambda xc=xc, xs=xs, wc=wc, ws=ws: ops.linear_fp8(xc, xs, wc, ws)), 2 * T * n * k,
+            T * k + n * k + T * n * 2, "fp8")
     for name, n, k in (("w13", 4096, HIDDEN), ("w2", HIDDEN, 2048)):
         x, w = _randn(T, k), _randn(n, k)
         xq = ops.fused_nvfp4_quant(x, tiled_scales=True)
@@ -154,11 +159,13 @@ def run_gemms(tokens: int, iters: int, flush: "L2Flusher") -> list[dict]:
         t = time_kernel(fn, iters=iters, flush=flush)
         tf = flops / (t["median_us"] * 1e-6) / 1e12
         # dense NVFP4 has no measured peak on this pool: quoted against the nominal 9 PFLOP/s
-        peak = bf16_peak if kind == "bf16" else 9000.0
+        # dense FP8 / NVFP4 have no measured peak on this pool: quoted against nominal 4.5 / 9 PFLOP/s
+        peak = {"bf16": bf16_peak, "fp8": 4500.0}.get(kind, 9000.0)
+        label = {"bf16": "measured bf16", "fp8": "nominal fp8"}.get(kind, "nominal nvfp4")
         rows.append({"kernel": name, **t, "tflops": tf, "frac_of_peak": tf / peak, "peak_tflops": peak,
                      "gbs": nbytes / (t["median_us"] * 1e-6) / 1e9})
         print(f"{name:40s} {t['median_us']:9.1f} us  {tf:8.1f} TFLOP/s  {100*tf/peak:5.1f}% of "
-              f"{peak:.0f} ({'measured bf16' if kind == 'bf16' else 'nominal nvfp4'})  "
+              f"{peak:.0f} ({label})  "
               f"{rows[-1]['gbs']:7.1f} GB/s", flush=True)
     ops.tc_error_state()
     return rows

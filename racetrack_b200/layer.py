@@ -145,25 +145,46 @@ def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.T
     return out.squeeze(0).transpose(0, 1)
 
 
+class Projection:
+    """A dense projection y = x W^T held either in bf16 or as FP8 e4m3 with 128 x 128 block
+    scales (racetrack/models/deepseek.py:316-345 `linear`: bf16 weights go to F.linear, FP8
+    weights to act_quant + fp8_gemm). FP8 needs K % 128 == 0; other widths stay bf16."""
+
+    def __init__(self, weight: torch.Tensor, dtype: str):
+        self.fp8 = dtype == "fp8" and weight.shape[1] % 128 == 0
+        if self.fp8:
+            self.codes, self.scales = ops.quantize_weight_fp8(weight)
+        else:
+            self.weight = weight.contiguous()
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        if self.fp8:
+            return ops.linear_fp8_act(x, self.codes, self.scales)
+        return ops.linear_bf16(x, self.weight)
+
+
 class RealisticLayer:
-    """One rank's shard of the synthetic layer; `forward_stack` applies it `layers` times."""
+    """One rank's shard of the synthetic layer; `forward_stack` applies it `layers` times.
+    proj = "bf16" | "fp8" selects the arithmetic of the dense projections."""
 
     def __init__(self, shape: LayerShape, weights: dict, rank: int = 0, world: int = 1, *,
-                 ffn: str = "moe", route: str = "topk_softmax", process_group=None):
+                 ffn: str = "moe", route: str = "topk_softmax", proj: str = "bf16",
+                 process_group=None):
         self.shape, self.rank, self.world, self.ffn, self.route = shape, rank, world, ffn, route
-        self.group = process_group
+        self.group, self.proj = process_group, proj
         self.local_heads = shape.heads // world
         dev = weights["w_qkv_a"].device
-        self.w_qkv_a = weights["w_qkv_a"].contiguous()
-        self.w_q_b = weights["w_q_b"].contiguous()
+        self.w_qkv_a = Projection(weights["w_qkv_a"], proj)
+        self.w_q_b = Projection(weights["w_q_b"], proj)
         # kv_b rows regrouped per head as [k_nope | rope-wide gap (zero rows) | v]: the GEMM then
         # leaves room for k_pe right behind k_nope and K / V are strided views of its output
         s = shape
         wkv = weights["w_kv_b"].view(self.local_heads, s.nope + s.v_dim, s.kv_lora)
         gap = torch.zeros(self.local_heads, s.rope, s.kv_lora, device=dev, dtype=wkv.dtype)
-        self.w_kv_b = torch.cat((wkv[:, :s.nope], gap, wkv[:, s.nope:]), dim=1) \
-            .reshape(self.local_heads * (s.nope + s.rope + s.v_dim), s.kv_lora).contiguous()
-        self.w_o = weights["w_o"].contiguous()
+        self.w_kv_b = Projection(
+            torch.cat((wkv[:, :s.nope], gap, wkv[:, s.nope:]), dim=1)
+            .reshape(self.local_heads * (s.nope + s.rope + s.v_dim), s.kv_lora), proj)
+        self.w_o = Projection(weights["w_o"], proj)
         self.w_gate = weights["w_gate"].contiguous()
         self.ones_h = torch.ones(shape.hidden, device=dev, dtype=torch.bfloat16)
         self.q_norm = torch.ones(shape.q_lora, device=dev, dtype=torch.bfloat16)
@@ -173,8 +194,8 @@ class RealisticLayer:
             self.experts = weights["experts"] if "experts" in weights else \
                 moe.quantize_experts(weights["w13"], weights["w2"])
         else:
-            self.w13d = torch.cat([weights["w1"], weights["w3"]]).contiguous()
-            self.w2d = weights["w2d"].contiguous()
+            self.w13d = Projection(torch.cat([weights["w1"], weights["w3"]]), proj)
+            self.w2d = Projection(weights["w2d"], proj)
 
     # -- pieces ---------------------------------------------------------------------------
     reduce = True   # set False to get this rank's partial sums (single-process checks)
@@ -189,16 +210,16 @@ class RealisticLayer:
         """racetrack/realistic_bench.py:286-317."""
         s, h = self.shape, self.local_heads
         tokens = normed.shape[0]
-        qkv = ops.linear_bf16(normed, self.w_qkv_a)
+        qkv = self.w_qkv_a(normed)
         q_c, kv_c, k_pe = ops.fused_norm_rope(
             qkv[:, :s.q_lora], self.q_norm, qkv[:, s.q_lora:s.q_lora + s.kv_lora], self.kv_norm,
             qkv[:, s.q_lora + s.kv_lora:], positions, eps=s.eps, rope_base=s.rope_base)
-        q = ops.linear_bf16(q_c, self.w_q_b).view(tokens, h, s.qk_dim)
+        q = self.w_q_b(q_c).view(tokens, h, s.qk_dim)
         ops.fused_rope_half(q[..., s.nope:], positions, rope_base=s.rope_base, inplace=True)
-        kv = ops.linear_bf16(kv_c, self.w_kv_b).view(tokens, h, s.qk_dim + s.v_dim)
+        kv = self.w_kv_b(kv_c).view(tokens, h, s.qk_dim + s.v_dim)
         ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
         local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
-        out = ops.linear_bf16(local.reshape(tokens, h * s.v_dim), self.w_o)
+        out = self.w_o(local.reshape(tokens, h * s.v_dim))
         return self._all_reduce(out)
 
     def ffn_forward(self, normed: torch.Tensor) -> torch.Tensor:
@@ -217,9 +238,13 @@ class RealisticLayer:
                                         n_experts=s.n_experts,
                                         expert_begin=self.rank * self.local_experts)
         else:
-            gate_up = ops.linear_bf16(normed, self.w13d)
+            gate_up = self.w13d(normed)
             inter = gate_up.shape[1] // 2
-            out = ops.linear_bf16(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]), self.w2d)
+            if self.w2d.fp8:     # SwiGLU and the FP8 quantisation of its result in one kernel
+                codes, scales = ops.fused_swiglu_quant(gate_up[:, :inter], gate_up[:, inter:])
+                out = ops.linear_fp8(codes, scales, self.w2d.codes, self.w2d.scales)
+            else:
+                out = self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]))
         return self._all_reduce(out)
 
     # -- the stack ----------------------------------------------------------------------------

@@ -528,6 +528,54 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
     return out
 
 
+def quantize_weight_fp8(weight: torch.Tensor):
+    """bf16/fp32 weight [N, K] -> (e4m3fn codes [N, K], fp32 scales [ceil(N/128), K/128]) with one
+    scale = amax / 448 per 128 x 128 block: the checkpoint layout `weight` / `weight.scale` of
+    racetrack/models/deepseek.py:361-371 (dequantised by `_block_dequant`, :148-161).
+    Set-up time helper in plain torch (weights are quantised once, not on the hot path)."""
+    n, k = weight.shape
+    if k % 128:
+        raise RuntimeError("quantize_weight_fp8: K must be a multiple of 128")
+    nb = (n + 127) // 128
+    w = torch.zeros(nb * 128, k, dtype=torch.float32, device=weight.device)
+    w[:n] = weight.float()
+    blocks = w.view(nb, 128, k // 128, 128)
+    scale = blocks.abs().amax(dim=(1, 3)).clamp(min=1e-4) / 448.0
+    codes = (blocks / scale[:, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
+    return codes.view(nb * 128, k)[:n].contiguous(), scale.contiguous()
+
+
+def linear_fp8(x_codes: torch.Tensor, x_scales: torch.Tensor, w_codes: torch.Tensor,
+               w_scales: torch.Tensor) -> torch.Tensor:
+    """FP8 block-scaled linear: fp8_gemm(a, a_s, b, b_s) of racetrack/models/deepseek.py:110-145
+    -> bf16 [..., N]. x_codes / x_scales as fused_act_quant returns them."""
+    _require_cuda(x_codes, x_scales, w_codes, w_scales)
+    k = x_codes.shape[-1]
+    n = w_codes.shape[0]
+    if w_codes.shape[1] != k or x_codes.dtype != torch.float8_e4m3fn or w_codes.dtype != torch.float8_e4m3fn:
+        raise RuntimeError("linear_fp8: expected e4m3fn codes with matching K")
+    xc = x_codes.reshape(-1, k)
+    xs = x_scales.reshape(-1, k // 128)
+    if not (xc.is_contiguous() and xs.is_contiguous() and w_codes.is_contiguous()
+            and w_scales.is_contiguous()):
+        raise RuntimeError("linear_fp8: operands must be contiguous")
+    if xs.dtype != torch.float32 or w_scales.dtype != torch.float32 \
+            or w_scales.shape != ((n + 127) // 128, k // 128):
+        raise RuntimeError("linear_fp8: scales must be fp32 [M, K/128] and [ceil(N/128), K/128]")
+    out = torch.empty(*x_codes.shape[:-1], n, dtype=torch.bfloat16, device=x_codes.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_gemm_fp8(xc.data_ptr(), xs.data_ptr(), w_codes.data_ptr(), w_scales.data_ptr(),
+                               out.data_ptr(), xc.shape[0], n, k, k, k, n, _stream()), "rt_gemm_fp8")
+    return out
+
+
+def linear_fp8_act(x: torch.Tensor, w_codes: torch.Tensor, w_scales: torch.Tensor) -> torch.Tensor:
+    """`linear(x, weight)` with an FP8 weight as racetrack/models/deepseek.py:343-345 runs it:
+    act_quant(x) then the FP8 block-scaled GEMM."""
+    codes, scales = fused_act_quant(x)
+    return linear_fp8(codes, scales, w_codes, w_scales)
+
+
 def moe_tile_map(offsets: torch.Tensor, g_begin: int, g_end: int, max_tiles: int):
     """Device-side work list of the grouped GEMM for groups [g_begin, g_end) of the row
     offsets written by fused_moe_permute -> (tile_map int32 [max_tiles, 4], tile_base

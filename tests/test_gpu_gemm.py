@@ -80,6 +80,49 @@ def test_router_logits_fp32_output(ops, m):
 
 
 # ---------------------------------------------------------------------------
+# FP8 block-scaled GEMM
+# ---------------------------------------------------------------------------
+
+@pytest.mark.parametrize("m,n,k", [
+    (128, 256, 128),       # one tile, one K block
+    (128, 256, 1024),      # partial buffers alternate, stages wrap
+    (256, 512, 512),
+    (100, 2112, 7168),     # qkv_a: ragged M, N not a multiple of 128 or 256
+    (1, 7168, 2048),       # decode row
+    (2048, 24576, 1536),   # q_b
+    (1024, 7168, 16384),   # w_o: 128 K blocks
+])
+def test_linear_fp8_block_scaled(ops, m, n, k):
+    from oracle import ref_ops as R
+    x = I.randn((m, k), 500 + m).cuda()
+    w = I.randn((n, k), 600 + n, std=0.05).cuda()
+    wc, ws = ops.quantize_weight_fp8(w)
+    xc, xs = ops.fused_act_quant(x)
+    out = ops.linear_fp8(xc, xs, wc, ws)
+    ops.tc_error_state()
+    assert out.shape == (m, n) and out.dtype == torch.bfloat16
+    # the formula of the reference's GPU kernel, in fp64
+    a = xc.double().view(m, k // 128, 128) * xs.double().unsqueeze(-1)
+    nb = ws.shape[0]
+    wpad = torch.zeros(nb * 128, k, dtype=torch.float64, device="cuda")
+    wpad[:n] = wc.double()
+    b = (wpad.view(nb, 128, k // 128, 128) * ws.double()[:, None, :, None]).view(nb * 128, k)[:n]
+    ref = a.view(m, k) @ b.t()
+    assert rel_err(out, ref.float()) <= 1e-2
+    diff = (out.float() - ref.float()).abs()
+    assert bool((diff <= 2.0 ** -7 * ref.float().abs() + 1e-3 * ref.float().abs().max()).all())
+    # weight codes/scales reproduce the reference's block dequantisation; its CPU fallback GEMM agrees
+    if m * n <= 300000:
+        deq = R.block_dequant(wc.cpu(), ws.cpu())
+        assert rel_err(deq, w.cpu()) <= 0.08
+        ref_cpu = R.fp8_gemm(xc.cpu(), xs.cpu(), wc.cpu(), ws.cpu())
+        assert rel_err(out, ref_cpu) <= 2e-2
+    # the composite the real model calls: act_quant + GEMM
+    out2 = ops.linear_fp8_act(x, wc, ws)
+    assert torch.equal(out2, out)
+
+
+# ---------------------------------------------------------------------------
 # NVFP4 block-scaled GEMM
 # ---------------------------------------------------------------------------
 

@@ -44,18 +44,23 @@ def _check(out, ref, tight):
     assert rel_err(out, ref) <= tight, f"relative error {rel_err(out, ref)}"
 
 
+@pytest.mark.parametrize("proj,tight", [("bf16", 2e-2), ("fp8", 1.5e-1)])
 @pytest.mark.parametrize("tokens,layers", [(96, 2), (1, 1), (130, 3)])
-def test_dense_layer_stack_matches_reference_layer(L, tokens, layers):
+def test_dense_layer_stack_matches_reference_layer(L, tokens, layers, proj, tight):
+    """bf16 projections: a couple of bf16 ulps. FP8 projections (e4m3 activations per 1 x 128,
+    weights per 128 x 128): the rounding noise of a 3-bit mantissa, still inside the
+    reference runner's criterion."""
     layer, ops = L
     shape = small_shape(layer)
     w = layer.make_weights(shape, 0, 1, "cpu", ffn="dense", std=0.05)
     hidden, pos = _inputs(shape, tokens)
     ref = ref_layer.forward_stack(hidden, pos, [w], shape, layers, ffn="dense")
-    model = layer.RealisticLayer(shape, _to_cuda(w), ffn="dense")
+    model = layer.RealisticLayer(shape, _to_cuda(w), ffn="dense", proj=proj)
+    assert model.w_qkv_a.fp8 == (proj == "fp8") and not model.w_kv_b.fp8   # kv_lora 64: stays bf16
     out = model.forward_stack(hidden.cuda(), pos.cuda(), layers)
     ops.tc_error_state()
     assert out.shape == ref.shape and out.dtype == torch.bfloat16
-    _check(out, ref, 2e-2)
+    _check(out, ref, tight)
 
 
 @pytest.mark.parametrize("tokens,layers", [(96, 2), (1, 1), (130, 3)])
