@@ -96,15 +96,24 @@ __global__ void __launch_bounds__(512) rms_norm_kernel(const __nv_bfloat16* __re
     const int64_t row = blockIdx.x;
     const uint4* xr = reinterpret_cast<const uint4*>(x + row * xstride);
     uint4* orow = reinterpret_cast<uint4*>(out + row * ostride);
-    float h[VPT][8];
+    // The row stays in registers in its packed bf16 form (4 registers per vector instead of
+    // 8) and is widened twice; the smaller footprint keeps more rows in flight per SM, which
+    // is what a kernel with a single load stream per thread needs.
+    uint4 raw[VPT];
     float ss = 0.f;
 #pragma unroll
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * blockDim.x;
-        if (v < nvec) {
-            unpack_bf16x8(ld_stream16(xr + v), h[i]);
+        if (v < nvec) raw[i] = ld_stream16(xr + v);
+    }
 #pragma unroll
-            for (int k = 0; k < 8; ++k) ss += h[i][k] * h[i][k];
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+            float h[8];
+            unpack_bf16x8(raw[i], h);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) ss += h[k] * h[k];
         }
     }
     ss = block_sum(ss, scratch);
@@ -113,10 +122,11 @@ __global__ void __launch_bounds__(512) rms_norm_kernel(const __nv_bfloat16* __re
     for (int i = 0; i < VPT; ++i) {
         const int v = threadIdx.x + i * blockDim.x;
         if (v < nvec) {
-            float w[8], o[8];
+            float h[8], w[8], o[8];
+            unpack_bf16x8(raw[i], h);
             load_weight8<W_BF16>(weight, v, w);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) o[k] = (h[i][k] * rs) * w[k];
+            for (int k = 0; k < 8; ++k) o[k] = (h[k] * rs) * w[k];
             st_stream16(orow + v, pack_bf16x8(o));
         }
     }
@@ -229,6 +239,101 @@ __global__ void __launch_bounds__(512) norm_rope_kernel(
             kout[half + i] = __float2bfloat16_rn(o2);
         } else {
             rot_pair(__bfloat162float(kin[2 * i]), __bfloat162float(kin[2 * i + 1]), c, s, o1, o2);
+            kout[2 * i] = __float2bfloat16_rn(o1);
+            kout[2 * i + 1] = __float2bfloat16_rn(o2);
+        }
+    }
+}
+
+// Same operation, one WARP per token (8 tokens per CTA): for the MLA widths (1536 + 512 + 64
+// columns = 4 KB per token) a CTA per token spends its life in block-barrier and launch
+// latency. Here a lane keeps up to 8 + 4 packed vectors, the two sums of squares are warp
+// shuffles, cos/sin are evaluated by the lane that rotates the pair; no shared memory, no
+// block barrier, 12 independent 16-byte loads in flight per lane.
+constexpr int kNrWarps = 8;
+constexpr int kNrQMax = 8;    // q_cols  <= 8 * 32 * 8 = 2048
+constexpr int kNrKvMax = 4;   // kv_cols <= 4 * 32 * 8 = 1024
+
+template <bool W_BF16>
+__global__ void __launch_bounds__(kNrWarps * 32) norm_rope_warp_kernel(
+    const __nv_bfloat16* __restrict__ q_c, const void* __restrict__ q_w,
+    const __nv_bfloat16* __restrict__ kv_c, const void* __restrict__ kv_w,
+    const __nv_bfloat16* __restrict__ k_pe, const int64_t* __restrict__ positions,
+    const float* __restrict__ table, int64_t table_rows, __nv_bfloat16* __restrict__ q_out,
+    __nv_bfloat16* __restrict__ kv_out, __nv_bfloat16* __restrict__ k_out, int64_t tokens, int nq,
+    int nkv, int rope_dim, int64_t q_stride, int64_t kv_stride, int64_t k_stride, float q_cols_f,
+    float kv_cols_f, float eps, int mode) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = static_cast<int64_t>(blockIdx.x) * kNrWarps + (threadIdx.x >> 5);
+    if (t >= tokens) return;
+    const uint4* qr = reinterpret_cast<const uint4*>(q_c + t * q_stride);
+    const uint4* kvr = reinterpret_cast<const uint4*>(kv_c + t * kv_stride);
+    uint4 qv[kNrQMax], kvv[kNrKvMax];
+#pragma unroll
+    for (int i = 0; i < kNrQMax; ++i)
+        if (lane + 32 * i < nq) qv[i] = ld_stream16(qr + lane + 32 * i);
+#pragma unroll
+    for (int i = 0; i < kNrKvMax; ++i)
+        if (lane + 32 * i < nkv) kvv[i] = ld_stream16(kvr + lane + 32 * i);
+    float sq = 0.f, skv = 0.f;
+#pragma unroll
+    for (int i = 0; i < kNrQMax; ++i)
+        if (lane + 32 * i < nq) {
+            float h[8];
+            unpack_bf16x8(qv[i], h);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) sq += h[k] * h[k];
+        }
+#pragma unroll
+    for (int i = 0; i < kNrKvMax; ++i)
+        if (lane + 32 * i < nkv) {
+            float h[8];
+            unpack_bf16x8(kvv[i], h);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) skv += h[k] * h[k];
+        }
+    sq = warp_sum(sq);
+    skv = warp_sum(skv);
+    const float rq = rsqrtf(sq / q_cols_f + eps);
+    const float rkv = rsqrtf(skv / kv_cols_f + eps);
+    uint4* qo = reinterpret_cast<uint4*>(q_out) + t * nq;
+    uint4* kvo = reinterpret_cast<uint4*>(kv_out) + t * nkv;
+#pragma unroll
+    for (int i = 0; i < kNrQMax; ++i)
+        if (lane + 32 * i < nq) {
+            float h[8], w[8], o[8];
+            unpack_bf16x8(qv[i], h);
+            load_weight8<W_BF16>(q_w, lane + 32 * i, w);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = (h[k] * rq) * w[k];
+            st_stream16(qo + lane + 32 * i, pack_bf16x8(o));
+        }
+#pragma unroll
+    for (int i = 0; i < kNrKvMax; ++i)
+        if (lane + 32 * i < nkv) {
+            float h[8], w[8], o[8];
+            unpack_bf16x8(kvv[i], h);
+            load_weight8<W_BF16>(kv_w, lane + 32 * i, w);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = (h[k] * rkv) * w[k];
+            st_stream16(kvo + lane + 32 * i, pack_bf16x8(o));
+        }
+    const int half = rope_dim >> 1;
+    const __nv_bfloat16* kin = k_pe + t * k_stride;
+    __nv_bfloat16* kout = k_out + t * rope_dim;
+    for (int i = lane; i < half; i += 32) {
+        float c, s, o1, o2;
+        if (mode == RT_ROPE_HALF) {
+            const float ang = __fmul_rn(static_cast<float>(positions[t]), __ldg(table + i));
+            c = round_bf16(cosf(ang));
+            s = round_bf16(sinf(ang));
+            rot_half(__bfloat162float(kin[i]), __bfloat162float(kin[half + i]), c, s, o1, o2);
+            kout[i] = __float2bfloat16_rn(o1);
+            kout[half + i] = __float2bfloat16_rn(o2);
+        } else {
+            const int64_t trow = positions ? positions[t] : (t % table_rows);
+            const float2 f = __ldg(reinterpret_cast<const float2*>(table) + trow * half + i);
+            rot_pair(__bfloat162float(kin[2 * i]), __bfloat162float(kin[2 * i + 1]), f.x, f.y, o1, o2);
             kout[2 * i] = __float2bfloat16_rn(o1);
             kout[2 * i + 1] = __float2bfloat16_rn(o2);
         }
@@ -441,7 +546,24 @@ extern "C" int rt_norm_rope(const void* q_c, const void* q_weight, const void* k
     const dim3 grid(static_cast<unsigned>(tokens));
     cudaStream_t st = as_stream(stream);
     const bool wb = weight_dtype == RT_BF16;
-#define RT_LAUNCH_NR(V)                                                                          \
+    if (nq <= kNrQMax * 32 && nkv <= kNrKvMax * 32) {   // the MLA widths: one warp per token
+        const unsigned wgrid = static_cast<unsigned>((tokens + kNrWarps - 1) / kNrWarps);
+        if (wb)
+            norm_rope_warp_kernel<true><<<wgrid, kNrWarps * 32, 0, st>>>(
+                (const __nv_bfloat16*)q_c, q_weight, (const __nv_bfloat16*)kv_c, kv_weight,
+                (const __nv_bfloat16*)k_pe, positions, table, table_rows, (__nv_bfloat16*)q_out,
+                (__nv_bfloat16*)kv_out, (__nv_bfloat16*)k_out, tokens, nq, nkv, (int)rope_dim,
+                q_stride, kv_stride, k_stride, (float)q_cols, (float)kv_cols, eps, rope_mode);
+        else
+            norm_rope_warp_kernel<false><<<wgrid, kNrWarps * 32, 0, st>>>(
+                (const __nv_bfloat16*)q_c, q_weight, (const __nv_bfloat16*)kv_c, kv_weight,
+                (const __nv_bfloat16*)k_pe, positions, table, table_rows, (__nv_bfloat16*)q_out,
+                (__nv_bfloat16*)kv_out, (__nv_bfloat16*)k_out, tokens, nq, nkv, (int)rope_dim,
+                q_stride, kv_stride, k_stride, (float)q_cols, (float)kv_cols, eps, rope_mode);
+        count_launch();
+        return check_launch("norm_rope_warp_kernel");
+    }
+#define RT_LAUNCH_NR(V)                                                                         \
     if (wb)                                                                                      \
         norm_rope_kernel<V, true><<<grid, threads, smem, st>>>(                                  \
             (const __nv_bfloat16*)q_c, q_weight, (const __nv_bfloat16*)kv_c, kv_weight,          \

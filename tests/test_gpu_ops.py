@@ -107,6 +107,24 @@ def test_fused_norm_rope_half_split(ops, tokens):
         assert_close_bf16(got, ref, name, ulps=2, max_frac=3e-2)
 
 
+@pytest.mark.parametrize("q_cols,kv_cols", [(4096, 2048), (2048, 1024), (128, 64), (8, 8)])
+def test_fused_norm_rope_other_widths(ops, q_cols, kv_cols):
+    """Widths beyond the warp-per-token kernel (CTA-per-token path) and tiny ones."""
+    tokens, rope = 19, 32
+    x = I.randn((tokens, q_cols + kv_cols + rope), 41)
+    wq = I.randn((q_cols,), 42, mean=1.0, std=0.02, dtype=torch.float32)
+    wkv = I.randn((kv_cols,), 43, mean=1.0, std=0.02, dtype=torch.float32)
+    pos = torch.arange(tokens, dtype=torch.int64) * 3
+    ref = R.fused_norm_rope(x[:, :q_cols], wq, x[:, q_cols:q_cols + kv_cols], wkv,
+                            x[:, q_cols + kv_cols:], pos, eps=1e-6, rope_base=10000.0)
+    xc = cu(x)
+    got = ops.fused_norm_rope(xc[:, :q_cols], cu(wq), xc[:, q_cols:q_cols + kv_cols], cu(wkv),
+                              xc[:, q_cols + kv_cols:], cu(pos), eps=1e-6, rope_base=10000.0)
+    for g, r, name in zip(got, ref, ("q", "kv", "k_pe")):
+        assert rel_err(g, r) <= REL_TOL, name
+        assert_close_bf16(g, r, name, ulps=2, max_frac=3e-2)
+
+
 def test_fused_norm_rope_bf16_weights_and_fixture(ops, golden_small):
     d = I.mla_prologue_inputs(4)
     q, kv, k = ops.fused_norm_rope(cu(d["q_c"]), cu(d["w_q"]), cu(d["kv_c"]), cu(d["w_kv"]),
