@@ -33,17 +33,20 @@ if str(ROOT) not in sys.path:
 
 UNIT = "tokens*layers/s"
 FALLBACK_HBM_GBS = 6650.0
+FALLBACK_BF16_TFLOPS = 1400.0     # sustained figure of the fallback measurement
 CPU_SAMPLE_TOKENS = 8
 
 
-def measured_peaks() -> tuple[float, str]:
+def measured_peaks() -> tuple[float, float, str]:
+    """(HBM GB/s, dense bf16 TFLOP/s sustained under the power cap, source)."""
     p = ROOT / "MEASURED_PEAKS.json"
     if p.exists():
         try:
-            return float(json.loads(p.read_text())["hbm_gbs"]), "measured"
+            d = json.loads(p.read_text())
+            return float(d["hbm_gbs"]), float(d["bf16_tflops_sustained"]), "measured"
         except Exception:
             pass
-    return FALLBACK_HBM_GBS, "fallback"
+    return FALLBACK_HBM_GBS, FALLBACK_BF16_TFLOPS, "fallback"
 
 
 class ClockSampler(threading.Thread):
@@ -149,6 +152,20 @@ class PrefillStackWorkload:
 
         self.recording = False
         ops.gemm_nvfp4_grouped = timed
+        # experts that actually receive tokens (their weights are what the GEMM reads)
+        inner_permute = ops.fused_moe_permute
+        self.touched = []
+
+        def permute(indices, n_experts):
+            out = inner_permute(indices, n_experts)
+            if wl.recording and len(wl.touched) < 64:
+                off = out[0]
+                lo = wl.rank * (n_experts // wl.world)
+                hi = lo + n_experts // wl.world
+                wl.touched.append(((off[lo + 1:hi + 1] - off[lo:hi]) > 0).sum())
+            return out
+
+        ops.fused_moe_permute = permute
 
     @property
     def units_per_step(self) -> int:
@@ -159,10 +176,22 @@ class PrefillStackWorkload:
         s = self.shape
         e_loc = s.n_experts // self.world
         pairs_local = self.tokens * s.topk // self.world       # expected rows of this rank
-        weights = e_loc * 2 * s.moe_inter * s.hidden * 9 // 16   # e2m1 codes + e4m3 scales
+        # experts that receive at least one token (all of them at prefill sizes; at decode
+        # sizes only the touched experts' weights are read): counted from the routing of the
+        # timed layers, else the expectation under uniform routing
+        if self.touched:
+            touched = float(torch.stack(self.touched).float().mean())
+        else:
+            touched = e_loc * (1.0 - (1.0 - 1.0 / s.n_experts) ** (self.tokens * s.topk))
+        weights = int(touched * 2 * s.moe_inter * s.hidden * 9 // 16)   # e2m1 codes + e4m3 scales
         acts = pairs_local * s.hidden * 9 // 16
         out = pairs_local * 2 * s.moe_inter * 2
         return weights + acts + out
+
+    @property
+    def dominant_flops(self) -> int:
+        s = self.shape
+        return 2 * (self.tokens * s.topk // self.world) * 2 * s.moe_inter * s.hidden
 
     def config(self) -> dict:
         s = self.shape
@@ -174,7 +203,28 @@ class PrefillStackWorkload:
                 "l2_policy": "inputs_exceed_l2 (6.3 GB of expert weights + 117 MB of hidden "
                              "states stream through the 126 MB L2 every layer)"}
 
+    graph = None
+
+    def capture_graph(self):
+        """Captures one forward of the stack in a CUDA graph (what racetrack/bench.py:98-111
+        does for its sweeps); steps then replay it. Every op only enqueues work on the current
+        stream and allocates through torch, so the whole stack is capturable."""
+        from racetrack_b200 import _lib
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        with torch.cuda.stream(side):
+            self.model.forward_stack(self.hidden, self.positions, self.layers)
+        torch.cuda.current_stream().wait_stream(side)
+        before = _lib.launch_count()
+        self.graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.graph):
+            self.graph_out = self.model.forward_stack(self.hidden, self.positions, self.layers)
+        self.launches_per_replay = _lib.launch_count() - before
+
     def step(self, record: bool = False):
+        if self.graph is not None and not record:
+            self.graph.replay()
+            return self.graph_out
         self.recording = record
         out = self.model.forward_stack(self.hidden, self.positions, self.layers)
         self.recording = False
@@ -187,6 +237,11 @@ class PrefillStackWorkload:
         self.host_out = torch.empty(self.hidden.shape, dtype=torch.bfloat16, pin_memory=True)
 
     def e2e_step(self):
+        if self.graph is not None:       # the graph reads self.hidden: refresh it from the host
+            self.hidden.copy_(self.host_in, non_blocking=True)
+            self.graph.replay()
+            self.host_out.copy_(self.graph_out, non_blocking=True)
+            return self.graph_out
         self.dev_in.copy_(self.host_in, non_blocking=True)
         out = self.model.forward_stack(self.dev_in, self.positions, self.layers)
         self.host_out.copy_(out, non_blocking=True)
@@ -372,6 +427,11 @@ def run_ours(args) -> None:
     _lib.load()
     wl = WORKLOADS[args.workload](device, rank, world, args)
 
+    use_graph = args.graph and hasattr(wl, "capture_graph")
+    if use_graph:
+        wl.step()
+        barrier()
+        wl.capture_graph()
     for _ in range(args.warmup):
         wl.step()
     barrier()
@@ -383,13 +443,20 @@ def run_ours(args) -> None:
         torch.cuda.profiler.start()
     start.record()
     for _ in range(args.steps):
-        wl.step(record=True)
+        wl.step(record=not use_graph)
     end.record()
     barrier()
     if args.profiler_range:
         torch.cuda.profiler.stop()
     launches = _lib.launch_count() - launches0
     ms_total = max_over_ranks(start.elapsed_time(end))
+    if use_graph:
+        # a replayed graph runs no host code: launches are those recorded at capture, and the
+        # dominant kernel is timed by events in two extra eager steps after the timed region
+        launches = wl.launches_per_replay * args.steps
+        for _ in range(2):
+            wl.step(record=True)
+        barrier()
     dom_us = statistics.mean(s.elapsed_time(e) for s, e in wl.dom_events) * 1e3
 
     wl.e2e_setup()
@@ -410,8 +477,29 @@ def run_ours(args) -> None:
     ops.tc_error_state()
 
     if rank == 0:
-        peak, peak_src = measured_peaks()
-        achieved = wl.dominant_bytes / (dom_us * 1e-6) / 1e9
+        hbm_peak, bf16_peak, peak_src = measured_peaks()
+        roof = {"bound": "hbm", "kernel": wl.dominant,
+                "achieved": wl.dominant_bytes / (dom_us * 1e-6) / 1e9, "peak": hbm_peak,
+                "unit": "GB/s"}
+        flops = getattr(wl, "dominant_flops", 0)
+        if flops:
+            # the kernel is a block-scaled e2m1 GEMM: its tensor ceiling is taken as 4 x the
+            # measured bf16 cuBLAS throughput (the nominal e2m1 : bf16 ratio of the part); the
+            # bound reported is whichever ideal time (bytes / HBM, flops / tensor) is longer
+            tensor_peak = 4.0 * bf16_peak
+            tensor = {"bound": "tensor", "kernel": wl.dominant,
+                      "achieved": flops / (dom_us * 1e-6) / 1e12, "peak": tensor_peak,
+                      "unit": "TFLOP/s",
+                      "peak_note": "4 x measured sustained bf16 cuBLAS (e2m1 : bf16 nominal ratio)"}
+            if flops / (tensor_peak * 1e12) > wl.dominant_bytes / (hbm_peak * 1e9):
+                roof, tensor = tensor, roof
+            roof["other_bound"] = {k: tensor[k] for k in ("bound", "achieved", "peak", "unit")}
+            roof["other_bound"]["frac"] = tensor["achieved"] / tensor["peak"]
+            roof["algorithmic_flops"] = flops
+        roof.update({"frac": roof["achieved"] / roof["peak"], "peak_source": peak_src,
+                     "traffic": getattr(wl, "dominant_traffic", None), "avg_launch_us": dom_us,
+                     "launches_timed": len(wl.dom_events),
+                     "algorithmic_bytes": wl.dominant_bytes})
         line = {
             "metric": wl.metric,
             "value": wl.units_per_step * args.steps / (ms_total * 1e-3)
@@ -422,10 +510,7 @@ def run_ours(args) -> None:
             "config": {**wl.config(),
                        "parallelism": f"tp{world}(heads)+ep{world}(experts)" if wl.scaling == "strong"
                        else f"replicated-stream x{world}"},
-            "roofline": {"bound": "hbm", "kernel": wl.dominant, "achieved": achieved, "peak": peak,
-                         "unit": "GB/s", "frac": achieved / peak, "peak_source": peak_src,
-                         "traffic": None, "avg_launch_us": dom_us, "launches_timed": len(wl.dom_events),
-                         "algorithmic_bytes": wl.dominant_bytes},
+            "roofline": roof,
             "e2e": {"value": wl.units_per_step * e2e_steps / (e2e_ms * 1e-3)
                              * (world if wl.scaling == "weak" else 1),
                     "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -433,6 +518,9 @@ def run_ours(args) -> None:
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        line["config"]["cuda_graph"] = bool(use_graph)
+        if use_graph:
+            line["roofline"]["timed_in"] = "two eager steps after the replayed region"
         if world == 1 and not args.no_cpu:
             cpu = cpu_line(type(wl), 3, 1)
             cpu.pop("ms_per_step")
@@ -454,6 +542,8 @@ def main() -> None:
     ap.add_argument("--proj", default="fp8", choices=("fp8", "bf16"),
                     help="arithmetic of the dense projections (FP8 e4m3 block-scaled or bf16)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--graph", action="store_true",
+                    help="capture the stack in a CUDA graph and replay it (decode sizes)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop")
     args = ap.parse_args()
