@@ -125,6 +125,10 @@ class PrefillStackWorkload:
         w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02)
         w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
         self.proj = args.proj
+        self.schedule = args.nvfp4_schedule
+        ops.gemm_nvfp4_schedule(1 if self.schedule == "single" else 2)
+        self.dominant = ("gemm_nvfp4_kernel" if self.schedule == "single"
+                         else "gemm_nvfp4_pair_kernel") + "[experts w13]"
         self.model = layer.RealisticLayer(self.shape, w, rank, world, proj=args.proj)
         gen = torch.Generator(device=device)
         gen.manual_seed(self.shape.seed)
@@ -197,7 +201,8 @@ class PrefillStackWorkload:
         s = self.shape
         return {"workload": self.name, "tokens": self.tokens, "layers": self.layers,
                 "hidden": s.hidden, "heads": s.heads, "experts": s.n_experts, "topk": s.topk,
-                "moe_inter": s.moe_inter, "experts_dtype": "nvfp4", "projections_dtype": self.proj,
+                "moe_inter": s.moe_inter, "experts_dtype": "nvfp4", "experts_gemm_schedule": self.schedule,
+                "projections_dtype": self.proj,
                 "attention_core": "torch sdpa (not a kernel of this backend)",
                 "routing": "topk_softmax (racetrack/realistic_bench.py:321-327)",
                 "l2_policy": "inputs_exceed_l2 (6.3 GB of expert weights + 117 MB of hidden "
@@ -541,6 +546,8 @@ def main() -> None:
     ap.add_argument("--layers", type=int, default=61)
     ap.add_argument("--proj", default="fp8", choices=("fp8", "bf16"),
                     help="arithmetic of the dense projections (FP8 e4m3 block-scaled or bf16)")
+    ap.add_argument("--nvfp4-schedule", default="pair", choices=("pair", "single"),
+                    help="schedule of the expert GEMMs (CTA pairs or single-CTA 128 x 128 tiles)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graph", action="store_true",
                     help="capture the stack in a CUDA graph and replay it (decode sizes)")

@@ -372,14 +372,19 @@ int rt_gemm_fp8(const void* a, const float* a_scales, const void* b, const float
                 void* stream);
 
 /*
- * Work list of the grouped GEMM, built on the device from the per-expert row offsets
+ * Work lists of the grouped GEMM, built on the device from the per-expert row offsets
  * that rt_moe_permute wrote (no host synchronisation). For groups g in [g_begin, g_end),
  * rows [offsets[g], offsets[g+1]) are cut into m-tiles of 128 rows:
- *   tile_map   int32 [max_tiles, 4], 16-byte aligned: {g - g_begin, first row, valid rows,
- *              scale row-tile index}; the scale row-tile index equals the tile's own index,
- *              so every group starts on a 128-row scale-tile boundary
+ *   tile_map   int32 [2 * max_tiles, 4], 16-byte aligned. Entries [0, tile_count[0]):
+ *              {g - g_begin, first row, valid rows (<= 128), scale row-tile index}; the scale
+ *              row-tile index equals the tile's own index, so every group starts on a 128-row
+ *              scale-tile boundary. Entries [max_tiles, max_tiles + tile_count[1]): the same
+ *              rows cut into tiles of up to 256 rows, {g - g_begin, first row, valid rows
+ *              (<= 256), scale row-tile index of the first 128 rows}, the work list of the
+ *              CTA-pair schedule of rt_gemm_nvfp4_grouped
  *   tile_base  int32 [g_end - g_begin + 1]: index of each group's first tile; last = total
- *   tile_count int32 [1]: number of tiles written (clamped to max_tiles)
+ *   tile_count int32 [2]: number of 128-row tiles and of 256-row tiles written (each
+ *              clamped to max_tiles)
  * max_tiles >= ceil(rows/128) + number of groups is always enough.
  * ref: racetrack/models/deepseek.py:1012-1017 (the per-expert loop bounds this replaces).
  */
@@ -395,8 +400,13 @@ int rt_moe_tile_map(const int32_t* offsets, int64_t g_begin, int64_t g_end,
  * = the tile map's scale row-tile index; b_codes [groups * n, k/2] and b_sf (each group tiled
  * on its own, ceil(n/128) row tiles per group) hold the weights; a_gs / b_gs [groups] are the
  * fp32 global scales (device memory). c is bf16 [total_rows, n] with row pitch ldc.
+ * tile_map / tile_count / max_m_tiles: as rt_moe_tile_map wrote them with max_tiles =
+ * max_m_tiles (both halves of the map are needed: the schedule picks its own work list).
  * With groups == 1 and a tile map over [0, m) this is a dense NVFP4 linear layer.
  * k % 256 == 0, n % 8 == 0 (n % 128 == 0 when groups > 1).
+ * Default schedule: CTA pairs (cta_group::2). 256 weight rows per pair are the MMA's M, up to
+ * 256 token rows of one group its N (rounded up to 16 only), each CTA fetching half of the
+ * token rows; 1.9 x the flops per byte brought into an SM of the single-CTA 128 x 128 tiling.
  * ref: racetrack/models/deepseek.py:1013-1018 (expert(x[idx]) per routed expert),
  *      racetrack/realistic_bench.py:338-346 (gathered-weight bmm it replaces). The NVFP4
  *      arithmetic itself has no counterpart in racetrack.
@@ -406,6 +416,14 @@ int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* a_
                           void* c, const int32_t* tile_map, const int32_t* tile_count,
                           int64_t max_m_tiles, int64_t total_rows, int64_t groups,
                           int64_t n, int64_t k, int64_t ldc, void* stream);
+
+/*
+ * Schedule of rt_gemm_nvfp4_grouped for this process: 0 = default (CTA pairs, unless
+ * max_m_tiles * ceil(n/256) is below the SM count: then single-CTA tiles), 1 = single-CTA
+ * 128 x 128 tiles, 2 = CTA pairs. Returns the previous value; any other argument only queries.
+ * For A/B measurements and tests. No counterpart in racetrack.
+ */
+int rt_gemm_nvfp4_schedule(int schedule);
 
 /*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when

@@ -453,19 +453,416 @@ __global__ void __launch_bounds__(kFThreads, 1) gemm_nvfp4_kernel(
     }
 }
 
-// Builds the work list of the grouped GEMM from the per-expert row offsets of the sorted
+// ---------------------------------------------------------------------------
+// Block-scaled NVFP4 grouped GEMM on CTA pairs (tcgen05 cta_group::2)
+// ---------------------------------------------------------------------------
+// Same contract as gemm_nvfp4_kernel, other schedule:
+//   * the WEIGHTS are the MMA's A operand: a pair of CTAs covers 256 weight rows, 128 each;
+//   * the TOKENS are the B operand: up to 256 rows of one group ("wide tile"); N is the
+//     power of two (16 ... 256) that covers them, so a group with few rows costs a narrow MMA
+//     instead of a padded 128-row tile; each CTA fetches half of the token rows and the tensor
+//     core reads both halves across the pair, which halves the token bytes per SM;
+//   * per 256 elements of K and CTA: 16 KB weights + <= 16 KB tokens for 2 * 128 * N * 256 flop.
+// What sets the pace of such a kernel on this part is not bytes but TMA INSTRUCTIONS: one SM
+// retires about one tiled load per 500 cycles whether its box holds 8 KB or 64 KB (measured:
+// 492 cycles per box of 8, 16 or 32 KB, 530 for 64 KB), while the MMAs of one 256-element K
+// block take about 540 cycles. So every load covers TWO K blocks (3-D tensor maps {128 bytes,
+// rows, K blocks}, box {128, rows, 2}): two instructions per 512 elements of K, and the
+// scale factors do not use the TMA unit at all (16-byte cp.async copies by one warp).
+// Shared memory: 3 operand stages of 64 KB (weights [2][128 rows][128 B], tokens
+// [2][N/2 rows][128 B], 128-byte swizzle) and a ring of 5 scale slots of 6 KB.
+// Tensor memory: the accumulator D[weight row, token] takes 256 columns (one buffer), the
+// other 240 hold the scales of 5 K blocks; the epilogue drains the accumulator into
+// registers, releases it, and only then writes: lane = weight row = output column, so one
+// warp store covers 64 contiguous bytes of one token's output row.
+// Warps (both CTAs): 0 operand producer (one elected thread), 1 tensor-memory owner and MMA
+// issuer (leader CTA, cluster rank 0) or relay (peer: tells the leader that its operands have
+// landed), 2-5 scale loaders (shared -> tensor memory), 6-13 epilogue (lane quarter w % 4,
+// token half (w - 6) / 4), 14 spare, 15 scale producer.
+// Barriers per CTA: cfull[d] (operands of stage d landed; in the leader also the peer's
+// relay), cempty[d] (MMAs of stage d done), sfull[s] / sfree[s] (scale slot s filled in /
+// copied out of shared memory), tsfree[s] (MMAs that read scale slot s of tensor memory
+// done), tfull (accumulator complete); in the leader: ready[s] (scales of both CTAs in tensor
+// memory, 8 warp arrivals) and tempty (accumulator drained by the 16 epilogue warps of the
+// pair). The leader commits cempty, tsfree and tfull to both CTAs.
+constexpr int kPStages = 3;                        // operand stages of two K blocks each
+constexpr int kPSlots = 5;                         // scale slots (shared and tensor memory)
+constexpr int kPThreads = 512;
+constexpr uint32_t kPWBytes = 2 * 128 * 128;       // weight rows of a stage (two K blocks)
+constexpr uint32_t kPXBytes = 2 * 128 * 128;       // token rows of a stage (this CTA's half)
+constexpr uint32_t kPStageBytes = kPWBytes + kPXBytes;
+constexpr uint32_t kPSfwBytes = 4 * 512;           // scale tiles of the weight rows, one K block
+constexpr uint32_t kPSfxBytes = 2 * 4 * 512;       // scale tiles of up to 256 token rows
+constexpr uint32_t kPSlotBytes = kPSfwBytes + kPSfxBytes;
+constexpr uint32_t kPSfOffset = kPStages * kPStageBytes;
+constexpr uint32_t kPBarOffset = kPSfOffset + kPSlots * kPSlotBytes;
+constexpr int kPBarriers = 2 * kPStages + 4 * kPSlots + 2;
+constexpr uint32_t kPSmemBytes = kPBarOffset + kPBarriers * 8 + 16 + 1024;
+constexpr uint32_t kPTmemCols = 512;
+constexpr uint32_t kPTmemSf = 256;                 // first scale column
+constexpr uint32_t kPSfCols = 48;                  // per slot: 16 weight + 32 token scale columns
+static_assert(kPStageBytes % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
+static_assert(kPTmemSf + kPSlots * kPSfCols <= kPTmemCols, "tensor memory budget");
+static_assert(kPSmemBytes <= 232448, "shared memory budget");
+
+struct TokenMaps {
+    CUtensorMap box[5];     // the token operand with boxes of 8, 16, 32, 64 and 128 rows
+};
+
+// Optional pipeline trace (never compiled into the library): with -DRT_PAIR_TRACE the leader
+// CTA of pair 0 stamps clock64() at eight points of its first 128 K blocks.
+#ifdef RT_PAIR_TRACE
+__device__ long long g_pair_trace[8 * 128];
+#define RT_TRACE(ev, it) \
+    do { if (blockIdx.x == 0 && (it) < 128) g_pair_trace[(ev) * 128 + (it)] = clock64(); } while (0)
+#else
+#define RT_TRACE(ev, it) do { } while (0)
+#endif
+
+// Token rows one CTA of the pair fetches for a wide tile of `valid` rows: the power of two
+// (>= 8) that covers half of them.
+__device__ __forceinline__ int pair_half_rows(int valid) {
+    int nh = 8;
+    while (2 * nh < valid) nh <<= 1;
+    return nh;
+}
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_nvfp4_pair_kernel(
+    const __grid_constant__ CUtensorMap tmap_w, const __grid_constant__ TokenMaps tmaps_x,
+    const uint8_t* __restrict__ sfx, const uint8_t* __restrict__ sfw,
+    const float* __restrict__ x_gs, const float* __restrict__ w_gs, __nv_bfloat16* __restrict__ c,
+    const int4* __restrict__ wide_map, const int* __restrict__ wide_count, int N, int K,
+    int64_t ldc) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + kPBarOffset;
+    auto cfull_bar = [&](int d) { return bars + 8u * d; };
+    auto cempty_bar = [&](int d) { return bars + 8u * (kPStages + d); };
+    auto sfull_bar = [&](int s) { return bars + 8u * (2 * kPStages + s); };
+    auto sfree_bar = [&](int s) { return bars + 8u * (2 * kPStages + kPSlots + s); };
+    auto tsfree_bar = [&](int s) { return bars + 8u * (2 * kPStages + 2 * kPSlots + s); };
+    auto ready_bar = [&](int s) { return bars + 8u * (2 * kPStages + 3 * kPSlots + s); };
+    const uint32_t tfull_bar = bars + 8u * (2 * kPStages + 4 * kPSlots);
+    const uint32_t tempty_bar = tfull_bar + 8u;
+    const uint32_t slot_addr = tfull_bar + 16u;
+    volatile uint32_t* slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(base_ptr + kPBarOffset + 8 * kPBarriers);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_w = (N + 255) / 256;              // weight tiles of 256 rows
+    const int num_tiles = __ldg(wide_count) * num_w;
+    const int num_kb = K / 256;                     // K blocks of 256 elements
+    const int num_ds = (num_kb + 1) / 2;            // operand stages per tile
+    const int kt = K / 64;                          // scale k-tiles per row tile
+    const int n_row_tiles = (N + 127) / 128;        // scale row tiles per group of weights
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int d = 0; d < kPStages; ++d) {
+            mbar_init(cfull_bar(d), rank == 0 ? 2 : 1);   // own producer (+ the peer's relay)
+            mbar_init(cempty_bar(d), 1);
+        }
+        for (int s = 0; s < kPSlots; ++s) {
+            mbar_init(sfull_bar(s), 32);     // 32 scale-copy lanes
+            mbar_init(sfree_bar(s), 4);      // 4 scale-loader warps
+            mbar_init(tsfree_bar(s), 1);
+            mbar_init(ready_bar(s), 8);      // 4 scale-loader warps in each CTA of the pair
+        }
+        mbar_init(tfull_bar, 1);
+        mbar_init(tempty_bar, 16);           // 8 epilogue warps in each CTA of the pair
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_w);
+#pragma unroll
+        for (int b = 0; b < 5; ++b) tma_prefetch_desc(&tmaps_x.box[b]);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(slot_addr, kPTmemCols);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                          // the peer's barriers exist before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *slot_ptr;
+
+    if (warp == 0) {
+        // Operand producer: per stage one load of this CTA's 128 weight rows and one of its
+        // half of the token rows, two K blocks each.
+        if (lane == 0) {
+            int stage = 0, it = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                const int4 tm = __ldg(wide_map + tile / num_w);
+                const int wn = tile % num_w;
+                const int nh = pair_half_rows(tm.z);
+                const int x_row = tm.y + static_cast<int>(rank) * nh;
+                const int w_row = tm.x * N + wn * 256 + static_cast<int>(rank) * 128;
+                const int xb = 31 - __clz(nh) - 3;           // index of the box with nh rows
+                const uint32_t bytes = kPWBytes + static_cast<uint32_t>(nh) * 256u;
+                for (int ds = 0; ds < num_ds; ++ds, ++it) {
+                    if (!(ok = mbar_wait(cempty_bar(stage), phase ^ 1u, abort_flag, 21))) break;
+                    const uint32_t sa = base + stage * kPStageBytes;
+                    RT_TRACE(0, it);
+                    mbar_arrive_expect_tx(cfull_bar(stage), bytes);
+                    tma_load_3d(sa, &tmap_w, 0, w_row, 2 * ds, cfull_bar(stage));
+                    RT_TRACE(1, it);
+                    tma_load_3d(sa + kPWBytes, &tmaps_x.box[xb], 0, x_row, 2 * ds,
+                                cfull_bar(stage));
+                    RT_TRACE(6, it);
+                    if (++stage == kPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (rank == 0 && lane == 0) {
+            // the peer's barriers sit at the same offsets of its shared-memory window
+            const uint32_t peer_cempty0 = map_to_cta(cempty_bar(0), 1);
+            const uint32_t peer_tsfree0 = map_to_cta(tsfree_bar(0), 1);
+            const uint32_t peer_tfull = map_to_cta(tfull_bar, 1);
+            int stage = 0, sf_slot = 0, it = 0;
+            uint32_t phase = 0, sf_phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                const int4 tm = __ldg(wide_map + tile / num_w);
+                const uint32_t nh = static_cast<uint32_t>(pair_half_rows(tm.z));
+                const uint32_t n_mma = 2u * nh;
+                // e2m1 x e2m1, e4m3 scales, K-major, M = 256 over the pair, N = n_mma
+                const uint32_t idesc = (1u << 7) | (1u << 10) | ((n_mma >> 3) << 17) | (16u << 24);
+                if (!(ok = mbar_wait(tempty_bar, acc_phase ^ 1u, abort_flag, 22))) break;
+                tc_fence_after();
+                for (int ds = 0; ok && ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 23))) break;
+                    const uint32_t sa = base + stage * kPStageBytes;
+                    const int halves = min(2, num_kb - 2 * ds);
+                    for (int h = 0; h < halves; ++h, ++it) {
+                        if (!(ok = mbar_wait(ready_bar(sf_slot), sf_phase, abort_flag, 29))) break;
+                        RT_TRACE(4, it);
+                        tc_fence_after();
+                        const uint32_t t_sfw = tmem_base + kPTmemSf + kPSfCols * sf_slot;
+                        const uint32_t t_sfx = t_sfw + 16u;
+                        const uint64_t adesc = smem_desc_sw128(sa + h * (kPWBytes / 2));
+                        const uint64_t bdesc = smem_desc_sw128(sa + kPWBytes + h * nh * 128u);
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            mma_nvfp4_pair(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc,
+                                           t_sfw + 4u * j, t_sfx + 8u * j,
+                                           (ds | h | j) != 0 ? 1u : 0u);
+                        }
+                        mma_commit_pair(tsfree_bar(sf_slot));
+                        mma_commit_pair(peer_tsfree0 + 8u * sf_slot);
+                        RT_TRACE(5, it);
+                        if (++sf_slot == kPSlots) {
+                            sf_slot = 0;
+                            sf_phase ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                    mma_commit_pair(cempty_bar(stage));
+                    mma_commit_pair(peer_cempty0 + 8u * stage);
+                    if (++stage == kPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                mma_commit_pair(tfull_bar);
+                mma_commit_pair(peer_tfull);
+                acc_phase ^= 1u;
+            }
+        } else if (rank == 1 && lane == 0) {
+            // Relay: tells the leader that this CTA's operands of a stage have landed.
+            const uint32_t leader_cfull0 = map_to_cta(cfull_bar(0), 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                for (int ds = 0; ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 26))) break;
+                    mbar_arrive_cluster(leader_cfull0 + 8u * stage);
+                    if (++stage == kPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp < 6) {
+        // Scale loaders: warp w serves the tensor-memory lanes [32 * (w % 4), +32) of its own CTA.
+        // Slot in tensor memory: 16 columns of weight scales (4 per 64-element K step), then 32
+        // columns of token scales (per K step: 4 for token rows 0-127, 4 for 128-255).
+        const int quad = warp & 3;
+        const uint32_t ready_leader = map_to_cta(ready_bar(0), 0);
+        int sf_slot = 0, it = 0;
+        uint32_t sf_phase = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            const int4 tm = __ldg(wide_map + tile / num_w);
+            const bool two = tm.z > 128;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                if (!(ok = mbar_wait(sfull_bar(sf_slot), sf_phase, abort_flag, 24))) break;
+                if (warp == 2 && lane == 0) RT_TRACE(2, it);
+                const uint8_t* sf_smem = base_ptr + kPSfOffset + sf_slot * kPSlotBytes;
+                uint32_t rw[16], rx[32];
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const uint4 v = *reinterpret_cast<const uint4*>(sf_smem + j * 512 + lane * 16);
+                    rw[4 * j] = v.x; rw[4 * j + 1] = v.y; rw[4 * j + 2] = v.z; rw[4 * j + 3] = v.w;
+                    const uint4 x0 = *reinterpret_cast<const uint4*>(sf_smem + kPSfwBytes +
+                                                                     j * 512 + lane * 16);
+                    uint4 x1 = make_uint4(0u, 0u, 0u, 0u);
+                    if (two)
+                        x1 = *reinterpret_cast<const uint4*>(sf_smem + kPSfwBytes + 2048 + j * 512 +
+                                                             lane * 16);
+                    rx[8 * j] = x0.x; rx[8 * j + 1] = x0.y; rx[8 * j + 2] = x0.z; rx[8 * j + 3] = x0.w;
+                    rx[8 * j + 4] = x1.x; rx[8 * j + 5] = x1.y; rx[8 * j + 6] = x1.z; rx[8 * j + 7] = x1.w;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(sfree_bar(sf_slot));      // the shared slot may refill
+                // the MMAs that read this slot of tensor memory one lap ago are done
+                if (!(ok = mbar_wait(tsfree_bar(sf_slot), sf_phase ^ 1u, abort_flag, 30))) break;
+                tc_fence_after();
+                const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                                        kPTmemSf + kPSfCols * sf_slot;
+                tmem_st_32x16(t_slot, rw);
+                tmem_st_32x32(t_slot + 16u, rx);
+                tmem_st_wait();
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(ready_leader + 8u * sf_slot);
+                if (warp == 2 && lane == 0) RT_TRACE(3, it);
+                if (++sf_slot == kPSlots) {
+                    sf_slot = 0;
+                    sf_phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp == 15) {
+        // Scale producer: the scale tiles of a K block (2 KB for this CTA's weight rows, 2 or 4 KB
+        // for all token rows of the tile) come in 16-byte cp.async copies, 4 per lane and tile
+        // set, through the load/store unit: the TMA unit is the bottleneck and stays free of
+        // them.
+        int sf_slot = 0, it = 0;
+        uint32_t sf_phase = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            const int4 tm = __ldg(wide_map + tile / num_w);
+            const int wn = tile % num_w;
+            int w_rt = wn * 2 + static_cast<int>(rank);
+            if (w_rt >= n_row_tiles) w_rt = n_row_tiles - 1;   // rows past N: results unused
+            const uint8_t* sfw_t =
+                sfw + (static_cast<int64_t>(tm.x) * n_row_tiles + w_rt) * kt * 512 + lane * 16;
+            const uint8_t* sfx_t = sfx + static_cast<int64_t>(tm.w) * kt * 512 + lane * 16;
+            const bool two = tm.z > 128;
+            for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                if (!(ok = mbar_wait(sfree_bar(sf_slot), sf_phase ^ 1u, abort_flag, 27))) break;
+                const uint32_t ssf = base + kPSfOffset + sf_slot * kPSlotBytes + lane * 16;
+                const int64_t o = static_cast<int64_t>(kb) * 2048;
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    cp_async16(ssf + j * 512, sfw_t + o + j * 512);
+                    cp_async16(ssf + kPSfwBytes + j * 512, sfx_t + o + j * 512);
+                    if (two)
+                        cp_async16(ssf + kPSfwBytes + 2048 + j * 512,
+                                   sfx_t + static_cast<int64_t>(kt) * 512 + o + j * 512);
+                }
+                cp_async_arrive(sfull_bar(sf_slot));
+                if (lane == 0) RT_TRACE(7, it);
+                if (++sf_slot == kPSlots) {
+                    sf_slot = 0;
+                    sf_phase ^= 1u;
+                }
+            }
+        }
+    } else if (warp >= 6 && warp < 14) {
+        const int quad = warp & 3, half = (warp - 6) >> 2;
+        const uint32_t tempty_leader = map_to_cta(tempty_bar, 0);
+        uint32_t tphase = 0;
+        bool ok = true;
+        const float xgs = __ldg(x_gs);
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            const int4 tm = __ldg(wide_map + tile / num_w);
+            const int wn = tile % num_w;
+            const int n_mma = 2 * pair_half_rows(tm.z);
+            const float alpha = xgs * __ldg(w_gs + tm.x);
+            if (!(ok = mbar_wait(tfull_bar, tphase, abort_flag, 25))) break;
+            tc_fence_after();
+            __nv_bfloat162 packed[64];
+#pragma unroll
+            for (int chunk = 0; chunk < 4; ++chunk) {
+                const int col0 = half * 128 + chunk * 32;
+                if (col0 < n_mma) {
+                    uint32_t r[32];
+                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                                      static_cast<uint32_t>(col0), r);
+                    tmem_ld_wait(r);
+#pragma unroll
+                    for (int i = 0; i < 16; ++i)
+                        packed[16 * chunk + i] =
+                            __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * alpha,
+                                                  __uint_as_float(r[2 * i + 1]) * alpha);
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader);
+            // the accumulator is free again; write this thread's output column
+            const int f = wn * 256 + static_cast<int>(rank) * 128 + quad * 32 + lane;
+            if (f < N) {
+#pragma unroll
+                for (int chunk = 0; chunk < 4; ++chunk) {
+                    const int col0 = half * 128 + chunk * 32;
+                    if (col0 < tm.z) {
+                        __nv_bfloat16* cp = c + static_cast<int64_t>(tm.y + col0) * ldc + f;
+#pragma unroll
+                        for (int i = 0; i < 16; ++i) {
+                            if (col0 + 2 * i < tm.z) cp[0] = packed[16 * chunk + i].x;
+                            if (col0 + 2 * i + 1 < tm.z) cp[ldc] = packed[16 * chunk + i].y;
+                            cp += 2 * ldc;
+                        }
+                    }
+                }
+            }
+            tphase ^= 1u;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();     // no CTA leaves, or frees tensor memory, while its peer may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, kPTmemCols);
+    }
+}
+
+// Builds the work lists of the grouped GEMMs from the per-expert row offsets of the sorted
 // (token, slot) pairs. One CTA. For groups g in [g_begin, g_end):
 //   tile_map[t] = {g - g_begin, first row, valid rows (<= 128), scale row-tile index}
 //   tile_base[g - g_begin] = index of the group's first tile (= its first scale row tile),
-//   tile_base[g_end - g_begin] = tile_count[0] = number of tiles.
+//   tile_base[g_end - g_begin] = tile_count[0] = number of tiles;
+// and, in the second half of tile_map, the same rows cut into "wide" tiles of up to 256 rows
+// (two scale row tiles) for the CTA-pair kernel:
+//   tile_map[max_tiles + u] = {g - g_begin, first row, valid rows (<= 256), scale row-tile
+//   index of its first 128 rows}, u < tile_count[1].
+// Both prefix sums ride in one 64-bit scan (128-row tiles in the low word, wide tiles in the
+// high word).
 __global__ void __launch_bounds__(1024) moe_tile_map_kernel(const int32_t* __restrict__ offsets,
                                                             int g_begin, int g_end,
                                                             int4* __restrict__ tile_map,
                                                             int32_t* __restrict__ tile_base,
                                                             int32_t* __restrict__ tile_count,
                                                             int max_tiles) {
-    __shared__ int warp_tot[32];
-    __shared__ int carry_s;
+    __shared__ long long warp_tot[32];
+    __shared__ long long carry_s;
     if (threadIdx.x == 0) carry_s = 0;
     __syncthreads();
     const int groups = g_end - g_begin;
@@ -476,28 +873,31 @@ __global__ void __launch_bounds__(1024) moe_tile_map_kernel(const int32_t* __res
             row0 = offsets[g_begin + g];
             rows = offsets[g_begin + g + 1] - row0;
         }
-        const int ntile = (rows + 127) >> 7;
+        const int ntile = (rows + 127) >> 7, nwide = (rows + 255) >> 8;
+        const long long mine = static_cast<long long>(ntile) | (static_cast<long long>(nwide) << 32);
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-        int incl = ntile;
+        long long incl = mine;
 #pragma unroll
         for (int o = 1; o < 32; o <<= 1) {
-            const int v = __shfl_up_sync(0xffffffffu, incl, o);
+            const long long v = __shfl_up_sync(0xffffffffu, incl, o);
             if (lane >= o) incl += v;
         }
         if (lane == 31) warp_tot[warp] = incl;
         __syncthreads();
         if (warp == 0) {
-            const int w = (lane < (int)(blockDim.x >> 5)) ? warp_tot[lane] : 0;
-            int wi = w;
+            const long long w = (lane < (int)(blockDim.x >> 5)) ? warp_tot[lane] : 0;
+            long long wi = w;
 #pragma unroll
             for (int o = 1; o < 32; o <<= 1) {
-                const int v = __shfl_up_sync(0xffffffffu, wi, o);
+                const long long v = __shfl_up_sync(0xffffffffu, wi, o);
                 if (lane >= o) wi += v;
             }
             warp_tot[lane] = wi - w;
         }
         __syncthreads();
-        const int first = carry_s + warp_tot[warp] + incl - ntile;
+        const long long excl = carry_s + warp_tot[warp] + incl - mine;
+        const int first = static_cast<int>(excl & 0xffffffffLL);
+        const int wfirst = static_cast<int>(excl >> 32);
         if (g < groups) {
             tile_base[g] = first;
             for (int t = 0; t < ntile; ++t) {
@@ -505,14 +905,21 @@ __global__ void __launch_bounds__(1024) moe_tile_map_kernel(const int32_t* __res
                     tile_map[first + t] =
                         make_int4(g, row0 + t * 128, min(128, rows - t * 128), first + t);
             }
+            for (int t = 0; t < nwide; ++t) {
+                if (wfirst + t < max_tiles)
+                    tile_map[max_tiles + wfirst + t] =
+                        make_int4(g, row0 + t * 256, min(256, rows - t * 256), first + 2 * t);
+            }
         }
         __syncthreads();
-        if (threadIdx.x == blockDim.x - 1) carry_s = first + ntile;
+        if (threadIdx.x == blockDim.x - 1) carry_s = excl + mine;
         __syncthreads();
     }
     if (threadIdx.x == 0) {
-        tile_base[groups] = carry_s;
-        tile_count[0] = min(carry_s, max_tiles);
+        const int total = static_cast<int>(carry_s & 0xffffffffLL);
+        tile_base[groups] = total;
+        tile_count[0] = min(total, max_tiles);
+        tile_count[1] = min(static_cast<int>(carry_s >> 32), max_tiles);
     }
 }
 
@@ -757,6 +1164,26 @@ int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint
     return RT_OK;
 }
 
+// 3-D K-major tensor map over a [rows, pitch] byte matrix whose rows are cut into K blocks of
+// 128 bytes: dims {128, rows, pitch / 128}, box {128, box_rows, box_kblocks}. One load brings
+// box_kblocks swizzled K-major tiles, stored one after the other.
+int make_tmap_kblocks(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t pitch_bytes,
+                      uint32_t box_rows, uint32_t box_kblocks) {
+    EncodeTiledFn fn = encode_fn();
+    RT_REQUIRE(fn, RT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {128, rows, pitch_bytes / 128};
+    const cuuint64_t strides[2] = {pitch_bytes, 128};
+    const cuuint32_t box[3] = {128, box_rows, box_kblocks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RT_REQUIRE(r == CUDA_SUCCESS, RT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d",
+               static_cast<int>(r));
+    return RT_OK;
+}
+
 int sm_count() {
     static int n = 0;
     if (n == 0) {
@@ -816,11 +1243,16 @@ static int launch_fp8(const void* a, const float* a_s, const void* b, const floa
     return check_launch("gemm_fp8_kernel");
 }
 
-static int launch_nvfp4(const void* a_codes, const void* a_sf, const float* a_gs,
-                        const void* b_codes, const void* b_sf, const float* b_gs, void* c,
-                        const int32_t* tile_map, const int32_t* tile_count, int64_t max_m_tiles,
-                        int64_t total_rows, int64_t groups, int64_t N, int64_t K, int64_t ldc,
-                        cudaStream_t st) {
+// Schedule of the NVFP4 GEMM: 0 = by size (CTA pairs unless the work list is too short to
+// occupy them), 1 = single-CTA 128 x 128 tiles, 2 = CTA pairs. Process-wide; meant for A/B
+// measurements and tests.
+static int g_nvfp4_schedule = 0;
+
+static int launch_nvfp4_single(const void* a_codes, const void* a_sf, const float* a_gs,
+                               const void* b_codes, const void* b_sf, const float* b_gs, void* c,
+                               const int32_t* tile_map, const int32_t* tile_count,
+                               int64_t max_m_tiles, int64_t total_rows, int64_t groups, int64_t N,
+                               int64_t K, int64_t ldc, cudaStream_t st) {
     CUtensorMap ta, tb;
     if (int rc = make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, a_codes, K / 2, total_rows,
                               K / 2, 128, kBM))
@@ -844,6 +1276,37 @@ static int launch_nvfp4(const void* a_codes, const void* a_sf, const float* a_gs
         static_cast<int>(N), static_cast<int>(K), ldc);
     count_launch();
     return check_launch("gemm_nvfp4_kernel");
+}
+
+static int launch_nvfp4_pair(const void* a_codes, const void* a_sf, const float* a_gs,
+                             const void* b_codes, const void* b_sf, const float* b_gs, void* c,
+                             const int32_t* tile_map, const int32_t* tile_count,
+                             int64_t max_m_tiles, int64_t total_rows, int64_t groups, int64_t N,
+                             int64_t K, int64_t ldc, cudaStream_t st) {
+    CUtensorMap tw;
+    TokenMaps tx;
+    if (int rc = make_tmap_kblocks(&tw, b_codes, groups * N, K / 2, 128, 2)) return rc;
+    for (int b = 0; b < 5; ++b) {
+        if (int rc = make_tmap_kblocks(&tx.box[b], a_codes, total_rows, K / 2, 8u << b, 2)) return rc;
+    }
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_pair_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kPSmemBytes));
+        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_nvfp4_grouped: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    // wide tiles: never more than 128-row tiles, so max_m_tiles bounds them as well
+    const int64_t tiles = max_m_tiles * ((N + 255) / 256);
+    const int64_t max_pairs = sm_count() / 2;
+    const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    gemm_nvfp4_pair_kernel<<<grid, kPThreads, kPSmemBytes, st>>>(
+        tw, tx, static_cast<const uint8_t*>(a_sf), static_cast<const uint8_t*>(b_sf), a_gs, b_gs,
+        static_cast<__nv_bfloat16*>(c), reinterpret_cast<const int4*>(tile_map) + max_m_tiles,
+        tile_count + 1, static_cast<int>(N), static_cast<int>(K), ldc);
+    count_launch();
+    return check_launch("gemm_nvfp4_pair_kernel");
 }
 
 }  // namespace tc
@@ -904,8 +1367,28 @@ extern "C" int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, cons
                RT_ERR_UNSUPPORTED, "rt_gemm_nvfp4_grouped: pointers must be 16-byte aligned");
     RT_REQUIRE(total_rows < (1LL << 31) && groups * n < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_nvfp4_grouped: dimension too large");
-    return tc::launch_nvfp4(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, c, tile_map, tile_count,
-                            max_m_tiles, total_rows, groups, n, k, ldc, as_stream(stream));
+    // Pairs need 2 x 74 CTAs' worth of 256-row weight tiles to pay off; below that the 128 x 128
+    // tiles spread the same work over more SMs.
+    const bool few_tiles = max_m_tiles * ((n + 255) / 256) < tc::sm_count();
+    if (tc::g_nvfp4_schedule == 1 || (tc::g_nvfp4_schedule == 0 && few_tiles))
+        return tc::launch_nvfp4_single(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, c, tile_map,
+                                       tile_count, max_m_tiles, total_rows, groups, n, k, ldc,
+                                       as_stream(stream));
+    return tc::launch_nvfp4_pair(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, c, tile_map, tile_count,
+                                 max_m_tiles, total_rows, groups, n, k, ldc, as_stream(stream));
+}
+
+#ifdef RT_PAIR_TRACE
+extern "C" int rt_pair_trace_read(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, tc::g_pair_trace, sizeof(long long) * 8 * 128) == cudaSuccess
+               ? RT_OK : RT_ERR_CUDA;
+}
+#endif
+
+extern "C" int rt_gemm_nvfp4_schedule(int schedule) {
+    const int previous = tc::g_nvfp4_schedule;
+    if (schedule >= 0 && schedule <= 2) tc::g_nvfp4_schedule = schedule;
+    return previous;
 }
 
 extern "C" int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, int64_t k,

@@ -41,6 +41,11 @@ __device__ __forceinline__ void fence_mbar_init() {
 __device__ __forceinline__ void fence_proxy_async() {
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
 }
+// Orders generic-proxy writes this thread has observed (st.shared, landed cp.async) before
+// later accesses through the async proxy (TMA, tcgen05.mma operand reads), all state spaces.
+__device__ __forceinline__ void fence_proxy_async_all() {
+    asm volatile("fence.proxy.async;" ::: "memory");
+}
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
@@ -48,14 +53,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes)
                  : "memory");
 }
+// The suspend-time hint bounds how long the hardware may park the thread inside one try_wait:
+// with the default limit a second warp waiting on the same barrier was seen to resume only when
+// the limit (about 2700 cycles) ran out instead of when the phase completed.
+#ifndef RT_TRY_WAIT_NS
+#define RT_TRY_WAIT_NS 100
+#endif
 __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok)
-        : "r"(bar), "r"(parity)
+        : "r"(bar), "r"(parity), "r"(static_cast<uint32_t>(RT_TRY_WAIT_NS))
         : "memory");
     return ok != 0;
 }
@@ -110,6 +121,22 @@ __device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_
             "r"(dst),
         "l"(src), "r"(bytes), "r"(bar)
         : "memory");
+}
+
+// 16-byte asynchronous copy global -> shared through the load/store unit (not the TMA unit),
+// bypassing L1.
+__device__ __forceinline__ void cp_async16(uint32_t dst, const void* src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+// Same, copying `src_bytes` (0 or 16) bytes and zero-filling the rest of the 16.
+__device__ __forceinline__ void cp_async16_zfill(uint32_t dst, const void* src, uint32_t src_bytes) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(src_bytes)
+                 : "memory");
+}
+// One arrival on `bar` (counted against its expected arrivals) once every cp.async this thread
+// has issued so far has landed.
+__device__ __forceinline__ void cp_async_arrive(uint32_t bar) {
+    asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(bar) : "memory");
 }
 
 // ---- tensor memory ----------------------------------------------------------------
@@ -239,6 +266,74 @@ __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r
 }
 __device__ __forceinline__ void tmem_st_wait() {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+// Same, 16 columns.
+__device__ __forceinline__ void tmem_st_32x16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+        "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};" ::"r"(taddr),
+        "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+        "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+        : "memory");
+}
+
+// ---- CTA pairs (cluster of two, tcgen05 cta_group::2) ---------------------------------
+// One thread of the pair's leader (cluster rank 0) issues MMAs that span both CTAs: each CTA
+// supplies 128 rows of A and half of the rows of B from its own shared memory (same offsets
+// in both), keeps the scale factors in its own tensor memory and receives the accumulator
+// rows of its A rows. Loads never use multicast: every CTA fetches its own operands.
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address, in the cluster's shared window, of the same shared-memory offset in CTA `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::
+                     : "memory");
+}
+// Arrival on an mbarrier of any CTA of the cluster (address from map_to_cta). Default
+// semantics (release at CTA scope): what the arrival has to order are tcgen05 operations,
+// which tcgen05.fence::before_thread_sync / after_thread_sync order around it, and
+// shared-memory traffic of the async proxy, which the mbarrier itself orders. A release at
+// cluster scope is a full memory fence and cost about a microsecond per arrival here.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Tensor memory of both CTAs of the pair; executed by one warp in each of the two CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t slot_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(slot_smem),
+                 "r"(ncols)
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols)
+                 : "memory");
+}
+// Block-scaled NVFP4 MMA over the pair: 256 x N x 64.
+__device__ __forceinline__ void mma_nvfp4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
+                                               uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X "
+        "[%0], %1, %2, %3, [%4], [%5], p;\n\t}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa_tmem), "r"(sfb_tmem), "r"(accumulate)
+        : "memory");
+}
+// Arrives on `bar` (any CTA of the cluster) once every pair MMA issued so far has completed.
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(
+                     cluster_addr)
+                 : "memory");
 }
 
 }  // namespace tc

@@ -142,13 +142,19 @@ def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, s
         x, w = _randn(T, k), _randn(n, k)
         xq = ops.fused_nvfp4_quant(x, tiled_scales=True)
         wq = ops.fused_nvfp4_quant(w, tiled_scales=True)
-        out[f"linear_nvfp4[{name} {T}x{n}x{k}]"] = (
-            (lambda xq=xq, wq=wq: ops.linear_nvfp4(*xq, *wq)), 2 * T * n * k,
-            (T * k + n * k) * 9 // 16 + T * n * 2, "nvfp4")
+        for sched, tag in ((2, "pair"), (1, "single")):
+            def run(xq=xq, wq=wq, sched=sched):
+                ops.gemm_nvfp4_schedule(sched)
+                try:
+                    return ops.linear_nvfp4(*xq, *wq)
+                finally:
+                    ops.gemm_nvfp4_schedule(0)
+            out[f"linear_nvfp4/{tag}[{name} {T}x{n}x{k}]"] = (
+                run, 2 * T * n * k, (T * k + n * k) * 9 // 16 + T * n * 2, "nvfp4")
     return out
 
 
-def run_gemms(tokens: int, iters: int, flush: "L2Flusher") -> list[dict]:
+def run_gemms(tokens: int, iters: int, flush: "L2Flusher", only: str = "") -> list[dict]:
     peaks = {}
     p = Path(__file__).resolve().parent.parent / "MEASURED_PEAKS.json"
     if p.exists():
@@ -156,6 +162,8 @@ def run_gemms(tokens: int, iters: int, flush: "L2Flusher") -> list[dict]:
     bf16_peak = float(peaks.get("bf16_tflops", 1590.0))
     rows = []
     for name, (fn, flops, nbytes, kind) in gemm_cases(tokens).items():
+        if only and only not in name:
+            continue
         t = time_kernel(fn, iters=iters, flush=flush)
         tf = flops / (t["median_us"] * 1e-6) / 1e12
         # dense NVFP4 has no measured peak on this pool: quoted against the nominal 9 PFLOP/s
@@ -177,6 +185,7 @@ def main() -> None:
     ap.add_argument("--kernel", action="append", default=None)
     ap.add_argument("--iters", type=int, default=20)
     ap.add_argument("--gemm", action="store_true", help="also time the tensor-core GEMMs")
+    ap.add_argument("--gemm-filter", default="", help="only GEMM cases whose name contains this")
     ap.add_argument("--json", type=Path, default=None)
     args = ap.parse_args()
     peak, peak_src = hbm_peak_gbs()
@@ -197,7 +206,7 @@ def main() -> None:
               f"({launches} launch{'es' if launches != 1 else ''})", flush=True)
     gemm_rows = []
     if args.gemm:
-        gemm_rows = run_gemms(args.tokens, args.iters, flush)
+        gemm_rows = run_gemms(args.tokens, args.iters, flush, args.gemm_filter)
     if args.json:
         args.json.write_text(json.dumps({"hbm_peak_gbs": peak, "peak_source": peak_src,
                                          "rows": rows, "gemm_rows": gemm_rows}, indent=1) + "\n")

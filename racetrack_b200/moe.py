@@ -84,7 +84,7 @@ def moe_quant_nvfp4(x: torch.Tensor, tile_map: torch.Tensor, tile_count: torch.T
     (rt_moe_quant_nvfp4): gathers token rows when sorted_pairs is given, applies SwiGLU when
     `up` is given. Rows outside every tile are left unwritten."""
     cols = x.shape[-1]
-    max_tiles = tile_map.shape[0]
+    max_tiles = tile_map.shape[0] // 2
     dev = x.device
     codes = torch.empty(total_rows, cols // 2, dtype=torch.uint8, device=dev)
     sf = torch.empty(max_tiles * (cols // 64) * 512, dtype=torch.uint8, device=dev)

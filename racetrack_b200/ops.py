@@ -577,16 +577,19 @@ def linear_fp8_act(x: torch.Tensor, w_codes: torch.Tensor, w_scales: torch.Tenso
 
 
 def moe_tile_map(offsets: torch.Tensor, g_begin: int, g_end: int, max_tiles: int):
-    """Device-side work list of the grouped GEMM for groups [g_begin, g_end) of the row
-    offsets written by fused_moe_permute -> (tile_map int32 [max_tiles, 4], tile_base
-    int32 [groups + 1], tile_count int32 [1]). No host synchronisation."""
+    """Device-side work lists of the grouped GEMM for groups [g_begin, g_end) of the row
+    offsets written by fused_moe_permute -> (tile_map int32 [2 * max_tiles, 4], tile_base
+    int32 [groups + 1], tile_count int32 [2]). Rows [0, tile_count[0]) of tile_map are the
+    128-row tiles (one scale row tile each); rows [max_tiles, max_tiles + tile_count[1]) cut
+    the same rows into tiles of up to 256 rows for the CTA-pair GEMM. No host
+    synchronisation."""
     _require_cuda(offsets)
     if offsets.dtype != torch.int32:
         raise RuntimeError("moe_tile_map: offsets must be int32")
     dev = offsets.device
-    tile_map = torch.empty(max_tiles, 4, dtype=torch.int32, device=dev)
+    tile_map = torch.empty(2 * max_tiles, 4, dtype=torch.int32, device=dev)
     tile_base = torch.empty(g_end - g_begin + 1, dtype=torch.int32, device=dev)
-    tile_count = torch.empty(1, dtype=torch.int32, device=dev)
+    tile_count = torch.empty(2, dtype=torch.int32, device=dev)
     lib = _lib.load()
     _lib.check(lib.rt_moe_tile_map(offsets.data_ptr(), g_begin, g_end, tile_map.data_ptr(),
                                    tile_base.data_ptr(), tile_count.data_ptr(), max_tiles,
@@ -601,7 +604,8 @@ def gemm_nvfp4_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, a_gs: torch.Te
     """Block-scaled NVFP4 grouped GEMM (see rt_gemm_nvfp4_grouped in include/rt_b200.h).
 
     a_codes uint8 [rows, K/2]; a_sf tiled e4m3 scales (bytes); a_gs fp32 [1];
-    b_codes uint8 [groups * n, K/2]; b_sf tiled scales per group; b_gs fp32 [groups].
+    b_codes uint8 [groups * n, K/2]; b_sf tiled scales per group; b_gs fp32 [groups];
+    tile_map / tile_count as moe_tile_map returns them.
     Returns bf16 [rows, n]; rows outside every tile are left untouched."""
     _require_cuda(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, tile_map, tile_count)
     rows, kh = a_codes.shape
@@ -615,10 +619,17 @@ def gemm_nvfp4_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, a_gs: torch.Te
     _lib.check(lib.rt_gemm_nvfp4_grouped(a_codes.data_ptr(), a_sf.data_ptr(), a_gs.data_ptr(),
                                          b_codes.data_ptr(), b_sf.data_ptr(), b_gs.data_ptr(),
                                          out.data_ptr(), tile_map.data_ptr(),
-                                         tile_count.data_ptr(), tile_map.shape[0], rows, groups,
+                                         tile_count.data_ptr(), tile_map.shape[0] // 2, rows,
+                                         groups,
                                          n, 2 * kh, out.stride(0), _stream()),
                "rt_gemm_nvfp4_grouped")
     return out
+
+
+def gemm_nvfp4_schedule(schedule: int) -> int:
+    """Selects the schedule of the NVFP4 GEMM for this process (0 default = CTA pairs,
+    1 single-CTA 128 x 128 tiles, 2 CTA pairs) and returns the previous setting."""
+    return int(_lib.load().rt_gemm_nvfp4_schedule(int(schedule)))
 
 
 _DENSE_TILES: dict[tuple, tuple] = {}

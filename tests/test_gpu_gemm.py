@@ -142,15 +142,29 @@ def _check_nvfp4(out, ref64):
     assert bool((diff <= tol).all()), f"worst {float(diff.max())} (max |ref| {float(ref.abs().max())})"
 
 
+@pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
+def nvfp4_schedule(request, ops):
+    """Runs a test under both schedules of the NVFP4 GEMM (single-CTA 128 x 128 tiles, CTA
+    pairs with 256 weight rows x up to 256 token rows) and restores the default."""
+    previous = ops.gemm_nvfp4_schedule(request.param)
+    yield request.param
+    ops.gemm_nvfp4_schedule(previous)
+
+
 @pytest.mark.parametrize("m,n,k", [
     (128, 128, 256),       # one tile, one K stage
     (128, 128, 1024),      # one tile, several stages (scale buffers alternate)
-    (256, 256, 512),       # 2 x 2 tiles
+    (256, 256, 512),       # 2 x 2 tiles (one pair tile with both token scale tiles)
+    (16, 256, 256),        # narrowest pair MMA (N = 16)
+    (17, 256, 1536),       # 17 tokens -> N = 32, the stage ring wraps once
+    (129, 512, 512),       # second token scale tile holds a single row
+    (200, 384, 768),       # token halves of 104 rows (64 + 32 + 8 row boxes), weight rows past n
+    (300, 256, 512),       # a full wide tile and a 44-row one
     (100, 2112, 7168),     # ragged M, N not a multiple of the tile
     (1, 4096, 7168),       # decode row
     (2048, 4096, 7168),    # expert up-projection shape, many tiles per CTA
 ])
-def test_linear_nvfp4_dense(ops, m, n, k):
+def test_linear_nvfp4_dense(ops, nvfp4_schedule, m, n, k):
     x = I.randn((m, k), 300 + m).cuda()
     w = I.randn((n, k), 400 + n, std=0.05).cuda()
     xq = ops.fused_nvfp4_quant(x, tiled_scales=True)
@@ -162,7 +176,7 @@ def test_linear_nvfp4_dense(ops, m, n, k):
     _check_nvfp4(out, ref)
 
 
-def test_gemm_nvfp4_grouped_ragged(ops):
+def test_gemm_nvfp4_grouped_ragged(ops, nvfp4_schedule):
     """Five groups of 130, 0, 5, 256 and 1 rows: tiles never straddle groups, every group
     uses its own weights and global scale, empty groups cost nothing."""
     sizes = [130, 0, 5, 256, 1]
@@ -186,9 +200,13 @@ def test_gemm_nvfp4_grouped_ragged(ops):
     b_sf = torch.cat([q[1].view(torch.uint8) for q in wq])
     b_gs = torch.cat([q[2] for q in wq])
     tile_map, tile_base, tile_count = ops.moe_tile_map(offsets, 0, len(sizes), rows // 128 + len(sizes) + 1)
-    assert tile_base.cpu().tolist() == [0, 2, 2, 3, 5, 6] and int(tile_count) == 6
+    max_tiles = tile_map.shape[0] // 2
+    assert tile_base.cpu().tolist() == [0, 2, 2, 3, 5, 6] and tile_count.cpu().tolist() == [6, 4]
     assert tile_map.cpu()[:6].tolist() == [[0, 0, 128, 0], [0, 128, 2, 1], [2, 130, 5, 2],
                                            [3, 135, 128, 3], [3, 263, 128, 4], [4, 391, 1, 5]]
+    # the same rows in tiles of up to 256 (work list of the CTA-pair schedule)
+    assert tile_map.cpu()[max_tiles:max_tiles + 4].tolist() == [[0, 0, 130, 0], [2, 130, 5, 2],
+                                                                [3, 135, 256, 3], [4, 391, 1, 5]]
     out = torch.full((rows, n), float("nan"), dtype=torch.bfloat16, device="cuda")
     ops.gemm_nvfp4_grouped(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, tile_map, tile_count,
                            n=n, groups=len(sizes), out=out)
@@ -202,4 +220,5 @@ def test_gemm_nvfp4_grouped_ragged(ops):
         r0 += s
     # a sub-range of groups (an expert-parallel rank owning groups 2..4)
     tm2, tb2, tc2 = ops.moe_tile_map(offsets, 2, 5, 8)
-    assert int(tc2) == 4 and tm2.cpu()[0].tolist() == [0, 130, 5, 0]
+    assert tc2.cpu().tolist() == [4, 3] and tm2.cpu()[0].tolist() == [0, 130, 5, 0]
+    assert tm2.cpu()[8:11].tolist() == [[0, 130, 5, 0], [1, 135, 256, 1], [2, 391, 1, 3]]
