@@ -544,8 +544,9 @@ def main() -> None:
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=61)
-    ap.add_argument("--proj", default="fp8", choices=("fp8", "bf16"),
-                    help="arithmetic of the dense projections (FP8 e4m3 block-scaled or bf16)")
+    ap.add_argument("--proj", default="mixed", choices=("mixed", "fp8", "bf16"),
+                    help="arithmetic of the dense projections: FP8 e4m3 block-scaled, bf16, or "
+                         "mixed (FP8 where K >= 4096, bf16 elsewhere)")
     ap.add_argument("--nvfp4-schedule", default="pair", choices=("pair", "single"),
                     help="schedule of the expert GEMMs (CTA pairs or single-CTA 128 x 128 tiles)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")

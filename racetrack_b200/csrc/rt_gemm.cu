@@ -212,6 +212,225 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
 }
 
 // ---------------------------------------------------------------------------
+// bf16 GEMM on CTA pairs (tcgen05 cta_group::2): C[M, N] = A[M, K] * B[N, K]^T
+// ---------------------------------------------------------------------------
+// A pair of CTAs computes a 256 x 256 tile: each CTA supplies 128 rows of A and 128 rows of B
+// (the tensor core reads B across the pair) and keeps the 128 x 256 accumulator of its A rows.
+// Per 64 elements of K a CTA brings in 32 KB instead of the 48 KB of the single-CTA 128 x 256
+// tile, and operand bytes per SM are what bounds these kernels. Every TMA load covers two K
+// blocks (3-D maps {64 elements, rows, K blocks}, box {64, 128, 2}), because an SM retires only
+// about one tiled load per 500 cycles whatever its size. 3 stages of 64 KB; two accumulators
+// of 256 columns fill tensor memory, so the epilogue of a tile overlaps the next tile's MMAs.
+// Warps (both CTAs): 0 producer (one elected thread), 1 tensor-memory owner and MMA issuer
+// (leader, cluster rank 0) or relay (peer: forwards "my operands have landed"), 2-9 epilogue
+// (lane quarter w % 4, column half (w - 2) / 4).
+// Requires K % 64 == 0.
+constexpr int kBPStages = 3;
+constexpr int kBPThreads = 320;
+constexpr uint32_t kBPABytes = 2 * 128 * 128;
+constexpr uint32_t kBPBBytes = 2 * 128 * 128;
+constexpr uint32_t kBPStageBytes = kBPABytes + kBPBBytes;
+constexpr uint32_t kBPBarOffset = kBPStages * kBPStageBytes;
+constexpr uint32_t kBPSmemBytes = kBPBarOffset + (2 * kBPStages + 4) * 8 + 16 + 1024;
+// fp32 accumulate, bf16 x bf16, both K-major, N = 256, M = 256 over the pair
+constexpr uint32_t kBPIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (32u << 17) | (16u << 24);
+
+template <bool F32OUT>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kBPThreads, 1) gemm_bf16_pair_kernel(
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    void* __restrict__ c_out, int M, int N, int K, int64_t ldc) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + kBPBarOffset;
+    auto cfull_bar = [&](int d) { return bars + 8u * d; };
+    auto cempty_bar = [&](int d) { return bars + 8u * (kBPStages + d); };
+    auto tfull_bar = [&](int a) { return bars + 8u * (2 * kBPStages + a); };
+    auto tempty_bar = [&](int a) { return bars + 8u * (2 * kBPStages + 2 + a); };
+    const uint32_t slot = bars + 8u * (2 * kBPStages + 4);
+    volatile uint32_t* slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(base_ptr + kBPBarOffset + 8 * (2 * kBPStages + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_m = (M + 255) / 256, num_n = (N + 255) / 256;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = K / 64;
+    const int num_ds = (num_kb + 1) / 2;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int d = 0; d < kBPStages; ++d) {
+            mbar_init(cfull_bar(d), rank == 0 ? 2 : 1);   // own producer (+ the peer's relay)
+            mbar_init(cempty_bar(d), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(tfull_bar(a), 1);
+            mbar_init(tempty_bar(a), 16);    // 8 epilogue warps in each CTA of the pair
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                          // the peer's barriers exist before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                int tm, tn;
+                tile_coords(tile, num_m, num_n, tm, tn);
+                const int a_row = tm * 256 + static_cast<int>(rank) * 128;
+                const int b_row = tn * 256 + static_cast<int>(rank) * 128;
+                for (int ds = 0; ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cempty_bar(stage), phase ^ 1u, abort_flag, 31))) break;
+                    const uint32_t sa = base + stage * kBPStageBytes;
+                    mbar_arrive_expect_tx(cfull_bar(stage), kBPStageBytes);
+                    tma_load_3d(sa, &tmap_a, 0, a_row, 2 * ds, cfull_bar(stage));
+                    tma_load_3d(sa + kBPABytes, &tmap_b, 0, b_row, 2 * ds, cfull_bar(stage));
+                    if (++stage == kBPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (rank == 0 && lane == 0) {
+            const uint32_t peer_cempty0 = map_to_cta(cempty_bar(0), 1);
+            const uint32_t peer_tfull0 = map_to_cta(tfull_bar(0), 1);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                if (!(ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 32))) break;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * 256);
+                for (int ds = 0; ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 33))) break;
+                    tc_fence_after();
+                    const uint32_t sa = base + stage * kBPStageBytes;
+                    const int halves = min(2, num_kb - 2 * ds);
+                    for (int h = 0; h < halves; ++h) {
+                        const uint64_t adesc = smem_desc_sw128(sa + h * (kBPABytes / 2));
+                        const uint64_t bdesc =
+                            smem_desc_sw128(sa + kBPABytes + h * (kBPBBytes / 2));
+#pragma unroll
+                        for (int k = 0; k < 4; ++k) {
+                            // 16 bf16 = 32 bytes along K: +2 in the 16-byte-unit address field
+                            mma_f16_pair(d_tmem, adesc + 2u * k, bdesc + 2u * k, kBPIdesc,
+                                         (ds | h | k) != 0 ? 1u : 0u);
+                        }
+                    }
+                    mma_commit_pair(cempty_bar(stage));
+                    mma_commit_pair(peer_cempty0 + 8u * stage);
+                    if (++stage == kBPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (!ok) break;
+                mma_commit_pair(tfull_bar(acc));
+                mma_commit_pair(peer_tfull0 + 8u * acc);
+                if (++acc == 2) {
+                    acc = 0;
+                    acc_phase ^= 1u;
+                }
+            }
+        } else if (rank == 1 && lane == 0) {
+            const uint32_t leader_cfull0 = map_to_cta(cfull_bar(0), 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                for (int ds = 0; ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 34))) break;
+                    mbar_arrive_cluster(leader_cfull0 + 8u * stage);
+                    if (++stage == kBPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quad = warp & 3;  // the TMEM lane quarter this warp may read
+        const int half = (warp - 2) >> 2;
+        const uint32_t tempty_leader0 = map_to_cta(tempty_bar(0), 0);
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            int tm, tn;
+            tile_coords(tile, num_m, num_n, tm, tn);
+            if (!(ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 35))) break;
+            tc_fence_after();
+            const int row = tm * 256 + static_cast<int>(rank) * 128 + quad * 32 + lane;
+            __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(c_out) + static_cast<int64_t>(row) * ldc;
+            float* crow_f = static_cast<float*>(c_out) + static_cast<int64_t>(row) * ldc;
+#pragma unroll 1
+            for (int chunk = 4 * half; chunk < 4 * half + 4; ++chunk) {
+                uint32_t r[32];
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                                       static_cast<uint32_t>(acc * 256 + chunk * 32);
+                tmem_ld_32x32(taddr, r);
+                tmem_ld_wait(r);
+                if (row < M) {
+                    const int col0 = tn * 256 + chunk * 32;
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const int col = col0 + v * 8;
+                        if (col < N) {  // N % 8 == 0, so a started vector is complete
+                            if constexpr (F32OUT) {
+                                *reinterpret_cast<uint4*>(crow_f + col) =
+                                    make_uint4(r[8 * v], r[8 * v + 1], r[8 * v + 2], r[8 * v + 3]);
+                                *reinterpret_cast<uint4*>(crow_f + col + 4) =
+                                    make_uint4(r[8 * v + 4], r[8 * v + 5], r[8 * v + 6], r[8 * v + 7]);
+                                continue;
+                            }
+                            uint4 o;
+                            o.x = pack_bf16x2(__uint_as_float(r[8 * v + 0]), __uint_as_float(r[8 * v + 1]));
+                            o.y = pack_bf16x2(__uint_as_float(r[8 * v + 2]), __uint_as_float(r[8 * v + 3]));
+                            o.z = pack_bf16x2(__uint_as_float(r[8 * v + 4]), __uint_as_float(r[8 * v + 5]));
+                            o.w = pack_bf16x2(__uint_as_float(r[8 * v + 6]), __uint_as_float(r[8 * v + 7]));
+                            *reinterpret_cast<uint4*>(crow + col) = o;
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty_leader0 + 8u * acc);
+            if (++acc == 2) {
+                acc = 0;
+                acc_phase ^= 1u;
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();     // no CTA leaves, or frees tensor memory, while its peer may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+// ---------------------------------------------------------------------------
 // Block-scaled NVFP4 grouped GEMM
 // ---------------------------------------------------------------------------
 // C[rows of group g, N] = alpha_g * (A_fp4 (x) sfa) * (B_g fp4 (x) sfb_g)^T
@@ -1220,6 +1439,50 @@ static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t
     return check_launch("gemm_bf16_kernel");
 }
 
+// bf16 operand as 64-element K blocks: dims {64, rows, K / 64}, box {64, 128, 2}.
+static int make_tmap_bf16_kblocks(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t k,
+                                  uint64_t pitch_bytes) {
+    EncodeTiledFn fn = encode_fn();
+    RT_REQUIRE(fn, RT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {64, rows, k / 64};
+    const cuuint64_t strides[2] = {pitch_bytes, 128};
+    const cuuint32_t box[3] = {64, 128, 2};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RT_REQUIRE(r == CUDA_SUCCESS, RT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d",
+               static_cast<int>(r));
+    return RT_OK;
+}
+
+// Schedule of the bf16 GEMM: 0 = by size, 1 = single-CTA tiles, 2 = CTA pairs (needs K % 64 == 0).
+static int g_bf16_schedule = 0;
+
+template <bool F32OUT>
+static int launch_bf16_pair(const void* a, const void* b, void* c, int64_t M, int64_t N, int64_t K,
+                            int64_t lda, int64_t ldb, int64_t ldc, cudaStream_t st) {
+    CUtensorMap ta, tb;
+    if (int rc = make_tmap_bf16_kblocks(&ta, a, M, K, lda * 2)) return rc;
+    if (int rc = make_tmap_bf16_kblocks(&tb, b, N, K, ldb * 2)) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<F32OUT>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kBPSmemBytes));
+        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_bf16: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t max_pairs = sm_count() / 2;
+    const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    gemm_bf16_pair_kernel<F32OUT><<<grid, kBPThreads, kBPSmemBytes, st>>>(
+        ta, tb, c, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldc);
+    count_launch();
+    return check_launch("gemm_bf16_pair_kernel");
+}
+
 static int launch_fp8(const void* a, const float* a_s, const void* b, const float* b_s, void* c,
                       int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                       cudaStream_t st) {
@@ -1385,6 +1648,12 @@ extern "C" int rt_pair_trace_read(long long* host_out) {
 }
 #endif
 
+extern "C" int rt_gemm_bf16_schedule(int schedule) {
+    const int previous = tc::g_bf16_schedule;
+    if (schedule >= 0 && schedule <= 2) tc::g_bf16_schedule = schedule;
+    return previous;
+}
+
 extern "C" int rt_gemm_nvfp4_schedule(int schedule) {
     const int previous = tc::g_nvfp4_schedule;
     if (schedule >= 0 && schedule <= 2) tc::g_nvfp4_schedule = schedule;
@@ -1405,6 +1674,13 @@ extern "C" int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, in
     RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_bf16: dimension too large");
     cudaStream_t st = as_stream(stream);
+    // CTA pairs (256 x 256 tiles) once they fill the machine; they need whole 64-element K blocks
+    const bool pair_ok = k % 64 == 0;
+    const bool pair_pays = ((m + 255) / 256) * ((n + 255) / 256) >= tc::sm_count() / 2;
+    if (pair_ok && (tc::g_bf16_schedule == 2 || (tc::g_bf16_schedule == 0 && pair_pays))) {
+        if (out_dtype == RT_F32) return tc::launch_bf16_pair<true>(a, b, c, m, n, k, lda, ldb, ldc, st);
+        return tc::launch_bf16_pair<false>(a, b, c, m, n, k, lda, ldb, ldc, st);
+    }
     if (out_dtype == RT_F32) {
         if (n <= 128) return tc::launch_bf16<128, true>(a, b, c, m, n, k, lda, ldb, ldc, st);
         return tc::launch_bf16<256, true>(a, b, c, m, n, k, lda, ldb, ldc, st);

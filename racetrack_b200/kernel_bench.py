@@ -131,8 +131,15 @@ def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, s
     for name, n, k in (("qkv_a", Q_LORA + KV_LORA + ROPE, HIDDEN), ("q_b", HEADS * 192, Q_LORA),
                        ("kv_b", HEADS * 256, KV_LORA), ("w_o", HIDDEN, HEADS * 128)):
         x, w = _randn(T, k), _randn(n, k)
-        out[f"linear_bf16[{name} {T}x{n}x{k}]"] = (
-            (lambda x=x, w=w: ops.linear_bf16(x, w)), 2 * T * n * k, (T * k + n * k + T * n) * 2, "bf16")
+        for sched, tag in ((2, "pair"), (1, "single")):
+            def run_bf16(x=x, w=w, sched=sched):
+                ops.gemm_bf16_schedule(sched)
+                try:
+                    return ops.linear_bf16(x, w)
+                finally:
+                    ops.gemm_bf16_schedule(0)
+            out[f"linear_bf16/{tag}[{name} {T}x{n}x{k}]"] = (
+                run_bf16, 2 * T * n * k, (T * k + n * k + T * n) * 2, "bf16")
         wc, ws = ops.quantize_weight_fp8(w)
         xc, xs = ops.fused_act_quant(x)
         out[f"linear_fp8[{name} {T}x{n}x{k}]"] = (

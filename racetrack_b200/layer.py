@@ -148,10 +148,16 @@ def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.T
 class Projection:
     """A dense projection y = x W^T held either in bf16 or as FP8 e4m3 with 128 x 128 block
     scales (racetrack/models/deepseek.py:316-345 `linear`: bf16 weights go to F.linear, FP8
-    weights to act_quant + fp8_gemm). FP8 needs K % 128 == 0; other widths stay bf16."""
+    weights to act_quant + fp8_gemm). FP8 needs K % 128 == 0; other widths stay bf16.
+    dtype "mixed" keeps FP8 for the long reductions only (K >= MIXED_FP8_MIN_K): the FP8 GEMM
+    rescales every 128-wide K block in registers, which pays off against the bf16 CTA-pair
+    GEMM only when the tensor core has long K loops to hide it behind."""
+
+    MIXED_FP8_MIN_K = 4096
 
     def __init__(self, weight: torch.Tensor, dtype: str):
-        self.fp8 = dtype == "fp8" and weight.shape[1] % 128 == 0
+        k = weight.shape[1]
+        self.fp8 = k % 128 == 0 and (dtype == "fp8" or (dtype == "mixed" and k >= self.MIXED_FP8_MIN_K))
         if self.fp8:
             self.codes, self.scales = ops.quantize_weight_fp8(weight)
         else:
@@ -165,7 +171,7 @@ class Projection:
 
 class RealisticLayer:
     """One rank's shard of the synthetic layer; `forward_stack` applies it `layers` times.
-    proj = "bf16" | "fp8" selects the arithmetic of the dense projections."""
+    proj = "bf16" | "fp8" | "mixed" selects the arithmetic of the dense projections."""
 
     def __init__(self, shape: LayerShape, weights: dict, rank: int = 0, world: int = 1, *,
                  ffn: str = "moe", route: str = "topk_softmax", proj: str = "bf16",

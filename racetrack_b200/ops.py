@@ -626,6 +626,13 @@ def gemm_nvfp4_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, a_gs: torch.Te
     return out
 
 
+def gemm_bf16_schedule(schedule: int) -> int:
+    """Selects the schedule of the bf16 GEMM for this process (0 default = by size, 1 single-CTA
+    128 x 256 tiles, 2 CTA pairs with 256 x 256 tiles where K % 64 == 0) and returns the
+    previous setting."""
+    return int(_lib.load().rt_gemm_bf16_schedule(int(schedule)))
+
+
 def gemm_nvfp4_schedule(schedule: int) -> int:
     """Selects the schedule of the NVFP4 GEMM for this process (0 default = CTA pairs,
     1 single-CTA 128 x 128 tiles, 2 CTA pairs) and returns the previous setting."""

@@ -20,6 +20,16 @@ def _ref(x, w):
     return x.float() @ w.float().t()
 
 
+@pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
+def bf16_schedule(request, ops):
+    """Runs a test under both schedules of the bf16 GEMM (single-CTA 128 x 256 tiles, CTA pairs
+    with 256 x 256 tiles; a K that is not a multiple of 64 always takes the single-CTA path)
+    and restores the default."""
+    previous = ops.gemm_bf16_schedule(request.param)
+    yield request.param
+    ops.gemm_bf16_schedule(previous)
+
+
 @pytest.mark.parametrize("m,n,k", [
     (128, 128, 64),        # one tile, one K block
     (128, 256, 256),       # one wide tile
@@ -29,8 +39,10 @@ def _ref(x, w):
     (4096, 2112, 7168),    # qkv_a projection
     (2048, 24576, 1536),   # q_b projection, all 128 heads
     (1000, 7168, 2048),    # expert down projection
+    (300, 264, 192),       # pair: odd number of K blocks (the second half of a stage is empty)
+    (257, 520, 64),        # pair: one K block, tiles ragged in both directions
 ])
-def test_linear_bf16(ops, m, n, k):
+def test_linear_bf16(ops, bf16_schedule, m, n, k):
     x = I.randn((m, k), 100 + m).cuda()
     w = I.randn((n, k), 200 + n, std=0.05).cuda()
     out = ops.linear_bf16(x, w)
@@ -45,7 +57,7 @@ def test_linear_bf16(ops, m, n, k):
     assert bool((diff <= tol).all()), f"worst {float(diff.max())}"
 
 
-def test_linear_bf16_strided_inputs_and_linearity(ops):
+def test_linear_bf16_strided_inputs_and_linearity(ops, bf16_schedule):
     big = I.randn((300, 1024), 5).cuda()
     w = I.randn((512, 512), 6, std=0.05).cuda()
     x = big[:, 256:768]                      # column slice: row pitch 1024
@@ -61,7 +73,7 @@ def test_linear_bf16_strided_inputs_and_linearity(ops):
 
 
 @pytest.mark.parametrize("m", [4096, 1, 77])
-def test_router_logits_fp32_output(ops, m):
+def test_router_logits_fp32_output(ops, bf16_schedule, m):
     """fp32 logits of bf16 hidden states and gate weights ([256, 7168]): every product is exact
     in fp32; the tensor-core accumulator aligns addends with a few bits less than an IEEE fp32
     sum, which shows as ~1e-5 of the largest logit."""

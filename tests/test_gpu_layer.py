@@ -44,7 +44,7 @@ def _check(out, ref, tight):
     assert rel_err(out, ref) <= tight, f"relative error {rel_err(out, ref)}"
 
 
-@pytest.mark.parametrize("proj,tight", [("bf16", 2e-2), ("fp8", 1.5e-1)])
+@pytest.mark.parametrize("proj,tight", [("bf16", 2e-2), ("fp8", 1.5e-1), ("mixed", 2e-2)])
 @pytest.mark.parametrize("tokens,layers", [(96, 2), (1, 1), (130, 3)])
 def test_dense_layer_stack_matches_reference_layer(L, tokens, layers, proj, tight):
     """bf16 projections: a couple of bf16 ulps. FP8 projections (e4m3 activations per 1 x 128,
@@ -56,7 +56,8 @@ def test_dense_layer_stack_matches_reference_layer(L, tokens, layers, proj, tigh
     hidden, pos = _inputs(shape, tokens)
     ref = ref_layer.forward_stack(hidden, pos, [w], shape, layers, ffn="dense")
     model = layer.RealisticLayer(shape, _to_cuda(w), ffn="dense", proj=proj)
-    assert model.w_qkv_a.fp8 == (proj == "fp8") and not model.w_kv_b.fp8   # kv_lora 64: stays bf16
+    # kv_lora 64: stays bf16; "mixed" keeps FP8 for K >= 4096 only, i.e. nowhere at this width
+    assert model.w_qkv_a.fp8 == (proj == "fp8") and not model.w_kv_b.fp8
     out = model.forward_stack(hidden.cuda(), pos.cuda(), layers)
     ops.tc_error_state()
     assert out.shape == ref.shape and out.dtype == torch.bfloat16
@@ -141,3 +142,19 @@ def test_rank_partials_sum_to_the_unsharded_layer(L):
     got_parts = [m.ffn_forward(normed) for m in ranks]
     for g, r_ in zip(got_parts, ref_parts):
         assert rel_err(g, r_) <= 2e-2
+
+
+def test_mixed_projection_picks_fp8_for_long_reductions_only(L):
+    """proj="mixed": FP8 block-scaled weights where K >= 4096 (qkv_a, w_o at full width), bf16
+    for the short reductions (q_b: 1536, kv_b: 512); both agree with the fp32 product."""
+    layer, ops = L
+    g = torch.Generator().manual_seed(11)
+    x_long = (torch.randn(64, 4096, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    w_long = (torch.randn(256, 4096, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    x_short = (torch.randn(64, 1536, generator=g) * 0.5).to(torch.bfloat16).cuda()
+    w_short = (torch.randn(256, 1536, generator=g) * 0.05).to(torch.bfloat16).cuda()
+    p_long, p_short = layer.Projection(w_long, "mixed"), layer.Projection(w_short, "mixed")
+    assert p_long.fp8 and not p_short.fp8
+    assert rel_err(p_long(x_long), x_long.float() @ w_long.float().t()) <= 6e-2
+    assert rel_err(p_short(x_short), x_short.float() @ w_short.float().t()) <= 1e-2
+    ops.tc_error_state()
