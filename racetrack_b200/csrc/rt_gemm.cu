@@ -1155,6 +1155,9 @@ __global__ void __launch_bounds__(1024) moe_tile_map_kernel(const int32_t* __res
 // Tile 128 x 256, stage = one K block: 16 KB of A + 32 KB of B, 4 stages.
 // Warps: 0 TMA producer, 1 MMA issuer, 2-9 epilogue (warp w: lane quarter w % 4, column half
 // (w - 2) / 4).
+// What bounds it is the folding, not the operands: a CTA-pair variant (256 x 256 tiles, half the
+// operand bytes and TMA loads per K block, the schedule that speeds the bf16 and NVFP4 GEMMs up)
+// ran at the same 1.6-1.8 PFLOP/s and was dropped.
 constexpr int kQBN = 256;
 constexpr int kQBK = 128;
 constexpr int kQStages = 4;
@@ -1383,14 +1386,15 @@ int make_tmap_2d(CUtensorMap* map, CUtensorMapDataType dt, const void* ptr, uint
     return RT_OK;
 }
 
-// 3-D K-major tensor map over a [rows, pitch] byte matrix whose rows are cut into K blocks of
-// 128 bytes: dims {128, rows, pitch / 128}, box {128, box_rows, box_kblocks}. One load brings
-// box_kblocks swizzled K-major tiles, stored one after the other.
-int make_tmap_kblocks(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t pitch_bytes,
-                      uint32_t box_rows, uint32_t box_kblocks) {
+// 3-D K-major tensor map over a byte matrix [rows, k_bytes] (row pitch pitch_bytes) whose rows
+// are cut into K blocks of 128 bytes: dims {128, rows, k_bytes / 128}, box {128, box_rows,
+// box_kblocks}. One load brings box_kblocks swizzled K-major tiles, stored one after the
+// other; K blocks past the end of a row read as zeros.
+int make_tmap_kblocks(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t k_bytes,
+                      uint64_t pitch_bytes, uint32_t box_rows, uint32_t box_kblocks) {
     EncodeTiledFn fn = encode_fn();
     RT_REQUIRE(fn, RT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
-    const cuuint64_t dims[3] = {128, rows, pitch_bytes / 128};
+    const cuuint64_t dims[3] = {128, rows, k_bytes / 128};
     const cuuint64_t strides[2] = {pitch_bytes, 128};
     const cuuint32_t box[3] = {128, box_rows, box_kblocks};
     const cuuint32_t estr[3] = {1, 1, 1};
@@ -1548,9 +1552,9 @@ static int launch_nvfp4_pair(const void* a_codes, const void* a_sf, const float*
                              int64_t K, int64_t ldc, cudaStream_t st) {
     CUtensorMap tw;
     TokenMaps tx;
-    if (int rc = make_tmap_kblocks(&tw, b_codes, groups * N, K / 2, 128, 2)) return rc;
+    if (int rc = make_tmap_kblocks(&tw, b_codes, groups * N, K / 2, K / 2, 128, 2)) return rc;
     for (int b = 0; b < 5; ++b) {
-        if (int rc = make_tmap_kblocks(&tx.box[b], a_codes, total_rows, K / 2, 8u << b, 2)) return rc;
+        if (int rc = make_tmap_kblocks(&tx.box[b], a_codes, total_rows, K / 2, K / 2, 8u << b, 2)) return rc;
     }
     static bool attr_set = false;
     if (!attr_set) {

@@ -103,6 +103,7 @@ def test_router_logits_fp32_output(ops, bf16_schedule, m):
     (1, 7168, 2048),       # decode row
     (2048, 24576, 1536),   # q_b
     (1024, 7168, 16384),   # w_o: 128 K blocks
+    (300, 520, 384),       # three K blocks, tiles ragged in both directions
 ])
 def test_linear_fp8_block_scaled(ops, m, n, k):
     from oracle import ref_ops as R
