@@ -415,6 +415,9 @@ def run_ours(args) -> None:
     device = torch.device("cuda", local_rank)
     distributed = world > 1
     if distributed:
+        # NCCL writes its version banner to stdout when NCCL_DEBUG is set in the environment;
+        # stdout carries the one JSON line only
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         dist.init_process_group("nccl", device_id=device)
 
     def barrier():
