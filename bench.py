@@ -126,9 +126,12 @@ class PrefillStackWorkload:
         w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
         self.proj = args.proj
         self.schedule = args.nvfp4_schedule
-        ops.gemm_nvfp4_schedule(1 if self.schedule == "single" else 2)
-        self.dominant = ("gemm_nvfp4_kernel" if self.schedule == "single"
-                         else "gemm_nvfp4_pair_kernel") + "[experts w13]"
+        ops.gemm_nvfp4_schedule({"auto": 0, "single": 1, "pair": 2}[self.schedule])
+        pairs_local = args.tokens * self.shape.topk // world
+        uses_pairs = self.schedule == "pair" or (
+            self.schedule == "auto" and pairs_local >= 128 * (self.shape.n_experts // world))
+        self.dominant = ("gemm_nvfp4_pair_kernel" if uses_pairs else "gemm_nvfp4_kernel") + \
+            "[experts w13]"
         self.model = layer.RealisticLayer(self.shape, w, rank, world, proj=args.proj)
         gen = torch.Generator(device=device)
         gen.manual_seed(self.shape.seed)
@@ -550,8 +553,9 @@ def main() -> None:
     ap.add_argument("--proj", default="mixed", choices=("mixed", "fp8", "bf16"),
                     help="arithmetic of the dense projections: FP8 e4m3 block-scaled, bf16, or "
                          "mixed (FP8 where K >= 4096, bf16 elsewhere)")
-    ap.add_argument("--nvfp4-schedule", default="pair", choices=("pair", "single"),
-                    help="schedule of the expert GEMMs (CTA pairs or single-CTA 128 x 128 tiles)")
+    ap.add_argument("--nvfp4-schedule", default="auto", choices=("auto", "pair", "single"),
+                    help="schedule of the expert GEMMs: the library's choice by size, CTA pairs, "
+                         "or single-CTA 128 x 128 tiles")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graph", action="store_true",
                     help="capture the stack in a CUDA graph and replay it (decode sizes)")

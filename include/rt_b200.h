@@ -199,6 +199,18 @@ int rt_absmax_rows(const void* x, const void* up, float* amax_out,
                    int64_t rows, int64_t cols, int64_t x_stride, int64_t up_stride,
                    const int32_t* row_begin, const int32_t* row_end, int dtype, void* stream);
 
+/*
+ * rt_absmax_rows over h = bf16(silu(gate) * up) that also WRITES h (bf16 [rows, cols], row pitch
+ * h_stride; rows outside the window are left untouched): the expert MLP needs max |h| before it
+ * can quantise h to NVFP4, and this way SwiGLU (an expf and an IEEE division per element) is
+ * evaluated once instead of once per pass.
+ * ref: racetrack/models/deepseek.py:958-959 (F.silu(w1(x)) * w3(x)).
+ */
+int rt_swiglu_absmax_rows(const void* gate, const void* up, void* h, float* amax_out,
+                          int64_t rows, int64_t cols, int64_t gate_stride, int64_t up_stride,
+                          int64_t h_stride, const int32_t* row_begin, const int32_t* row_end,
+                          int dtype, void* stream);
+
 /* Block-scale layouts for NVFP4 */
 typedef enum rt_sf_layout {
     RT_SF_ROWMAJOR = 0,   /* [rows, cols/16] bytes */
@@ -427,7 +439,8 @@ int rt_gemm_bf16_schedule(int schedule);
 
 /*
  * Schedule of rt_gemm_nvfp4_grouped for this process: 0 = default (CTA pairs, unless
- * max_m_tiles * ceil(n/256) is below the SM count: then single-CTA tiles), 1 = single-CTA
+ * max_m_tiles * ceil(n/256) is below the SM count or total_rows < 128 * groups: then
+ * single-CTA tiles), 1 = single-CTA
  * 128 x 128 tiles, 2 = CTA pairs. Returns the previous value; any other argument only queries.
  * For A/B measurements and tests. No counterpart in racetrack.
  */

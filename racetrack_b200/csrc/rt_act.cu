@@ -138,11 +138,14 @@ __global__ void __launch_bounds__(kActThreads) quant_fp8_kernel(
 // ---------------------------------------------------------------------------
 __global__ void absmax_clear_kernel(float* out) { *out = 0.f; }
 
-template <bool UP>
+// STORE: also writes the values it took the maximum of (bf16(silu(x) * up) when UP) to
+// h[row, col], so that a later pass can quantise them without evaluating SwiGLU again.
+template <bool UP, bool STORE>
 __global__ void __launch_bounds__(kActThreads) absmax_kernel(
     const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ up,
     float* __restrict__ out, uint32_t items, uint32_t items_per_row, int64_t xstride,
-    int64_t ustride, const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end) {
+    int64_t ustride, const int32_t* __restrict__ row_begin, const int32_t* __restrict__ row_end,
+    __nv_bfloat16* __restrict__ h, int64_t hstride) {
     __shared__ float scratch[32];
     float m = 0.f;
     // optional row window read from device memory (the rows an expert-parallel rank owns)
@@ -156,6 +159,17 @@ __global__ void __launch_bounds__(kActThreads) absmax_kernel(
         float v[16];
         load_item<UP>(x, up, row, col, xstride, ustride, v);
         m = fmaxf(m, absmax16(v));
+        if constexpr (STORE) {
+            float lo[8], hi[8];
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                lo[k] = v[k];
+                hi[k] = v[8 + k];
+            }
+            uint4* ph = reinterpret_cast<uint4*>(h + static_cast<int64_t>(row) * hstride + col);
+            st_stream16(ph, pack_bf16x8(lo));
+            st_stream16(ph + 1, pack_bf16x8(hi));
+        }
     }
     m = warp_max(m);
     if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
@@ -374,7 +388,7 @@ extern "C" int rt_swiglu_quant_fp8(const void* gate, const void* up, void* codes
 static int absmax_common(const void* x, const void* up, float* amax_out, int64_t rows,
                          int64_t cols, int64_t x_stride, int64_t up_stride,
                          const int32_t* row_begin, const int32_t* row_end, int dtype,
-                         void* stream) {
+                         void* stream, void* h = nullptr, int64_t h_stride = 0) {
     uint32_t items, per_row;
     if (int rc = check_stream_args("rt_absmax", x, rows, cols, x_stride, 16, dtype, items, per_row,
                                    kItem))
@@ -389,15 +403,18 @@ static int absmax_common(const void* x, const void* up, float* amax_out, int64_t
     // persistent grid: 148 SMs x 8 resident CTAs, each thread loops over items
     unsigned grid = (items + kActThreads - 1) / kActThreads;
     if (grid > 148u * 8u) grid = 148u * 8u;
-    if (up)
-        absmax_kernel<true><<<grid, kActThreads, 0, st>>>((const __nv_bfloat16*)x,
-                                                          (const __nv_bfloat16*)up, amax_out, items,
-                                                          per_row, x_stride, up_stride, row_begin,
-                                                          row_end);
+    const __nv_bfloat16* xb = static_cast<const __nv_bfloat16*>(x);
+    const __nv_bfloat16* ub = static_cast<const __nv_bfloat16*>(up);
+    __nv_bfloat16* hb = static_cast<__nv_bfloat16*>(h);
+    if (up && h)
+        absmax_kernel<true, true><<<grid, kActThreads, 0, st>>>(
+            xb, ub, amax_out, items, per_row, x_stride, up_stride, row_begin, row_end, hb, h_stride);
+    else if (up)
+        absmax_kernel<true, false><<<grid, kActThreads, 0, st>>>(
+            xb, ub, amax_out, items, per_row, x_stride, up_stride, row_begin, row_end, nullptr, 0);
     else
-        absmax_kernel<false><<<grid, kActThreads, 0, st>>>((const __nv_bfloat16*)x, nullptr,
-                                                           amax_out, items, per_row, x_stride, 0,
-                                                           row_begin, row_end);
+        absmax_kernel<false, false><<<grid, kActThreads, 0, st>>>(
+            xb, nullptr, amax_out, items, per_row, x_stride, 0, row_begin, row_end, nullptr, 0);
     count_launch();
     return check_launch("absmax_kernel");
 }
@@ -415,6 +432,18 @@ extern "C" int rt_absmax_rows(const void* x, const void* up, float* amax_out, in
                               void* stream) {
     return absmax_common(x, up, amax_out, rows, cols, x_stride, up_stride, row_begin, row_end,
                          dtype, stream);
+}
+
+extern "C" int rt_swiglu_absmax_rows(const void* gate, const void* up, void* h, float* amax_out,
+                                     int64_t rows, int64_t cols, int64_t gate_stride,
+                                     int64_t up_stride, int64_t h_stride,
+                                     const int32_t* row_begin, const int32_t* row_end, int dtype,
+                                     void* stream) {
+    RT_REQUIRE(up && h, RT_ERR_BAD_ARG, "rt_swiglu_absmax_rows: null pointer");
+    RT_REQUIRE(h_stride % 8 == 0 && aligned16(h), RT_ERR_UNSUPPORTED,
+               "rt_swiglu_absmax_rows: h must be 16-byte aligned with stride %% 8 == 0");
+    return absmax_common(gate, up, amax_out, rows, cols, gate_stride, up_stride, row_begin, row_end,
+                         dtype, stream, h, h_stride);
 }
 
 extern "C" int rt_moe_quant_nvfp4(const void* x, const void* up, const int32_t* sorted_pairs,

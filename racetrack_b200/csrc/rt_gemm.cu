@@ -1511,7 +1511,8 @@ static int launch_fp8(const void* a, const float* a_s, const void* b, const floa
 }
 
 // Schedule of the NVFP4 GEMM: 0 = by size (CTA pairs unless the work list is too short to
-// occupy them), 1 = single-CTA 128 x 128 tiles, 2 = CTA pairs. Process-wide; meant for A/B
+// occupy them or the groups average fewer than 128 rows), 1 = single-CTA 128 x 128 tiles,
+// 2 = CTA pairs. Process-wide; meant for A/B
 // measurements and tests.
 static int g_nvfp4_schedule = 0;
 
@@ -1634,10 +1635,13 @@ extern "C" int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, cons
                RT_ERR_UNSUPPORTED, "rt_gemm_nvfp4_grouped: pointers must be 16-byte aligned");
     RT_REQUIRE(total_rows < (1LL << 31) && groups * n < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_nvfp4_grouped: dimension too large");
-    // Pairs need 2 x 74 CTAs' worth of 256-row weight tiles to pay off; below that the 128 x 128
-    // tiles spread the same work over more SMs.
+    // Pairs pay off when the tensor cores are the bottleneck: at least 128 rows per group on
+    // average and 2 x 74 CTAs' worth of 256-row weight tiles. With fewer rows the launch streams
+    // the weights once from HBM and the single-CTA tiles, which keep more loads in flight, were
+    // 4-7 % faster from 8 to 1024 tokens of a 256-expert layer.
     const bool few_tiles = max_m_tiles * ((n + 255) / 256) < tc::sm_count();
-    if (tc::g_nvfp4_schedule == 1 || (tc::g_nvfp4_schedule == 0 && few_tiles))
+    const bool few_rows = total_rows < 128 * groups;
+    if (tc::g_nvfp4_schedule == 1 || (tc::g_nvfp4_schedule == 0 && (few_tiles || few_rows)))
         return tc::launch_nvfp4_single(a_codes, a_sf, a_gs, b_codes, b_sf, b_gs, c, tile_map,
                                        tile_count, max_m_tiles, total_rows, groups, n, k, ldc,
                                        as_stream(stream));

@@ -77,6 +77,22 @@ def _absmax_rows(x: torch.Tensor, up: Optional[torch.Tensor], window) -> torch.T
     return out
 
 
+def swiglu_absmax_rows(gate: torch.Tensor, up: torch.Tensor, window):
+    """(h, amax): h = bf16(silu(gate) * up) and max |h| over the rows of `window` (a pair of
+    one-element device tensors [begin], [end], or None for all rows); rows outside the window
+    are not written (rt_swiglu_absmax_rows)."""
+    h = torch.empty(gate.shape, dtype=torch.bfloat16, device=gate.device)
+    out = torch.empty(1, dtype=torch.float32, device=gate.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_swiglu_absmax_rows(
+        gate.data_ptr(), up.data_ptr(), h.data_ptr(), out.data_ptr(), gate.shape[0], gate.shape[1],
+        gate.stride(0), up.stride(0), h.stride(0),
+        window[0].data_ptr() if window is not None else None,
+        window[1].data_ptr() if window is not None else None, _lib.RT_BF16, ops._stream()),
+        "rt_swiglu_absmax_rows")
+    return h, out
+
+
 def moe_quant_nvfp4(x: torch.Tensor, tile_map: torch.Tensor, tile_count: torch.Tensor,
                     total_rows: int, *, amax: torch.Tensor, sorted_pairs=None, topk: int = 1,
                     up: Optional[torch.Tensor] = None):
@@ -127,8 +143,9 @@ def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
                                      experts.w13_gs, tile_map, tile_count, n=2 * experts.inter,
                                      groups=count)
     gate, up = gate_up[:, :experts.inter], gate_up[:, experts.inter:]
-    h_amax = _absmax_rows(gate, up, window)
-    h_codes, h_sf, h_gs = moe_quant_nvfp4(gate, tile_map, tile_count, pairs, amax=h_amax, up=up)
+    # SwiGLU once: this pass writes h and finds the tensor-wide amax its quantisation needs
+    h, h_amax = swiglu_absmax_rows(gate, up, window)
+    h_codes, h_sf, h_gs = moe_quant_nvfp4(h, tile_map, tile_count, pairs, amax=h_amax)
     expert_out = ops.gemm_nvfp4_grouped(h_codes, h_sf, h_gs, experts.w2_codes, experts.w2_sf,
                                         experts.w2_gs, tile_map, tile_count, n=hidden, groups=count)
     return ops.fused_moe_combine(expert_out, pair_pos, weights, shared, pos_window=window)

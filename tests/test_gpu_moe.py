@@ -116,3 +116,23 @@ def test_fused_moe_forward_routes_and_combines(mods):
     w, idx = ops.fused_moe_route(logits, d["bias"].cuda(), **kw)
     ref = R.moe_experts_nvfp4(d["hidden"], w.cpu(), idx.cpu(), w13, w2)
     assert rel_err(y, ref) <= 1e-2
+
+
+@pytest.mark.parametrize("window", [None, (37, 211)])
+def test_swiglu_absmax_rows_writes_h_and_its_amax(mods, window):
+    """One pass: h = bf16(silu(gate) * up) for the rows of the window and max |h| over them,
+    bit for bit what the SwiGLU kernel and the windowed amax kernel give separately."""
+    ops, moe = mods
+    rows, inter = 300, 512
+    gate_up = I.randn((rows, 2 * inter), 31, std=2.0).cuda()
+    gate, up = gate_up[:, :inter], gate_up[:, inter:]
+    win = None
+    if window is not None:
+        win = (torch.tensor([window[0]], dtype=torch.int32).cuda(),
+               torch.tensor([window[1]], dtype=torch.int32).cuda())
+    h, amax = moe.swiglu_absmax_rows(gate, up, win)
+    lo, hi = window if window is not None else (0, rows)
+    ref = ops.fused_swiglu(gate, up)
+    assert_bit_exact(h[lo:hi], ref[lo:hi], "h")
+    assert_bit_exact(amax, moe._absmax_rows(gate, up, win), "amax")
+    assert_bit_exact(amax, ref[lo:hi].float().abs().max().reshape(1), "amax of h")
