@@ -373,6 +373,11 @@ DEFAULT_WORKLOAD = PrefillStackWorkload.name
 
 
 def cpu_line(wl_cls, steps: int, warmup: int) -> dict:
+    # all host threads, also under torchrun (which exports OMP_NUM_THREADS=1 to every rank)
+    try:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
+    except (AttributeError, RuntimeError):
+        torch.set_num_threads(os.cpu_count() or 1)
     run, units = wl_cls.cpu_runner(CPU_SAMPLE_TOKENS)
     for _ in range(max(warmup, 1)):
         run()
@@ -419,9 +424,19 @@ def run_ours(args) -> None:
     distributed = world > 1
     if distributed:
         # NCCL writes its version banner to stdout when NCCL_DEBUG is set in the environment;
-        # stdout carries the one JSON line only
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
-        dist.init_process_group("nccl", device_id=device)
+        # stdout carries the one JSON line only, so file descriptor 1 points at stderr while
+        # the communicator comes up
+        sys.stdout.flush()
+        saved = os.dup(1)
+        os.dup2(2, 1)
+        try:
+            dist.init_process_group("nccl", device_id=device)
+            dist.barrier(device_ids=[local_rank])
+            torch.cuda.synchronize(device)
+        finally:
+            sys.stdout.flush()
+            os.dup2(saved, 1)
+            os.close(saved)
 
     def barrier():
         if distributed:
