@@ -59,7 +59,7 @@ int64_t rt_launch_count(void);
  * hidden = update + residual (fp32); normed = weight * (hidden * rsqrt(mean(hidden^2) + eps)),
  * computed from the un-rounded fp32 sum; both outputs rounded to `dtype`.
  * One pass: each input element is read once, each output written once.
- * `normed` and `hidden` are contiguous [rows, cols]. cols % 8 == 0, cols <= 65536.
+ * `normed` and `hidden` are contiguous [rows, cols]. cols % 8 == 0, cols <= 32768.
  * ref: racetrack/models/deepseek.py:485-495 (RMSNorm.forward fallback),
  *      partitions/dsv3_2/a1f6d7e2/kernels/cutedsl/residual_norm.py:47-147 (the op it replaces).
  */
@@ -72,7 +72,7 @@ int rt_residual_norm(const void* update, const void* residual,
 
 /*
  * out = (x * rsqrt(mean(x^2) + eps)) * weight, fp32 math, rounded to `dtype`.
- * `out` has row stride `out_stride`. cols % 8 == 0, cols <= 65536.
+ * `out` has row stride `out_stride`. cols % 8 == 0, cols <= 32768.
  * ref: partitions/_base.py:24-28 (rms_norm), racetrack/models/deepseek.py:478-483.
  */
 int rt_rms_norm(const void* x, const void* weight, int weight_dtype, void* out,
