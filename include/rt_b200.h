@@ -256,6 +256,21 @@ int rt_moe_quant_nvfp4(const void* x, const void* up, const int32_t* sorted_pair
                        const int32_t* tile_count, int64_t max_tiles, int64_t cols,
                        int64_t x_stride, int64_t up_stride, int dtype, void* stream);
 
+/*
+ * MoE dispatch of token rows that are already NVFP4 (quantised ONCE per token with
+ * rt_nvfp4_quant, RT_SF_ROWMAJOR scales): for every 128-row tile of the tile map, copies the
+ * rows its sorted (token, slot) pairs name (source row = sorted_pairs[r] / topk) -- codes
+ * [tokens, cols/2] -> codes_out at the tiles' compact rows, scales [tokens, cols/16] -> sf_out
+ * in the RT_SF_TILED128x4 layout with row tile = the tile map's scale row-tile index, zeros for
+ * rows past a tile's valid rows. Same result as rt_moe_quant_nvfp4 with sorted_pairs (the
+ * quantisation is per row), without reading the bf16 rows topk times. cols % 64 == 0;
+ * sf_out must hold max_tiles * (cols/64) * 512 bytes.
+ * ref: racetrack/models/deepseek.py:1017 (x[idx] gather); NVFP4 has no counterpart in racetrack.
+ */
+int rt_moe_gather_nvfp4(const void* codes_in, const void* sf_in, const int32_t* sorted_pairs,
+                        int64_t topk, void* codes_out, void* sf_out, const int32_t* tile_map,
+                        const int32_t* tile_count, int64_t max_tiles, int64_t cols, void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* MoE routing and token permutation                                          */
 /* ------------------------------------------------------------------------ */

@@ -44,6 +44,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_absmax_rows": (_I, [_P, _P, _P, _L, _L, _L, _L, _P, _P, _I, _P]),
     "rt_swiglu_absmax_rows": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _P, _P, _I, _P]),
     "rt_moe_quant_nvfp4": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),
+    "rt_moe_gather_nvfp4": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _L, _L, _P]),
     "rt_gemm_bf16": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P]),
     "rt_gemm_fp8": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
     "rt_tc_error_state": (_I, []),

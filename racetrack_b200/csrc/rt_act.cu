@@ -292,6 +292,55 @@ __global__ void __launch_bounds__(kActThreads) quant_nvfp4_tiles_kernel(
     }
 }
 
+// MoE dispatch of activations that are ALREADY NVFP4: the token rows were quantised once
+// (codes [tokens, cols/2], row-major scales [tokens, cols/16]); this kernel copies, for every
+// 128-row tile of the tile map, the rows its sorted (token, slot) pairs name: codes to the
+// compact destination rows, scales into the 128 x 4 tiled layout of the tile (zeros for the rows
+// past the tile's valid rows). One CTA per tile: each warp copies 16 rows (a row's codes in 7
+// coalesced 16-byte sweeps for 7168 columns) and parks their scales in shared memory (row pitch
+// padded to an odd number of words so the column reads below spread over all banks); then every
+// warp assembles 512-byte scale tiles: lane l packs the 4 scale bytes of rows l, l + 32, l + 64,
+// l + 96 and stores 16 bytes.
+constexpr int kGatherThreads = 256;
+
+__global__ void __launch_bounds__(kGatherThreads) moe_gather_nvfp4_kernel(
+    const uint8_t* __restrict__ codes_in, const uint8_t* __restrict__ sf_in,
+    const int32_t* __restrict__ sorted_pairs, int topk, uint8_t* __restrict__ codes_out,
+    uint8_t* __restrict__ sf_out, const int4* __restrict__ tile_map,
+    const int32_t* __restrict__ tile_count, int64_t cols) {
+    extern __shared__ uint32_t sf_smem[];
+    const int tile = blockIdx.x;
+    if (tile >= __ldg(tile_count)) return;
+    const int4 tm = __ldg(tile_map + tile);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t code_bytes = cols >> 1;            // per row, a multiple of 32
+    const int sf_words = static_cast<int>(cols >> 6);   // 4-byte scale groups per row (k-tiles)
+    const int pitch = sf_words | 1;                  // odd word pitch
+    for (int r = warp; r < 128; r += kGatherThreads / 32) {
+        if (r >= tm.z) {
+            for (int w = lane; w < sf_words; w += 32) sf_smem[r * pitch + w] = 0u;
+            continue;
+        }
+        const int64_t dst_row = tm.y + r;
+        const int64_t src_row = __ldg(sorted_pairs + dst_row) / topk;
+        const uint4* src = reinterpret_cast<const uint4*>(codes_in + src_row * code_bytes);
+        uint4* dst = reinterpret_cast<uint4*>(codes_out + dst_row * code_bytes);
+        for (int64_t i = lane; i < (code_bytes >> 4); i += 32) st_stream16(dst + i, ld_cached16(src + i));
+        const uint32_t* ssf = reinterpret_cast<const uint32_t*>(sf_in + src_row * (cols >> 4));
+        for (int w = lane; w < sf_words; w += 32) sf_smem[r * pitch + w] = __ldg(ssf + w);
+    }
+    __syncthreads();
+    uint8_t* sf_tile = sf_out + static_cast<int64_t>(tm.w) * sf_words * 512;
+    for (int kt = warp; kt < sf_words; kt += kGatherThreads / 32) {
+        uint4 v;
+        v.x = sf_smem[lane * pitch + kt];
+        v.y = sf_smem[(lane + 32) * pitch + kt];
+        v.z = sf_smem[(lane + 64) * pitch + kt];
+        v.w = sf_smem[(lane + 96) * pitch + kt];
+        st_stream16(sf_tile + static_cast<int64_t>(kt) * 512 + lane * 16, v);
+    }
+}
+
 // Zero-fills the padding entries of a 128x4-tiled scale buffer (rows beyond
 // `rows` inside the last 128-row tile, blocks beyond nblk inside the last 4-block tile).
 __global__ void sf_pad_kernel(uint8_t* __restrict__ sf, int64_t rows, int64_t nblk,
@@ -479,6 +528,40 @@ extern "C" int rt_moe_quant_nvfp4(const void* x, const void* up, const int32_t* 
             x_stride, 0, cols);
     count_launch();
     return check_launch("quant_nvfp4_tiles_kernel");
+}
+
+extern "C" int rt_moe_gather_nvfp4(const void* codes_in, const void* sf_in,
+                                   const int32_t* sorted_pairs, int64_t topk, void* codes_out,
+                                   void* sf_out, const int32_t* tile_map,
+                                   const int32_t* tile_count, int64_t max_tiles, int64_t cols,
+                                   void* stream) {
+    RT_REQUIRE(max_tiles >= 0 && cols > 0 && topk > 0, RT_ERR_BAD_ARG,
+               "rt_moe_gather_nvfp4: bad shape");
+    if (max_tiles == 0) return RT_OK;
+    RT_REQUIRE(codes_in && sf_in && sorted_pairs && codes_out && sf_out && tile_map && tile_count,
+               RT_ERR_BAD_ARG, "rt_moe_gather_nvfp4: null pointer");
+    RT_REQUIRE(cols % 64 == 0, RT_ERR_UNSUPPORTED,
+               "rt_moe_gather_nvfp4: cols must be a multiple of 64 (whole scale tiles)");
+    RT_REQUIRE(aligned16(codes_in) && aligned16(codes_out) && aligned16(sf_out) &&
+                   aligned16(tile_map) && (reinterpret_cast<uintptr_t>(sf_in) & 3u) == 0,
+               RT_ERR_UNSUPPORTED, "rt_moe_gather_nvfp4: alignment (16-byte codes and tiles, 4-byte scales)");
+    const int64_t smem = 128 * ((cols >> 6) | 1) * 4;
+    RT_REQUIRE(smem <= 200 * 1024, RT_ERR_UNSUPPORTED, "rt_moe_gather_nvfp4: cols too large");
+    RT_REQUIRE(max_tiles < (1LL << 31), RT_ERR_UNSUPPORTED, "rt_moe_gather_nvfp4: too many tiles");
+    static int64_t attr_smem = 0;
+    if (smem > attr_smem) {
+        cudaError_t e = cudaFuncSetAttribute(moe_gather_nvfp4_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(smem));
+        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_moe_gather_nvfp4: %s", cudaGetErrorString(e));
+        attr_smem = smem;
+    }
+    moe_gather_nvfp4_kernel<<<static_cast<unsigned>(max_tiles), kGatherThreads, smem,
+                              as_stream(stream)>>>(
+        (const uint8_t*)codes_in, (const uint8_t*)sf_in, sorted_pairs, (int)topk,
+        (uint8_t*)codes_out, (uint8_t*)sf_out, (const int4*)tile_map, tile_count, cols);
+    count_launch();
+    return check_launch("moe_gather_nvfp4_kernel");
 }
 
 extern "C" int rt_nvfp4_quant(const void* x, const void* up, const float* amax_in, void* codes,

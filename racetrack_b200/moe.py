@@ -77,6 +77,24 @@ def _absmax_rows(x: torch.Tensor, up: Optional[torch.Tensor], window) -> torch.T
     return out
 
 
+def moe_gather_nvfp4(codes: torch.Tensor, sf: torch.Tensor, sorted_pairs: torch.Tensor, topk: int,
+                     tile_map: torch.Tensor, tile_count: torch.Tensor, total_rows: int):
+    """MoE dispatch of token rows quantised once (codes [T, cols/2], row-major scales
+    [T, cols/16] from ops.fused_nvfp4_quant): (codes [total_rows, cols/2] in expert order,
+    tile-aligned scales) for the rows of a tile map (rt_moe_gather_nvfp4)."""
+    cols = codes.shape[1] * 2
+    max_tiles = tile_map.shape[0] // 2
+    dev = codes.device
+    out = torch.empty(total_rows, cols // 2, dtype=torch.uint8, device=dev)
+    sf_out = torch.empty(max_tiles * (cols // 64) * 512, dtype=torch.uint8, device=dev)
+    lib = _lib.load()
+    _lib.check(lib.rt_moe_gather_nvfp4(
+        codes.data_ptr(), sf.data_ptr(), sorted_pairs.data_ptr(), topk, out.data_ptr(),
+        sf_out.data_ptr(), tile_map.data_ptr(), tile_count.data_ptr(), max_tiles, cols,
+        ops._stream()), "rt_moe_gather_nvfp4")
+    return out, sf_out
+
+
 def swiglu_absmax_rows(gate: torch.Tensor, up: torch.Tensor, window):
     """(h, amax): h = bf16(silu(gate) * up) and max |h| over the rows of `window` (a pair of
     one-element device tensors [begin], [end], or None for all rows); rows outside the window
@@ -136,9 +154,11 @@ def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     local = count != n_experts
     window = (offsets[expert_begin:expert_begin + 1], offsets[expert_begin + count:expert_begin + count + 1]) \
         if local else None
-    # dispatch: gather token rows into expert order while quantising them
-    a_codes, a_sf, a_gs = moe_quant_nvfp4(x, tile_map, tile_count, pairs, amax=ops.tensor_absmax(x),
-                                          sorted_pairs=sorted_pairs, topk=topk)
+    # dispatch: every token row is quantised once, then its codes and scales are copied into
+    # expert order (the bf16 rows are not read topk times)
+    x_codes, x_sf, a_gs = ops.fused_nvfp4_quant(x, amax=ops.tensor_absmax(x))
+    a_codes, a_sf = moe_gather_nvfp4(x_codes, x_sf.view(torch.uint8), sorted_pairs, topk, tile_map,
+                                     tile_count, pairs)
     gate_up = ops.gemm_nvfp4_grouped(a_codes, a_sf, a_gs, experts.w13_codes, experts.w13_sf,
                                      experts.w13_gs, tile_map, tile_count, n=2 * experts.inter,
                                      groups=count)

@@ -136,3 +136,26 @@ def test_swiglu_absmax_rows_writes_h_and_its_amax(mods, window):
     assert_bit_exact(h[lo:hi], ref[lo:hi], "h")
     assert_bit_exact(amax, moe._absmax_rows(gate, up, win), "amax")
     assert_bit_exact(amax, ref[lo:hi].float().abs().max().reshape(1), "amax of h")
+
+
+@pytest.mark.parametrize("tokens,hidden,n_experts,topk", [(300, 512, 8, 2), (5, 7168, 16, 4),
+                                                           (1000, 1024, 4, 1)])
+def test_moe_gather_nvfp4_equals_gather_fused_quantiser(mods, tokens, hidden, n_experts, topk):
+    """Quantising every token once and copying codes and scales into expert order gives the
+    bytes the gather-fused quantiser writes (quantisation is per row), padding rows included."""
+    ops, moe = mods
+    x, _, _, _, indices = _setup(tokens, hidden, 256, n_experts, topk, seed=tokens)
+    xc = x.cuda()
+    offsets, sorted_pairs, _ = ops.fused_moe_permute(indices.cuda(), n_experts)
+    pairs = tokens * topk
+    tile_map, _, tile_count = ops.moe_tile_map(offsets, 0, n_experts, pairs // 128 + n_experts + 1)
+    amax = ops.tensor_absmax(xc)
+    ref_codes, ref_sf, ref_gs = moe.moe_quant_nvfp4(xc, tile_map, tile_count, pairs, amax=amax,
+                                                   sorted_pairs=sorted_pairs, topk=topk)
+    q_codes, q_sf, q_gs = ops.fused_nvfp4_quant(xc, amax=amax)
+    codes, sf = moe.moe_gather_nvfp4(q_codes, q_sf.view(torch.uint8), sorted_pairs, topk, tile_map,
+                                     tile_count, pairs)
+    assert_bit_exact(q_gs, ref_gs, "global scale")
+    assert_bit_exact(codes, ref_codes, "codes")
+    used = int(tile_count[0]) * (hidden // 64) * 512
+    assert_bit_exact(sf[:used], ref_sf[:used], "tiled scales")
