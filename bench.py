@@ -454,6 +454,11 @@ def run_ours(args) -> None:
     wl = WORKLOADS[args.workload](device, rank, world, args)
 
     use_graph = args.graph and hasattr(wl, "capture_graph")
+    if use_graph and distributed:
+        # a captured graph that holds NCCL kernels kept the process from exiting here
+        # (torch 2.11, NCCL 2.28): multi-GPU runs stay eager
+        print("bench.py: --graph is single-GPU only, running eagerly", file=sys.stderr)
+        use_graph = False
     if use_graph:
         wl.step()
         barrier()
