@@ -1296,27 +1296,28 @@ __global__ void __launch_bounds__(kQThreads, 1) gemm_fp8_kernel(
                 const float scale = __ldg(as_row + kb) * __ldg(bs_row + kb);
                 if (!(ok = mbar_wait(pfull_bar(buf), buf_phase, abort_flag, 24))) break;
                 tc_fence_after();
-                // two register buffers: the load of chunk c+1 is in flight while chunk c is folded in
+                // 64 columns per wait: the latency of a tensor-memory load (a few hundred cycles)
+                // is paid twice per K block, not four times
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                        static_cast<uint32_t>(buf * kQBN + half * 128);
                 uint32_t r0[32], r1[32];
                 tmem_ld_32x32(taddr, r0);
-                tmem_ld_wait(r0);
                 tmem_ld_32x32(taddr + 32, r1);
+                tmem_ld_wait(r0);
+                tmem_ld_wait(r1);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), scale, acc[i]);
-                tmem_ld_wait(r1);
-                tmem_ld_32x32(taddr + 64, r0);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[32 + i]);
-                tmem_ld_wait(r0);
+                tmem_ld_32x32(taddr + 64, r0);
                 tmem_ld_32x32(taddr + 96, r1);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), scale, acc[64 + i]);
+                tmem_ld_wait(r0);
                 tmem_ld_wait(r1);
                 // every column of the buffer has been read: hand it back before the last fold
                 tc_fence_before();
                 mbar_arrive(pempty_bar(buf));
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), scale, acc[64 + i]);
 #pragma unroll
                 for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[96 + i]);
                 if (++buf == 2) {
@@ -1344,6 +1345,234 @@ __global__ void __launch_bounds__(kQThreads, 1) gemm_fp8_kernel(
     if (warp == 1) {
         tc_fence_after();
         tmem_dealloc(tmem_base, kQTmemCols);
+    }
+}
+
+// ---------------------------------------------------------------------------
+// FP8 e4m3 GEMM with DeepSeek block scales on CTA pairs (tcgen05 cta_group::2)
+// ---------------------------------------------------------------------------
+// Same arithmetic as gemm_fp8_kernel (every 128-wide K block multiplied on its own into one
+// of two 256-column tensor-memory buffers and folded, scaled, into fp32 registers by eight
+// epilogue warps), on 256 x 256 tiles over a pair of CTAs: each CTA supplies 128 rows of A and
+// 128 rows of B per K block (32 KB instead of 48 KB), and every TMA load covers two K blocks
+// (an SM retires about one tiled load per 500 cycles; the single-CTA kernel needs two per K
+// block, which alone costs as much as twice the MMA time of the block). 3 stages of 64 KB.
+// Warps (both CTAs): 0 producer, 1 tensor-memory owner and MMA issuer (leader) or relay
+// (peer), 2-9 epilogue (lane quarter w % 4, column half (w - 2) / 4).
+constexpr int kQPStages = 3;
+constexpr int kQPThreads = 320;
+constexpr uint32_t kQPABytes = 2 * 128 * 128;
+constexpr uint32_t kQPBBytes = 2 * 128 * 128;
+constexpr uint32_t kQPStageBytes = kQPABytes + kQPBBytes;
+constexpr uint32_t kQPBarOffset = kQPStages * kQPStageBytes;
+constexpr uint32_t kQPSmemBytes = kQPBarOffset + (2 * kQPStages + 4) * 8 + 16 + 1024;
+// fp32 accumulate, e4m3 x e4m3 (format code 0), K-major, N = 256, M = 256 over the pair
+constexpr uint32_t kQPIdesc = (1u << 4) | (32u << 17) | (16u << 24);
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kQPThreads, 1) gemm_fp8_pair_kernel(
+    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+    const float* __restrict__ a_s, const float* __restrict__ b_s, __nv_bfloat16* __restrict__ c,
+    int M, int N, int K, int64_t ldc) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + kQPBarOffset;
+    auto cfull_bar = [&](int d) { return bars + 8u * d; };
+    auto cempty_bar = [&](int d) { return bars + 8u * (kQPStages + d); };
+    auto pfull_bar = [&](int a) { return bars + 8u * (2 * kQPStages + a); };
+    auto pempty_bar = [&](int a) { return bars + 8u * (2 * kQPStages + 2 + a); };
+    const uint32_t slot = bars + 8u * (2 * kQPStages + 4);
+    volatile uint32_t* slot_ptr =
+        reinterpret_cast<volatile uint32_t*>(base_ptr + kQPBarOffset + 8 * (2 * kQPStages + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();
+    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+    const int num_m = (M + 255) / 256, num_n = (N + 255) / 256;
+    const int num_tiles = num_m * num_n;
+    const int num_kb = K / 128;
+    const int num_ds = (num_kb + 1) / 2;
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int d = 0; d < kQPStages; ++d) {
+            mbar_init(cfull_bar(d), rank == 0 ? 2 : 1);   // own producer (+ the peer's relay)
+            mbar_init(cempty_bar(d), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            mbar_init(pfull_bar(a), 1);
+            mbar_init(pempty_bar(a), 16);    // 8 epilogue warps in each CTA of the pair
+        }
+        fence_mbar_init();
+        tma_prefetch_desc(&tmap_a);
+        tma_prefetch_desc(&tmap_b);
+    }
+    if (warp == 1) {
+        tmem_alloc_pair(slot, 512);
+        tmem_relinquish_pair();
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();                          // the peer's barriers exist before anyone signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                int tm, tn;
+                tile_coords(tile, num_m, num_n, tm, tn);
+                const int a_row = tm * 256 + static_cast<int>(rank) * 128;
+                const int b_row = tn * 256 + static_cast<int>(rank) * 128;
+                for (int ds = 0; ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cempty_bar(stage), phase ^ 1u, abort_flag, 41))) break;
+                    const uint32_t sa = base + stage * kQPStageBytes;
+                    mbar_arrive_expect_tx(cfull_bar(stage), kQPStageBytes);
+                    tma_load_3d(sa, &tmap_a, 0, a_row, 2 * ds, cfull_bar(stage));
+                    tma_load_3d(sa + kQPABytes, &tmap_b, 0, b_row, 2 * ds, cfull_bar(stage));
+                    if (++stage == kQPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (rank == 0 && lane == 0) {
+            const uint32_t peer_cempty0 = map_to_cta(cempty_bar(0), 1);
+            const uint32_t peer_pfull0 = map_to_cta(pfull_bar(0), 1);
+            int stage = 0, buf = 0;
+            uint32_t phase = 0, buf_phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                for (int ds = 0; ok && ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 43))) break;
+                    const uint32_t sa = base + stage * kQPStageBytes;
+                    const int halves = min(2, num_kb - 2 * ds);
+                    for (int h = 0; h < halves; ++h) {
+                        if (!(ok = mbar_wait(pempty_bar(buf), buf_phase ^ 1u, abort_flag, 42))) break;
+                        tc_fence_after();
+                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * 256);
+                        const uint64_t adesc = smem_desc_sw128(sa + h * (kQPABytes / 2));
+                        const uint64_t bdesc =
+                            smem_desc_sw128(sa + kQPABytes + h * (kQPBBytes / 2));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            // 32 e4m3 = 32 bytes along K: +2 in the 16-byte-unit address field
+                            mma_f8f6f4_pair(d_tmem, adesc + 2u * j, bdesc + 2u * j, kQPIdesc,
+                                            j != 0 ? 1u : 0u);
+                        }
+                        mma_commit_pair(pfull_bar(buf));            // partial product complete
+                        mma_commit_pair(peer_pfull0 + 8u * buf);
+                        if (++buf == 2) {
+                            buf = 0;
+                            buf_phase ^= 1u;
+                        }
+                    }
+                    if (!ok) break;
+                    mma_commit_pair(cempty_bar(stage));             // smem stage reusable
+                    mma_commit_pair(peer_cempty0 + 8u * stage);
+                    if (++stage == kQPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        } else if (rank == 1 && lane == 0) {
+            const uint32_t leader_cfull0 = map_to_cta(cfull_bar(0), 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+                for (int ds = 0; ds < num_ds; ++ds) {
+                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 44))) break;
+                    mbar_arrive_cluster(leader_cfull0 + 8u * stage);
+                    if (++stage == kQPStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+        __syncwarp();
+    } else {
+        const int quad = warp & 3;
+        const int half = (warp - 2) >> 2;       // which 128 columns of the tile
+        const int kbs = num_kb;                 // scales per row of A / per block row of B
+        const uint32_t pempty_leader0 = map_to_cta(pempty_bar(0), 0);
+        int buf = 0;
+        uint32_t buf_phase = 0;
+        bool ok = true;
+        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
+            int tm, tn;
+            tile_coords(tile, num_m, num_n, tm, tn);
+            const int row = tm * 256 + static_cast<int>(rank) * 128 + quad * 32 + lane;
+            const int col_base = tn * 256 + half * 128;
+            const bool live = col_base < N;                       // whole half outside the matrix?
+            const float* as_row = a_s + static_cast<int64_t>(row < M ? row : 0) * kbs;
+            const float* bs_row = b_s + static_cast<int64_t>(live ? col_base >> 7 : 0) * kbs;
+            float acc[128];
+#pragma unroll
+            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
+            for (int kb = 0; kb < num_kb; ++kb) {
+                const float scale = __ldg(as_row + kb) * __ldg(bs_row + kb);
+                if (!(ok = mbar_wait(pfull_bar(buf), buf_phase, abort_flag, 45))) break;
+                tc_fence_after();
+                // 64 columns per wait: the latency of a tensor-memory load is paid twice per K block
+                const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                                       static_cast<uint32_t>(buf * 256 + half * 128);
+                uint32_t r0[32], r1[32];
+                tmem_ld_32x32(taddr, r0);
+                tmem_ld_32x32(taddr + 32, r1);
+                tmem_ld_wait(r0);
+                tmem_ld_wait(r1);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), scale, acc[i]);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[32 + i]);
+                tmem_ld_32x32(taddr + 64, r0);
+                tmem_ld_32x32(taddr + 96, r1);
+                tmem_ld_wait(r0);
+                tmem_ld_wait(r1);
+                // every column of the buffer has been read: hand it back before the last fold
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(pempty_leader0 + 8u * buf);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), scale, acc[64 + i]);
+#pragma unroll
+                for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[96 + i]);
+                if (++buf == 2) {
+                    buf = 0;
+                    buf_phase ^= 1u;
+                }
+            }
+            if (!ok) break;
+            if (row < M && live) {
+                __nv_bfloat16* crow = c + static_cast<int64_t>(row) * ldc + col_base;
+#pragma unroll
+                for (int v = 0; v < 16; ++v) {
+                    if (col_base + v * 8 < N) {
+                        float f[8];
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) f[i] = acc[v * 8 + i];
+                        *reinterpret_cast<uint4*>(crow + v * 8) = pack_bf16x8(f);
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync();     // no CTA leaves, or frees tensor memory, while its peer may still signal it
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc_pair(tmem_base, 512);
     }
 }
 
@@ -1487,6 +1716,33 @@ static int launch_bf16_pair(const void* a, const void* b, void* c, int64_t M, in
     return check_launch("gemm_bf16_pair_kernel");
 }
 
+// Schedule of the FP8 GEMM: 0 = by size, 1 = single-CTA tiles, 2 = CTA pairs.
+static int g_fp8_schedule = 0;
+
+static int launch_fp8_pair(const void* a, const float* a_s, const void* b, const float* b_s,
+                           void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
+                           int64_t ldc, cudaStream_t st) {
+    CUtensorMap ta, tb;
+    if (int rc = make_tmap_kblocks(&ta, a, M, K, lda, 128, 2)) return rc;
+    if (int rc = make_tmap_kblocks(&tb, b, N, K, ldb, 128, 2)) return rc;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_pair_kernel,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                             static_cast<int>(kQPSmemBytes));
+        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_fp8: %s", cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    const int64_t max_pairs = sm_count() / 2;
+    const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
+    gemm_fp8_pair_kernel<<<grid, kQPThreads, kQPSmemBytes, st>>>(
+        ta, tb, a_s, b_s, static_cast<__nv_bfloat16*>(c), static_cast<int>(M), static_cast<int>(N),
+        static_cast<int>(K), ldc);
+    count_launch();
+    return check_launch("gemm_fp8_pair_kernel");
+}
+
 static int launch_fp8(const void* a, const float* a_s, const void* b, const float* b_s, void* c,
                       int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
                       cudaStream_t st) {
@@ -1595,7 +1851,17 @@ extern "C" int rt_gemm_fp8(const void* a, const float* a_scales, const void* b,
                "rt_gemm_fp8: pointers must be 16-byte aligned");
     RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_fp8: dimension too large");
+    const bool pair_pays = ((m + 255) / 256) * ((n + 255) / 256) >= tc::sm_count() / 2;
+    if (tc::g_fp8_schedule == 2 || (tc::g_fp8_schedule == 0 && pair_pays))
+        return tc::launch_fp8_pair(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc,
+                                   as_stream(stream));
     return tc::launch_fp8(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc, as_stream(stream));
+}
+
+extern "C" int rt_gemm_fp8_schedule(int schedule) {
+    const int previous = tc::g_fp8_schedule;
+    if (schedule >= 0 && schedule <= 2) tc::g_fp8_schedule = schedule;
+    return previous;
 }
 
 extern "C" int rt_moe_tile_map(const int32_t* offsets, int64_t g_begin, int64_t g_end,

@@ -142,9 +142,15 @@ def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, s
                 run_bf16, 2 * T * n * k, (T * k + n * k + T * n) * 2, "bf16")
         wc, ws = ops.quantize_weight_fp8(w)
         xc, xs = ops.fused_act_quant(x)
-        out[f"linear_fp8[{name} {T}x{n}x{k}]"] = (
-            (lambda xc=xc, xs=xs, wc=wc, ws=ws: ops.linear_fp8(xc, xs, wc, ws)), 2 * T * n * k,
-            T * k + n * k + T * n * 2, "fp8")
+        for sched, tag in ((2, "pair"), (1, "single")):
+            def run_fp8(xc=xc, xs=xs, wc=wc, ws=ws, sched=sched):
+                ops.gemm_fp8_schedule(sched)
+                try:
+                    return ops.linear_fp8(xc, xs, wc, ws)
+                finally:
+                    ops.gemm_fp8_schedule(0)
+            out[f"linear_fp8/{tag}[{name} {T}x{n}x{k}]"] = (
+                run_fp8, 2 * T * n * k, T * k + n * k + T * n * 2, "fp8")
     for name, n, k in (("w13", 4096, HIDDEN), ("w2", HIDDEN, 2048)):
         x, w = _randn(T, k), _randn(n, k)
         xq = ops.fused_nvfp4_quant(x, tiled_scales=True)

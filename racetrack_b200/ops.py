@@ -633,6 +633,12 @@ def gemm_bf16_schedule(schedule: int) -> int:
     return int(_lib.load().rt_gemm_bf16_schedule(int(schedule)))
 
 
+def gemm_fp8_schedule(schedule: int) -> int:
+    """Selects the schedule of the FP8 GEMM for this process (0 default = by size, 1 single-CTA
+    128 x 256 tiles, 2 CTA pairs with 256 x 256 tiles) and returns the previous setting."""
+    return int(_lib.load().rt_gemm_fp8_schedule(int(schedule)))
+
+
 def gemm_nvfp4_schedule(schedule: int) -> int:
     """Selects the schedule of the NVFP4 GEMM for this process (0 default = CTA pairs,
     1 single-CTA 128 x 128 tiles, 2 CTA pairs) and returns the previous setting."""
