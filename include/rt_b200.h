@@ -453,9 +453,9 @@ int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* a_
 int rt_gemm_bf16_schedule(int schedule);
 
 /*
- * Schedule of rt_gemm_fp8 for this process: 0 = default (CTA pairs with 256 x 256 tiles when
- * ceil(m/256) * ceil(n/256) is at least half the SM count, else single-CTA 128 x 256 tiles),
- * 1 = single-CTA, 2 = CTA pairs. Returns the previous value; any other argument only queries.
+ * Schedule of rt_gemm_fp8 for this process: 0 = default (single-CTA 128 x 256 tiles),
+ * 1 = single-CTA, 2 = CTA pairs with 256 x 256 tiles. Returns the previous value; any other
+ * argument only queries.
  * No counterpart in racetrack.
  */
 int rt_gemm_fp8_schedule(int schedule);

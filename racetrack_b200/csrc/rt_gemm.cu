@@ -1716,7 +1716,7 @@ static int launch_bf16_pair(const void* a, const void* b, void* c, int64_t M, in
     return check_launch("gemm_bf16_pair_kernel");
 }
 
-// Schedule of the FP8 GEMM: 0 = by size, 1 = single-CTA tiles, 2 = CTA pairs.
+// Schedule of the FP8 GEMM: 0 = default (single-CTA tiles), 1 = single-CTA tiles, 2 = CTA pairs.
 static int g_fp8_schedule = 0;
 
 static int launch_fp8_pair(const void* a, const float* a_s, const void* b, const float* b_s,
@@ -1851,8 +1851,7 @@ extern "C" int rt_gemm_fp8(const void* a, const float* a_scales, const void* b,
                "rt_gemm_fp8: pointers must be 16-byte aligned");
     RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_fp8: dimension too large");
-    const bool pair_pays = ((m + 255) / 256) * ((n + 255) / 256) >= tc::sm_count() / 2;
-    if (tc::g_fp8_schedule == 2 || (tc::g_fp8_schedule == 0 && pair_pays))
+    if (tc::g_fp8_schedule == 2)
         return tc::launch_fp8_pair(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc,
                                    as_stream(stream));
     return tc::launch_fp8(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc, as_stream(stream));

@@ -634,8 +634,8 @@ def gemm_bf16_schedule(schedule: int) -> int:
 
 
 def gemm_fp8_schedule(schedule: int) -> int:
-    """Selects the schedule of the FP8 GEMM for this process (0 default = by size, 1 single-CTA
-    128 x 256 tiles, 2 CTA pairs with 256 x 256 tiles) and returns the previous setting."""
+    """Selects the schedule of the FP8 GEMM for this process (0 default = single-CTA 128 x 256
+    tiles, 1 the same, 2 CTA pairs with 256 x 256 tiles) and returns the previous setting."""
     return int(_lib.load().rt_gemm_fp8_schedule(int(schedule)))
 
 
