@@ -453,14 +453,6 @@ int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, const float* a_
 int rt_gemm_bf16_schedule(int schedule);
 
 /*
- * Schedule of rt_gemm_fp8 for this process: 0 = default (single-CTA 128 x 256 tiles),
- * 1 = single-CTA, 2 = CTA pairs with 256 x 256 tiles. Returns the previous value; any other
- * argument only queries.
- * No counterpart in racetrack.
- */
-int rt_gemm_fp8_schedule(int schedule);
-
-/*
  * Schedule of rt_gemm_nvfp4_grouped for this process: 0 = default (CTA pairs, unless
  * max_m_tiles * ceil(n/256) is below the SM count or total_rows < 128 * groups: then
  * single-CTA tiles), 1 = single-CTA
@@ -468,6 +460,31 @@ int rt_gemm_fp8_schedule(int schedule);
  * For A/B measurements and tests. No counterpart in racetrack.
  */
 int rt_gemm_nvfp4_schedule(int schedule);
+
+/*
+ * Index scores of the sparse-attention indexer (tcgen05, FP8 x FP8, fp32 accumulate):
+ *   scores[m, n] = k_scale[n] * sum_h weights[m, h] * relu(q[m, h, :] . k[n, :])
+ * q e4m3 [queries, heads, dim], k e4m3 [keys, dim] (both contiguous), weights fp32 [queries,
+ * heads] (per-head weight times the query's quantisation scale and the softmax scale),
+ * k_scale fp32 [keys], scores fp32 [queries, keys] with row pitch score_stride.
+ * causal_offset >= 0: key n is visible to query m iff n <= m + causal_offset, other scores are
+ * written as -inf (the reference adds a -inf mask, deepseek.py:681-682); causal_offset < 0:
+ * no mask. dim == 128; heads in {16, 32, 64, 128}.
+ * ref: racetrack/models/deepseek.py:164-176 (fp8_index), :677-682 (Indexer.forward).
+ */
+int rt_fp8_index(const void* q, const float* weights, const void* k, const float* k_scale,
+                 float* scores, int64_t queries, int64_t heads, int64_t keys, int64_t dim,
+                 int64_t score_stride, int64_t causal_offset, void* stream);
+
+/*
+ * Top-k selection of the indexer: indices [queries, topk] (int32) of the topk largest scores
+ * of every row, written in ascending index order; among scores equal to the k-th largest the
+ * lower indices are taken. Exact (radix select on the ordered bit patterns), -inf allowed.
+ * topk <= keys. The reference consumes the indices as a set (deepseek.py:683, :757-759).
+ * ref: racetrack/models/deepseek.py:683 (index_score.topk).
+ */
+int rt_index_topk(const float* scores, int32_t* indices, int64_t queries, int64_t keys,
+                  int64_t score_stride, int64_t topk, void* stream);
 
 /*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when

@@ -94,6 +94,27 @@ def gate_inputs(tokens: int = 4096, *, hidden: int = HIDDEN, n_experts: int = N_
     }
 
 
+INDEX_HEADS = 64
+INDEX_DIM = 128
+INDEX_TOPK = 2048
+
+
+def indexer_inputs(queries: int, keys: int, *, heads: int = INDEX_HEADS, dim: int = INDEX_DIM,
+                   seed: int = SEED) -> dict:
+    """Operands of the sparse indexer's scoring step as the reference forms them
+    (racetrack/models/deepseek.py:671-680): q [1, m, h, d] and k [1, n, d] N(0, 1) quantised
+    per 128 to e4m3 (one group per head / key), weights = N(0, 1) * h^-0.5 * q_scale * d^-0.5."""
+    from . import ref_ops as R
+    q = randn((1, queries, heads, dim), seed + 700)
+    k = randn((1, keys, dim), seed + 701)
+    q_fp8, q_scale = R.act_quant(q)                       # scales [1, m, h, 1]
+    k_fp8, k_scale = R.act_quant(k)                       # scales [1, n, 1]
+    w = randn((1, queries, heads), seed + 702, dtype=torch.float32) * heads ** -0.5
+    weights = (w.unsqueeze(-1) * q_scale * dim ** -0.5).squeeze(-1)
+    return {"q": q_fp8, "weights": weights.contiguous(), "k": k_fp8,
+            "k_scale": k_scale.squeeze(-1).contiguous()}
+
+
 def expert_weights(n_experts: int, hidden: int, inter: int, *, seed: int = SEED,
                    dtype: torch.dtype = torch.bfloat16):
     """[(w1 [inter, hidden], w2 [hidden, inter], w3 [inter, hidden])] ~ N(0, 0.02)."""

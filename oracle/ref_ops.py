@@ -162,6 +162,25 @@ def swiglu_quant(gate: torch.Tensor, up: torch.Tensor):
     return act_quant(swiglu(gate, up))
 
 
+def fp8_index(q: torch.Tensor, q_s: torch.Tensor, k: torch.Tensor, k_s: torch.Tensor) -> torch.Tensor:
+    """Index scores of the sparse-attention indexer.
+        score[b, m, n] = k_s[b, n] * sum_h q_s[b, m, h] * relu(q[b, m, h, :] . k[b, n, :])
+    q [b, m, h, d] and k [b, n, d] are e4m3 codes, q_s [b, m, h] fp32 (per-head weight already
+    multiplied by the query's quantisation scale and the softmax scale), k_s [b, n] fp32.
+    ref: racetrack/models/deepseek.py:164-176 (fp8_index)."""
+    logits = torch.einsum("bmhd,bnd->bmhn", q.float(), k.float())
+    logits = torch.relu(logits) * q_s.unsqueeze(-1)
+    return logits.sum(dim=2) * k_s.unsqueeze(1)
+
+
+def index_topk(scores: torch.Tensor, topk: int, mask: torch.Tensor | None = None) -> torch.Tensor:
+    """Indices of the `min(topk, n)` largest scores per query, after adding the (causal)
+    mask. ref: racetrack/models/deepseek.py:681-683."""
+    if mask is not None:
+        scores = scores + mask
+    return scores.topk(min(topk, scores.shape[-1]), dim=-1)[1]
+
+
 def block_dequant(weight: torch.Tensor, scale: torch.Tensor, block: int = FP8_BLOCK) -> torch.Tensor:
     """FP8 weight [out, in] with [out/128, in/128] scales -> bf16.
     ref: racetrack/models/deepseek.py:148-161."""

@@ -697,7 +697,7 @@ __global__ void __launch_bounds__(kFThreads, 1) gemm_nvfp4_kernel(
 // Warps (both CTAs): 0 operand producer (one elected thread), 1 tensor-memory owner and MMA
 // issuer (leader CTA, cluster rank 0) or relay (peer: tells the leader that its operands have
 // landed), 2-5 scale loaders (shared -> tensor memory), 6-13 epilogue (lane quarter w % 4,
-// token half (w - 6) / 4), 14 spare, 15 scale producer.
+// token half (w - 6) / 4), 14 scale producer.
 // Barriers per CTA: cfull[d] (operands of stage d landed; in the leader also the peer's
 // relay), cempty[d] (MMAs of stage d done), sfull[s] / sfree[s] (scale slot s filled in /
 // copied out of shared memory), tsfree[s] (MMAs that read scale slot s of tensor memory
@@ -706,7 +706,7 @@ __global__ void __launch_bounds__(kFThreads, 1) gemm_nvfp4_kernel(
 // pair). The leader commits cempty, tsfree and tfull to both CTAs.
 constexpr int kPStages = 3;                        // operand stages of two K blocks each
 constexpr int kPSlots = 5;                         // scale slots (shared and tensor memory)
-constexpr int kPThreads = 512;
+constexpr int kPThreads = 480;
 constexpr uint32_t kPWBytes = 2 * 128 * 128;       // weight rows of a stage (two K blocks)
 constexpr uint32_t kPXBytes = 2 * 128 * 128;       // token rows of a stage (this CTA's half)
 constexpr uint32_t kPStageBytes = kPWBytes + kPXBytes;
@@ -965,7 +965,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                 }
             }
         }
-    } else if (warp == 15) {
+    } else if (warp == 14) {
         // Scale producer: the scale tiles of a K block (2 KB for this CTA's weight rows, 2 or 4 KB
         // for all token rows of the tile) come in 16-byte cp.async copies, 4 per lane and tile
         // set, through the load/store unit: the TMA unit is the bottleneck and stays free of
@@ -1016,19 +1016,32 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
             if (!(ok = mbar_wait(tfull_bar, tphase, abort_flag, 25))) break;
             tc_fence_after();
             __nv_bfloat162 packed[64];
+            // two 32-column loads per wait: the accumulator is single-buffered, so the latency
+            // of its drain (a few hundred cycles per tensor-memory load) is on the critical path
 #pragma unroll
-            for (int chunk = 0; chunk < 4; ++chunk) {
+            for (int chunk = 0; chunk < 4; chunk += 2) {
                 const int col0 = half * 128 + chunk * 32;
                 if (col0 < n_mma) {
-                    uint32_t r[32];
-                    tmem_ld_32x32(tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
-                                      static_cast<uint32_t>(col0), r);
-                    tmem_ld_wait(r);
+                    const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
+                                           static_cast<uint32_t>(col0);
+                    const bool second = col0 + 32 < n_mma;       // warp-uniform
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(taddr, r0);
+                    if (second) tmem_ld_32x32(taddr + 32, r1);
+                    tmem_ld_wait(r0);
+                    if (second) tmem_ld_wait(r1);
 #pragma unroll
                     for (int i = 0; i < 16; ++i)
                         packed[16 * chunk + i] =
-                            __floats2bfloat162_rn(__uint_as_float(r[2 * i]) * alpha,
-                                                  __uint_as_float(r[2 * i + 1]) * alpha);
+                            __floats2bfloat162_rn(__uint_as_float(r0[2 * i]) * alpha,
+                                                  __uint_as_float(r0[2 * i + 1]) * alpha);
+                    if (second) {
+#pragma unroll
+                        for (int i = 0; i < 16; ++i)
+                            packed[16 * chunk + 16 + i] =
+                                __floats2bfloat162_rn(__uint_as_float(r1[2 * i]) * alpha,
+                                                      __uint_as_float(r1[2 * i + 1]) * alpha);
+                    }
                 }
             }
             tc_fence_before();
@@ -1155,9 +1168,10 @@ __global__ void __launch_bounds__(1024) moe_tile_map_kernel(const int32_t* __res
 // Tile 128 x 256, stage = one K block: 16 KB of A + 32 KB of B, 4 stages.
 // Warps: 0 TMA producer, 1 MMA issuer, 2-9 epilogue (warp w: lane quarter w % 4, column half
 // (w - 2) / 4).
-// What bounds it is the folding, not the operands: a CTA-pair variant (256 x 256 tiles, half the
-// operand bytes and TMA loads per K block, the schedule that speeds the bf16 and NVFP4 GEMMs up)
-// ran at the same 1.6-1.8 PFLOP/s and was dropped.
+// A CTA-pair variant (256 x 256 tiles, half the operand bytes and TMA loads per K block, the
+// schedule that speeds the bf16 and NVFP4 GEMMs up) ran at the same 1.6-1.8 PFLOP/s, with the fold
+// waiting four times or twice per K block on tensor-memory loads, and was dropped: neither the
+// operands nor the fold's load latency is what holds this kernel at about 1000 cycles per K block.
 constexpr int kQBN = 256;
 constexpr int kQBK = 128;
 constexpr int kQStages = 4;
@@ -1349,230 +1363,224 @@ __global__ void __launch_bounds__(kQThreads, 1) gemm_fp8_kernel(
 }
 
 // ---------------------------------------------------------------------------
-// FP8 e4m3 GEMM with DeepSeek block scales on CTA pairs (tcgen05 cta_group::2)
+// Index scores of the sparse-attention indexer (FP8 x FP8, tcgen05)
 // ---------------------------------------------------------------------------
-// Same arithmetic as gemm_fp8_kernel (every 128-wide K block multiplied on its own into one
-// of two 256-column tensor-memory buffers and folded, scaled, into fp32 registers by eight
-// epilogue warps), on 256 x 256 tiles over a pair of CTAs: each CTA supplies 128 rows of A and
-// 128 rows of B per K block (32 KB instead of 48 KB), and every TMA load covers two K blocks
-// (an SM retires about one tiled load per 500 cycles; the single-CTA kernel needs two per K
-// block, which alone costs as much as twice the MMA time of the block). 3 stages of 64 KB.
-// Warps (both CTAs): 0 producer, 1 tensor-memory owner and MMA issuer (leader) or relay
-// (peer), 2-9 epilogue (lane quarter w % 4, column half (w - 2) / 4).
-constexpr int kQPStages = 3;
-constexpr int kQPThreads = 320;
-constexpr uint32_t kQPABytes = 2 * 128 * 128;
-constexpr uint32_t kQPBBytes = 2 * 128 * 128;
-constexpr uint32_t kQPStageBytes = kQPABytes + kQPBBytes;
-constexpr uint32_t kQPBarOffset = kQPStages * kQPStageBytes;
-constexpr uint32_t kQPSmemBytes = kQPBarOffset + (2 * kQPStages + 4) * 8 + 16 + 1024;
-// fp32 accumulate, e4m3 x e4m3 (format code 0), K-major, N = 256, M = 256 over the pair
-constexpr uint32_t kQPIdesc = (1u << 4) | (32u << 17) | (16u << 24);
+//   score[m, n] = k_s[n] * sum_h w[m, h] * relu(q[m, h, :] . k[n, :])        (dim = 128)
+// The KEYS are the MMA's M (128 per tile, so an epilogue thread owns one key), the (query, head)
+// pairs its N (256 per tile = 256 / heads queries): the sum over heads is then a loop over the
+// thread's own accumulator columns, no cross-lane traffic, and for one query a warp stores 32
+// consecutive keys' scores. One K block (128 e4m3) per MMA group, so each key tile costs one TMA
+// load; the query block (32 KB) is loaded once per work item and reused for a chunk of key tiles.
+// Work item = (query block, chunk of up to kIdxChunk key tiles); persistent CTAs.
+// Warps: 0 producer, 1 MMA issuer, 2-9 epilogue (lane quarter w % 4, column half (w - 2) / 4).
+// Barriers: kfull/kempty[4] (key tiles), qfull/qempty[2] (query blocks), pfull/pempty[2]
+// (accumulator buffers of 256 columns).
+constexpr int kIdxStages = 4;
+constexpr int kIdxChunk = 16;
+constexpr int kIdxThreads = 320;
+constexpr uint32_t kIdxKBytes = 128 * 128;
+constexpr uint32_t kIdxQBytes = 256 * 128;
+constexpr uint32_t kIdxQOffset = kIdxStages * kIdxKBytes;
+constexpr uint32_t kIdxWOffset = kIdxQOffset + 2 * kIdxQBytes;      // 2 x 256 fp32 head weights
+constexpr uint32_t kIdxBarOffset = kIdxWOffset + 2 * 256 * 4;
+constexpr int kIdxBarriers = 2 * kIdxStages + 4 + 4;
+constexpr uint32_t kIdxSmemBytes = kIdxBarOffset + kIdxBarriers * 8 + 16 + 1024;
+// fp32 accumulate, e4m3 x e4m3, K-major, N = 256, M = 128
+constexpr uint32_t kIdxIdesc = (1u << 4) | (32u << 17) | (8u << 24);
 
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kQPThreads, 1) gemm_fp8_pair_kernel(
-    const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-    const float* __restrict__ a_s, const float* __restrict__ b_s, __nv_bfloat16* __restrict__ c,
-    int M, int N, int K, int64_t ldc) {
+__global__ void __launch_bounds__(kIdxThreads, 1) index_score_kernel(
+    const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
+    const float* __restrict__ weights, const float* __restrict__ k_scale,
+    float* __restrict__ scores, int queries, int heads, int keys, int64_t ld,
+    int64_t causal_offset) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
-    const uint32_t bars = base + kQPBarOffset;
-    auto cfull_bar = [&](int d) { return bars + 8u * d; };
-    auto cempty_bar = [&](int d) { return bars + 8u * (kQPStages + d); };
-    auto pfull_bar = [&](int a) { return bars + 8u * (2 * kQPStages + a); };
-    auto pempty_bar = [&](int a) { return bars + 8u * (2 * kQPStages + 2 + a); };
-    const uint32_t slot = bars + 8u * (2 * kQPStages + 4);
+    float* wsm = reinterpret_cast<float*>(base_ptr + kIdxWOffset);
+    const uint32_t bars = base + kIdxBarOffset;
+    auto kfull_bar = [&](int s) { return bars + 8u * s; };
+    auto kempty_bar = [&](int s) { return bars + 8u * (kIdxStages + s); };
+    auto qfull_bar = [&](int s) { return bars + 8u * (2 * kIdxStages + s); };
+    auto qempty_bar = [&](int s) { return bars + 8u * (2 * kIdxStages + 2 + s); };
+    auto pfull_bar = [&](int a) { return bars + 8u * (2 * kIdxStages + 4 + a); };
+    auto pempty_bar = [&](int a) { return bars + 8u * (2 * kIdxStages + 6 + a); };
+    const uint32_t slot = bars + 8u * kIdxBarriers;
     volatile uint32_t* slot_ptr =
-        reinterpret_cast<volatile uint32_t*>(base_ptr + kQPBarOffset + 8 * (2 * kQPStages + 4));
+        reinterpret_cast<volatile uint32_t*>(base_ptr + kIdxBarOffset + 8 * kIdxBarriers);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();
-    const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-    const int num_m = (M + 255) / 256, num_n = (N + 255) / 256;
-    const int num_tiles = num_m * num_n;
-    const int num_kb = K / 128;
-    const int num_ds = (num_kb + 1) / 2;
+    const int q_rows = queries * heads;
+    const int num_qb = (q_rows + 255) / 256;
+    const int num_kt = (keys + 127) / 128;
+    const int num_kc = (num_kt + kIdxChunk - 1) / kIdxChunk;
+    const int num_items = num_qb * num_kc;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
-        for (int d = 0; d < kQPStages; ++d) {
-            mbar_init(cfull_bar(d), rank == 0 ? 2 : 1);   // own producer (+ the peer's relay)
-            mbar_init(cempty_bar(d), 1);
+        for (int s = 0; s < kIdxStages; ++s) {
+            mbar_init(kfull_bar(s), 1);
+            mbar_init(kempty_bar(s), 1);
         }
         for (int a = 0; a < 2; ++a) {
+            mbar_init(qfull_bar(a), 1);
+            mbar_init(qempty_bar(a), 1);
             mbar_init(pfull_bar(a), 1);
-            mbar_init(pempty_bar(a), 16);    // 8 epilogue warps in each CTA of the pair
+            mbar_init(pempty_bar(a), 8);     // one arrival per epilogue warp
         }
         fence_mbar_init();
-        tma_prefetch_desc(&tmap_a);
-        tma_prefetch_desc(&tmap_b);
+        tma_prefetch_desc(&tmap_k);
+        tma_prefetch_desc(&tmap_q);
     }
     if (warp == 1) {
-        tmem_alloc_pair(slot, 512);
-        tmem_relinquish_pair();
+        tmem_alloc(slot, 512);
+        tmem_relinquish();
     }
     tc_fence_before();
     __syncthreads();
-    cluster_sync();                          // the peer's barriers exist before anyone signals them
     tc_fence_after();
     const uint32_t tmem_base = *slot_ptr;
 
     if (warp == 0) {
         if (lane == 0) {
-            int stage = 0;
-            uint32_t phase = 0;
+            int stage = 0, qs = 0;
+            uint32_t phase = 0, qphase = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                int tm, tn;
-                tile_coords(tile, num_m, num_n, tm, tn);
-                const int a_row = tm * 256 + static_cast<int>(rank) * 128;
-                const int b_row = tn * 256 + static_cast<int>(rank) * 128;
-                for (int ds = 0; ds < num_ds; ++ds) {
-                    if (!(ok = mbar_wait(cempty_bar(stage), phase ^ 1u, abort_flag, 41))) break;
-                    const uint32_t sa = base + stage * kQPStageBytes;
-                    mbar_arrive_expect_tx(cfull_bar(stage), kQPStageBytes);
-                    tma_load_3d(sa, &tmap_a, 0, a_row, 2 * ds, cfull_bar(stage));
-                    tma_load_3d(sa + kQPABytes, &tmap_b, 0, b_row, 2 * ds, cfull_bar(stage));
-                    if (++stage == kQPStages) {
+            for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+                const int qb = item / num_kc, kc = item % num_kc;
+                if (!(ok = mbar_wait(qempty_bar(qs), qphase ^ 1u, abort_flag, 51))) break;
+                mbar_arrive_expect_tx(qfull_bar(qs), kIdxQBytes);
+                tma_load_2d(base + kIdxQOffset + qs * kIdxQBytes, &tmap_q, 0, qb * 256, qfull_bar(qs));
+                const int kt_end = min(num_kt, (kc + 1) * kIdxChunk);
+                for (int kt = kc * kIdxChunk; kt < kt_end; ++kt) {
+                    if (!(ok = mbar_wait(kempty_bar(stage), phase ^ 1u, abort_flag, 52))) break;
+                    mbar_arrive_expect_tx(kfull_bar(stage), kIdxKBytes);
+                    tma_load_2d(base + stage * kIdxKBytes, &tmap_k, 0, kt * 128, kfull_bar(stage));
+                    if (++stage == kIdxStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
+                }
+                if (++qs == 2) {
+                    qs = 0;
+                    qphase ^= 1u;
                 }
             }
         }
         __syncwarp();
     } else if (warp == 1) {
-        if (rank == 0 && lane == 0) {
-            const uint32_t peer_cempty0 = map_to_cta(cempty_bar(0), 1);
-            const uint32_t peer_pfull0 = map_to_cta(pfull_bar(0), 1);
-            int stage = 0, buf = 0;
-            uint32_t phase = 0, buf_phase = 0;
+        if (lane == 0) {
+            int stage = 0, qs = 0, buf = 0;
+            uint32_t phase = 0, qphase = 0, buf_phase = 0;
             bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                for (int ds = 0; ok && ds < num_ds; ++ds) {
-                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 43))) break;
-                    const uint32_t sa = base + stage * kQPStageBytes;
-                    const int halves = min(2, num_kb - 2 * ds);
-                    for (int h = 0; h < halves; ++h) {
-                        if (!(ok = mbar_wait(pempty_bar(buf), buf_phase ^ 1u, abort_flag, 42))) break;
-                        tc_fence_after();
-                        const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * 256);
-                        const uint64_t adesc = smem_desc_sw128(sa + h * (kQPABytes / 2));
-                        const uint64_t bdesc =
-                            smem_desc_sw128(sa + kQPABytes + h * (kQPBBytes / 2));
+            for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
+                const int kc = item % num_kc;
+                if (!(ok = mbar_wait(qfull_bar(qs), qphase, abort_flag, 53))) break;
+                const uint64_t bdesc = smem_desc_sw128(base + kIdxQOffset + qs * kIdxQBytes);
+                const int kt_end = min(num_kt, (kc + 1) * kIdxChunk);
+                for (int kt = kc * kIdxChunk; kt < kt_end; ++kt) {
+                    if (!(ok = mbar_wait(pempty_bar(buf), buf_phase ^ 1u, abort_flag, 54))) break;
+                    if (!(ok = mbar_wait(kfull_bar(stage), phase, abort_flag, 55))) break;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(buf * 256);
+                    const uint64_t adesc = smem_desc_sw128(base + stage * kIdxKBytes);
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            // 32 e4m3 = 32 bytes along K: +2 in the 16-byte-unit address field
-                            mma_f8f6f4_pair(d_tmem, adesc + 2u * j, bdesc + 2u * j, kQPIdesc,
-                                            j != 0 ? 1u : 0u);
-                        }
-                        mma_commit_pair(pfull_bar(buf));            // partial product complete
-                        mma_commit_pair(peer_pfull0 + 8u * buf);
-                        if (++buf == 2) {
-                            buf = 0;
-                            buf_phase ^= 1u;
-                        }
-                    }
-                    if (!ok) break;
-                    mma_commit_pair(cempty_bar(stage));             // smem stage reusable
-                    mma_commit_pair(peer_cempty0 + 8u * stage);
-                    if (++stage == kQPStages) {
+                    for (int j = 0; j < 4; ++j)
+                        mma_f8f6f4(d_tmem, adesc + 2u * j, bdesc + 2u * j, kIdxIdesc, j != 0 ? 1u : 0u);
+                    mma_commit(kempty_bar(stage));
+                    mma_commit(pfull_bar(buf));
+                    if (++stage == kIdxStages) {
                         stage = 0;
                         phase ^= 1u;
+                    }
+                    if (++buf == 2) {
+                        buf = 0;
+                        buf_phase ^= 1u;
                     }
                 }
-            }
-        } else if (rank == 1 && lane == 0) {
-            const uint32_t leader_cfull0 = map_to_cta(cfull_bar(0), 0);
-            int stage = 0;
-            uint32_t phase = 0;
-            bool ok = true;
-            for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-                for (int ds = 0; ds < num_ds; ++ds) {
-                    if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 44))) break;
-                    mbar_arrive_cluster(leader_cfull0 + 8u * stage);
-                    if (++stage == kQPStages) {
-                        stage = 0;
-                        phase ^= 1u;
-                    }
+                if (!ok) break;
+                mma_commit(qempty_bar(qs));      // the query block is free when these MMAs retire
+                if (++qs == 2) {
+                    qs = 0;
+                    qphase ^= 1u;
                 }
             }
         }
         __syncwarp();
     } else {
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;       // which 128 columns of the tile
-        const int kbs = num_kb;                 // scales per row of A / per block row of B
-        const uint32_t pempty_leader0 = map_to_cta(pempty_bar(0), 0);
-        int buf = 0;
+        const int half = (warp - 2) >> 2;       // which 128 (query, head) columns of the tile
+        const int et = threadIdx.x - 64;        // 0..255 among the epilogue threads
+        const int q_per_half = 128 / heads;
+        int buf = 0, parity = 0;
         uint32_t buf_phase = 0;
         bool ok = true;
-        for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
-            int tm, tn;
-            tile_coords(tile, num_m, num_n, tm, tn);
-            const int row = tm * 256 + static_cast<int>(rank) * 128 + quad * 32 + lane;
-            const int col_base = tn * 256 + half * 128;
-            const bool live = col_base < N;                       // whole half outside the matrix?
-            const float* as_row = a_s + static_cast<int64_t>(row < M ? row : 0) * kbs;
-            const float* bs_row = b_s + static_cast<int64_t>(live ? col_base >> 7 : 0) * kbs;
-            float acc[128];
-#pragma unroll
-            for (int i = 0; i < 128; ++i) acc[i] = 0.f;
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const float scale = __ldg(as_row + kb) * __ldg(bs_row + kb);
-                if (!(ok = mbar_wait(pfull_bar(buf), buf_phase, abort_flag, 45))) break;
+        for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, parity ^= 1) {
+            const int qb = item / num_kc, kc = item % num_kc;
+            // head weights of the block's 256 (query, head) rows; the named barrier also says
+            // that every epilogue thread has left the item that used this half of wsm before
+            const int qrow = qb * 256 + et;
+            wsm[parity * 256 + et] = qrow < q_rows ? __ldg(weights + qrow) : 0.f;
+            asm volatile("bar.sync 1, 256;" ::: "memory");
+            const float* wv = wsm + parity * 256 + half * 128;
+            const int m0 = (qb * 256 + half * 128) / heads;     // first query of this half
+            const int kt_end = min(num_kt, (kc + 1) * kIdxChunk);
+            for (int kt = kc * kIdxChunk; kt < kt_end; ++kt) {
+                const int n = kt * 128 + quad * 32 + lane;
+                const float ks = n < keys ? __ldg(k_scale + n) : 0.f;
+                if (!(ok = mbar_wait(pfull_bar(buf), buf_phase, abort_flag, 56))) break;
                 tc_fence_after();
-                // 64 columns per wait: the latency of a tensor-memory load is paid twice per K block
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
                                        static_cast<uint32_t>(buf * 256 + half * 128);
-                uint32_t r0[32], r1[32];
-                tmem_ld_32x32(taddr, r0);
-                tmem_ld_32x32(taddr + 32, r1);
-                tmem_ld_wait(r0);
-                tmem_ld_wait(r1);
+                float sums[8];
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[i] = fmaf(__uint_as_float(r0[i]), scale, acc[i]);
+                for (int j = 0; j < 8; ++j) sums[j] = 0.f;
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[32 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[32 + i]);
-                tmem_ld_32x32(taddr + 64, r0);
-                tmem_ld_32x32(taddr + 96, r1);
-                tmem_ld_wait(r0);
-                tmem_ld_wait(r1);
-                // every column of the buffer has been read: hand it back before the last fold
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(pempty_leader0 + 8u * buf);
+                for (int pairi = 0; pairi < 2; ++pairi) {
+                    uint32_t r0[32], r1[32];
+                    tmem_ld_32x32(taddr + pairi * 64, r0);
+                    tmem_ld_32x32(taddr + pairi * 64 + 32, r1);
+                    tmem_ld_wait(r0);
+                    tmem_ld_wait(r1);
+                    if (pairi == 1) {
+                        // every column of the buffer has been read: hand it back
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(pempty_bar(buf));
+                    }
 #pragma unroll
-                for (int i = 0; i < 32; ++i) acc[64 + i] = fmaf(__uint_as_float(r0[i]), scale, acc[64 + i]);
-#pragma unroll
-                for (int i = 0; i < 32; ++i) acc[96 + i] = fmaf(__uint_as_float(r1[i]), scale, acc[96 + i]);
+                    for (int i = 0; i < 32; ++i) {
+                        const int c0 = pairi * 64 + i, c1 = c0 + 32;
+                        sums[c0 / 16] = fmaf(fmaxf(__uint_as_float(r0[i]), 0.f), wv[c0], sums[c0 / 16]);
+                        sums[c1 / 16] = fmaf(fmaxf(__uint_as_float(r1[i]), 0.f), wv[c1], sums[c1 / 16]);
+                    }
+                }
+                // sums[] holds 16-column partial sums; a query owns heads / 16 of them
+                if (n < keys) {
+                    const int per_q = heads / 16;
+                    for (int j = 0; j < q_per_half; ++j) {
+                        float s = 0.f;
+                        for (int t = 0; t < per_q; ++t) s += sums[j * per_q + t];
+                        const int m = m0 + j;
+                        if (m < queries) {
+                            const bool visible = causal_offset < 0 || n <= m + causal_offset;
+                            scores[static_cast<int64_t>(m) * ld + n] =
+                                visible ? s * ks : __int_as_float(0xff800000);
+                        }
+                    }
+                }
                 if (++buf == 2) {
                     buf = 0;
                     buf_phase ^= 1u;
-                }
-            }
-            if (!ok) break;
-            if (row < M && live) {
-                __nv_bfloat16* crow = c + static_cast<int64_t>(row) * ldc + col_base;
-#pragma unroll
-                for (int v = 0; v < 16; ++v) {
-                    if (col_base + v * 8 < N) {
-                        float f[8];
-#pragma unroll
-                        for (int i = 0; i < 8; ++i) f[i] = acc[v * 8 + i];
-                        *reinterpret_cast<uint4*>(crow + v * 8) = pack_bf16x8(f);
-                    }
                 }
             }
         }
     }
     tc_fence_before();
     __syncthreads();
-    cluster_sync();     // no CTA leaves, or frees tensor memory, while its peer may still signal it
     if (warp == 1) {
         tc_fence_after();
-        tmem_dealloc_pair(tmem_base, 512);
+        tmem_dealloc(tmem_base, 512);
     }
 }
 
@@ -1716,31 +1724,32 @@ static int launch_bf16_pair(const void* a, const void* b, void* c, int64_t M, in
     return check_launch("gemm_bf16_pair_kernel");
 }
 
-// Schedule of the FP8 GEMM: 0 = default (single-CTA tiles), 1 = single-CTA tiles, 2 = CTA pairs.
-static int g_fp8_schedule = 0;
-
-static int launch_fp8_pair(const void* a, const float* a_s, const void* b, const float* b_s,
-                           void* c, int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb,
-                           int64_t ldc, cudaStream_t st) {
-    CUtensorMap ta, tb;
-    if (int rc = make_tmap_kblocks(&ta, a, M, K, lda, 128, 2)) return rc;
-    if (int rc = make_tmap_kblocks(&tb, b, N, K, ldb, 128, 2)) return rc;
+static int launch_index_score(const void* q, const float* weights, const void* k,
+                              const float* k_scale, float* scores, int64_t queries, int64_t heads,
+                              int64_t keys, int64_t ld, int64_t causal_offset, cudaStream_t st) {
+    CUtensorMap tk, tq;
+    if (int rc = make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, k, 128, keys, 128, 128, 128))
+        return rc;
+    if (int rc = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, q, 128, queries * heads, 128, 128,
+                              256))
+        return rc;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_pair_kernel,
+        cudaError_t e = cudaFuncSetAttribute(index_score_kernel,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kQPSmemBytes));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_fp8: %s", cudaGetErrorString(e));
+                                             static_cast<int>(kIdxSmemBytes));
+        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_fp8_index: %s", cudaGetErrorString(e));
         attr_set = true;
     }
-    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    const int64_t max_pairs = sm_count() / 2;
-    const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
-    gemm_fp8_pair_kernel<<<grid, kQPThreads, kQPSmemBytes, st>>>(
-        ta, tb, a_s, b_s, static_cast<__nv_bfloat16*>(c), static_cast<int>(M), static_cast<int>(N),
-        static_cast<int>(K), ldc);
+    const int64_t num_qb = (queries * heads + 255) / 256;
+    const int64_t num_kt = (keys + 127) / 128;
+    const int64_t items = num_qb * ((num_kt + kIdxChunk - 1) / kIdxChunk);
+    const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
+    index_score_kernel<<<grid, kIdxThreads, kIdxSmemBytes, st>>>(
+        tk, tq, weights, k_scale, scores, static_cast<int>(queries), static_cast<int>(heads),
+        static_cast<int>(keys), ld, causal_offset);
     count_launch();
-    return check_launch("gemm_fp8_pair_kernel");
+    return check_launch("index_score_kernel");
 }
 
 static int launch_fp8(const void* a, const float* a_s, const void* b, const float* b_s, void* c,
@@ -1851,16 +1860,26 @@ extern "C" int rt_gemm_fp8(const void* a, const float* a_scales, const void* b,
                "rt_gemm_fp8: pointers must be 16-byte aligned");
     RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_fp8: dimension too large");
-    if (tc::g_fp8_schedule == 2)
-        return tc::launch_fp8_pair(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc,
-                                   as_stream(stream));
     return tc::launch_fp8(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc, as_stream(stream));
 }
 
-extern "C" int rt_gemm_fp8_schedule(int schedule) {
-    const int previous = tc::g_fp8_schedule;
-    if (schedule >= 0 && schedule <= 2) tc::g_fp8_schedule = schedule;
-    return previous;
+extern "C" int rt_fp8_index(const void* q, const float* weights, const void* k, const float* k_scale,
+                            float* scores, int64_t queries, int64_t heads, int64_t keys,
+                            int64_t dim, int64_t score_stride, int64_t causal_offset,
+                            void* stream) {
+    RT_REQUIRE(queries >= 0 && heads > 0 && keys > 0, RT_ERR_BAD_ARG, "rt_fp8_index: bad shape");
+    if (queries == 0) return RT_OK;
+    RT_REQUIRE(q && weights && k && k_scale && scores, RT_ERR_BAD_ARG, "rt_fp8_index: null pointer");
+    RT_REQUIRE(dim == 128, RT_ERR_UNSUPPORTED, "rt_fp8_index: the index head dimension must be 128");
+    RT_REQUIRE(heads % 16 == 0 && 128 % heads == 0, RT_ERR_UNSUPPORTED,
+               "rt_fp8_index: heads must be 16, 32, 64 or 128");
+    RT_REQUIRE(aligned16(q) && aligned16(k), RT_ERR_UNSUPPORTED,
+               "rt_fp8_index: q and k must be 16-byte aligned");
+    RT_REQUIRE(score_stride >= keys, RT_ERR_BAD_ARG, "rt_fp8_index: score stride below keys");
+    RT_REQUIRE(queries * heads < (1LL << 31) && keys < (1LL << 31), RT_ERR_UNSUPPORTED,
+               "rt_fp8_index: dimension too large");
+    return tc::launch_index_score(q, weights, k, k_scale, scores, queries, heads, keys, score_stride,
+                                  causal_offset, as_stream(stream));
 }
 
 extern "C" int rt_moe_tile_map(const int32_t* offsets, int64_t g_begin, int64_t g_end,

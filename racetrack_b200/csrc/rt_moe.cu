@@ -305,6 +305,97 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(
     }
 }
 
+
+// ---------------------------------------------------------------------------
+// Top-k selection of the sparse indexer: the k largest scores of every query row
+// ---------------------------------------------------------------------------
+// One CTA per row. fp32 scores become order-preserving 32-bit keys; four 8-bit radix passes
+// (shared-memory histograms, most significant digit first) find the k-th largest key exactly
+// and how many elements equal to it still belong to the selection; a last pass writes the
+// indices of all larger keys and of the first of the equal ones, in ascending index order
+// (ballot-based ordered compaction, 1024 elements per sweep).
+constexpr int kTopkThreads = 1024;
+
+__device__ __forceinline__ uint32_t order_key(float v) {
+    uint32_t u = __float_as_uint(v);
+    if (u == 0x80000000u) u = 0u;                           // -0.0 compares equal to +0.0
+    return (u & 0x80000000u) ? ~u : (u | 0x80000000u);      // larger float <=> larger key
+}
+
+__global__ void __launch_bounds__(kTopkThreads) index_topk_kernel(
+    const float* __restrict__ scores, int32_t* __restrict__ indices, int keys, int64_t ld,
+    int topk) {
+    __shared__ int hist[256];
+    __shared__ uint32_t s_prefix;
+    __shared__ int s_remaining;
+    __shared__ int warp_count[kTopkThreads / 32];
+    __shared__ int s_base, s_eq_base;
+    const float* row = scores + static_cast<int64_t>(blockIdx.x) * ld;
+    int32_t* out = indices + static_cast<int64_t>(blockIdx.x) * topk;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    if (tid == 0) {
+        s_prefix = 0u;
+        s_remaining = topk;          // elements still to take among those matching the prefix
+    }
+    __syncthreads();
+    for (int pass = 0; pass < 4; ++pass) {
+        const int shift = 24 - 8 * pass;
+        const uint32_t mask_hi = pass == 0 ? 0u : (0xffffffffu << (shift + 8));
+        if (tid < 256) hist[tid] = 0;
+        __syncthreads();
+        const uint32_t prefix = s_prefix;
+        for (int i = tid; i < keys; i += kTopkThreads) {
+            const uint32_t key = order_key(row[i]);
+            if ((key & mask_hi) == prefix) atomicAdd(&hist[(key >> shift) & 0xffu], 1);
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int remaining = s_remaining, bin = 255;
+            for (; bin > 0; --bin) {
+                if (hist[bin] >= remaining) break;
+                remaining -= hist[bin];
+            }
+            s_prefix = prefix | (static_cast<uint32_t>(bin) << shift);
+            s_remaining = remaining;
+        }
+        __syncthreads();
+    }
+    const uint32_t kth = s_prefix;       // key of the k-th largest element
+    const int take_eq = s_remaining;     // how many elements equal to it are selected
+    if (tid == 0) {
+        s_base = 0;
+        s_eq_base = 0;
+    }
+    __syncthreads();
+    for (int start = 0; start < keys; start += kTopkThreads) {
+        const int i = start + tid;
+        uint32_t key = 0u;
+        if (i < keys) key = order_key(row[i]);
+        const bool gt = i < keys && key > kth;
+        const bool eq = i < keys && key == kth;
+        // rank of this element among the equal ones of the row, in index order
+        const uint32_t eq_ballot = __ballot_sync(0xffffffffu, eq);
+        const int eq_before_in_warp = __popc(eq_ballot & ((1u << lane) - 1u));
+        if (lane == 0) warp_count[warp] = __popc(eq_ballot);
+        __syncthreads();
+        int eq_before = s_eq_base + eq_before_in_warp;
+        for (int w = 0; w < warp; ++w) eq_before += warp_count[w];
+        const bool sel = gt || (eq && eq_before < take_eq);
+        __syncthreads();
+        if (tid == kTopkThreads - 1) s_eq_base = eq_before + (eq ? 1 : 0);
+        const uint32_t sel_ballot = __ballot_sync(0xffffffffu, sel);
+        const int sel_before_in_warp = __popc(sel_ballot & ((1u << lane) - 1u));
+        if (lane == 0) warp_count[warp] = __popc(sel_ballot);
+        __syncthreads();
+        int pos = s_base + sel_before_in_warp;
+        for (int w = 0; w < warp; ++w) pos += warp_count[w];
+        if (sel && pos < topk) out[pos] = i;
+        __syncthreads();
+        if (tid == kTopkThreads - 1) s_base = pos + (sel ? 1 : 0);
+        __syncthreads();
+    }
+}
+
 }  // namespace rt
 
 using namespace rt;
@@ -492,6 +583,21 @@ extern "C" int rt_moe_permute_static(const int64_t* indices, int32_t* expert_off
         if (int rc = check_launch("moe_scatter_kernel")) return rc;
     }
     return RT_OK;
+}
+
+extern "C" int rt_index_topk(const float* scores, int32_t* indices, int64_t queries, int64_t keys,
+                             int64_t score_stride, int64_t topk, void* stream) {
+    RT_REQUIRE(queries >= 0 && keys > 0 && topk > 0, RT_ERR_BAD_ARG, "rt_index_topk: bad shape");
+    if (queries == 0) return RT_OK;
+    RT_REQUIRE(scores && indices, RT_ERR_BAD_ARG, "rt_index_topk: null pointer");
+    RT_REQUIRE(topk <= keys, RT_ERR_BAD_ARG, "rt_index_topk: topk (%lld) exceeds keys (%lld)",
+               (long long)topk, (long long)keys);
+    RT_REQUIRE(keys < (1LL << 31) && queries < (1LL << 31) && score_stride >= keys,
+               RT_ERR_UNSUPPORTED, "rt_index_topk: dimension too large or stride below keys");
+    index_topk_kernel<<<static_cast<unsigned>(queries), kTopkThreads, 0, as_stream(stream)>>>(
+        scores, indices, static_cast<int>(keys), score_stride, static_cast<int>(topk));
+    count_launch();
+    return check_launch("index_topk_kernel");
 }
 
 extern "C" int rt_moe_gather(const void* x, const int32_t* sorted_pairs, void* out,

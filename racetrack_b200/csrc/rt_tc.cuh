@@ -327,15 +327,6 @@ __device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t adesc, ui
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
-// e4m3 / e5m2 MMA over the pair: 256 x N x 32.
-__device__ __forceinline__ void mma_f8f6f4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
-                                                uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::f8f6f4 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
-        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
 // Block-scaled NVFP4 MMA over the pair: 256 x N x 64.
 __device__ __forceinline__ void mma_nvfp4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                                uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,

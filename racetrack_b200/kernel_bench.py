@@ -117,6 +117,9 @@ def cases(tokens: int) -> dict[str, tuple[Callable[[], object], int]]:
     off, sp, pp = ops.fused_moe_permute(idx, EXPERTS)
     out["fused_moe_gather"] = (lambda: ops.fused_moe_gather(u, sp, TOPK),
                                T * HIDDEN * 2 + T * TOPK * HIDDEN * 2)
+    sc = torch.randn(min(T, 2048), 4096, device="cuda")
+    out["index_topk[2048 of 4096]"] = (lambda: ops.index_topk(sc, 2048),
+                                       sc.numel() * 4 + sc.shape[0] * 2048 * 4)
     eo = _randn(T * TOPK, HIDDEN)
     wts = torch.rand(T, TOPK, device="cuda")
     out["fused_moe_combine"] = (lambda: ops.fused_moe_combine(eo, pp, wts, u),
@@ -142,15 +145,18 @@ def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, s
                 run_bf16, 2 * T * n * k, (T * k + n * k + T * n) * 2, "bf16")
         wc, ws = ops.quantize_weight_fp8(w)
         xc, xs = ops.fused_act_quant(x)
-        for sched, tag in ((2, "pair"), (1, "single")):
-            def run_fp8(xc=xc, xs=xs, wc=wc, ws=ws, sched=sched):
-                ops.gemm_fp8_schedule(sched)
-                try:
-                    return ops.linear_fp8(xc, xs, wc, ws)
-                finally:
-                    ops.gemm_fp8_schedule(0)
-            out[f"linear_fp8/{tag}[{name} {T}x{n}x{k}]"] = (
-                run_fp8, 2 * T * n * k, T * k + n * k + T * n * 2, "fp8")
+        out[f"linear_fp8[{name} {T}x{n}x{k}]"] = (
+            (lambda xc=xc, xs=xs, wc=wc, ws=ws: ops.linear_fp8(xc, xs, wc, ws)), 2 * T * n * k,
+            T * k + n * k + T * n * 2, "fp8")
+    # sparse indexer: index scores (64 heads x 128) of T queries over 4096 and T keys
+    for keys in sorted({4096, max(T, 128)}):
+        q = torch.randn(1, T, 64, 128, device="cuda").to(torch.float8_e4m3fn)
+        kk = torch.randn(1, keys, 128, device="cuda").to(torch.float8_e4m3fn)
+        wts = torch.randn(1, T, 64, device="cuda") * 0.01
+        ksc = torch.rand(1, keys, device="cuda") * 0.01
+        out[f"fp8_index[{T} queries x {keys} keys]"] = (
+            (lambda q=q, wts=wts, kk=kk, ksc=ksc: ops.fp8_index(q, wts, kk, ksc)),
+            2 * T * 64 * keys * 128, T * 64 * 128 + keys * 128 + T * keys * 4, "fp8")
     for name, n, k in (("w13", 4096, HIDDEN), ("w2", HIDDEN, 2048)):
         x, w = _randn(T, k), _randn(n, k)
         xq = ops.fused_nvfp4_quant(x, tiled_scales=True)

@@ -626,17 +626,57 @@ def gemm_nvfp4_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, a_gs: torch.Te
     return out
 
 
+def fp8_index(q: torch.Tensor, weights: torch.Tensor, k: torch.Tensor, k_scale: torch.Tensor, *,
+              causal_offset: Optional[int] = None) -> torch.Tensor:
+    """Index scores of the sparse-attention indexer (racetrack/models/deepseek.py:164-176):
+    scores[m, n] = k_scale[n] * sum_h weights[m, h] * relu(q[m, h, :] . k[n, :]).
+
+    q float8_e4m3fn [..., M, H, 128], weights fp32 [..., M, H], k float8_e4m3fn [..., N, 128],
+    k_scale fp32 [..., N]; leading dims must be 1 (one sequence). With causal_offset = c, keys
+    n > m + c get -inf (the mask the reference adds before top-k). Returns fp32 [..., M, N]."""
+    _require_cuda(q, weights, k, k_scale)
+    if q.dtype != torch.float8_e4m3fn or k.dtype != torch.float8_e4m3fn:
+        raise RuntimeError("fp8_index: q and k must be float8_e4m3fn")
+    m, h, d = q.shape[-3:]
+    n = k.shape[-2]
+    lead = q.shape[:-3]
+    if any(x != 1 for x in lead) or k.shape[:-2] != lead:
+        raise RuntimeError("fp8_index: one sequence at a time (leading dims of q and k must be 1)")
+    q2, k2 = q.reshape(m, h, d).contiguous(), k.reshape(n, d).contiguous()
+    w2 = weights.reshape(m, h).to(torch.float32).contiguous()
+    ks = k_scale.reshape(n).to(torch.float32).contiguous()
+    scores = torch.empty(m, n, dtype=torch.float32, device=q.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_fp8_index(q2.data_ptr(), w2.data_ptr(), k2.data_ptr(), ks.data_ptr(),
+                                scores.data_ptr(), m, h, n, d, scores.stride(0),
+                                -1 if causal_offset is None else int(causal_offset), _stream()),
+               "rt_fp8_index")
+    return scores.reshape(*lead, m, n)
+
+
+def index_topk(scores: torch.Tensor, topk: int) -> torch.Tensor:
+    """Indices (int32 [..., M, min(topk, N)], ascending) of the largest scores of every row
+    (racetrack/models/deepseek.py:683; the reference uses them as a set)."""
+    _require_cuda(scores)
+    if scores.dtype != torch.float32:
+        raise RuntimeError("index_topk: scores must be float32")
+    n = scores.shape[-1]
+    s2 = scores.reshape(-1, n)
+    if s2.stride(1) != 1:
+        s2 = s2.contiguous()
+    kk = min(int(topk), n)
+    out = torch.empty(s2.shape[0], kk, dtype=torch.int32, device=scores.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_index_topk(s2.data_ptr(), out.data_ptr(), s2.shape[0], n, s2.stride(0), kk,
+                                 _stream()), "rt_index_topk")
+    return out.reshape(*scores.shape[:-1], kk)
+
+
 def gemm_bf16_schedule(schedule: int) -> int:
     """Selects the schedule of the bf16 GEMM for this process (0 default = by size, 1 single-CTA
     128 x 256 tiles, 2 CTA pairs with 256 x 256 tiles where K % 64 == 0) and returns the
     previous setting."""
     return int(_lib.load().rt_gemm_bf16_schedule(int(schedule)))
-
-
-def gemm_fp8_schedule(schedule: int) -> int:
-    """Selects the schedule of the FP8 GEMM for this process (0 default = single-CTA 128 x 256
-    tiles, 1 the same, 2 CTA pairs with 256 x 256 tiles) and returns the previous setting."""
-    return int(_lib.load().rt_gemm_fp8_schedule(int(schedule)))
 
 
 def gemm_nvfp4_schedule(schedule: int) -> int:

@@ -158,6 +158,21 @@ def main() -> None:
     small["moe.out_cols0_256"] = y[:, :256].clone()
     hashes["moe.out"] = sha(y)
 
+    # ---- sparse indexer: fp8_index scores and the top-k selection (deepseek.py:164-176, 681-683)
+    for tag, queries, keys, topk in (("idx_small", 5, 300, 64), ("idx_decode", 16, 4096, 2048)):
+        d = I.indexer_inputs(queries, keys)
+        scores = rm.fp8_index(d["q"], d["weights"], d["k"], d["k_scale"])
+        if tag == "idx_small":
+            small["idx_small.scores"] = scores.clone()
+            small["idx_small.topk"] = scores.topk(topk, dim=-1)[1].sort(dim=-1)[0].to(torch.int32)
+        else:
+            # full decode width: the selected sets as a bit mask per query (512 bytes each)
+            sel = torch.zeros(1, queries, keys, dtype=torch.bool)
+            sel.scatter_(2, scores.topk(topk, dim=-1)[1], True)
+            small["idx_decode.kth_score"] = scores.topk(topk, dim=-1)[0][..., -1].clone()
+            small["idx_decode.score_sum_selected"] = (scores * sel).sum(-1)
+            hashes["idx_decode.selected_mask"] = sha(sel.to(torch.uint8))
+
     meta = {"torch": torch.__version__, "cpu_capability": torch.backends.cpu.get_cpu_capability(),
             "threads": torch.get_num_threads()}
     torch.save(small, HERE / "golden_small.pt")

@@ -95,14 +95,6 @@ def test_router_logits_fp32_output(ops, bf16_schedule, m):
 # FP8 block-scaled GEMM
 # ---------------------------------------------------------------------------
 
-@pytest.fixture(params=[1, 2], ids=["single_cta", "cta_pair"])
-def fp8_schedule(request, ops):
-    """Runs a test under both schedules of the FP8 GEMM and restores the default."""
-    previous = ops.gemm_fp8_schedule(request.param)
-    yield request.param
-    ops.gemm_fp8_schedule(previous)
-
-
 @pytest.mark.parametrize("m,n,k", [
     (128, 256, 128),       # one tile, one K block
     (128, 256, 1024),      # partial buffers alternate, stages wrap
@@ -113,7 +105,7 @@ def fp8_schedule(request, ops):
     (1024, 7168, 16384),   # w_o: 128 K blocks
     (300, 520, 384),       # three K blocks, tiles ragged in both directions
 ])
-def test_linear_fp8_block_scaled(ops, fp8_schedule, m, n, k):
+def test_linear_fp8_block_scaled(ops, m, n, k):
     from oracle import ref_ops as R
     x = I.randn((m, k), 500 + m).cuda()
     w = I.randn((n, k), 600 + n, std=0.05).cuda()

@@ -193,3 +193,41 @@ def test_sf_tiled_offsets_are_a_bijection():
     assert int(off.max()) == 2 * 2 * 512 - 1
     assert int(off[0, 1]) == 1 and int(off[1, 0]) == 16 and int(off[32, 0]) == 4
     assert int(off[128, 0]) == 2 * 512 and int(off[0, 4]) == 512
+
+
+def test_indexer_scores_and_topk_match_reference(golden_small, golden_hashes, same_cpu_as_golden):
+    """fp8_index and the top-k selection of the sparse indexer against racetrack's own
+    functions. The fp32 head and dimension sums may be ordered differently on another CPU, so
+    scores are compared to 1e-5 of the largest score and selections through the scores they
+    pick (a near-tie at the k-th place may legitimately swap two indices)."""
+    d = I.indexer_inputs(5, 300)
+    scores = R.fp8_index(d["q"], d["weights"], d["k"], d["k_scale"])
+    want = golden_small["idx_small.scores"]
+    tol = 1e-5 * float(want.abs().max())
+    assert float((scores - want).abs().max()) <= tol
+    got_idx = R.index_topk(scores, 64).sort(dim=-1)[0].to(torch.int32)
+    if same_cpu_as_golden:
+        assert_bit_exact(scores, want, "idx_small.scores")
+        assert_bit_exact(got_idx, golden_small["idx_small.topk"], "idx_small.topk")
+    picked = want.gather(2, got_idx.long()).sum(-1)
+    best = want.gather(2, golden_small["idx_small.topk"].long()).sum(-1)
+    assert float((picked - best).abs().max()) <= 64 * tol
+
+    d = I.indexer_inputs(16, 4096)
+    scores = R.fp8_index(d["q"], d["weights"], d["k"], d["k_scale"])
+    idx = R.index_topk(scores, I.INDEX_TOPK)
+    assert idx.shape == (1, 16, I.INDEX_TOPK)
+    kth = scores.gather(2, idx)[..., -1]
+    tol = 1e-5 * float(scores.abs().max())
+    assert float((kth - golden_small["idx_decode.kth_score"]).abs().max()) <= tol
+    sel = torch.zeros(1, 16, 4096, dtype=torch.bool)
+    sel.scatter_(2, idx, True)
+    assert int(sel.sum()) == 16 * I.INDEX_TOPK
+    ssum = (scores * sel).sum(-1)
+    assert float((ssum - golden_small["idx_decode.score_sum_selected"]).abs().max()) <= 2048 * tol
+    if same_cpu_as_golden:
+        assert sha(sel.to(torch.uint8)) == golden_hashes["sha256"]["idx_decode.selected_mask"]
+    # a causal mask removes later keys from the selection
+    mask = torch.full((16, 4096), float("-inf")).triu_(1 + 4096 - 16)
+    idx_m = R.index_topk(scores, I.INDEX_TOPK, mask)
+    assert int((idx_m[0, 0] > 4096 - 16).sum()) == 0
