@@ -1372,12 +1372,14 @@ __global__ void __launch_bounds__(kQThreads, 1) gemm_fp8_kernel(
 // consecutive keys' scores. One K block (128 e4m3) per MMA group, so each key tile costs one TMA
 // load; the query block (32 KB) is loaded once per work item and reused for a chunk of key tiles.
 // Work item = (query block, chunk of up to kIdxChunk key tiles); persistent CTAs.
-// Warps: 0 producer, 1 MMA issuer, 2-9 epilogue (lane quarter w % 4, column half (w - 2) / 4).
+// Warps: 0 producer, 1 MMA issuer, then EW epilogue warps (lane quarter w % 4, column slice
+// (w - 2) / 4 of 256 / (EW / 4) columns). EW = 16 (64 columns each: four warps per scheduler hide
+// the tensor-memory load latency, which 8 warps do not) whenever a query's heads fit into 64
+// columns, EW = 8 for 128 heads.
 // Barriers: kfull/kempty[4] (key tiles), qfull/qempty[2] (query blocks), pfull/pempty[2]
 // (accumulator buffers of 256 columns).
 constexpr int kIdxStages = 4;
 constexpr int kIdxChunk = 16;
-constexpr int kIdxThreads = 320;
 constexpr uint32_t kIdxKBytes = 128 * 128;
 constexpr uint32_t kIdxQBytes = 256 * 128;
 constexpr uint32_t kIdxQOffset = kIdxStages * kIdxKBytes;
@@ -1388,7 +1390,8 @@ constexpr uint32_t kIdxSmemBytes = kIdxBarOffset + kIdxBarriers * 8 + 16 + 1024;
 // fp32 accumulate, e4m3 x e4m3, K-major, N = 256, M = 128
 constexpr uint32_t kIdxIdesc = (1u << 4) | (32u << 17) | (8u << 24);
 
-__global__ void __launch_bounds__(kIdxThreads, 1) index_score_kernel(
+template <int EW>
+__global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
     const float* __restrict__ weights, const float* __restrict__ k_scale,
     float* __restrict__ scores, int queries, int heads, int keys, int64_t ld,
@@ -1426,7 +1429,7 @@ __global__ void __launch_bounds__(kIdxThreads, 1) index_score_kernel(
             mbar_init(qfull_bar(a), 1);
             mbar_init(qempty_bar(a), 1);
             mbar_init(pfull_bar(a), 1);
-            mbar_init(pempty_bar(a), 8);     // one arrival per epilogue warp
+            mbar_init(pempty_bar(a), EW);    // one arrival per epilogue warp
         }
         fence_mbar_init();
         tma_prefetch_desc(&tmap_k);
@@ -1508,10 +1511,11 @@ __global__ void __launch_bounds__(kIdxThreads, 1) index_score_kernel(
         }
         __syncwarp();
     } else {
+        constexpr int kCols = 256 / (EW / 4);   // accumulator columns per epilogue warp
         const int quad = warp & 3;
-        const int half = (warp - 2) >> 2;       // which 128 (query, head) columns of the tile
-        const int et = threadIdx.x - 64;        // 0..255 among the epilogue threads
-        const int q_per_half = 128 / heads;
+        const int slice = (warp - 2) >> 2;      // which kCols (query, head) columns of the tile
+        const int et = threadIdx.x - 64;        // index among the epilogue threads
+        const int q_per_slice = kCols / heads;
         int buf = 0, parity = 0;
         uint32_t buf_phase = 0;
         bool ok = true;
@@ -1519,11 +1523,13 @@ __global__ void __launch_bounds__(kIdxThreads, 1) index_score_kernel(
             const int qb = item / num_kc, kc = item % num_kc;
             // head weights of the block's 256 (query, head) rows; the named barrier also says
             // that every epilogue thread has left the item that used this half of wsm before
-            const int qrow = qb * 256 + et;
-            wsm[parity * 256 + et] = qrow < q_rows ? __ldg(weights + qrow) : 0.f;
-            asm volatile("bar.sync 1, 256;" ::: "memory");
-            const float* wv = wsm + parity * 256 + half * 128;
-            const int m0 = (qb * 256 + half * 128) / heads;     // first query of this half
+            if (et < 256) {
+                const int qrow = qb * 256 + et;
+                wsm[parity * 256 + et] = qrow < q_rows ? __ldg(weights + qrow) : 0.f;
+            }
+            asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
+            const float4* wv = reinterpret_cast<const float4*>(wsm + parity * 256 + slice * kCols);
+            const int m0 = (qb * 256 + slice * kCols) / heads;      // first query of this slice
             const int kt_end = min(num_kt, (kc + 1) * kIdxChunk);
             for (int kt = kc * kIdxChunk; kt < kt_end; ++kt) {
                 const int n = kt * 128 + quad * 32 + lane;
@@ -1531,34 +1537,43 @@ __global__ void __launch_bounds__(kIdxThreads, 1) index_score_kernel(
                 if (!(ok = mbar_wait(pfull_bar(buf), buf_phase, abort_flag, 56))) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
-                                       static_cast<uint32_t>(buf * 256 + half * 128);
-                float sums[8];
+                                       static_cast<uint32_t>(buf * 256 + slice * kCols);
+                float sums[kCols / 16];          // 16-column partial sums
 #pragma unroll
-                for (int j = 0; j < 8; ++j) sums[j] = 0.f;
+                for (int j = 0; j < kCols / 16; ++j) sums[j] = 0.f;
 #pragma unroll
-                for (int pairi = 0; pairi < 2; ++pairi) {
+                for (int pairi = 0; pairi < kCols / 64; ++pairi) {
                     uint32_t r0[32], r1[32];
                     tmem_ld_32x32(taddr + pairi * 64, r0);
                     tmem_ld_32x32(taddr + pairi * 64 + 32, r1);
                     tmem_ld_wait(r0);
                     tmem_ld_wait(r1);
-                    if (pairi == 1) {
-                        // every column of the buffer has been read: hand it back
+                    if (pairi == kCols / 64 - 1) {
+                        // every column of the slice has been read: hand the buffer back
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) mbar_arrive(pempty_bar(buf));
                     }
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) {
-                        const int c0 = pairi * 64 + i, c1 = c0 + 32;
-                        sums[c0 / 16] = fmaf(fmaxf(__uint_as_float(r0[i]), 0.f), wv[c0], sums[c0 / 16]);
-                        sums[c1 / 16] = fmaf(fmaxf(__uint_as_float(r1[i]), 0.f), wv[c1], sums[c1 / 16]);
+                    for (int i = 0; i < 32; i += 4) {
+                        const float4 w0 = wv[(pairi * 64 + i) >> 2];
+                        const float4 w1 = wv[(pairi * 64 + 32 + i) >> 2];
+                        float& s0 = sums[(pairi * 64 + i) / 16];
+                        float& s1 = sums[(pairi * 64 + 32 + i) / 16];
+                        s0 = fmaf(fmaxf(__uint_as_float(r0[i]), 0.f), w0.x, s0);
+                        s0 = fmaf(fmaxf(__uint_as_float(r0[i + 1]), 0.f), w0.y, s0);
+                        s0 = fmaf(fmaxf(__uint_as_float(r0[i + 2]), 0.f), w0.z, s0);
+                        s0 = fmaf(fmaxf(__uint_as_float(r0[i + 3]), 0.f), w0.w, s0);
+                        s1 = fmaf(fmaxf(__uint_as_float(r1[i]), 0.f), w1.x, s1);
+                        s1 = fmaf(fmaxf(__uint_as_float(r1[i + 1]), 0.f), w1.y, s1);
+                        s1 = fmaf(fmaxf(__uint_as_float(r1[i + 2]), 0.f), w1.z, s1);
+                        s1 = fmaf(fmaxf(__uint_as_float(r1[i + 3]), 0.f), w1.w, s1);
                     }
                 }
-                // sums[] holds 16-column partial sums; a query owns heads / 16 of them
+                // a query owns heads / 16 of the partial sums
                 if (n < keys) {
                     const int per_q = heads / 16;
-                    for (int j = 0; j < q_per_half; ++j) {
+                    for (int j = 0; j < q_per_slice; ++j) {
                         float s = 0.f;
                         for (int t = 0; t < per_q; ++t) s += sums[j * per_q + t];
                         const int m = m0 + j;
@@ -1735,9 +1750,13 @@ static int launch_index_score(const void* q, const float* weights, const void* k
         return rc;
     static bool attr_set = false;
     if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(index_score_kernel,
+        cudaError_t e = cudaFuncSetAttribute(index_score_kernel<16>,
                                              cudaFuncAttributeMaxDynamicSharedMemorySize,
                                              static_cast<int>(kIdxSmemBytes));
+        if (e == cudaSuccess)
+            e = cudaFuncSetAttribute(index_score_kernel<8>,
+                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                     static_cast<int>(kIdxSmemBytes));
         RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_fp8_index: %s", cudaGetErrorString(e));
         attr_set = true;
     }
@@ -1745,9 +1764,14 @@ static int launch_index_score(const void* q, const float* weights, const void* k
     const int64_t num_kt = (keys + 127) / 128;
     const int64_t items = num_qb * ((num_kt + kIdxChunk - 1) / kIdxChunk);
     const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
-    index_score_kernel<<<grid, kIdxThreads, kIdxSmemBytes, st>>>(
-        tk, tq, weights, k_scale, scores, static_cast<int>(queries), static_cast<int>(heads),
-        static_cast<int>(keys), ld, causal_offset);
+    if (heads <= 64)
+        index_score_kernel<16><<<grid, 64 + 32 * 16, kIdxSmemBytes, st>>>(
+            tk, tq, weights, k_scale, scores, static_cast<int>(queries), static_cast<int>(heads),
+            static_cast<int>(keys), ld, causal_offset);
+    else
+        index_score_kernel<8><<<grid, 64 + 32 * 8, kIdxSmemBytes, st>>>(
+            tk, tq, weights, k_scale, scores, static_cast<int>(queries), static_cast<int>(heads),
+            static_cast<int>(keys), ld, causal_offset);
     count_launch();
     return check_launch("index_score_kernel");
 }
