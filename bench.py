@@ -200,6 +200,15 @@ class PrefillStackWorkload:
         s = self.shape
         return 2 * (self.tokens * s.topk // self.world) * 2 * s.moe_inter * s.hidden
 
+    @property
+    def dominant_traffic(self):
+        """dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch, from a one-pass ncu
+        capture of this very configuration (profiles/gemm_nvfp4_pair_grouped_T8192_dram_traffic.md);
+        other sizes were not captured."""
+        if self.tokens == 8192 and self.world == 1 and self.shape.n_experts == 256:
+            return 4.82e9 + 0.60e9
+        return None
+
     def config(self) -> dict:
         s = self.shape
         return {"workload": self.name, "tokens": self.tokens, "layers": self.layers,
@@ -287,6 +296,139 @@ class PrefillStackWorkload:
 
 
 # ---------------------------------------------------------------------------
+# workload: routed MoE layer at T=4096 (sigmoid + bias grouped top-k gate, NVFP4 experts, one
+# bf16 shared expert)
+# ---------------------------------------------------------------------------
+
+class MoeLayerWorkload:
+    """One routed-MoE layer of DeepSeek-V3.2 (racetrack/models/deepseek.py:998-1022): gate
+    [256, 7168] with sigmoid scores + bias, 8 groups / top-4 groups / top-8 experts, route scale
+    2.5, NVFP4 experts (w13 [4096, 7168], w2 [7168, 2048]), one shared expert in bf16.
+    Experts are replicated work on N GPUs here (weak scaling: every rank runs its own tokens)."""
+    name = "dsv3_2_moe_layer_T4096"
+    metric = "dsv3_2_layer_tokens_per_s"
+    scaling = "weak"
+
+    def __init__(self, device, rank: int, world: int, args):
+        from racetrack_b200 import layer, moe, ops
+        self.ops, self.moe, self.rank, self.world = ops, moe, rank, world
+        self.tokens = args.tokens if args.tokens != 8192 else 4096
+        self.shape = s = layer.DSV32
+        ops.gemm_nvfp4_schedule({"auto": 0, "single": 1, "pair": 2}[args.nvfp4_schedule])
+        uses_pairs = args.nvfp4_schedule == "pair" or (
+            args.nvfp4_schedule == "auto" and self.tokens * s.topk >= 128 * s.n_experts)
+        self.dominant = ("gemm_nvfp4_pair_kernel" if uses_pairs else "gemm_nvfp4_kernel") + \
+            "[experts w13]"
+        self.experts = layer.make_nvfp4_experts(s, 0, 1, device, std=0.02)
+        self.kw = dict(n_experts=s.n_experts, n_groups=8, topk_groups=4, topk=s.topk,
+                       route_scale=2.5, score_func="sigmoid")
+        gen = torch.Generator(device=device)
+        gen.manual_seed(s.seed + 7 + rank)
+        self.x = torch.empty(self.tokens, s.hidden, device=device, dtype=torch.bfloat16)
+        self.x.normal_(mean=0.0, std=1.0, generator=gen)
+        self.w_gate = torch.empty(s.n_experts, s.hidden, device=device, dtype=torch.bfloat16)
+        self.w_gate.normal_(mean=0.0, std=0.02, generator=gen)
+        self.bias = torch.empty(s.n_experts, device=device, dtype=torch.float32)
+        self.bias.uniform_(-0.1, 0.1, generator=gen)
+        sw13, sw2 = layer.draw_expert(s, s.n_experts, device, std=0.02)     # the shared expert
+        self.sw13, self.sw2 = sw13.contiguous(), sw2.contiguous()
+        self.dom_events, self.recording = [], False
+        inner = ops.gemm_nvfp4_grouped
+        wl = self
+
+        def timed(*a, **kw):
+            if wl.recording and kw.get("n") == 2 * s.moe_inter:
+                e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                e0.record()
+                out = inner(*a, **kw)
+                e1.record()
+                wl.dom_events.append((e0, e1))
+                return out
+            return inner(*a, **kw)
+
+        ops.gemm_nvfp4_grouped = timed
+
+    @property
+    def units_per_step(self) -> int:
+        return self.tokens
+
+    @property
+    def dominant_bytes(self) -> int:
+        s = self.shape
+        pairs = self.tokens * s.topk
+        return (s.n_experts * 2 * s.moe_inter * s.hidden * 9 // 16 + pairs * s.hidden * 9 // 16
+                + pairs * 2 * s.moe_inter * 2)
+
+    @property
+    def dominant_flops(self) -> int:
+        s = self.shape
+        return 2 * self.tokens * s.topk * 2 * s.moe_inter * s.hidden
+
+    def config(self) -> dict:
+        s = self.shape
+        return {"workload": self.name, "tokens": self.tokens, "layers": 1, "hidden": s.hidden,
+                "experts": s.n_experts, "topk": s.topk, "moe_inter": s.moe_inter,
+                "experts_dtype": "nvfp4", "shared_expert": "bf16",
+                "routing": "sigmoid + bias, 8 groups, top-4 groups, top-8 (deepseek.py:888-920)",
+                "l2_policy": "inputs_exceed_l2 (6.3 GB of expert weights stream through the "
+                             "126 MB L2 every step)"}
+
+    def _run(self, x, record):
+        ops, s = self.ops, self.shape
+        self.recording = record
+        gate_up = ops.linear_bf16(x, self.sw13)
+        shared = ops.linear_bf16(ops.fused_swiglu(gate_up[:, :s.moe_inter], gate_up[:, s.moe_inter:]),
+                                 self.sw2)
+        out = self.moe.fused_moe_forward(x, self.w_gate, self.bias, self.experts, shared=shared,
+                                         **self.kw)
+        self.recording = False
+        return out
+
+    def step(self, record: bool = False):
+        return self._run(self.x, record)
+
+    def e2e_setup(self):
+        self.host_in = torch.empty(self.x.shape, dtype=torch.bfloat16, pin_memory=True)
+        self.host_in.copy_(self.x)
+        self.dev_in = torch.empty_like(self.x)
+        self.host_out = torch.empty(self.x.shape, dtype=torch.bfloat16, pin_memory=True)
+
+    def e2e_step(self):
+        self.dev_in.copy_(self.host_in, non_blocking=True)
+        out = self._run(self.dev_in, False)
+        self.host_out.copy_(out, non_blocking=True)
+        return out
+
+    def e2e_bytes(self):
+        n = self.host_in.numel() * self.host_in.element_size()
+        return n, n
+
+    @staticmethod
+    def cpu_runner(sample_tokens: int):
+        """racetrack's MoE.forward (oracle/ref_ops.moe_forward) on `sample_tokens` tokens at full
+        width, bf16 weights; only the experts the sample routes to are materialised."""
+        from oracle import inputs as I, ref_ops as R
+        from racetrack_b200 import layer
+        s = layer.DSV32
+        d = I.gate_inputs(sample_tokens)
+        kw = dict(n_groups=d["n_groups"], topk_groups=d["topk_groups"], topk=d["topk"],
+                  route_scale=d["route_scale"])
+        _, idx = R.gate_forward(d["hidden"], d["w_gate"], d["bias"], **kw)
+        experts = [None] * s.n_experts
+        inter = s.moe_inter
+
+        def split(w13, w2):
+            return w13[:inter], w2, w13[inter:]          # (w1, w2, w3)
+        for e in sorted(set(idx.flatten().tolist())):
+            experts[e] = split(*layer.draw_expert(s, e, "cpu", std=0.02))
+        shared = split(*layer.draw_expert(s, s.n_experts, "cpu", std=0.02))
+
+        def run():
+            return R.moe_forward(d["hidden"], d["w_gate"], d["bias"], experts, shared, **kw)
+        return run, sample_tokens
+
+
+# ---------------------------------------------------------------------------
 # workload: SwiGLU + activation quantisation at T=4096 (gate_up [T, 2*18432] bf16)
 # ---------------------------------------------------------------------------
 
@@ -368,7 +510,7 @@ class SwigluQuantWorkload:
         return run, sample_tokens
 
 
-WORKLOADS = {w.name: w for w in (PrefillStackWorkload, SwigluQuantWorkload)}
+WORKLOADS = {w.name: w for w in (PrefillStackWorkload, MoeLayerWorkload, SwigluQuantWorkload)}
 DEFAULT_WORKLOAD = PrefillStackWorkload.name
 
 
