@@ -115,6 +115,7 @@ class PrefillStackWorkload:
     metric = "dsv3_2_layer_tokens_per_s"
     scaling = "strong"
     dominant = "gemm_nvfp4_kernel[experts w13]"
+    ffn = "moe"          # "dense": the first-three-layers variant (SwiGLU FFN of width 18432)
 
     def __init__(self, device, rank: int, world: int, args):
         from racetrack_b200 import layer, moe, ops
@@ -122,8 +123,12 @@ class PrefillStackWorkload:
         self.device, self.rank, self.world = device, rank, world
         self.tokens, self.layers = args.tokens, args.layers
         self.shape = layer.DSV32
-        w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02)
-        w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
+        self.ffn = args.ffn
+        if self.ffn == "dense":
+            w = layer.make_weights(self.shape, rank, world, device, ffn="dense", std=0.02)
+        else:
+            w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02)
+            w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
         self.proj = args.proj
         self.schedule = args.nvfp4_schedule
         ops.gemm_nvfp4_schedule({"auto": 0, "single": 1, "pair": 2}[self.schedule])
@@ -132,7 +137,10 @@ class PrefillStackWorkload:
             self.schedule == "auto" and pairs_local >= 128 * (self.shape.n_experts // world))
         self.dominant = ("gemm_nvfp4_pair_kernel" if uses_pairs else "gemm_nvfp4_kernel") + \
             "[experts w13]"
-        self.model = layer.RealisticLayer(self.shape, w, rank, world, proj=args.proj)
+        if self.ffn == "dense":
+            fp8 = args.proj in ("fp8", "mixed")
+            self.dominant = ("gemm_fp8_kernel" if fp8 else "gemm_bf16_pair_kernel") + "[dense w13]"
+        self.model = layer.RealisticLayer(self.shape, w, rank, world, ffn=self.ffn, proj=args.proj)
         gen = torch.Generator(device=device)
         gen.manual_seed(self.shape.seed)
         self.hidden = torch.empty(self.tokens, self.shape.hidden, device=device, dtype=torch.bfloat16)
@@ -159,6 +167,24 @@ class PrefillStackWorkload:
 
         self.recording = False
         ops.gemm_nvfp4_grouped = timed
+        if self.ffn == "dense":
+            # the gate-up projection [2 * 18432 / world, 7168] of the dense FFN
+            rows13 = 2 * self.shape.dense_inter // self.world
+
+            def timed_linear(inner_fn, weight_arg):
+                def call(*a, **kw):
+                    if wl.recording and a[weight_arg].shape[0] == rows13:
+                        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        s.record()
+                        out = inner_fn(*a, **kw)
+                        e.record()
+                        wl.dom_events.append((s, e))
+                        return out
+                    return inner_fn(*a, **kw)
+                return call
+
+            ops.linear_fp8 = timed_linear(ops.linear_fp8, 2)      # (codes, scales, w_codes, w_scales)
+            ops.linear_bf16 = timed_linear(ops.linear_bf16, 1)    # (x, weight)
         # experts that actually receive tokens (their weights are what the GEMM reads)
         inner_permute = ops.fused_moe_permute
         self.touched = []
@@ -181,6 +207,10 @@ class PrefillStackWorkload:
     @property
     def dominant_bytes(self) -> int:
         s = self.shape
+        if self.ffn == "dense":
+            n = 2 * s.dense_inter // self.world
+            per = 1 if self.proj in ("fp8", "mixed") else 2
+            return per * (self.tokens * s.hidden + n * s.hidden) + self.tokens * n * 2
         e_loc = s.n_experts // self.world
         pairs_local = self.tokens * s.topk // self.world       # expected rows of this rank
         # experts that receive at least one token (all of them at prefill sizes; at decode
@@ -198,14 +228,24 @@ class PrefillStackWorkload:
     @property
     def dominant_flops(self) -> int:
         s = self.shape
+        if self.ffn == "dense":
+            return 2 * self.tokens * (2 * s.dense_inter // self.world) * s.hidden
         return 2 * (self.tokens * s.topk // self.world) * 2 * s.moe_inter * s.hidden
+
+    @property
+    def tensor_peak_factor(self) -> float:
+        """Tensor ceiling of the dominant kernel in units of the measured bf16 rate (the nominal
+        ratios of the part: e2m1 4 x, e4m3 2 x)."""
+        if self.ffn == "dense":
+            return 2.0 if self.proj in ("fp8", "mixed") else 1.0
+        return 4.0
 
     @property
     def dominant_traffic(self):
         """dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch, from a one-pass ncu
         capture of this very configuration (profiles/gemm_nvfp4_pair_grouped_T8192_dram_traffic.md);
         other sizes were not captured."""
-        if self.tokens == 8192 and self.world == 1 and self.shape.n_experts == 256:
+        if self.ffn == "moe" and self.tokens == 8192 and self.world == 1 and self.shape.n_experts == 256:
             return 4.82e9 + 0.60e9
         return None
 
@@ -213,7 +253,7 @@ class PrefillStackWorkload:
         s = self.shape
         return {"workload": self.name, "tokens": self.tokens, "layers": self.layers,
                 "hidden": s.hidden, "heads": s.heads, "experts": s.n_experts, "topk": s.topk,
-                "moe_inter": s.moe_inter, "experts_dtype": "nvfp4", "experts_gemm_schedule": self.schedule,
+                "moe_inter": s.moe_inter, "ffn": self.ffn, "experts_dtype": "nvfp4", "experts_gemm_schedule": self.schedule,
                 "projections_dtype": self.proj,
                 "attention_core": "torch sdpa (not a kernel of this backend)",
                 "routing": "topk_softmax (racetrack/realistic_bench.py:321-327)",
@@ -275,10 +315,16 @@ class PrefillStackWorkload:
         from oracle import ref_layer, ref_ops as R
         from racetrack_b200 import layer
         shape = layer.DSV32
-        w = layer.make_weights(shape, 0, 1, "cpu", ffn="none", std=0.02)
         g = torch.Generator().manual_seed(shape.seed)
         hidden = (torch.randn(sample_tokens, shape.hidden, generator=g) * 0.01).to(torch.bfloat16)
         pos = torch.arange(sample_tokens, dtype=torch.int64)
+        if PrefillStackWorkload.ffn == "dense":
+            wd = layer.make_weights(shape, 0, 1, "cpu", ffn="dense", std=0.02)
+
+            def run_dense():
+                return ref_layer.forward_stack(hidden, pos, [wd], shape, 1, ffn="dense")
+            return run_dense, sample_tokens * 1
+        w = layer.make_weights(shape, 0, 1, "cpu", ffn="none", std=0.02)
         ones = torch.ones(shape.hidden, dtype=torch.bfloat16)
         # routing of the sample decides which experts need weights
         h = R.rms_norm(hidden, ones, shape.eps)
@@ -659,11 +705,13 @@ def run_ours(args) -> None:
             # the kernel is a block-scaled e2m1 GEMM: its tensor ceiling is taken as 4 x the
             # measured bf16 cuBLAS throughput (the nominal e2m1 : bf16 ratio of the part); the
             # bound reported is whichever ideal time (bytes / HBM, flops / tensor) is longer
-            tensor_peak = 4.0 * bf16_peak
+            factor = float(getattr(wl, "tensor_peak_factor", 4.0))
+            tensor_peak = factor * bf16_peak
             tensor = {"bound": "tensor", "kernel": wl.dominant,
                       "achieved": flops / (dom_us * 1e-6) / 1e12, "peak": tensor_peak,
                       "unit": "TFLOP/s",
-                      "peak_note": "4 x measured sustained bf16 cuBLAS (e2m1 : bf16 nominal ratio)"}
+                      "peak_note": f"{factor:g} x measured sustained bf16 cuBLAS (nominal ratio "
+                                   "of the operand format to bf16)"}
             if flops / (tensor_peak * 1e12) > wl.dominant_bytes / (hbm_peak * 1e9):
                 roof, tensor = tensor, roof
             roof["other_bound"] = {k: tensor[k] for k in ("bound", "achieved", "peak", "unit")}
@@ -718,12 +766,16 @@ def main() -> None:
     ap.add_argument("--nvfp4-schedule", default="auto", choices=("auto", "pair", "single"),
                     help="schedule of the expert GEMMs: the library's choice by size, CTA pairs, "
                          "or single-CTA 128 x 128 tiles")
+    ap.add_argument("--ffn", default="moe", choices=("moe", "dense"),
+                    help="FFN of the layer: 256 routed NVFP4 experts, or the dense SwiGLU FFN of "
+                         "width 18432 that the first three layers of the model use")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graph", action="store_true",
                     help="capture the stack in a CUDA graph and replay it (decode sizes)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop")
     args = ap.parse_args()
+    PrefillStackWorkload.ffn = args.ffn          # the CPU legs draw the same variant
     if args.impl == "reference":
         run_reference(args)
     else:
