@@ -548,14 +548,9 @@ extern "C" int rt_moe_gather_nvfp4(const void* codes_in, const void* sf_in,
     const int64_t smem = 128 * ((cols >> 6) | 1) * 4;
     RT_REQUIRE(smem <= 200 * 1024, RT_ERR_UNSUPPORTED, "rt_moe_gather_nvfp4: cols too large");
     RT_REQUIRE(max_tiles < (1LL << 31), RT_ERR_UNSUPPORTED, "rt_moe_gather_nvfp4: too many tiles");
-    static int64_t attr_smem = 0;
-    if (smem > attr_smem) {
-        cudaError_t e = cudaFuncSetAttribute(moe_gather_nvfp4_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(smem));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_moe_gather_nvfp4: %s", cudaGetErrorString(e));
-        attr_smem = smem;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&moe_gather_nvfp4_kernel),
+                                     static_cast<int>(smem), "rt_moe_gather_nvfp4"))
+        return rc;
     moe_gather_nvfp4_kernel<<<static_cast<unsigned>(max_tiles), kGatherThreads, smem,
                               as_stream(stream)>>>(
         (const uint8_t*)codes_in, (const uint8_t*)sf_in, sorted_pairs, (int)topk,

@@ -3,6 +3,9 @@
 #include <atomic>
 #include <cstdarg>
 #include <cstdio>
+#include <map>
+#include <mutex>
+#include <utility>
 
 #include "rt_common.cuh"
 
@@ -28,6 +31,27 @@ int check_launch(const char* kernel_name) {
 }
 
 const char* last_error() { return g_error; }
+
+int ensure_dynamic_smem(const void* kernel, int bytes, const char* who) {
+    static std::mutex mu;
+    static std::map<std::pair<const void*, int>, int> granted;   // (kernel, device) -> bytes
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RT_ERR_CUDA, "%s: no current CUDA device", who);
+    }
+    std::lock_guard<std::mutex> lock(mu);
+    int& have = granted[std::make_pair(kernel, dev)];
+    if (have >= bytes) return RT_OK;
+    const cudaError_t e =
+        cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RT_ERR_CUDA, "%s: %s", who, cudaGetErrorString(e));
+    }
+    have = bytes;
+    return RT_OK;
+}
 
 }  // namespace rt
 

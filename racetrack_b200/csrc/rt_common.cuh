@@ -20,6 +20,9 @@ int fail(int code, const char* fmt, ...);
 void count_launch(int n = 1);
 // cudaGetLastError() after a launch; records the kernel name on failure.
 int check_launch(const char* kernel_name);
+// Opts `kernel` in to `bytes` of dynamic shared memory on the current device; the attribute is
+// per device and per kernel, so it is set once for each pair (thread-safe).
+int ensure_dynamic_smem(const void* kernel, int bytes, const char* who);
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

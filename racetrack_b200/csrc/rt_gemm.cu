@@ -1679,14 +1679,9 @@ static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t
         return rc;
     if (int rc = make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, K, N, ldb * 2, kBK, BN))
         return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_kernel<BN, F32OUT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(Cfg::kSmemBytes));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_bf16: %s", cudaGetErrorString(e));
-        attr_set = true;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_bf16_kernel<BN, F32OUT>),
+                                     static_cast<int>(Cfg::kSmemBytes), "rt_gemm_bf16"))
+        return rc;
     const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     gemm_bf16_kernel<BN, F32OUT><<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(
@@ -1722,14 +1717,9 @@ static int launch_bf16_pair(const void* a, const void* b, void* c, int64_t M, in
     CUtensorMap ta, tb;
     if (int rc = make_tmap_bf16_kblocks(&ta, a, M, K, lda * 2)) return rc;
     if (int rc = make_tmap_bf16_kblocks(&tb, b, N, K, ldb * 2)) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_bf16_pair_kernel<F32OUT>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kBPSmemBytes));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_bf16: %s", cudaGetErrorString(e));
-        attr_set = true;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_bf16_pair_kernel<F32OUT>),
+                                     static_cast<int>(kBPSmemBytes), "rt_gemm_bf16"))
+        return rc;
     const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
     const int64_t max_pairs = sm_count() / 2;
     const int grid = 2 * static_cast<int>(tiles < max_pairs ? tiles : max_pairs);
@@ -1748,18 +1738,12 @@ static int launch_index_score(const void* q, const float* weights, const void* k
     if (int rc = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, q, 128, queries * heads, 128, 128,
                               256))
         return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(index_score_kernel<16>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kIdxSmemBytes));
-        if (e == cudaSuccess)
-            e = cudaFuncSetAttribute(index_score_kernel<8>,
-                                     cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                     static_cast<int>(kIdxSmemBytes));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_fp8_index: %s", cudaGetErrorString(e));
-        attr_set = true;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&index_score_kernel<16>),
+                                     static_cast<int>(kIdxSmemBytes), "rt_fp8_index"))
+        return rc;
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&index_score_kernel<8>),
+                                     static_cast<int>(kIdxSmemBytes), "rt_fp8_index"))
+        return rc;
     const int64_t num_qb = (queries * heads + 255) / 256;
     const int64_t num_kt = (keys + 127) / 128;
     const int64_t items = num_qb * ((num_kt + kIdxChunk - 1) / kIdxChunk);
@@ -1782,14 +1766,9 @@ static int launch_fp8(const void* a, const float* a_s, const void* b, const floa
     CUtensorMap ta, tb;
     if (int rc = make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_UINT8, a, K, M, lda, kQBK, kBM)) return rc;
     if (int rc = make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, b, K, N, ldb, kQBK, kQBN)) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_fp8_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kQSmemBytes));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_fp8: %s", cudaGetErrorString(e));
-        attr_set = true;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_fp8_kernel),
+                                     static_cast<int>(kQSmemBytes), "rt_gemm_fp8"))
+        return rc;
     const int64_t tiles = ((M + kBM - 1) / kBM) * ((N + kQBN - 1) / kQBN);
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     gemm_fp8_kernel<<<grid, kQThreads, kQSmemBytes, st>>>(
@@ -1817,14 +1796,9 @@ static int launch_nvfp4_single(const void* a_codes, const void* a_sf, const floa
     if (int rc = make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_UINT8, b_codes, K / 2, groups * N, K / 2,
                               128, kFBN))
         return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kFSmemBytes));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_nvfp4_grouped: %s", cudaGetErrorString(e));
-        attr_set = true;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_nvfp4_kernel),
+                                     static_cast<int>(kFSmemBytes), "rt_gemm_nvfp4_grouped"))
+        return rc;
     const int64_t tiles = max_m_tiles * ((N + kFBN - 1) / kFBN);
     const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
     gemm_nvfp4_kernel<<<grid, kFThreads, kFSmemBytes, st>>>(
@@ -1846,14 +1820,9 @@ static int launch_nvfp4_pair(const void* a_codes, const void* a_sf, const float*
     for (int b = 0; b < 5; ++b) {
         if (int rc = make_tmap_kblocks(&tx.box[b], a_codes, total_rows, K / 2, K / 2, 8u << b, 2)) return rc;
     }
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_nvfp4_pair_kernel,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                             static_cast<int>(kPSmemBytes));
-        RT_REQUIRE(e == cudaSuccess, RT_ERR_CUDA, "rt_gemm_nvfp4_grouped: %s", cudaGetErrorString(e));
-        attr_set = true;
-    }
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_nvfp4_pair_kernel),
+                                     static_cast<int>(kPSmemBytes), "rt_gemm_nvfp4_grouped"))
+        return rc;
     // wide tiles: never more than 128-row tiles, so max_m_tiles bounds them as well
     const int64_t tiles = max_m_tiles * ((N + 255) / 256);
     const int64_t max_pairs = sm_count() / 2;
