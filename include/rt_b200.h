@@ -462,6 +462,27 @@ int rt_gemm_bf16_schedule(int schedule);
 int rt_gemm_nvfp4_schedule(int schedule);
 
 /*
+ * Indexer prologue, one pass per 128-wide row (an index head of a query, or a key):
+ *   [LayerNorm(weight, bias, eps) when ln_weight != NULL]  -> bf16
+ *   RoPE on the first 64 dims, non-interleaved pairs (i, i + 32), complex product with
+ *   freqs[position][i] (freqs: fp32 [table_rows, 32, 2] = view_as_real of freqs_cis)   -> bf16
+ *   Hadamard rotation x . H_128 * 128^-0.5 (Sylvester order, fp32 butterflies)          -> bf16
+ *   act_quant with one 128-wide group: codes e4m3 [rows, 128], scales fp32 [rows].
+ * The position of row r is positions[r / rows_per_position] (positions int64, may be NULL:
+ * then r / rows_per_position itself); rows_per_position = index heads for queries, 1 for keys.
+ * rotated (bf16 [rows, 128], may be NULL) receives the tensor that is quantised.
+ * dim == 128, rope_dim == 64.
+ * ref: racetrack/models/deepseek.py:659-676 (Indexer.forward: k_norm, apply_rotary_emb(...,
+ *      False), rotate_activation, act_quant), :508-520 (LayerNorm), :627-631 (rotate_activation:
+ *      fast_hadamard_transform, a third-party package racetrack does not vendor).
+ */
+int rt_index_prep(const void* x, const float* ln_weight, const float* ln_bias,
+                  const int64_t* positions, const float* freqs, int64_t table_rows,
+                  int64_t rows_per_position, void* codes, float* scales, void* rotated,
+                  int64_t rows, int64_t dim, int64_t rope_dim, int64_t x_stride, float eps,
+                  int dtype, void* stream);
+
+/*
  * Index scores of the sparse-attention indexer (tcgen05, FP8 x FP8, fp32 accumulate):
  *   scores[m, n] = k_scale[n] * sum_h weights[m, h] * relu(q[m, h, :] . k[n, :])
  * q e4m3 [queries, heads, dim], k e4m3 [keys, dim] (both contiguous), weights fp32 [queries,

@@ -162,6 +162,46 @@ def swiglu_quant(gate: torch.Tensor, up: torch.Tensor):
     return act_quant(swiglu(gate, up))
 
 
+def layer_norm(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor, eps: float = 1e-6) -> torch.Tensor:
+    """ref: racetrack/models/deepseek.py:508-520 (LayerNorm: fp32 F.layer_norm, cast back)."""
+    return F.layer_norm(x.float(), (x.shape[-1],), weight, bias, eps).type_as(x)
+
+
+def hadamard_matrix(n: int) -> torch.Tensor:
+    """Sylvester Hadamard matrix of order n (a power of two), entries +-1, natural ordering:
+    H[i, k] = (-1)^popcount(i & k)."""
+    h = torch.ones(1, 1)
+    while h.shape[0] < n:
+        h = torch.cat((torch.cat((h, h), 1), torch.cat((h, -h), 1)), 0)
+    return h
+
+
+def rotate_activation(x: torch.Tensor) -> torch.Tensor:
+    """x @ H_n * n^-0.5 in fp32, rounded to x's dtype.
+    ref: racetrack/models/deepseek.py:627-631, which calls hadamard_transform(x, scale) of the
+    third-party package fast_hadamard_transform (Dao-AILab, not vendored in racetrack and not
+    installed here: parity of this step is unpinned). Its documented contract is the product
+    with the Sylvester Hadamard matrix times `scale`, accumulated in fp32."""
+    n = x.shape[-1]
+    return ((x.float() @ hadamard_matrix(n)) * n ** -0.5).to(x.dtype)
+
+
+def index_prep(x: torch.Tensor, freqs_cis: torch.Tensor, *, rope_dim: int = 64,
+               ln_weight: Optional[torch.Tensor] = None, ln_bias: Optional[torch.Tensor] = None,
+               eps: float = 1e-6):
+    """The indexer's path from a projected row to FP8 (racetrack/models/deepseek.py:659-676):
+    (LayerNorm for keys) -> non-interleaved RoPE on the first rope_dim dims -> Hadamard rotation
+    -> act_quant. x [S, H, D] bf16 (H = 1 for keys), freqs_cis complex [S, rope_dim/2].
+    Returns (codes e4m3 [S, H, D], scales fp32 [S, H], rotated bf16 [S, H, D])."""
+    if ln_weight is not None:
+        x = layer_norm(x, ln_weight, ln_bias, eps)
+    pe, nope = torch.split(x, [rope_dim, x.shape[-1] - rope_dim], dim=-1)
+    pe = apply_rotary_emb(pe.unsqueeze(0).contiguous(), freqs_cis, False).squeeze(0)
+    rotated = rotate_activation(torch.cat([pe, nope], dim=-1))
+    codes, scales = act_quant(rotated)
+    return codes, scales.squeeze(-1), rotated
+
+
 def fp8_index(q: torch.Tensor, q_s: torch.Tensor, k: torch.Tensor, k_s: torch.Tensor) -> torch.Tensor:
     """Index scores of the sparse-attention indexer.
         score[b, m, n] = k_s[b, n] * sum_h q_s[b, m, h] * relu(q[b, m, h, :] . k[b, n, :])

@@ -50,6 +50,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_tc_error_state": (_I, []),
     "rt_moe_tile_map": (_I, [_P, _L, _L, _P, _P, _P, _L, _P]),
     "rt_gemm_nvfp4_schedule": (_I, [_I]),
+    "rt_index_prep": (_I, [_P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _L, _L, _L, _L, _F, _I, _P]),
     "rt_fp8_index": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
     "rt_index_topk": (_I, [_P, _P, _L, _L, _L, _L, _P]),
     "rt_gemm_bf16_schedule": (_I, [_I]),

@@ -134,6 +134,98 @@ __global__ void __launch_bounds__(kActThreads) quant_fp8_kernel(
 }
 
 // ---------------------------------------------------------------------------
+// Indexer prologue: (LayerNorm) -> non-interleaved RoPE -> Hadamard rotation -> FP8 quantisation
+// ---------------------------------------------------------------------------
+// One warp per 128-wide row (an index head of a query, or a key), lane l owning elements
+// 4l .. 4l + 3; every stage rounds to bf16 where the reference's op-by-op path does.
+//   LayerNorm (keys only): fp32 mean / biased variance, (x * rstd - rstd * mean) * w + b.
+//   RoPE on dims [0, 64), pairs (i, i + 32): complex product with freqs[pos][i] in fp32.
+//   Hadamard: fast Walsh-Hadamard transform in natural (Sylvester) order, two butterfly stages
+//   inside the lane and five across lanes, times 128^-0.5.
+//   act_quant: one 128-wide group per row: scale = max(amax, 1e-4) / 448, e4m3 codes.
+template <bool HAS_LN>
+__global__ void __launch_bounds__(256) index_prep_kernel(
+    const __nv_bfloat16* __restrict__ x, const float* __restrict__ ln_w,
+    const float* __restrict__ ln_b, const int64_t* __restrict__ positions,
+    const float2* __restrict__ freqs, int table_rows, int rows_per_pos,
+    uint8_t* __restrict__ codes, float* __restrict__ scales, __nv_bfloat16* __restrict__ rotated,
+    int64_t rows, int64_t xstride, float eps) {
+    const int lane = threadIdx.x & 31;
+    const int64_t row = static_cast<int64_t>(blockIdx.x) * 8 + (threadIdx.x >> 5);
+    if (row >= rows) return;
+    const uint2 raw = *reinterpret_cast<const uint2*>(x + row * xstride + 4 * lane);
+    float v[4];
+    v[0] = __uint_as_float(raw.x << 16);
+    v[1] = __uint_as_float(raw.x & 0xffff0000u);
+    v[2] = __uint_as_float(raw.y << 16);
+    v[3] = __uint_as_float(raw.y & 0xffff0000u);
+    if constexpr (HAS_LN) {
+        const float mean = warp_sum((v[0] + v[1]) + (v[2] + v[3])) * (1.0f / 128.0f);
+        float d[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) d[j] = v[j] - mean;
+        const float var = warp_sum((d[0] * d[0] + d[1] * d[1]) + (d[2] * d[2] + d[3] * d[3])) *
+                          (1.0f / 128.0f);
+        const float rstd = __fdiv_rn(1.0f, __fsqrt_rn(var + eps));
+        const float shift = -(rstd * mean);
+        const float4 w = *reinterpret_cast<const float4*>(ln_w + 4 * lane);
+        const float4 b = *reinterpret_cast<const float4*>(ln_b + 4 * lane);
+        v[0] = round_bf16((v[0] * rstd + shift) * w.x + b.x);
+        v[1] = round_bf16((v[1] * rstd + shift) * w.y + b.y);
+        v[2] = round_bf16((v[2] * rstd + shift) * w.z + b.z);
+        v[3] = round_bf16((v[3] * rstd + shift) * w.w + b.w);
+    }
+    // RoPE: lanes 0-7 hold dims 0-31 (real parts), lanes 8-15 dims 32-63 (imaginary parts)
+    {
+        int64_t pos = positions ? positions[row / rows_per_pos] : row / rows_per_pos;
+        if (pos >= table_rows) pos = table_rows - 1;
+        float other[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) other[j] = __shfl_xor_sync(0xffffffffu, v[j], 8);
+        if (lane < 16) {
+            const float2* f = freqs + pos * 32 + 4 * (lane & 7);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 cs = f[j];
+                const float re = lane < 8 ? v[j] : other[j];
+                const float im = lane < 8 ? other[j] : v[j];
+                const float out = lane < 8 ? (re * cs.x - im * cs.y) : (re * cs.y + im * cs.x);
+                v[j] = round_bf16(out);
+            }
+        }
+    }
+    // Hadamard rotation
+    {
+        float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];
+        v[0] = a + c; v[1] = b + d; v[2] = a - c; v[3] = b - d;
+#pragma unroll
+        for (int m = 1; m < 32; m <<= 1) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float p = __shfl_xor_sync(0xffffffffu, v[j], m);
+                v[j] = (lane & m) ? (p - v[j]) : (v[j] + p);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) v[j] = round_bf16(v[j] * 0.08838834764831845f);
+    }
+    if (rotated) {
+        uint2 o;
+        o.x = pack_bf16x2(v[0], v[1]);
+        o.y = pack_bf16x2(v[2], v[3]);
+        *reinterpret_cast<uint2*>(rotated + row * 128 + 4 * lane) = o;
+    }
+    float amax = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    amax = fmaxf(warp_max(amax), 1.0e-4f);
+    const float scale = __fdiv_rn(amax, 448.0f);
+    const float rscale = __frcp_rn(scale);
+    const uint32_t packed = cvt_e4m3x2(div_shared(v[0], scale, rscale), div_shared(v[1], scale, rscale)) |
+                            (cvt_e4m3x2(div_shared(v[2], scale, rscale), div_shared(v[3], scale, rscale)) << 16);
+    *reinterpret_cast<uint32_t*>(codes + row * 128 + 4 * lane) = packed;
+    if (lane == 0) scales[row] = scale;
+}
+
+// ---------------------------------------------------------------------------
 // Tensor-wide abs-max (NVFP4 global scale)
 // ---------------------------------------------------------------------------
 __global__ void absmax_clear_kernel(float* out) { *out = 0.f; }
@@ -557,6 +649,44 @@ extern "C" int rt_moe_gather_nvfp4(const void* codes_in, const void* sf_in,
         (uint8_t*)codes_out, (uint8_t*)sf_out, (const int4*)tile_map, tile_count, cols);
     count_launch();
     return check_launch("moe_gather_nvfp4_kernel");
+}
+
+extern "C" int rt_index_prep(const void* x, const float* ln_weight, const float* ln_bias,
+                             const int64_t* positions, const float* freqs, int64_t table_rows,
+                             int64_t rows_per_position, void* codes, float* scales, void* rotated,
+                             int64_t rows, int64_t dim, int64_t rope_dim, int64_t x_stride,
+                             float eps, int dtype, void* stream) {
+    RT_REQUIRE(rows >= 0 && rows_per_position > 0 && table_rows > 0, RT_ERR_BAD_ARG,
+               "rt_index_prep: bad shape");
+    if (rows == 0) return RT_OK;
+    RT_REQUIRE(x && freqs && codes && scales, RT_ERR_BAD_ARG, "rt_index_prep: null pointer");
+    RT_REQUIRE((ln_weight == nullptr) == (ln_bias == nullptr), RT_ERR_BAD_ARG,
+               "rt_index_prep: LayerNorm weight and bias come together");
+    RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_index_prep: only bf16 activations");
+    RT_REQUIRE(dim == 128 && rope_dim == 64, RT_ERR_UNSUPPORTED,
+               "rt_index_prep: index head dimension 128 with a 64-wide rope slice only");
+    RT_REQUIRE(x_stride % 4 == 0 && (reinterpret_cast<uintptr_t>(x) & 7u) == 0 &&
+                   (reinterpret_cast<uintptr_t>(codes) & 3u) == 0 &&
+                   (!rotated || (reinterpret_cast<uintptr_t>(rotated) & 7u) == 0) &&
+                   (!ln_weight || (aligned16(ln_weight) && aligned16(ln_bias))) &&
+                   (reinterpret_cast<uintptr_t>(freqs) & 7u) == 0,
+               RT_ERR_UNSUPPORTED, "rt_index_prep: alignment (8-byte rows, stride %% 4 == 0)");
+    RT_REQUIRE(rows < (1LL << 34) && table_rows < (1LL << 31), RT_ERR_UNSUPPORTED,
+               "rt_index_prep: tensor too large");
+    const unsigned grid = static_cast<unsigned>((rows + 7) / 8);
+    cudaStream_t st = as_stream(stream);
+    if (ln_weight)
+        index_prep_kernel<true><<<grid, 256, 0, st>>>(
+            (const __nv_bfloat16*)x, ln_weight, ln_bias, positions, (const float2*)freqs,
+            (int)table_rows, (int)rows_per_position, (uint8_t*)codes, scales,
+            (__nv_bfloat16*)rotated, rows, x_stride, eps);
+    else
+        index_prep_kernel<false><<<grid, 256, 0, st>>>(
+            (const __nv_bfloat16*)x, nullptr, nullptr, positions, (const float2*)freqs,
+            (int)table_rows, (int)rows_per_position, (uint8_t*)codes, scales,
+            (__nv_bfloat16*)rotated, rows, x_stride, eps);
+    count_launch();
+    return check_launch("index_prep_kernel");
 }
 
 extern "C" int rt_nvfp4_quant(const void* x, const void* up, const float* amax_in, void* codes,

@@ -626,6 +626,44 @@ def gemm_nvfp4_grouped(a_codes: torch.Tensor, a_sf: torch.Tensor, a_gs: torch.Te
     return out
 
 
+def index_prep(x: torch.Tensor, freqs_cis: torch.Tensor, *, positions: Optional[torch.Tensor] = None,
+               ln_weight: Optional[torch.Tensor] = None, ln_bias: Optional[torch.Tensor] = None,
+               eps: float = 1e-6, return_rotated: bool = False):
+    """The indexer's path from projected rows to FP8 in one pass (racetrack/models/deepseek.py:
+    659-676): [LayerNorm for keys] -> non-interleaved RoPE on the first 64 dims -> Hadamard
+    rotation -> act_quant.
+
+    x bf16 [S, H, 128] (H = 1 for keys); freqs_cis complex64 [table, 32]; positions int64 [S]
+    (default 0..S-1). Returns (codes float8_e4m3fn [S, H, 128], scales fp32 [S, H]) and, on
+    request, the rotated bf16 tensor that was quantised."""
+    _require_cuda(x, freqs_cis)
+    _require_bf16("index_prep", x)
+    if x.dim() != 3 or x.shape[-1] != 128:
+        raise RuntimeError("index_prep: x must be [S, H, 128]")
+    s_len, heads, dim = x.shape
+    x2 = x.reshape(s_len * heads, dim)
+    if x2.stride(1) != 1:
+        x2 = x2.contiguous()
+    fr = torch.view_as_real(freqs_cis).to(torch.float32).contiguous()
+    if fr.shape[-2:] != (32, 2):
+        raise RuntimeError("index_prep: freqs_cis must be [table, 32] complex")
+    codes = torch.empty(s_len, heads, dim, dtype=torch.float8_e4m3fn, device=x.device)
+    scales = torch.empty(s_len, heads, dtype=torch.float32, device=x.device)
+    rotated = torch.empty(s_len, heads, dim, dtype=torch.bfloat16, device=x.device) \
+        if return_rotated else None
+    lw = ln_weight.to(torch.float32).contiguous() if ln_weight is not None else None
+    lb = ln_bias.to(torch.float32).contiguous() if ln_bias is not None else None
+    pos = positions.to(torch.int64).contiguous() if positions is not None else None
+    lib = _lib.load()
+    _lib.check(lib.rt_index_prep(
+        x2.data_ptr(), lw.data_ptr() if lw is not None else None,
+        lb.data_ptr() if lb is not None else None, pos.data_ptr() if pos is not None else None,
+        fr.data_ptr(), fr.shape[0], heads, codes.data_ptr(), scales.data_ptr(),
+        rotated.data_ptr() if rotated is not None else None, s_len * heads, dim, 64,
+        x2.stride(0), float(eps), _lib.RT_BF16, _stream()), "rt_index_prep")
+    return (codes, scales, rotated) if return_rotated else (codes, scales)
+
+
 def fp8_index(q: torch.Tensor, weights: torch.Tensor, k: torch.Tensor, k_scale: torch.Tensor, *,
               causal_offset: Optional[int] = None) -> torch.Tensor:
     """Index scores of the sparse-attention indexer (racetrack/models/deepseek.py:164-176):

@@ -173,6 +173,18 @@ def main() -> None:
             small["idx_decode.score_sum_selected"] = (scores * sel).sum(-1)
             hashes["idx_decode.selected_mask"] = sha(sel.to(torch.uint8))
 
+    # ---- indexer prologue of the key path: LayerNorm + non-interleaved RoPE (deepseek.py:665-670)
+    k_in = I.randn((9, 1, 128), I.SEED + 710)
+    ln = rm.LayerNorm(128)
+    with torch.no_grad():
+        ln.weight.copy_(I.randn((128,), I.SEED + 711, mean=1.0, std=0.02, dtype=torch.float32))
+        ln.bias.copy_(I.randn((128,), I.SEED + 712, std=0.02, dtype=torch.float32))
+        k_ln = ln(k_in)
+        k_pe, k_nope = torch.split(k_ln, [64, 64], dim=-1)
+        fc = rm.precompute_freqs_cis(rm.ModelArgs())[:9]
+        k_pe = rm.apply_rotary_emb(k_pe.unsqueeze(0), fc, False).squeeze(0)
+    small["idxprep.k_ln_rope"] = torch.cat([k_pe, k_nope], dim=-1).clone()
+
     meta = {"torch": torch.__version__, "cpu_capability": torch.backends.cpu.get_cpu_capability(),
             "threads": torch.get_num_threads()}
     torch.save(small, HERE / "golden_small.pt")

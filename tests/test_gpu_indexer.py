@@ -22,6 +22,16 @@ def _cuda(d):
     return {k: v.cuda() for k, v in d.items()}
 
 
+def _close_rotated(got, want, what, max_frac=2e-2):
+    """One bf16 ulp, with an absolute floor: a Hadamard output is a sum of 128 terms of either
+    sign, so next to zero the fp32 summation order alone moves it by more than its own ulp."""
+    g, w = got.detach().float().cpu(), want.detach().float().cpu()
+    bad = (g - w).abs() > 2.0 ** -7 * w.abs() + 1e-5
+    assert not bool(bad.any()), f"{what}: {int(bad.sum())} elements off, worst {float((g - w).abs().max())}"
+    frac = float((got.detach().cpu().view(torch.int16) != want.view(torch.int16)).float().mean())
+    assert frac <= max_frac, f"{what}: {frac:.2e} of the elements differ"
+
+
 @pytest.mark.parametrize("queries,keys,heads", [
     (5, 300, 64),          # ragged everywhere: 1.25 query blocks, 2.3 key tiles
     (1, 4096, 64),         # one decode query over a 4096-key cache
@@ -125,3 +135,48 @@ def test_indexer_end_to_end_matches_reference_selection(ops, golden_small):
     assert float((picked - golden_small["idx_decode.score_sum_selected"]).abs().max()) <= 2048 * tol
     kth = ref.gather(2, idx.cpu().long()).min(-1)[0]
     assert float((kth - golden_small["idx_decode.kth_score"]).abs().max()) <= tol
+
+
+@pytest.mark.parametrize("rows,heads,with_ln", [(9, 1, True), (300, 1, True), (5, 64, False),
+                                                (130, 64, False)])
+def test_index_prep_matches_reference_chain(ops, rows, heads, with_ln):
+    """[LayerNorm] -> non-interleaved RoPE -> Hadamard rotation -> act_quant in one kernel: the
+    rotated tensor agrees with the op-by-op reference to one bf16 ulp (fp32 sums are ordered
+    differently), and codes / scales are exactly act_quant of the kernel's own rotated tensor."""
+    from helpers import assert_bit_exact
+    x = I.randn((rows, heads, 128), 40 + rows)
+    w = I.randn((128,), 41, mean=1.0, std=0.02, dtype=torch.float32) if with_ln else None
+    b = I.randn((128,), 42, std=0.02, dtype=torch.float32) if with_ln else None
+    table = R.precompute_freqs_cis(64, 16384)
+    pos = (torch.arange(rows) * 37) % 5000            # arbitrary positions inside the table
+    codes, scales, rotated = ops.index_prep(
+        x.cuda(), table.cuda(), positions=pos.cuda(), ln_weight=w.cuda() if with_ln else None,
+        ln_bias=b.cuda() if with_ln else None, return_rotated=True)
+    ref_codes, ref_scales, ref_rot = R.index_prep(x, table[pos], ln_weight=w, ln_bias=b)
+    _close_rotated(rotated, ref_rot, "rotated")
+    c2, s2 = ops.fused_act_quant(rotated.reshape(rows * heads, 128))
+    assert_bit_exact(codes.reshape(rows * heads, 128), c2, "codes")
+    assert_bit_exact(scales.reshape(rows * heads, 1), s2, "scales")
+    # where the rotated rows agree exactly, so do the quantised ones
+    same = (rotated.cpu().view(torch.int16) == ref_rot.view(torch.int16)).all(dim=-1)
+    assert float(same.float().mean()) >= 0.3
+    assert torch.equal(codes.cpu().view(torch.uint8)[same], ref_codes.view(torch.uint8)[same])
+    assert torch.equal(scales.cpu()[same], ref_scales[same])
+
+
+def test_index_prep_default_positions_and_golden(ops, golden_small):
+    """Keys at positions 0..8 with LayerNorm: the stage before the rotation is pinned by
+    racetrack's own LayerNorm + apply_rotary_emb (fixture), the rotation by its definition."""
+    k_in = I.randn((9, 1, 128), I.SEED + 710)
+    w = I.randn((128,), I.SEED + 711, mean=1.0, std=0.02, dtype=torch.float32)
+    b = I.randn((128,), I.SEED + 712, std=0.02, dtype=torch.float32)
+    table = R.precompute_freqs_cis(64, 16384)
+    _, _, rotated = ops.index_prep(k_in.cuda(), table.cuda(), ln_weight=w.cuda(), ln_bias=b.cuda(),
+                                   return_rotated=True)
+    want = R.rotate_activation(golden_small["idxprep.k_ln_rope"])
+    _close_rotated(rotated, want, "rotated keys")
+    # the rotation is an involution: rotating the result again returns its input, up to the
+    # bf16 rounding of the intermediate
+    back = R.rotate_activation(rotated.cpu()).float()
+    src = golden_small["idxprep.k_ln_rope"].float()
+    assert float((back - src).abs().max()) <= 0.05 * float(src.abs().max())

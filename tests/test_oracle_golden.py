@@ -231,3 +231,35 @@ def test_indexer_scores_and_topk_match_reference(golden_small, golden_hashes, sa
     mask = torch.full((16, 4096), float("-inf")).triu_(1 + 4096 - 16)
     idx_m = R.index_topk(scores, I.INDEX_TOPK, mask)
     assert int((idx_m[0, 0] > 4096 - 16).sum()) == 0
+
+
+def test_indexer_key_prologue_matches_reference(golden_small, same_cpu_as_golden):
+    """LayerNorm + non-interleaved RoPE of the indexer's key path against racetrack's own
+    LayerNorm / apply_rotary_emb; the Hadamard rotation that follows comes from a package
+    racetrack does not vendor, so it is only checked against its definition."""
+    k_in = I.randn((9, 1, 128), I.SEED + 710)
+    w = I.randn((128,), I.SEED + 711, mean=1.0, std=0.02, dtype=torch.float32)
+    b = I.randn((128,), I.SEED + 712, std=0.02, dtype=torch.float32)
+    k_ln = R.layer_norm(k_in, w, b)
+    pe, nope = torch.split(k_ln, [64, 64], dim=-1)
+    fc = R.precompute_freqs_cis(64, 16384)[:9]     # ModelArgs(): max_seq_len 16384 (YaRN on)
+    got = torch.cat([R.apply_rotary_emb(pe.unsqueeze(0), fc, False).squeeze(0), nope], dim=-1)
+    if same_cpu_as_golden:
+        assert_bit_exact(got, golden_small["idxprep.k_ln_rope"], "idxprep.k_ln_rope")
+    else:
+        assert_close_bf16(got, golden_small["idxprep.k_ln_rope"], "idxprep.k_ln_rope", ulps=1)
+    # the rotation: orthonormal, an involution, and equal to the butterfly network
+    h = R.hadamard_matrix(128)
+    assert torch.equal(h @ h.t(), 128 * torch.eye(128))
+    x = I.randn((5, 128), 3).float()
+    y = x.clone().view(5, 128)
+    step = 1
+    while step < 128:                       # fast Walsh-Hadamard transform, natural order
+        y = y.view(5, -1, 2, step)
+        y = torch.cat((y[:, :, 0] + y[:, :, 1], y[:, :, 0] - y[:, :, 1]), dim=-1).view(5, 128)
+        step *= 2
+    torch.testing.assert_close(y, x @ h, rtol=1e-5, atol=1e-4)
+    codes, scales, rotated = R.index_prep(k_in, fc, ln_weight=w, ln_bias=b)
+    assert codes.shape == (9, 1, 128) and scales.shape == (9, 1)
+    c2, s2 = R.act_quant(rotated)
+    assert torch.equal(codes.view(torch.uint8), c2.view(torch.uint8)) and torch.equal(scales, s2.squeeze(-1))
