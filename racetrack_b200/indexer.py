@@ -1,0 +1,58 @@
+"""The DeepSeek-V3.2 sparse-attention indexer on the B200 kernels.
+
+Counterpart of `Indexer.forward` (racetrack/models/deepseek.py:656-686): which `index_topk`
+cached keys each query attends to. The two projections are bf16 GEMMs, everything between them
+and the scores is one fused kernel per operand (ops.index_prep), the scores come from the
+tensor cores (ops.fp8_index) and the selection is an exact radix select (ops.index_topk).
+Nothing reads device data back to the host.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from . import ops
+
+
+@dataclass
+class IndexerWeights:
+    """wq_b [heads * 128, q_lora] bf16, wk [128, dim] bf16, k_norm weight / bias fp32 [128],
+    weights_proj [heads, dim] fp32 (racetrack/models/deepseek.py:644-648)."""
+    wq_b: torch.Tensor
+    wk: torch.Tensor
+    k_norm_weight: torch.Tensor
+    k_norm_bias: torch.Tensor
+    weights_proj: torch.Tensor
+    heads: int = 64
+    head_dim: int = 128
+
+
+def indexer_forward(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cache: torch.Tensor,
+                    k_scale_cache: torch.Tensor, start_pos: int, freqs_cis: torch.Tensor,
+                    index_topk: int, *, causal: bool = True,
+                    positions: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """x [S, dim] and qr [S, q_lora] bf16 (one sequence); k_cache float8_e4m3fn [max_len, 128]
+    and k_scale_cache fp32 [max_len] are updated in place at [start_pos, start_pos + S).
+    freqs_cis complex64 [table, 32] for the whole position range. Returns int32
+    [S, min(index_topk, start_pos + S)], ascending: the cached positions query s may attend to
+    (with `causal`, only positions <= start_pos + s compete, as with the reference's mask)."""
+    s_len = x.shape[0]
+    end_pos = start_pos + s_len
+    if positions is None:
+        positions = torch.arange(start_pos, end_pos, device=x.device, dtype=torch.int64)
+    q = ops.linear_bf16(qr, w.wq_b).view(s_len, w.heads, w.head_dim)
+    q_fp8, q_scale = ops.index_prep(q, freqs_cis, positions=positions)
+    k = ops.linear_bf16(x, w.wk).view(s_len, 1, w.head_dim)
+    k_fp8, k_scale = ops.index_prep(k, freqs_cis, positions=positions,
+                                    ln_weight=w.k_norm_weight, ln_bias=w.k_norm_bias)
+    k_cache[start_pos:end_pos] = k_fp8.view(s_len, w.head_dim)
+    k_scale_cache[start_pos:end_pos] = k_scale.view(s_len)
+    # per-head weights in fp32, as the reference forms them (deepseek.py:677-678)
+    head_w = torch.nn.functional.linear(x.float(), w.weights_proj) * w.heads ** -0.5
+    head_w = head_w * q_scale * w.head_dim ** -0.5
+    scores = ops.fp8_index(q_fp8.unsqueeze(0), head_w.unsqueeze(0), k_cache[:end_pos].unsqueeze(0),
+                           k_scale_cache[:end_pos].unsqueeze(0),
+                           causal_offset=start_pos if causal else None)
+    return ops.index_topk(scores[0], index_topk)

@@ -180,3 +180,59 @@ def test_index_prep_default_positions_and_golden(ops, golden_small):
     back = R.rotate_activation(rotated.cpu()).float()
     src = golden_small["idxprep.k_ln_rope"].float()
     assert float((back - src).abs().max()) <= 0.05 * float(src.abs().max())
+
+
+def test_indexer_forward_selects_like_the_reference_chain():
+    """The whole indexer (projections, prologues, cache update, scores, top-k) for a prefill of
+    300 tokens followed by a decode step, against the reference's op sequence on the CPU. The
+    selection is compared through the reference scores it picks (a near-tie may swap two
+    indices), the cache contents row by row where the rotated keys agree bit for bit."""
+    from racetrack_b200 import indexer, ops
+    dim, q_lora, heads, topk = 1024, 256, 64, 128
+    prefill, max_len = 300, 512
+    g = torch.Generator().manual_seed(77)
+    mk = lambda *s, std=1.0: (torch.randn(*s, generator=g) * std)
+    wq_b, wk = mk(heads * 128, q_lora, std=0.06).bfloat16(), mk(128, dim, std=0.03).bfloat16()
+    lnw, lnb = 1 + mk(128, std=0.02), mk(128, std=0.02)
+    wproj = mk(heads, dim, std=0.03)
+    table = R.precompute_freqs_cis(64, 16384)
+    w = indexer.IndexerWeights(wq_b.cuda(), wk.cuda(), lnw.cuda(), lnb.cuda(), wproj.cuda())
+    k_cache = torch.zeros(max_len, 128, dtype=torch.float8_e4m3fn, device="cuda")
+    ks_cache = torch.zeros(max_len, dtype=torch.float32, device="cuda")
+    ref_k = torch.zeros(max_len, 128, dtype=torch.float8_e4m3fn)
+    ref_ks = torch.zeros(max_len)
+
+    def reference(x, qr, start):
+        s_len, end = x.shape[0], start + x.shape[0]
+        fc = table[start:end]
+        q = torch.nn.functional.linear(qr, wq_b).view(s_len, heads, 128)
+        q_fp8, q_scale, _ = R.index_prep(q, fc)
+        k = torch.nn.functional.linear(x, wk).view(s_len, 1, 128)
+        k_fp8, k_scale, _ = R.index_prep(k, fc, ln_weight=lnw, ln_bias=lnb)
+        ref_k[start:end], ref_ks[start:end] = k_fp8.view(s_len, 128), k_scale.view(s_len)
+        hw = torch.nn.functional.linear(x.float(), wproj) * heads ** -0.5 * q_scale * 128 ** -0.5
+        scores = R.fp8_index(q_fp8.unsqueeze(0), hw.unsqueeze(0), ref_k[:end].unsqueeze(0),
+                             ref_ks[:end].unsqueeze(0))[0]
+        mask = torch.full((s_len, end), float("-inf")).triu_(1 + start)
+        return scores + mask
+
+    for start, s_len in ((0, prefill), (prefill, 1)):
+        x, qr = mk(s_len, dim).bfloat16(), mk(s_len, q_lora).bfloat16()
+        idx = indexer.indexer_forward(x.cuda(), qr.cuda(), w, k_cache, ks_cache, start, table.cuda(), topk)
+        ops.tc_error_state()
+        ref_scores = reference(x, qr, start)
+        end = start + s_len
+        kk = min(topk, end)
+        assert idx.shape == (s_len, kk)
+        i = idx.cpu().long()
+        # rows that see fewer than kk keys also pick masked (-inf) entries, as the reference's
+        # topk does; the others pick visible keys only
+        full = torch.arange(start, end) + 1 >= kk
+        assert bool((i[full] <= torch.arange(start, end)[full].unsqueeze(1)).all()), "causality"
+        picked = ref_scores.gather(1, i).sum(1)[full]
+        best = ref_scores.topk(kk, dim=1)[0].sum(1)[full]
+        scale = float(ref_scores[torch.isfinite(ref_scores)].abs().max())
+        assert float((picked - best).abs().max()) <= 2e-3 * kk * scale
+        same = (k_cache[:end].cpu().view(torch.uint8) == ref_k[:end].view(torch.uint8)).all(dim=1)
+        assert float(same.float().mean()) >= 0.5
+        assert torch.equal(ks_cache[:end].cpu()[same], ref_ks[:end][same])
