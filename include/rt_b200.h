@@ -508,6 +508,33 @@ int rt_index_topk(const float* scores, int32_t* indices, int64_t queries, int64_
                   int64_t score_stride, int64_t topk, void* stream);
 
 /*
+ * Sparse multi-query attention of the MLA decode step (tcgen05): for every sequence b and head h
+ *   s_j      = softmax_scale * (q_abs[b, h, :] . kv[b, i_j, :] + q_pe[b, h, :] . pe[b, i_j, :])
+ *   out[b, h] = sum_j softmax(s)_j * kv[b, i_j, :]          i_j = indices[b, j], j < n_sel
+ * i.e. the decode branch of MLA.forward with the indexer's mask (0 on the selected keys, -inf
+ * elsewhere) applied by visiting only the selected cache rows. q_abs is q_nope times the key
+ * half of wkv_b (bf16 [batch, heads, 512], strides in elements), q_pe bf16 [batch, heads, 64],
+ * kv the latent cache bf16 [batch, keys, 512], pe the rope cache bf16 [batch, keys, 64], indices
+ * int32 [batch, n_sel] (entries < 0 or >= keys are skipped; NULL: all keys, n_sel == keys), out
+ * bf16 [batch, heads, 512] contiguous (the caller applies the value half of wkv_b).
+ * splits = rt_mla_sparse_decode_splits(batch, heads, n_sel) partial results are merged by a
+ * second kernel; the caller provides part_o fp32 [batch * splits * heads * 512] and part_ml fp32
+ * [batch * splits * heads * 2]. heads: 8, 16, 24, 32 or a multiple of 32; all strides multiples
+ * of 8 elements; pointers 16-byte aligned. No allocation, no host synchronisation.
+ * ref: racetrack/models/deepseek.py:793-810 (MLA.forward, "MQA decode").
+ */
+int64_t rt_mla_sparse_decode_splits(int64_t batch, int64_t heads, int64_t n_sel);
+int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const void* kv, const void* pe,
+                         const int32_t* indices, void* out, float* part_o, float* part_ml,
+                         int64_t batch, int64_t heads, int64_t keys, int64_t n_sel,
+                         int64_t qa_batch_stride, int64_t qa_head_stride,
+                         int64_t qp_batch_stride, int64_t qp_head_stride,
+                         int64_t kv_batch_stride, int64_t kv_row_stride,
+                         int64_t pe_batch_stride, int64_t pe_row_stride,
+                         int64_t idx_batch_stride, int64_t splits, float softmax_scale,
+                         void* stream);
+
+/*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when
  * one of its bounded waits expired. RT_OK when no kernel gave up since the last call,
  * RT_ERR_TIMEOUT otherwise. Call after synchronising the stream; not graph-capturable.

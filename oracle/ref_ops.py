@@ -221,6 +221,26 @@ def index_topk(scores: torch.Tensor, topk: int, mask: torch.Tensor | None = None
     return scores.topk(min(topk, scores.shape[-1]), dim=-1)[1]
 
 
+def mla_sparse_decode(q_abs: torch.Tensor, q_pe: torch.Tensor, kv_cache: torch.Tensor,
+                      pe_cache: torch.Tensor, indices: torch.Tensor | None,
+                      softmax_scale: float) -> torch.Tensor:
+    """The attention core of the MLA decode branch in fp32: scores of the absorbed query against
+    the latent and rope caches, the indexer's mask (0 on the selected keys, -inf elsewhere),
+    softmax, weighted sum of the latent rows. q_abs [B,H,512], q_pe [B,H,64], kv_cache [B,S,512],
+    pe_cache [B,S,64], indices [B,n] (entries < 0 are ignored) or None -> fp32 [B,H,512].
+    ref: racetrack/models/deepseek.py:799-809 (the reference runs these einsums in bf16)."""
+    scores = (torch.einsum("bhc,btc->bht", q_abs.float(), kv_cache.float()) +
+              torch.einsum("bhr,btr->bht", q_pe.float(), pe_cache.float())) * softmax_scale
+    if indices is not None:
+        b, s = kv_cache.shape[0], kv_cache.shape[1]
+        mask = torch.full((b, s + 1), float("-inf"))
+        idx = indices.long().clone()
+        idx[(idx < 0) | (idx >= s)] = s
+        mask.scatter_(-1, idx, 0.0)
+        scores = scores + mask[:, None, :s]
+    return torch.einsum("bht,btc->bhc", scores.softmax(dim=-1), kv_cache.float())
+
+
 def block_dequant(weight: torch.Tensor, scale: torch.Tensor, block: int = FP8_BLOCK) -> torch.Tensor:
     """FP8 weight [out, in] with [out/128, in/128] scales -> bf16.
     ref: racetrack/models/deepseek.py:148-161."""

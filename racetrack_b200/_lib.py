@@ -53,6 +53,8 @@ SIGNATURES: dict[str, tuple] = {
     "rt_index_prep": (_I, [_P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _L, _L, _L, _L, _F, _I, _P]),
     "rt_fp8_index": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
     "rt_index_topk": (_I, [_P, _P, _L, _L, _L, _L, _P]),
+    "rt_mla_sparse_decode_splits": (_L, [_L, _L, _L]),
+    "rt_mla_sparse_decode": (_I, [_P] * 8 + [_L] * 14 + [_F, _P]),
     "rt_gemm_bf16_schedule": (_I, [_I]),
     "rt_gemm_nvfp4_grouped": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
 }

@@ -27,6 +27,7 @@ SOURCES = {
     "rt_act.cu": ["-fmad=false"],
     "rt_moe.cu": ["-fmad=false"],
     "rt_gemm.cu": [],
+    "rt_attn.cu": [],
 }
 
 COMMON = [

@@ -1974,12 +1974,18 @@ extern "C" int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, in
     return tc::launch_bf16<256, false>(a, b, c, m, n, k, lda, ldb, ldc, st);
 }
 
+namespace rt { namespace tc { int attn_error_take(); } }   // the flag of the attention kernels (rt_attn.cu)
+
 extern "C" int rt_tc_error_state(void) {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, tc::g_tc_error, sizeof(int)) != cudaSuccess) {
         cudaGetLastError();
         return fail(RT_ERR_CUDA, "rt_tc_error_state: cannot read the device flag");
     }
+    const int va = tc::attn_error_take();
+    if (va < 0) return fail(RT_ERR_CUDA, "rt_tc_error_state: cannot read the device flag");
+    if (v == 0 && va > 0)
+        return fail(RT_ERR_TIMEOUT, "a tensor-core kernel abandoned wait #%d (bounded spin expired)", va);
     if (v != 0) {
         const int zero = 0;
         cudaMemcpyToSymbol(tc::g_tc_error, &zero, sizeof(int));

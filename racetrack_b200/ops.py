@@ -710,6 +710,47 @@ def index_topk(scores: torch.Tensor, topk: int) -> torch.Tensor:
     return out.reshape(*scores.shape[:-1], kk)
 
 
+def mla_sparse_decode(q_abs: torch.Tensor, q_pe: torch.Tensor, kv_cache: torch.Tensor,
+                      pe_cache: torch.Tensor, indices: Optional[torch.Tensor],
+                      softmax_scale: float) -> torch.Tensor:
+    """Sparse multi-query attention of the MLA decode step (racetrack/models/deepseek.py:793-810):
+    q_abs bf16 [B, H, 512] (q_nope times the key half of wkv_b), q_pe bf16 [B, H, 64], kv_cache
+    bf16 [B, S, 512], pe_cache bf16 [B, S, 64], indices int32 [B, n_sel] of the keys each sequence
+    attends to (the indexer's top-k; None = all S keys) -> bf16 [B, H, 512], the softmax-weighted
+    sum of the selected latent rows."""
+    _require_cuda(q_abs)
+    for name, t in (("q_abs", q_abs), ("q_pe", q_pe), ("kv_cache", kv_cache), ("pe_cache", pe_cache)):
+        if t.dtype != torch.bfloat16 or t.dim() != 3 or t.stride(2) != 1:
+            raise RuntimeError(f"mla_sparse_decode: {name} must be bf16 [*, *, d] with a contiguous last dim")
+    batch, heads, dim = q_abs.shape
+    keys = kv_cache.shape[1]
+    if dim != 512 or kv_cache.shape[2] != 512 or q_pe.shape != (batch, heads, 64) or \
+            pe_cache.shape != (batch, keys, 64) or kv_cache.shape[0] != batch:
+        raise RuntimeError("mla_sparse_decode: shapes must be [B,H,512], [B,H,64], [B,S,512], [B,S,64]")
+    if indices is not None:
+        if indices.dtype != torch.int32 or indices.dim() != 2 or indices.shape[0] != batch:
+            raise RuntimeError("mla_sparse_decode: indices must be int32 [B, n_sel]")
+        if indices.stride(1) != 1:
+            indices = indices.contiguous()
+        n_sel = indices.shape[1]
+    else:
+        n_sel = keys
+    lib = _lib.load()
+    splits = int(lib.rt_mla_sparse_decode_splits(batch, heads, n_sel))
+    dev = q_abs.device
+    out = torch.empty(batch, heads, 512, dtype=torch.bfloat16, device=dev)
+    part_o = torch.empty(batch * splits * heads * 512, dtype=torch.float32, device=dev)
+    part_ml = torch.empty(batch * splits * heads * 2, dtype=torch.float32, device=dev)
+    _lib.check(lib.rt_mla_sparse_decode(
+        q_abs.data_ptr(), q_pe.data_ptr(), kv_cache.data_ptr(), pe_cache.data_ptr(),
+        indices.data_ptr() if indices is not None else None, out.data_ptr(), part_o.data_ptr(),
+        part_ml.data_ptr(), batch, heads, keys, n_sel, q_abs.stride(0), q_abs.stride(1),
+        q_pe.stride(0), q_pe.stride(1), kv_cache.stride(0), kv_cache.stride(1), pe_cache.stride(0),
+        pe_cache.stride(1), indices.stride(0) if indices is not None else 0, splits,
+        float(softmax_scale), _stream()), "rt_mla_sparse_decode")
+    return out
+
+
 def gemm_bf16_schedule(schedule: int) -> int:
     """Selects the schedule of the bf16 GEMM for this process (0 default = by size, 1 single-CTA
     128 x 256 tiles, 2 CTA pairs with 256 x 256 tiles where K % 64 == 0) and returns the
