@@ -498,6 +498,21 @@ int rt_fp8_index(const void* q, const float* weights, const void* k, const float
                  int64_t score_stride, int64_t causal_offset, void* stream);
 
 /*
+ * The same for `batch` sequences with caches of their own (a decode step: one query per
+ * sequence): q e4m3 [batch, queries, heads, dim] contiguous, weights fp32 [batch, queries,
+ * heads], k e4m3 [batch, keys, dim] with k_batch_stride ROWS between sequences (the cache may be
+ * longer than `keys`), k_scale fp32 with ks_batch_stride elements between sequences, scores
+ * fp32 [batch, queries, keys] with score_stride / score_batch_stride elements between rows /
+ * sequences. One launch; the mask is that of rt_fp8_index within each sequence.
+ * ref: racetrack/models/deepseek.py:656-686 (Indexer.forward with bsz > 1).
+ */
+int rt_fp8_index_batched(const void* q, const float* weights, const void* k, const float* k_scale,
+                         float* scores, int64_t batch, int64_t queries, int64_t heads,
+                         int64_t keys, int64_t dim, int64_t score_stride, int64_t causal_offset,
+                         int64_t k_batch_stride, int64_t ks_batch_stride,
+                         int64_t score_batch_stride, void* stream);
+
+/*
  * Top-k selection of the indexer: indices [queries, topk] (int32) of the topk largest scores
  * of every row, written in ascending index order; among scores equal to the k-th largest the
  * lower indices are taken. Exact (radix select on the ordered bit patterns), -inf allowed.

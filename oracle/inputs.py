@@ -124,3 +124,30 @@ def expert_weights(n_experts: int, hidden: int, inter: int, *, seed: int = SEED,
                     randn((hidden, inter), seed + 1001 + 3 * e, std=0.02, dtype=dtype),
                     randn((inter, hidden), seed + 1002 + 3 * e, std=0.02, dtype=dtype)))
     return out
+
+
+MLA_DECODE = dict(dim=256, heads=4, q_lora=64, kv_lora=64, nope=32, rope=16, v_dim=32, batch=2,
+                  max_len=64, start_pos=40, topk=16)
+
+
+def mla_decode_inputs(seed: int = SEED) -> dict:
+    """A small MLA module in decode mode (racetrack/models/deepseek.py:697-811): weights, the
+    token of each of `batch` sequences, caches holding `start_pos` earlier positions ~ N(0, 1)
+    and the positions the indexer is taken to have selected."""
+    c = MLA_DECODE
+    b, L = c["batch"], c["max_len"]
+    w = {"wq_a": randn((c["q_lora"], c["dim"]), seed + 800, std=0.06),
+         "q_norm": randn((c["q_lora"],), seed + 801, mean=1.0, std=0.02, dtype=torch.float32),
+         "wq_b": randn((c["heads"] * (c["nope"] + c["rope"]), c["q_lora"]), seed + 802, std=0.12),
+         "wkv_a": randn((c["kv_lora"] + c["rope"], c["dim"]), seed + 803, std=0.06),
+         "kv_norm": randn((c["kv_lora"],), seed + 804, mean=1.0, std=0.02, dtype=torch.float32),
+         "wkv_b": randn((c["heads"] * (c["nope"] + c["v_dim"]), c["kv_lora"]), seed + 805, std=0.12),
+         "wo": randn((c["dim"], c["heads"] * c["v_dim"]), seed + 806, std=0.09)}
+    kv_cache = torch.zeros(b, L, c["kv_lora"], dtype=torch.bfloat16)
+    pe_cache = torch.zeros(b, L, c["rope"], dtype=torch.bfloat16)
+    kv_cache[:, :c["start_pos"]] = randn((b, c["start_pos"], c["kv_lora"]), seed + 807)
+    pe_cache[:, :c["start_pos"]] = randn((b, c["start_pos"], c["rope"]), seed + 808)
+    g = _gen(seed + 809)
+    topk = torch.stack([torch.randperm(c["start_pos"] + 1, generator=g)[:c["topk"]] for _ in range(b)])
+    return {"w": w, "x": randn((b, 1, c["dim"]), seed + 810), "kv_cache": kv_cache,
+            "pe_cache": pe_cache, "topk_indices": topk.view(b, 1, c["topk"])}

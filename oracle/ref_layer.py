@@ -116,3 +116,73 @@ def forward_stack(hidden, positions, rank_weights, shape, layers, ffn="moe", exp
             out = _all_reduce([dense_ffn(h, w) for w in rank_weights])
         hidden = residual + out
     return hidden
+
+
+# ---------------------------------------------------------------------------
+# decode step: B sequences, one token each, per-sequence caches, sparse attention
+# ---------------------------------------------------------------------------
+def indexer_decode(h, q_c, iw, caches, start_pos, freqs, index_topk):
+    """Indexer.forward for bsz = B, seqlen = 1 (ref: racetrack/models/deepseek.py:656-686).
+    iw: dict with wq_b, wk, k_norm_weight, k_norm_bias, weights_proj; caches: dict with index_k
+    [B, L, 128] e4m3 and index_scale [B, L]. Returns int64 [B, 1, k]."""
+    batch = h.shape[0]
+    heads = iw["weights_proj"].shape[0]
+    fc = freqs[start_pos:start_pos + 1].expand(batch, -1)
+    q = F.linear(q_c, iw["wq_b"]).view(batch, heads, 128)
+    q_fp8, q_scale, _ = R.index_prep(q, fc)
+    k = F.linear(h, iw["wk"]).view(batch, 1, 128)
+    k_fp8, k_scale, _ = R.index_prep(k, fc, ln_weight=iw["k_norm_weight"], ln_bias=iw["k_norm_bias"])
+    caches["index_k"][:, start_pos] = k_fp8.view(batch, 128)
+    caches["index_scale"][:, start_pos] = k_scale.view(batch)
+    head_w = F.linear(h.float(), iw["weights_proj"]) * heads ** -0.5 * q_scale * 128 ** -0.5
+    end = start_pos + 1
+    scores = R.fp8_index(q_fp8.unsqueeze(1), head_w.unsqueeze(1), caches["index_k"][:, :end],
+                         caches["index_scale"][:, :end])
+    return R.index_topk(scores, index_topk)
+
+
+def decode_attention(h, start_pos, w, iw, caches, shape, local_heads, freqs, index_topk):
+    """One rank's attention partial of the decode step: the synthetic layer's projections
+    (racetrack/realistic_bench.py:286-303) followed by the reference's "MQA decode" branch with
+    the indexer's mask (racetrack/models/deepseek.py:777-778,793-811). The caches (kv, pe: bf16
+    [B, L, .]) are this rank's copies and are updated in place."""
+    s = shape
+    batch = h.shape[0]
+    positions = torch.full((batch,), start_pos, dtype=torch.int64)
+    qkv = F.linear(h, w["w_qkv_a"])
+    q_c, kv_c, k_pe = qkv.split([s.q_lora, s.kv_lora, s.rope], dim=-1)
+    ones_q = torch.ones(s.q_lora, dtype=h.dtype)
+    ones_kv = torch.ones(s.kv_lora, dtype=h.dtype)
+    q_c, kv_c, k_pe = R.fused_norm_rope(q_c, ones_q, kv_c, ones_kv, k_pe, positions, eps=s.eps,
+                                        rope_base=s.rope_base)
+    q = F.linear(q_c, w["w_q_b"]).view(batch, local_heads, s.nope + s.rope)
+    q_nope, q_pe = q.split([s.nope, s.rope], dim=-1)
+    q_pe = R.apply_rope(q_pe, positions, base=s.rope_base)
+    caches["kv"][:, start_pos] = kv_c
+    caches["pe"][:, start_pos] = k_pe
+    picked = indexer_decode(h, q_c, iw, caches, start_pos, freqs, index_topk)
+    end = start_pos + 1
+    out = R.mla_decode_core(q_nope.unsqueeze(1), q_pe.unsqueeze(1), w["w_kv_b"], caches["kv"][:, :end],
+                            caches["pe"][:, :end], picked, (s.nope + s.rope) ** -0.5, s.nope, s.v_dim)
+    return F.linear(out.reshape(batch, local_heads * s.v_dim), w["w_o"])
+
+
+def decode_stack(hidden, start_pos, rank_weights, iw, rank_caches, shape, layers, freqs, index_topk,
+                 experts="bf16"):
+    """The decode step applied `layers` times (one layer reused, as in forward_stack)."""
+    moe_fn = moe if experts == "bf16" else moe_nvfp4
+    world = len(rank_weights)
+    ones = torch.ones(shape.hidden, dtype=hidden.dtype)
+    local_heads = shape.heads // world
+    local_experts = shape.n_experts // world
+    for _ in range(layers):
+        residual = hidden
+        h = R.rms_norm(hidden, ones, shape.eps)
+        attn = _all_reduce([decode_attention(h, start_pos, w, iw, c, shape, local_heads, freqs, index_topk)
+                            for w, c in zip(rank_weights, rank_caches)])
+        hidden = residual + attn
+        residual = hidden
+        h = R.rms_norm(hidden, ones, shape.eps)
+        out = _all_reduce([moe_fn(h, w, shape, r, local_experts) for r, w in enumerate(rank_weights)])
+        hidden = residual + out
+    return hidden

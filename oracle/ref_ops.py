@@ -241,6 +241,53 @@ def mla_sparse_decode(q_abs: torch.Tensor, q_pe: torch.Tensor, kv_cache: torch.T
     return torch.einsum("bht,btc->bhc", scores.softmax(dim=-1), kv_cache.float())
 
 
+def mla_decode_core(q_nope: torch.Tensor, q_pe: torch.Tensor, wkv_b: torch.Tensor,
+                    kv_cache: torch.Tensor, pe_cache: torch.Tensor, topk_indices: torch.Tensor,
+                    softmax_scale: float, nope: int, v_dim: int) -> torch.Tensor:
+    """The "MQA decode" branch in the reference's own dtype flow (every einsum and the softmax in
+    the tensors' dtype, bf16 in the model): absorb q_nope through the key half of wkv_b, score
+    against the latent and rope caches, add the index mask, softmax, weight the latent rows, apply
+    the value half of wkv_b. q_nope [B,S,H,nope], q_pe [B,S,H,rope], wkv_b [H*(nope+v), C],
+    kv_cache [B,T,C], pe_cache [B,T,rope] (T = end_pos), topk_indices [B,S,k] -> [B,S,H,v].
+    ref: racetrack/models/deepseek.py:794-810."""
+    bsz, _, heads, _ = q_nope.shape
+    end_pos = kv_cache.shape[1]
+    w = wkv_b.view(heads, -1, kv_cache.shape[-1])
+    q_abs = torch.einsum("bshd,hdc->bshc", q_nope, w[:, :nope])
+    scores = (torch.einsum("bshc,btc->bsht", q_abs, kv_cache) +
+              torch.einsum("bshr,btr->bsht", q_pe, pe_cache)) * softmax_scale
+    index_mask = torch.full((bsz, 1, end_pos), float("-inf"), dtype=scores.dtype).scatter_(
+        -1, topk_indices.long(), 0)
+    scores = scores + index_mask.unsqueeze(2)
+    scores = scores.softmax(dim=-1)
+    x = torch.einsum("bsht,btc->bshc", scores, kv_cache)
+    return torch.einsum("bshc,hdc->bshd", x, w[:, -v_dim:])
+
+
+def mla_decode(x: torch.Tensor, start_pos: int, freqs_cis: torch.Tensor, w: dict,
+               kv_cache: torch.Tensor, pe_cache: torch.Tensor, topk_indices: torch.Tensor, *,
+               heads: int, nope: int, rope: int, v_dim: int, eps: float = 1e-6) -> torch.Tensor:
+    """MLA.forward with mask=None (one new token per sequence): x [B,1,dim] bf16; w holds wq_a,
+    q_norm, wq_b, wkv_a, kv_norm, wkv_b, wo; the caches [B, max_len, .] are updated in place at
+    start_pos; topk_indices [B,1,k] is what the indexer returned. freqs_cis complex [1, rope/2]
+    for this position. ref: racetrack/models/deepseek.py:765-811."""
+    bsz, seqlen, _ = x.shape
+    end_pos = start_pos + seqlen
+    qr = rms_norm(F.linear(x, w["wq_a"]), w["q_norm"], eps)
+    q = F.linear(qr, w["wq_b"]).view(bsz, seqlen, heads, nope + rope)
+    q_nope, q_pe = torch.split(q, [nope, rope], dim=-1)
+    q_pe = apply_rotary_emb(q_pe, freqs_cis)
+    kv = F.linear(x, w["wkv_a"])
+    kv, k_pe = torch.split(kv, [kv.shape[-1] - rope, rope], dim=-1)
+    kv = rms_norm(kv, w["kv_norm"], eps)
+    k_pe = apply_rotary_emb(k_pe.unsqueeze(2), freqs_cis)
+    kv_cache[:bsz, start_pos:end_pos] = kv
+    pe_cache[:bsz, start_pos:end_pos] = k_pe.squeeze(2)
+    out = mla_decode_core(q_nope, q_pe, w["wkv_b"], kv_cache[:bsz, :end_pos], pe_cache[:bsz, :end_pos],
+                          topk_indices, (nope + rope) ** -0.5, nope, v_dim)
+    return F.linear(out.flatten(2), w["wo"])
+
+
 def block_dequant(weight: torch.Tensor, scale: torch.Tensor, block: int = FP8_BLOCK) -> torch.Tensor:
     """FP8 weight [out, in] with [out/128, in/128] scales -> bf16.
     ref: racetrack/models/deepseek.py:148-161."""

@@ -52,6 +52,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_gemm_nvfp4_schedule": (_I, [_I]),
     "rt_index_prep": (_I, [_P, _P, _P, _P, _P, _L, _L, _P, _P, _P, _L, _L, _L, _L, _F, _I, _P]),
     "rt_fp8_index": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
+    "rt_fp8_index_batched": (_I, [_P, _P, _P, _P, _P] + [_L] * 10 + [_P]),
     "rt_index_topk": (_I, [_P, _P, _L, _L, _L, _L, _P]),
     "rt_mla_sparse_decode_splits": (_L, [_L, _L, _L]),
     "rt_mla_sparse_decode": (_I, [_P] * 8 + [_L] * 14 + [_F, _P]),

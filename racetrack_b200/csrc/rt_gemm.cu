@@ -1395,7 +1395,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
     const __grid_constant__ CUtensorMap tmap_k, const __grid_constant__ CUtensorMap tmap_q,
     const float* __restrict__ weights, const float* __restrict__ k_scale,
     float* __restrict__ scores, int queries, int heads, int keys, int64_t ld,
-    int64_t causal_offset) {
+    int64_t causal_offset, int batch, int64_t ks_batch_stride, int64_t score_batch_stride) {
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
@@ -1417,7 +1417,8 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
     const int num_qb = (q_rows + 255) / 256;
     const int num_kt = (keys + 127) / 128;
     const int num_kc = (num_kt + kIdxChunk - 1) / kIdxChunk;
-    const int num_items = num_qb * num_kc;
+    const int per_seq = num_qb * num_kc;            // work items of one sequence
+    const int num_items = batch * per_seq;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -1450,15 +1451,17 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
             uint32_t phase = 0, qphase = 0;
             bool ok = true;
             for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-                const int qb = item / num_kc, kc = item % num_kc;
+                const int bi = item / per_seq, rem = item % per_seq;
+                const int qb = rem / num_kc, kc = rem % num_kc;
                 if (!(ok = mbar_wait(qempty_bar(qs), qphase ^ 1u, abort_flag, 51))) break;
                 mbar_arrive_expect_tx(qfull_bar(qs), kIdxQBytes);
-                tma_load_2d(base + kIdxQOffset + qs * kIdxQBytes, &tmap_q, 0, qb * 256, qfull_bar(qs));
+                tma_load_3d(base + kIdxQOffset + qs * kIdxQBytes, &tmap_q, 0, qb * 256, bi,
+                            qfull_bar(qs));
                 const int kt_end = min(num_kt, (kc + 1) * kIdxChunk);
                 for (int kt = kc * kIdxChunk; kt < kt_end; ++kt) {
                     if (!(ok = mbar_wait(kempty_bar(stage), phase ^ 1u, abort_flag, 52))) break;
                     mbar_arrive_expect_tx(kfull_bar(stage), kIdxKBytes);
-                    tma_load_2d(base + stage * kIdxKBytes, &tmap_k, 0, kt * 128, kfull_bar(stage));
+                    tma_load_3d(base + stage * kIdxKBytes, &tmap_k, 0, kt * 128, bi, kfull_bar(stage));
                     if (++stage == kIdxStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -1477,7 +1480,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
             uint32_t phase = 0, qphase = 0, buf_phase = 0;
             bool ok = true;
             for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x) {
-                const int kc = item % num_kc;
+                const int kc = (item % per_seq) % num_kc;
                 if (!(ok = mbar_wait(qfull_bar(qs), qphase, abort_flag, 53))) break;
                 const uint64_t bdesc = smem_desc_sw128(base + kIdxQOffset + qs * kIdxQBytes);
                 const int kt_end = min(num_kt, (kc + 1) * kIdxChunk);
@@ -1520,12 +1523,16 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
         uint32_t buf_phase = 0;
         bool ok = true;
         for (int item = blockIdx.x; ok && item < num_items; item += gridDim.x, parity ^= 1) {
-            const int qb = item / num_kc, kc = item % num_kc;
+            const int bi = item / per_seq, rem = item % per_seq;
+            const int qb = rem / num_kc, kc = rem % num_kc;
+            const float* ks_b = k_scale + bi * ks_batch_stride;
+            float* scores_b = scores + bi * score_batch_stride;
             // head weights of the block's 256 (query, head) rows; the named barrier also says
             // that every epilogue thread has left the item that used this half of wsm before
             if (et < 256) {
                 const int qrow = qb * 256 + et;
-                wsm[parity * 256 + et] = qrow < q_rows ? __ldg(weights + qrow) : 0.f;
+                wsm[parity * 256 + et] =
+                    qrow < q_rows ? __ldg(weights + static_cast<int64_t>(bi) * q_rows + qrow) : 0.f;
             }
             asm volatile("bar.sync 1, %0;" ::"n"(32 * EW) : "memory");
             const float4* wv = reinterpret_cast<const float4*>(wsm + parity * 256 + slice * kCols);
@@ -1533,7 +1540,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
             const int kt_end = min(num_kt, (kc + 1) * kIdxChunk);
             for (int kt = kc * kIdxChunk; kt < kt_end; ++kt) {
                 const int n = kt * 128 + quad * 32 + lane;
-                const float ks = n < keys ? __ldg(k_scale + n) : 0.f;
+                const float ks = n < keys ? __ldg(ks_b + n) : 0.f;
                 if (!(ok = mbar_wait(pfull_bar(buf), buf_phase, abort_flag, 56))) break;
                 tc_fence_after();
                 const uint32_t taddr = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
@@ -1579,7 +1586,7 @@ __global__ void __launch_bounds__(64 + 32 * EW, 1) index_score_kernel(
                         const int m = m0 + j;
                         if (m < queries) {
                             const bool visible = causal_offset < 0 || n <= m + causal_offset;
-                            scores[static_cast<int64_t>(m) * ld + n] =
+                            scores_b[static_cast<int64_t>(m) * ld + n] =
                                 visible ? s * ks : __int_as_float(0xff800000);
                         }
                     }
@@ -1649,6 +1656,25 @@ int make_tmap_kblocks(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t
     const cuuint64_t dims[3] = {128, rows, k_bytes / 128};
     const cuuint64_t strides[2] = {pitch_bytes, 128};
     const cuuint32_t box[3] = {128, box_rows, box_kblocks};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RT_REQUIRE(r == CUDA_SUCCESS, RT_ERR_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d",
+               static_cast<int>(r));
+    return RT_OK;
+}
+
+// 3-D map over `batch` K-major matrices of 128-byte rows: dims {128 bytes, rows, batch}, box
+// {128, box_rows, 1}; the batch stride is in bytes (a multiple of 16).
+int make_tmap_rows128_batched(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t batch,
+                              uint64_t batch_stride_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    RT_REQUIRE(fn, RT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {128, rows, batch};
+    const cuuint64_t strides[2] = {128, batch_stride_bytes};
+    const cuuint32_t box[3] = {128, box_rows, 1};
     const cuuint32_t estr[3] = {1, 1, 1};
     const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 3, const_cast<void*>(ptr), dims,
                           strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -1730,13 +1756,15 @@ static int launch_bf16_pair(const void* a, const void* b, void* c, int64_t M, in
 }
 
 static int launch_index_score(const void* q, const float* weights, const void* k,
-                              const float* k_scale, float* scores, int64_t queries, int64_t heads,
-                              int64_t keys, int64_t ld, int64_t causal_offset, cudaStream_t st) {
+                              const float* k_scale, float* scores, int64_t batch, int64_t queries,
+                              int64_t heads, int64_t keys, int64_t ld, int64_t causal_offset,
+                              int64_t k_batch_stride, int64_t ks_batch_stride,
+                              int64_t score_batch_stride, cudaStream_t st) {
     CUtensorMap tk, tq;
-    if (int rc = make_tmap_2d(&tk, CU_TENSOR_MAP_DATA_TYPE_UINT8, k, 128, keys, 128, 128, 128))
-        return rc;
-    if (int rc = make_tmap_2d(&tq, CU_TENSOR_MAP_DATA_TYPE_UINT8, q, 128, queries * heads, 128, 128,
-                              256))
+    const uint64_t kbs = batch > 1 ? static_cast<uint64_t>(k_batch_stride) * 128u : static_cast<uint64_t>(keys) * 128u;
+    if (int rc = make_tmap_rows128_batched(&tk, k, keys, batch, kbs, 128)) return rc;
+    if (int rc = make_tmap_rows128_batched(&tq, q, queries * heads, batch,
+                                           static_cast<uint64_t>(queries * heads) * 128u, 256))
         return rc;
     if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&index_score_kernel<16>),
                                      static_cast<int>(kIdxSmemBytes), "rt_fp8_index"))
@@ -1746,16 +1774,18 @@ static int launch_index_score(const void* q, const float* weights, const void* k
         return rc;
     const int64_t num_qb = (queries * heads + 255) / 256;
     const int64_t num_kt = (keys + 127) / 128;
-    const int64_t items = num_qb * ((num_kt + kIdxChunk - 1) / kIdxChunk);
+    const int64_t items = batch * num_qb * ((num_kt + kIdxChunk - 1) / kIdxChunk);
     const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
     if (heads <= 64)
         index_score_kernel<16><<<grid, 64 + 32 * 16, kIdxSmemBytes, st>>>(
             tk, tq, weights, k_scale, scores, static_cast<int>(queries), static_cast<int>(heads),
-            static_cast<int>(keys), ld, causal_offset);
+            static_cast<int>(keys), ld, causal_offset, static_cast<int>(batch), ks_batch_stride,
+            score_batch_stride);
     else
         index_score_kernel<8><<<grid, 64 + 32 * 8, kIdxSmemBytes, st>>>(
             tk, tq, weights, k_scale, scores, static_cast<int>(queries), static_cast<int>(heads),
-            static_cast<int>(keys), ld, causal_offset);
+            static_cast<int>(keys), ld, causal_offset, static_cast<int>(batch), ks_batch_stride,
+            score_batch_stride);
     count_launch();
     return check_launch("index_score_kernel");
 }
@@ -1856,12 +1886,14 @@ extern "C" int rt_gemm_fp8(const void* a, const float* a_scales, const void* b,
     return tc::launch_fp8(a, a_scales, b, b_scales, c, m, n, k, lda, ldb, ldc, as_stream(stream));
 }
 
-extern "C" int rt_fp8_index(const void* q, const float* weights, const void* k, const float* k_scale,
-                            float* scores, int64_t queries, int64_t heads, int64_t keys,
-                            int64_t dim, int64_t score_stride, int64_t causal_offset,
-                            void* stream) {
-    RT_REQUIRE(queries >= 0 && heads > 0 && keys > 0, RT_ERR_BAD_ARG, "rt_fp8_index: bad shape");
-    if (queries == 0) return RT_OK;
+static int fp8_index_checked(const void* q, const float* weights, const void* k,
+                             const float* k_scale, float* scores, int64_t batch, int64_t queries,
+                             int64_t heads, int64_t keys, int64_t dim, int64_t score_stride,
+                             int64_t causal_offset, int64_t k_batch_stride,
+                             int64_t ks_batch_stride, int64_t score_batch_stride, void* stream) {
+    RT_REQUIRE(batch >= 0 && queries >= 0 && heads > 0 && keys > 0, RT_ERR_BAD_ARG,
+               "rt_fp8_index: bad shape");
+    if (queries == 0 || batch == 0) return RT_OK;
     RT_REQUIRE(q && weights && k && k_scale && scores, RT_ERR_BAD_ARG, "rt_fp8_index: null pointer");
     RT_REQUIRE(dim == 128, RT_ERR_UNSUPPORTED, "rt_fp8_index: the index head dimension must be 128");
     RT_REQUIRE(heads % 16 == 0 && 128 % heads == 0, RT_ERR_UNSUPPORTED,
@@ -1869,10 +1901,34 @@ extern "C" int rt_fp8_index(const void* q, const float* weights, const void* k, 
     RT_REQUIRE(aligned16(q) && aligned16(k), RT_ERR_UNSUPPORTED,
                "rt_fp8_index: q and k must be 16-byte aligned");
     RT_REQUIRE(score_stride >= keys, RT_ERR_BAD_ARG, "rt_fp8_index: score stride below keys");
-    RT_REQUIRE(queries * heads < (1LL << 31) && keys < (1LL << 31), RT_ERR_UNSUPPORTED,
-               "rt_fp8_index: dimension too large");
-    return tc::launch_index_score(q, weights, k, k_scale, scores, queries, heads, keys, score_stride,
-                                  causal_offset, as_stream(stream));
+    RT_REQUIRE(queries * heads < (1LL << 31) && keys < (1LL << 31) && batch < (1LL << 20) &&
+                   batch * queries * heads < (1LL << 31),
+               RT_ERR_UNSUPPORTED, "rt_fp8_index: dimension too large");
+    RT_REQUIRE(batch == 1 || (k_batch_stride >= keys && ks_batch_stride >= keys &&
+                              score_batch_stride >= queries * score_stride),
+               RT_ERR_BAD_ARG, "rt_fp8_index: a batch stride is below the extent of one sequence");
+    return tc::launch_index_score(q, weights, k, k_scale, scores, batch, queries, heads, keys,
+                                  score_stride, causal_offset, k_batch_stride, ks_batch_stride,
+                                  score_batch_stride, as_stream(stream));
+}
+
+extern "C" int rt_fp8_index(const void* q, const float* weights, const void* k, const float* k_scale,
+                            float* scores, int64_t queries, int64_t heads, int64_t keys,
+                            int64_t dim, int64_t score_stride, int64_t causal_offset,
+                            void* stream) {
+    return fp8_index_checked(q, weights, k, k_scale, scores, 1, queries, heads, keys, dim,
+                             score_stride, causal_offset, 0, 0, 0, stream);
+}
+
+extern "C" int rt_fp8_index_batched(const void* q, const float* weights, const void* k,
+                                    const float* k_scale, float* scores, int64_t batch,
+                                    int64_t queries, int64_t heads, int64_t keys, int64_t dim,
+                                    int64_t score_stride, int64_t causal_offset,
+                                    int64_t k_batch_stride, int64_t ks_batch_stride,
+                                    int64_t score_batch_stride, void* stream) {
+    return fp8_index_checked(q, weights, k, k_scale, scores, batch, queries, heads, keys, dim,
+                             score_stride, causal_offset, k_batch_stride, ks_batch_stride,
+                             score_batch_stride, stream);
 }
 
 extern "C" int rt_moe_tile_map(const int32_t* offsets, int64_t g_begin, int64_t g_end,

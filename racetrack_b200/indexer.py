@@ -56,3 +56,29 @@ def indexer_forward(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cach
                            k_scale_cache[:end_pos].unsqueeze(0),
                            causal_offset=start_pos if causal else None)
     return ops.index_topk(scores[0], index_topk)
+
+
+
+def indexer_decode(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cache: torch.Tensor,
+                   k_scale_cache: torch.Tensor, start_pos: int, freqs_cis: torch.Tensor,
+                   index_topk: int) -> torch.Tensor:
+    """One decode step of B sequences (the reference's bsz = B, seqlen = 1): x [B, dim] and qr
+    [B, q_lora] bf16 hold the token of every sequence at position start_pos; k_cache
+    float8_e4m3fn [B, max_len, 128] and k_scale_cache fp32 [B, max_len] are updated in place at
+    start_pos. Returns int32 [B, min(index_topk, start_pos + 1)], ascending. Every kernel runs
+    once for the whole batch."""
+    batch = x.shape[0]
+    end_pos = start_pos + 1
+    positions = torch.full((batch,), start_pos, device=x.device, dtype=torch.int64)
+    q = ops.linear_bf16(qr, w.wq_b).view(batch, w.heads, w.head_dim)
+    q_fp8, q_scale = ops.index_prep(q, freqs_cis, positions=positions)
+    k = ops.linear_bf16(x, w.wk).view(batch, 1, w.head_dim)
+    k_fp8, k_scale = ops.index_prep(k, freqs_cis, positions=positions,
+                                    ln_weight=w.k_norm_weight, ln_bias=w.k_norm_bias)
+    k_cache[:, start_pos] = k_fp8.view(batch, w.head_dim)
+    k_scale_cache[:, start_pos] = k_scale.view(batch)
+    head_w = torch.nn.functional.linear(x.float(), w.weights_proj) * w.heads ** -0.5
+    head_w = head_w * q_scale.view(batch, w.heads) * w.head_dim ** -0.5
+    scores = ops.fp8_index(q_fp8.view(batch, 1, w.heads, w.head_dim), head_w.view(batch, 1, w.heads),
+                           k_cache[:, :end_pos], k_scale_cache[:, :end_pos])
+    return ops.index_topk(scores.view(batch, end_pos), index_topk)

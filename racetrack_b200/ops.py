@@ -667,28 +667,36 @@ def index_prep(x: torch.Tensor, freqs_cis: torch.Tensor, *, positions: Optional[
 def fp8_index(q: torch.Tensor, weights: torch.Tensor, k: torch.Tensor, k_scale: torch.Tensor, *,
               causal_offset: Optional[int] = None) -> torch.Tensor:
     """Index scores of the sparse-attention indexer (racetrack/models/deepseek.py:164-176):
-    scores[m, n] = k_scale[n] * sum_h weights[m, h] * relu(q[m, h, :] . k[n, :]).
+    scores[b, m, n] = k_scale[b, n] * sum_h weights[b, m, h] * relu(q[b, m, h, :] . k[b, n, :]).
 
-    q float8_e4m3fn [..., M, H, 128], weights fp32 [..., M, H], k float8_e4m3fn [..., N, 128],
-    k_scale fp32 [..., N]; leading dims must be 1 (one sequence). With causal_offset = c, keys
-    n > m + c get -inf (the mask the reference adds before top-k). Returns fp32 [..., M, N]."""
+    q float8_e4m3fn [B, M, H, 128], weights fp32 [B, M, H], k float8_e4m3fn [B, N, 128] (may be the
+    first N rows of longer per-sequence caches), k_scale fp32 [B, N] or [B, N, 1]; the batch
+    dimension may be missing. With causal_offset = c, keys n > m + c get -inf (the mask the
+    reference adds before top-k). One launch for all sequences. Returns fp32 [B, M, N]."""
     _require_cuda(q, weights, k, k_scale)
     if q.dtype != torch.float8_e4m3fn or k.dtype != torch.float8_e4m3fn:
         raise RuntimeError("fp8_index: q and k must be float8_e4m3fn")
     m, h, d = q.shape[-3:]
     n = k.shape[-2]
     lead = q.shape[:-3]
-    if any(x != 1 for x in lead) or k.shape[:-2] != lead:
-        raise RuntimeError("fp8_index: one sequence at a time (leading dims of q and k must be 1)")
-    q2, k2 = q.reshape(m, h, d).contiguous(), k.reshape(n, d).contiguous()
-    w2 = weights.reshape(m, h).to(torch.float32).contiguous()
-    ks = k_scale.reshape(n).to(torch.float32).contiguous()
-    scores = torch.empty(m, n, dtype=torch.float32, device=q.device)
+    if k.shape[:-2] != lead or len(lead) > 1:
+        raise RuntimeError("fp8_index: q [B, M, H, D] and k [B, N, D] must share at most one batch dim")
+    batch = lead[0] if lead else 1
+    q3 = q.reshape(batch, m, h, d).contiguous()
+    k3 = k.reshape(batch, n, d)
+    if k3.stride(2) != 1 or k3.stride(1) != d or (batch > 1 and k3.stride(0) % d):
+        k3 = k3.contiguous()
+    w3 = weights.reshape(batch, m, h).to(torch.float32).contiguous()
+    ks = k_scale.reshape(batch, n).to(torch.float32)
+    if ks.stride(1) != 1:
+        ks = ks.contiguous()
+    scores = torch.empty(batch, m, n, dtype=torch.float32, device=q.device)
     lib = _lib.load()
-    _lib.check(lib.rt_fp8_index(q2.data_ptr(), w2.data_ptr(), k2.data_ptr(), ks.data_ptr(),
-                                scores.data_ptr(), m, h, n, d, scores.stride(0),
-                                -1 if causal_offset is None else int(causal_offset), _stream()),
-               "rt_fp8_index")
+    _lib.check(lib.rt_fp8_index_batched(
+        q3.data_ptr(), w3.data_ptr(), k3.data_ptr(), ks.data_ptr(), scores.data_ptr(), batch, m, h,
+        n, d, scores.stride(1), -1 if causal_offset is None else int(causal_offset),
+        (k3.stride(0) // d) if batch > 1 else n, ks.stride(0) if batch > 1 else n, scores.stride(0),
+        _stream()), "rt_fp8_index_batched")
     return scores.reshape(*lead, m, n)
 
 

@@ -185,6 +185,37 @@ def main() -> None:
         k_pe = rm.apply_rotary_emb(k_pe.unsqueeze(0), fc, False).squeeze(0)
     small["idxprep.k_ln_rope"] = torch.cat([k_pe, k_nope], dim=-1).clone()
 
+    # ---- MLA.forward, decode branch (deepseek.py:765-811), the indexer replaced by a fixed selection
+    c = I.MLA_DECODE
+    d = I.mla_decode_inputs()
+    torch.set_default_dtype(torch.bfloat16)     # the model's caches take the default dtype (deepseek.py:1135)
+    try:
+        margs = rm.ModelArgs(max_batch_size=c["batch"], max_seq_len=c["max_len"], dim=c["dim"],
+                             n_heads=c["heads"], q_lora_rank=c["q_lora"], kv_lora_rank=c["kv_lora"],
+                             qk_nope_head_dim=c["nope"], qk_rope_head_dim=c["rope"],
+                             v_head_dim=c["v_dim"])
+        mla = rm.MLA(margs)
+        picked = d["topk_indices"]
+
+        class FixedSelection(torch.nn.Module):
+            def forward(self, x, qr, start_pos, freqs_cis, mask):
+                return picked
+
+        mla.indexer = FixedSelection()
+        with torch.no_grad():
+            mla.wq_a.weight.copy_(d["w"]["wq_a"]); mla.q_norm.weight.copy_(d["w"]["q_norm"])
+            mla.wq_b.weight.copy_(d["w"]["wq_b"]); mla.wkv_a.weight.copy_(d["w"]["wkv_a"])
+            mla.kv_norm.weight.copy_(d["w"]["kv_norm"]); mla.wkv_b.weight.copy_(d["w"]["wkv_b"])
+            mla.wo.weight.copy_(d["w"]["wo"])
+            mla.kv_cache.copy_(d["kv_cache"]); mla.pe_cache.copy_(d["pe_cache"])
+            fc = rm.precompute_freqs_cis(margs)[c["start_pos"]:c["start_pos"] + 1]
+            y = mla(d["x"], c["start_pos"], fc, None)
+        small["mla_decode.out"] = y.clone()
+        small["mla_decode.kv_row"] = mla.kv_cache[:, c["start_pos"]].clone()
+        small["mla_decode.pe_row"] = mla.pe_cache[:, c["start_pos"]].clone()
+    finally:
+        torch.set_default_dtype(torch.float32)
+
     meta = {"torch": torch.__version__, "cpu_capability": torch.backends.cpu.get_cpu_capability(),
             "threads": torch.get_num_threads()}
     torch.save(small, HERE / "golden_small.pt")

@@ -236,3 +236,46 @@ def test_indexer_forward_selects_like_the_reference_chain():
         same = (k_cache[:end].cpu().view(torch.uint8) == ref_k[:end].view(torch.uint8)).all(dim=1)
         assert float(same.float().mean()) >= 0.5
         assert torch.equal(ks_cache[:end].cpu()[same], ref_ks[:end][same])
+
+
+def test_fp8_index_batched_equals_one_call_per_sequence(ops):
+    """Three sequences with caches of their own (rows of longer buffers) in one launch."""
+    batch, keys, max_len, heads = 3, 300, 384, 64
+    seqs = [_cuda(I.indexer_inputs(1, keys, heads=heads, seed=40 + b)) for b in range(batch)]
+    q = torch.cat([d["q"] for d in seqs])                     # [B, 1, H, 128]
+    wts = torch.cat([d["weights"] for d in seqs])             # [B, 1, H]
+    k_cache = torch.zeros(batch, max_len, 128, dtype=torch.float8_e4m3fn, device="cuda")
+    ks_cache = torch.zeros(batch, max_len, device="cuda")
+    for b, d in enumerate(seqs):
+        k_cache[b, :keys] = d["k"][0]
+        ks_cache[b, :keys] = d["k_scale"][0]
+    got = ops.fp8_index(q, wts, k_cache[:, :keys], ks_cache[:, :keys])
+    ops.tc_error_state()
+    assert got.shape == (batch, 1, keys)
+    for b, d in enumerate(seqs):
+        one = ops.fp8_index(d["q"], d["weights"], d["k"], d["k_scale"])
+        assert torch.equal(got[b], one[0])
+
+
+def test_indexer_decode_equals_the_single_sequence_path():
+    """A decode step of four sequences in one go picks what four single-sequence calls pick."""
+    from racetrack_b200 import indexer, ops
+    dim, q_lora, heads, topk, batch, start, max_len = 1024, 256, 64, 128, 4, 299, 384
+    g = torch.Generator().manual_seed(78)
+    mk = lambda *s, std=1.0: (torch.randn(*s, generator=g) * std)
+    w = indexer.IndexerWeights(mk(heads * 128, q_lora, std=0.06).bfloat16().cuda(),
+                               mk(128, dim, std=0.03).bfloat16().cuda(), (1 + mk(128, std=0.02)).cuda(),
+                               mk(128, std=0.02).cuda(), mk(heads, dim, std=0.03).cuda())
+    table = R.precompute_freqs_cis(64, 16384).cuda()
+    k_cache = (mk(batch, max_len, 128) * 2).cuda().to(torch.float8_e4m3fn)
+    ks_cache = (mk(batch, max_len).abs() * 0.01 + 0.005).cuda()
+    x, qr = mk(batch, dim).bfloat16().cuda(), mk(batch, q_lora).bfloat16().cuda()
+    k1, s1 = k_cache.clone(), ks_cache.clone()
+    idx = indexer.indexer_decode(x, qr, w, k_cache, ks_cache, start, table, topk)
+    ops.tc_error_state()
+    assert idx.shape == (batch, topk) and idx.dtype == torch.int32
+    for b in range(batch):
+        one = indexer.indexer_forward(x[b:b + 1], qr[b:b + 1], w, k1[b], s1[b], start, table, topk)
+        assert torch.equal(idx[b], one[0])
+    assert torch.equal(k_cache.view(torch.uint8), k1.view(torch.uint8))
+    assert torch.equal(ks_cache, s1)

@@ -263,3 +263,36 @@ def test_indexer_key_prologue_matches_reference(golden_small, same_cpu_as_golden
     assert codes.shape == (9, 1, 128) and scales.shape == (9, 1)
     c2, s2 = R.act_quant(rotated)
     assert torch.equal(codes.view(torch.uint8), c2.view(torch.uint8)) and torch.equal(scales, s2.squeeze(-1))
+
+
+def test_mla_decode_matches_reference(golden_small, same_cpu_as_golden):
+    """The whole decode branch of MLA.forward (projections, cache append, absorbed scores, index
+    mask, softmax, value projection, wo) against racetrack's own module run with a fixed
+    selection in place of the indexer; and the fp32 attention core the GPU kernel is tested
+    against agrees with that bf16 flow to bf16 accuracy."""
+    c = I.MLA_DECODE
+    d = I.mla_decode_inputs()
+    fc = R.precompute_freqs_cis(c["rope"], c["max_len"])[c["start_pos"]:c["start_pos"] + 1]
+    kv_cache, pe_cache = d["kv_cache"].clone(), d["pe_cache"].clone()
+    y = R.mla_decode(d["x"], c["start_pos"], fc, d["w"], kv_cache, pe_cache, d["topk_indices"],
+                     heads=c["heads"], nope=c["nope"], rope=c["rope"], v_dim=c["v_dim"])
+    for got, key in ((y, "mla_decode.out"), (kv_cache[:, c["start_pos"]], "mla_decode.kv_row"),
+                     (pe_cache[:, c["start_pos"]], "mla_decode.pe_row")):
+        if same_cpu_as_golden:
+            assert_bit_exact(got, golden_small[key], key)
+        else:
+            assert_close_bf16(got, golden_small[key], key, ulps=2)
+    # the fp32 core (oracle of rt_mla_sparse_decode) against the bf16 flow, value projection aside
+    end = c["start_pos"] + 1
+    g = torch.Generator().manual_seed(5)
+    q_abs = torch.randn(c["batch"], c["heads"], c["kv_lora"], generator=g).mul(0.3).bfloat16()
+    q_pe = torch.randn(c["batch"], c["heads"], c["rope"], generator=g).mul(0.3).bfloat16()
+    scale = (c["nope"] + c["rope"]) ** -0.5
+    core = R.mla_sparse_decode(q_abs, q_pe, kv_cache[:, :end], pe_cache[:, :end],
+                               d["topk_indices"][:, 0], scale)
+    scores = (torch.einsum("bhc,btc->bht", q_abs, kv_cache[:, :end]) +
+              torch.einsum("bhr,btr->bht", q_pe, pe_cache[:, :end])) * scale
+    mask = torch.full((c["batch"], 1, end), float("-inf"), dtype=scores.dtype).scatter_(
+        -1, d["topk_indices"][:, 0:1, :].reshape(c["batch"], 1, -1), 0)
+    flow = torch.einsum("bht,btc->bhc", (scores + mask).softmax(dim=-1), kv_cache[:, :end])
+    assert float((core - flow.float()).abs().max()) <= 3e-2 * float(core.abs().max())
