@@ -116,12 +116,15 @@ class PrefillStackWorkload:
     scaling = "strong"
     dominant = "gemm_nvfp4_kernel[experts w13]"
     ffn = "moe"          # "dense": the first-three-layers variant (SwiGLU FFN of width 18432)
+    default_tokens = 8192
 
     def __init__(self, device, rank: int, world: int, args):
         from racetrack_b200 import layer, moe, ops
         self.layer_mod, self.moe, self.ops = layer, moe, ops
         self.device, self.rank, self.world = device, rank, world
         self.tokens, self.layers = args.tokens, args.layers
+        if self.default_tokens != 8192 and args.tokens == 8192:
+            self.tokens = self.default_tokens         # --tokens was not given
         self.shape = layer.DSV32
         self.ffn = args.ffn
         if self.ffn == "dense":
@@ -132,7 +135,7 @@ class PrefillStackWorkload:
         self.proj = args.proj
         self.schedule = args.nvfp4_schedule
         ops.gemm_nvfp4_schedule({"auto": 0, "single": 1, "pair": 2}[self.schedule])
-        pairs_local = args.tokens * self.shape.topk // world
+        pairs_local = self.tokens * self.shape.topk // world
         uses_pairs = self.schedule == "pair" or (
             self.schedule == "auto" and pairs_local >= 128 * (self.shape.n_experts // world))
         self.dominant = ("gemm_nvfp4_pair_kernel" if uses_pairs else "gemm_nvfp4_kernel") + \
@@ -140,7 +143,7 @@ class PrefillStackWorkload:
         if self.ffn == "dense":
             fp8 = args.proj in ("fp8", "mixed")
             self.dominant = ("gemm_fp8_kernel" if fp8 else "gemm_bf16_pair_kernel") + "[dense w13]"
-        self.model = layer.RealisticLayer(self.shape, w, rank, world, ffn=self.ffn, proj=args.proj)
+        self.model = self._build_model(w, args)
         gen = torch.Generator(device=device)
         gen.manual_seed(self.shape.seed)
         self.hidden = torch.empty(self.tokens, self.shape.hidden, device=device, dtype=torch.bfloat16)
@@ -148,6 +151,13 @@ class PrefillStackWorkload:
         self.positions = torch.arange(self.tokens, device=device, dtype=torch.int64)
         self.dom_events = []
         self._wrap_dominant()
+
+    def _build_model(self, w, args):
+        return self.layer_mod.RealisticLayer(self.shape, w, self.rank, self.world, ffn=self.ffn,
+                                             proj=args.proj)
+
+    def _forward(self, hidden):
+        return self.model.forward_stack(hidden, self.positions, self.layers)
 
     def _wrap_dominant(self):
         """CUDA events around every first expert GEMM (w13) of the timed region."""
@@ -270,12 +280,12 @@ class PrefillStackWorkload:
         side = torch.cuda.Stream()
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
-            self.model.forward_stack(self.hidden, self.positions, self.layers)
+            self._forward(self.hidden)
         torch.cuda.current_stream().wait_stream(side)
         before = _lib.launch_count()
         self.graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(self.graph):
-            self.graph_out = self.model.forward_stack(self.hidden, self.positions, self.layers)
+            self.graph_out = self._forward(self.hidden)
         self.launches_per_replay = _lib.launch_count() - before
 
     def step(self, record: bool = False):
@@ -283,7 +293,7 @@ class PrefillStackWorkload:
             self.graph.replay()
             return self.graph_out
         self.recording = record
-        out = self.model.forward_stack(self.hidden, self.positions, self.layers)
+        out = self._forward(self.hidden)
         self.recording = False
         return out
 
@@ -300,7 +310,7 @@ class PrefillStackWorkload:
             self.host_out.copy_(self.graph_out, non_blocking=True)
             return self.graph_out
         self.dev_in.copy_(self.host_in, non_blocking=True)
-        out = self.model.forward_stack(self.dev_in, self.positions, self.layers)
+        out = self._forward(self.dev_in)
         self.host_out.copy_(out, non_blocking=True)
         return out
 
@@ -556,7 +566,89 @@ class SwigluQuantWorkload:
         return run, sample_tokens
 
 
-WORKLOADS = {w.name: w for w in (PrefillStackWorkload, MoeLayerWorkload, SwigluQuantWorkload)}
+# ---------------------------------------------------------------------------
+# workload: decode step of the layer (B sequences, one token each, caches of 4096 positions,
+# sparse indexer + sparse attention, NVFP4 experts)
+# ---------------------------------------------------------------------------
+
+class DecodeLayerWorkload(PrefillStackWorkload):
+    """`tokens` sequences decode one token each through `layers` applications of the layer; every
+    sequence has a latent / rope / indexer cache of `cache_len` positions ~ N(0, 1), the indexer
+    keeps 2048 of them. Heads and experts are sharded as in the prefill stack; the token batch and
+    the (head-shared) latent caches are replicated on every rank."""
+    name = "dsv3_2_decode_layer"
+    cache_len = 4096
+    default_tokens = 64
+
+    def _build_model(self, w, args):
+        from racetrack_b200 import decode
+        self.decode = decode
+        self.start_pos = self.cache_len - 1
+        caches = decode.DecodeCaches(self.shape, self.tokens, self.cache_len, self.device,
+                                     fill=self.start_pos)
+        iw = decode.make_indexer_weights(self.shape, self.device, std=0.02)
+        return decode.DecodeLayer(self.shape, w, self.rank, self.world, index_weights=iw,
+                                  caches=caches, proj=args.proj)
+
+    def _forward(self, hidden):
+        return self.model.decode_stack(hidden, self.start_pos, self.layers)
+
+    @property
+    def dominant_traffic(self):
+        return None
+
+    def config(self) -> dict:
+        c = super().config()
+        c.update({"workload": self.name, "sequences": self.tokens, "cache_len": self.cache_len,
+                  "index_heads": self.decode.INDEX_HEADS, "index_topk": self.decode.INDEX_TOPK,
+                  "attention_core": "rt_mla_sparse_decode (tcgen05, this backend)",
+                  "l2_policy": "inputs_exceed_l2 at 64 sequences (every layer reads the touched "
+                               "experts' weights, up to 6.3 GB, and 151 MB of selected cache rows); "
+                               "below that the touched experts alone exceed the 126 MB L2 from "
+                               "4 sequences on"})
+        return c
+
+    @staticmethod
+    def cpu_runner(sample_tokens: int):
+        """The reference's decode branch (oracle/ref_layer.py decode_stack) for `sample_tokens`
+        sequences, one layer, full width, caches of 4096 positions."""
+        from oracle import ref_layer, ref_ops as R
+        from racetrack_b200 import layer
+        shape = layer.DSV32
+        L = DecodeLayerWorkload.cache_len
+        start = L - 1
+        g = torch.Generator().manual_seed(shape.seed)
+        b = sample_tokens
+        hidden = (torch.randn(b, shape.hidden, generator=g) * 0.01).to(torch.bfloat16)
+        w = layer.make_weights(shape, 0, 1, "cpu", ffn="none", std=0.02)
+        mk = lambda *s, std=1.0: torch.randn(*s, generator=g) * std
+        iw = {"wq_b": mk(64 * 128, shape.q_lora, std=0.02).bfloat16(),
+              "wk": mk(128, shape.hidden, std=0.02).bfloat16(), "k_norm_weight": torch.ones(128),
+              "k_norm_bias": torch.zeros(128), "weights_proj": mk(64, shape.hidden, std=0.02)}
+        keys, scales = R.act_quant(mk(b, L, 128).bfloat16())
+        caches = {"kv": mk(b, L, shape.kv_lora).bfloat16(), "pe": mk(b, L, shape.rope).bfloat16(),
+                  "index_k": keys, "index_scale": scales.squeeze(-1).contiguous()}
+        freqs = R.precompute_freqs_cis(shape.rope, L)
+        w["w13"] = torch.empty(shape.n_experts, 2 * shape.moe_inter, shape.hidden, dtype=torch.bfloat16)
+        w["w2"] = torch.empty(shape.n_experts, shape.hidden, shape.moe_inter, dtype=torch.bfloat16)
+        drawn = set()
+
+        def run():
+            # experts are drawn when the routing of this sample first asks for them
+            ones = torch.ones(shape.hidden, dtype=torch.bfloat16)
+            h = R.rms_norm(hidden, ones, shape.eps)
+            mid = hidden + ref_layer.decode_attention(h, start, w, iw, caches, shape, shape.heads,
+                                                      freqs, 2048)
+            logits = torch.nn.functional.linear(R.rms_norm(mid, ones, shape.eps).float(), w["w_gate"].float())
+            for e in set(torch.topk(logits, shape.topk, dim=-1)[1].flatten().tolist()) - drawn:
+                w["w13"][e], w["w2"][e] = layer.draw_expert(shape, e, "cpu", std=0.02)
+                drawn.add(e)
+            return ref_layer.decode_stack(hidden, start, [w], iw, [caches], shape, 1, freqs, 2048)
+        return run, sample_tokens * 1
+
+
+WORKLOADS = {w.name: w for w in (PrefillStackWorkload, MoeLayerWorkload, SwigluQuantWorkload,
+                                 DecodeLayerWorkload)}
 DEFAULT_WORKLOAD = PrefillStackWorkload.name
 
 

@@ -534,7 +534,7 @@ int rt_index_topk(const float* scores, int32_t* indices, int64_t queries, int64_
  * bf16 [batch, heads, 512] contiguous (the caller applies the value half of wkv_b).
  * splits = rt_mla_sparse_decode_splits(batch, heads, n_sel) partial results are merged by a
  * second kernel; the caller provides part_o fp32 [batch * splits * heads * 512] and part_ml fp32
- * [batch * splits * heads * 2]. heads: 8, 16, 24, 32 or a multiple of 32; all strides multiples
+ * [batch * splits * heads * 2]. heads: a multiple of 8 up to 64, or a multiple of 64; all strides multiples
  * of 8 elements; pointers 16-byte aligned. No allocation, no host synchronisation.
  * ref: racetrack/models/deepseek.py:793-810 (MLA.forward, "MQA decode").
  */

@@ -9,19 +9,28 @@
 // [batch, keys, 512], pe the rope cache [batch, keys, 64]; the value half of wkv_b is applied to
 // `out` by the caller.
 //
-// Work item = (sequence b, split of the selected keys, group of G <= 32 heads, half of the 512
-// output dims); one CTA each. Per tile of 64 selected keys:
-//   loaders   gather the 64 cache rows (1152 bytes each: 1024 latent + 128 rope) with 16-byte
-//             cp.async copies into nine 64-dim column blocks [64 keys][128 B], 128-byte swizzle;
-//   S = Q K^T 36 tcgen05.mma (M = 128 head rows of which G are real, N = 64 keys, K = 16 dims),
+// Work item = (sequence b, split of the selected keys, group of G <= 64 heads); one CTA each.
+// Per tile of 32 selected keys:
+//   loaders   gather the 32 cache rows (1152 bytes each: 1024 latent + 128 rope) with 16-byte
+//             cp.async copies into nine 64-dim column blocks [32 keys][128 B], 128-byte swizzle,
+//             a ring of 4 tiles (3 when G > 32). What bounds this kernel is the gather: the
+//             load/store path of one SM sustains about 12 B/clk for it (measured; it keeps about
+//             8 KB in flight), so the ring only has to keep that path busy all the time;
+//   S = Q K^T 36 tcgen05.mma (M = 128 head rows of which G are real, N = 32 keys, K = 16 dims),
 //             the tile read as a K-major B operand;
-//   softmax   one thread per head row: tcgen05.ld of its 64 scores, running maximum with a lazy
+//   softmax   one thread per head row: tcgen05.ld of its 32 scores, running maximum with a lazy
 //             rescale (the accumulator is only rescaled when the maximum grows by more than 2^8),
 //             P = exp2(s - m) as bf16 into shared memory (K-major A operand);
-//   O += P V  4 tcgen05.mma (N = 256 dims, K = 16 keys) reading THE SAME shared-memory tile as an
-//             MN-major B operand (dims contiguous): the gathered rows are staged once.
-// Tensor memory: O in columns [0, 256), two S buffers of 64 columns behind it; QK^T of tile t + 1
-// is issued before P V of tile t, so the tensor core computes scores while the softmax runs.
+//   O += P V  tcgen05.mma (N = 256 dims, K = 16 keys) reading THE SAME shared-memory tile as an
+//             MN-major B operand (dims contiguous): the gathered rows are staged once. The 512
+//             output dims would fill all of tensor memory as columns, so they are folded into the
+//             LANES instead: P occupies 64 rows with a block of 64 zero rows before and behind
+//             it; the MMA whose A operand starts at P writes dims [0, 256) of head r to lane r
+//             (and adds zeros to lanes 64-127), the MMA whose A operand starts at the zero block
+//             before P writes dims [256, 512) to lane 64 + r, both into the same 256 columns.
+// Tensor memory: O in columns [0, 256), two S buffers of 32 columns behind it. One thread issues
+// all MMAs and takes whichever is ready first, the scores of the next landed tile or P V of the
+// tile whose probabilities are written, so the tensor core computes scores while the softmax runs.
 // Each CTA leaves an unnormalised fp32 partial (O, running maximum, denominator); a second kernel
 // merges the splits. Every wait is bounded (rt_tc.cuh).
 #include "rt_tc.cuh"
@@ -29,25 +38,27 @@
 namespace rt {
 namespace tc {
 
-constexpr int kATile = 64;                          // keys per tile
+constexpr int kATile = 32;                          // keys per tile
 constexpr int kABlocks = 9;                         // 64-dim column blocks of a cache row (8 latent + 1 rope)
-constexpr int kAMaxG = 32;                          // head rows staged per CTA
-constexpr uint32_t kAPBytes = 128 * 128;            // P: 128 rows x 64 keys bf16
-constexpr uint32_t kAQBytes = kABlocks * kAMaxG * 128;
+constexpr int kAMaxG = 64;                          // head rows staged per CTA
+constexpr int kAMaxStages = 4;
+constexpr uint32_t kAPOffset = 64 * 128;            // 64 zero rows | P: 64 rows of 128 bytes | 64 zero rows
 constexpr uint32_t kAKBytes = kABlocks * kATile * 128;
-constexpr uint32_t kAQOffset = kAPBytes;
-constexpr uint32_t kAKOffset = kAQOffset + kAQBytes;
-constexpr uint32_t kABarOffset = kAKOffset + 2 * kAKBytes;
-constexpr int kABarriers = 9;                       // qfull, kfull[2], kfree[2], sfull[2], pfull, pfree
-constexpr uint32_t kASmemBytes = kABarOffset + kABarriers * 8 + 16 + 1024;
+constexpr uint32_t kAQOffset = 3 * 64 * 128;
+// the tile ring follows the G staged head rows: 4 tiles for G <= 32, 3 for G = 64
+constexpr uint32_t kABarOffset = kAQOffset + kABlocks * 32 * 128 + kAMaxStages * kAKBytes;
+constexpr int kABarriers = 1 + 2 * kAMaxStages + 2 + 2 + 2;   // qfull, kfull[4], kfree[4], sfull[2], pfull, pfree, afull[2]
+constexpr uint32_t kAAlphaOffset = kABarOffset + kABarriers * 8 + 16;   // rescale factors [2][64] + flags [2][2]
+constexpr uint32_t kASmemBytes = kAAlphaOffset + 2 * 64 * 4 + 16 + 1024;
 constexpr int kAThreads = 512;
 constexpr int kALoaders = 256;                      // warps 8..15
 constexpr uint32_t kATmemCols = 512;
 constexpr uint32_t kATmemS = 256;                   // first score column
-// fp32 accumulate, bf16 x bf16, M = 128; S: both K-major, N = 64; O: B MN-major, N = 256
-constexpr uint32_t kASIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (8u << 17) | (8u << 24);
+// fp32 accumulate, bf16 x bf16, M = 128; S: both K-major, N = 32; O: B MN-major, N = 256
+constexpr uint32_t kASIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((kATile >> 3) << 17) | (8u << 24);
 constexpr uint32_t kAOIdesc = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (32u << 17) | (8u << 24);
-static_assert(kAKOffset % 1024 == 0 && kAKBytes % 1024 == 0, "swizzle atoms are 1024-byte aligned");
+static_assert(kAKBytes % 1024 == 0 && kAQOffset % 1024 == 0, "swizzle atoms are 1024-byte aligned");
+static_assert(kAQOffset + kABlocks * 64 * 128 + 3 * kAKBytes <= kABarOffset, "G = 64 leaves room for 3 tiles");
 static_assert(kASmemBytes <= 232448, "shared memory budget");
 
 // Shared-memory descriptor of an MN-major operand stored with the 128-byte swizzle: a 128-byte
@@ -70,6 +81,16 @@ __device__ __forceinline__ void cp_async_wait() {
     asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
+// Optional pipeline trace (never compiled into the library): with -DRT_ATTN_TRACE the CTA
+// (0, 0, 0) stamps clock64() at eight points of its first 64 tiles.
+#ifdef RT_ATTN_TRACE
+__device__ long long g_attn_trace[8 * 64];
+#define RT_ATRACE(ev, it) \
+    do { if ((blockIdx.x | blockIdx.y | blockIdx.z) == 0 && (it) < 64) g_attn_trace[(ev) * 64 + (it)] = clock64(); } while (0)
+#else
+#define RT_ATRACE(ev, it) do { } while (0)
+#endif
+
 struct AttnArgs {
     const __nv_bfloat16* q_abs;   // [batch, heads, 512]
     const __nv_bfloat16* q_pe;    // [batch, heads, 64]
@@ -90,9 +111,10 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
     const uint32_t bars = base + kABarOffset;
     const uint32_t qfull = bars;
     auto kfull = [&](int s) { return bars + 8u * (1 + s); };
-    auto kfree = [&](int s) { return bars + 8u * (3 + s); };
-    auto sfull = [&](int s) { return bars + 8u * (5 + s); };
-    const uint32_t pfull = bars + 8u * 7, pfree = bars + 8u * 8;
+    auto kfree = [&](int s) { return bars + 8u * (1 + kAMaxStages + s); };
+    auto sfull = [&](int s) { return bars + 8u * (1 + 2 * kAMaxStages + s); };
+    const uint32_t pfull = bars + 8u * (3 + 2 * kAMaxStages), pfree = pfull + 8u;
+    auto afull = [&](int s) { return pfree + 8u * (1 + s); };
     const uint32_t slot = bars + 8u * kABarriers;
     volatile uint32_t* slot_ptr =
         reinterpret_cast<volatile uint32_t*>(base_ptr + kABarOffset + 8 * kABarriers);
@@ -100,9 +122,11 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int split = blockIdx.x;
-    const int half = blockIdx.y & 1, hg = blockIdx.y >> 1;
+    const int hg = blockIdx.y;
     const int b = blockIdx.z;
     const int G = a.group;
+    const int stages = G > 32 ? 3 : kAMaxStages;
+    const uint32_t k_off = kAQOffset + static_cast<uint32_t>(kABlocks * (G > 32 ? 64 : 32) * 128);
     const int total_tiles = (a.n_sel + kATile - 1) / kATile;
     const int tile0 = split * a.tiles_per_split;
     const int n_tiles = min(a.tiles_per_split, total_tiles - tile0);
@@ -111,10 +135,13 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         mbar_init(qfull, kALoaders);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < kAMaxStages; ++s) {
             mbar_init(kfull(s), kALoaders);
             mbar_init(kfree(s), 1);
+        }
+        for (int s = 0; s < 2; ++s) {
             mbar_init(sfull(s), 1);
+            mbar_init(afull(s), 2);          // lane 0 of the two softmax warps
         }
         mbar_init(pfull, 4);
         mbar_init(pfree, 1);
@@ -132,130 +159,171 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
     if (warp == 0) {
         if (lane == 0 && n_tiles > 0) {
             bool ok = mbar_wait(qfull, 0, abort_flag, 61);
-            auto issue_qk = [&](int t) {
-                const uint32_t kb = base + kAKOffset + (t & 1) * kAKBytes;
-                const uint32_t d = tmem_base + kATmemS + static_cast<uint32_t>(t & 1) * 64u;
-#pragma unroll
-                for (int cb = 0; cb < kABlocks; ++cb) {
-                    const uint64_t adesc = smem_desc_sw128(base + kAQOffset + cb * G * 128);
-                    const uint64_t bdesc = smem_desc_sw128(kb + cb * (kATile * 128));
-#pragma unroll
-                    for (int j = 0; j < 4; ++j)
-                        mma_f16(d, adesc + 2u * j, bdesc + 2u * j, kASIdesc, (cb | j) != 0 ? 1u : 0u);
-                }
-                mma_commit(sfull(t & 1));
-            };
-            if (ok && (ok = mbar_wait(kfull(0), 0, abort_flag, 62))) {
-                tc_fence_after();
-                issue_qk(0);
-            }
-            for (int t = 0; ok && t < n_tiles; ++t) {
-                if (t + 1 < n_tiles) {
-                    if (!(ok = mbar_wait(kfull((t + 1) & 1), ((t + 1) >> 1) & 1, abort_flag, 63))) break;
+            // Scores of tile q are issued as soon as its rows have landed and a score buffer is
+            // free (q - v < 2), P V of tile v as soon as its probabilities are written: whichever
+            // comes first, so neither the gather nor the softmax waits behind the other.
+            int q = 0, v = 0, qs = 0, vs = 0;          // tile counters and their ring slots
+            uint32_t qphase = 0;
+            long long t0 = 0;
+            uint32_t spins = 0;
+            while (ok && v < n_tiles) {
+                bool progressed = false;
+                if (q < n_tiles && q - v < 2 && mbar_try_wait(kfull(qs), qphase)) {
                     tc_fence_after();
-                    issue_qk(t + 1);
-                }
-                if (!(ok = mbar_wait(pfull, t & 1, abort_flag, 64))) break;
-                tc_fence_after();
-                const uint32_t kb = base + kAKOffset + (t & 1) * kAKBytes + half * 4 * (kATile * 128);
-                const uint64_t adesc = smem_desc_sw128(base);
+                    RT_ATRACE(0, q);
+                    const uint32_t kb = base + k_off + qs * kAKBytes;
+                    const uint32_t d = tmem_base + kATmemS + static_cast<uint32_t>(q & 1) * kATile;
 #pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                    const uint64_t bdesc = smem_desc_sw128_mn(kb + j * 2048, kATile * 128);
-                    mma_f16(tmem_base, adesc + 2u * j, bdesc, kAOIdesc, (t | j) != 0 ? 1u : 0u);
+                    for (int cb = 0; cb < kABlocks; ++cb) {
+                        const uint64_t adesc = smem_desc_sw128(base + kAQOffset + cb * G * 128);
+                        const uint64_t bdesc = smem_desc_sw128(kb + cb * (kATile * 128));
+#pragma unroll
+                        for (int j = 0; j < 4; ++j)
+                            mma_f16(d, adesc + 2u * j, bdesc + 2u * j, kASIdesc, (cb | j) != 0 ? 1u : 0u);
+                    }
+                    mma_commit(sfull(q & 1));
+                    ++q;
+                    if (++qs == stages) {
+                        qs = 0;
+                        qphase ^= 1u;
+                    }
+                    progressed = true;
                 }
-                mma_commit(kfree(t & 1));
-                mma_commit(pfree);
+                if (v < q && mbar_try_wait(pfull, v & 1)) {
+                    RT_ATRACE(1, v);
+                    tc_fence_after();
+                    const uint32_t kb = base + k_off + vs * kAKBytes;
+                    const uint64_t a_lo = smem_desc_sw128(base + kAPOffset);      // [P; zeros]
+                    const uint64_t a_hi = smem_desc_sw128(base);                  // [zeros; P]
+#pragma unroll
+                    for (int j = 0; j < kATile / 16; ++j) {
+                        const uint64_t b_lo = smem_desc_sw128_mn(kb + j * 2048, kATile * 128);
+                        const uint64_t b_hi = smem_desc_sw128_mn(kb + 4 * (kATile * 128) + j * 2048, kATile * 128);
+                        mma_f16(tmem_base, a_lo + 2u * j, b_lo, kAOIdesc, (v | j) != 0 ? 1u : 0u);
+                        mma_f16(tmem_base, a_hi + 2u * j, b_hi, kAOIdesc, 1u);
+                    }
+                    mma_commit(kfree(vs));
+                    mma_commit(pfree);
+                    RT_ATRACE(2, v);
+                    ++v;
+                    if (++vs == stages) vs = 0;
+                    progressed = true;
+                }
+                if (progressed) {
+                    spins = 0;
+                } else if ((++spins & 63u) == 0) {
+                    // bounded like mbar_wait: give up after the cycle budget or when another
+                    // thread of the CTA already has
+                    if (spins == 64) t0 = clock64();
+                    if (*abort_flag) ok = false;
+                    else if (clock64() - t0 > kWaitCycles) {
+                        *abort_flag = 63;
+                        atomicCAS(&g_tc_error, 0, 63);
+                        ok = false;
+                    }
+                }
             }
         }
         __syncwarp();
     } else if (warp >= 4 && warp < 8) {
-        // softmax: thread = head row
+        // Softmax (warps 4, 5: thread = head row, lanes 0-63 of tensor memory) and the keepers of
+        // lanes 64-127 (warps 6, 7: the upper 256 dims of the same heads), which only take part
+        // in rescaling and in the final read-out.
         const int quad = warp & 3;
-        const int row = quad * 32 + lane;
+        const int row = (quad & 1) * 32 + lane;            // head row within the group
+        const bool upper = quad >= 2;
         const bool live = row < G && hg * G + row < a.heads;
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-        float m_ref = __int_as_float(0xff800000), l = 0.f;
+        const float ninf = __int_as_float(0xff800000);
+        float* alpha_s = reinterpret_cast<float*>(base_ptr + kAAlphaOffset);       // [2][64]
+        volatile int* grow_s = reinterpret_cast<volatile int*>(alpha_s + 128);     // [2][2]
+        float m_ref = ninf, l = 0.f;
         bool ok = n_tiles > 0;
         for (int t = 0; ok && t < n_tiles; ++t) {
-            // which of the tile's 64 slots hold a key
-            const int j0 = (tile0 + t) * kATile + lane, j1 = j0 + 32;
-            bool v0 = j0 < a.n_sel, v1 = j1 < a.n_sel;
-            if (idx_row) {
-                if (v0) { const int k = __ldg(idx_row + j0); v0 = k >= 0 && k < a.keys; }
-                if (v1) { const int k = __ldg(idx_row + j1); v1 = k >= 0 && k < a.keys; }
-            }
-            const uint32_t mask0 = __ballot_sync(0xffffffffu, v0), mask1 = __ballot_sync(0xffffffffu, v1);
-            if (!(ok = mbar_wait(sfull(t & 1), (t >> 1) & 1, abort_flag, 65))) break;
-            tc_fence_after();
-            uint32_t r0[32], r1[32];
-            const uint32_t taddr = tmem_base + lane_base + kATmemS + static_cast<uint32_t>(t & 1) * 64u;
-            tmem_ld_32x32(taddr, r0);
-            tmem_ld_32x32(taddr + 32, r1);
-            tmem_ld_wait(r0);
-            tmem_ld_wait(r1);
-            const float ninf = __int_as_float(0xff800000);
-            float mt = ninf;
+            float alpha = 1.f;
+            uint32_t packed[16];
+            if (!upper) {
+                // which of the tile's 32 slots hold a key
+                const int j0 = (tile0 + t) * kATile + lane;
+                bool v0 = j0 < a.n_sel;
+                if (idx_row && v0) {
+                    const int k = __ldg(idx_row + j0);
+                    v0 = k >= 0 && k < a.keys;
+                }
+                const uint32_t mask0 = __ballot_sync(0xffffffffu, v0);
+                if (!(ok = mbar_wait(sfull(t & 1), (t >> 1) & 1, abort_flag, 65))) break;
+                if (threadIdx.x == 128) RT_ATRACE(3, t);
+                tc_fence_after();
+                uint32_t r0[32];
+                tmem_ld_32x32(tmem_base + lane_base + kATmemS + static_cast<uint32_t>(t & 1) * kATile, r0);
+                tmem_ld_wait(r0);
+                float mt = ninf;
 #pragma unroll
-            for (int i = 0; i < 32; ++i) {
-                const float s0 = (live && ((mask0 >> i) & 1u)) ? __uint_as_float(r0[i]) * a.scale_log2 : ninf;
-                const float s1 = (live && ((mask1 >> i) & 1u)) ? __uint_as_float(r1[i]) * a.scale_log2 : ninf;
-                r0[i] = __float_as_uint(s0);
-                r1[i] = __float_as_uint(s1);
-                mt = fmaxf(mt, fmaxf(s0, s1));
-            }
-            const bool grow = mt > m_ref + 8.f;          // false while mt is -inf
-            const float m_new = grow ? mt : m_ref;
-            const float alpha = grow ? exp2f(m_ref - m_new) : 1.f;     // exp2f(-inf) = 0 on the first tile
-            const float m_use = m_new == ninf ? 0.f : m_new;
-            float sum = 0.f;
-            uint32_t packed[32];
+                for (int i = 0; i < 32; ++i) {
+                    const float s0 = (live && ((mask0 >> i) & 1u)) ? __uint_as_float(r0[i]) * a.scale_log2 : ninf;
+                    r0[i] = __float_as_uint(s0);
+                    mt = fmaxf(mt, s0);
+                }
+                const bool grow = mt > m_ref + 8.f;          // false while mt is -inf
+                const float m_new = grow ? mt : m_ref;
+                alpha = grow ? exp2f(m_ref - m_new) : 1.f;   // exp2f(-inf) = 0 on the first tile
+                const float m_use = m_new == ninf ? 0.f : m_new;
+                float sum = 0.f;
 #pragma unroll
-            for (int i = 0; i < 16; ++i) {
-                const float p0 = exp2f(__uint_as_float(r0[2 * i]) - m_use);
-                const float p1 = exp2f(__uint_as_float(r0[2 * i + 1]) - m_use);
-                const float p2 = exp2f(__uint_as_float(r1[2 * i]) - m_use);
-                const float p3 = exp2f(__uint_as_float(r1[2 * i + 1]) - m_use);
-                sum += (p0 + p1) + (p2 + p3);
-                __nv_bfloat162 lo = __floats2bfloat162_rn(p0, p1), hi = __floats2bfloat162_rn(p2, p3);
-                packed[i] = *reinterpret_cast<uint32_t*>(&lo);
-                packed[16 + i] = *reinterpret_cast<uint32_t*>(&hi);
+                for (int i = 0; i < 16; ++i) {
+                    const float p0 = exp2f(__uint_as_float(r0[2 * i]) - m_use);
+                    const float p1 = exp2f(__uint_as_float(r0[2 * i + 1]) - m_use);
+                    sum += p0 + p1;
+                    __nv_bfloat162 pk = __floats2bfloat162_rn(p0, p1);
+                    packed[i] = *reinterpret_cast<uint32_t*>(&pk);
+                }
+                l = l * alpha + sum;
+                m_ref = m_new;
+                alpha_s[(t & 1) * 64 + row] = alpha;
+                const bool any = __any_sync(0xffffffffu, grow);
+                if (lane == 0) grow_s[(t & 1) * 2 + quad] = any ? 1 : 0;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(afull(t & 1));
             }
-            l = l * alpha + sum;
-            m_ref = m_new;
+            // rescale factors and flags of this tile are visible to all four warps
+            if (!(ok = mbar_wait(afull(t & 1), (t >> 1) & 1, abort_flag, 69))) break;
             if (t > 0) {
                 // P V of the previous tile has retired: P may be overwritten, O is at rest
                 if (!(ok = mbar_wait(pfree, (t - 1) & 1, abort_flag, 66))) break;
                 tc_fence_after();
-                if (__any_sync(0xffffffffu, grow)) {
+                if (grow_s[(t & 1) * 2] | grow_s[(t & 1) * 2 + 1]) {
+                    const float al = alpha_s[(t & 1) * 64 + row];
 #pragma unroll 1
                     for (int c = 0; c < 8; ++c) {
                         uint32_t o[32];
                         tmem_ld_32x32(tmem_base + lane_base + c * 32, o);
                         tmem_ld_wait(o);
 #pragma unroll
-                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * al);
                         tmem_st_32x32(tmem_base + lane_base + c * 32, o);
                     }
                     tmem_st_wait();
                 }
             }
-            // P row: 64 bf16 = 8 chunks of 16 bytes, 128-byte swizzle
-            uint8_t* prow = base_ptr + row * 128;
+            if (!upper) {
+                // P row: 32 bf16 = 4 chunks of 16 bytes in a 128-byte swizzled row
+                uint8_t* prow = base_ptr + kAPOffset + row * 128;
 #pragma unroll
-            for (int c = 0; c < 8; ++c)
-                *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
-                    make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
-            fence_proxy_async();
+                for (int c = 0; c < 4; ++c)
+                    *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+                        make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
+                fence_proxy_async();
+            }
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(pfull);
+            if (threadIdx.x == 128) RT_ATRACE(4, t);
         }
         if (ok && n_tiles > 0 && (ok = mbar_wait(pfree, (n_tiles - 1) & 1, abort_flag, 67))) {
             tc_fence_after();
             const int head = hg * G + row;
             const int64_t prt = (static_cast<int64_t>(b) * a.splits + split) * a.heads + head;
-            float* po = a.part_o + prt * 512 + half * 256;
+            float* po = a.part_o + prt * 512 + (upper ? 256 : 0);
 #pragma unroll 1
             for (int c = 0; c < 8; ++c) {
                 uint32_t o[32];
@@ -267,7 +335,7 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
                         *reinterpret_cast<uint4*>(po + c * 32 + i) = make_uint4(o[i], o[i + 1], o[i + 2], o[i + 3]);
                 }
             }
-            if (live && half == 0) {
+            if (live && !upper) {
                 a.part_ml[prt * 2] = m_ref;
                 a.part_ml[prt * 2 + 1] = l;
             }
@@ -287,24 +355,29 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
                 cp_async16(base + kAQOffset + cb * G * 128 + r * 128 + ((j ^ (r & 7)) << 4), src);
             }
             cp_async_commit();
+            // the zero rows before and behind P
+            for (int c = lt; c < 2 * 64 * 8; c += kALoaders) {
+                const int blk = c >> 9, off = (c & 511) << 4;
+                *reinterpret_cast<uint4*>(base_ptr + (blk ? 2 * kAPOffset : 0) + off) = make_uint4(0u, 0u, 0u, 0u);
+            }
             cp_async_wait<0>();
             fence_proxy_async();
             mbar_arrive(qfull);
         }
         const __nv_bfloat16* kvb = a.kv + b * a.kv_bs;
         const __nv_bfloat16* peb = a.pe + b * a.pe_bs;
+        // Tile t goes into ring slot t % stages once P V of tile t - stages has retired. Its copies
+        // are committed as one group and tile t - 1 is published when ITS group has landed, so
+        // two tiles are in flight; a tile that is waited for never depends on a later one (the
+        // MMA thread takes scores and P V in whichever order they become ready).
         bool ok = true;
+        int ls = 0;
+        uint32_t lphase = 0;
         for (int t = 0; t < n_tiles; ++t) {
-            if (t > 0) {
-                // tile t - 1 has landed: publish it BEFORE waiting for a free buffer, because the
-                // buffer is freed by an MMA that is issued behind the scores of tile t - 1
-                cp_async_wait<0>();
-                fence_proxy_async();
-                mbar_arrive(kfull((t - 1) & 1));
-            }
-            if (!(ok = mbar_wait(kfree(t & 1), ((t >> 1) & 1) ^ 1u, abort_flag, 68))) break;
-            const uint32_t kb = base + kAKOffset + (t & 1) * kAKBytes;
-#pragma unroll 2
+            if (!(ok = mbar_wait(kfree(ls), lphase ^ 1u, abort_flag, 68))) break;
+            if (lt == 0) RT_ATRACE(5, t);
+            const uint32_t kb = base + k_off + ls * kAKBytes;
+#pragma unroll 3
             for (int c = lt; c < kATile * 72; c += kALoaders) {
                 const int r = c / 72, ch = c % 72, cb = ch >> 3, j = ch & 7;
                 const int slot_j = (tile0 + t) * kATile + r;
@@ -318,11 +391,22 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
                                  valid ? 16u : 0u);
             }
             cp_async_commit();
+            if (lt == 0) RT_ATRACE(6, t);
+            if (t > 0) {
+                cp_async_wait<1>();
+                fence_proxy_async();
+                mbar_arrive(kfull(ls == 0 ? stages - 1 : ls - 1));
+                if (lt == 0) RT_ATRACE(7, t - 1);
+            }
+            if (++ls == stages) {
+                ls = 0;
+                lphase ^= 1u;
+            }
         }
         cp_async_wait<0>();
         if (ok && n_tiles > 0) {
             fence_proxy_async();
-            mbar_arrive(kfull((n_tiles - 1) & 1));
+            mbar_arrive(kfull(ls == 0 ? stages - 1 : ls - 1));
         }
     }
     tc_fence_before();
@@ -380,10 +464,17 @@ int attn_error_take() {
 
 using namespace rt;
 
+#ifdef RT_ATTN_TRACE
+extern "C" int rt_attn_trace_read(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, tc::g_attn_trace, sizeof(long long) * 8 * 64) == cudaSuccess
+               ? RT_OK : RT_ERR_CUDA;
+}
+#endif
+
 extern "C" int64_t rt_mla_sparse_decode_splits(int64_t batch, int64_t heads, int64_t n_sel) {
     if (batch <= 0 || heads <= 0 || n_sel <= 0) return 1;
     const int64_t group = heads < tc::kAMaxG ? heads : tc::kAMaxG;
-    const int64_t per_split = batch * 2 * ((heads + group - 1) / group);
+    const int64_t per_split = batch * ((heads + group - 1) / group);
     const int64_t tiles = (n_sel + tc::kATile - 1) / tc::kATile;
     int64_t splits = (2 * 148 + per_split - 1) / per_split;
     if (splits > tiles) splits = tiles;
@@ -407,7 +498,7 @@ extern "C" int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const v
     RT_REQUIRE(q_abs && q_pe && kv && pe && out && part_o && part_ml, RT_ERR_BAD_ARG,
                "rt_mla_sparse_decode: null pointer");
     RT_REQUIRE(heads % 8 == 0 && (heads <= tc::kAMaxG || heads % tc::kAMaxG == 0), RT_ERR_UNSUPPORTED,
-               "rt_mla_sparse_decode: heads must be 8, 16, 24, 32 or a multiple of 32");
+               "rt_mla_sparse_decode: heads must be a multiple of 8 up to 64, or a multiple of 64");
     RT_REQUIRE(aligned16(q_abs) && aligned16(q_pe) && aligned16(kv) && aligned16(pe) && aligned16(part_o),
                RT_ERR_BAD_ARG, "rt_mla_sparse_decode: pointers must be 16-byte aligned");
     RT_REQUIRE(qa_batch_stride % 8 == 0 && qa_head_stride % 8 == 0 && qp_batch_stride % 8 == 0 &&
@@ -448,7 +539,7 @@ extern "C" int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const v
     a.group = static_cast<int>(heads < tc::kAMaxG ? heads : tc::kAMaxG);
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
     const int groups = static_cast<int>((heads + a.group - 1) / a.group);
-    dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(2 * groups), static_cast<unsigned>(batch));
+    dim3 grid(static_cast<unsigned>(splits), static_cast<unsigned>(groups), static_cast<unsigned>(batch));
     tc::mla_sparse_decode_kernel<<<grid, tc::kAThreads, tc::kASmemBytes, st>>>(a);
     count_launch();
     if (int rc = check_launch("mla_sparse_decode_kernel")) return rc;
