@@ -124,6 +124,16 @@ def cases(tokens: int) -> dict[str, tuple[Callable[[], object], int]]:
     wts = torch.rand(T, TOPK, device="cuda")
     out["fused_moe_combine"] = (lambda: ops.fused_moe_combine(eo, pp, wts, u),
                                 T * TOPK * HIDDEN * 2 + 2 * T * HIDDEN * 2)
+    # sparse MLA decode attention: min(T, 64) sequences, 2048 of 4096 cached positions each;
+    # algorithmic bytes = every selected cache row once + queries + output
+    B = min(T, 64)
+    kv, pe = _randn(B, 4096, KV_LORA), _randn(B, 4096, ROPE)
+    sel = torch.stack([torch.randperm(4096, device="cuda")[:2048].sort().values for _ in range(B)]).int()
+    for heads in (16, 128):
+        qa, qp = _randn(B, heads, KV_LORA) * 0.3, _randn(B, heads, ROPE) * 0.3
+        out[f"mla_sparse_decode[{B} seq x {heads} heads]"] = (
+            (lambda qa=qa, qp=qp: ops.mla_sparse_decode(qa, qp, kv, pe, sel, 192 ** -0.5)),
+            B * 2048 * (KV_LORA + ROPE) * 2 + B * heads * (2 * KV_LORA + ROPE) * 2)
     return out
 
 
