@@ -476,11 +476,23 @@ extern "C" int64_t rt_mla_sparse_decode_splits(int64_t batch, int64_t heads, int
     const int64_t group = heads < tc::kAMaxG ? heads : tc::kAMaxG;
     const int64_t per_split = batch * ((heads + group - 1) / group);
     const int64_t tiles = (n_sel + tc::kATile - 1) / tc::kATile;
-    int64_t splits = (2 * 148 + per_split - 1) / per_split;
-    if (splits > tiles) splits = tiles;
-    if (splits < 1) splits = 1;
-    const int64_t tps = (tiles + splits - 1) / splits;
-    return (tiles + tps - 1) / tps;          // every split owns at least one tile
+    // One CTA per SM at a time: the launch takes (waves of CTAs) x (tiles per CTA + the CTA's
+    // fixed cost: query rows, tensor-memory allocation, fp32 partials; about a tile and a half).
+    // Pick the split count that minimises it; every split owns at least one tile.
+    const int64_t sms = 148;
+    int64_t best = 1;
+    double best_cost = 1e30;
+    for (int64_t s = 1; s <= tiles && s <= 64; ++s) {
+        const int64_t tps = (tiles + s - 1) / s;
+        const int64_t eff = (tiles + tps - 1) / tps;
+        const int64_t waves = (per_split * eff + sms - 1) / sms;
+        const double cost = static_cast<double>(waves) * (static_cast<double>(tps) + 1.5) + 0.02 * eff;
+        if (cost < best_cost - 1e-9) {
+            best_cost = cost;
+            best = eff;
+        }
+    }
+    return best;
 }
 
 extern "C" int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const void* kv, const void* pe,
