@@ -579,6 +579,7 @@ class DecodeLayerWorkload(PrefillStackWorkload):
     name = "dsv3_2_decode_layer"
     cache_len = 4096
     default_tokens = 64
+    graph_default = True      # a decode step is replayed from a CUDA graph, as racetrack/bench.py:98-111 does
 
     def _build_model(self, w, args):
         from racetrack_b200 import decode
@@ -733,7 +734,8 @@ def run_ours(args) -> None:
     _lib.load()
     wl = WORKLOADS[args.workload](device, rank, world, args)
 
-    use_graph = args.graph and hasattr(wl, "capture_graph")
+    use_graph = (args.graph or getattr(wl, "graph_default", False)) and not args.no_graph \
+        and hasattr(wl, "capture_graph")
     if use_graph:
         wl.step()
         barrier()
@@ -869,6 +871,8 @@ def main() -> None:
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--graph", action="store_true",
                     help="capture the stack in a CUDA graph and replay it (decode sizes)")
+    ap.add_argument("--no-graph", action="store_true",
+                    help="run eagerly even where the workload replays a CUDA graph by default (decode)")
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop")
     args = ap.parse_args()
