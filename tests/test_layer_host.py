@@ -100,3 +100,36 @@ def test_two_gloo_ranks_reduce_to_the_single_rank_result(tmp_path):
     moe = ref_layer.moe(h, w, shape, 0, shape.n_experts).float()
     assert float((got["attn"] - attn).abs().max()) <= 0.03 * float(attn.abs().max()) + 1e-3
     assert float((got["moe"] - moe).abs().max()) <= 0.03 * float(moe.abs().max()) + 1e-3
+
+
+def test_reference_decode_step_is_invariant_to_the_world_size():
+    """The decode branch of the oracle (cache append, indexer, sparse attention, experts) with the
+    heads and experts split over 1, 2 and 4 ranks: every rank appends the same cache rows and
+    selects the same positions, and the partial sums add up to the one-rank result."""
+    from oracle import ref_ops as R
+    shape = layer.DSV32.scaled(name="small_decode", hidden=256, heads=8, q_lora=64, kv_lora=64,
+                               nope=16, rope=64, v_dim=16, moe_inter=64, n_experts=8, topk=2)
+    batch, cache_len, start, topk = 3, 80, 70, 24
+    g = torch.Generator().manual_seed(3)
+    mk = lambda *s, std=1.0: torch.randn(*s, generator=g) * std
+    iw = {"wq_b": mk(64 * 128, shape.q_lora, std=0.05).bfloat16(),
+          "wk": mk(128, shape.hidden, std=0.05).bfloat16(), "k_norm_weight": torch.ones(128),
+          "k_norm_bias": torch.zeros(128), "weights_proj": mk(64, shape.hidden, std=0.05)}
+    keys, scales = R.act_quant(mk(batch, cache_len, 128).bfloat16())
+    base = {"kv": mk(batch, cache_len, shape.kv_lora).bfloat16(),
+            "pe": mk(batch, cache_len, shape.rope).bfloat16(), "index_k": keys,
+            "index_scale": scales.squeeze(-1).contiguous()}
+    freqs = R.precompute_freqs_cis(shape.rope, cache_len)
+    hidden = (mk(batch, shape.hidden) * 0.5).bfloat16()
+    outs, caches = {}, {}
+    for world in (1, 2, 4):
+        weights = [layer.make_weights(shape, r, world, "cpu", std=0.05) for r in range(world)]
+        rank_caches = [{k: v.clone() for k, v in base.items()} for _ in range(world)]
+        outs[world] = ref_layer.decode_stack(hidden, start, weights, iw, rank_caches, shape, 2, freqs, topk)
+        caches[world] = rank_caches
+        for c in rank_caches[1:]:
+            for k in base:
+                assert torch.equal(c[k].view(torch.uint8), rank_caches[0][k].view(torch.uint8)), k
+    scale = float(outs[1].float().abs().max())
+    for world in (2, 4):
+        assert float((outs[world].float() - outs[1].float()).abs().max()) <= 0.05 * scale
