@@ -385,6 +385,19 @@ int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, in
                  int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, void* stream);
 
 /*
+ * The same product for FEW rows (decode: m up to a few dozen tokens), where a projection has too
+ * few output tiles to occupy the GPU although its whole weight matrix must be streamed: the K
+ * range is cut into `splits` pieces, each work item ADDS its partial product to c, which is
+ * fp32 [m, n] (row pitch ldc elements) and must be ZERO on entry. splits =
+ * rt_gemm_bf16_splitk_splits(m, n, k). The caller rounds c to bf16 where the reference's linear
+ * returns bf16 (one rounding of the fp32 sum, as a single-pass GEMM does).
+ * ref: racetrack/models/deepseek.py:316-345 (linear with bf16 weights -> F.linear).
+ */
+int64_t rt_gemm_bf16_splitk_splits(int64_t m, int64_t n, int64_t k);
+int rt_gemm_bf16_splitk(const void* a, const void* b, float* c, int64_t m, int64_t n, int64_t k,
+                        int64_t lda, int64_t ldb, int64_t ldc, int64_t splits, void* stream);
+
+/*
  * FP8 e4m3 GEMM with DeepSeek block scales, bf16 output:
  *   c[m, n] = sum_kb (a[m, kb] . b[n, kb]) * a_scales[m, kb] * b_scales[n / 128, kb]
  * a [m, k] and b [n, k] are e4m3fn bytes (row pitches lda / ldb in bytes = elements);

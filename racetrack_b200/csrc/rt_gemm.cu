@@ -46,10 +46,15 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 }
 
 // F32OUT: c is fp32 (the router logits), otherwise bf16.
-template <int BN, bool F32OUT>
+// SPLITK (with F32OUT): the K blocks of a tile are cut into k_splits ranges, one work item each,
+// and every item ADDS its partial product to the zero-initialised fp32 output (red.global.add):
+// a projection of a few dozen decode tokens has too few output tiles to occupy the GPU, while
+// its weight matrix is what has to be streamed.
+template <int BN, bool F32OUT, bool SPLITK = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-    void* __restrict__ c_out, int M, int N, int K, int64_t ldc) {
+    void* __restrict__ c_out, int M, int N, int K, int64_t ldc, int k_splits_arg = 1) {
+    static_assert(!SPLITK || F32OUT, "split-K accumulates into an fp32 output");
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -66,8 +71,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_m = (M + kBM - 1) / kBM, num_n = (N + BN - 1) / BN;
-    const int num_tiles = num_m * num_n;
-    const int num_kb = (K + kBK - 1) / kBK;
+    const int k_splits = SPLITK ? k_splits_arg : 1;
+    const int num_tiles = num_m * num_n * k_splits;         // work items
+    const int num_kb_all = (K + kBK - 1) / kBK;
+    const int kb_per = (num_kb_all + k_splits - 1) / k_splits;
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
@@ -99,8 +106,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile, num_m, num_n, tm, tn);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                tile_coords(tile / k_splits, num_m, num_n, tm, tn);
+                const int kb0 = (tile % k_splits) * kb_per, kb1 = min(num_kb_all, kb0 + kb_per);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1))) break;
                     const uint32_t sa = base + stage * Cfg::kStageBytes;
                     mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
@@ -125,7 +133,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
                 if (!(ok = mbar_wait(tempty_bar(acc), acc_phase ^ 1u, abort_flag, 2))) break;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc * BN);
-                for (int kb = 0; kb < num_kb; ++kb) {
+                const int kb0 = (tile % k_splits) * kb_per, kb1 = min(num_kb_all, kb0 + kb_per);
+                for (int kb = kb0; kb < kb1; ++kb) {
                     if (!(ok = mbar_wait(full_bar(stage), phase, abort_flag, 3))) break;
                     tc_fence_after();
                     const uint32_t sa = base + stage * Cfg::kStageBytes;
@@ -135,7 +144,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
                     for (int k = 0; k < kBK / 16; ++k) {
                         // 16 bf16 = 32 bytes along K: +2 in the 16-byte-unit address field
                         mma_f16(d_tmem, adesc + 2u * k, bdesc + 2u * k, Cfg::kIdesc,
-                                (kb | k) != 0 ? 1u : 0u);
+                                ((kb - kb0) | k) != 0 ? 1u : 0u);
                     }
                     mma_commit(empty_bar(stage));  // frees the stage when these MMAs retire
                     if (++stage == Cfg::kStages) {
@@ -159,7 +168,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             int tm, tn;
-            tile_coords(tile, num_m, num_n, tm, tn);
+            tile_coords(tile / k_splits, num_m, num_n, tm, tn);
             if (!(ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4))) break;
             tc_fence_after();
             const int row = tm * kBM + quad * 32 + lane;
@@ -178,6 +187,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
                     for (int v = 0; v < 4; ++v) {
                         const int col = col0 + v * 8;
                         if (col < N) {  // N % 8 == 0, so a started vector is complete
+                            if constexpr (SPLITK) {
+#pragma unroll
+                                for (int i = 0; i < 8; ++i)
+                                    atomicAdd(crow_f + col + i, __uint_as_float(r[8 * v + i]));
+                                continue;
+                            }
                             if constexpr (F32OUT) {
                                 *reinterpret_cast<uint4*>(crow_f + col) =
                                     make_uint4(r[8 * v], r[8 * v + 1], r[8 * v + 2], r[8 * v + 3]);
@@ -1716,6 +1731,26 @@ static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t
     return check_launch("gemm_bf16_kernel");
 }
 
+// Split-K launch of the 128 x 128 tiling: c is fp32, zero-initialised by the caller.
+static int launch_bf16_splitk(const void* a, const void* b, float* c, int64_t M, int64_t N, int64_t K,
+                              int64_t lda, int64_t ldb, int64_t ldc, int splits, cudaStream_t st) {
+    using Cfg = GemmCfg<128>;
+    CUtensorMap ta, tb;
+    if (int rc = make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, K, M, lda * 2, kBK, kBM))
+        return rc;
+    if (int rc = make_tmap_2d(&tb, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, b, K, N, ldb * 2, kBK, 128))
+        return rc;
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_bf16_kernel<128, true, true>),
+                                     static_cast<int>(Cfg::kSmemBytes), "rt_gemm_bf16_splitk"))
+        return rc;
+    const int64_t items = ((M + kBM - 1) / kBM) * ((N + 127) / 128) * splits;
+    const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
+    gemm_bf16_kernel<128, true, true><<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(
+        ta, tb, c, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldc, splits);
+    count_launch();
+    return check_launch("gemm_bf16_kernel<split-K>");
+}
+
 // bf16 operand as 64-element K blocks: dims {64, rows, K / 64}, box {64, 128, 2}.
 static int make_tmap_bf16_kblocks(CUtensorMap* map, const void* ptr, uint64_t rows, uint64_t k,
                                   uint64_t pitch_bytes) {
@@ -2028,6 +2063,39 @@ extern "C" int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, in
     }
     if (n <= 128) return tc::launch_bf16<128, false>(a, b, c, m, n, k, lda, ldb, ldc, st);
     return tc::launch_bf16<256, false>(a, b, c, m, n, k, lda, ldb, ldc, st);
+}
+
+extern "C" int64_t rt_gemm_bf16_splitk_splits(int64_t m, int64_t n, int64_t k) {
+    if (m <= 0 || n <= 0 || k <= 0) return 1;
+    const int64_t tiles = ((m + 127) / 128) * ((n + 127) / 128);
+    const int64_t num_kb = (k + 63) / 64;
+    // enough work items for two per SM, at least 4 K blocks each
+    int64_t splits = (2 * tc::sm_count() + tiles - 1) / tiles;
+    if (splits > num_kb / 4) splits = num_kb / 4;
+    if (splits < 1) splits = 1;
+    const int64_t per = (num_kb + splits - 1) / splits;
+    return (num_kb + per - 1) / per;          // no split is empty
+}
+
+extern "C" int rt_gemm_bf16_splitk(const void* a, const void* b, float* c, int64_t m, int64_t n,
+                                   int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t splits,
+                                   void* stream) {
+    RT_REQUIRE(m >= 0 && n > 0 && k > 0, RT_ERR_BAD_ARG, "rt_gemm_bf16_splitk: bad shape");
+    if (m == 0) return RT_OK;
+    RT_REQUIRE(a && b && c, RT_ERR_BAD_ARG, "rt_gemm_bf16_splitk: null pointer");
+    RT_REQUIRE(k % 8 == 0 && n % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 4 == 0,
+               RT_ERR_UNSUPPORTED, "rt_gemm_bf16_splitk: k, n, lda, ldb must be multiples of 8, ldc of 4");
+    RT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c), RT_ERR_UNSUPPORTED,
+               "rt_gemm_bf16_splitk: pointers must be 16-byte aligned");
+    RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
+               "rt_gemm_bf16_splitk: dimension too large");
+    const int64_t num_kb = (k + 63) / 64;
+    RT_REQUIRE(splits >= 1 && splits <= num_kb, RT_ERR_BAD_ARG, "rt_gemm_bf16_splitk: bad split count");
+    const int64_t per = (num_kb + splits - 1) / splits;
+    RT_REQUIRE((num_kb + per - 1) / per == splits, RT_ERR_BAD_ARG,
+               "rt_gemm_bf16_splitk: a split would be empty (use rt_gemm_bf16_splitk_splits)");
+    return tc::launch_bf16_splitk(a, b, c, m, n, k, lda, ldb, ldc, static_cast<int>(splits),
+                                  as_stream(stream));
 }
 
 namespace rt { namespace tc { int attn_error_take(); } }   // the flag of the attention kernels (rt_attn.cu)

@@ -502,6 +502,10 @@ def tc_error_state() -> None:
     _lib.check(_lib.load().rt_tc_error_state(), "tensor-core kernel")
 
 
+SPLITK_MAX_ROWS = 128          # linear_bf16 splits K for at most this many rows ...
+SPLITK_MIN_WEIGHT = 1 << 20    # ... against a weight matrix of at least this many elements
+
+
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
                 out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """F.linear(x, weight) for bf16 x [..., K] and weight [N, K] on the tcgen05 tensor cores
@@ -519,8 +523,18 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
     n = w.shape[0]
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise RuntimeError("linear_bf16: out_dtype must be bfloat16 or float32")
-    out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
     lib = _lib.load()
+    rows = x2.shape[0]
+    if 0 < rows <= SPLITK_MAX_ROWS and n * k >= SPLITK_MIN_WEIGHT:
+        # a few decode tokens against a whole weight matrix: split the K range over the SMs
+        splits = int(lib.rt_gemm_bf16_splitk_splits(rows, n, k))
+        if splits > 1:
+            acc = torch.zeros(rows, n, dtype=torch.float32, device=x.device)
+            _lib.check(lib.rt_gemm_bf16_splitk(x2.data_ptr(), w.data_ptr(), acc.data_ptr(), rows, n, k,
+                                               x2.stride(0), w.stride(0), n, splits, _stream()),
+                       "rt_gemm_bf16_splitk")
+            return acc.to(out_dtype).view(*x.shape[:-1], n)
+    out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
     _lib.check(lib.rt_gemm_bf16(x2.data_ptr(), w.data_ptr(), out.data_ptr(), x2.shape[0], n, k,
                                 x2.stride(0), w.stride(0), n,
                                 _lib.RT_F32 if out_dtype == torch.float32 else _lib.RT_BF16,

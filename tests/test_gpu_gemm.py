@@ -235,3 +235,34 @@ def test_gemm_nvfp4_grouped_ragged(ops, nvfp4_schedule):
     tm2, tb2, tc2 = ops.moe_tile_map(offsets, 2, 5, 8)
     assert tc2.cpu().tolist() == [4, 3] and tm2.cpu()[0].tolist() == [0, 130, 5, 0]
     assert tm2.cpu()[8:11].tolist() == [[0, 130, 5, 0], [1, 135, 256, 1], [2, 391, 1, 3]]
+
+
+@pytest.mark.parametrize("m,n,k,out_dtype", [
+    (1, 2112, 7168, torch.bfloat16),       # one decode token, qkv_a
+    (64, 7168, 16384, torch.bfloat16),     # the decode batch, w_o: 256 K blocks
+    (64, 256, 7168, torch.float32),        # router logits of the decode batch, fp32 out
+    (17, 8192, 1536, torch.bfloat16),      # the indexer's wq_b, ragged rows
+    (128, 1024, 1032, torch.bfloat16),     # K not a multiple of 64: the last block is partial
+])
+def test_linear_bf16_split_k_for_few_rows(ops, m, n, k, out_dtype):
+    """Few rows against a whole weight matrix take the split-K schedule (rt_gemm_bf16_splitk):
+    same product, fp32 partial sums added up in memory, one rounding at the end."""
+    from racetrack_b200 import _lib
+    assert int(_lib.load().rt_gemm_bf16_splitk_splits(m, n, k)) > 1
+    x = I.randn((m, k), 300 + m).cuda()
+    w = I.randn((n, k), 400 + n, std=0.05).cuda()
+    before = _lib.launch_count()
+    out = ops.linear_bf16(x, w, out_dtype=out_dtype)
+    ops.tc_error_state()
+    assert _lib.launch_count() - before == 1 and out.dtype == out_dtype and out.shape == (m, n)
+    ref = _ref(x, w)
+    diff = (out.float() - ref).abs()
+    tol = (2.0 ** -7 if out_dtype == torch.bfloat16 else 1e-5) * ref.abs() + 2e-3 * ref.abs().max()
+    assert bool((diff <= tol).all()), f"worst {float(diff.max())}"
+    # the single-pass kernel gives the same result to the last bf16 bit or one
+    saved, ops.SPLITK_MAX_ROWS = ops.SPLITK_MAX_ROWS, 0
+    try:
+        one = ops.linear_bf16(x, w, out_dtype=out_dtype)
+    finally:
+        ops.SPLITK_MAX_ROWS = saved
+    assert float((out.float() - one.float()).abs().max()) <= 2.0 ** -6 * float(ref.abs().max())
