@@ -418,26 +418,51 @@ __global__ void __launch_bounds__(kAThreads, 1) mla_sparse_decode_kernel(const A
 }
 
 // out[b, h, :] = sum_s o_s 2^(m_s - M) / sum_s l_s 2^(m_s - M): one CTA of 128 threads per
-// (sequence, head), 4 dims per thread.
+// (sequence, head), 4 dims per thread; the partials of eight splits are loaded before any of
+// them is used, so a merge of many splits is not a chain of dependent loads.
 __global__ void __launch_bounds__(128) mla_merge_kernel(const float* __restrict__ part_o,
                                                         const float* __restrict__ part_ml,
                                                         __nv_bfloat16* __restrict__ out, int heads,
                                                         int splits) {
     const int head = blockIdx.x, b = blockIdx.y;
     const float ninf = __int_as_float(0xff800000);
-    float m = ninf;
-    for (int s = 0; s < splits; ++s)
-        m = fmaxf(m, __ldg(part_ml + ((static_cast<int64_t>(b) * splits + s) * heads + head) * 2));
+    const int64_t prt0 = static_cast<int64_t>(b) * splits * heads + head;      // + s * heads
+    __shared__ float w_s[64], red_s[2];
+    // weights of the splits: lane s of the first two warps owns split s (splits <= 64)
+    if (threadIdx.x < 64) {
+        const int s = threadIdx.x;
+        const float ms = s < splits ? __ldg(part_ml + (prt0 + static_cast<int64_t>(s) * heads) * 2) : ninf;
+        const float ls = s < splits ? __ldg(part_ml + (prt0 + static_cast<int64_t>(s) * heads) * 2 + 1) : 0.f;
+        float m = ms;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if ((threadIdx.x & 31) == 0) red_s[threadIdx.x >> 5] = m;
+        asm volatile("bar.sync 1, 64;" ::: "memory");
+        m = fmaxf(red_s[0], red_s[1]);
+        const float w = ms == ninf ? 0.f : exp2f(ms - m);
+        w_s[s] = w;
+        float den = ls * w;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) den += __shfl_xor_sync(0xffffffffu, den, o);
+        asm volatile("bar.sync 1, 64;" ::: "memory");      // both maxima have been read
+        if ((threadIdx.x & 31) == 0) red_s[threadIdx.x >> 5] = den;
+    }
+    __syncthreads();
+    const float den = red_s[0] + red_s[1];
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    float den = 0.f;
-    for (int s = 0; s < splits; ++s) {
-        const int64_t prt = (static_cast<int64_t>(b) * splits + s) * heads + head;
-        const float ms = __ldg(part_ml + prt * 2), ls = __ldg(part_ml + prt * 2 + 1);
-        if (ms == ninf) continue;
-        const float w = exp2f(ms - m);
-        const float4 o = __ldg(reinterpret_cast<const float4*>(part_o + prt * 512) + threadIdx.x);
-        acc.x += o.x * w; acc.y += o.y * w; acc.z += o.z * w; acc.w += o.w * w;
-        den += ls * w;
+    for (int s0 = 0; s0 < splits; s0 += 8) {
+        float4 o[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int s = min(s0 + i, splits - 1);
+            o[i] = __ldg(reinterpret_cast<const float4*>(part_o + (prt0 + static_cast<int64_t>(s) * heads) * 512) +
+                         threadIdx.x);
+        }
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const float w = s0 + i < splits ? w_s[s0 + i] : 0.f;
+            acc.x += o[i].x * w; acc.y += o[i].y * w; acc.z += o[i].z * w; acc.w += o[i].w * w;
+        }
     }
     const float inv = den > 0.f ? 1.f / den : 0.f;
     __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
@@ -522,7 +547,8 @@ extern "C" int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const v
     RT_REQUIRE(indices || n_sel == keys, RT_ERR_BAD_ARG,
                "rt_mla_sparse_decode: without indices n_sel must equal keys");
     const int64_t tiles = (n_sel + tc::kATile - 1) / tc::kATile;
-    RT_REQUIRE(splits >= 1 && splits <= tiles, RT_ERR_BAD_ARG, "rt_mla_sparse_decode: bad split count");
+    RT_REQUIRE(splits >= 1 && splits <= tiles && splits <= 64, RT_ERR_BAD_ARG,
+               "rt_mla_sparse_decode: the split count must lie in [1, min(tiles, 64)]");
     const int64_t tps = (tiles + splits - 1) / splits;
     RT_REQUIRE((tiles + tps - 1) / tps == splits, RT_ERR_BAD_ARG,
                "rt_mla_sparse_decode: a split would own no tile (use rt_mla_sparse_decode_splits)");
