@@ -61,15 +61,17 @@ def indexer_forward(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cach
 
 def indexer_decode(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cache: torch.Tensor,
                    k_scale_cache: torch.Tensor, start_pos: int, freqs_cis: torch.Tensor,
-                   index_topk: int) -> torch.Tensor:
+                   index_topk: int, *, positions: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One decode step of B sequences (the reference's bsz = B, seqlen = 1): x [B, dim] and qr
     [B, q_lora] bf16 hold the token of every sequence at position start_pos; k_cache
     float8_e4m3fn [B, max_len, 128] and k_scale_cache fp32 [B, max_len] are updated in place at
     start_pos. Returns int32 [B, min(index_topk, start_pos + 1)], ascending. Every kernel runs
-    once for the whole batch."""
+    once for the whole batch. `positions` (int64 [B]) are the rows of freqs_cis to rotate by
+    (default: start_pos for every sequence, i.e. freqs_cis is the whole table)."""
     batch = x.shape[0]
     end_pos = start_pos + 1
-    positions = torch.full((batch,), start_pos, device=x.device, dtype=torch.int64)
+    if positions is None:
+        positions = torch.full((batch,), start_pos, device=x.device, dtype=torch.int64)
     q = ops.linear_bf16(qr, w.wq_b).view(batch, w.heads, w.head_dim)
     q_fp8, q_scale = ops.index_prep(q, freqs_cis, positions=positions)
     k = ops.linear_bf16(x, w.wk).view(batch, 1, w.head_dim)

@@ -139,3 +139,54 @@ def test_moe_patcher_runs_the_nvfp4_expert_path(spec, cuda_backend):
     # bf16 experts against NVFP4 experts: the format's rounding noise, not a wiring error
     assert rel_err(got, want) <= 0.35
     assert hasattr(moe, "_rt_nvfp4_experts")
+
+
+def test_indexer_patcher_runs_the_b200_indexer(spec, cuda_backend):
+    """An `Indexer` module with the reference's attributes (racetrack/models/deepseek.py:635-653),
+    patched through the partition's pre_trace op: beyond index_topk positions the kernel wrapper
+    answers (prefill of one chunk, then a decode step of both sequences), and its selections and
+    cache updates are those of racetrack_b200.indexer called directly."""
+    from racetrack_b200 import indexer as rt_indexer, ops, pre_trace
+    from racetrack_b200.dispatch import KernelDispatcher
+    from oracle import ref_ops as R
+    dim, q_lora, heads, topk, max_len, bsz = 512, 128, 64, 32, 128, 2
+
+    class Indexer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.n_heads, self.head_dim, self.index_topk = heads, 128, topk
+            self.wq_b = nn.Linear(q_lora, heads * 128, bias=False)
+            self.wk = nn.Linear(dim, 128, bias=False)
+            self.k_norm = nn.LayerNorm(128)
+            self.weights_proj = nn.Linear(dim, heads, bias=False)
+            self.register_buffer("k_cache", torch.zeros(bsz, max_len, 128, dtype=torch.float8_e4m3fn))
+            self.register_buffer("k_scale_cache", torch.zeros(bsz, max_len, 1))
+
+        def forward(self, x, qr, start_pos, freqs_cis, mask):
+            raise AssertionError("the original forward must not run beyond index_topk positions")
+
+    torch.manual_seed(3)
+    mod = Indexer().cuda()
+    mod.wq_b.to(torch.bfloat16), mod.wk.to(torch.bfloat16)
+    table = R.precompute_freqs_cis(64, max_len).cuda()
+    w = rt_indexer.IndexerWeights(mod.wq_b.weight, mod.wk.weight, mod.k_norm.weight.float(),
+                                  mod.k_norm.bias.float(), mod.weights_proj.weight.float(), heads, 128)
+    ref_k = torch.zeros(bsz, max_len, 128, dtype=torch.float8_e4m3fn, device="cuda")
+    ref_s = torch.zeros(bsz, max_len, device="cuda")
+    originals = pre_trace.apply_pre_trace_patches(mod, spec, KernelDispatcher(spec.kernel_root))
+    assert len(originals) == 1
+    with torch.no_grad():
+        for start, seqlen in ((0, 48), (48, 1)):
+            x = torch.randn(bsz, seqlen, dim, device="cuda").bfloat16()
+            qr = torch.randn(bsz, seqlen, q_lora, device="cuda").bfloat16()
+            mask = torch.full((seqlen, seqlen), float("-inf"), device="cuda").triu_(1) if seqlen > 1 else None
+            got = mod(x, qr, start, table[start:start + seqlen], mask)
+            ops.tc_error_state()
+            assert got.dtype == torch.int64 and got.shape == (bsz, seqlen, topk)
+            for b in range(bsz):
+                want = rt_indexer.indexer_forward(x[b], qr[b], w, ref_k[b], ref_s[b], start, table, topk,
+                                                  causal=mask is not None)
+                assert torch.equal(got[b], want.long())
+        assert torch.equal(mod.k_cache.view(torch.uint8), ref_k.view(torch.uint8))
+        assert torch.equal(mod.k_scale_cache.view(bsz, max_len), ref_s)
+    pre_trace.rollback_patches(originals)

@@ -44,7 +44,7 @@ def test_shipped_partition_loads_and_its_hash_names_the_directory():
     assert spec.label == f"dsv3_2/{spec.partition_hash}"
     assert [op.name for op in spec.fx_ops] == ["fused_norm_rope", "fused_swiglu",
                                                "fused_residual_norm", "fused_act_quant"]
-    assert [op.name for op in spec.pre_trace_ops] == ["fused_single_token_moe"]
+    assert [op.name for op in spec.pre_trace_ops] == ["fused_single_token_moe", "fused_full_topk_indexer"]
     assert [op.name for op in spec.module_patch_ops] == ["fused_mlp_gate_up_proj"]
     assert spec.op_names == tuple(op.name for op in spec.fused_ops)
     assert load_spec("dsv3_2", spec.partition_hash) == spec
