@@ -579,6 +579,7 @@ class DecodeLayerWorkload(PrefillStackWorkload):
     name = "dsv3_2_decode_layer"
     cache_len = 4096
     default_tokens = 64
+    default_proj = "bf16"
     graph_default = True      # a decode step is replayed from a CUDA graph, as racetrack/bench.py:98-111 does
 
     def _build_model(self, w, args):
@@ -859,7 +860,7 @@ def main() -> None:
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--layers", type=int, default=61)
-    ap.add_argument("--proj", default="mixed", choices=("mixed", "fp8", "bf16"),
+    ap.add_argument("--proj", default=None, choices=("mixed", "fp8", "bf16"),
                     help="arithmetic of the dense projections: FP8 e4m3 block-scaled, bf16, or "
                          "mixed (FP8 where K >= 4096, bf16 elsewhere)")
     ap.add_argument("--nvfp4-schedule", default="auto", choices=("auto", "pair", "single"),
@@ -876,6 +877,10 @@ def main() -> None:
     ap.add_argument("--profiler-range", action="store_true",
                     help="bracket the timed steps with cudaProfilerStart/Stop")
     args = ap.parse_args()
+    if args.proj is None:
+        # prefill: FP8 where the reduction is long; decode: bf16, as BASELINE.json's decode
+        # configuration states ("bf16 with NVFP4 experts") and where few rows take the split-K path
+        args.proj = getattr(WORKLOADS[args.workload], "default_proj", "mixed")
     PrefillStackWorkload.ffn = args.ffn          # the CPU legs draw the same variant
     if args.impl == "reference":
         run_reference(args)
