@@ -40,7 +40,7 @@ def sha(t: torch.Tensor) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", required=True, help="path of the racetrack checkout")
     args = ap.parse_args()
     sys.path.insert(0, args.reference)
 
