@@ -9,7 +9,11 @@ of oracle/inputs.py and writes
   * golden_small.pt    - input-free output tensors of small cases (inputs are regenerated
                          from their seeds by the tests), a few hundred KB;
   * golden_hashes.json - SHA-256 of the reference outputs at full hot-path sizes, plus the
-                         torch version / CPU capability they were produced with.
+                         torch version / CPU capability they were produced with;
+  * golden_layer.pt    - racetrack's own ShardedRealisticBlock (racetrack/realistic_bench.py:
+                         118-427) on a small shape, world sizes 1 and 2 (gloo ranks as threads of
+                         this process are not possible, so the two ranks run as child processes):
+                         the weights it drew, its input and its output after 1 and 3 layers.
 The fixtures only ever travel as data: nothing at test time imports the reference.
 """
 from __future__ import annotations
@@ -36,6 +40,71 @@ def sha(t: torch.Tensor) -> str:
     else:
         raw = t
     return hashlib.sha256(raw.numpy().tobytes()).hexdigest()
+
+
+LAYER_SHAPE = dict(name="pin", source="fixture", vocab_size=1, hidden_size=64, num_layers=3,
+                   num_attention_heads=4, q_lora_rank=32, kv_lora_rank=16, qk_nope_head_dim=8,
+                   qk_rope_head_dim=8, v_head_dim=8, moe_intermediate_size=32,
+                   n_routed_experts=8, num_experts_per_tok=2, seed=38595)
+LAYER_TOKENS = 24
+
+
+def _layer_rank(rank: int, world: int, reference: str, port: int, out_path: str) -> None:
+    """One gloo rank: builds racetrack's ShardedRealisticBlock (backend "torch", bf16, CPU), runs
+    1 and 3 layers on the runner's own kind of input (racetrack/realistic_bench.py:495-505) and
+    saves this rank's weights and outputs."""
+    import os
+    import torch.distributed as dist
+    sys.path.insert(0, reference)
+    from racetrack import realistic_bench as rb
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        shape = rb.RealisticShape(**LAYER_SHAPE)
+        dev = torch.device("cpu")
+        g = torch.Generator().manual_seed(shape.seed + 17)
+        hidden = torch.empty(LAYER_TOKENS, shape.hidden_size, dtype=torch.bfloat16)
+        hidden.normal_(mean=0.0, std=0.5, generator=g)
+        positions = torch.arange(LAYER_TOKENS, dtype=torch.int64)
+        outs = {}
+        for layers in (1, 3):
+            model = rb.ShardedRealisticModel(shape, device=dev, dtype=torch.bfloat16, rank=rank,
+                                             world_size=world, backend="torch", layers=layers)
+            with torch.no_grad():
+                outs[layers] = model.forward(hidden.clone(), positions).clone()
+        b = model.block
+        torch.save({"hidden": hidden, "out1": outs[1], "out3": outs[3],
+                    "weights": {k: getattr(b, k).clone() for k in
+                                ("w_qkv_a", "w_q_b", "w_kv_b", "w_o", "w_gate", "w13", "w2")}},
+                   out_path)
+    finally:
+        dist.destroy_process_group()
+
+
+def make_layer_fixture(reference: str) -> None:
+    import tempfile
+    import torch.multiprocessing as mp
+    fixture = {"shape": dict(LAYER_SHAPE), "tokens": LAYER_TOKENS}
+    with tempfile.TemporaryDirectory() as tmp:
+        for world, port in ((1, 29611), (2, 29612)):
+            paths = [f"{tmp}/w{world}_r{r}.pt" for r in range(world)]
+            ctx = mp.get_context("spawn")
+            procs = [ctx.Process(target=_layer_rank, args=(r, world, reference, port, paths[r]))
+                     for r in range(world)]
+            for p in procs:
+                p.start()
+            for p in procs:
+                p.join()
+                if p.exitcode != 0:
+                    raise RuntimeError(f"layer fixture: a rank of world {world} failed")
+            ranks = [torch.load(p) for p in paths]
+            assert all(torch.equal(r["out3"], ranks[0]["out3"]) for r in ranks)
+            fixture[f"world{world}"] = {
+                "hidden": ranks[0]["hidden"], "out1": ranks[0]["out1"], "out3": ranks[0]["out3"],
+                "rank_weights": [r["weights"] for r in ranks]}
+    torch.save(fixture, HERE / "golden_layer.pt")
+    size = (HERE / "golden_layer.pt").stat().st_size
+    print(f"wrote golden_layer.pt ({size/1024:.0f} KiB)")
 
 
 def main() -> None:
@@ -215,6 +284,8 @@ def main() -> None:
         small["mla_decode.pe_row"] = mla.pe_cache[:, c["start_pos"]].clone()
     finally:
         torch.set_default_dtype(torch.float32)
+
+    make_layer_fixture(args.reference)
 
     meta = {"torch": torch.__version__, "cpu_capability": torch.backends.cpu.get_cpu_capability(),
             "threads": torch.get_num_threads()}

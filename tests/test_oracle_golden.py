@@ -296,3 +296,33 @@ def test_mla_decode_matches_reference(golden_small, same_cpu_as_golden):
         -1, d["topk_indices"][:, 0:1, :].reshape(c["batch"], 1, -1), 0)
     flow = torch.einsum("bht,btc->bhc", (scores + mask).softmax(dim=-1), kv_cache[:, :end])
     assert float((core - flow.float()).abs().max()) <= 3e-2 * float(core.abs().max())
+
+
+@pytest.mark.parametrize("world", [1, 2])
+def test_layer_oracle_matches_reference_block(world, same_cpu_as_golden):
+    """oracle/ref_layer.forward_stack against racetrack's own ShardedRealisticBlock / Model
+    (racetrack/realistic_bench.py:118-427) run by tests/golden/make_golden.py on CPU in bf16:
+    one process (world 1) and two gloo ranks (world 2; each rank's weights as the reference
+    drew them from seed + rank). Exact on the host class that made the fixture, one bf16 ulp
+    of the largest element elsewhere (the matmuls' summation order follows the vector width)."""
+    from conftest import GOLDEN_DIR
+    from oracle import ref_layer
+    from racetrack_b200.layer import LayerShape
+    fx = torch.load(GOLDEN_DIR / "golden_layer.pt")
+    s = fx["shape"]
+    shape = LayerShape(name="pin", hidden=s["hidden_size"], heads=s["num_attention_heads"],
+                       q_lora=s["q_lora_rank"], kv_lora=s["kv_lora_rank"],
+                       nope=s["qk_nope_head_dim"], rope=s["qk_rope_head_dim"],
+                       v_dim=s["v_head_dim"], moe_inter=s["moe_intermediate_size"],
+                       n_experts=s["n_routed_experts"], topk=s["num_experts_per_tok"],
+                       seed=s["seed"])
+    case = fx[f"world{world}"]
+    positions = torch.arange(fx["tokens"], dtype=torch.int64)
+    for layers in (1, 3):
+        got = ref_layer.forward_stack(case["hidden"], positions, case["rank_weights"], shape, layers)
+        want = case[f"out{layers}"]
+        if same_cpu_as_golden:
+            assert_bit_exact(got, want, f"world {world}, {layers} layer(s)")
+        else:
+            tol = 2.0 ** -7 * float(want.float().abs().max())
+            assert float((got.float() - want.float()).abs().max()) <= tol * layers
