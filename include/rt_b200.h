@@ -105,6 +105,8 @@ typedef enum rt_rope_mode {
  *   RT_ROPE_INTERLEAVED: `table` = [table_rows, rope_dim/2] (cos, sin) fp32 pairs, the
  *                        memory image of the complex64 tensor precompute_freqs_cis returns;
  *                        row = positions[t], or t % table_rows when positions is NULL.
+ *                        positions must lie in [0, table_rows) when table_rows > 0; values
+ *                        outside are clamped to the nearest row (memory-safe, not meaningful).
  * q_cols % 8 == 0, kv_cols % 8 == 0, rope_dim % 2 == 0, rope_dim <= 512.
  * ref: partitions/dsv3_2/model.py:84-99 (fused_norm_rope), :333-344 (its call site),
  *      racetrack/models/deepseek.py:766-776 (q_norm / kv_norm / k_pe rotary in MLA.forward).
@@ -352,8 +354,10 @@ int rt_moe_gather(const void* x, const int32_t* sorted_pairs, void* out,
 
 /*
  * Weighted combine: y[t, :] = sum_s weights[t, s] * expert_out[pair_pos[t*topk + s], :]
- * (+ shared[t, :] when `shared` is non-NULL), fp32 accumulation in slot order,
- * rounded to `dtype`. Pairs whose sorted position lies outside
+ * (+ shared[t, :] when `shared` is non-NULL), fp32 accumulation in slot order.
+ * expert_out and shared are bf16; `dtype` is the type of y: RT_BF16 (rounded once) or RT_F32
+ * (the fp32 sums, which an expert-parallel rank all-reduces before the cast, as the reference
+ * does with its fp32 y). Pairs whose sorted position lies outside
  * [pos_begin, pos_end) are skipped (expert-parallel ranks own a slice of the
  * sorted range); pos_begin_ptr / pos_end_ptr, when non-NULL, are device int32 values that
  * override the host ones (entries of expert_offsets, so no host read-back is needed).
@@ -387,15 +391,19 @@ int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, in
 /*
  * The same product for FEW rows (decode: m up to a few dozen tokens), where a projection has too
  * few output tiles to occupy the GPU although its whole weight matrix must be streamed: the K
- * range is cut into `splits` pieces, each work item ADDS its partial product to c, which is
- * fp32 [m, n] (row pitch ldc elements) and must be ZERO on entry. splits =
- * rt_gemm_bf16_splitk_splits(m, n, k). The caller rounds c to bf16 where the reference's linear
- * returns bf16 (one rounding of the fp32 sum, as a single-pass GEMM does).
+ * range is cut into `splits` pieces, work item (tile, split) stores its partial product into
+ * slab `split` of `workspace` (fp32 [splits, m, ldw], caller-provided scratch, no initialisation
+ * needed), and a second kernel adds the slabs in split order and writes out [m, n] (row pitch
+ * ldo) as RT_BF16 (one rounding of the fp32 sum, as a single-pass GEMM does) or RT_F32.
+ * The summation order is fixed, so the result is bit-reproducible from run to run and equal
+ * on every rank that computes it from the same operands. splits =
+ * rt_gemm_bf16_splitk_splits(m, n, k).
  * ref: racetrack/models/deepseek.py:316-345 (linear with bf16 weights -> F.linear).
  */
 int64_t rt_gemm_bf16_splitk_splits(int64_t m, int64_t n, int64_t k);
-int rt_gemm_bf16_splitk(const void* a, const void* b, float* c, int64_t m, int64_t n, int64_t k,
-                        int64_t lda, int64_t ldb, int64_t ldc, int64_t splits, void* stream);
+int rt_gemm_bf16_splitk(const void* a, const void* b, float* workspace, void* out, int64_t m,
+                        int64_t n, int64_t k, int64_t lda, int64_t ldb, int64_t ldw, int64_t ldo,
+                        int64_t splits, int out_dtype, void* stream);
 
 /*
  * FP8 e4m3 GEMM with DeepSeek block scales, bf16 output:
@@ -483,6 +491,8 @@ int rt_gemm_nvfp4_schedule(int schedule);
  *   act_quant with one 128-wide group: codes e4m3 [rows, 128], scales fp32 [rows].
  * The position of row r is positions[r / rows_per_position] (positions int64, may be NULL:
  * then r / rows_per_position itself); rows_per_position = index heads for queries, 1 for keys.
+ * Positions must lie in [0, table_rows); values outside are clamped to the nearest table row
+ * (memory-safe, not meaningful).
  * rotated (bf16 [rows, 128], may be NULL) receives the tensor that is quantised.
  * dim == 128, rope_dim == 64.
  * ref: racetrack/models/deepseek.py:659-676 (Indexer.forward: k_norm, apply_rotary_emb(...,

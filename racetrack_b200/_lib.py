@@ -47,7 +47,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_moe_gather_nvfp4": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _L, _L, _P]),
     "rt_gemm_bf16": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P]),
     "rt_gemm_bf16_splitk_splits": (_L, [_L, _L, _L]),
-    "rt_gemm_bf16_splitk": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _P]),
+    "rt_gemm_bf16_splitk": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P]),
     "rt_gemm_fp8": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
     "rt_tc_error_state": (_I, []),
     "rt_moe_tile_map": (_I, [_P, _L, _L, _P, _P, _P, _L, _P]),

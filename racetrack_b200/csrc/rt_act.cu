@@ -178,7 +178,9 @@ __global__ void __launch_bounds__(256) index_prep_kernel(
     // RoPE: lanes 0-7 hold dims 0-31 (real parts), lanes 8-15 dims 32-63 (imaginary parts)
     {
         int64_t pos = positions ? positions[row / rows_per_pos] : row / rows_per_pos;
+        // positions must lie in [0, table_rows); others are clamped (memory-safe, not meaningful)
         if (pos >= table_rows) pos = table_rows - 1;
+        if (pos < 0) pos = 0;
         float other[4];
 #pragma unroll
         for (int j = 0; j < 4; ++j) other[j] = __shfl_xor_sync(0xffffffffu, v[j], 8);

@@ -9,6 +9,8 @@
 //   warps 2..5  epilogue: tensor memory -> registers -> bf16 -> global
 // The accumulator is double buffered in tensor memory, so the epilogue of tile i
 // overlaps the main loop of tile i+1. Every wait is bounded (rt_tc.cuh).
+#include <algorithm>
+
 #include "rt_tc.cuh"
 
 namespace rt {
@@ -47,13 +49,16 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 
 // F32OUT: c is fp32 (the router logits), otherwise bf16.
 // SPLITK (with F32OUT): the K blocks of a tile are cut into k_splits ranges, one work item each,
-// and every item ADDS its partial product to the zero-initialised fp32 output (red.global.add):
-// a projection of a few dozen decode tokens has too few output tiles to occupy the GPU, while
-// its weight matrix is what has to be streamed.
+// and item (tile, split) STORES its partial product into slab `split` of an fp32 workspace
+// [k_splits][M][ldc] (slabs split_stride elements apart); splitk_reduce_kernel then adds the
+// slabs in split order, so the result does not depend on which SM finished first. A projection
+// of a few dozen decode tokens has too few output tiles to occupy the GPU, while its weight
+// matrix is what has to be streamed.
 template <int BN, bool F32OUT, bool SPLITK = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-    void* __restrict__ c_out, int M, int N, int K, int64_t ldc, int k_splits_arg = 1) {
+    void* __restrict__ c_out, int M, int N, int K, int64_t ldc, int k_splits_arg = 1,
+    int64_t split_stride = 0) {
     static_assert(!SPLITK || F32OUT, "split-K accumulates into an fp32 output");
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
@@ -173,7 +178,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
             tc_fence_after();
             const int row = tm * kBM + quad * 32 + lane;
             __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(c_out) + static_cast<int64_t>(row) * ldc;
-            float* crow_f = static_cast<float*>(c_out) + static_cast<int64_t>(row) * ldc;
+            float* crow_f = static_cast<float*>(c_out) + static_cast<int64_t>(row) * ldc +
+                            (SPLITK ? static_cast<int64_t>(tile % k_splits) * split_stride : 0);
 #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; ++chunk) {
                 uint32_t r[32];
@@ -187,12 +193,6 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
                     for (int v = 0; v < 4; ++v) {
                         const int col = col0 + v * 8;
                         if (col < N) {  // N % 8 == 0, so a started vector is complete
-                            if constexpr (SPLITK) {
-#pragma unroll
-                                for (int i = 0; i < 8; ++i)
-                                    atomicAdd(crow_f + col + i, __uint_as_float(r[8 * v + i]));
-                                continue;
-                            }
                             if constexpr (F32OUT) {
                                 *reinterpret_cast<uint4*>(crow_f + col) =
                                     make_uint4(r[8 * v], r[8 * v + 1], r[8 * v + 2], r[8 * v + 3]);
@@ -1731,9 +1731,38 @@ static int launch_bf16(const void* a, const void* b, void* c, int64_t M, int64_t
     return check_launch("gemm_bf16_kernel");
 }
 
-// Split-K launch of the 128 x 128 tiling: c is fp32, zero-initialised by the caller.
-static int launch_bf16_splitk(const void* a, const void* b, float* c, int64_t M, int64_t N, int64_t K,
-                              int64_t lda, int64_t ldb, int64_t ldc, int splits, cudaStream_t st) {
+// out[m, n] = part[0][m, n] + part[1][m, n] + ... in split order (fp32), rounded to bf16 or kept.
+template <bool F32OUT>
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ part,
+                                                            void* __restrict__ out, int64_t total4,
+                                                            int n4, int64_t ld4, int64_t ldo,
+                                                            int64_t slab4, int splits) {
+    for (int64_t i = blockIdx.x * static_cast<int64_t>(blockDim.x) + threadIdx.x; i < total4;
+         i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+        const int64_t row = i / n4;
+        const int c4 = static_cast<int>(i - row * n4);
+        const float4* src = reinterpret_cast<const float4*>(part) + row * ld4 + c4;
+        float4 acc = __ldg(src);
+        for (int sidx = 1; sidx < splits; ++sidx) {
+            const float4 v = __ldg(src + sidx * slab4);
+            acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+        }
+        if constexpr (F32OUT) {
+            *reinterpret_cast<float4*>(static_cast<float*>(out) + row * ldo + 4 * c4) = acc;
+        } else {
+            uint2 o;
+            o.x = pack_bf16x2(acc.x, acc.y);
+            o.y = pack_bf16x2(acc.z, acc.w);
+            *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + row * ldo + 4 * c4) = o;
+        }
+    }
+}
+
+// Split-K launch of the 128 x 128 tiling: partial products into the workspace slabs, then the
+// ordered sum into `out`.
+static int launch_bf16_splitk(const void* a, const void* b, float* c, void* out, int out_dtype,
+                              int64_t M, int64_t N, int64_t K, int64_t lda, int64_t ldb, int64_t ldc,
+                              int64_t ldo, int splits, cudaStream_t st) {
     using Cfg = GemmCfg<128>;
     CUtensorMap ta, tb;
     if (int rc = make_tmap_2d(&ta, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, a, K, M, lda * 2, kBK, kBM))
@@ -1746,9 +1775,16 @@ static int launch_bf16_splitk(const void* a, const void* b, float* c, int64_t M,
     const int64_t items = ((M + kBM - 1) / kBM) * ((N + 127) / 128) * splits;
     const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
     gemm_bf16_kernel<128, true, true><<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(
-        ta, tb, c, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldc, splits);
+        ta, tb, c, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldc, splits, M * ldc);
     count_launch();
-    return check_launch("gemm_bf16_kernel<split-K>");
+    if (int rc = check_launch("gemm_bf16_kernel<split-K>")) return rc;
+    const int64_t total4 = M * (N / 4);
+    const int blocks = static_cast<int>(std::min<int64_t>((total4 + 255) / 256, 8 * sm_count()));
+    auto reduce = out_dtype == RT_F32 ? splitk_reduce_kernel<true> : splitk_reduce_kernel<false>;
+    reduce<<<blocks, 256, 0, st>>>(c, out, total4, static_cast<int>(N / 4), ldc / 4, ldo, M * ldc / 4,
+                                   splits);
+    count_launch();
+    return check_launch("splitk_reduce_kernel");
 }
 
 // bf16 operand as 64-element K blocks: dims {64, rows, K / 64}, box {64, 128, 2}.
@@ -2077,15 +2113,21 @@ extern "C" int64_t rt_gemm_bf16_splitk_splits(int64_t m, int64_t n, int64_t k) {
     return (num_kb + per - 1) / per;          // no split is empty
 }
 
-extern "C" int rt_gemm_bf16_splitk(const void* a, const void* b, float* c, int64_t m, int64_t n,
-                                   int64_t k, int64_t lda, int64_t ldb, int64_t ldc, int64_t splits,
+extern "C" int rt_gemm_bf16_splitk(const void* a, const void* b, float* workspace, void* out,
+                                   int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                                   int64_t ldw, int64_t ldo, int64_t splits, int out_dtype,
                                    void* stream) {
+    float* c = workspace;
+    const int64_t ldc = ldw;
     RT_REQUIRE(m >= 0 && n > 0 && k > 0, RT_ERR_BAD_ARG, "rt_gemm_bf16_splitk: bad shape");
     if (m == 0) return RT_OK;
-    RT_REQUIRE(a && b && c, RT_ERR_BAD_ARG, "rt_gemm_bf16_splitk: null pointer");
-    RT_REQUIRE(k % 8 == 0 && n % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 4 == 0,
-               RT_ERR_UNSUPPORTED, "rt_gemm_bf16_splitk: k, n, lda, ldb must be multiples of 8, ldc of 4");
-    RT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c), RT_ERR_UNSUPPORTED,
+    RT_REQUIRE(a && b && c && out, RT_ERR_BAD_ARG, "rt_gemm_bf16_splitk: null pointer");
+    RT_REQUIRE(out_dtype == RT_BF16 || out_dtype == RT_F32, RT_ERR_BAD_ARG,
+               "rt_gemm_bf16_splitk: out_dtype must be RT_BF16 or RT_F32");
+    RT_REQUIRE(k % 8 == 0 && n % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 4 == 0 && ldo % 4 == 0,
+               RT_ERR_UNSUPPORTED,
+               "rt_gemm_bf16_splitk: k, n, lda, ldb must be multiples of 8, ldw and ldo of 4");
+    RT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c) && aligned16(out), RT_ERR_UNSUPPORTED,
                "rt_gemm_bf16_splitk: pointers must be 16-byte aligned");
     RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31), RT_ERR_UNSUPPORTED,
                "rt_gemm_bf16_splitk: dimension too large");
@@ -2094,8 +2136,8 @@ extern "C" int rt_gemm_bf16_splitk(const void* a, const void* b, float* c, int64
     const int64_t per = (num_kb + splits - 1) / splits;
     RT_REQUIRE((num_kb + per - 1) / per == splits, RT_ERR_BAD_ARG,
                "rt_gemm_bf16_splitk: a split would be empty (use rt_gemm_bf16_splitk_splits)");
-    return tc::launch_bf16_splitk(a, b, c, m, n, k, lda, ldb, ldc, static_cast<int>(splits),
-                                  as_stream(stream));
+    return tc::launch_bf16_splitk(a, b, c, out, out_dtype, m, n, k, lda, ldb, ldc, ldo,
+                                  static_cast<int>(splits), as_stream(stream));
 }
 
 namespace rt { namespace tc { int attn_error_take(); } }   // the flag of the attention kernels (rt_attn.cu)

@@ -272,10 +272,11 @@ __global__ void __launch_bounds__(256) moe_gather_kernel(
     st_stream16(reinterpret_cast<uint4*>(out) + r * nvec + v, d);
 }
 
+template <bool F32OUT>
 __global__ void __launch_bounds__(256) moe_combine_kernel(
     const __nv_bfloat16* __restrict__ expert_out, const int32_t* __restrict__ pair_pos,
     const float* __restrict__ weights, const __nv_bfloat16* __restrict__ shared,
-    __nv_bfloat16* __restrict__ y, int nvec, int topk, int pos_begin, int pos_end,
+    void* __restrict__ y, int nvec, int topk, int pos_begin, int pos_end,
     const int32_t* __restrict__ pos_begin_ptr, const int32_t* __restrict__ pos_end_ptr) {
     const int64_t t = blockIdx.x;
     // a window given in device memory (expert offsets of this rank) overrides the host values
@@ -301,7 +302,16 @@ __global__ void __launch_bounds__(256) moe_combine_kernel(
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[k] = __fadd_rn(acc[k], f[k]);
         }
-        st_stream16(reinterpret_cast<uint4*>(y) + t * nvec + v, pack_bf16x8(acc));
+        if constexpr (F32OUT) {
+            // the fp32 sums themselves (an expert-parallel rank all-reduces them before the cast)
+            uint4* dst = reinterpret_cast<uint4*>(y) + (t * nvec + v) * 2;
+            st_stream16(dst, make_uint4(__float_as_uint(acc[0]), __float_as_uint(acc[1]),
+                                        __float_as_uint(acc[2]), __float_as_uint(acc[3])));
+            st_stream16(dst + 1, make_uint4(__float_as_uint(acc[4]), __float_as_uint(acc[5]),
+                                            __float_as_uint(acc[6]), __float_as_uint(acc[7])));
+        } else {
+            st_stream16(reinterpret_cast<uint4*>(y) + t * nvec + v, pack_bf16x8(acc));
+        }
     }
 }
 
@@ -626,7 +636,8 @@ extern "C" int rt_moe_combine(const void* expert_out, const int32_t* pair_pos,
     RT_REQUIRE(expert_out && pair_pos && weights && y, RT_ERR_BAD_ARG,
                "rt_moe_combine: null pointer");
     RT_REQUIRE(tokens >= 0 && topk > 0 && cols > 0, RT_ERR_BAD_ARG, "rt_moe_combine: bad shape");
-    RT_REQUIRE(dtype == RT_BF16, RT_ERR_UNSUPPORTED, "rt_moe_combine: only bf16");
+    RT_REQUIRE(dtype == RT_BF16 || dtype == RT_F32, RT_ERR_UNSUPPORTED,
+               "rt_moe_combine: y must be bf16 or fp32");
     RT_REQUIRE(cols % 8 == 0 && aligned16(expert_out) && aligned16(y) &&
                    (!shared || aligned16(shared)),
                RT_ERR_UNSUPPORTED, "rt_moe_combine: cols %% 8 and 16-byte alignment needed");
@@ -636,10 +647,10 @@ extern "C" int rt_moe_combine(const void* expert_out, const int32_t* pair_pos,
     const int nvec = static_cast<int>(cols / 8);
     int threads = (nvec + 31) / 32 * 32;
     if (threads > 256) threads = 256;
-    moe_combine_kernel<<<static_cast<unsigned>(tokens), threads, 0, as_stream(stream)>>>(
-        (const __nv_bfloat16*)expert_out, pair_pos, weights, (const __nv_bfloat16*)shared,
-        (__nv_bfloat16*)y, nvec, (int)topk, (int)pos_begin, (int)pos_end, pos_begin_ptr,
-        pos_end_ptr);
+    auto kernel = dtype == RT_F32 ? moe_combine_kernel<true> : moe_combine_kernel<false>;
+    kernel<<<static_cast<unsigned>(tokens), threads, 0, as_stream(stream)>>>(
+        (const __nv_bfloat16*)expert_out, pair_pos, weights, (const __nv_bfloat16*)shared, y, nvec,
+        (int)topk, (int)pos_begin, (int)pos_end, pos_begin_ptr, pos_end_ptr);
     count_launch();
     return check_launch("moe_combine_kernel");
 }

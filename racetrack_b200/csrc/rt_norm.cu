@@ -136,6 +136,14 @@ __global__ void __launch_bounds__(512) rms_norm_kernel(const __nv_bfloat16* __re
 // RoPE helpers
 // ---------------------------------------------------------------------------
 
+// Row of the rotary table for a caller-given position: positions must lie in [0, table_rows);
+// anything else is clamped to the nearest row so that no load leaves the table (the rotation is
+// then meaningless, but memory-safe). table_rows == 0 means the caller did not state the size.
+__device__ __forceinline__ int64_t table_row(int64_t pos, int64_t table_rows) {
+    if (table_rows <= 0) return pos;
+    return pos < 0 ? 0 : (pos >= table_rows ? table_rows - 1 : pos);
+}
+
 // Fills cs[0..half) = cos, cs[half..2*half) = sin for one token.
 // HALF mode rounds both to bf16 (the reference casts the tables to x.dtype).
 __device__ __forceinline__ void fill_cos_sin(float* cs, int half, int64_t token,
@@ -149,7 +157,7 @@ __device__ __forceinline__ void fill_cos_sin(float* cs, int half, int64_t token,
             c = round_bf16(cosf(ang));
             s = round_bf16(sinf(ang));
         } else {
-            const int64_t trow = positions ? positions[token] : (token % table_rows);
+            const int64_t trow = positions ? table_row(positions[token], table_rows) : (token % table_rows);
             const float2 f = __ldg(reinterpret_cast<const float2*>(table) + trow * half + i);
             c = f.x;
             s = f.y;
@@ -331,7 +339,7 @@ __global__ void __launch_bounds__(kNrWarps * 32) norm_rope_warp_kernel(
             kout[i] = __float2bfloat16_rn(o1);
             kout[half + i] = __float2bfloat16_rn(o2);
         } else {
-            const int64_t trow = positions ? positions[t] : (t % table_rows);
+            const int64_t trow = positions ? table_row(positions[t], table_rows) : (t % table_rows);
             const float2 f = __ldg(reinterpret_cast<const float2*>(table) + trow * half + i);
             rot_pair(__bfloat162float(kin[2 * i]), __bfloat162float(kin[2 * i + 1]), f.x, f.y, o1, o2);
             kout[2 * i] = __float2bfloat16_rn(o1);

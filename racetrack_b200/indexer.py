@@ -29,6 +29,44 @@ class IndexerWeights:
     head_dim: int = 128
 
 
+def weights_of_module(indexer) -> IndexerWeights:
+    """IndexerWeights of a racetrack `Indexer` module (racetrack/models/deepseek.py:634-654),
+    converted once and cached on the module. FP8 checkpoint weights of wq_b / wk are dequantised
+    with their block scales; weights_proj stays fp32 as the reference keeps it."""
+    cached = getattr(indexer, "_rt_index_weights", None)
+    if cached is None:
+        cached = IndexerWeights(
+            ops.module_weight_bf16(indexer.wq_b), ops.module_weight_bf16(indexer.wk),
+            indexer.k_norm.weight.detach().float().contiguous(),
+            indexer.k_norm.bias.detach().float().contiguous(),
+            indexer.weights_proj.weight.detach().float().contiguous(),
+            indexer.n_heads, indexer.head_dim)
+        indexer._rt_index_weights = cached
+    return cached
+
+
+def write_k_cache(x: torch.Tensor, w: IndexerWeights, k_cache: torch.Tensor,
+                  k_scale_cache: torch.Tensor, start_pos: int, freqs_cis: torch.Tensor,
+                  positions: Optional[torch.Tensor] = None) -> None:
+    """The key half of `Indexer.forward` alone (racetrack/models/deepseek.py:665-676): project,
+    LayerNorm, non-interleaved RoPE, Hadamard rotation, FP8 quantisation, and the append to the
+    caches at [start_pos, start_pos + S). x [B, S, dim] bf16; k_cache float8_e4m3fn
+    [>= B, max_len, 128]; k_scale_cache fp32 [>= B, max_len] or [.., 1]; freqs_cis complex64
+    [S, 32] (the rows of the tokens) unless `positions` names rows of a longer table. What the
+    reference's full-top-k short-circuit runs so that later steps find valid cached keys
+    (racetrack/pre_trace.py:82-112)."""
+    bsz, s_len, _ = x.shape
+    end_pos = start_pos + s_len
+    if positions is None:
+        positions = torch.arange(s_len, device=x.device, dtype=torch.int64)
+    pos = positions.repeat(bsz) if positions.numel() == s_len else positions.reshape(-1)
+    k = ops.linear_bf16(x.reshape(bsz * s_len, -1), w.wk).view(bsz * s_len, 1, w.head_dim)
+    k_fp8, k_scale = ops.index_prep(k, freqs_cis, positions=pos, ln_weight=w.k_norm_weight,
+                                    ln_bias=w.k_norm_bias)
+    k_cache[:bsz, start_pos:end_pos] = k_fp8.view(bsz, s_len, w.head_dim)
+    k_scale_cache[:bsz, start_pos:end_pos] = k_scale.view(bsz, s_len, *k_scale_cache.shape[2:])
+
+
 def indexer_forward(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cache: torch.Tensor,
                     k_scale_cache: torch.Tensor, start_pos: int, freqs_cis: torch.Tensor,
                     index_topk: int, *, causal: bool = True,

@@ -135,7 +135,8 @@ def moe_quant_nvfp4(x: torch.Tensor, tile_map: torch.Tensor, tile_count: torch.T
 
 def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor,
                       experts: NVFP4Experts, *, n_experts: int, expert_begin: int = 0,
-                      shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      shared: Optional[torch.Tensor] = None,
+                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """y[t] = sum over the token's routed experts owned here of w * expert(x[t]) (+ shared[t]).
 
     x [T, hidden] bf16; weights fp32 [T, k] and indices int64 [T, k] from fused_moe_route;
@@ -168,13 +169,15 @@ def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     h_codes, h_sf, h_gs = moe_quant_nvfp4(h, tile_map, tile_count, pairs, amax=h_amax)
     expert_out = ops.gemm_nvfp4_grouped(h_codes, h_sf, h_gs, experts.w2_codes, experts.w2_sf,
                                         experts.w2_gs, tile_map, tile_count, n=hidden, groups=count)
-    return ops.fused_moe_combine(expert_out, pair_pos, weights, shared, pos_window=window)
+    return ops.fused_moe_combine(expert_out, pair_pos, weights, shared, pos_window=window,
+                                 out_dtype=out_dtype)
 
 
 def fused_moe_forward(x: torch.Tensor, gate_weight: torch.Tensor, gate_bias: Optional[torch.Tensor],
                       experts: NVFP4Experts, *, n_experts: int, n_groups: int, topk_groups: int,
                       topk: int, route_scale: float, score_func: str = "sigmoid",
-                      expert_begin: int = 0, shared: Optional[torch.Tensor] = None) -> torch.Tensor:
+                      expert_begin: int = 0, shared: Optional[torch.Tensor] = None,
+                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """Gate (fp32 logits as in racetrack/models/deepseek.py:898, formed on the tensor cores from
     the bf16 operands with the fp32 accumulators kept) + routing kernel + experts."""
     logits = ops.linear_bf16(x, gate_weight.to(torch.bfloat16), out_dtype=torch.float32)
@@ -182,4 +185,4 @@ def fused_moe_forward(x: torch.Tensor, gate_weight: torch.Tensor, gate_bias: Opt
                                            topk_groups=topk_groups, topk=topk,
                                            route_scale=route_scale, score_func=score_func)
     return fused_moe_experts(x, weights, indices, experts, n_experts=n_experts,
-                             expert_begin=expert_begin, shared=shared)
+                             expert_begin=expert_begin, shared=shared, out_dtype=out_dtype)

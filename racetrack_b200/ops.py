@@ -464,11 +464,13 @@ def fused_moe_gather(x: torch.Tensor, sorted_pairs: torch.Tensor, topk: int) -> 
 def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights: torch.Tensor,
                       shared: Optional[torch.Tensor] = None, *, pos_begin: int = 0,
                       pos_end: Optional[int] = None,
-                      pos_window: Optional[tuple] = None) -> torch.Tensor:
+                      pos_window: Optional[tuple] = None,
+                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
     """y[t] = sum_s weights[t, s] * expert_out[pair_pos[t, s]] (+ shared[t]);
     racetrack/models/deepseek.py:1018-1022. ``pos_window`` = (begin, end) as 1-element int32
     CUDA tensors (entries of expert_offsets) restricts the sum to an expert-parallel rank's
-    slice of the sorted range without a host read-back."""
+    slice of the sorted range without a host read-back. ``out_dtype=torch.float32`` returns the
+    fp32 sums (what the reference all-reduces across expert-parallel ranks before its cast)."""
     _require_cuda(expert_out, pair_pos, weights)
     _require_bf16("fused_moe_combine", expert_out)
     tokens, topk = weights.shape
@@ -480,14 +482,17 @@ def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights:
         shared = shared.reshape(tokens, cols).contiguous()
     if pos_end is None:
         pos_end = tokens * topk
-    y = torch.empty(tokens, cols, dtype=expert_out.dtype, device=expert_out.device)
+    if out_dtype not in (torch.bfloat16, torch.float32):
+        raise RuntimeError("fused_moe_combine: out_dtype must be bfloat16 or float32")
+    y = torch.empty(tokens, cols, dtype=out_dtype, device=expert_out.device)
     lib = _lib.load()
     _lib.check(lib.rt_moe_combine(expert_out.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(),
                                   shared.data_ptr() if shared is not None else None, y.data_ptr(),
                                   tokens, topk, cols, pos_begin, pos_end,
                                   pos_window[0].data_ptr() if pos_window is not None else None,
                                   pos_window[1].data_ptr() if pos_window is not None else None,
-                                  _lib.RT_BF16, _stream()),
+                                  _lib.RT_F32 if out_dtype == torch.float32 else _lib.RT_BF16,
+                                  _stream()),
                "rt_moe_combine")
     return y
 
@@ -529,11 +534,16 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
         # a few decode tokens against a whole weight matrix: split the K range over the SMs
         splits = int(lib.rt_gemm_bf16_splitk_splits(rows, n, k))
         if splits > 1:
-            acc = torch.zeros(rows, n, dtype=torch.float32, device=x.device)
-            _lib.check(lib.rt_gemm_bf16_splitk(x2.data_ptr(), w.data_ptr(), acc.data_ptr(), rows, n, k,
-                                               x2.stride(0), w.stride(0), n, splits, _stream()),
-                       "rt_gemm_bf16_splitk")
-            return acc.to(out_dtype).view(*x.shape[:-1], n)
+            # partial products per K range, then their sum in a fixed order: bit-reproducible,
+            # and identical on every rank that forms the same replicated projection
+            part = torch.empty(splits, rows, n, dtype=torch.float32, device=x.device)
+            out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
+            _lib.check(lib.rt_gemm_bf16_splitk(
+                x2.data_ptr(), w.data_ptr(), part.data_ptr(), out.data_ptr(), rows, n, k,
+                x2.stride(0), w.stride(0), n, n, splits,
+                _lib.RT_F32 if out_dtype == torch.float32 else _lib.RT_BF16, _stream()),
+                "rt_gemm_bf16_splitk")
+            return out
     out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
     _lib.check(lib.rt_gemm_bf16(x2.data_ptr(), w.data_ptr(), out.data_ptr(), x2.shape[0], n, k,
                                 x2.stride(0), w.stride(0), n,
@@ -557,6 +567,35 @@ def quantize_weight_fp8(weight: torch.Tensor):
     scale = blocks.abs().amax(dim=(1, 3)).clamp(min=1e-4) / 448.0
     codes = (blocks / scale[:, None, :, None]).clamp(-448, 448).to(torch.float8_e4m3fn)
     return codes.view(nb * 128, k)[:n].contiguous(), scale.contiguous()
+
+
+def dequant_weight_fp8(weight: torch.Tensor, scale: torch.Tensor) -> torch.Tensor:
+    """e4m3fn codes [N, K] with fp32 scales [ceil(N/128), ceil(K/128)] (one per 128 x 128 block)
+    -> bf16 [N, K]; `weight_dequant` / `_block_dequant` of racetrack/models/deepseek.py:148-161,
+    689-694. Set-up time helper in plain torch (a weight is converted once)."""
+    if weight.dtype != torch.float8_e4m3fn or weight.dim() != 2:
+        raise RuntimeError("dequant_weight_fp8: expected a 2-D float8_e4m3fn weight")
+    n, k = weight.shape
+    nb, kb = (n + 127) // 128, (k + 127) // 128
+    if scale is None or tuple(scale.shape) != (nb, kb):
+        raise RuntimeError(f"dequant_weight_fp8: scale must be [{nb}, {kb}]")
+    full = scale.float().repeat_interleave(128, dim=0)[:n].repeat_interleave(128, dim=1)[:, :k]
+    return (weight.float() * full).to(torch.bfloat16)
+
+
+def module_weight_bf16(linear) -> torch.Tensor:
+    """The weight of a racetrack `Linear` (racetrack/models/deepseek.py:361-371) as a contiguous
+    bf16 matrix: bf16 / fp32 weights are cast, FP8 weights (element size 1) are dequantised with
+    their `weight.scale` block scales; an FP8 weight without scales is an error."""
+    w = linear.weight
+    if w.element_size() == 1:
+        scale = getattr(w, "scale", None)
+        if scale is None:
+            scale = getattr(linear, "scale", None)
+        if scale is None:
+            raise RuntimeError("an FP8 weight needs its 128 x 128 block scales (weight.scale)")
+        return dequant_weight_fp8(w.detach(), scale.detach()).contiguous()
+    return w.detach().to(torch.bfloat16).contiguous()
 
 
 def linear_fp8(x_codes: torch.Tensor, x_scales: torch.Tensor, w_codes: torch.Tensor,

@@ -11,22 +11,10 @@ from racetrack_b200 import _lib, indexer as rt_indexer
 BACKEND_AVAILABLE = _lib.available()
 
 
-def _weights_of(indexer):
-    cached = getattr(indexer, "_rt_index_weights", None)
-    if cached is None:
-        cached = rt_indexer.IndexerWeights(
-            indexer.wq_b.weight.to(torch.bfloat16).contiguous(),
-            indexer.wk.weight.to(torch.bfloat16).contiguous(),
-            indexer.k_norm.weight.float().contiguous(), indexer.k_norm.bias.float().contiguous(),
-            indexer.weights_proj.weight.float().contiguous(), indexer.n_heads, indexer.head_dim)
-        indexer._rt_index_weights = cached
-    return cached
-
-
 def fused_full_topk_indexer(indexer, x, qr, start_pos, freqs_cis, mask, *, fallback):
     del fallback
     bsz, seqlen, _ = x.size()
-    w = _weights_of(indexer)
+    w = rt_indexer.weights_of_module(indexer)
     k_cache = indexer.k_cache[:bsz]
     k_scale = indexer.k_scale_cache[:bsz].view(bsz, -1)
     # freqs_cis is the slice of the table for positions [start_pos, start_pos + seqlen)
@@ -34,9 +22,18 @@ def fused_full_topk_indexer(indexer, x, qr, start_pos, freqs_cis, mask, *, fallb
         local = torch.zeros(bsz, device=x.device, dtype=torch.int64)
         picked = rt_indexer.indexer_decode(x[:, 0], qr[:, 0], w, k_cache, k_scale, start_pos, freqs_cis,
                                            indexer.index_topk, positions=local)
-        return picked.long().unsqueeze(1)
-    local = torch.arange(seqlen, device=x.device, dtype=torch.int64)
-    rows = [rt_indexer.indexer_forward(x[b], qr[b], w, k_cache[b], k_scale[b], start_pos, freqs_cis,
-                                       indexer.index_topk, causal=mask is not None, positions=local)
-            for b in range(bsz)]
-    return torch.stack(rows).long()
+        picked = picked.long().unsqueeze(1)
+    else:
+        local = torch.arange(seqlen, device=x.device, dtype=torch.int64)
+        rows = [rt_indexer.indexer_forward(x[b], qr[b], w, k_cache[b], k_scale[b], start_pos, freqs_cis,
+                                           indexer.index_topk, causal=mask is not None, positions=local)
+                for b in range(bsz)]
+        picked = torch.stack(rows).long()
+    # every rank computes the same scores from replicated inputs, but a split-K projection or
+    # a different kernel schedule may round differently on a near tie: rank 0's selection wins,
+    # as in the reference (racetrack/models/deepseek.py:684-685)
+    dist = torch.distributed
+    if dist.is_available() and dist.is_initialized() and dist.get_world_size() > 1:
+        picked = picked.contiguous()
+        dist.broadcast(picked, src=0)
+    return picked

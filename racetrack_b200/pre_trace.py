@@ -75,6 +75,19 @@ def _modules_named(model: nn.Module, *class_names: str):
 # forward replacements
 # ---------------------------------------------------------------------------
 
+def _write_indexer_k_cache(indexer, x, start_pos, freqs_cis) -> None:
+    """Fills the indexer's key cache for positions the full-top-k short-circuit answers without
+    running the indexer (racetrack/pre_trace.py:82-112): once the context outgrows index_topk
+    the indexer scores the WHOLE prefix [0, end_pos) from this cache. Modules without a key
+    cache (light stubs) have nothing to fill. The keys come from this backend's own kernels
+    (projection GEMM + the fused LayerNorm / RoPE / Hadamard / FP8 pass)."""
+    if not hasattr(indexer, "k_cache"):
+        return
+    from . import indexer as rt_indexer
+    rt_indexer.write_k_cache(x, rt_indexer.weights_of_module(indexer), indexer.k_cache,
+                             indexer.k_scale_cache, start_pos, freqs_cis)
+
+
 @register_patcher("fused_full_topk_indexer")
 def _patch_full_topk_indexer(model: nn.Module, dispatcher: KernelDispatcher,
                              originals: Originals) -> None:
@@ -91,9 +104,7 @@ def _patch_full_topk_indexer(model: nn.Module, dispatcher: KernelDispatcher,
                 bsz, seqlen, _ = x.size()
                 end_pos = start_pos + seqlen
                 if end_pos <= limit:
-                    writer = getattr(indexer, "write_k_cache", None)
-                    if callable(writer):
-                        writer(x, start_pos, freqs_cis)
+                    _write_indexer_k_cache(indexer, x, start_pos, freqs_cis)
                     return torch.arange(end_pos, device=x.device, dtype=torch.long) \
                         .view(1, 1, end_pos).expand(bsz, seqlen, end_pos)
                 if kernel_fn is None:

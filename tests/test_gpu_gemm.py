@@ -246,7 +246,8 @@ def test_gemm_nvfp4_grouped_ragged(ops, nvfp4_schedule):
 ])
 def test_linear_bf16_split_k_for_few_rows(ops, m, n, k, out_dtype):
     """Few rows against a whole weight matrix take the split-K schedule (rt_gemm_bf16_splitk):
-    same product, fp32 partial sums added up in memory, one rounding at the end."""
+    same product, fp32 partial sums per K range added in a fixed order, one rounding at the
+    end; two runs give the same bits."""
     from racetrack_b200 import _lib
     assert int(_lib.load().rt_gemm_bf16_splitk_splits(m, n, k)) > 1
     x = I.randn((m, k), 300 + m).cuda()
@@ -254,7 +255,9 @@ def test_linear_bf16_split_k_for_few_rows(ops, m, n, k, out_dtype):
     before = _lib.launch_count()
     out = ops.linear_bf16(x, w, out_dtype=out_dtype)
     ops.tc_error_state()
-    assert _lib.launch_count() - before == 1 and out.dtype == out_dtype and out.shape == (m, n)
+    assert _lib.launch_count() - before == 2 and out.dtype == out_dtype and out.shape == (m, n)
+    again = ops.linear_bf16(x, w, out_dtype=out_dtype)
+    assert torch.equal(out, again), "split-K must be bit-reproducible"
     ref = _ref(x, w)
     diff = (out.float() - ref).abs()
     tol = (2.0 ** -7 if out_dtype == torch.bfloat16 else 1e-5) * ref.abs() + 2e-3 * ref.abs().max()

@@ -190,3 +190,80 @@ def test_indexer_patcher_runs_the_b200_indexer(spec, cuda_backend):
         assert torch.equal(mod.k_cache.view(torch.uint8), ref_k.view(torch.uint8))
         assert torch.equal(mod.k_scale_cache.view(bsz, max_len), ref_s)
     pre_trace.rollback_patches(originals)
+
+
+def test_indexer_short_circuit_fills_the_key_cache(spec, cuda_backend):
+    """Prefill of at most index_topk tokens (the patcher answers arange without running the
+    indexer), then decode steps that cross index_topk: the first step past the limit scores the
+    WHOLE prefix from the module's key cache, so the short-circuit must have written it
+    (racetrack/pre_trace.py:82-112,138). The caches must equal those of the indexer run on
+    every chunk, the selection past the limit must equal the full indexer's, and it must pick
+    (nearly) the best keys of the CPU oracle's scores over the whole context."""
+    from racetrack_b200 import indexer as rt_indexer, ops, pre_trace
+    from racetrack_b200.dispatch import KernelDispatcher
+    from oracle import ref_ops as R
+    dim, q_lora, heads, topk, max_len, bsz, prefill, last = 512, 128, 64, 64, 128, 2, 40, 70
+
+    class Indexer(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.n_heads, self.head_dim, self.index_topk = heads, 128, topk
+            self.wq_b = nn.Linear(q_lora, heads * 128, bias=False)
+            self.wk = nn.Linear(dim, 128, bias=False)
+            self.k_norm = nn.LayerNorm(128)
+            self.weights_proj = nn.Linear(dim, heads, bias=False)
+            self.register_buffer("k_cache", torch.zeros(bsz, max_len, 128, dtype=torch.float8_e4m3fn))
+            self.register_buffer("k_scale_cache", torch.zeros(bsz, max_len, 1))
+
+        def forward(self, x, qr, start_pos, freqs_cis, mask):
+            raise AssertionError("the original forward must not run: short-circuit or kernel")
+
+    torch.manual_seed(5)
+    mod = Indexer().cuda()
+    mod.wq_b.to(torch.bfloat16), mod.wk.to(torch.bfloat16)
+    with torch.no_grad():
+        mod.k_norm.weight.add_(torch.randn(128, device="cuda") * 0.02)
+        mod.k_norm.bias.add_(torch.randn(128, device="cuda") * 0.02)
+    table = R.precompute_freqs_cis(64, max_len).cuda()
+    w = rt_indexer.weights_of_module(mod)
+    ref_k = torch.zeros(bsz, max_len, 128, dtype=torch.float8_e4m3fn, device="cuda")
+    ref_s = torch.zeros(bsz, max_len, device="cuda")
+    originals = pre_trace.apply_pre_trace_patches(mod, spec, KernelDispatcher(spec.kernel_root))
+    xs, qrs = [], []
+    with torch.no_grad():
+        chunks = [(0, prefill)] + [(p, 1) for p in range(prefill, last)]
+        for start, seqlen in chunks:
+            x = torch.randn(bsz, seqlen, dim, device="cuda").bfloat16()
+            qr = torch.randn(bsz, seqlen, q_lora, device="cuda").bfloat16()
+            xs.append(x), qrs.append(qr)
+            mask = torch.full((seqlen, seqlen), float("-inf"), device="cuda").triu_(1) if seqlen > 1 else None
+            got = mod(x, qr, start, table[start:start + seqlen], mask)
+            ops.tc_error_state()
+            end = start + seqlen
+            want = torch.stack([rt_indexer.indexer_forward(x[b], qr[b], w, ref_k[b], ref_s[b], start,
+                                                           table, topk, causal=mask is not None)
+                                for b in range(bsz)]).long()
+            if end <= topk:
+                assert torch.equal(got, torch.arange(end, device="cuda").view(1, 1, end).expand(bsz, seqlen, end))
+            else:
+                assert torch.equal(got, want), f"selection at position {start}"
+            assert torch.equal(mod.k_cache[:, :end].view(torch.uint8), ref_k[:, :end].view(torch.uint8))
+            assert torch.equal(mod.k_scale_cache.view(bsz, max_len)[:, :end], ref_s[:, :end])
+        assert int((mod.k_scale_cache.view(bsz, max_len)[:, :last] > 0).sum()) == bsz * last
+    pre_trace.rollback_patches(originals)
+    # CPU oracle over the whole context of sequence 0: scores of the last query against keys
+    # built by the reference chain (racetrack/models/deepseek.py:656-683)
+    x_all = torch.cat([x[0] for x in xs]).cpu()
+    qr_last, x_last = qrs[-1][0].cpu(), xs[-1][0].cpu()
+    fc = table.cpu()
+    k = F.linear(x_all, mod.wk.weight.cpu()).view(last, 1, 128)
+    k_fp8, k_scale, _ = R.index_prep(k, fc[:last], ln_weight=mod.k_norm.weight.float().cpu(),
+                                     ln_bias=mod.k_norm.bias.float().cpu())
+    q = F.linear(qr_last, mod.wq_b.weight.cpu()).view(1, heads, 128)
+    q_fp8, q_scale, _ = R.index_prep(q, fc[last - 1:last])
+    hw = F.linear(x_last.float(), mod.weights_proj.weight.float().cpu()) * heads ** -0.5 * q_scale * 128 ** -0.5
+    scores = R.fp8_index(q_fp8.unsqueeze(0), hw.unsqueeze(0), k_fp8.view(1, last, 128),
+                         k_scale.view(1, last))[0, 0]
+    picked = scores[got[0, 0].cpu()].sum()
+    best = scores.topk(topk)[0].sum()
+    assert float((picked - best).abs()) <= 2e-3 * topk * float(scores.abs().max())
