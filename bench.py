@@ -109,6 +109,20 @@ class ClockSampler(threading.Thread):
 # workload: realistic prefill stack (default)
 # ---------------------------------------------------------------------------
 
+CHECK_ATOL, CHECK_RTOL = 0.5, 0.1     # racetrack/realistic_bench.py:538,645-646
+
+
+def _criterion(out: torch.Tensor, ref: torch.Tensor, **what) -> dict:
+    """The reference runner's pass criterion for a configuration: max |out - ref| against
+    atol + rtol * max |ref| (racetrack/realistic_bench.py:530-538)."""
+    diff = float((out.float().cpu() - ref.float()).abs().max())
+    scale = float(ref.float().abs().max())
+    return {"diff": diff, "rel": diff / max(scale, 1e-30), "max_abs_ref": scale,
+            "ok": bool(diff <= CHECK_ATOL + CHECK_RTOL * scale),
+            "criterion": f"diff <= {CHECK_ATOL} + {CHECK_RTOL} * max|ref|",
+            "against": "CPU restatement of the reference's torch path, same bf16 weights", **what}
+
+
 class PrefillStackWorkload:
     """T tokens through `layers` applications of one synthetic DeepSeek-V3.2 layer."""
     name = "dsv3_2_prefill_stack"
@@ -236,6 +250,14 @@ class PrefillStackWorkload:
         return weights + acts + out
 
     @property
+    def dominant_bytes_all_experts(self) -> int:
+        """Algorithmic bytes of a w13 launch in which every local expert receives tokens."""
+        s = self.shape
+        pairs_local = self.tokens * s.topk // self.world
+        return ((s.n_experts // self.world) * 2 * s.moe_inter * s.hidden * 9 // 16
+                + pairs_local * s.hidden * 9 // 16 + pairs_local * 2 * s.moe_inter * 2)
+
+    @property
     def dominant_flops(self) -> int:
         s = self.shape
         if self.ffn == "dense":
@@ -253,8 +275,8 @@ class PrefillStackWorkload:
     @property
     def dominant_traffic(self):
         """dram__bytes_read.sum + dram__bytes_write.sum of one w13 launch, from a one-pass ncu
-        capture of this very configuration (profiles/gemm_nvfp4_pair_grouped_T8192_dram_traffic.md);
-        other sizes were not captured."""
+        capture of the layer-1 launch of this very configuration (all 256 experts receive
+        tokens there: 5.03 GB of algorithmic bytes); other sizes were not captured."""
         if self.ffn == "moe" and self.tokens == 8192 and self.world == 1 and self.shape.n_experts == 256:
             return 4.82e9 + 0.60e9
         return None
@@ -296,6 +318,43 @@ class PrefillStackWorkload:
         out = self._forward(self.hidden)
         self.recording = False
         return out
+
+    CHECK_TOKENS, CHECK_LAYERS = 16, 2
+
+    def check(self):
+        """Validation of what is timed, outside the timed region, as the reference runner does
+        for every configuration (racetrack/realistic_bench.py:530-538): the benchmark's own model
+        object runs the first CHECK_TOKENS tokens of its input through CHECK_LAYERS layers (all
+        ranks, collectives included) and rank 0 compares the result with the CPU restatement of
+        the reference layer on the same bf16 weights: ok = diff <= 0.5 + 0.1 * max|ref|."""
+        from oracle import ref_layer, ref_ops as R
+        layer, s = self.layer_mod, self.shape
+        t, n_layers = min(self.CHECK_TOKENS, self.tokens), self.CHECK_LAYERS
+        sample, pos = self.hidden[:t].clone(), self.positions[:t]
+        out = self.model.forward_stack(sample, pos, n_layers)
+        if self.rank != 0:
+            return None
+        dense = self.ffn == "dense"
+        full = layer.make_weights(s, 0, 1, self.device, ffn="dense" if dense else "none", std=0.02)
+        w = {k: v.cpu() for k, v in full.items()}
+        del full
+        h, p = sample.cpu(), pos.cpu()
+        if dense:
+            ref = ref_layer.forward_stack(h, p, [w], s, n_layers, ffn="dense")
+        else:
+            w["w13"] = torch.empty(s.n_experts, 2 * s.moe_inter, s.hidden, dtype=torch.bfloat16)
+            w["w2"] = torch.empty(s.n_experts, s.hidden, s.moe_inter, dtype=torch.bfloat16)
+            ones, drawn, ref = torch.ones(s.hidden, dtype=torch.bfloat16), set(), h
+            for _ in range(n_layers):
+                mid = ref + ref_layer.attention(R.rms_norm(ref, ones, s.eps), p, w, s, s.heads)
+                normed = R.rms_norm(mid, ones, s.eps)
+                logits = torch.nn.functional.linear(normed.float(), w["w_gate"].float())
+                for e in sorted(set(torch.topk(logits, s.topk, dim=-1)[1].flatten().tolist()) - drawn):
+                    w13, w2 = layer.draw_expert(s, e, self.device, std=0.02)
+                    w["w13"][e], w["w2"][e] = w13.cpu(), w2.cpu()
+                    drawn.add(e)
+                ref = mid + ref_layer.moe(normed, w, s, 0, s.n_experts)
+        return _criterion(out, ref, tokens=t, layers=n_layers)
 
     def e2e_setup(self):
         self.host_in = torch.empty(self.hidden.shape, dtype=torch.bfloat16, pin_memory=True)
@@ -443,6 +502,26 @@ class MoeLayerWorkload:
     def step(self, record: bool = False):
         return self._run(self.x, record)
 
+    def check(self):
+        """The first 16 tokens of the timed input through the same code path, against
+        racetrack's MoE.forward (oracle/ref_ops.moe_forward) on the bf16 weights."""
+        from oracle import ref_ops as R
+        from racetrack_b200 import layer
+        s, t = self.shape, min(16, self.tokens)
+        out = self._run(self.x[:t].clone(), False)
+        if self.rank != 0:
+            return None
+        kw = dict(n_groups=8, topk_groups=4, topk=s.topk, route_scale=2.5)
+        x, wg, b = self.x[:t].cpu(), self.w_gate.cpu(), self.bias.cpu()
+        _, idx = R.gate_forward(x, wg, b, **kw)
+        inter = s.moe_inter
+        split = lambda w13, w2: (w13[:inter].cpu(), w2.cpu(), w13[inter:].cpu())     # (w1, w2, w3)
+        experts = [None] * s.n_experts
+        for e in sorted(set(idx.flatten().tolist())):
+            experts[e] = split(*layer.draw_expert(s, e, self.x.device, std=0.02))
+        ref = R.moe_forward(x, wg, b, experts, split(self.sw13, self.sw2), **kw)
+        return _criterion(out, ref, tokens=t, layers=1)
+
     def e2e_setup(self):
         self.host_in = torch.empty(self.x.shape, dtype=torch.bfloat16, pin_memory=True)
         self.host_in.copy_(self.x)
@@ -537,6 +616,20 @@ class SwigluQuantWorkload:
     def step(self, record: bool = False):
         return self._run(self.gate_up, record)
 
+    def check(self):
+        """Codes and scales of the first 64 rows against act_quant(swiglu(.)) on the CPU
+        (racetrack/models/deepseek.py:85-107): the fraction of FP8 codes that differ (the CPU's
+        expf may differ from the GPU's in the last ulp before the bf16 rounding)."""
+        from oracle import ref_ops as R
+        rows = self.gate_up[:64]
+        codes, scales, *_ = self._run(rows, False)
+        g, u = rows[:, :self.inter].cpu(), rows[:, self.inter:].cpu()
+        rc, rs = R.swiglu_quant(g, u)
+        bad = float((codes.cpu().view(torch.uint8) != rc.view(torch.uint8)).float().mean())
+        return {"fp8_codes_differing": bad, "scales_equal": bool(torch.equal(scales.cpu(), rs)),
+                "ok": bad <= 1e-3, "tokens": 64, "layers": 1,
+                "against": "CPU restatement of act_quant(swiglu(gate, up))"}
+
     def e2e_setup(self):
         self.host_in = torch.empty(self.gate_up.shape, dtype=torch.bfloat16, pin_memory=True)
         self.host_in.copy_(self.gate_up)
@@ -598,6 +691,41 @@ class DecodeLayerWorkload(PrefillStackWorkload):
     @property
     def dominant_traffic(self):
         return None
+
+    def check(self):
+        """One eager decode step of the whole batch through one layer; the first two sequences
+        are compared with the CPU restatement of the reference's decode branch
+        (oracle/ref_layer.decode_stack) on the same bf16 weights and cache contents."""
+        from oracle import ref_layer, ref_ops as R
+        layer, s, m = self.layer_mod, self.shape, self.model
+        b = min(2, self.tokens)
+        out = m.decode_stack(self.hidden, self.start_pos, 1)
+        if self.rank != 0:
+            return None
+        full = layer.make_weights(s, 0, 1, self.device, ffn="none", std=0.02)
+        w = {k: v.cpu() for k, v in full.items()}
+        del full
+        iw_dev = m.index_weights
+        iw = {"wq_b": iw_dev.wq_b.cpu(), "wk": iw_dev.wk.cpu(),
+              "k_norm_weight": iw_dev.k_norm_weight.cpu(), "k_norm_bias": iw_dev.k_norm_bias.cpu(),
+              "weights_proj": iw_dev.weights_proj.cpu()}
+        c = m.caches
+        caches = {"kv": c.kv[:b].cpu(), "pe": c.pe[:b].cpu(), "index_k": c.index_k[:b].cpu(),
+                  "index_scale": c.index_scale[:b].cpu()}
+        freqs, topk = m.freqs.cpu(), m.index_topk
+        hidden = self.hidden[:b].cpu()
+        ones = torch.ones(s.hidden, dtype=torch.bfloat16)
+        probe = {k: v.clone() for k, v in caches.items()}
+        mid = hidden + ref_layer.decode_attention(R.rms_norm(hidden, ones, s.eps), self.start_pos, w, iw,
+                                                  probe, s, s.heads, freqs, topk)
+        logits = torch.nn.functional.linear(R.rms_norm(mid, ones, s.eps).float(), w["w_gate"].float())
+        w["w13"] = torch.empty(s.n_experts, 2 * s.moe_inter, s.hidden, dtype=torch.bfloat16)
+        w["w2"] = torch.empty(s.n_experts, s.hidden, s.moe_inter, dtype=torch.bfloat16)
+        for e in sorted(set(torch.topk(logits, s.topk, dim=-1)[1].flatten().tolist())):
+            w13, w2 = layer.draw_expert(s, e, self.device, std=0.02)
+            w["w13"][e], w["w2"][e] = w13.cpu(), w2.cpu()
+        ref = ref_layer.decode_stack(hidden, self.start_pos, [w], iw, [caches], s, 1, freqs, topk)
+        return _criterion(out[:b], ref, tokens=b, layers=1)
 
     def config(self) -> dict:
         c = super().config()
@@ -782,6 +910,15 @@ def run_ours(args) -> None:
     e2e_ms = max_over_ranks(s2.elapsed_time(e2))
     clocks = sampler.stop()
     h2d, d2h = wl.e2e_bytes()
+    # validation of the timed configuration (outside every timed region)
+    check = None
+    if not args.no_check and hasattr(wl, "check"):
+        try:
+            torch.set_num_threads(len(os.sched_getaffinity(0)))
+        except (AttributeError, RuntimeError):
+            pass
+        check = wl.check()
+        barrier()
     from racetrack_b200 import ops
     ops.tc_error_state()
 
@@ -807,8 +944,13 @@ def run_ours(args) -> None:
             roof["other_bound"] = {k: tensor[k] for k in ("bound", "achieved", "peak", "unit")}
             roof["other_bound"]["frac"] = tensor["achieved"] / tensor["peak"]
             roof["algorithmic_flops"] = flops
+        traffic = getattr(wl, "dominant_traffic", None)
+        if traffic is not None:
+            # the captured launch touches every expert; its own algorithmic bytes stand beside
+            # the measured traffic (the average launch of the timed region touches fewer experts)
+            roof["traffic_launch_algorithmic_bytes"] = wl.dominant_bytes_all_experts
         roof.update({"frac": roof["achieved"] / roof["peak"], "peak_source": peak_src,
-                     "traffic": getattr(wl, "dominant_traffic", None), "avg_launch_us": dom_us,
+                     "traffic": traffic, "avg_launch_us": dom_us,
                      "launches_timed": len(wl.dom_events),
                      "algorithmic_bytes": wl.dominant_bytes})
         line = {
@@ -829,6 +971,7 @@ def run_ours(args) -> None:
             "gpu_launches": launches,
             "clocks": clocks,
         }
+        line["check"] = check
         line["config"]["cuda_graph"] = bool(use_graph)
         if use_graph:
             line["roofline"]["timed_in"] = "two eager steps after the replayed region"
@@ -870,6 +1013,8 @@ def main() -> None:
                     help="FFN of the layer: 256 routed NVFP4 experts, or the dense SwiGLU FFN of "
                          "width 18432 that the first three layers of the model use")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-check", action="store_true",
+                    help="skip the validation of the timed configuration against the CPU oracle")
     ap.add_argument("--graph", action="store_true",
                     help="capture the stack in a CUDA graph and replay it (decode sizes)")
     ap.add_argument("--no-graph", action="store_true",
@@ -878,8 +1023,8 @@ def main() -> None:
                     help="bracket the timed steps with cudaProfilerStart/Stop")
     args = ap.parse_args()
     if args.proj is None:
-        # prefill: FP8 where the reduction is long; decode: bf16, as BASELINE.json's decode
-        # configuration states ("bf16 with NVFP4 experts") and where few rows take the split-K path
+        # prefill: FP8 where the reduction is long; decode: bf16 ("bf16 with NVFP4 experts" is
+        # how the decode configuration is stated), where few rows take the split-K path
         args.proj = getattr(WORKLOADS[args.workload], "default_proj", "mixed")
     PrefillStackWorkload.ffn = args.ffn          # the CPU legs draw the same variant
     if args.impl == "reference":

@@ -11,8 +11,9 @@ namespace rt {
 namespace tc {
 
 // Set by a kernel whose bounded wait expired (value = code of the wait that gave up).
-// Read and cleared by rt_tc_error_state(). One copy per translation unit: every
-// tensor-core kernel of the library is compiled into the same unit (rt_gemm.cu).
+// Read and cleared by rt_tc_error_state(). One copy per translation unit that includes this
+// header (the GEMMs in rt_gemm.cu, the attention kernels in rt_attn.cu); rt_tc_error_state()
+// collects all of them.
 static __device__ int g_tc_error = 0;
 
 // Spin budget of every device-side wait, in SM clock cycles (~1 s at 2 GHz). A healthy

@@ -136,13 +136,16 @@ def moe_quant_nvfp4(x: torch.Tensor, tile_map: torch.Tensor, tile_count: torch.T
 def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor,
                       experts: NVFP4Experts, *, n_experts: int, expert_begin: int = 0,
                       shared: Optional[torch.Tensor] = None,
-                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                      out_dtype: torch.dtype = torch.bfloat16,
+                      parts: Optional[dict] = None) -> torch.Tensor:
     """y[t] = sum over the token's routed experts owned here of w * expert(x[t]) (+ shared[t]).
 
     x [T, hidden] bf16; weights fp32 [T, k] and indices int64 [T, k] from fused_moe_route;
     `experts` holds the experts [expert_begin, expert_begin + experts.count) of n_experts (an
     expert-parallel rank passes its own slice and all-reduces the result). Expert arithmetic:
     NVFP4(x) . NVFP4(w13)^T -> bf16 gate/up -> NVFP4(swiglu) . NVFP4(w2)^T -> bf16, fp32 combine.
+    A dict passed as `parts` receives the intermediates (expert offsets, permutation, the two
+    tensor-wide amax values, gate_up, h and the per-pair expert outputs) for stage-wise checks.
     """
     tokens, hidden = x.shape
     topk = indices.shape[1]
@@ -169,6 +172,9 @@ def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     h_codes, h_sf, h_gs = moe_quant_nvfp4(h, tile_map, tile_count, pairs, amax=h_amax)
     expert_out = ops.gemm_nvfp4_grouped(h_codes, h_sf, h_gs, experts.w2_codes, experts.w2_sf,
                                         experts.w2_gs, tile_map, tile_count, n=hidden, groups=count)
+    if parts is not None:
+        parts.update(offsets=offsets, sorted_pairs=sorted_pairs, pair_pos=pair_pos, x_gs=a_gs,
+                     gate_up=gate_up, h=h, h_amax=h_amax, expert_out=expert_out)
     return ops.fused_moe_combine(expert_out, pair_pos, weights, shared, pos_window=window,
                                  out_dtype=out_dtype)
 
@@ -177,12 +183,16 @@ def fused_moe_forward(x: torch.Tensor, gate_weight: torch.Tensor, gate_bias: Opt
                       experts: NVFP4Experts, *, n_experts: int, n_groups: int, topk_groups: int,
                       topk: int, route_scale: float, score_func: str = "sigmoid",
                       expert_begin: int = 0, shared: Optional[torch.Tensor] = None,
-                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                      out_dtype: torch.dtype = torch.bfloat16,
+                      parts: Optional[dict] = None) -> torch.Tensor:
     """Gate (fp32 logits as in racetrack/models/deepseek.py:898, formed on the tensor cores from
     the bf16 operands with the fp32 accumulators kept) + routing kernel + experts."""
     logits = ops.linear_bf16(x, gate_weight.to(torch.bfloat16), out_dtype=torch.float32)
     weights, indices = ops.fused_moe_route(logits, gate_bias, n_groups=n_groups,
                                            topk_groups=topk_groups, topk=topk,
                                            route_scale=route_scale, score_func=score_func)
+    if parts is not None:
+        parts.update(logits=logits, weights=weights, indices=indices)
     return fused_moe_experts(x, weights, indices, experts, n_experts=n_experts,
-                             expert_begin=expert_begin, shared=shared, out_dtype=out_dtype)
+                             expert_begin=expert_begin, shared=shared, out_dtype=out_dtype,
+                             parts=parts)

@@ -94,3 +94,36 @@ def test_two_rank_partials_sum_to_the_single_rank_result(D):
         parts.append(m.decode_attention(normed, START).float())
     ops.tc_error_state()
     assert rel_err(parts[0] + parts[1], whole) <= 2e-2
+
+
+def test_replayed_cuda_graph_equals_the_eager_step(D):
+    """The decode step as the benchmark runs it by default: captured once in a CUDA graph and
+    replayed (racetrack/bench.py:98-111 does the same for its sweeps). No kernel of the step
+    depends on launch timing (the split-K projections add their partial sums in a fixed
+    order), so a replay must reproduce the eager result bit for bit, twice in a row, and leave
+    the same cache rows behind."""
+    decode, layer, ops = D
+    shape, w, iw, c_cpu, model, hidden = _setup(D)
+    x = hidden.cuda()
+    eager = model.decode_stack(x, START, 2).clone()
+    ops.tc_error_state()
+    rows = [t[:, START].clone() for t in (model.caches.kv, model.caches.pe, model.caches.index_k.view(torch.uint8),
+                                          model.caches.index_scale)]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        model.decode_stack(x, START, 2)
+    torch.cuda.current_stream().wait_stream(side)
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        out = model.decode_stack(x, START, 2)
+    for _ in range(2):
+        model.caches.kv[:, START].zero_()
+        model.caches.pe[:, START].zero_()
+        graph.replay()
+        ops.tc_error_state()
+        assert torch.equal(out, eager), "graph replay differs from the eager step"
+        now = [t[:, START] for t in (model.caches.kv, model.caches.pe, model.caches.index_k.view(torch.uint8),
+                                     model.caches.index_scale)]
+        for a, b in zip(now, rows):
+            assert torch.equal(a, b), "cache rows after a replay differ from the eager step's"

@@ -43,6 +43,36 @@ def test_baseline_model_with_partition_matches_torch_baseline(spec, cuda_backend
     assert part.backend_status["cuda"] == "native"
 
 
+def test_torch_compile_of_the_baseline_model_with_the_shipped_partition(spec, cuda_backend):
+    """The partition swapped in for the dsv3_2 baseline model under torch.compile: the model is
+    compiled with the partition's backend (pre-trace patches, Dynamo, FX rewrite of the SwiGLU
+    pattern to the custom op) and must agree with the eager torch baseline within the
+    reference's smoke criterion (racetrack/bench.py:266-268,409), running this library's
+    kernels (fused_norm_rope through the dispatcher, fused_swiglu through the rewrite)."""
+    from racetrack_b200 import _lib, compile_backend
+    from racetrack_b200.partitions.dsv3_2 import model as syn
+    cfg = syn.DSV3_2_CONFIG
+    base = syn.FlattenedDeepSeekModel(cfg).cuda().to(torch.bfloat16)
+    part = syn.FlattenedDeepSeekModel(cfg, partition_root=spec.partition_dir).cuda().to(torch.bfloat16)
+    part.load_state_dict(base.state_dict())
+    tokens = torch.randint(0, cfg.vocab_size, (64,), device="cuda")
+    try:
+        with torch.no_grad():
+            want = base(tokens)
+            compiled, originals = compile_backend.compile_with_partition(part, spec, backend_override="cuda")
+            before = _lib.launch_count()
+            got = compiled(tokens)
+            launches = _lib.launch_count() - before
+            again = compiled(tokens)
+    finally:
+        compile_backend.cleanup_compile_state()
+    from racetrack_b200 import pre_trace
+    pre_trace.rollback_patches(originals)
+    assert launches >= cfg.num_layers, f"only {launches} kernel launches under torch.compile"
+    assert float((got.float() - want.float()).abs().max()) <= 5e-2
+    assert torch.equal(got, again)
+
+
 class Block(nn.Module):
     def __init__(self):
         super().__init__()

@@ -288,3 +288,35 @@ def test_baseline_model_dispatches_fused_norm_rope(tmp_path, backend_env):
     assert calls == [((16, 128), (16, 128), (16, 16), False)]     # column slices, not copies
     assert part_model.backend_status == {"torch": "native", "cuda": "native"}
     assert syn.build_model(num_layers=1).config.num_layers == 1
+
+
+def test_fp8_module_weights_are_dequantised_with_their_block_scales():
+    """A racetrack `Linear` holds float8_e4m3fn codes plus one fp32 scale per 128 x 128 block
+    when its dtype is FP8 (racetrack/models/deepseek.py:361-371). The kernel wrappers that
+    convert a module's weights (experts to NVFP4, indexer projections to bf16) must dequantise
+    them as `weight_dequant` does (deepseek.py:689-694) instead of reading the codes as values,
+    and must refuse an FP8 weight that has no scales."""
+    import pytest
+    from oracle import ref_ops as R
+    from racetrack_b200 import ops
+    g = torch.Generator().manual_seed(9)
+    full = torch.randn(200, 384, generator=g) * 0.05
+    scale = torch.rand(2, 3, generator=g) * 0.01 + 0.001
+    codes = (full / scale.repeat_interleave(128, 0)[:200].repeat_interleave(128, 1)).clamp(-448, 448) \
+        .to(torch.float8_e4m3fn)
+
+    class Linear(torch.nn.Module):
+        def __init__(self, weight, scale=None):
+            super().__init__()
+            self.weight = torch.nn.Parameter(weight, requires_grad=False)
+            if scale is not None:
+                self.weight.scale = self.scale = torch.nn.Parameter(scale, requires_grad=False)
+
+    got = ops.module_weight_bf16(Linear(codes, scale))
+    want = R.block_dequant(codes, scale)
+    assert got.dtype == torch.bfloat16 and torch.equal(got, want.to(torch.bfloat16))
+    assert float((got.float() - full).abs().max()) <= 0.07 * float(full.abs().max())
+    plain = ops.module_weight_bf16(Linear(full))
+    assert torch.equal(plain, full.to(torch.bfloat16))
+    with pytest.raises(RuntimeError):
+        ops.module_weight_bf16(Linear(codes))
