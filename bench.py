@@ -112,15 +112,26 @@ class ClockSampler(threading.Thread):
 CHECK_ATOL, CHECK_RTOL = 0.5, 0.1     # racetrack/realistic_bench.py:538,645-646
 
 
-def _criterion(out: torch.Tensor, ref: torch.Tensor, **what) -> dict:
+def _criterion(out: torch.Tensor, ref: torch.Tensor, ref_bf16=None, **what) -> dict:
     """The reference runner's pass criterion for a configuration: max |out - ref| against
-    atol + rtol * max |ref| (racetrack/realistic_bench.py:530-538)."""
-    diff = float((out.float().cpu() - ref.float()).abs().max())
-    scale = float(ref.float().abs().max())
-    return {"diff": diff, "rel": diff / max(scale, 1e-30), "max_abs_ref": scale,
-            "ok": bool(diff <= CHECK_ATOL + CHECK_RTOL * scale),
-            "criterion": f"diff <= {CHECK_ATOL} + {CHECK_RTOL} * max|ref|",
-            "against": "CPU restatement of the reference's torch path, same bf16 weights", **what}
+    atol + rtol * max |ref| (racetrack/realistic_bench.py:530-538). `ref` is the CPU
+    restatement of the reference's torch path in the timed configuration's own arithmetic;
+    `ref_bf16`, when given, the same layers with every weight and activation left in bf16."""
+    def dist(r):
+        diff = float((out.float().cpu() - r.float()).abs().max())
+        scale = float(r.float().abs().max())
+        return {"diff": diff, "rel": diff / max(scale, 1e-30), "max_abs_ref": scale,
+                "ok": bool(diff <= CHECK_ATOL + CHECK_RTOL * scale)}
+    res = dist(ref)
+    res.update({"criterion": f"diff <= {CHECK_ATOL} + {CHECK_RTOL} * max|ref|",
+                "against": "CPU restatement of the reference's torch path in the timed "
+                           "configuration's arithmetic (both operands of a quantised linear "
+                           "quantised, dequantised values multiplied), same weights", **what})
+    if ref_bf16 is not None:
+        res["vs_unquantised_bf16"] = dist(ref_bf16)
+        own = float((ref.float() - ref_bf16.float()).abs().max()) / max(float(ref_bf16.float().abs().max()), 1e-30)
+        res["vs_unquantised_bf16"]["oracle_own_rel"] = own
+    return res
 
 
 class PrefillStackWorkload:
@@ -319,15 +330,19 @@ class PrefillStackWorkload:
         self.recording = False
         return out
 
-    CHECK_TOKENS, CHECK_LAYERS = 16, 2
+    CHECK_TOKENS, CHECK_LAYERS = 8, 2
 
     def check(self):
         """Validation of what is timed, outside the timed region, as the reference runner does
         for every configuration (racetrack/realistic_bench.py:530-538): the benchmark's own model
         object runs the first CHECK_TOKENS tokens of its input through CHECK_LAYERS layers (all
         ranks, collectives included) and rank 0 compares the result with the CPU restatement of
-        the reference layer on the same bf16 weights: ok = diff <= 0.5 + 0.1 * max|ref|."""
-        from oracle import ref_layer, ref_ops as R
+        the reference layer on the same weights, evaluated in the same arithmetic (the
+        reference's torch path of a quantised linear quantises both operands and multiplies
+        the dequantised values, racetrack/models/deepseek.py:113-121,343-345; the oracle does
+        that for the FP8 projections and the NVFP4 experts): ok = diff <= 0.5 + 0.1 * max|ref|.
+        The distance to the un-quantised bf16 layer is reported beside it."""
+        from oracle import ref_layer
         layer, s = self.layer_mod, self.shape
         t, n_layers = min(self.CHECK_TOKENS, self.tokens), self.CHECK_LAYERS
         sample, pos = self.hidden[:t].clone(), self.positions[:t]
@@ -340,21 +355,16 @@ class PrefillStackWorkload:
         del full
         h, p = sample.cpu(), pos.cpu()
         if dense:
-            ref = ref_layer.forward_stack(h, p, [w], s, n_layers, ffn="dense")
+            ref = ref_layer.forward_stack(h, p, [w], s, n_layers, ffn="dense", proj=self.proj)
+            ref16 = ref_layer.forward_stack(h, p, [w], s, n_layers, ffn="dense")
         else:
-            w["w13"] = torch.empty(s.n_experts, 2 * s.moe_inter, s.hidden, dtype=torch.bfloat16)
-            w["w2"] = torch.empty(s.n_experts, s.hidden, s.moe_inter, dtype=torch.bfloat16)
-            ones, drawn, ref = torch.ones(s.hidden, dtype=torch.bfloat16), set(), h
-            for _ in range(n_layers):
-                mid = ref + ref_layer.attention(R.rms_norm(ref, ones, s.eps), p, w, s, s.heads)
-                normed = R.rms_norm(mid, ones, s.eps)
-                logits = torch.nn.functional.linear(normed.float(), w["w_gate"].float())
-                for e in sorted(set(torch.topk(logits, s.topk, dim=-1)[1].flatten().tolist()) - drawn):
-                    w13, w2 = layer.draw_expert(s, e, self.device, std=0.02)
-                    w["w13"][e], w["w2"][e] = w13.cpu(), w2.cpu()
-                    drawn.add(e)
-                ref = mid + ref_layer.moe(normed, w, s, 0, s.n_experts)
-        return _criterion(out, ref, tokens=t, layers=n_layers)
+            bank = ref_layer.ExpertBank(
+                s, w, lambda e: layer.draw_expert(s, e, self.device, std=0.02),
+                quantise=lambda x: self.ops.fused_nvfp4_quant(x))
+            ref = ref_layer.forward_stack(h, p, [w], s, n_layers, experts="nvfp4", proj=self.proj,
+                                          before_moe=bank.route)
+            ref16 = ref_layer.forward_stack(h, p, [w], s, n_layers, before_moe=bank.route)
+        return _criterion(out, ref, ref16, tokens=t, layers=n_layers)
 
     def e2e_setup(self):
         self.host_in = torch.empty(self.hidden.shape, dtype=torch.bfloat16, pin_memory=True)
@@ -503,24 +513,37 @@ class MoeLayerWorkload:
         return self._run(self.x, record)
 
     def check(self):
-        """The first 16 tokens of the timed input through the same code path, against
-        racetrack's MoE.forward (oracle/ref_ops.moe_forward) on the bf16 weights."""
+        """The first 8 tokens of the timed input through the same code path, against
+        racetrack's MoE.forward on the CPU (oracle/ref_ops: Gate.forward, the expert loop on
+        NVFP4 operands, the bf16 shared expert); the un-quantised MoE.forward stands beside it."""
         from oracle import ref_ops as R
         from racetrack_b200 import layer
-        s, t = self.shape, min(16, self.tokens)
+        s, t = self.shape, min(8, self.tokens)
         out = self._run(self.x[:t].clone(), False)
         if self.rank != 0:
             return None
         kw = dict(n_groups=8, topk_groups=4, topk=s.topk, route_scale=2.5)
         x, wg, b = self.x[:t].cpu(), self.w_gate.cpu(), self.bias.cpu()
-        _, idx = R.gate_forward(x, wg, b, **kw)
-        inter = s.moe_inter
+        wts, idx = R.gate_forward(x, wg, b, **kw)
+        inter, dev = s.moe_inter, self.x.device
         split = lambda w13, w2: (w13[:inter].cpu(), w2.cpu(), w13[inter:].cpu())     # (w1, w2, w3)
         experts = [None] * s.n_experts
+        w13 = torch.empty(s.n_experts, 2 * inter, s.hidden, dtype=torch.bfloat16)
+        w2 = torch.empty(s.n_experts, s.hidden, inter, dtype=torch.bfloat16)
+        gs13, gs2 = torch.zeros(s.n_experts), torch.zeros(s.n_experts)
+        one = torch.ones((), device=dev)
         for e in sorted(set(idx.flatten().tolist())):
-            experts[e] = split(*layer.draw_expert(s, e, self.x.device, std=0.02))
-        ref = R.moe_forward(x, wg, b, experts, split(self.sw13, self.sw2), **kw)
-        return _criterion(out, ref, tokens=t, layers=1)
+            a, c = layer.draw_expert(s, e, dev, std=0.02)
+            experts[e] = split(a, c)
+            for dst, gsv, m in ((w13, gs13, a), (w2, gs2, c)):
+                codes, sf, gs = self.ops.fused_nvfp4_quant(m)
+                dst[e] = R.nvfp4_dequant(codes, sf, one).to(torch.bfloat16).cpu()
+                gsv[e] = float(gs)
+        shared = split(self.sw13, self.sw2)
+        ref = R.moe_experts_nvfp4(x, wts.float(), idx, w13, w2, shared_out=R.expert_mlp(x, *shared),
+                                  weights_dequantised=(gs13, gs2))
+        ref16 = R.moe_forward(x, wg, b, experts, shared, **kw)
+        return _criterion(out, ref, ref16, tokens=t, layers=1)
 
     def e2e_setup(self):
         self.host_in = torch.empty(self.x.shape, dtype=torch.bfloat16, pin_memory=True)
@@ -718,14 +741,14 @@ class DecodeLayerWorkload(PrefillStackWorkload):
         probe = {k: v.clone() for k, v in caches.items()}
         mid = hidden + ref_layer.decode_attention(R.rms_norm(hidden, ones, s.eps), self.start_pos, w, iw,
                                                   probe, s, s.heads, freqs, topk)
-        logits = torch.nn.functional.linear(R.rms_norm(mid, ones, s.eps).float(), w["w_gate"].float())
-        w["w13"] = torch.empty(s.n_experts, 2 * s.moe_inter, s.hidden, dtype=torch.bfloat16)
-        w["w2"] = torch.empty(s.n_experts, s.hidden, s.moe_inter, dtype=torch.bfloat16)
-        for e in sorted(set(torch.topk(logits, s.topk, dim=-1)[1].flatten().tolist())):
-            w13, w2 = layer.draw_expert(s, e, self.device, std=0.02)
-            w["w13"][e], w["w2"][e] = w13.cpu(), w2.cpu()
-        ref = ref_layer.decode_stack(hidden, self.start_pos, [w], iw, [caches], s, 1, freqs, topk)
-        return _criterion(out[:b], ref, tokens=b, layers=1)
+        bank = ref_layer.ExpertBank(s, w, lambda e: layer.draw_expert(s, e, self.device, std=0.02),
+                                    quantise=lambda x: self.ops.fused_nvfp4_quant(x))
+        bank.route(R.rms_norm(mid, ones, s.eps))
+        again = {k: v.clone() for k, v in caches.items()}
+        ref = ref_layer.decode_stack(hidden, self.start_pos, [w], iw, [caches], s, 1, freqs, topk,
+                                     experts="nvfp4")
+        ref16 = ref_layer.decode_stack(hidden, self.start_pos, [w], iw, [again], s, 1, freqs, topk)
+        return _criterion(out[:b], ref, ref16, tokens=b, layers=1)
 
     def config(self) -> dict:
         c = super().config()

@@ -32,24 +32,47 @@ def _all_reduce(parts):
     return total.to(parts[0].dtype)
 
 
-def attention(hidden, positions, w, shape, local_heads):
-    """One rank's attention partial. ref: racetrack/realistic_bench.py:286-315."""
+MIXED_FP8_MIN_K = 4096
+
+
+def make_linear(proj: str = "bf16"):
+    """The projection arithmetic of a stack: "bf16" = F.linear; "fp8" / "mixed" = the
+    reference's own path for FP8 weights (act_quant + dequantise-then-matmul fp8_gemm, ref:
+    racetrack/models/deepseek.py:316-345) for every projection whose K is a multiple of 128
+    ("mixed": only where K >= 4096). Quantised weights are cached per weight tensor."""
+    cache: dict = {}
+
+    def linear(x, weight):
+        k = weight.shape[1]
+        fp8 = k % 128 == 0 and (proj == "fp8" or (proj == "mixed" and k >= MIXED_FP8_MIN_K))
+        if not fp8:
+            return F.linear(x, weight)
+        key = (weight.data_ptr(), tuple(weight.shape))
+        if key not in cache:
+            cache[key] = R.quantize_weight_fp8(weight)
+        return R.linear_fp8(x, *cache[key])
+    return linear
+
+
+def attention(hidden, positions, w, shape, local_heads, linear=F.linear):
+    """One rank's attention partial. ref: racetrack/realistic_bench.py:286-315. `linear` swaps the
+    four projections' arithmetic (make_linear)."""
     s = shape
-    qkv = F.linear(hidden, w["w_qkv_a"])
+    qkv = linear(hidden, w["w_qkv_a"])
     q_c, kv_c, k_pe = qkv.split([s.q_lora, s.kv_lora, s.rope], dim=-1)
     ones_q = torch.ones(s.q_lora, dtype=hidden.dtype)
     ones_kv = torch.ones(s.kv_lora, dtype=hidden.dtype)
     q_c, kv_c, k_pe = R.fused_norm_rope(q_c, ones_q, kv_c, ones_kv, k_pe, positions, eps=s.eps,
                                         rope_base=s.rope_base)
     tokens = hidden.shape[0]
-    q = F.linear(q_c, w["w_q_b"]).view(tokens, local_heads, s.nope + s.rope)
+    q = linear(q_c, w["w_q_b"]).view(tokens, local_heads, s.nope + s.rope)
     q_nope, q_pe = q.split([s.nope, s.rope], dim=-1)
     q = torch.cat((q_nope, R.apply_rope(q_pe, positions, base=s.rope_base)), dim=-1)
-    kv = F.linear(kv_c, w["w_kv_b"]).view(tokens, local_heads, s.nope + s.v_dim)
+    kv = linear(kv_c, w["w_kv_b"]).view(tokens, local_heads, s.nope + s.v_dim)
     k_nope, v = kv.split([s.nope, s.v_dim], dim=-1)
     k = torch.cat((k_nope, k_pe.unsqueeze(1).expand(-1, local_heads, -1)), dim=-1)
     local = causal_attention(q, k, v)
-    return F.linear(local.reshape(tokens, local_heads * s.v_dim), w["w_o"])
+    return linear(local.reshape(tokens, local_heads * s.v_dim), w["w_o"])
 
 
 def moe(hidden, w, shape, rank, local_experts):
@@ -77,7 +100,18 @@ def moe(hidden, w, shape, rank, local_experts):
 def moe_nvfp4(hidden, w, shape, rank, local_experts):
     """Same routing as `moe`, experts evaluated on NVFP4-quantised operands
     (ref_ops.moe_experts_nvfp4): what the B200 layer computes, for tight comparisons. The
-    NVFP4 arithmetic has no reference counterpart (parity unpinned)."""
+    NVFP4 arithmetic has no reference counterpart (parity unpinned). A weight dict that carries
+    "w13_dq" / "w2_dq" ([E, ...] for ALL experts, values already dequant(NVFP4(w))) is used as
+    is; otherwise the rank's bf16 "w13" / "w2" are quantised here."""
+    if "w13_dq" in w:
+        s = shape
+        logits = F.linear(hidden.float(), w["w_gate"].float())
+        topk_logits, topk_ids = torch.topk(logits, s.topk, dim=-1)
+        topk_weights = torch.softmax(topk_logits, dim=-1).to(hidden.dtype).float()
+        lo, hi = rank * local_experts, (rank + 1) * local_experts
+        return R.moe_experts_nvfp4(hidden, topk_weights, topk_ids, w["w13_dq"], w["w2_dq"],
+                                   expert_range=(lo, hi),
+                                   weights_dequantised=(w["w13_gs"], w["w2_gs"]))
     s = shape
     logits = F.linear(hidden.float(), w["w_gate"].float())
     topk_logits, topk_ids = torch.topk(logits, s.topk, dim=-1)
@@ -90,15 +124,68 @@ def moe_nvfp4(hidden, w, shape, rank, local_experts):
     return R.moe_experts_nvfp4(hidden, topk_weights, topk_ids, w13, w2, expert_range=(lo, hi))
 
 
+class ExpertBank:
+    """Full-width expert weights for the oracle, materialised one expert at a time: only the
+    experts a sample routes to exist (all 256 in bf16 would take 22.5 GB). `draw(e)` returns
+    the bf16 (w13 [2I, H], w2 [H, I]) of expert e on any device; `quantise(t)` returns the NVFP4
+    (codes, row-major block scales, global scale) of a matrix on that device (default: the
+    CPU quantiser of ref_ops; a caller with a GPU passes a device quantiser that its own tests
+    show bit-identical, because the CPU one takes about a second per expert). The dict
+    `weights` gains "w13" / "w2" (bf16) and "w13_dq" / "w2_dq" / "w13_gs" / "w2_gs" (NVFP4 values
+    code * block scale, exact in bf16, and the global scales) for forward_stack."""
+
+    def __init__(self, shape, weights: dict, draw, quantise=None):
+        s = shape
+        self.shape, self.w, self.draw, self.drawn = shape, weights, draw, set()
+        self.quantise = quantise if quantise is not None else R.nvfp4_quant
+        e, i, h = s.n_experts, s.moe_inter, s.hidden
+        for key, dims in (("w13", (e, 2 * i, h)), ("w2", (e, h, i))):
+            weights[key] = torch.empty(dims, dtype=torch.bfloat16)
+            weights[key + "_dq"] = torch.empty(dims, dtype=torch.bfloat16)
+            weights[key + "_gs"] = torch.zeros(e, dtype=torch.float32)
+
+    def need(self, experts) -> None:
+        for e in sorted(set(int(x) for x in experts) - self.drawn):
+            for key, t in zip(("w13", "w2"), self.draw(e)):
+                codes, sf, gs = self.quantise(t)
+                one = torch.ones((), dtype=torch.float32, device=codes.device)
+                dq = R.nvfp4_dequant(codes, sf, one).to(torch.bfloat16)
+                self.w[key][e], self.w[key + "_dq"][e] = t.cpu(), dq.cpu()
+                self.w[key + "_gs"][e] = gs.reshape(()).float().cpu()
+            self.drawn.add(e)
+
+    def route(self, normed) -> None:
+        """Materialises the experts the top-k router sends `normed` to (a near-tie may go the
+        other way in another arithmetic, so the runner-up is drawn as well)."""
+        logits = F.linear(normed.float(), self.w["w_gate"].float())
+        self.need(torch.topk(logits, self.shape.topk + 1, dim=-1)[1].flatten().tolist())
+
+
 def dense_ffn(hidden, w):
     """Dense SwiGLU FFN shard (the first-layers variant): w2(silu(w1 x) * w3 x)."""
     return F.linear(F.silu(F.linear(hidden, w["w1"])) * F.linear(hidden, w["w3"]), w["w2d"])
 
 
-def forward_stack(hidden, positions, rank_weights, shape, layers, ffn="moe", experts="bf16"):
+def dense_ffn_fp8(hidden, w, linear):
+    """The dense FFN with the projections' arithmetic swapped (gate and up as one projection of
+    the concatenated weight, as the product runs it; the FP8 block scales of w1 and w3 are
+    per 128 rows, so the concatenation quantises exactly like the two halves)."""
+    if "w13d" not in w:
+        w["w13d"] = torch.cat([w["w1"], w["w3"]])
+    gate_up = linear(hidden, w["w13d"])
+    inter = gate_up.shape[1] // 2
+    return linear(R.swiglu(gate_up[:, :inter], gate_up[:, inter:]), w["w2d"])
+
+
+def forward_stack(hidden, positions, rank_weights, shape, layers, ffn="moe", experts="bf16",
+                  proj="bf16", before_moe=None):
     """ref: racetrack/realistic_bench.py:375-389 (hc_mult == 1 branch) applied `layers` times.
-    experts="nvfp4" swaps the bf16 expert matmuls for their NVFP4-quantised evaluation."""
+    experts="nvfp4" swaps the bf16 expert matmuls for their NVFP4-quantised evaluation and
+    proj="fp8" / "mixed" the projections for the reference's FP8 path (make_linear): the same
+    model in the arithmetic the B200 layer runs. `before_moe(normed)` is called with the MoE's
+    input of every layer (a full-width caller materialises the experts that input routes to)."""
     moe_fn = moe if experts == "bf16" else moe_nvfp4
+    linear = make_linear(proj)
     world = len(rank_weights)
     ones = torch.ones(shape.hidden, dtype=hidden.dtype)
     local_heads = shape.heads // world
@@ -106,14 +193,18 @@ def forward_stack(hidden, positions, rank_weights, shape, layers, ffn="moe", exp
     for _ in range(layers):
         residual = hidden
         h = R.rms_norm(hidden, ones, shape.eps)
-        attn = _all_reduce([attention(h, positions, w, shape, local_heads) for w in rank_weights])
+        attn = _all_reduce([attention(h, positions, w, shape, local_heads, linear) for w in rank_weights])
         hidden = residual + attn
         residual = hidden
         h = R.rms_norm(hidden, ones, shape.eps)
         if ffn == "moe":
+            if before_moe is not None:
+                before_moe(h)
             out = _all_reduce([moe_fn(h, w, shape, r, local_experts) for r, w in enumerate(rank_weights)])
-        else:
+        elif proj == "bf16":
             out = _all_reduce([dense_ffn(h, w) for w in rank_weights])
+        else:
+            out = _all_reduce([dense_ffn_fp8(h, w, linear) for w in rank_weights])
         hidden = residual + out
     return hidden
 

@@ -296,6 +296,28 @@ def block_dequant(weight: torch.Tensor, scale: torch.Tensor, block: int = FP8_BL
     return (weight.float() * s).to(torch.bfloat16)
 
 
+def quantize_weight_fp8(weight: torch.Tensor, block: int = FP8_BLOCK):
+    """bf16 / fp32 weight [out, in] -> (e4m3fn codes, fp32 scales [ceil(out/128), in/128]): one
+    scale = amax / 448 (amax clamped at 1e-4) per 128 x 128 block, the checkpoint layout that
+    `Linear` holds (ref: racetrack/models/deepseek.py:361-371) and `block_dequant` inverts."""
+    n, k = weight.shape
+    nb = (n + block - 1) // block
+    w = torch.zeros(nb * block, k, dtype=torch.float32)
+    w[:n] = weight.float()
+    blocks = w.view(nb, block, k // block, block)
+    scale = blocks.abs().amax(dim=(1, 3)).clamp(min=1e-4) / FP8_MAX
+    codes = (blocks / scale[:, None, :, None]).clamp(-FP8_MAX, FP8_MAX).to(torch.float8_e4m3fn)
+    return codes.view(nb * block, k)[:n].contiguous(), scale.contiguous()
+
+
+def linear_fp8(x: torch.Tensor, w_codes: torch.Tensor, w_scales: torch.Tensor) -> torch.Tensor:
+    """`linear(x, weight)` for an FP8 weight as the reference's torch path runs it: act_quant of
+    the activations, then the dequantise-then-matmul fp8_gemm.
+    ref: racetrack/models/deepseek.py:343-345, 113-121."""
+    codes, scales = act_quant(x.contiguous())
+    return fp8_gemm(codes, scales, w_codes, w_scales)
+
+
 def fp8_gemm(a: torch.Tensor, a_s: torch.Tensor, b: torch.Tensor, b_s: torch.Tensor) -> torch.Tensor:
     """Dequantise-then-matmul fallback of the FP8 block-scaled GEMM.
     ref: racetrack/models/deepseek.py:113-121."""
@@ -323,7 +345,7 @@ def e2m1_encode(v: torch.Tensor) -> torch.Tensor:
 
 
 def e2m1_decode(code: torch.Tensor) -> torch.Tensor:
-    mag = _E2M1_VALUES[(code & 7).long()]
+    mag = _E2M1_VALUES.to(code.device)[(code & 7).long()]
     return torch.where((code & 8) != 0, -mag, mag)
 
 
@@ -452,13 +474,24 @@ def nvfp4_roundtrip(x: torch.Tensor, amax: Optional[torch.Tensor] = None) -> tor
     return nvfp4_dequant(*nvfp4_quant(x, amax))
 
 
-def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_range=None):
+def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_range=None,
+                      weights_dequantised=False):
     """MoE.forward's expert loop (ref: racetrack/models/deepseek.py:1011-1022) with NVFP4
     operands: x and swiglu(h) quantised with one tensor-wide global scale each (over the rows
     routed to the experts in `expert_range`), every expert's w13 [2I, H] / w2 [H, I] with its own;
     products of dequantised operands accumulate in fp32, GEMM outputs round to bf16.
     NVFP4 itself has no reference counterpart (parity unpinned); the control flow follows the
-    reference. Returns bf16 [T, H]."""
+    reference. With weights_dequantised = (w13_gs, w2_gs) (fp32 [E] global scales), w13 / w2 hold
+    code * block_scale of the already quantised weights (exact in bf16) and the products are
+    multiplied by the expert's global scale afterwards (a full-width caller quantises 256
+    experts once instead of on every call). Returns bf16 [T, H]."""
+    if weights_dequantised:
+        gs13, gs2 = weights_dequantised
+        mm13 = lambda a, e: (a @ w13[e].float().t()) * gs13[e]
+        mm2 = lambda a, e: (a @ w2[e].float().t()) * gs2[e]
+    else:
+        mm13 = lambda a, e: a @ nvfp4_roundtrip(w13[e]).t()
+        mm2 = lambda a, e: a @ nvfp4_roundtrip(w2[e]).t()
     tokens, hidden = x.shape
     n_experts = w13.shape[0]
     inter = w13.shape[1] // 2
@@ -469,7 +502,7 @@ def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_rang
         idx, top = torch.where(indices == e)
         if idx.numel() == 0:
             continue
-        gate_up = (xq[idx] @ nvfp4_roundtrip(w13[e]).t()).to(torch.bfloat16)
+        gate_up = mm13(xq[idx], e).to(torch.bfloat16)
         rows[e] = (idx, top, swiglu(gate_up[:, :inter], gate_up[:, inter:]))
     y = torch.zeros(tokens, hidden, dtype=torch.float32)
     if rows:
@@ -477,7 +510,7 @@ def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_rang
         # fp32 accumulation in slot order, as the combine kernel does
         outs = torch.zeros(tokens, indices.shape[1], hidden, dtype=torch.float32)
         for e, (idx, top, h) in rows.items():
-            out = (nvfp4_roundtrip(h, h_amax) @ nvfp4_roundtrip(w2[e]).t()).to(torch.bfloat16)
+            out = mm2(nvfp4_roundtrip(h, h_amax), e).to(torch.bfloat16)
             outs[idx, top] = out.float() * weights[idx, top, None]
         for s in range(indices.shape[1]):
             y = y + outs[:, s]

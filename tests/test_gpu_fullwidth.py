@@ -2,9 +2,11 @@
 experts of width 2048, FP8 / bf16 projections), not scaled-down copies of them.
 
 * the prefill layer on a few dozen tokens against the CPU restatement of racetrack's
-  ShardedRealisticBlock with bf16 weights, under the reference runner's own criterion
-  diff <= 0.5 + 0.1 * max|ref| (racetrack/realistic_bench.py:530-538), with the expert stage also
-  compared tightly against the NVFP4 oracle on the rows of a handful of experts;
+  ShardedRealisticBlock evaluated in the layer's own arithmetic (FP8 projections as the
+  reference's torch path runs them, NVFP4 experts), under the reference runner's criterion
+  diff <= 0.5 + 0.1 * max|ref| (racetrack/realistic_bench.py:530-538); the distance to the
+  un-quantised bf16 layer is reported beside it, and the expert stage is compared tightly with
+  the NVFP4 oracle on the rows of a handful of experts;
 * the routed MoE layer at T = 4096 (sigmoid + bias gate, 8 groups / top-4 / top-8, shared expert):
   routing indices against racetrack's Gate, expert outputs against the NVFP4 oracle for a handful
   of experts, the combine against the slot-ordered fp32 sum.
@@ -42,10 +44,20 @@ def _oracle_expert(x_rt, rows, w13, w2, h_amax, inter):
     return (R.nvfp4_roundtrip(h, h_amax) @ R.nvfp4_roundtrip(w2).t()).to(torch.bfloat16)
 
 
-@pytest.mark.parametrize("tokens,layers", [(32, 1), (24, 2)])
+@pytest.mark.parametrize("tokens,layers", [(16, 1), (8, 2)])
 def test_full_width_prefill_layer_meets_the_runner_criterion(tokens, layers):
     """The benchmark's own model object (mixed FP8 / bf16 projections, NVFP4 experts, this
-    backend's attention core) on a short sequence, against the bf16 reference layer."""
+    backend's attention core) on a short sequence.
+
+    The reference's torch path for a quantised linear layer quantises BOTH operands and multiplies
+    the dequantised values (act_quant + fp8_gemm's dequantise-then-matmul, deepseek.py:113-121,
+    343-345); the oracle evaluates the layer the same way for the FP8 projections and the NVFP4
+    experts, and that is what the runner's criterion diff <= 0.5 + 0.1 * max|ref| is asserted
+    against, together with a tighter bound. Against the UN-quantised bf16 layer the distance is
+    reported and only loosely bounded: e2m1 keeps one mantissa bit, so NVFP4 weights alone move
+    the expert outputs of this white-noise model by 17 % RMS and NVFP4 activations by as much
+    again; no implementation of the format can meet a 10 % bound there (the oracle's own NVFP4
+    evaluation sits as far from the bf16 layer as the GPU does)."""
     from racetrack_b200 import layer, ops
     shape = layer.DSV32
     dev = torch.device("cuda")
@@ -55,38 +67,39 @@ def test_full_width_prefill_layer_meets_the_runner_criterion(tokens, layers):
     hidden.normal_(mean=0.0, std=0.01, generator=g)
     positions = torch.arange(tokens, device=dev)
     cpu_w = {k: v.cpu() for k, v in w.items()}
-
-    # the reference decides which experts the sample needs, layer by layer; an expert is drawn
-    # on the GPU (the benchmark's generator), quantised for the product, copied for the oracle
-    cpu_w["w13"] = torch.empty(shape.n_experts, 2 * shape.moe_inter, shape.hidden, dtype=torch.bfloat16)
-    cpu_w["w2"] = torch.empty(shape.n_experts, shape.hidden, shape.moe_inter, dtype=torch.bfloat16)
-    ones = torch.ones(shape.hidden, dtype=torch.bfloat16)
-    drawn: set = set()
+    bank = ref_layer.ExpertBank(shape, cpu_w, lambda e: layer.draw_expert(shape, e, dev, std=0.02),
+                                quantise=lambda t: ops.fused_nvfp4_quant(t))
     h_cpu, pos_cpu = hidden.cpu(), positions.cpu()
-    ref = h_cpu
-    for _ in range(layers):
-        mid = ref + ref_layer.attention(R.rms_norm(ref, ones, shape.eps), pos_cpu, cpu_w, shape, shape.heads)
-        normed = R.rms_norm(mid, ones, shape.eps)
-        logits = F.linear(normed.float(), cpu_w["w_gate"].float())
-        for e in sorted(set(torch.topk(logits, shape.topk, dim=-1)[1].flatten().tolist()) - drawn):
-            w13, w2 = layer.draw_expert(shape, e, dev, std=0.02)
-            cpu_w["w13"][e], cpu_w["w2"][e] = w13.cpu(), w2.cpu()
-            drawn.add(e)
-        ref = mid + ref_layer.moe(normed, cpu_w, shape, 0, shape.n_experts)
-    # every expert exists in the product (a near-tie in the router may pick a neighbour)
+    ref = ref_layer.forward_stack(h_cpu, pos_cpu, [cpu_w], shape, layers, experts="nvfp4", proj="mixed",
+                                  before_moe=bank.route)
+    ref_bf16 = ref_layer.forward_stack(h_cpu, pos_cpu, [cpu_w], shape, layers, before_moe=bank.route)
+
+    # the device quantiser that filled the bank writes what the CPU oracle's quantiser writes
+    e0 = min(bank.drawn)
+    w2 = layer.draw_expert(shape, e0, dev, std=0.02)[1]
+    codes, sf, gs = ops.fused_nvfp4_quant(w2)
+    rc, rsf, rgs = R.nvfp4_quant(w2.cpu())
+    assert torch.equal(codes.cpu(), rc) and torch.equal(gs.cpu(), rgs)
+    assert torch.equal(sf.cpu().view(torch.uint8), rsf.view(torch.uint8))
+
     w["experts"] = layer.make_nvfp4_experts(shape, 0, 1, dev, std=0.02)
     model = layer.RealisticLayer(shape, w, proj="mixed")
     assert model.w_qkv_a.fp8 and model.w_o.fp8 and not model.w_q_b.fp8
     out = model.forward_stack(hidden, positions, layers)
     ops.tc_error_state()
+    assert bool(torch.isfinite(out.float()).all())
     diff = float((out.float().cpu() - ref.float()).abs().max())
     scale = float(ref.float().abs().max())
-    print(f"full-width prefill layer: tokens={tokens} layers={layers} diff={diff:.4f} "
-          f"max|ref|={scale:.4f} rel={diff / scale:.4f}")
-    assert bool(torch.isfinite(out.float()).all())
+    diff16 = float((out.float().cpu() - ref_bf16.float()).abs().max())
+    scale16 = float(ref_bf16.float().abs().max())
+    own16 = float((ref.float() - ref_bf16.float()).abs().max())
+    print(f"full-width prefill layer: tokens={tokens} layers={layers} "
+          f"vs quantised oracle diff={diff:.4f} max|ref|={scale:.4f} rel={diff / scale:.4f}; "
+          f"vs bf16 layer diff={diff16:.4f} rel={diff16 / scale16:.4f} "
+          f"(oracle's own NVFP4/FP8 evaluation vs bf16: {own16 / scale16:.4f})")
     assert diff <= ATOL + RTOL * scale, f"diff {diff} exceeds {ATOL} + {RTOL} * {scale}"
-    # tighter than the runner asks: a quarter of the largest reference element
-    assert diff <= 0.25 * scale, f"diff {diff} vs max|ref| {scale}"
+    assert diff <= 0.12 * scale, f"diff {diff} vs max|ref| {scale}"
+    assert diff16 <= 0.6 * scale16, f"diff {diff16} vs the bf16 layer's max {scale16}"
 
     # the expert stage against the NVFP4 oracle, on identical inputs, for a handful of experts
     normed = ops.fused_rms_norm(hidden, model.ones_h, eps=shape.eps)
@@ -103,10 +116,10 @@ def test_full_width_prefill_layer_meets_the_runner_criterion(tokens, layers):
     x_rt = R.nvfp4_roundtrip(n2.cpu())
     counts = parts["offsets"][1:] - parts["offsets"][:-1]
     busiest = counts.topk(5)[1].tolist()
+    bank.need(busiest)
     for e in busiest:
         lo, hi, rows, _ = _expert_rows(parts, e, shape.topk)
-        w13, w2 = (t.cpu() for t in layer.draw_expert(shape, e, dev, std=0.02))
-        want = _oracle_expert(x_rt, rows, w13, w2, parts["h_amax"], shape.moe_inter)
+        want = _oracle_expert(x_rt, rows, cpu_w["w13"][e], cpu_w["w2"][e], parts["h_amax"], shape.moe_inter)
         got = parts["expert_out"][lo:hi]
         assert rel_err(got, want) <= 3e-2, f"expert {e}: {rel_err(got, want)}"
 
