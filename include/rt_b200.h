@@ -573,6 +573,32 @@ int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const void* kv, co
                          void* stream);
 
 /*
+ * Causal attention of the prefill stack on the tensor cores (flash-style: scores and
+ * probabilities never leave the SM):
+ *   out[t, h, :] = sum_{j <= t} softmax_j(softmax_scale * q[t, h, :] . key[j, h, :]) * v[j, h, :]
+ * where key[j, h] = [k_nope[j, h, :nope_dim] | k_pe[j, (h), :rope_dim]] and q[t, h] =
+ * [q_nope | q_pe] with the same split. All operands bf16, strides in elements (multiples of 8),
+ * so q / k_nope / v may be column slices of wider projection outputs. kp_head_stride == 0 means
+ * one rope key per token shared by all heads (MLA: the k_pe broadcast of the reference's
+ * torch.cat is never materialised); rope_dim == 0 means the key is k_nope alone (k_pe may be
+ * NULL). fp32 scores / softmax / accumulation, probabilities rounded to bf16 before they
+ * multiply v, as the reference's probs.to(v.dtype).
+ * nope_dim <= 128, rope_dim <= 64, v_dim <= 128, each a multiple of 8.
+ * ref: racetrack/runtime/torch_ops.py:97-110 (causal_attention),
+ *      racetrack/realistic_bench.py:304-313 (q / k / v of the synthetic layer),
+ *      racetrack/models/deepseek.py:780-792 (MHA prefill of MLA.forward).
+ */
+int rt_attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, const void* v,
+                           void* out, int64_t tokens, int64_t heads, int64_t nope_dim,
+                           int64_t rope_dim, int64_t v_dim,
+                           int64_t q_token_stride, int64_t q_head_stride,
+                           int64_t kn_token_stride, int64_t kn_head_stride,
+                           int64_t kp_token_stride, int64_t kp_head_stride,
+                           int64_t v_token_stride, int64_t v_head_stride,
+                           int64_t o_token_stride, int64_t o_head_stride,
+                           float softmax_scale, void* stream);
+
+/*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when
  * one of its bounded waits expired. RT_OK when no kernel gave up since the last call,
  * RT_ERR_TIMEOUT otherwise. Call after synchronising the stream; not graph-capturable.

@@ -475,7 +475,7 @@ def nvfp4_roundtrip(x: torch.Tensor, amax: Optional[torch.Tensor] = None) -> tor
 
 
 def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_range=None,
-                      weights_dequantised=False):
+                      weights_dequantised=False, x_amax=None, h_amax=None):
     """MoE.forward's expert loop (ref: racetrack/models/deepseek.py:1011-1022) with NVFP4
     operands: x and swiglu(h) quantised with one tensor-wide global scale each (over the rows
     routed to the experts in `expert_range`), every expert's w13 [2I, H] / w2 [H, I] with its own;
@@ -484,7 +484,9 @@ def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_rang
     reference. With weights_dequantised = (w13_gs, w2_gs) (fp32 [E] global scales), w13 / w2 hold
     code * block_scale of the already quantised weights (exact in bf16) and the products are
     multiplied by the expert's global scale afterwards (a full-width caller quantises 256
-    experts once instead of on every call). Returns bf16 [T, H]."""
+    experts once instead of on every call). x_amax / h_amax override the two tensor-wide
+    maxima (a caller that evaluates a few rows of a larger batch passes the batch's own).
+    Returns bf16 [T, H]."""
     if weights_dequantised:
         gs13, gs2 = weights_dequantised
         mm13 = lambda a, e: (a @ w13[e].float().t()) * gs13[e]
@@ -496,7 +498,7 @@ def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_rang
     n_experts = w13.shape[0]
     inter = w13.shape[1] // 2
     lo, hi = expert_range if expert_range is not None else (0, n_experts)
-    xq = nvfp4_roundtrip(x)                       # global amax over the un-permuted activations
+    xq = nvfp4_roundtrip(x, x_amax)               # global amax over the un-permuted activations
     rows = {}
     for e in range(lo, hi):
         idx, top = torch.where(indices == e)
@@ -506,7 +508,8 @@ def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_rang
         rows[e] = (idx, top, swiglu(gate_up[:, :inter], gate_up[:, inter:]))
     y = torch.zeros(tokens, hidden, dtype=torch.float32)
     if rows:
-        h_amax = torch.stack([h.float().abs().max() for (_, _, h) in rows.values()]).max()
+        if h_amax is None:
+            h_amax = torch.stack([h.float().abs().max() for (_, _, h) in rows.values()]).max()
         # fp32 accumulation in slot order, as the combine kernel does
         outs = torch.zeros(tokens, indices.shape[1], hidden, dtype=torch.float32)
         for e, (idx, top, h) in rows.items():

@@ -58,6 +58,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_index_topk": (_I, [_P, _P, _L, _L, _L, _L, _P]),
     "rt_mla_sparse_decode_splits": (_L, [_L, _L, _L]),
     "rt_mla_sparse_decode": (_I, [_P] * 8 + [_L] * 14 + [_F, _P]),
+    "rt_attn_causal_prefill": (_I, [_P] * 5 + [_L] * 15 + [_F, _P]),
     "rt_gemm_bf16_schedule": (_I, [_I]),
     "rt_gemm_nvfp4_grouped": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
 }

@@ -1,4 +1,6 @@
-// Sparse multi-query attention of the MLA decode step on the 5th-generation tensor cores.
+// Attention kernels on the 5th-generation tensor cores: the sparse multi-query attention of the
+// MLA decode step (first part of this file) and the causal attention of the prefill stack
+// (attn_prefill_kernel, second part).
 //
 //   out[b, h, :] = softmax_j( scale * (q_abs[b, h, :] . kv[b, idx_j, :] + q_pe[b, h, :] . pe[b, idx_j, :]) )
 //                  . kv[b, idx_j, :]                                   j over the selected keys
@@ -471,6 +473,354 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const float* __restrict_
     *reinterpret_cast<uint2*>(out + (static_cast<int64_t>(b) * heads + head) * 512 + threadIdx.x * 4) = v;
 }
 
+
+// ---------------------------------------------------------------------------
+// Causal attention of the prefill stack (racetrack/runtime/torch_ops.py:97-110,
+// racetrack/realistic_bench.py:304-313): out[t, h] = softmax_j<=t(scale q[t, h] . k[j, h]) v[j, h]
+// ---------------------------------------------------------------------------
+// The key of head h is [k_nope[j, h] | k_pe[j]]: the rope part may be one row per token shared by
+// all heads (MLA), so it is a separate operand and is never broadcast in memory.
+//
+// One CTA per (block of 256 query rows, head): two query tiles of 128 rows, processed in
+// ping-pong against key tiles of 128 keys, so that the tensor core works on one tile while the
+// other tile's softmax runs. Per key tile j and query tile t:
+//   S_t = Q_t K_j^T    tcgen05.mma, both operands K-major in shared memory (64-dim chunks of
+//                      [128 rows][128 B], 128-byte swizzle), 128 x 128 fp32 scores in tensor memory;
+//   softmax            one thread per query row (4 warps per tile): tcgen05.ld of the row, causal
+//                      mask on the diagonal tile, running maximum with a lazy rescale (the
+//                      accumulator is rescaled only when the maximum grows by more than 2^8),
+//                      P = exp2(s - m) written back as bf16 INTO THE SCORE COLUMNS (two per column);
+//   O_t += P_t V_j     tcgen05.mma with A = P read from tensor memory and B = V read from shared
+//                      memory MN-major (the value dims contiguous), so P never touches shared memory.
+// Tensor memory (512 columns): S_0 | S_1 | O_0 | O_1, 128 columns each. Shared memory: the two
+// query tiles (96 KB), two stages of key tiles (96 KB), one value tile (32 KB). MMAs issued by
+// one thread execute in order, which is what lets P alias S: S_t(j + 1) is issued after
+// O_t += P_t(j) V_j. Warps: 0 TMA producer, 1 tensor-memory owner and MMA issuer, 2-5 softmax and
+// epilogue of tile 0, 6-9 of tile 1. Every wait is bounded (rt_tc.cuh).
+// CTAs are launched heaviest first (the last query block of a head attends to the most keys)
+// and head-major, so the CTAs in flight share few heads' keys and values in L2.
+constexpr int kFThreads = 320;
+constexpr uint32_t kFChunk = 128 * 128;                    // [128 rows][64 bf16]
+constexpr uint32_t kFQOff = 0;                             // 2 tiles x 3 chunks
+constexpr uint32_t kFKOff = 6 * kFChunk;                   // 2 stages x 3 chunks
+constexpr uint32_t kFVOff = 12 * kFChunk;                  // 2 chunks
+constexpr uint32_t kFBarOff = 14 * kFChunk;
+constexpr int kFBars = 12;     // q_full[2] k_full[2] k_empty[2] v_full v_empty s_full[2] p_full[2] + o_full[2] below
+constexpr uint32_t kFSmemBytes = kFBarOff + (kFBars + 2) * 8 + 16 + 1024;
+static_assert(kFSmemBytes <= 232448, "shared memory budget");
+
+struct PrefillArgs {
+    __nv_bfloat16* out;          // [tokens, heads, v_dim] with strides o_ts / o_hs (elements)
+    int64_t o_ts, o_hs;
+    int tokens, heads;
+    int cn, cp, cv;              // 64-dim chunks of the nope part, the rope part, the values
+    int v_dim;
+    int one_op;                  // bit i set: operand i (q_nope, q_pe, k_nope, k_pe, v) arrives as ONE box
+    int pe_shared;               // k_pe has one row per token for all heads
+    float scale_log2;
+};
+
+__device__ __forceinline__ float ex2_approx(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+__global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
+    const __grid_constant__ CUtensorMap tm_qn, const __grid_constant__ CUtensorMap tm_qp,
+    const __grid_constant__ CUtensorMap tm_kn, const __grid_constant__ CUtensorMap tm_kp,
+    const __grid_constant__ CUtensorMap tm_v, const PrefillArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
+    const uint32_t bars = base + kFBarOff;
+    auto q_full = [&](int t) { return bars + 8u * t; };
+    auto k_full = [&](int st) { return bars + 8u * (2 + st); };
+    auto k_empty = [&](int st) { return bars + 8u * (4 + st); };
+    const uint32_t v_full = bars + 8u * 6, v_empty = bars + 8u * 7;
+    auto s_full = [&](int t) { return bars + 8u * (8 + t); };
+    auto p_full = [&](int t) { return bars + 8u * (10 + t); };
+    auto o_full = [&](int t) { return bars + 8u * (12 + t); };
+    const uint32_t slot = bars + 8u * (kFBars + 2);
+    volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + kFBarOff + 8 * (kFBars + 2));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int qb = static_cast<int>(gridDim.x) - 1 - static_cast<int>(blockIdx.x);   // heaviest first
+    const int h = blockIdx.y;
+    const int q0 = qb * 256;
+    const int n0 = q0 / 128 + 1;                        // key tiles of query tile 0 (the last one is diagonal)
+    const bool has1 = q0 + 128 < a.tokens;
+    const int n1 = has1 ? n0 + 1 : 0;
+    const int n_max = has1 ? n1 : n0;
+    const int nk = a.cn + a.cp;                         // 64-dim chunks of a query / key row
+
+    if (threadIdx.x == 0) {
+        *abort_flag = 0;
+        for (int i = 0; i < 2; ++i) {
+            mbar_init(q_full(i), 1);
+            mbar_init(k_full(i), 1);
+            mbar_init(k_empty(i), 1);
+            mbar_init(s_full(i), 1);
+            mbar_init(p_full(i), 4);                    // lane 0 of the tile's four softmax warps
+            mbar_init(o_full(i), 1);
+        }
+        mbar_init(v_full, 1);
+        mbar_init(v_empty, 1);
+        fence_mbar_init();
+        tma_prefetch_desc(&tm_qn);
+        tma_prefetch_desc(&tm_kn);
+        tma_prefetch_desc(&tm_v);
+    }
+    if (warp == 1) {
+        tmem_alloc(slot, 512);
+        tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *slot_ptr;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            // one operand: `chunks` 64-dim blocks of 128 rows starting at `row`, as one box or one per chunk
+            auto load = [&](const CUtensorMap* m, bool one, int chunks, uint32_t dst, int row, int head,
+                            uint32_t bar) {
+                if (one) {
+                    tma_load_4d(dst, m, 0, row, 0, head, bar);
+                } else {
+                    for (int c = 0; c < chunks; ++c) tma_load_4d(dst + c * kFChunk, m, 64 * c, row, 0, head, bar);
+                }
+            };
+            const int pe_head = a.pe_shared ? 0 : h;
+            for (int t = 0; t < (has1 ? 2 : 1); ++t) {
+                const uint32_t dst = base + kFQOff + t * 3 * kFChunk;
+                mbar_arrive_expect_tx(q_full(t), nk * kFChunk);
+                load(&tm_qn, a.one_op & 1, a.cn, dst, q0 + 128 * t, h, q_full(t));
+                if (a.cp) load(&tm_qp, a.one_op & 2, a.cp, dst + a.cn * kFChunk, q0 + 128 * t, h, q_full(t));
+            }
+            bool ok = true;
+            auto load_k = [&](int j) {
+                const int st = j & 1;
+                if (!(ok = mbar_wait(k_empty(st), ((j >> 1) & 1) ^ 1u, abort_flag, 71))) return;
+                const uint32_t dst = base + kFKOff + st * 3 * kFChunk;
+                mbar_arrive_expect_tx(k_full(st), nk * kFChunk);
+                load(&tm_kn, a.one_op & 4, a.cn, dst, 128 * j, h, k_full(st));
+                if (a.cp) load(&tm_kp, a.one_op & 8, a.cp, dst + a.cn * kFChunk, 128 * j, pe_head, k_full(st));
+            };
+            auto load_v = [&](int j) {
+                if (!(ok = mbar_wait(v_empty, (j & 1) ^ 1u, abort_flag, 72))) return;
+                mbar_arrive_expect_tx(v_full, a.cv * kFChunk);
+                load(&tm_v, a.one_op & 16, a.cv, base + kFVOff, 128 * j, h, v_full);
+            };
+            // in the order the buffers become free: K_0 V_0 K_1, then K_(j+2) V_(j+1)
+            load_k(0);
+            if (ok) load_v(0);
+            if (ok && n_max > 1) load_k(1);
+            for (int j = 0; ok && j < n_max; ++j) {
+                if (j + 2 < n_max) load_k(j + 2);
+                if (ok && j + 1 < n_max) load_v(j + 1);
+            }
+        }
+        __syncwarp();
+    } else if (warp == 1) {
+        if (lane == 0) {
+            // fp32 accumulate, bf16 x bf16, M = 128; S: both K-major, N = 128; O: B MN-major, N = 64 * cv
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (8u << 24);
+            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) |
+                                     (static_cast<uint32_t>(8 * a.cv) << 17) | (8u << 24);
+            auto t_s = [&](int t) { return tmem_base + static_cast<uint32_t>(128 * t); };
+            auto t_o = [&](int t) { return tmem_base + static_cast<uint32_t>(256 + 128 * t); };
+            auto issue_s = [&](int t, int j) {
+                const uint32_t qa = base + kFQOff + t * 3 * kFChunk, kb = base + kFKOff + (j & 1) * 3 * kFChunk;
+                for (int c = 0; c < nk; ++c) {
+                    const uint64_t adesc = smem_desc_sw128(qa + c * kFChunk);
+                    const uint64_t bdesc = smem_desc_sw128(kb + c * kFChunk);
+#pragma unroll
+                    for (int k = 0; k < 4; ++k)
+                        mma_f16(t_s(t), adesc + 2u * k, bdesc + 2u * k, idesc_s, (c | k) != 0 ? 1u : 0u);
+                }
+                mma_commit(s_full(t));
+            };
+            auto issue_pv = [&](int t, int j) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) {
+                    const uint64_t bdesc = smem_desc_sw128_mn(base + kFVOff + k * 2048, kFChunk);
+                    mma_f16_ts(t_o(t), t_s(t) + 8u * k, bdesc, idesc_o, (j | k) != 0 ? 1u : 0u);
+                }
+            };
+            bool ok = mbar_wait(q_full(0), 0, abort_flag, 73) && mbar_wait(k_full(0), 0, abort_flag, 74);
+            if (ok) {
+                tc_fence_after();
+                issue_s(0, 0);
+                if (has1 && (ok = mbar_wait(q_full(1), 0, abort_flag, 73))) {
+                    tc_fence_after();
+                    issue_s(1, 0);
+                }
+                if (ok) mma_commit(k_empty(0));
+            }
+            for (int j = 0; ok && j < n_max; ++j) {
+                const uint32_t vpar = j & 1, kpar = ((j + 1) >> 1) & 1;
+                if (j < n0) {
+                    if (!(ok = mbar_wait(p_full(0), j & 1, abort_flag, 75))) break;
+                    if (!(ok = mbar_wait(v_full, vpar, abort_flag, 76))) break;
+                    tc_fence_after();
+                    issue_pv(0, j);
+                    if (j == n0 - 1) mma_commit(o_full(0));
+                }
+                if (j + 1 < n0) {
+                    if (!(ok = mbar_wait(k_full((j + 1) & 1), kpar, abort_flag, 74))) break;
+                    tc_fence_after();
+                    issue_s(0, j + 1);
+                }
+                if (j < n1) {
+                    if (!(ok = mbar_wait(p_full(1), j & 1, abort_flag, 75))) break;
+                    if (!(ok = mbar_wait(v_full, vpar, abort_flag, 76))) break;
+                    tc_fence_after();
+                    issue_pv(1, j);
+                    if (j == n1 - 1) mma_commit(o_full(1));
+                }
+                mma_commit(v_empty);
+                if (j + 1 < n1) {
+                    if (!(ok = mbar_wait(k_full((j + 1) & 1), kpar, abort_flag, 74))) break;
+                    tc_fence_after();
+                    issue_s(1, j + 1);
+                }
+                if (j + 1 < n_max) mma_commit(k_empty((j + 1) & 1));
+            }
+        }
+        __syncwarp();
+    } else {
+        const int t = (warp - 2) >> 2;                        // query tile of this warp
+        const int quad = warp & 3;                            // the tensor-memory lane quarter it may touch
+        const int row = quad * 32 + lane;                     // query row within the tile
+        const int n_t = t == 0 ? n0 : n1;
+        const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
+        const uint32_t ts = tmem_base + lane_base + static_cast<uint32_t>(128 * t);
+        const uint32_t to = tmem_base + lane_base + static_cast<uint32_t>(256 + 128 * t);
+        const float ninf = __int_as_float(0xff800000);
+        const int o_chunks = a.cv * 2;                        // 32-column chunks of the accumulator
+        float m_ref = ninf, l = 0.f;
+        bool ok = n_t > 0;
+        for (int j = 0; ok && j < n_t; ++j) {
+            if (!(ok = mbar_wait(s_full(t), j & 1, abort_flag, 77))) break;
+            tc_fence_after();
+            const int limit = j == n_t - 1 ? row : 127;        // last visible key column of this row
+            // pass 1: the row maximum
+            float mt = ninf;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(ts + 32u * c, r);
+                tmem_ld_wait(r);
+#pragma unroll
+                for (int i = 0; i < 32; ++i)
+                    if (32 * c + i <= limit) mt = fmaxf(mt, __uint_as_float(r[i]));
+            }
+            mt *= a.scale_log2;
+            const bool grow = mt > m_ref + 8.f;
+            const float m_new = grow ? mt : m_ref;
+            if (j > 0 && __any_sync(0xffffffffu, grow)) {
+                // O_t is at rest: the scores of this tile were committed after O_t += P V of the last one
+                const float alpha = grow ? ex2_approx(m_ref - m_new) : 1.f;
+                l *= alpha;
+#pragma unroll 1
+                for (int c = 0; c < o_chunks; ++c) {
+                    uint32_t o[32];
+                    tmem_ld_32x32(to + 32u * c, o);
+                    tmem_ld_wait(o);
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_32x32(to + 32u * c, o);
+                }
+            }
+            m_ref = m_new;
+            // pass 2: P = exp2(s * scale - m) as bf16 pairs into the first 64 columns of S_t
+            float sum = 0.f;
+#pragma unroll 1
+            for (int c = 0; c < 4; ++c) {
+                uint32_t r[32];
+                tmem_ld_32x32(ts + 32u * c, r);
+                tmem_ld_wait(r);
+                uint32_t pk[16];
+#pragma unroll
+                for (int i = 0; i < 16; ++i) {
+                    float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), a.scale_log2, -m_new));
+                    float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), a.scale_log2, -m_new));
+                    if (32 * c + 2 * i > limit) p0 = 0.f;
+                    if (32 * c + 2 * i + 1 > limit) p1 = 0.f;
+                    sum += p0 + p1;
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
+                    pk[i] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                tmem_st_32x16(ts + 16u * c, pk);
+            }
+            l += sum;
+            tmem_st_wait();
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(t));
+        }
+        if (ok && n_t > 0 && (ok = mbar_wait(o_full(t), 0, abort_flag, 78))) {
+            tc_fence_after();
+            const int token = q0 + 128 * t + row;
+            const float inv = 1.f / l;
+            __nv_bfloat16* orow = a.out + static_cast<int64_t>(token) * a.o_ts + static_cast<int64_t>(h) * a.o_hs;
+#pragma unroll 1
+            for (int c = 0; c < o_chunks; ++c) {
+                uint32_t o[32];
+                tmem_ld_32x32(to + 32u * c, o);
+                tmem_ld_wait(o);
+                if (token < a.tokens) {
+#pragma unroll
+                    for (int v = 0; v < 4; ++v) {
+                        const int d = 32 * c + 8 * v;
+                        if (d < a.v_dim) {                  // v_dim % 8 == 0: a started vector is complete
+                            uint4 w;
+                            w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                            w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                            w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                            w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                            *reinterpret_cast<uint4*>(orow + d) = w;
+                        }
+                    }
+                }
+            }
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        tmem_dealloc(tmem_base, 512);
+    }
+}
+
+int make_tmap_bf16_4d(CUtensorMap* map, const void* ptr, const uint64_t dims[4], const uint64_t strides[3],
+                      const uint32_t box[4]);      // rt_gemm.cu
+
+// Tensor map of one attention operand x[token, head, dim] (element strides ts / hs): when dim is
+// a multiple of 64 its 64-dim chunks are a dimension of their own, so one box brings all of them
+// (an SM retires about one tiled load per 500 cycles whatever its size); otherwise the row is
+// the fastest dimension and one box per chunk is issued, the part beyond dim reading as zero.
+static int make_attn_tmap(CUtensorMap* map, const void* ptr, int64_t dim, int64_t tokens, int64_t heads,
+                          int64_t ts, int64_t hs, bool* one_op) {
+    *one_op = dim % 64 == 0;
+    if (*one_op) {
+        const uint64_t dims[4] = {64, static_cast<uint64_t>(tokens), static_cast<uint64_t>(dim / 64),
+                                  static_cast<uint64_t>(heads)};
+        const uint64_t strides[3] = {static_cast<uint64_t>(ts) * 2, 128, static_cast<uint64_t>(hs) * 2};
+        const uint32_t box[4] = {64, 128, static_cast<uint32_t>(dim / 64), 1};
+        return make_tmap_bf16_4d(map, ptr, dims, strides, box);
+    }
+    const uint64_t dims[4] = {static_cast<uint64_t>(dim), static_cast<uint64_t>(tokens), 1,
+                              static_cast<uint64_t>(heads)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(ts) * 2, static_cast<uint64_t>(ts) * 2,
+                                 static_cast<uint64_t>(hs) * 2};
+    const uint32_t box[4] = {64, 128, 1, 1};
+    return make_tmap_bf16_4d(map, ptr, dims, strides, box);
+}
+
 int attn_error_take() {
     int v = 0;
     if (cudaMemcpyFromSymbol(&v, g_tc_error, sizeof(int)) != cudaSuccess) {
@@ -586,4 +936,74 @@ extern "C" int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const v
                                                  static_cast<int>(heads), static_cast<int>(splits));
     count_launch();
     return check_launch("mla_merge_kernel");
+}
+
+extern "C" int rt_attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, const void* v,
+                                      void* out, int64_t tokens, int64_t heads, int64_t nope_dim,
+                                      int64_t rope_dim, int64_t v_dim, int64_t q_token_stride,
+                                      int64_t q_head_stride, int64_t kn_token_stride,
+                                      int64_t kn_head_stride, int64_t kp_token_stride,
+                                      int64_t kp_head_stride, int64_t v_token_stride,
+                                      int64_t v_head_stride, int64_t o_token_stride,
+                                      int64_t o_head_stride, float softmax_scale, void* stream) {
+    RT_REQUIRE(tokens >= 0 && heads > 0, RT_ERR_BAD_ARG, "rt_attn_causal_prefill: bad shape");
+    if (tokens == 0) return RT_OK;
+    RT_REQUIRE(q && k_nope && v && out && (k_pe || rope_dim == 0), RT_ERR_BAD_ARG,
+               "rt_attn_causal_prefill: null pointer");
+    RT_REQUIRE(nope_dim > 0 && nope_dim <= 128 && rope_dim >= 0 && rope_dim <= 64 && v_dim > 0 && v_dim <= 128 &&
+                   nope_dim % 8 == 0 && rope_dim % 8 == 0 && v_dim % 8 == 0,
+               RT_ERR_UNSUPPORTED,
+               "rt_attn_causal_prefill: dims must be multiples of 8 with nope <= 128, rope <= 64, v <= 128");
+    const int64_t strides[] = {q_token_stride, q_head_stride, kn_token_stride, kn_head_stride, kp_token_stride,
+                               kp_head_stride, v_token_stride, v_head_stride, o_token_stride, o_head_stride};
+    for (int64_t st : strides)
+        RT_REQUIRE(st >= 0 && st % 8 == 0, RT_ERR_BAD_ARG,
+                   "rt_attn_causal_prefill: strides must be non-negative multiples of 8 elements");
+    RT_REQUIRE(aligned16(q) && aligned16(k_nope) && aligned16(v) && aligned16(out) && (!k_pe || aligned16(k_pe)),
+               RT_ERR_BAD_ARG, "rt_attn_causal_prefill: pointers must be 16-byte aligned");
+    RT_REQUIRE(tokens < (1ll << 31) - 256 && heads < 65536, RT_ERR_UNSUPPORTED,
+               "rt_attn_causal_prefill: dimension too large");
+    const bool pe_shared = rope_dim > 0 && kp_head_stride == 0;
+    tc::PrefillArgs a;
+    a.out = static_cast<__nv_bfloat16*>(out);
+    a.o_ts = o_token_stride;
+    a.o_hs = o_head_stride;
+    a.tokens = static_cast<int>(tokens);
+    a.heads = static_cast<int>(heads);
+    a.cn = static_cast<int>((nope_dim + 63) / 64);
+    a.cp = static_cast<int>((rope_dim + 63) / 64);
+    a.cv = static_cast<int>((v_dim + 63) / 64);
+    a.v_dim = static_cast<int>(v_dim);
+    a.pe_shared = pe_shared ? 1 : 0;
+    a.scale_log2 = softmax_scale * 1.4426950408889634f;
+    CUtensorMap tm_qn, tm_qp, tm_kn, tm_kp, tm_v;
+    bool one[5] = {false, false, false, false, false};
+    const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
+    if (int rc = tc::make_attn_tmap(&tm_qn, qb, nope_dim, tokens, heads, q_token_stride, q_head_stride, &one[0]))
+        return rc;
+    if (int rc = tc::make_attn_tmap(&tm_kn, k_nope, nope_dim, tokens, heads, kn_token_stride, kn_head_stride, &one[2]))
+        return rc;
+    if (int rc = tc::make_attn_tmap(&tm_v, v, v_dim, tokens, heads, v_token_stride, v_head_stride, &one[4]))
+        return rc;
+    if (rope_dim > 0) {
+        if (int rc = tc::make_attn_tmap(&tm_qp, qb + nope_dim, rope_dim, tokens, heads, q_token_stride,
+                                        q_head_stride, &one[1]))
+            return rc;
+        // a shared rope key has no head dimension: one "head" whose stride is never used
+        if (int rc = tc::make_attn_tmap(&tm_kp, k_pe, rope_dim, tokens, pe_shared ? 1 : heads, kp_token_stride,
+                                        pe_shared ? kp_token_stride : kp_head_stride, &one[3]))
+            return rc;
+    } else {
+        tm_qp = tm_qn;
+        tm_kp = tm_kn;
+    }
+    a.one_op = (one[0] ? 1 : 0) | (one[1] ? 2 : 0) | (one[2] ? 4 : 0) | (one[3] ? 8 : 0) | (one[4] ? 16 : 0);
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&tc::attn_prefill_kernel),
+                                     static_cast<int>(tc::kFSmemBytes), "rt_attn_causal_prefill"))
+        return rc;
+    dim3 grid(static_cast<unsigned>((tokens + 255) / 256), static_cast<unsigned>(heads));
+    tc::attn_prefill_kernel<<<grid, tc::kFThreads, tc::kFSmemBytes, as_stream(stream)>>>(
+        tm_qn, tm_qp, tm_kn, tm_kp, tm_v, a);
+    count_launch();
+    return check_launch("attn_prefill_kernel");
 }

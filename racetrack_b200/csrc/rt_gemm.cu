@@ -1700,6 +1700,25 @@ int make_tmap_rows128_batched(CUtensorMap* map, const void* ptr, uint64_t rows, 
     return RT_OK;
 }
 
+// 4-D bf16 tensor map with the 128-byte swizzle for the attention kernels (rt_attn.cu): dims and
+// box are given fastest dimension first, strides in bytes for dimensions 1..3.
+int make_tmap_bf16_4d(CUtensorMap* map, const void* ptr, const uint64_t dims_in[4],
+                      const uint64_t strides_in[3], const uint32_t box_in[4]) {
+    EncodeTiledFn fn = encode_fn();
+    RT_REQUIRE(fn, RT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[4] = {dims_in[0], dims_in[1], dims_in[2], dims_in[3]};
+    const cuuint64_t strides[3] = {strides_in[0], strides_in[1], strides_in[2]};
+    const cuuint32_t box[4] = {box_in[0], box_in[1], box_in[2], box_in[3]};
+    const cuuint32_t estr[4] = {1, 1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(ptr), dims,
+                          strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                          CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RT_REQUIRE(r == CUDA_SUCCESS, RT_ERR_CUDA, "cuTensorMapEncodeTiled (4-D) failed with CUresult %d",
+               static_cast<int>(r));
+    return RT_OK;
+}
+
 int sm_count() {
     static int n = 0;
     if (n == 0) {

@@ -160,7 +160,8 @@ def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
         if local else None
     # dispatch: every token row is quantised once, then its codes and scales are copied into
     # expert order (the bf16 rows are not read topk times)
-    x_codes, x_sf, a_gs = ops.fused_nvfp4_quant(x, amax=ops.tensor_absmax(x))
+    x_amax = ops.tensor_absmax(x)
+    x_codes, x_sf, a_gs = ops.fused_nvfp4_quant(x, amax=x_amax)
     a_codes, a_sf = moe_gather_nvfp4(x_codes, x_sf.view(torch.uint8), sorted_pairs, topk, tile_map,
                                      tile_count, pairs)
     gate_up = ops.gemm_nvfp4_grouped(a_codes, a_sf, a_gs, experts.w13_codes, experts.w13_sf,
@@ -173,7 +174,7 @@ def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
     expert_out = ops.gemm_nvfp4_grouped(h_codes, h_sf, h_gs, experts.w2_codes, experts.w2_sf,
                                         experts.w2_gs, tile_map, tile_count, n=hidden, groups=count)
     if parts is not None:
-        parts.update(offsets=offsets, sorted_pairs=sorted_pairs, pair_pos=pair_pos, x_gs=a_gs,
+        parts.update(offsets=offsets, sorted_pairs=sorted_pairs, pair_pos=pair_pos, x_gs=a_gs, x_amax=x_amax,
                      gate_up=gate_up, h=h, h_amax=h_amax, expert_out=expert_out)
     return ops.fused_moe_combine(expert_out, pair_pos, weights, shared, pos_window=window,
                                  out_dtype=out_dtype)

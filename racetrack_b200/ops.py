@@ -812,6 +812,59 @@ def mla_sparse_decode(q_abs: torch.Tensor, q_pe: torch.Tensor, kv_cache: torch.T
     return out
 
 
+def attention_prefill(q: torch.Tensor, k_nope: torch.Tensor, k_pe: Optional[torch.Tensor],
+                      v: torch.Tensor, softmax_scale: Optional[float] = None) -> torch.Tensor:
+    """Causal attention over [tokens, heads, dim] tensors on the tensor cores
+    (racetrack/runtime/torch_ops.py:97-110; the attention core of
+    racetrack/realistic_bench.py:304-313): q bf16 [T, H, nope + rope]; the key of head h is
+    [k_nope[:, h] | k_pe] with k_nope [T, H, nope] and k_pe [T, rope] (one rope key per token for
+    all heads, never broadcast in memory) or [T, H, rope], or None; v [T, H, v_dim]. Operands may
+    be strided views (column slices of projection outputs). Returns bf16 [T, H, v_dim]."""
+    _require_cuda(q, k_nope, v)
+    tokens, heads, qk = q.shape
+    nope = k_nope.shape[-1]
+    rope = qk - nope
+    v_dim = v.shape[-1]
+    ok = k_nope.shape == (tokens, heads, nope) and v.shape == (tokens, heads, v_dim) and rope >= 0
+    if rope:
+        ok = ok and k_pe is not None and k_pe.shape in ((tokens, rope), (tokens, heads, rope))
+    if not ok:
+        raise RuntimeError("attention_prefill: expected q [T,H,nope+rope], k_nope [T,H,nope], "
+                           "k_pe [T,rope] or [T,H,rope], v [T,H,v]")
+
+    def view(t, name):
+        if t.dtype != torch.bfloat16:
+            raise RuntimeError(f"attention_prefill: {name} must be bfloat16")
+        if t.stride(-1) != 1 or any(st % 8 for st in t.stride()[:-1]) or t.data_ptr() % 16:
+            t = t.contiguous()
+        return t
+    q, k_nope, v = view(q, "q"), view(k_nope, "k_nope"), view(v, "v")
+    kp_ts = kp_hs = 0
+    if rope:
+        k_pe = view(k_pe, "k_pe")
+        kp_ts = k_pe.stride(0)
+        kp_hs = k_pe.stride(1) if k_pe.dim() == 3 else 0
+        if k_pe.dim() == 3 and kp_hs == 0:         # an expanded view: the shared form
+            k_pe = k_pe[:, 0]
+    if softmax_scale is None:
+        softmax_scale = qk ** -0.5
+    out = torch.empty(tokens, heads, v_dim, dtype=torch.bfloat16, device=q.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_attn_causal_prefill(
+        q.data_ptr(), k_nope.data_ptr(), k_pe.data_ptr() if rope else None, v.data_ptr(),
+        out.data_ptr(), tokens, heads, nope, rope, v_dim, q.stride(0), q.stride(1),
+        k_nope.stride(0), k_nope.stride(1), kp_ts, kp_hs, v.stride(0), v.stride(1),
+        out.stride(0), out.stride(1), float(softmax_scale), _stream()), "rt_attn_causal_prefill")
+    return out
+
+
+def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
+    """racetrack/runtime/torch_ops.py:97-110 with whole keys k [T, H, qk] (qk <= 192): the first
+    min(qk, 128) dims take the place of the nope part, the rest that of a per-head rope part."""
+    nope = min(k.shape[-1], 128)
+    return attention_prefill(q, k[..., :nope], k[..., nope:] if k.shape[-1] > nope else None, v)
+
+
 def gemm_bf16_schedule(schedule: int) -> int:
     """Selects the schedule of the bf16 GEMM for this process (0 default = by size, 1 single-CTA
     128 x 256 tiles, 2 CTA pairs with 256 x 256 tiles where K % 64 == 0) and returns the
