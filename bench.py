@@ -224,6 +224,7 @@ class PrefillStackWorkload:
         from racetrack_b200 import layer, moe, ops
         self.layer_mod, self.moe, self.ops = layer, moe, ops
         self.device, self.rank, self.world = device, rank, world
+        layer.ATTENTION_CORE = args.attn_core
         self.tokens, self.layers = args.tokens, args.layers
         if self.default_tokens != 8192 and args.tokens == 8192:
             self.tokens = self.default_tokens         # --tokens was not given
@@ -375,7 +376,8 @@ class PrefillStackWorkload:
                 "hidden": s.hidden, "heads": s.heads, "experts": s.n_experts, "topk": s.topk,
                 "moe_inter": s.moe_inter, "ffn": self.ffn, "experts_dtype": "nvfp4", "experts_gemm_schedule": self.schedule,
                 "projections_dtype": self.proj,
-                "attention_core": "torch sdpa (not a kernel of this backend)",
+                "attention_core": "rt_attn_causal_prefill (tcgen05, this backend)"
+                if self.layer_mod.ATTENTION_CORE == "rt" else "torch sdpa (yardstick: not a kernel of this backend)",
                 "routing": "topk_softmax (racetrack/realistic_bench.py:321-327)",
                 "l2_policy": "inputs_exceed_l2 (6.3 GB of expert weights + 117 MB of hidden "
                              "states stream through the 126 MB L2 every layer)"}
@@ -1104,6 +1106,9 @@ def main() -> None:
     ap.add_argument("--ffn", default="moe", choices=("moe", "dense"),
                     help="FFN of the layer: 256 routed NVFP4 experts, or the dense SwiGLU FFN of "
                          "width 18432 that the first three layers of the model use")
+    ap.add_argument("--attn-core", default="rt", choices=("rt", "sdpa"),
+                    help="attention core of the prefill layer: this backend's causal attention "
+                         "kernel, or torch's SDPA as the yardstick it is measured against")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true",
                     help="skip the validation of the timed configuration against the CPU oracle")

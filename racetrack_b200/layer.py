@@ -7,14 +7,14 @@ all-reduce after w_o); routed experts expert-parallel (each rank owns a contiguo
 replicated, all-reduce after the combine); router replicated. Per layer:
 
     rms_norm -> qkv_a GEMM -> fused q_a/kv_a RMSNorm + k_pe RoPE -> q_b GEMM -> q_pe RoPE (in place)
-    -> kv_b GEMM -> causal attention over the local heads -> w_o GEMM -> all-reduce
+    -> kv_b GEMM -> causal attention over the local heads (tcgen05) -> w_o GEMM -> all-reduce
     -> fused residual-add + rms_norm -> router GEMM (fp32) -> routing kernel -> NVFP4 grouped
     expert GEMMs with SwiGLU -> weighted combine -> all-reduce -> residual add (fused with the
     next layer's first rms_norm)
 
 Dense projections run on the bf16 tcgen05 GEMM, experts on the NVFP4 block-scaled grouped GEMM,
-everything element-wise on the fused kernels of ops.py. The attention core (QK^T, softmax, PV) is
-torch's scaled_dot_product_attention: it is not one of this backend's kernels.
+everything element-wise on the fused kernels of ops.py, the attention core (QK^T, softmax, PV) on
+the causal attention kernel of this library (ops.attention_prefill).
 
 Unlike the reference, which seeds each rank's weights with seed + rank (so a 2-rank model is a
 different model from a 1-rank one), weights here are defined per shard unit (one eighth of the
@@ -132,10 +132,17 @@ def make_nvfp4_experts(shape: LayerShape, rank: int, world: int, device, *,
         cat([p[2] for p in parts2]))
 
 
+# "rt": the causal attention kernel of this library (ops.attention_prefill, tcgen05);
+# "sdpa": torch's scaled_dot_product_attention, kept only as the yardstick the kernel is
+# measured against (a library kernel, not part of the backend).
+ATTENTION_CORE = "rt"
+
+
 def attention_core(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch.Tensor:
     """Causal softmax(q k^T / sqrt(d)) v over [T, H, D] tensors -> [T, H, Dv]
-    (racetrack/runtime/torch_ops.py:97-110). torch SDPA; when the value width differs from the
-    query width and the fused kernels refuse that, v is zero-padded to the query width."""
+    (racetrack/runtime/torch_ops.py:97-110) through torch SDPA (the yardstick, see
+    ATTENTION_CORE); when the value width differs from the query width and the fused kernels
+    refuse that, v is zero-padded to the query width."""
     qt, kt, vt = (t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
     try:
         out = F.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
@@ -182,14 +189,20 @@ class RealisticLayer:
         dev = weights["w_qkv_a"].device
         self.w_qkv_a = Projection(weights["w_qkv_a"], proj)
         self.w_q_b = Projection(weights["w_q_b"], proj)
-        # kv_b rows regrouped per head as [k_nope | rope-wide gap (zero rows) | v]: the GEMM then
-        # leaves room for k_pe right behind k_nope and K / V are strided views of its output
         s = shape
-        wkv = weights["w_kv_b"].view(self.local_heads, s.nope + s.v_dim, s.kv_lora)
-        gap = torch.zeros(self.local_heads, s.rope, s.kv_lora, device=dev, dtype=wkv.dtype)
-        self.w_kv_b = Projection(
-            torch.cat((wkv[:, :s.nope], gap, wkv[:, s.nope:]), dim=1)
-            .reshape(self.local_heads * (s.nope + s.rope + s.v_dim), s.kv_lora), proj)
+        self.attn_core = ATTENTION_CORE
+        if self.attn_core == "rt":
+            # K and V are column slices of the kv_b output; the attention kernel takes the
+            # rope key as an operand of its own, one row per token for all heads
+            self.w_kv_b = Projection(weights["w_kv_b"], proj)
+        else:
+            # kv_b rows regrouped per head as [k_nope | rope-wide gap (zero rows) | v]: the GEMM
+            # then leaves room for k_pe right behind k_nope (a whole-key tensor for SDPA)
+            wkv = weights["w_kv_b"].view(self.local_heads, s.nope + s.v_dim, s.kv_lora)
+            gap = torch.zeros(self.local_heads, s.rope, s.kv_lora, device=dev, dtype=wkv.dtype)
+            self.w_kv_b = Projection(
+                torch.cat((wkv[:, :s.nope], gap, wkv[:, s.nope:]), dim=1)
+                .reshape(self.local_heads * (s.nope + s.rope + s.v_dim), s.kv_lora), proj)
         self.w_o = Projection(weights["w_o"], proj)
         self.w_gate = weights["w_gate"].contiguous()
         self.ones_h = torch.ones(shape.hidden, device=dev, dtype=torch.bfloat16)
@@ -222,9 +235,13 @@ class RealisticLayer:
             qkv[:, s.q_lora + s.kv_lora:], positions, eps=s.eps, rope_base=s.rope_base)
         q = self.w_q_b(q_c).view(tokens, h, s.qk_dim)
         ops.fused_rope_half(q[..., s.nope:], positions, rope_base=s.rope_base, inplace=True)
-        kv = self.w_kv_b(kv_c).view(tokens, h, s.qk_dim + s.v_dim)
-        ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
-        local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
+        if self.attn_core == "rt":
+            kv = self.w_kv_b(kv_c).view(tokens, h, s.nope + s.v_dim)
+            local = ops.attention_prefill(q, kv[..., :s.nope], k_pe, kv[..., s.nope:])
+        else:
+            kv = self.w_kv_b(kv_c).view(tokens, h, s.qk_dim + s.v_dim)
+            ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
+            local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
         out = self.w_o(local.reshape(tokens, h * s.v_dim))
         return self._all_reduce(out)
 
