@@ -166,6 +166,19 @@ def layer_check(model, shape, sample, positions, n_layers, *, proj, ffn="moe", r
         out_ffn = model.ffn_forward(normed2)
         taps.append((normed, attn, normed2, out_ffn))
         normed, hidden = ops.fused_residual_norm(out_ffn, hidden, model.ones_h, eps=s.eps)
+    # on several ranks the timed forward runs the token-sharded schedule (reduce-scatter, token-wise
+    # kernels on the rank's rows, all-gather of their compact outputs); the stages above ran the
+    # replicated one (all-reduce): same sums, so ONE layer of each must agree closely
+    sharded_vs_replicated = None
+    if getattr(model, "world", 1) > 1:
+        one = model.forward_stack(sample, positions, 1)
+        n_a, h_a = taps[0][2], None
+        _, h_mid = ops.fused_residual_norm(taps[0][1], sample, model.ones_h, eps=s.eps)
+        _, h_a = ops.fused_residual_norm(taps[0][3], h_mid, model.ones_h, eps=s.eps)
+        d = float((one.float() - h_a.float()).abs().max())
+        sc = float(h_a.float().abs().max())
+        sharded_vs_replicated = {"layers": 1, "diff": round(d, 5), "rel": round(d / max(sc, 1e-30), 5),
+                                 "ok": bool(d <= CHECK_ATOL + CHECK_RTOL * sc)}
     ops.tc_error_state()
     if rank != 0:
         return None
@@ -204,6 +217,11 @@ def layer_check(model, shape, sample, positions, n_layers, *, proj, ffn="moe", r
     e2e = {"vs_same_arithmetic_oracle": dist(hidden, ref), "vs_unquantised_bf16": dist(hidden, ref16)}
     e2e["vs_unquantised_bf16"]["oracle_own_rel"] = round(
         float((ref.float() - ref16.float()).abs().max()) / max(float(ref16.float().abs().max()), 1e-30), 5)
+    if sharded_vs_replicated is not None:
+        e2e["token_sharded_vs_replicated_schedule"] = sharded_vs_replicated
+        stages.append({"layer": 0, "stage": "token-sharded schedule vs replicated schedule",
+                       **{k: sharded_vs_replicated[k] for k in ("diff", "rel", "ok")},
+                       "max_abs_ref": None})
     return {"ok": all(st["ok"] for st in stages), "tokens": int(sample.shape[0]), "layers": n_layers,
             "criterion": f"diff <= {CHECK_ATOL} + {CHECK_RTOL} * max|ref|",
             "mode": "every layer's attention half and feed-forward half against the CPU restatement of "

@@ -1,0 +1,75 @@
+"""Collectives of the sharded layer: thin wrappers over torch.distributed.
+
+One process per GPU, NCCL over NVLink. The layer exchanges activations in three ways only
+(the counterpart of the two all-reduces of racetrack/realistic_bench.py:315-316,351):
+
+  reduce_scatter_rows   partial sums [T, H] of every rank -> this rank's T / world rows of
+                        their sum (the first half of an all-reduce; the token-wise kernels that
+                        follow run on those rows only)
+  all_gather_rows       this rank's rows -> all rows, in rank order (the second half, moved
+                        behind the token-wise kernels and carrying their SMALLER outputs:
+                        the [T, 2112] latent projection or NVFP4 codes instead of bf16 hidden
+                        states)
+  all_reduce_max        a one-element maximum (the tensor-wide amax of the NVFP4 global scale)
+
+The gloo backend has no reduce-scatter; there (CPU tests of the host logic) it is an all-reduce
+followed by taking the rank's rows, which is the same result.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+
+class Group:
+    """A process group with the rank / world size the layer was built for. world == 1 makes
+    every collective the identity, so single-GPU code paths need no branches."""
+
+    def __init__(self, rank: int = 0, world: int = 1, group: Optional["dist.ProcessGroup"] = None):
+        self.rank, self.world, self.group = rank, world, group
+        if world > 1 and not (dist.is_available() and dist.is_initialized()):
+            raise RuntimeError("a sharded layer needs an initialised torch.distributed process group")
+        self._no_reduce_scatter = world > 1 and dist.get_backend(group) == "gloo"
+
+    def rows_of(self, total_rows: int) -> tuple[int, int]:
+        """[begin, end) of this rank's rows of a [total_rows, ...] tensor."""
+        if total_rows % self.world:
+            raise RuntimeError(f"{total_rows} rows do not divide over {self.world} ranks")
+        per = total_rows // self.world
+        return self.rank * per, (self.rank + 1) * per
+
+    def reduce_scatter_rows(self, partial: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return partial
+        lo, hi = self.rows_of(partial.shape[0])
+        partial = partial.contiguous()
+        if self._no_reduce_scatter:
+            dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
+            return partial[lo:hi].clone()
+        out = torch.empty((hi - lo, *partial.shape[1:]), dtype=partial.dtype, device=partial.device)
+        dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM, group=self.group)
+        return out
+
+    def all_gather_rows(self, rows: torch.Tensor) -> torch.Tensor:
+        if self.world == 1:
+            return rows
+        rows = rows.contiguous()
+        out = torch.empty((rows.shape[0] * self.world, *rows.shape[1:]), dtype=rows.dtype,
+                          device=rows.device)
+        if rows.dtype == torch.float8_e4m3fn:       # collectives move bytes
+            dist.all_gather_into_tensor(out.view(torch.uint8), rows.view(torch.uint8), group=self.group)
+        else:
+            dist.all_gather_into_tensor(out, rows, group=self.group)
+        return out
+
+    def all_reduce_max(self, value: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(value, op=dist.ReduceOp.MAX, group=self.group)
+        return value
+
+    def all_reduce_sum(self, value: torch.Tensor) -> torch.Tensor:
+        if self.world > 1:
+            dist.all_reduce(value, op=dist.ReduceOp.SUM, group=self.group)
+        return value

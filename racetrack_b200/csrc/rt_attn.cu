@@ -486,28 +486,46 @@ __global__ void __launch_bounds__(128) mla_merge_kernel(const float* __restrict_
 // other tile's softmax runs. Per key tile j and query tile t:
 //   S_t = Q_t K_j^T    tcgen05.mma, both operands K-major in shared memory (64-dim chunks of
 //                      [128 rows][128 B], 128-byte swizzle), 128 x 128 fp32 scores in tensor memory;
-//   softmax            one thread per query row (4 warps per tile): tcgen05.ld of the row, causal
-//                      mask on the diagonal tile, running maximum with a lazy rescale (the
-//                      accumulator is rescaled only when the maximum grows by more than 2^8),
-//                      P = exp2(s - m) written back as bf16 INTO THE SCORE COLUMNS (two per column);
+//   softmax            two threads per query row (8 warps per tile: the special-function unit
+//                      evaluates 16 exponentials per clock and SM, so a tile's 16384 take 1024
+//                      clocks whoever issues them; two warps per scheduler keep it busy), each
+//                      with 64 of the row's scores in registers after one tcgen05.ld pass: causal
+//                      mask on the diagonal tile, the two half-row maxima exchanged through shared
+//                      memory (as bf16, so both threads use the same value), running maximum with a
+//                      lazy rescale (the accumulator is rescaled only when the maximum grows by
+//                      more than 2^8), P = exp2(s - m) written back as bf16 INTO THE SCORE COLUMNS
+//                      (two per column);
 //   O_t += P_t V_j     tcgen05.mma with A = P read from tensor memory and B = V read from shared
 //                      memory MN-major (the value dims contiguous), so P never touches shared memory.
 // Tensor memory (512 columns): S_0 | S_1 | O_0 | O_1, 128 columns each. Shared memory: the two
 // query tiles (96 KB), two stages of key tiles (96 KB), one value tile (32 KB). MMAs issued by
 // one thread execute in order, which is what lets P alias S: S_t(j + 1) is issued after
-// O_t += P_t(j) V_j. Warps: 0 TMA producer, 1 tensor-memory owner and MMA issuer, 2-5 softmax and
-// epilogue of tile 0, 6-9 of tile 1. Every wait is bounded (rt_tc.cuh).
+// O_t += P_t(j) V_j. Warps: 0 TMA producer, 1 tensor-memory owner and MMA issuer, 2-9 softmax and
+// epilogue of tile 0, 10-17 of tile 1 (within a tile the first four warps take key columns
+// 0-63, the other four 64-127; a warp touches the tensor-memory lanes of quarter warp % 4).
+// Every wait is bounded (rt_tc.cuh).
 // CTAs are launched heaviest first (the last query block of a head attends to the most keys)
 // and head-major, so the CTAs in flight share few heads' keys and values in L2.
-constexpr int kFThreads = 320;
+constexpr int kFThreads = 576;                             // 2 + 2 tiles x 8 softmax warps
 constexpr uint32_t kFChunk = 128 * 128;                    // [128 rows][64 bf16]
 constexpr uint32_t kFQOff = 0;                             // 2 tiles x 3 chunks
 constexpr uint32_t kFKOff = 6 * kFChunk;                   // 2 stages x 3 chunks
 constexpr uint32_t kFVOff = 12 * kFChunk;                  // 2 chunks
 constexpr uint32_t kFBarOff = 14 * kFChunk;
 constexpr int kFBars = 12;     // q_full[2] k_full[2] k_empty[2] v_full v_empty s_full[2] p_full[2] + o_full[2] below
-constexpr uint32_t kFSmemBytes = kFBarOff + (kFBars + 2) * 8 + 16 + 1024;
+constexpr uint32_t kFXmOff = kFBarOff + (kFBars + 2) * 8 + 16;        // row maxima exchanged as bf16 [2][128][2]
+constexpr uint32_t kFSmemBytes = kFXmOff + 2 * 128 * 2 * 2 + 1024;
 static_assert(kFSmemBytes <= 232448, "shared memory budget");
+
+// Optional pipeline trace (never compiled into the library): with -DRT_FA_TRACE the CTA of the
+// heaviest query block of head 0 stamps clock64() at ten points of its first 64 key tiles.
+#ifdef RT_FA_TRACE
+__device__ long long g_fa_trace[10 * 64];
+#define RT_FTRACE(ev, it) \
+    do { if ((blockIdx.x | blockIdx.y) == 0 && (it) < 64) g_fa_trace[(ev) * 64 + (it)] = clock64(); } while (0)
+#else
+#define RT_FTRACE(ev, it) do { } while (0)
+#endif
 
 struct PrefillArgs {
     __nv_bfloat16* out;          // [tokens, heads, v_dim] with strides o_ts / o_hs (elements)
@@ -524,6 +542,53 @@ __device__ __forceinline__ float ex2_approx(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+
+// 2^x for x <= 8 on the FMA pipe (the special-function unit evaluates only 4 exponentials per
+// clock and scheduler, which would bound the softmax): x = n + f with n = round(x), |f| <= 1/2,
+// 2^f by a degree-4 polynomial (relative error 4e-6, far below the bf16 rounding of P), 2^n by
+// adding n to the exponent field. Inputs below -125 give 0 like ex2.approx.ftz.
+__device__ __forceinline__ float ex2_poly(float x) {
+    x = fmaxf(x, -125.f);
+    const float t = x + 12582912.f;                       // 1.5 * 2^23: the integer part lands in the low bits
+    const float f = x - (t - 12582912.f);
+    float p = fmaf(f, 9.6181291e-3f, 5.5504109e-2f);
+    p = fmaf(p, f, 2.4022651e-1f);
+    p = fmaf(p, f, 6.9314718e-1f);
+    p = fmaf(p, f, 1.0f);
+    return __uint_as_float(__float_as_uint(p) + (__float_as_uint(t) << 23));
+}
+
+// 32 scores of one row -> 32 probabilities as 16 bf16 pairs, and their fp32 sum. One pair in
+// kFPolyEvery takes the polynomial route, the rest the special-function unit.
+#ifndef RT_FA_POLY_EVERY
+#define RT_FA_POLY_EVERY 0
+#endif
+constexpr int kFPolyEvery = RT_FA_POLY_EVERY;
+__device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale,
+                                              float m, float& sum) {
+    float acc0 = 0.f, acc1 = 0.f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+        const float x0 = fmaf(__uint_as_float(r[2 * i]), scale, -m);
+        const float x1 = fmaf(__uint_as_float(r[2 * i + 1]), scale, -m);
+        float p0, p1;
+        if (kFPolyEvery > 0 && (i % (kFPolyEvery > 0 ? kFPolyEvery : 1)) == kFPolyEvery - 1) {
+            p0 = ex2_poly(x0);
+            p1 = ex2_poly(x1);
+        } else {
+            p0 = ex2_approx(x0);
+            p1 = ex2_approx(x1);
+        }
+#if defined(RT_FA_DIAG) && RT_FA_DIAG == 2      // diagnostic build only: no exponentials
+        p0 = x0;
+        p1 = x1;
+#endif
+        acc0 += p0;
+        acc1 += p1;
+        pk[i] = pack_bf16x2(p0, p1);
+    }
+    sum += acc0 + acc1;
 }
 
 __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
@@ -562,7 +627,7 @@ __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
             mbar_init(k_full(i), 1);
             mbar_init(k_empty(i), 1);
             mbar_init(s_full(i), 1);
-            mbar_init(p_full(i), 4);                    // lane 0 of the tile's four softmax warps
+            mbar_init(p_full(i), 8);                    // lane 0 of the tile's eight softmax warps
             mbar_init(o_full(i), 1);
         }
         mbar_init(v_full, 1);
@@ -662,8 +727,11 @@ __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
             for (int j = 0; ok && j < n_max; ++j) {
                 const uint32_t vpar = j & 1, kpar = ((j + 1) >> 1) & 1;
                 if (j < n0) {
+                    RT_FTRACE(0, j);
                     if (!(ok = mbar_wait(p_full(0), j & 1, abort_flag, 75))) break;
+                    RT_FTRACE(1, j);
                     if (!(ok = mbar_wait(v_full, vpar, abort_flag, 76))) break;
+                    RT_FTRACE(2, j);
                     tc_fence_after();
                     issue_pv(0, j);
                     if (j == n0 - 1) mma_commit(o_full(0));
@@ -674,7 +742,9 @@ __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
                     issue_s(0, j + 1);
                 }
                 if (j < n1) {
+                    RT_FTRACE(3, j);
                     if (!(ok = mbar_wait(p_full(1), j & 1, abort_flag, 75))) break;
+                    RT_FTRACE(4, j);
                     if (!(ok = mbar_wait(v_full, vpar, abort_flag, 76))) break;
                     tc_fence_after();
                     issue_pv(1, j);
@@ -685,39 +755,64 @@ __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
                     if (!(ok = mbar_wait(k_full((j + 1) & 1), kpar, abort_flag, 74))) break;
                     tc_fence_after();
                     issue_s(1, j + 1);
+                    RT_FTRACE(5, j);
                 }
                 if (j + 1 < n_max) mma_commit(k_empty((j + 1) & 1));
             }
         }
         __syncwarp();
     } else {
-        const int t = (warp - 2) >> 2;                        // query tile of this warp
+        const int t = (warp - 2) >> 3;                        // query tile of this warp
+        const int hh = ((warp - 2) >> 2) & 1;                 // which 64 key columns of the tile
         const int quad = warp & 3;                            // the tensor-memory lane quarter it may touch
         const int row = quad * 32 + lane;                     // query row within the tile
         const int n_t = t == 0 ? n0 : n1;
+        const int pair_bar = 1 + 4 * t + quad;                // named barrier of the two warps of these rows
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
         const uint32_t ts = tmem_base + lane_base + static_cast<uint32_t>(128 * t);
         const uint32_t to = tmem_base + lane_base + static_cast<uint32_t>(256 + 128 * t);
         const float ninf = __int_as_float(0xff800000);
-        const int o_chunks = a.cv * 2;                        // 32-column chunks of the accumulator
+        const int o_half = a.cv;                              // 32-column accumulator chunks per thread
+        __nv_bfloat16* xm = reinterpret_cast<__nv_bfloat16*>(base_ptr + kFXmOff) + (t * 128 + row) * 2;
         float m_ref = ninf, l = 0.f;
         bool ok = n_t > 0;
         for (int j = 0; ok && j < n_t; ++j) {
             if (!(ok = mbar_wait(s_full(t), j & 1, abort_flag, 77))) break;
+            if (threadIdx.x == 64) RT_FTRACE(6, j);
             tc_fence_after();
-            const int limit = j == n_t - 1 ? row : 127;        // last visible key column of this row
-            // pass 1: the row maximum
-            float mt = ninf;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(ts + 32u * c, r);
-                tmem_ld_wait(r);
+#if defined(RT_FA_DIAG) && RT_FA_DIAG == 1      // diagnostic build only: the pipeline without any softmax
+            __syncwarp();
+            if (lane == 0) mbar_arrive(p_full(t));
+            continue;
+#endif
+            // this thread's 64 scores in registers: one pass over tensor memory
+            uint32_t r0[32], r1[32];
+            tmem_ld_32x32(ts + 64u * hh, r0);
+            tmem_ld_32x32(ts + 64u * hh + 32u, r1);
+            tmem_ld_wait(r0);
+            tmem_ld_wait(r1);
+            if (threadIdx.x == 64) RT_FTRACE(7, j);
+            if (j == n_t - 1) {                               // diagonal tile: keys beyond the row's own are masked
+                const int c0 = 64 * hh;
 #pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (32 * c + i <= limit) mt = fmaxf(mt, __uint_as_float(r[i]));
+                for (int i = 0; i < 32; ++i) {
+                    if (c0 + i > row) r0[i] = 0xff800000u;
+                    if (c0 + 32 + i > row) r1[i] = 0xff800000u;
+                }
             }
-            mt *= a.scale_log2;
+            float mx0 = ninf, mx1 = ninf, mx2 = ninf, mx3 = ninf;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) {
+                mx0 = fmaxf(mx0, __uint_as_float(r0[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(r0[16 + i]));
+                mx2 = fmaxf(mx2, __uint_as_float(r1[i]));
+                mx3 = fmaxf(mx3, __uint_as_float(r1[16 + i]));
+            }
+            // both threads of a row round both half maxima to bf16, so they agree on the maximum
+            const __nv_bfloat16 mine = __float2bfloat16_rn(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2);
+            xm[hh] = mine;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            const float mt = fmaxf(__bfloat162float(mine), __bfloat162float(xm[hh ^ 1]));
             const bool grow = mt > m_ref + 8.f;
             const float m_new = grow ? mt : m_ref;
             if (j > 0 && __any_sync(0xffffffffu, grow)) {
@@ -725,49 +820,45 @@ __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
                 const float alpha = grow ? ex2_approx(m_ref - m_new) : 1.f;
                 l *= alpha;
 #pragma unroll 1
-                for (int c = 0; c < o_chunks; ++c) {
-                    uint32_t o[32];
-                    tmem_ld_32x32(to + 32u * c, o);
+                for (int c = 4 * o_half * hh; c < 4 * o_half * (hh + 1); ++c) {      // 8 columns at a time
+                    uint32_t o[8];
+                    tmem_ld_32x8(to + 8u * c, o);
                     tmem_ld_wait(o);
 #pragma unroll
-                    for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st_32x32(to + 32u * c, o);
+                    for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                    tmem_st_32x8(to + 8u * c, o);
                 }
             }
             m_ref = m_new;
-            // pass 2: P = exp2(s * scale - m) as bf16 pairs into the first 64 columns of S_t
-            float sum = 0.f;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t r[32];
-                tmem_ld_32x32(ts + 32u * c, r);
-                tmem_ld_wait(r);
-                uint32_t pk[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) {
-                    float p0 = ex2_approx(fmaf(__uint_as_float(r[2 * i]), a.scale_log2, -m_new));
-                    float p1 = ex2_approx(fmaf(__uint_as_float(r[2 * i + 1]), a.scale_log2, -m_new));
-                    if (32 * c + 2 * i > limit) p0 = 0.f;
-                    if (32 * c + 2 * i + 1 > limit) p1 = 0.f;
-                    sum += p0 + p1;
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(p0, p1);
-                    pk[i] = *reinterpret_cast<uint32_t*>(&b2);
-                }
-                tmem_st_32x16(ts + 16u * c, pk);
-            }
-            l += sum;
+            // P = exp2(s * scale - m) as bf16 pairs into columns [32 hh, 32 hh + 32) of S_t
+            float s0 = 0.f, s1 = 0.f;
+            uint32_t pk[16];
+            softmax_chunk(r0, pk, a.scale_log2, m_new, s0);
+            tmem_st_32x16(ts + 32u * hh, pk);
+            softmax_chunk(r1, pk, a.scale_log2, m_new, s1);
+            tmem_st_32x16(ts + 32u * hh + 16u, pk);
+            l += s0 + s1;
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
+            // (the partner reads this step's maximum before it arrives here, and the next scores
+            // only exist once both warps have arrived: the slot is free to overwrite by then)
             if (lane == 0) mbar_arrive(p_full(t));
+            if (threadIdx.x == 64) RT_FTRACE(8, j);
+            if (threadIdx.x == 320) RT_FTRACE(9, j);
         }
         if (ok && n_t > 0 && (ok = mbar_wait(o_full(t), 0, abort_flag, 78))) {
             tc_fence_after();
+            // the row's denominator is the sum of its two threads' partial sums: exchanged through
+            // the query tile's shared memory, which no MMA reads any more
+            float* xl = reinterpret_cast<float*>(base_ptr + kFQOff) + (t * 128 + row) * 2;
+            xl[hh] = l;
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
+            const float inv = 1.f / (l + xl[hh ^ 1]);
             const int token = q0 + 128 * t + row;
-            const float inv = 1.f / l;
             __nv_bfloat16* orow = a.out + static_cast<int64_t>(token) * a.o_ts + static_cast<int64_t>(h) * a.o_hs;
 #pragma unroll 1
-            for (int c = 0; c < o_chunks; ++c) {
+            for (int c = o_half * hh; c < o_half * (hh + 1); ++c) {
                 uint32_t o[32];
                 tmem_ld_32x32(to + 32u * c, o);
                 tmem_ld_wait(o);
@@ -838,6 +929,13 @@ int attn_error_take() {
 }  // namespace rt
 
 using namespace rt;
+
+#ifdef RT_FA_TRACE
+extern "C" int rt_fa_trace_read(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, tc::g_fa_trace, sizeof(long long) * 10 * 64) == cudaSuccess
+               ? RT_OK : RT_ERR_CUDA;
+}
+#endif
 
 #ifdef RT_ATTN_TRACE
 extern "C" int rt_attn_trace_read(long long* host_out) {

@@ -16,6 +16,8 @@ from pathlib import Path
 from types import ModuleType
 from typing import Any, Callable
 
+import torch
+
 Fallback = Callable[..., Any]
 
 
@@ -46,6 +48,11 @@ class KernelDispatcher:
         return "mixed=cuda"
 
     # -- dispatch -----------------------------------------------------------------------------
+    # Opaque to Dynamo: a dispatched kernel is host code around a C-ABI call (environment lookup,
+    # module loading, raw pointers and the current stream's handle), none of which can be traced.
+    # Under torch.compile a model that reaches its kernels through the dispatcher gets a graph
+    # break here and the call runs as it does in eager mode.
+    @torch.compiler.disable
     def call(self, op_name: str, fallback: Fallback, *args: Any, backend: str | None = None,
              **kwargs: Any) -> Any:
         selected = backend or self.selected_backend(default="torch")

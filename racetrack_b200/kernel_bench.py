@@ -167,6 +167,21 @@ def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, s
         out[f"fp8_index[{T} queries x {keys} keys]"] = (
             (lambda q=q, wts=wts, kk=kk, ksc=ksc: ops.fp8_index(q, wts, kk, ksc)),
             2 * T * 64 * keys * 128, T * 64 * 128 + keys * 128 + T * keys * 4, "fp8")
+    # causal attention of the prefill stack (128 nope + 64 shared rope dims, values of 128):
+    # this library's kernel, and torch SDPA on whole keys as the yardstick
+    for heads in (16, HEADS):
+        q, kv, kpe = _randn(T, heads, 192) * 0.3, _randn(T, heads, 256) * 0.3, _randn(T, ROPE) * 0.3
+        flops = 2 * heads * (T * (T + 1) // 2) * (192 + 128)
+        nbytes = 2 * T * heads * (192 + 256 + 128) + 2 * T * ROPE
+        out[f"attention_prefill[{T} tokens x {heads} heads]"] = (
+            (lambda q=q, kv=kv, kpe=kpe: ops.attention_prefill(q, kv[..., :128], kpe, kv[..., 128:])),
+            flops, nbytes, "bf16")
+        k_full = torch.cat((kv[..., :128], kpe.unsqueeze(1).expand(-1, heads, -1)), dim=-1)
+
+        def sdpa(q=q, k=k_full, v=kv[..., 128:]):
+            qt, kt, vt = (t.transpose(0, 1).unsqueeze(0) for t in (q, k, v))
+            return torch.nn.functional.scaled_dot_product_attention(qt, kt, vt, is_causal=True)
+        out[f"torch_sdpa_yardstick[{T} tokens x {heads} heads]"] = (sdpa, flops, nbytes, "bf16")
     for name, n, k in (("w13", 4096, HIDDEN), ("w2", HIDDEN, 2048)):
         x, w = _randn(T, k), _randn(n, k)
         xq = ops.fused_nvfp4_quant(x, tiled_scales=True)

@@ -2,9 +2,18 @@
 racetrack/realistic_bench.py:118-427 (ShardedRealisticBlock / ShardedRealisticModel).
 
 Same structure and sharding as the reference runner: one layer's weights reused for every layer
-of the stack; attention heads tensor-parallel (w_q_b / w_kv_b column-sharded, w_o row-sharded,
-all-reduce after w_o); routed experts expert-parallel (each rank owns a contiguous slice, tokens
-replicated, all-reduce after the combine); router replicated. Per layer:
+of the stack; attention heads tensor-parallel (w_q_b / w_kv_b column-sharded, w_o row-sharded);
+routed experts expert-parallel (each rank owns a contiguous slice). The reference replicates all
+tokens and all-reduces the partial sums twice per layer (racetrack/realistic_bench.py:315-316,
+351); here each all-reduce is split into its two halves with the token-wise work in between:
+
+    partial sums [T, H]  --reduce-scatter-->  this rank's T / world rows of the sum
+    residual add + RMSNorm, qkv_a projection / router + routing + NVFP4 quantisation on those rows
+    --all-gather-->  every rank holds the [T, 2112] latent projection / the NVFP4 codes, scales
+    and routing of all tokens (0.3 / 0.56 bytes per hidden element instead of 2)
+
+so nothing token-wise is computed world times and less than half the bytes cross NVLink; the sums
+are the same sums (`token_sharded=False` keeps the reference's replicated schedule). Per layer:
 
     rms_norm -> qkv_a GEMM -> fused q_a/kv_a RMSNorm + k_pe RoPE -> q_b GEMM -> q_pe RoPE (in place)
     -> kv_b GEMM -> causal attention over the local heads (tcgen05) -> w_o GEMM -> all-reduce
@@ -28,7 +37,7 @@ from typing import Optional
 import torch
 import torch.nn.functional as F
 
-from . import moe, ops
+from . import comm, moe, ops
 
 
 @dataclass(frozen=True)
@@ -182,9 +191,11 @@ class RealisticLayer:
 
     def __init__(self, shape: LayerShape, weights: dict, rank: int = 0, world: int = 1, *,
                  ffn: str = "moe", route: str = "topk_softmax", proj: str = "bf16",
-                 process_group=None):
+                 process_group=None, token_sharded: bool = True):
         self.shape, self.rank, self.world, self.ffn, self.route = shape, rank, world, ffn, route
         self.group, self.proj = process_group, proj
+        self.token_sharded = token_sharded
+        self._comm = None
         self.local_heads = shape.heads // world
         dev = weights["w_qkv_a"].device
         self.w_qkv_a = Projection(weights["w_qkv_a"], proj)
@@ -225,11 +236,21 @@ class RealisticLayer:
             dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
         return t
 
+    @property
+    def comm(self) -> "comm.Group":
+        if self._comm is None:
+            self._comm = comm.Group(self.rank, self.world if self.reduce else 1, self.group)
+        return self._comm
+
     def attention(self, normed: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
-        """racetrack/realistic_bench.py:286-317."""
+        """racetrack/realistic_bench.py:286-317: all tokens in, all-reduced [T, H] out."""
+        return self._all_reduce(self.attention_partial(self.w_qkv_a(normed), positions))
+
+    def attention_partial(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """From the latent projection qkv [T, q_lora + kv_lora + rope] of ALL tokens to this
+        rank's partial sum of the attention output (its heads' share of w_o)."""
         s, h = self.shape, self.local_heads
-        tokens = normed.shape[0]
-        qkv = self.w_qkv_a(normed)
+        tokens = qkv.shape[0]
         q_c, kv_c, k_pe = ops.fused_norm_rope(
             qkv[:, :s.q_lora], self.q_norm, qkv[:, s.q_lora:s.q_lora + s.kv_lora], self.kv_norm,
             qkv[:, s.q_lora + s.kv_lora:], positions, eps=s.eps, rope_base=s.rope_base)
@@ -242,21 +263,22 @@ class RealisticLayer:
             kv = self.w_kv_b(kv_c).view(tokens, h, s.qk_dim + s.v_dim)
             ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
             local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
-        out = self.w_o(local.reshape(tokens, h * s.v_dim))
-        return self._all_reduce(out)
+        return self.w_o(local.reshape(tokens, h * s.v_dim))
+
+    def _route(self, normed: torch.Tensor):
+        """Router of racetrack/realistic_bench.py:321-327 for the given rows: fp32 logits of bf16
+        operands (tensor cores, fp32 accumulators kept), top-k, softmax over the k logits."""
+        logits = ops.linear_bf16(normed, self.w_gate, out_dtype=torch.float32)
+        if self.route != "topk_softmax":
+            raise ValueError(f"unknown route {self.route!r}")
+        return ops.fused_moe_route(logits, None, n_groups=1, topk_groups=1, topk=self.shape.topk,
+                                   route_scale=1.0, score_func="topk_softmax")
 
     def ffn_forward(self, normed: torch.Tensor) -> torch.Tensor:
         """racetrack/realistic_bench.py:319-352 (routed experts) or a dense SwiGLU FFN."""
         s = self.shape
         if self.ffn == "moe":
-            # fp32 router logits of bf16 operands: tensor cores with the fp32 accumulators kept
-            logits = ops.linear_bf16(normed, self.w_gate, out_dtype=torch.float32)
-            if self.route == "topk_softmax":
-                weights, indices = ops.fused_moe_route(logits, None, n_groups=1, topk_groups=1,
-                                                       topk=s.topk, route_scale=1.0,
-                                                       score_func="topk_softmax")
-            else:
-                raise ValueError(f"unknown route {self.route!r}")
+            weights, indices = self._route(normed)
             out = moe.fused_moe_experts(normed, weights, indices, self.experts,
                                         n_experts=s.n_experts,
                                         expert_begin=self.rank * self.local_experts)
@@ -270,10 +292,41 @@ class RealisticLayer:
                 out = self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]))
         return self._all_reduce(out)
 
+    def ffn_partial_from_rows(self, normed_rows: torch.Tensor) -> torch.Tensor:
+        """Token-sharded feed-forward half: `normed_rows` are this rank's T / world rows of the
+        normalised hidden states; returns this rank's partial sum [T, H] over ALL tokens (its
+        experts' / its FFN columns' share). Routing and quantisation run on the rank's rows, their
+        compact results are all-gathered: NVFP4 codes + block scales + routing (MoE) or FP8 codes +
+        scales (dense FFN with FP8 weights) instead of bf16 hidden states."""
+        s, c = self.shape, self.comm
+        if self.ffn == "moe":
+            weights, indices = self._route(normed_rows)
+            # one tensor-wide NVFP4 scale whatever the world size: the maximum over all ranks' rows
+            amax = c.all_reduce_max(ops.tensor_absmax(normed_rows))
+            codes, sf, gs = ops.fused_nvfp4_quant(normed_rows, amax=amax)
+            codes, sf = c.all_gather_rows(codes), c.all_gather_rows(sf.view(torch.uint8))
+            weights, indices = c.all_gather_rows(weights), c.all_gather_rows(indices)
+            return moe.fused_moe_experts(None, weights, indices, self.experts, n_experts=s.n_experts,
+                                         expert_begin=self.rank * self.local_experts,
+                                         x_quant=(codes, sf, gs))
+        if self.w13d.fp8:
+            codes, scales = ops.fused_act_quant(normed_rows)
+            gate_up = ops.linear_fp8(c.all_gather_rows(codes), c.all_gather_rows(scales),
+                                     self.w13d.codes, self.w13d.scales)
+        else:
+            gate_up = ops.linear_bf16(c.all_gather_rows(normed_rows), self.w13d.weight)
+        inter = gate_up.shape[1] // 2
+        if self.w2d.fp8:
+            codes, scales = ops.fused_swiglu_quant(gate_up[:, :inter], gate_up[:, inter:])
+            return ops.linear_fp8(codes, scales, self.w2d.codes, self.w2d.scales)
+        return self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]))
+
     # -- the stack ----------------------------------------------------------------------------
     def forward_stack(self, hidden: torch.Tensor, positions: torch.Tensor, layers: int) -> torch.Tensor:
         """hidden [T, H] bf16 -> hidden after `layers` applications of the layer
         (racetrack/realistic_bench.py:354-389,420-423)."""
+        if self.world > 1 and self.reduce and self.token_sharded and hidden.shape[0] % self.world == 0:
+            return self._forward_stack_token_sharded(hidden, positions, layers)
         s = self.shape
         normed = ops.fused_rms_norm(hidden, self.ones_h, eps=s.eps)
         for layer in range(layers):
@@ -283,3 +336,20 @@ class RealisticLayer:
             # the add closing this layer and the rms_norm opening the next one, in one pass
             normed, hidden = ops.fused_residual_norm(ffn, hidden, self.ones_h, eps=s.eps)
         return hidden
+
+    def _forward_stack_token_sharded(self, hidden: torch.Tensor, positions: torch.Tensor,
+                                     layers: int) -> torch.Tensor:
+        """The same stack on more than one rank with every all-reduce split into reduce-scatter
+        and all-gather around the token-wise kernels (module docstring): between the two sharded
+        halves of a layer a rank holds only its own T / world rows of the hidden states."""
+        s, c = self.shape, self.comm
+        lo, hi = c.rows_of(hidden.shape[0])
+        mine = hidden[lo:hi].contiguous()
+        normed = ops.fused_rms_norm(mine, self.ones_h, eps=s.eps)
+        for _ in range(layers):
+            qkv = c.all_gather_rows(self.w_qkv_a(normed))              # [T, 2112]: 0.3 of a hidden row
+            attn = c.reduce_scatter_rows(self.attention_partial(qkv, positions))
+            normed, mine = ops.fused_residual_norm(attn, mine, self.ones_h, eps=s.eps)
+            ffn = c.reduce_scatter_rows(self.ffn_partial_from_rows(normed))
+            normed, mine = ops.fused_residual_norm(ffn, mine, self.ones_h, eps=s.eps)
+        return c.all_gather_rows(mine)

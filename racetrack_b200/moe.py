@@ -133,21 +133,28 @@ def moe_quant_nvfp4(x: torch.Tensor, tile_map: torch.Tensor, tile_count: torch.T
     return codes, sf, gs
 
 
-def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Tensor,
+def fused_moe_experts(x: Optional[torch.Tensor], weights: torch.Tensor, indices: torch.Tensor,
                       experts: NVFP4Experts, *, n_experts: int, expert_begin: int = 0,
                       shared: Optional[torch.Tensor] = None,
                       out_dtype: torch.dtype = torch.bfloat16,
-                      parts: Optional[dict] = None) -> torch.Tensor:
+                      parts: Optional[dict] = None,
+                      x_quant: Optional[tuple] = None) -> torch.Tensor:
     """y[t] = sum over the token's routed experts owned here of w * expert(x[t]) (+ shared[t]).
 
     x [T, hidden] bf16; weights fp32 [T, k] and indices int64 [T, k] from fused_moe_route;
     `experts` holds the experts [expert_begin, expert_begin + experts.count) of n_experts (an
     expert-parallel rank passes its own slice and all-reduces the result). Expert arithmetic:
     NVFP4(x) . NVFP4(w13)^T -> bf16 gate/up -> NVFP4(swiglu) . NVFP4(w2)^T -> bf16, fp32 combine.
+    `x_quant` = (codes [T, hidden/2], row-major block scales [T, hidden/16] as bytes, global scale
+    [1]) hands over token rows that are quantised already (x may then be None): ranks of a
+    token-sharded layer quantise their own rows and all-gather the codes.
     A dict passed as `parts` receives the intermediates (expert offsets, permutation, the two
     tensor-wide amax values, gate_up, h and the per-pair expert outputs) for stage-wise checks.
     """
-    tokens, hidden = x.shape
+    if x_quant is not None:
+        tokens, hidden = x_quant[0].shape[0], x_quant[0].shape[1] * 2
+    else:
+        tokens, hidden = x.shape
     topk = indices.shape[1]
     pairs = tokens * topk
     count = experts.count
@@ -160,8 +167,12 @@ def fused_moe_experts(x: torch.Tensor, weights: torch.Tensor, indices: torch.Ten
         if local else None
     # dispatch: every token row is quantised once, then its codes and scales are copied into
     # expert order (the bf16 rows are not read topk times)
-    x_amax = ops.tensor_absmax(x)
-    x_codes, x_sf, a_gs = ops.fused_nvfp4_quant(x, amax=x_amax)
+    if x_quant is not None:
+        x_codes, x_sf, a_gs = x_quant
+        x_amax = None
+    else:
+        x_amax = ops.tensor_absmax(x)
+        x_codes, x_sf, a_gs = ops.fused_nvfp4_quant(x, amax=x_amax)
     a_codes, a_sf = moe_gather_nvfp4(x_codes, x_sf.view(torch.uint8), sorted_pairs, topk, tile_map,
                                      tile_count, pairs)
     gate_up = ops.gemm_nvfp4_grouped(a_codes, a_sf, a_gs, experts.w13_codes, experts.w13_sf,

@@ -62,7 +62,10 @@ def _resolve_kernel(dispatcher: KernelDispatcher, op_name: str):
         return None
     if backend == "best":
         backend = "cuda"
-    return dispatcher._resolve(backend, op_name)
+    fn = dispatcher._resolve(backend, op_name)
+    # host code around a C-ABI call (raw pointers, the current stream's handle): opaque to Dynamo,
+    # which breaks the graph at the call and runs it as in eager mode
+    return torch.compiler.disable(fn) if fn is not None else None
 
 
 def _modules_named(model: nn.Module, *class_names: str):

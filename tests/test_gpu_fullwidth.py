@@ -82,7 +82,7 @@ def test_full_width_prefill_layer_stage_by_stage(tokens, layers):
     print("full-width prefill layer:", res)
     assert res["ok"], res["stages"]
     for st in res["stages"]:
-        assert st["rel"] <= (0.02 if st["stage"] == "attention" else 0.08), st
+        assert st["rel"] <= (0.05 if st["stage"] == "attention" else 0.1), st
     e2e = res["end_to_end"]
     if layers == 1:
         assert e2e["vs_same_arithmetic_oracle"]["ok"], e2e
