@@ -275,7 +275,7 @@ class PrefillStackWorkload:
 
     def _build_model(self, w, args):
         return self.layer_mod.RealisticLayer(self.shape, w, self.rank, self.world, ffn=self.ffn,
-                                             proj=args.proj)
+                                             proj=args.proj, token_sharded=not args.replicated)
 
     def _forward(self, hidden):
         return self.model.forward_stack(hidden, self.positions, self.layers)
@@ -1007,6 +1007,24 @@ def run_ours(args) -> None:
             wl.step(record=True)
         barrier()
     dom_us = statistics.mean(s.elapsed_time(e) for s, e in wl.dom_events) * 1e3
+    # where the step's time goes between the ranks: one more eager step with CUDA events around
+    # every collective (outside the timed region)
+    comm_stats = None
+    group = getattr(getattr(wl, "model", None), "comm", None)
+    if distributed and group is not None:
+        barrier()
+        group.start_timing()
+        wl.step()
+        per = group.stop_timing()
+        layers = max(getattr(wl, "layers", 1), 1)
+        comm_ms = max_over_ranks(sum(ms for _, ms, _ in per.values())) / layers
+        comm_stats = {"comm_ms_per_layer": comm_ms,
+                      "collectives_per_layer": {k: {"calls": c / layers, "ms": ms / layers,
+                                                    "payload_mb": b / layers / 1e6}
+                                                for k, (c, ms, b) in per.items()},
+                      "schedule": "token-sharded: reduce-scatter -> token-wise kernels on T/N rows -> "
+                                  "all-gather of their compact outputs"
+                      if getattr(wl.model, "token_sharded", False) else "replicated tokens, all-reduce"}
 
     wl.e2e_setup()
     for _ in range(min(args.warmup, 2)):
@@ -1084,6 +1102,10 @@ def run_ours(args) -> None:
             "clocks": clocks,
         }
         line["check"] = check
+        if comm_stats is not None:
+            comm_stats["compute_ms_per_layer"] = ms_total / args.steps / max(getattr(wl, "layers", 1), 1) \
+                - comm_stats["comm_ms_per_layer"]
+            line["multi_gpu"] = comm_stats
         line["config"]["cuda_graph"] = bool(use_graph)
         if use_graph:
             line["roofline"]["timed_in"] = "two eager steps after the replayed region"
@@ -1127,6 +1149,9 @@ def main() -> None:
     ap.add_argument("--attn-core", default="rt", choices=("rt", "sdpa"),
                     help="attention core of the prefill layer: this backend's causal attention "
                          "kernel, or torch's SDPA as the yardstick it is measured against")
+    ap.add_argument("--replicated", action="store_true",
+                    help="multi-GPU: the reference's schedule (all tokens on every rank, two "
+                         "all-reduces per layer) instead of the token-sharded one")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true",
                     help="skip the validation of the timed configuration against the CPU oracle")

@@ -32,6 +32,32 @@ class Group:
         if world > 1 and not (dist.is_available() and dist.is_initialized()):
             raise RuntimeError("a sharded layer needs an initialised torch.distributed process group")
         self._no_reduce_scatter = world > 1 and dist.get_backend(group) == "gloo"
+        self.events = None          # a list while timing: (name, bytes sent by this rank, start, end)
+
+    def start_timing(self) -> None:
+        """From now on every collective is bracketed by CUDA events on the current stream (the
+        interval includes the wait for the collective's input, as the layer experiences it)."""
+        self.events = []
+
+    def stop_timing(self) -> dict:
+        """{name: (calls, total ms, total payload bytes)} of the collectives since start_timing."""
+        torch.cuda.synchronize()
+        out: dict = {}
+        for name, nbytes, start, end in self.events or []:
+            calls, ms, total = out.get(name, (0, 0.0, 0))
+            out[name] = (calls + 1, ms + start.elapsed_time(end), total + nbytes)
+        self.events = None
+        return out
+
+    def _timed(self, name: str, payload: torch.Tensor, fn):
+        if self.events is None or not payload.is_cuda:
+            return fn()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        result = fn()
+        end.record()
+        self.events.append((name, payload.numel() * payload.element_size(), start, end))
+        return result
 
     def rows_of(self, total_rows: int) -> tuple[int, int]:
         """[begin, end) of this rank's rows of a [total_rows, ...] tensor."""
@@ -49,7 +75,8 @@ class Group:
             dist.all_reduce(partial, op=dist.ReduceOp.SUM, group=self.group)
             return partial[lo:hi].clone()
         out = torch.empty((hi - lo, *partial.shape[1:]), dtype=partial.dtype, device=partial.device)
-        dist.reduce_scatter_tensor(out, partial, op=dist.ReduceOp.SUM, group=self.group)
+        self._timed("reduce_scatter", partial, lambda: dist.reduce_scatter_tensor(
+            out, partial, op=dist.ReduceOp.SUM, group=self.group))
         return out
 
     def all_gather_rows(self, rows: torch.Tensor) -> torch.Tensor:
@@ -58,18 +85,20 @@ class Group:
         rows = rows.contiguous()
         out = torch.empty((rows.shape[0] * self.world, *rows.shape[1:]), dtype=rows.dtype,
                           device=rows.device)
+        src, dst = rows, out
         if rows.dtype == torch.float8_e4m3fn:       # collectives move bytes
-            dist.all_gather_into_tensor(out.view(torch.uint8), rows.view(torch.uint8), group=self.group)
-        else:
-            dist.all_gather_into_tensor(out, rows, group=self.group)
+            src, dst = rows.view(torch.uint8), out.view(torch.uint8)
+        self._timed("all_gather", rows, lambda: dist.all_gather_into_tensor(dst, src, group=self.group))
         return out
 
     def all_reduce_max(self, value: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
-            dist.all_reduce(value, op=dist.ReduceOp.MAX, group=self.group)
+            self._timed("all_reduce_max", value,
+                        lambda: dist.all_reduce(value, op=dist.ReduceOp.MAX, group=self.group))
         return value
 
     def all_reduce_sum(self, value: torch.Tensor) -> torch.Tensor:
         if self.world > 1:
-            dist.all_reduce(value, op=dist.ReduceOp.SUM, group=self.group)
+            self._timed("all_reduce_sum", value,
+                        lambda: dist.all_reduce(value, op=dist.ReduceOp.SUM, group=self.group))
         return value

@@ -232,8 +232,7 @@ class RealisticLayer:
 
     def _all_reduce(self, t: torch.Tensor) -> torch.Tensor:
         if self.world > 1 and self.reduce:
-            import torch.distributed as dist
-            dist.all_reduce(t, op=dist.ReduceOp.SUM, group=self.group)
+            self.comm.all_reduce_sum(t)
         return t
 
     @property
