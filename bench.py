@@ -275,7 +275,8 @@ class PrefillStackWorkload:
 
     def _build_model(self, w, args):
         return self.layer_mod.RealisticLayer(self.shape, w, self.rank, self.world, ffn=self.ffn,
-                                             proj=args.proj, token_sharded=not args.replicated)
+                                             proj=args.proj, token_sharded=not args.replicated,
+                                             peer_reduce=not args.nccl_reduce)
 
     def _forward(self, hidden):
         return self.model.forward_stack(hidden, self.positions, self.layers)
@@ -1152,6 +1153,9 @@ def main() -> None:
     ap.add_argument("--replicated", action="store_true",
                     help="multi-GPU: the reference's schedule (all tokens on every rank, two "
                          "all-reduces per layer) instead of the token-sharded one")
+    ap.add_argument("--nccl-reduce", action="store_true",
+                    help="multi-GPU: NCCL reduce-scatter + the plain residual-norm kernel instead of "
+                         "the fused kernel that reads the peers' partial sums over NVLink")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-check", action="store_true",
                     help="skip the validation of the timed configuration against the CPU oracle")

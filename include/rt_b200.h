@@ -598,6 +598,41 @@ int rt_attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, 
                            int64_t o_token_stride, int64_t o_head_stride,
                            float softmax_scale, void* stream);
 
+/* ------------------------------------------------------------------------ */
+/* Collective steps over NVLink peer memory (one process per GPU)              */
+/* ------------------------------------------------------------------------ */
+
+/*
+ * Device-side barrier of `world` ranks (<= 8). flag_ptrs[q] is rank q's flag array (int32
+ * [world + 1], zero at start) as mapped into THIS process (CUDA IPC; flag_ptrs[rank] is the
+ * local one). The kernel counts its own barriers in the last slot of the local array, stores
+ * that count into slot `rank` of every rank's array and waits until all slots of its own array
+ * have reached it; every rank must call the barrier the same number of times. What a rank
+ * wrote on `stream` before the barrier is visible to every rank after it. The wait is bounded
+ * (about two seconds): a rank that never arrives makes the others record an error, which
+ * rt_peer_error_state() reports, instead of hanging them.
+ * ref: the rendezvous inside dist.all_reduce of racetrack/realistic_bench.py:315-316,351.
+ */
+int rt_peer_barrier(int* const* flag_ptrs, int64_t rank, int64_t world, void* stream);
+int rt_peer_error_state(void);
+
+/*
+ * Reduce-scatter fused with residual add + RMSNorm: for rows [row0, row0 + rows) of the
+ * [T, cols] bf16 partial sums that every rank holds (partial_ptrs[q] = rank q's buffer as
+ * mapped into this process, row pitch partial_stride elements),
+ *   update = bf16(sum over ranks, fp32, rank order)        (what the all-reduce would leave)
+ *   hidden = bf16(update + residual)    normed = bf16(weight * (hidden_fp32 * rsqrt(mean^2 + eps)))
+ * exactly as rt_residual_norm computes them from `update`. residual / normed / hidden hold
+ * only this rank's `rows` rows. Peer memory is read with plain loads over NVLink; call
+ * rt_peer_barrier first so that all ranks have finished writing their partial sums.
+ * ref: racetrack/realistic_bench.py:315-316,351 (all_reduce SUM) followed by :375-389
+ *      (residual add, rms_norm); racetrack/models/deepseek.py:485-495.
+ */
+int rt_peer_reduce_residual_norm(const void* const* partial_ptrs, int64_t world, int64_t row0,
+                                 int64_t partial_stride, const void* residual, const void* weight,
+                                 int weight_dtype, void* normed, void* hidden, int64_t rows,
+                                 int64_t cols, int64_t residual_stride, float eps, void* stream);
+
 /*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when
  * one of its bounded waits expired. RT_OK when no kernel gave up since the last call,

@@ -28,6 +28,7 @@ SOURCES = {
     "rt_moe.cu": ["-fmad=false"],
     "rt_gemm.cu": [],
     "rt_attn.cu": [],
+    "rt_peer.cu": ["-fmad=false"],
 }
 
 COMMON = [

@@ -126,6 +126,19 @@ __device__ __forceinline__ float warp_max(float v) {
     return v;
 }
 
+// Loads 8 consecutive weights as fp32 (weights are tiny and shared by all rows).
+template <bool W_BF16>
+__device__ __forceinline__ void load_weight8(const void* w, int vec, float (&out)[8]) {
+    if constexpr (W_BF16) {
+        unpack_bf16x8(ld_cached16(static_cast<const uint4*>(w) + vec), out);
+    } else {
+        const float4 a = __ldg(static_cast<const float4*>(w) + 2 * vec);
+        const float4 b = __ldg(static_cast<const float4*>(w) + 2 * vec + 1);
+        out[0] = a.x; out[1] = a.y; out[2] = a.z; out[3] = a.w;
+        out[4] = b.x; out[5] = b.y; out[6] = b.z; out[7] = b.w;
+    }
+}
+
 // Sum of `a` and of `b` over the whole block; result broadcast to every thread.
 // `scratch` is 64 floats of shared memory. blockDim.x must be a multiple of 32.
 __device__ __forceinline__ void block_sum2(float& a, float& b, float* scratch) {

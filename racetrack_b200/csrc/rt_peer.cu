@@ -1,0 +1,210 @@
+// Collective steps of the tensor/expert-parallel layer over NVLink peer memory.
+//
+// One process per GPU; every rank maps the other ranks' exchange buffers into its own address
+// space (CUDA IPC, set up by the host side) and the kernels here read or write them with plain
+// loads and stores over NVLink / NVSwitch: no multicast, no tensor maps over peer memory.
+//
+//   peer_barrier_kernel        all ranks have finished writing their partial sums (and have
+//                              finished reading the previous ones): every rank stores a step
+//                              counter into a flag slot of every peer and waits, with a bounded
+//                              spin, until its own slots carry that counter.
+//   peer_reduce_norm_kernel    the reduce-scatter of the reference's all-reduce
+//                              (racetrack/realistic_bench.py:315-316,351) fused with the token-wise
+//                              kernel that follows it: for this rank's rows, the partial sums of
+//                              all ranks are read (own memory + peers), added in rank order in
+//                              fp32, rounded to bf16 like the all-reduced tensor, then residual
+//                              add + RMSNorm exactly as residual_norm_kernel does. The summed
+//                              tensor never exists in memory.
+#include "rt_common.cuh"
+
+namespace rt {
+
+static __device__ int g_peer_error = 0;
+
+constexpr int kMaxPeers = 8;
+
+struct PeerPtrs {
+    const void* p[kMaxPeers];
+};
+struct PeerFlagPtrs {
+    int* p[kMaxPeers];
+};
+
+// flags: int32 [world + 1] in every rank's memory; slot r of rank q is written by rank r only,
+// slot `world` is the rank's own count of barriers passed (kept on the device, so a barrier
+// replayed from a CUDA graph takes the next step like an eagerly launched one).
+__global__ void peer_barrier_kernel(PeerFlagPtrs flags, int rank, int world, long long max_spins) {
+    __shared__ int step_s;
+    if (threadIdx.x == 0) step_s = ++flags.p[rank][world];
+    __syncthreads();
+    const int step = step_s;
+    const int peer = threadIdx.x;
+    if (peer >= world) return;
+    // everything this rank wrote before the barrier is visible system-wide before the flag is
+    __threadfence_system();
+    asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.p[peer] + rank), "r"(step) : "memory");
+    const int* mine = flags.p[rank] + peer;
+    long long spins = 0;
+    while (true) {
+        int v;
+        asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
+        if (v >= step) break;
+        if (++spins > max_spins) {            // a peer never arrived: report instead of hanging
+            atomicCAS(&g_peer_error, 0, 100 + peer);
+            break;
+        }
+        __nanosleep(64);
+    }
+}
+
+// One CTA per row of this rank's share. VPT = 16-byte vectors per thread.
+template <int VPT, bool W_BF16>
+__global__ void __launch_bounds__(512) peer_reduce_norm_kernel(
+    PeerPtrs partial, int world, int64_t row0, int64_t pstride,
+    const __nv_bfloat16* __restrict__ residual, const void* __restrict__ weight,
+    __nv_bfloat16* __restrict__ normed, __nv_bfloat16* __restrict__ hidden, int nvec,
+    int64_t rstride, float cols_f, float eps) {
+    __shared__ float scratch[32];
+    const int64_t row = blockIdx.x;
+    const uint4* r = reinterpret_cast<const uint4*>(residual + row * rstride);
+    uint4* hrow = reinterpret_cast<uint4*>(hidden) + row * nvec;
+    uint4* nrow = reinterpret_cast<uint4*>(normed) + row * nvec;
+    float h[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+            // all ranks' vectors first (independent loads over NVLink), then the sum in rank order
+            uint4 pv[kMaxPeers];
+#pragma unroll
+            for (int q = 0; q < kMaxPeers; ++q)
+                if (q < world)
+                    pv[q] = ld_once16(reinterpret_cast<const uint4*>(
+                                          static_cast<const __nv_bfloat16*>(partial.p[q]) + (row0 + row) * pstride) + v);
+            const uint4 rv = ld_stream16(r + v);
+            float acc[8];
+            unpack_bf16x8(pv[0], acc);
+#pragma unroll
+            for (int q = 1; q < kMaxPeers; ++q) {
+                if (q < world) {
+                    float a[8];
+                    unpack_bf16x8(pv[q], a);
+#pragma unroll
+                    for (int k = 0; k < 8; ++k) acc[k] += a[k];
+                }
+            }
+            float b[8], u[8];
+            unpack_bf16x8(pack_bf16x8(acc), u);      // the all-reduced tensor is bf16
+            unpack_bf16x8(rv, b);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                h[i][k] = u[k] + b[k];
+                ss += h[i][k] * h[i][k];
+            }
+            st_stream16(hrow + v, pack_bf16x8(h[i]));
+        }
+    }
+    ss = block_sum(ss, scratch);
+    const float rs = rsqrtf(ss / cols_f + eps);
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int v = threadIdx.x + i * blockDim.x;
+        if (v < nvec) {
+            float w[8], o[8];
+            load_weight8<W_BF16>(weight, v, w);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) o[k] = w[k] * (h[i][k] * rs);
+            st_stream16(nrow + v, pack_bf16x8(o));
+        }
+    }
+}
+
+}  // namespace rt
+
+using namespace rt;
+
+extern "C" int rt_peer_barrier(int* const* flag_ptrs, int64_t rank, int64_t world, void* stream) {
+    RT_REQUIRE(flag_ptrs && world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world,
+               RT_ERR_BAD_ARG, "rt_peer_barrier: bad arguments (at most %d ranks)", kMaxPeers);
+    PeerFlagPtrs f;
+    for (int q = 0; q < kMaxPeers; ++q) f.p[q] = q < world ? flag_ptrs[q] : nullptr;
+    for (int q = 0; q < world; ++q) RT_REQUIRE(f.p[q], RT_ERR_BAD_ARG, "rt_peer_barrier: null flag pointer");
+    // about two seconds of polling at 64 ns per sleep, then the error flag
+    peer_barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(f, (int)rank, (int)world, 20000000LL);
+    count_launch();
+    return check_launch("peer_barrier_kernel");
+}
+
+extern "C" int rt_peer_error_state(void) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_peer_error, sizeof(int)) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RT_ERR_CUDA, "rt_peer_error_state: cannot read the device flag");
+    }
+    if (v != 0) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(g_peer_error, &zero, sizeof(int));
+        return fail(RT_ERR_TIMEOUT, "a peer barrier gave up waiting for rank %d", v - 100);
+    }
+    return RT_OK;
+}
+
+extern "C" int rt_peer_reduce_residual_norm(const void* const* partial_ptrs, int64_t world, int64_t row0,
+                                            int64_t partial_stride, const void* residual,
+                                            const void* weight, int weight_dtype, void* normed,
+                                            void* hidden, int64_t rows, int64_t cols,
+                                            int64_t residual_stride, float eps, void* stream) {
+    RT_REQUIRE(partial_ptrs && residual && weight && normed && hidden, RT_ERR_BAD_ARG,
+               "rt_peer_reduce_residual_norm: null pointer");
+    RT_REQUIRE(world >= 1 && world <= kMaxPeers, RT_ERR_BAD_ARG,
+               "rt_peer_reduce_residual_norm: 1 to %d ranks", kMaxPeers);
+    RT_REQUIRE(rows >= 0 && cols > 0 && cols % 8 == 0 && cols <= 32768 && partial_stride % 8 == 0 &&
+                   residual_stride % 8 == 0 && row0 >= 0,
+               RT_ERR_UNSUPPORTED,
+               "rt_peer_reduce_residual_norm: cols must be a multiple of 8 up to 32768, strides multiples of 8");
+    RT_REQUIRE(weight_dtype == RT_BF16 || weight_dtype == RT_F32, RT_ERR_BAD_ARG,
+               "rt_peer_reduce_residual_norm: weight must be bf16 or fp32");
+    if (rows == 0) return RT_OK;
+    PeerPtrs p;
+    for (int q = 0; q < kMaxPeers; ++q) {
+        p.p[q] = q < world ? partial_ptrs[q] : nullptr;
+        RT_REQUIRE(q >= world || (p.p[q] && aligned16(p.p[q])), RT_ERR_BAD_ARG,
+                   "rt_peer_reduce_residual_norm: partial pointers must be non-null and 16-byte aligned");
+    }
+    RT_REQUIRE(aligned16(residual) && aligned16(normed) && aligned16(hidden), RT_ERR_BAD_ARG,
+               "rt_peer_reduce_residual_norm: pointers must be 16-byte aligned");
+    const int nvec = static_cast<int>(cols / 8);
+    int vpt = 0, threads = 0;
+    for (int cand : {1, 2, 4, 8}) {
+        const int th = ((nvec + cand - 1) / cand + 31) / 32 * 32;
+        if (th <= 256 || (cand == 8 && th <= 512)) {
+            vpt = cand;
+            threads = th < 32 ? 32 : th;
+            break;
+        }
+    }
+    RT_REQUIRE(vpt, RT_ERR_UNSUPPORTED, "rt_peer_reduce_residual_norm: row too wide");
+    const dim3 grid(static_cast<unsigned>(rows));
+    cudaStream_t st = as_stream(stream);
+    const bool wb = weight_dtype == RT_BF16;
+    const auto* res = static_cast<const __nv_bfloat16*>(residual);
+    auto* n = static_cast<__nv_bfloat16*>(normed);
+    auto* h = static_cast<__nv_bfloat16*>(hidden);
+#define RT_LAUNCH_PR(V)                                                                               \
+    if (wb)                                                                                           \
+        peer_reduce_norm_kernel<V, true><<<grid, threads, 0, st>>>(                                   \
+            p, (int)world, row0, partial_stride, res, weight, n, h, nvec, residual_stride, (float)cols, eps); \
+    else                                                                                              \
+        peer_reduce_norm_kernel<V, false><<<grid, threads, 0, st>>>(                                  \
+            p, (int)world, row0, partial_stride, res, weight, n, h, nvec, residual_stride, (float)cols, eps);
+    switch (vpt) {
+        case 1: RT_LAUNCH_PR(1) break;
+        case 2: RT_LAUNCH_PR(2) break;
+        case 4: RT_LAUNCH_PR(4) break;
+        default: RT_LAUNCH_PR(8) break;
+    }
+#undef RT_LAUNCH_PR
+    count_launch();
+    return check_launch("peer_reduce_norm_kernel");
+}

@@ -120,6 +120,14 @@ def cases(tokens: int) -> dict[str, tuple[Callable[[], object], int]]:
     sc = torch.randn(min(T, 2048), 4096, device="cuda")
     out["index_topk[2048 of 4096]"] = (lambda: ops.index_topk(sc, 2048),
                                        sc.numel() * 4 + sc.shape[0] * 2048 * 4)
+    # indexer prologue: LayerNorm + RoPE + Hadamard + FP8 quantisation of the keys (one 128-wide
+    # row per token) and of the 64 index heads of every query
+    table = torch.polar(torch.ones(max(T, 16), 32, device="cuda"), torch.rand(max(T, 16), 32, device="cuda"))
+    xk, xq = _randn(T, 1, 128), _randn(T, 64, 128)
+    lnw, lnb = torch.ones(128, device="cuda"), torch.zeros(128, device="cuda")
+    out["index_prep[keys]"] = (lambda: ops.index_prep(xk, table, ln_weight=lnw, ln_bias=lnb),
+                               T * (256 + 132))
+    out["index_prep[queries x 64 heads]"] = (lambda: ops.index_prep(xq, table), T * 64 * (256 + 132))
     eo = _randn(T * TOPK, HIDDEN)
     wts = torch.rand(T, TOPK, device="cuda")
     out["fused_moe_combine"] = (lambda: ops.fused_moe_combine(eo, pp, wts, u),

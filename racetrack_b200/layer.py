@@ -179,10 +179,10 @@ class Projection:
         else:
             self.weight = weight.contiguous()
 
-    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         if self.fp8:
-            return ops.linear_fp8_act(x, self.codes, self.scales)
-        return ops.linear_bf16(x, self.weight)
+            return ops.linear_fp8_act(x, self.codes, self.scales, out=out)
+        return ops.linear_bf16(x, self.weight, out=out)
 
 
 class RealisticLayer:
@@ -191,10 +191,14 @@ class RealisticLayer:
 
     def __init__(self, shape: LayerShape, weights: dict, rank: int = 0, world: int = 1, *,
                  ffn: str = "moe", route: str = "topk_softmax", proj: str = "bf16",
-                 process_group=None, token_sharded: bool = True):
+                 process_group=None, token_sharded: bool = True, peer_reduce: bool = True):
         self.shape, self.rank, self.world, self.ffn, self.route = shape, rank, world, ffn, route
         self.group, self.proj = process_group, proj
         self.token_sharded = token_sharded
+        # reduce-scatter by peer loads over NVLink fused into the residual-add + RMSNorm kernel
+        # (False: NCCL reduce-scatter, then the plain kernel)
+        self.peer_reduce = peer_reduce
+        self._peer: dict = {}
         self._comm = None
         self.local_heads = shape.heads // world
         dev = weights["w_qkv_a"].device
@@ -245,9 +249,11 @@ class RealisticLayer:
         """racetrack/realistic_bench.py:286-317: all tokens in, all-reduced [T, H] out."""
         return self._all_reduce(self.attention_partial(self.w_qkv_a(normed), positions))
 
-    def attention_partial(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    def attention_partial(self, qkv: torch.Tensor, positions: torch.Tensor,
+                          out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """From the latent projection qkv [T, q_lora + kv_lora + rope] of ALL tokens to this
-        rank's partial sum of the attention output (its heads' share of w_o)."""
+        rank's partial sum of the attention output (its heads' share of w_o), written into `out`
+        when given (a buffer the other ranks read)."""
         s, h = self.shape, self.local_heads
         tokens = qkv.shape[0]
         q_c, kv_c, k_pe = ops.fused_norm_rope(
@@ -262,7 +268,7 @@ class RealisticLayer:
             kv = self.w_kv_b(kv_c).view(tokens, h, s.qk_dim + s.v_dim)
             ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
             local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
-        return self.w_o(local.reshape(tokens, h * s.v_dim))
+        return self.w_o(local.reshape(tokens, h * s.v_dim), out=out)
 
     def _route(self, normed: torch.Tensor):
         """Router of racetrack/realistic_bench.py:321-327 for the given rows: fp32 logits of bf16
@@ -291,7 +297,8 @@ class RealisticLayer:
                 out = self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]))
         return self._all_reduce(out)
 
-    def ffn_partial_from_rows(self, normed_rows: torch.Tensor) -> torch.Tensor:
+    def ffn_partial_from_rows(self, normed_rows: torch.Tensor,
+                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
         """Token-sharded feed-forward half: `normed_rows` are this rank's T / world rows of the
         normalised hidden states; returns this rank's partial sum [T, H] over ALL tokens (its
         experts' / its FFN columns' share). Routing and quantisation run on the rank's rows, their
@@ -307,7 +314,7 @@ class RealisticLayer:
             weights, indices = c.all_gather_rows(weights), c.all_gather_rows(indices)
             return moe.fused_moe_experts(None, weights, indices, self.experts, n_experts=s.n_experts,
                                          expert_begin=self.rank * self.local_experts,
-                                         x_quant=(codes, sf, gs))
+                                         x_quant=(codes, sf, gs), out=out)
         if self.w13d.fp8:
             codes, scales = ops.fused_act_quant(normed_rows)
             gate_up = ops.linear_fp8(c.all_gather_rows(codes), c.all_gather_rows(scales),
@@ -317,8 +324,8 @@ class RealisticLayer:
         inter = gate_up.shape[1] // 2
         if self.w2d.fp8:
             codes, scales = ops.fused_swiglu_quant(gate_up[:, :inter], gate_up[:, inter:])
-            return ops.linear_fp8(codes, scales, self.w2d.codes, self.w2d.scales)
-        return self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]))
+            return ops.linear_fp8(codes, scales, self.w2d.codes, self.w2d.scales, out=out)
+        return self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]), out=out)
 
     # -- the stack ----------------------------------------------------------------------------
     def forward_stack(self, hidden: torch.Tensor, positions: torch.Tensor, layers: int) -> torch.Tensor:
@@ -342,13 +349,34 @@ class RealisticLayer:
         and all-gather around the token-wise kernels (module docstring): between the two sharded
         halves of a layer a rank holds only its own T / world rows of the hidden states."""
         s, c = self.shape, self.comm
-        lo, hi = c.rows_of(hidden.shape[0])
+        tokens = hidden.shape[0]
+        lo, hi = c.rows_of(tokens)
         mine = hidden[lo:hi].contiguous()
         normed = ops.fused_rms_norm(mine, self.ones_h, eps=s.eps)
+        px = self._peer_exchange(tokens) if self.peer_reduce and hidden.is_cuda else None
         for _ in range(layers):
             qkv = c.all_gather_rows(self.w_qkv_a(normed))              # [T, 2112]: 0.3 of a hidden row
+            if px is not None:
+                # the partial sums land in buffers the other ranks have mapped; reduce-scatter,
+                # residual add and RMSNorm are ONE kernel that reads them over NVLink
+                self.attention_partial(qkv, positions, out=px.local["attn"])
+                normed, mine = px.reduce_residual_norm("attn", mine, self.ones_h, eps=s.eps)
+                self.ffn_partial_from_rows(normed, out=px.local["ffn"])
+                normed, mine = px.reduce_residual_norm("ffn", mine, self.ones_h, eps=s.eps)
+                continue
             attn = c.reduce_scatter_rows(self.attention_partial(qkv, positions))
             normed, mine = ops.fused_residual_norm(attn, mine, self.ones_h, eps=s.eps)
             ffn = c.reduce_scatter_rows(self.ffn_partial_from_rows(normed))
             normed, mine = ops.fused_residual_norm(ffn, mine, self.ones_h, eps=s.eps)
         return c.all_gather_rows(mine)
+
+    def _peer_exchange(self, tokens: int):
+        """The two [T, H] partial-sum buffers of this token count, mapped across the ranks once."""
+        from . import peer
+        px = self._peer.get(tokens)
+        if px is None:
+            shape = (tokens, self.shape.hidden)
+            px = peer.PeerExchange(self.comm, self.ones_h.device,
+                                   {"attn": (shape, torch.bfloat16), "ffn": (shape, torch.bfloat16)})
+            self._peer[tokens] = px
+        return px

@@ -138,7 +138,8 @@ def fused_moe_experts(x: Optional[torch.Tensor], weights: torch.Tensor, indices:
                       shared: Optional[torch.Tensor] = None,
                       out_dtype: torch.dtype = torch.bfloat16,
                       parts: Optional[dict] = None,
-                      x_quant: Optional[tuple] = None) -> torch.Tensor:
+                      x_quant: Optional[tuple] = None,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[t] = sum over the token's routed experts owned here of w * expert(x[t]) (+ shared[t]).
 
     x [T, hidden] bf16; weights fp32 [T, k] and indices int64 [T, k] from fused_moe_route;
@@ -188,7 +189,7 @@ def fused_moe_experts(x: Optional[torch.Tensor], weights: torch.Tensor, indices:
         parts.update(offsets=offsets, sorted_pairs=sorted_pairs, pair_pos=pair_pos, x_gs=a_gs, x_amax=x_amax,
                      gate_up=gate_up, h=h, h_amax=h_amax, expert_out=expert_out)
     return ops.fused_moe_combine(expert_out, pair_pos, weights, shared, pos_window=window,
-                                 out_dtype=out_dtype)
+                                 out_dtype=out_dtype, out=out)
 
 
 def fused_moe_forward(x: torch.Tensor, gate_weight: torch.Tensor, gate_bias: Optional[torch.Tensor],

@@ -465,7 +465,8 @@ def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights:
                       shared: Optional[torch.Tensor] = None, *, pos_begin: int = 0,
                       pos_end: Optional[int] = None,
                       pos_window: Optional[tuple] = None,
-                      out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                      out_dtype: torch.dtype = torch.bfloat16,
+                      out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """y[t] = sum_s weights[t, s] * expert_out[pair_pos[t, s]] (+ shared[t]);
     racetrack/models/deepseek.py:1018-1022. ``pos_window`` = (begin, end) as 1-element int32
     CUDA tensors (entries of expert_offsets) restricts the sum to an expert-parallel rank's
@@ -484,7 +485,7 @@ def fused_moe_combine(expert_out: torch.Tensor, pair_pos: torch.Tensor, weights:
         pos_end = tokens * topk
     if out_dtype not in (torch.bfloat16, torch.float32):
         raise RuntimeError("fused_moe_combine: out_dtype must be bfloat16 or float32")
-    y = torch.empty(tokens, cols, dtype=out_dtype, device=expert_out.device)
+    y = _out_buffer(out, (tokens, cols), out_dtype, expert_out.device)
     lib = _lib.load()
     _lib.check(lib.rt_moe_combine(expert_out.data_ptr(), pair_pos.data_ptr(), weights.data_ptr(),
                                   shared.data_ptr() if shared is not None else None, y.data_ptr(),
@@ -511,8 +512,19 @@ SPLITK_MAX_ROWS = 128          # linear_bf16 splits K for at most this many rows
 SPLITK_MIN_WEIGHT = 1 << 20    # ... against a weight matrix of at least this many elements
 
 
+def _out_buffer(out: Optional[torch.Tensor], shape: tuple, dtype: torch.dtype, device) -> torch.Tensor:
+    """The caller's output buffer when it fits (contiguous, right shape and type: e.g. a buffer
+    other ranks read over NVLink), else a fresh tensor."""
+    if out is None:
+        return torch.empty(shape, dtype=dtype, device=device)
+    if tuple(out.shape) != tuple(shape) or out.dtype != dtype or not out.is_contiguous():
+        raise RuntimeError(f"out must be a contiguous {dtype} tensor of shape {tuple(shape)}")
+    return out
+
+
 def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
-                out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+                out_dtype: torch.dtype = torch.bfloat16,
+                out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """F.linear(x, weight) for bf16 x [..., K] and weight [N, K] on the tcgen05 tensor cores
     (the bf16 branch of racetrack/models/deepseek.py:316-345 `linear`). out_dtype=torch.float32
     returns the fp32 accumulators (router logits, racetrack/models/deepseek.py:898)."""
@@ -537,14 +549,14 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
             # partial products per K range, then their sum in a fixed order: bit-reproducible,
             # and identical on every rank that forms the same replicated projection
             part = torch.empty(splits, rows, n, dtype=torch.float32, device=x.device)
-            out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
+            out = _out_buffer(out, (*x.shape[:-1], n), out_dtype, x.device)
             _lib.check(lib.rt_gemm_bf16_splitk(
                 x2.data_ptr(), w.data_ptr(), part.data_ptr(), out.data_ptr(), rows, n, k,
                 x2.stride(0), w.stride(0), n, n, splits,
                 _lib.RT_F32 if out_dtype == torch.float32 else _lib.RT_BF16, _stream()),
                 "rt_gemm_bf16_splitk")
             return out
-    out = torch.empty(*x.shape[:-1], n, dtype=out_dtype, device=x.device)
+    out = _out_buffer(out, (*x.shape[:-1], n), out_dtype, x.device)
     _lib.check(lib.rt_gemm_bf16(x2.data_ptr(), w.data_ptr(), out.data_ptr(), x2.shape[0], n, k,
                                 x2.stride(0), w.stride(0), n,
                                 _lib.RT_F32 if out_dtype == torch.float32 else _lib.RT_BF16,
@@ -599,7 +611,7 @@ def module_weight_bf16(linear) -> torch.Tensor:
 
 
 def linear_fp8(x_codes: torch.Tensor, x_scales: torch.Tensor, w_codes: torch.Tensor,
-               w_scales: torch.Tensor) -> torch.Tensor:
+               w_scales: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """FP8 block-scaled linear: fp8_gemm(a, a_s, b, b_s) of racetrack/models/deepseek.py:110-145
     -> bf16 [..., N]. x_codes / x_scales as fused_act_quant returns them."""
     _require_cuda(x_codes, x_scales, w_codes, w_scales)
@@ -615,18 +627,19 @@ def linear_fp8(x_codes: torch.Tensor, x_scales: torch.Tensor, w_codes: torch.Ten
     if xs.dtype != torch.float32 or w_scales.dtype != torch.float32 \
             or w_scales.shape != ((n + 127) // 128, k // 128):
         raise RuntimeError("linear_fp8: scales must be fp32 [M, K/128] and [ceil(N/128), K/128]")
-    out = torch.empty(*x_codes.shape[:-1], n, dtype=torch.bfloat16, device=x_codes.device)
+    out = _out_buffer(out, (*x_codes.shape[:-1], n), torch.bfloat16, x_codes.device)
     lib = _lib.load()
     _lib.check(lib.rt_gemm_fp8(xc.data_ptr(), xs.data_ptr(), w_codes.data_ptr(), w_scales.data_ptr(),
                                out.data_ptr(), xc.shape[0], n, k, k, k, n, _stream()), "rt_gemm_fp8")
     return out
 
 
-def linear_fp8_act(x: torch.Tensor, w_codes: torch.Tensor, w_scales: torch.Tensor) -> torch.Tensor:
+def linear_fp8_act(x: torch.Tensor, w_codes: torch.Tensor, w_scales: torch.Tensor,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """`linear(x, weight)` with an FP8 weight as racetrack/models/deepseek.py:343-345 runs it:
     act_quant(x) then the FP8 block-scaled GEMM."""
     codes, scales = fused_act_quant(x)
-    return linear_fp8(codes, scales, w_codes, w_scales)
+    return linear_fp8(codes, scales, w_codes, w_scales, out=out)
 
 
 def moe_tile_map(offsets: torch.Tensor, g_begin: int, g_end: int, max_tiles: int):
