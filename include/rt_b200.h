@@ -603,8 +603,23 @@ int rt_attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, 
 /* ------------------------------------------------------------------------ */
 
 /*
+ * Exchange buffers of a rank group. rt_peer_alloc: `bytes` of zeroed device memory on the
+ * current device (cudaMalloc) and its 64-byte CUDA IPC handle; the handle travels to the other
+ * ranks by any host channel. rt_peer_open: maps a peer's buffer into this process WITH THE
+ * CALLER'S OWN DEVICE CURRENT and returns a pointer kernels of that device may dereference
+ * (peer access over NVLink). rt_peer_close unmaps it, rt_peer_free releases an own buffer
+ * (after every peer has closed it). Set-up time calls: they allocate and synchronise.
+ * ref: none in racetrack (its collectives are torch.distributed calls); the buffers replace the
+ * NCCL staging of the all-reduces at racetrack/realistic_bench.py:315-316,351.
+ */
+int rt_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle_out);
+int rt_peer_open(const unsigned char* handle, void** ptr);
+int rt_peer_close(void* ptr);
+int rt_peer_free(void* ptr);
+
+/*
  * Device-side barrier of `world` ranks (<= 8). flag_ptrs[q] is rank q's flag array (int32
- * [world + 1], zero at start) as mapped into THIS process (CUDA IPC; flag_ptrs[rank] is the
+ * [world + 1], zero at start) as mapped into THIS process (rt_peer_open; flag_ptrs[rank] is the
  * local one). The kernel counts its own barriers in the last slot of the local array, stores
  * that count into slot `rank` of every rank's array and waits until all slots of its own array
  * have reached it; every rank must call the barrier the same number of times. What a rank

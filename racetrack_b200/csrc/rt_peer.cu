@@ -15,6 +15,8 @@
 //                              fp32, rounded to bf16 like the all-reduced tensor, then residual
 //                              add + RMSNorm exactly as residual_norm_kernel does. The summed
 //                              tensor never exists in memory.
+#include <string.h>
+
 #include "rt_common.cuh"
 
 namespace rt {
@@ -33,7 +35,7 @@ struct PeerFlagPtrs {
 // flags: int32 [world + 1] in every rank's memory; slot r of rank q is written by rank r only,
 // slot `world` is the rank's own count of barriers passed (kept on the device, so a barrier
 // replayed from a CUDA graph takes the next step like an eagerly launched one).
-__global__ void peer_barrier_kernel(PeerFlagPtrs flags, int rank, int world, long long max_spins) {
+__global__ void peer_barrier_kernel(PeerFlagPtrs flags, int rank, int world, long long max_cycles) {
     __shared__ int step_s;
     if (threadIdx.x == 0) step_s = ++flags.p[rank][world];
     __syncthreads();
@@ -44,12 +46,12 @@ __global__ void peer_barrier_kernel(PeerFlagPtrs flags, int rank, int world, lon
     __threadfence_system();
     asm volatile("st.release.sys.global.s32 [%0], %1;" ::"l"(flags.p[peer] + rank), "r"(step) : "memory");
     const int* mine = flags.p[rank] + peer;
-    long long spins = 0;
+    const long long t0 = clock64();
     while (true) {
         int v;
         asm volatile("ld.acquire.sys.global.s32 %0, [%1];" : "=r"(v) : "l"(mine) : "memory");
         if (v >= step) break;
-        if (++spins > max_spins) {            // a peer never arrived: report instead of hanging
+        if (clock64() - t0 > max_cycles) {    // a peer never arrived: report instead of hanging
             atomicCAS(&g_peer_error, 0, 100 + peer);
             break;
         }
@@ -124,14 +126,69 @@ __global__ void __launch_bounds__(512) peer_reduce_norm_kernel(
 
 using namespace rt;
 
+// Exchange buffers are plain cudaMalloc allocations of the calling process's current device,
+// exported with cudaIpcGetMemHandle and opened by the other ranks WITH THEIR OWN DEVICE CURRENT
+// (cudaIpcMemLazyEnablePeerAccess then enables the peer mapping for that device), so a kernel on
+// a rank's GPU may dereference the returned pointer directly.
+extern "C" int rt_peer_alloc(int64_t bytes, void** ptr, unsigned char* handle_out) {
+    RT_REQUIRE(bytes > 0 && ptr && handle_out, RT_ERR_BAD_ARG, "rt_peer_alloc: bad arguments");
+    void* p = nullptr;
+    RT_REQUIRE(cudaMalloc(&p, static_cast<size_t>(bytes)) == cudaSuccess, RT_ERR_CUDA,
+               "rt_peer_alloc: cudaMalloc of %lld bytes failed", (long long)bytes);
+    if (cudaMemset(p, 0, static_cast<size_t>(bytes)) != cudaSuccess || cudaDeviceSynchronize() != cudaSuccess) {
+        cudaFree(p);
+        return fail(RT_ERR_CUDA, "rt_peer_alloc: cannot clear the buffer");
+    }
+    cudaIpcMemHandle_t h;
+    if (cudaIpcGetMemHandle(&h, p) != cudaSuccess) {
+        cudaGetLastError();
+        cudaFree(p);
+        return fail(RT_ERR_CUDA, "rt_peer_alloc: cudaIpcGetMemHandle failed");
+    }
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handles travel as 64 bytes");
+    memcpy(handle_out, &h, 64);
+    *ptr = p;
+    return RT_OK;
+}
+
+extern "C" int rt_peer_open(const unsigned char* handle, void** ptr) {
+    RT_REQUIRE(handle && ptr, RT_ERR_BAD_ARG, "rt_peer_open: null pointer");
+    cudaIpcMemHandle_t h;
+    memcpy(&h, handle, 64);
+    void* p = nullptr;
+    const cudaError_t e = cudaIpcOpenMemHandle(&p, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RT_ERR_CUDA, "rt_peer_open: cudaIpcOpenMemHandle failed: %s", cudaGetErrorString(e));
+    }
+    *ptr = p;
+    return RT_OK;
+}
+
+extern "C" int rt_peer_close(void* ptr) {
+    if (ptr && cudaIpcCloseMemHandle(ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RT_ERR_CUDA, "rt_peer_close: cudaIpcCloseMemHandle failed");
+    }
+    return RT_OK;
+}
+
+extern "C" int rt_peer_free(void* ptr) {
+    if (ptr && cudaFree(ptr) != cudaSuccess) {
+        cudaGetLastError();
+        return fail(RT_ERR_CUDA, "rt_peer_free: cudaFree failed");
+    }
+    return RT_OK;
+}
+
 extern "C" int rt_peer_barrier(int* const* flag_ptrs, int64_t rank, int64_t world, void* stream) {
     RT_REQUIRE(flag_ptrs && world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world,
                RT_ERR_BAD_ARG, "rt_peer_barrier: bad arguments (at most %d ranks)", kMaxPeers);
     PeerFlagPtrs f;
     for (int q = 0; q < kMaxPeers; ++q) f.p[q] = q < world ? flag_ptrs[q] : nullptr;
     for (int q = 0; q < world; ++q) RT_REQUIRE(f.p[q], RT_ERR_BAD_ARG, "rt_peer_barrier: null flag pointer");
-    // about two seconds of polling at 64 ns per sleep, then the error flag
-    peer_barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(f, (int)rank, (int)world, 20000000LL);
+    // 3e9 SM cycles (about two seconds) of polling, then the error flag
+    peer_barrier_kernel<<<1, 32, 0, as_stream(stream)>>>(f, (int)rank, (int)world, 3000000000LL);
     count_launch();
     return check_launch("peer_barrier_kernel");
 }

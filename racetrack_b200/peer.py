@@ -8,6 +8,10 @@ plain loads over NVLink / NVSwitch: the reduce-scatter half of the reference's a
 (rt_peer_reduce_residual_norm), after a device-side barrier (rt_peer_barrier). No multicast
 object and no tensor map ever covers another GPU's memory.
 
+The buffers are cudaMalloc allocations of this library (rt_peer_alloc), not torch storage: a peer
+opens them with its own device current (rt_peer_open), which is what lets kernels on that device
+dereference the mapping; torch sees the local ones as tensors through __cuda_array_interface__.
+
 Order of use for one exchange, on every rank and on one stream:
     write the local buffer  ->  barrier()  ->  read the peers' buffers
 A buffer may be rewritten after the NEXT barrier of the group (by then every rank has finished
@@ -24,34 +28,84 @@ import torch.distributed as dist
 from . import _lib, comm, ops
 
 
+class _RawCuda:
+    """A device allocation of this library exposed through __cuda_array_interface__, so that torch
+    can view it as a tensor without copying."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False),
+                                         "version": 3, "strides": None}
+
+
+def _as_tensor(ptr: int, shape: tuple, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    nbytes = int(torch.empty((), dtype=dtype).element_size())
+    for d in shape:
+        nbytes *= int(d)
+    raw = torch.as_tensor(_RawCuda(ptr, nbytes), device=device)
+    return raw.view(dtype).view(shape)
+
+
 class PeerExchange:
     def __init__(self, group: comm.Group, device: torch.device, buffers: dict[str, tuple]):
         """buffers: name -> (shape, dtype) of the local tensor every rank allocates."""
-        from torch.multiprocessing.reductions import reduce_tensor
         if group.world > 8:
             raise RuntimeError("peer exchange supports at most 8 ranks")
-        self.group, self.rank, self.world = group, group.rank, group.world
-        self.local = {name: torch.empty(shape, dtype=dtype, device=device)
-                      for name, (shape, dtype) in buffers.items()}
-        self.flags = torch.zeros(self.world + 1, dtype=torch.int32, device=device)
-        torch.cuda.synchronize(device)
-        exported = {name: reduce_tensor(t) for name, t in {**self.local, "__flags__": self.flags}.items()}
-        gathered = [None] * self.world
-        dist.all_gather_object(gathered, exported, group=group.group)
-        self.views: dict[str, list[torch.Tensor]] = {}
-        for name in exported:
-            views = []
-            for q in range(self.world):
-                if q == self.rank:
-                    views.append(self.flags if name == "__flags__" else self.local[name])
-                else:
-                    rebuild, args = gathered[q][name]
-                    views.append(rebuild(*args))
-            self.views[name] = views
-        self._ptrs = {name: (ctypes.c_void_p * self.world)(*[v.data_ptr() for v in views])
-                      for name, views in self.views.items()}
+        self.group, self.rank, self.world, self.device = group, group.rank, group.world, device
+        lib = _lib.load()
+        specs = {**buffers, "__flags__": ((self.world + 1,), torch.int32)}
+        self._own: dict[str, int] = {}
+        handles: dict[str, bytes] = {}
+        self.local: dict[str, torch.Tensor] = {}
+        with torch.cuda.device(device):
+            for name, (shape, dtype) in specs.items():
+                nbytes = int(torch.empty((), dtype=dtype).element_size())
+                for d in shape:
+                    nbytes *= int(d)
+                ptr, handle = ctypes.c_void_p(), (ctypes.c_ubyte * 64)()
+                _lib.check(lib.rt_peer_alloc(max(nbytes, 16), ctypes.byref(ptr), handle), "rt_peer_alloc")
+                self._own[name] = ptr.value
+                handles[name] = bytes(handle)
+                self.local[name] = _as_tensor(ptr.value, tuple(shape), dtype, device)
+            gathered = [handles]
+            if self.world > 1:
+                gathered = [None] * self.world
+                dist.all_gather_object(gathered, handles, group=group.group)
+            # a peer's buffer is opened with THIS rank's device current: the mapping (and the
+            # NVLink peer access behind it) then belongs to the device whose kernels will use it
+            self._mapped: dict[str, list[int]] = {}
+            for name in specs:
+                ptrs = []
+                for q in range(self.world):
+                    if q == self.rank:
+                        ptrs.append(self._own[name])
+                        continue
+                    ptr = ctypes.c_void_p()
+                    buf = (ctypes.c_ubyte * 64).from_buffer_copy(gathered[q][name])
+                    _lib.check(lib.rt_peer_open(buf, ctypes.byref(ptr)), "rt_peer_open")
+                    ptrs.append(ptr.value)
+                self._mapped[name] = ptrs
+        self.flags = self.local.pop("__flags__")
+        self._ptrs = {name: (ctypes.c_void_p * self.world)(*ptrs) for name, ptrs in self._mapped.items()}
         # every rank has mapped every buffer before anyone uses them
-        dist.barrier(group=group.group)
+        if self.world > 1:
+            dist.barrier(group=group.group)
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers and, once every rank has done so, frees the own ones."""
+        if not self._own:
+            return
+        lib = _lib.load()
+        torch.cuda.synchronize(self.device)
+        with torch.cuda.device(self.device):
+            for name, ptrs in self._mapped.items():
+                for q, ptr in enumerate(ptrs):
+                    if q != self.rank:
+                        lib.rt_peer_close(ctypes.c_void_p(ptr))
+            if self.world > 1:
+                dist.barrier(group=self.group.group)
+            for ptr in self._own.values():
+                lib.rt_peer_free(ctypes.c_void_p(ptr))
+        self._own, self._mapped, self.local = {}, {}, {}
 
     def barrier(self) -> None:
         """All ranks' work enqueued before this call (on the current stream of each) is complete

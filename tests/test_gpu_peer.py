@@ -1,0 +1,103 @@
+"""The collective steps over NVLink peer memory (racetrack_b200/peer.py, rt_peer_*): the
+reduce-scatter of the reference's all-reduce (racetrack/realistic_bench.py:315-316,351) fused with
+residual add + RMSNorm, and the device-side barrier in front of it.
+
+One rank: the fused kernel must equal rt_residual_norm bit for bit. Two ranks (skipped on a
+single-GPU box): two processes over NCCL map each other's buffers; every rank's rows must equal
+fused_residual_norm of the bf16-rounded fp32 sum of the two partial tensors, and a barrier whose
+partner never arrives must report a timeout instead of hanging."""
+from __future__ import annotations
+
+import os
+import socket
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def test_single_rank_reduce_equals_residual_norm():
+    from racetrack_b200 import comm, ops, peer
+    g = torch.Generator().manual_seed(2)
+    tokens, hidden = 37, 7168
+    part = torch.randn(tokens, hidden, generator=g).bfloat16().cuda()
+    res = torch.randn(tokens, hidden, generator=g).bfloat16().cuda()
+    w = (1 + 0.02 * torch.randn(hidden, generator=g)).cuda()
+    px = peer.PeerExchange(comm.Group(), torch.device("cuda", 0), {"attn": ((tokens, hidden), torch.bfloat16)})
+    px.local["attn"].copy_(part)
+    for _ in range(2):                                  # the barrier counts its own steps
+        normed, summed = px.reduce_residual_norm("attn", res, w, eps=1e-6)
+        px.check()
+        want_n, want_h = ops.fused_residual_norm(part, res, w, eps=1e-6)
+        assert torch.equal(normed, want_n) and torch.equal(summed, want_h)
+    assert int(px.flags[1]) == 2 and int(px.flags[0]) == 2
+    px.close()
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _two_ranks(rank: int, world: int, port: int, out_dir: str):
+    import torch.distributed as dist
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from racetrack_b200 import comm, ops, peer
+        tokens, hidden = 64, 7168
+        g = torch.Generator().manual_seed(11)
+        parts = [torch.randn(tokens, hidden, generator=g).bfloat16() for _ in range(world)]
+        res = torch.randn(tokens, hidden, generator=g).bfloat16()
+        w = torch.ones(hidden, device=dev)
+        grp = comm.Group(rank, world)
+        px = peer.PeerExchange(grp, dev, {"attn": ((tokens, hidden), torch.bfloat16),
+                                          "ffn": ((tokens, hidden), torch.bfloat16)})
+        lo, hi = grp.rows_of(tokens)
+        ok = True
+        for name in ("attn", "ffn", "attn"):
+            px.local[name].copy_(parts[rank].to(dev))
+            normed, summed = px.reduce_residual_norm(name, res[lo:hi].to(dev), w, eps=1e-6)
+            px.check()
+            total = (parts[0].float() + parts[1].float()).bfloat16()[lo:hi].to(dev)
+            want_n, want_h = ops.fused_residual_norm(total, res[lo:hi].to(dev), w, eps=1e-6)
+            ok = ok and torch.equal(normed, want_n) and torch.equal(summed, want_h)
+        # and the NCCL path of the same step gives the same rows
+        rs = grp.reduce_scatter_rows(parts[rank].to(dev))
+        ok = ok and torch.equal(rs, (parts[0].float() + parts[1].float()).bfloat16()[lo:hi].to(dev))
+        # a partner that never arrives: rank 1 skips this barrier, rank 0 must get a timeout
+        # status (about two seconds) and keep a usable context; then both realign
+        timed_out = None
+        if rank == 0:
+            px.barrier()
+            try:
+                px.check()
+                timed_out = False
+            except RuntimeError as e:
+                timed_out = "gave up waiting" in str(e)
+        dist.barrier()
+        if rank == 1:
+            px.barrier()                                # catches up: its step is now rank 0's
+            px.check()
+        dist.barrier()
+        normed, _ = px.reduce_residual_norm("ffn", res[lo:hi].to(dev), w, eps=1e-6)
+        px.check()
+        torch.save({"ok": bool(ok), "timed_out": timed_out, "finite": bool(torch.isfinite(normed.float()).all())},
+                   f"{out_dir}/rank{rank}.pt")
+        px.close()
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_ranks_reduce_over_peer_memory(tmp_path):
+    import torch.multiprocessing as mp
+    mp.spawn(_two_ranks, args=(2, _free_port(), str(tmp_path)), nprocs=2, join=True)
+    r0, r1 = (torch.load(tmp_path / f"rank{r}.pt") for r in range(2))
+    assert r0["ok"] and r1["ok"]
+    assert r0["timed_out"] is True, "a barrier without its partner must report a timeout"
+    assert r0["finite"] and r1["finite"]
