@@ -389,6 +389,19 @@ int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, int64_t n, in
                  int64_t lda, int64_t ldb, int64_t ldc, int out_dtype, void* stream);
 
 /*
+ * `batch` independent products c[i] = a[i] . b[i]^T of one shape in one launch: a[i] is [m, k] at
+ * a + i * a_batch_stride (row pitch lda), b[i] is [n, k] at b + i * b_batch_stride (row pitch
+ * ldb), c[i] is [m, n] bf16 at c + i * c_batch_stride (row pitch ldc); all bf16, strides in
+ * elements (multiples of 8), so the operands may be per-head slices of [tokens, heads, dim]
+ * tensors. The per-head absorbed projections of the MLA decode branch:
+ * ref: racetrack/models/deepseek.py:799 (einsum "bshd,hdc->bshc" of q_nope with wkv_b[:, :nope]),
+ *      :810 (einsum "bshc,hdc->bshd" of the attention output with wkv_b[:, -v_head_dim:]).
+ */
+int rt_gemm_bf16_batched(const void* a, const void* b, void* c, int64_t batch, int64_t m, int64_t n,
+                         int64_t k, int64_t lda, int64_t a_batch_stride, int64_t ldb,
+                         int64_t b_batch_stride, int64_t ldc, int64_t c_batch_stride, void* stream);
+
+/*
  * The same product for FEW rows (decode: m up to a few dozen tokens), where a projection has too
  * few output tiles to occupy the GPU although its whole weight matrix must be streamed: the K
  * range is cut into `splits` pieces, work item (tile, split) stores its partial product into

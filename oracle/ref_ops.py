@@ -520,3 +520,70 @@ def moe_experts_nvfp4(x, weights, indices, w13, w2, shared_out=None, expert_rang
     if shared_out is not None:
         y = y + shared_out.float()
     return y.to(torch.bfloat16)
+
+
+# ---------------------------------------------------------------------------
+# MLA prologue ops of the dsv3_2_nvfp4 partitions (torch definitions the partitions fall back to)
+# ---------------------------------------------------------------------------
+def fused_ar_rms_qkv_proj(x, residual, norm_weight, wq_a_weight, wkv_a_weight, indexer_wk_weight, *,
+                          eps, q_lora_rank, kv_lora_rank, qk_rope_head_dim):
+    """Residual add + RMSNorm, the fused q_a / kv_a projection and the indexer's key projection.
+    Returns (residual_out, normed, q_c, kv_c, k_pe, indexer_k).
+    ref: scripts/recipes_nvfp4.py:38-66."""
+    hidden = x.float() + residual.float() if residual is not None else x.float()
+    var = hidden.square().mean(dim=-1, keepdim=True)
+    normed = (norm_weight.float() * hidden * torch.rsqrt(var + eps)).to(x.dtype)
+    qkv = F.linear(normed, torch.cat([wq_a_weight, wkv_a_weight], dim=0))
+    total = q_lora_rank + kv_lora_rank + qk_rope_head_dim
+    return (hidden.to(x.dtype), normed, qkv[..., :q_lora_rank],
+            qkv[..., q_lora_rank:q_lora_rank + kv_lora_rank],
+            qkv[..., q_lora_rank + kv_lora_rank:total], F.linear(normed, indexer_wk_weight))
+
+
+def fused_indexer_k_path(k, ln_weight, ln_bias, freqs_cis, k_cache, k_scale_cache, *, ln_eps,
+                         rope_head_dim, start_pos):
+    """Indexer key path: LayerNorm, non-interleaved RoPE, Hadamard rotation, FP8 quantisation and
+    the cache append. k [bsz, seqlen, 128]; freqs_cis complex [seqlen, rope/2]. Returns (k_fp8,
+    k_scale [bsz, seqlen, 1]). ref: scripts/recipes_nvfp4.py:68-94."""
+    bsz, seqlen, dim = k.shape
+    codes, scales = [], []
+    for b in range(bsz):
+        c, s, _ = index_prep(k[b].unsqueeze(1), freqs_cis, rope_dim=rope_head_dim, ln_weight=ln_weight,
+                             ln_bias=ln_bias, eps=ln_eps)
+        codes.append(c.squeeze(1))
+        scales.append(s)
+    k_fp8, k_scale = torch.stack(codes), torch.stack(scales)
+    k_cache[:bsz, start_pos:start_pos + seqlen] = k_fp8.to(k_cache.dtype)
+    k_scale_cache[:bsz, start_pos:start_pos + seqlen] = k_scale.view(bsz, seqlen, *k_scale_cache.shape[2:])
+    return k_fp8, k_scale
+
+
+def fused_q_indexer_score(qr, normed_x, wq_b_weight, idx_wq_b_weight, idx_weights_proj_weight, wkv_b_weight,
+                          freqs_cis, k_cache, k_scale_cache, *, n_heads, qk_head_dim, qk_nope_head_dim,
+                          kv_lora_rank, idx_n_heads, idx_head_dim, rope_head_dim, idx_softmax_scale,
+                          index_topk, end_pos):
+    """Query projection, absorbed nope query, indexer query path, index scores and top-k.
+    Returns (q_nope, q_nope_absorbed, q_pe, topk_indices). ref: scripts/recipes_nvfp4.py:96-140."""
+    bsz, seqlen, _ = qr.shape
+    q = F.linear(qr, wq_b_weight).view(bsz, seqlen, n_heads, qk_head_dim)
+    q_nope, q_pe = torch.split(q, [qk_nope_head_dim, qk_head_dim - qk_nope_head_dim], dim=-1)
+    wkv_b = wkv_b_weight.view(n_heads, -1, kv_lora_rank)
+    q_abs = torch.einsum("bshd,hdc->bshc", q_nope, wkv_b[:, :qk_nope_head_dim])
+    idx_q = F.linear(qr, idx_wq_b_weight).view(bsz, seqlen, idx_n_heads, idx_head_dim)
+    codes, scales = [], []
+    for b in range(bsz):
+        c, s, _ = index_prep(idx_q[b], freqs_cis, rope_dim=rope_head_dim)
+        codes.append(c)
+        scales.append(s)
+    q_fp8, q_scale = torch.stack(codes), torch.stack(scales)             # [b, s, h, d], [b, s, h]
+    weights = F.linear(normed_x.float(), idx_weights_proj_weight.float()) * idx_n_heads ** -0.5
+    weights = weights * q_scale * idx_softmax_scale
+    k_s = k_scale_cache[:bsz, :end_pos].reshape(bsz, end_pos).contiguous()
+    k_cached = k_cache[:bsz, :end_pos].contiguous()
+    score = fp8_index(q_fp8, weights, k_cached, k_s)
+    return q_nope, q_abs, q_pe, score.topk(min(index_topk, end_pos), dim=-1)[1]
+
+
+def fused_q_rope_quant(q_pe, freqs_cis):
+    """Interleaved RoPE of the query's rope part. ref: scripts/recipes_nvfp4.py:142-151."""
+    return apply_rotary_emb(q_pe, freqs_cis, True)

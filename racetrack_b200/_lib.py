@@ -46,6 +46,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_moe_quant_nvfp4": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _I, _P]),
     "rt_moe_gather_nvfp4": (_I, [_P, _P, _P, _L, _P, _P, _P, _P, _L, _L, _P]),
     "rt_gemm_bf16": (_I, [_P, _P, _P, _L, _L, _L, _L, _L, _L, _I, _P]),
+    "rt_gemm_bf16_batched": (_I, [_P, _P, _P] + [_L] * 10 + [_P]),
     "rt_gemm_bf16_splitk_splits": (_L, [_L, _L, _L]),
     "rt_gemm_bf16_splitk": (_I, [_P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _L, _L, _I, _P]),
     "rt_gemm_fp8": (_I, [_P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),

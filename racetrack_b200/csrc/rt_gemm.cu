@@ -54,12 +54,17 @@ __device__ __forceinline__ void tile_coords(int tile, int num_m, int num_n, int&
 // slabs in split order, so the result does not depend on which SM finished first. A projection
 // of a few dozen decode tokens has too few output tiles to occupy the GPU, while its weight
 // matrix is what has to be streamed.
-template <int BN, bool F32OUT, bool SPLITK = false>
+// BATCHED: `batch` independent products of the same shape in one launch (the per-head absorbed
+// projections of MLA: q_nope . W_UK and latent . W_UV, racetrack/models/deepseek.py:799,810): the
+// tensor maps are 3-D {K, rows, batch}, a work item is (batch, m-tile, n-tile) and c advances
+// by c_batch_stride elements per batch.
+template <int BN, bool F32OUT, bool SPLITK = false, bool BATCHED = false>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
     const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
     void* __restrict__ c_out, int M, int N, int K, int64_t ldc, int k_splits_arg = 1,
-    int64_t split_stride = 0) {
+    int64_t split_stride = 0, int batch = 1, int64_t c_batch_stride = 0) {
     static_assert(!SPLITK || F32OUT, "split-K accumulates into an fp32 output");
+    static_assert(!(SPLITK && BATCHED), "one or the other");
     using Cfg = GemmCfg<BN>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
@@ -77,7 +82,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_m = (M + kBM - 1) / kBM, num_n = (N + BN - 1) / BN;
     const int k_splits = SPLITK ? k_splits_arg : 1;
-    const int num_tiles = num_m * num_n * k_splits;         // work items
+    const int tiles_per_batch = num_m * num_n;
+    const int num_tiles = tiles_per_batch * k_splits * (BATCHED ? batch : 1);         // work items
     const int num_kb_all = (K + kBK - 1) / kBK;
     const int kb_per = (num_kb_all + k_splits - 1) / k_splits;
 
@@ -111,14 +117,20 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
             bool ok = true;
             for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
                 int tm, tn;
-                tile_coords(tile / k_splits, num_m, num_n, tm, tn);
+                const int bidx = BATCHED ? tile / tiles_per_batch : 0;
+                tile_coords(BATCHED ? tile % tiles_per_batch : tile / k_splits, num_m, num_n, tm, tn);
                 const int kb0 = (tile % k_splits) * kb_per, kb1 = min(num_kb_all, kb0 + kb_per);
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!(ok = mbar_wait(empty_bar(stage), phase ^ 1u, abort_flag, 1))) break;
                     const uint32_t sa = base + stage * Cfg::kStageBytes;
                     mbar_arrive_expect_tx(full_bar(stage), Cfg::kStageBytes);
-                    tma_load_2d(sa, &tmap_a, kb * kBK, tm * kBM, full_bar(stage));
-                    tma_load_2d(sa + Cfg::kABytes, &tmap_b, kb * kBK, tn * BN, full_bar(stage));
+                    if constexpr (BATCHED) {
+                        tma_load_3d(sa, &tmap_a, kb * kBK, tm * kBM, bidx, full_bar(stage));
+                        tma_load_3d(sa + Cfg::kABytes, &tmap_b, kb * kBK, tn * BN, bidx, full_bar(stage));
+                    } else {
+                        tma_load_2d(sa, &tmap_a, kb * kBK, tm * kBM, full_bar(stage));
+                        tma_load_2d(sa + Cfg::kABytes, &tmap_b, kb * kBK, tn * BN, full_bar(stage));
+                    }
                     if (++stage == Cfg::kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -173,12 +185,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_bf16_kernel(
         bool ok = true;
         for (int tile = blockIdx.x; ok && tile < num_tiles; tile += gridDim.x) {
             int tm, tn;
-            tile_coords(tile / k_splits, num_m, num_n, tm, tn);
+            const int bidx = BATCHED ? tile / tiles_per_batch : 0;
+            tile_coords(BATCHED ? tile % tiles_per_batch : tile / k_splits, num_m, num_n, tm, tn);
             if (!(ok = mbar_wait(tfull_bar(acc), acc_phase, abort_flag, 4))) break;
             tc_fence_after();
             const int row = tm * kBM + quad * 32 + lane;
-            __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(c_out) + static_cast<int64_t>(row) * ldc;
-            float* crow_f = static_cast<float*>(c_out) + static_cast<int64_t>(row) * ldc +
+            const int64_t c_off = static_cast<int64_t>(row) * ldc + static_cast<int64_t>(bidx) * c_batch_stride;
+            __nv_bfloat16* crow = static_cast<__nv_bfloat16*>(c_out) + c_off;
+            float* crow_f = static_cast<float*>(c_out) + c_off +
                             (SPLITK ? static_cast<int64_t>(tile % k_splits) * split_stride : 0);
 #pragma unroll 1
             for (int chunk = 0; chunk < BN / 32; ++chunk) {
@@ -1777,6 +1791,42 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
     }
 }
 
+// 3-D bf16 operand {K, rows, batch} with box {64, box_rows, 1}.
+static int make_tmap_bf16_batched(CUtensorMap* map, const void* ptr, uint64_t k, uint64_t rows, uint64_t batch,
+                                  uint64_t pitch_bytes, uint64_t batch_pitch_bytes, uint32_t box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    RT_REQUIRE(fn, RT_ERR_CUDA, "cuTensorMapEncodeTiled is not available from this driver");
+    const cuuint64_t dims[3] = {k, rows, batch};
+    const cuuint64_t strides[2] = {pitch_bytes, batch_pitch_bytes};
+    const cuuint32_t box[3] = {static_cast<cuuint32_t>(kBK), box_rows, 1};
+    const cuuint32_t estr[3] = {1, 1, 1};
+    const CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(ptr), dims, strides, box,
+                          estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                          CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    RT_REQUIRE(r == CUDA_SUCCESS, RT_ERR_CUDA, "cuTensorMapEncodeTiled (batched) failed with CUresult %d",
+               static_cast<int>(r));
+    return RT_OK;
+}
+
+static int launch_bf16_batched(const void* a, const void* b, void* c, int64_t batch, int64_t M, int64_t N,
+                               int64_t K, int64_t lda, int64_t a_bs, int64_t ldb, int64_t b_bs, int64_t ldc,
+                               int64_t c_bs, cudaStream_t st) {
+    using Cfg = GemmCfg<128>;
+    CUtensorMap ta, tb;
+    if (int rc = make_tmap_bf16_batched(&ta, a, K, M, batch, lda * 2, a_bs * 2, kBM)) return rc;
+    if (int rc = make_tmap_bf16_batched(&tb, b, K, N, batch, ldb * 2, b_bs * 2, 128)) return rc;
+    if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&gemm_bf16_kernel<128, false, false, true>),
+                                     static_cast<int>(Cfg::kSmemBytes), "rt_gemm_bf16_batched"))
+        return rc;
+    const int64_t items = ((M + kBM - 1) / kBM) * ((N + 127) / 128) * batch;
+    const int grid = static_cast<int>(items < sm_count() ? items : sm_count());
+    gemm_bf16_kernel<128, false, false, true><<<grid, kGemmThreads, Cfg::kSmemBytes, st>>>(
+        ta, tb, c, static_cast<int>(M), static_cast<int>(N), static_cast<int>(K), ldc, 1, 0,
+        static_cast<int>(batch), c_bs);
+    count_launch();
+    return check_launch("gemm_bf16_kernel<batched>");
+}
+
 // Split-K launch of the 128 x 128 tiling: partial products into the workspace slabs, then the
 // ordered sum into `out`.
 static int launch_bf16_splitk(const void* a, const void* b, float* c, void* out, int out_dtype,
@@ -2118,6 +2168,24 @@ extern "C" int rt_gemm_bf16(const void* a, const void* b, void* c, int64_t m, in
     }
     if (n <= 128) return tc::launch_bf16<128, false>(a, b, c, m, n, k, lda, ldb, ldc, st);
     return tc::launch_bf16<256, false>(a, b, c, m, n, k, lda, ldb, ldc, st);
+}
+
+extern "C" int rt_gemm_bf16_batched(const void* a, const void* b, void* c, int64_t batch, int64_t m,
+                                    int64_t n, int64_t k, int64_t lda, int64_t a_batch_stride, int64_t ldb,
+                                    int64_t b_batch_stride, int64_t ldc, int64_t c_batch_stride, void* stream) {
+    RT_REQUIRE(batch >= 0 && m >= 0 && n > 0 && k > 0, RT_ERR_BAD_ARG, "rt_gemm_bf16_batched: bad shape");
+    if (batch == 0 || m == 0) return RT_OK;
+    RT_REQUIRE(a && b && c, RT_ERR_BAD_ARG, "rt_gemm_bf16_batched: null pointer");
+    RT_REQUIRE(k % 8 == 0 && n % 8 == 0 && lda % 8 == 0 && ldb % 8 == 0 && ldc % 8 == 0 &&
+                   a_batch_stride % 8 == 0 && b_batch_stride % 8 == 0 && c_batch_stride % 8 == 0,
+               RT_ERR_UNSUPPORTED, "rt_gemm_bf16_batched: k, n and every stride must be multiples of 8");
+    RT_REQUIRE(aligned16(a) && aligned16(b) && aligned16(c), RT_ERR_UNSUPPORTED,
+               "rt_gemm_bf16_batched: pointers must be 16-byte aligned");
+    RT_REQUIRE(m < (1LL << 31) && n < (1LL << 31) && k < (1LL << 31) && batch < (1LL << 20) &&
+                   ((m + 127) / 128) * ((n + 127) / 128) * batch < (1LL << 31),
+               RT_ERR_UNSUPPORTED, "rt_gemm_bf16_batched: dimension too large");
+    return tc::launch_bf16_batched(a, b, c, batch, m, n, k, lda, a_batch_stride, ldb, b_batch_stride, ldc,
+                                   c_batch_stride, as_stream(stream));
 }
 
 extern "C" int64_t rt_gemm_bf16_splitk_splits(int64_t m, int64_t n, int64_t k) {

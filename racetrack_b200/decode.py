@@ -8,9 +8,9 @@ sequence, attention runs over those rows only (ops.mla_sparse_decode, tcgen05), 
 of wkv_b and wo follow, and the head-parallel partial sums are all-reduced. The feed-forward
 half is the routed NVFP4 expert MLP of racetrack_b200.layer, expert-parallel.
 
-The two absorbed projections are batched per-head matmuls of a [B, 128] by [128, 512] shape
-(torch.bmm); every other step is a kernel of this library. Nothing reads device data back to
-the host, so a step can be captured in a CUDA graph.
+The two absorbed projections are per-head products of a [B, 128] by [128, 512] shape, all heads
+in one launch of the batched bf16 GEMM (ops.linear_bf16_batched). Nothing reads device data back
+to the host, so a step can be captured in a CUDA graph.
 """
 from __future__ import annotations
 
@@ -84,8 +84,9 @@ class DecodeLayer(RealisticLayer):
                          process_group=process_group)
         s, h = shape, self.local_heads
         wkv = weights["w_kv_b"].view(h, s.nope + s.v_dim, s.kv_lora)
-        self.w_uk = wkv[:, :s.nope].contiguous()                  # [h, nope, kv_lora]
-        self.w_uv_t = wkv[:, s.nope:].transpose(1, 2).contiguous()    # [h, kv_lora, v]
+        # per-head operands of the two absorbed projections, K-major for the batched GEMM
+        self.w_uk_t = wkv[:, :s.nope].transpose(1, 2).contiguous()    # [h, kv_lora, nope]: q_nope -> latent
+        self.w_uv = wkv[:, s.nope:].contiguous()                       # [h, v, kv_lora]: latent -> v
         self.index_weights, self.caches, self.index_topk = index_weights, caches, index_topk
         self.softmax_scale = s.qk_dim ** -0.5
         self.freqs = rope_table(s.rope, caches.kv.shape[1], s.rope_base, weights["w_qkv_a"].device)
@@ -104,12 +105,12 @@ class DecodeLayer(RealisticLayer):
         c.kv[:, start_pos] = kv_c
         c.pe[:, start_pos] = k_pe
         # absorbed query: q_nope . W_UK per head (deepseek.py:799)
-        q_abs = torch.bmm(q[..., :s.nope].transpose(0, 1), self.w_uk).transpose(0, 1)    # [B, h, kv_lora]
+        q_abs = ops.linear_bf16_batched(q[..., :s.nope], self.w_uk_t)                    # [B, h, kv_lora]
         picked = indexer.indexer_decode(normed, q_c, self.index_weights, c.index_k, c.index_scale,
                                         start_pos, self.freqs, self.index_topk)
         latent = ops.mla_sparse_decode(q_abs, q[..., s.nope:], c.kv[:, :end], c.pe[:, :end], picked,
                                        self.softmax_scale)                                 # [B, h, kv_lora]
-        heads_out = torch.bmm(latent.transpose(0, 1), self.w_uv_t).transpose(0, 1)       # [B, h, v]
+        heads_out = ops.linear_bf16_batched(latent, self.w_uv)                          # [B, h, v]
         out = self.w_o(heads_out.reshape(batch, h * s.v_dim))
         return self._all_reduce(out)
 

@@ -1,7 +1,8 @@
 """The DeepSeek-V3.2 sparse-attention indexer on the B200 kernels.
 
 Counterpart of `Indexer.forward` (racetrack/models/deepseek.py:656-686): which `index_topk`
-cached keys each query attends to. The two projections are bf16 GEMMs, everything between them
+cached keys each query attends to. The two projections are bf16 GEMMs (the fp32 head-weight
+projection as two bf16 halves of its weight with fp32 accumulation), everything between them
 and the scores is one fused kernel per operand (ops.index_prep), the scores come from the
 tensor cores (ops.fp8_index) and the selection is an exact radix select (ops.index_topk).
 Nothing reads device data back to the host.
@@ -88,7 +89,7 @@ def indexer_forward(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cach
     k_cache[start_pos:end_pos] = k_fp8.view(s_len, w.head_dim)
     k_scale_cache[start_pos:end_pos] = k_scale.view(s_len)
     # per-head weights in fp32, as the reference forms them (deepseek.py:677-678)
-    head_w = torch.nn.functional.linear(x.float(), w.weights_proj) * w.heads ** -0.5
+    head_w = ops.linear_f32_weight(x, w.weights_proj) * w.heads ** -0.5
     head_w = head_w * q_scale * w.head_dim ** -0.5
     scores = ops.fp8_index(q_fp8.unsqueeze(0), head_w.unsqueeze(0), k_cache[:end_pos].unsqueeze(0),
                            k_scale_cache[:end_pos].unsqueeze(0),
@@ -117,7 +118,7 @@ def indexer_decode(x: torch.Tensor, qr: torch.Tensor, w: IndexerWeights, k_cache
                                     ln_weight=w.k_norm_weight, ln_bias=w.k_norm_bias)
     k_cache[:, start_pos] = k_fp8.view(batch, w.head_dim)
     k_scale_cache[:, start_pos] = k_scale.view(batch)
-    head_w = torch.nn.functional.linear(x.float(), w.weights_proj) * w.heads ** -0.5
+    head_w = ops.linear_f32_weight(x, w.weights_proj) * w.heads ** -0.5
     head_w = head_w * q_scale.view(batch, w.heads) * w.head_dim ** -0.5
     scores = ops.fp8_index(q_fp8.view(batch, 1, w.heads, w.head_dim), head_w.view(batch, 1, w.heads),
                            k_cache[:, :end_pos], k_scale_cache[:, :end_pos])

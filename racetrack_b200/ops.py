@@ -564,6 +564,55 @@ def linear_bf16(x: torch.Tensor, weight: torch.Tensor, *,
     return out
 
 
+def linear_bf16_batched(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """out[t, h, :] = x[t, h, :] @ weight[h]^T for x bf16 [T, H, K] (any token / head strides, e.g.
+    a column slice of a projection output) and weight bf16 [H, N, K] -> bf16 [T, H, N], one launch
+    for all heads. The absorbed projections of the MLA decode branch
+    (racetrack/models/deepseek.py:799,810)."""
+    _require_cuda(x, weight)
+    _require_bf16("linear_bf16_batched x", x)
+    _require_bf16("linear_bf16_batched weight", weight)
+    if x.dim() != 3 or weight.dim() != 3 or weight.shape[0] != x.shape[1] or weight.shape[2] != x.shape[2]:
+        raise RuntimeError("linear_bf16_batched: expected x [T, H, K] and weight [H, N, K]")
+    if x.stride(2) != 1 or x.stride(0) % 8 or x.stride(1) % 8 or x.data_ptr() % 16:
+        x = x.contiguous()
+    if weight.stride(2) != 1 or weight.stride(0) % 8 or weight.stride(1) % 8 or weight.data_ptr() % 16:
+        weight = weight.contiguous()
+    tokens, heads, k = x.shape
+    n = weight.shape[1]
+    out = torch.empty(tokens, heads, n, dtype=torch.bfloat16, device=x.device)
+    lib = _lib.load()
+    _lib.check(lib.rt_gemm_bf16_batched(x.data_ptr(), weight.data_ptr(), out.data_ptr(), heads, tokens, n, k,
+                                        x.stride(0), x.stride(1), weight.stride(1), weight.stride(0),
+                                        out.stride(0), out.stride(1), _stream()), "rt_gemm_bf16_batched")
+    return out
+
+
+_SPLIT_WEIGHTS: dict[tuple, torch.Tensor] = {}
+
+
+def linear_f32_weight(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """F.linear(x.float(), weight) for bf16 x [..., K] and an fp32 weight [N, K] -> fp32 [..., N] on
+    the tensor cores: the weight is split once into two bf16 matrices hi + lo (exact to 16
+    mantissa bits: a relative 2^-17 per weight, below the fp32 round-off of a K-long sum), both
+    multiply x with fp32 accumulation in one launch, and the two halves are added. The fp32
+    projections of the model: the indexer's weights_proj (racetrack/models/deepseek.py:677)."""
+    _require_cuda(x, weight)
+    _require_bf16("linear_f32_weight x", x)
+    if weight.dtype != torch.float32 or weight.dim() != 2:
+        raise RuntimeError("linear_f32_weight: weight must be a 2-D float32 tensor")
+    key = (weight.data_ptr(), tuple(weight.shape), weight._version)
+    split = _SPLIT_WEIGHTS.get(key)
+    if split is None:
+        hi = weight.to(torch.bfloat16)
+        lo = (weight - hi.float()).to(torch.bfloat16)
+        split = torch.cat((hi, lo)).contiguous()
+        _SPLIT_WEIGHTS[key] = split
+    n = weight.shape[0]
+    both = linear_bf16(x, split, out_dtype=torch.float32)
+    return both[..., :n] + both[..., n:]
+
+
 def quantize_weight_fp8(weight: torch.Tensor):
     """bf16/fp32 weight [N, K] -> (e4m3fn codes [N, K], fp32 scales [ceil(N/128), K/128]) with one
     scale = amax / 448 per 128 x 128 block: the checkpoint layout `weight` / `weight.scale` of

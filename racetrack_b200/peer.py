@@ -120,11 +120,13 @@ class PeerExchange:
         + residual_rows, normed = rms_norm(hidden) * weight. Includes the barrier that makes
         every rank's partial sums visible."""
         part = self.local[name]
-        return self.group._timed("peer_barrier+reduce_residual_norm", part,
+        # timed apart: the barrier's interval is the wait for the slowest rank (load imbalance),
+        # the kernel's interval is the transfer itself
+        self.group._timed("peer_barrier (wait for the slowest rank)", self.flags, self.barrier)
+        return self.group._timed("peer_reduce_residual_norm", part,
                                  lambda: self._reduce_residual_norm(part, name, residual_rows, weight, eps))
 
     def _reduce_residual_norm(self, part, name, residual_rows, weight, eps):
-        self.barrier()
         total_rows, cols = part.shape
         lo, hi = self.group.rows_of(total_rows)
         res = residual_rows if residual_rows.stride(-1) == 1 else residual_rows.contiguous()
