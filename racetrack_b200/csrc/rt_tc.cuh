@@ -368,6 +368,16 @@ __device__ __forceinline__ void mma_f16_pair(uint32_t d_tmem, uint64_t adesc, ui
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+// bf16/f16 MMA over the pair with the A operand in TENSOR memory (each CTA's 128 rows of A in
+// its own tensor memory, same columns in both; layout as for mma_f16_ts).
+__device__ __forceinline__ void mma_f16_ts_pair(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc,
+                                                uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
 // Block-scaled NVFP4 MMA over the pair: 256 x N x 64.
 __device__ __forceinline__ void mma_nvfp4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc,
                                                uint32_t idesc, uint32_t sfa_tmem, uint32_t sfb_tmem,

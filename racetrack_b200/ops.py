@@ -927,6 +927,13 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch
     return attention_prefill(q, k[..., :nope], k[..., nope:] if k.shape[-1] > nope else None, v)
 
 
+def attention_prefill_schedule(schedule: int) -> int:
+    """Selects the schedule of attention_prefill for this process (0 / 1 one CTA per 256 query
+    rows, the default; 2 CTA pairs where the head shape allows) and returns the previous
+    setting."""
+    return int(_lib.load().rt_attn_prefill_schedule(int(schedule)))
+
+
 def gemm_bf16_schedule(schedule: int) -> int:
     """Selects the schedule of the bf16 GEMM for this process (0 default = by size, 1 single-CTA
     128 x 256 tiles, 2 CTA pairs with 256 x 256 tiles where K % 64 == 0) and returns the

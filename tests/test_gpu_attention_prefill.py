@@ -35,14 +35,20 @@ def _reference(q, k_nope, k_pe, v):
     return ref_layer.causal_attention(q, torch.cat((k_nope, pe), dim=-1), v)
 
 
+@pytest.mark.parametrize("schedule", [1, 2])
 @pytest.mark.parametrize("tokens,heads", [(1, 1), (7, 2), (128, 1), (129, 3), (256, 2), (300, 4),
-                                          (513, 2), (1000, 3)])
-def test_mla_shape_matches_the_reference(ops, tokens, heads):
+                                          (513, 2), (640, 1), (1000, 3), (1300, 2)])
+def test_mla_shape_matches_the_reference(ops, tokens, heads, schedule):
     """The DeepSeek-V3.2 head: 128 nope + 64 shared rope dims, values of width 128; ragged
-    lengths around the 128-row tiles and the 256-row blocks."""
+    lengths around the 128-row tiles, the 256-row blocks of the single-CTA schedule (1) and
+    the 512-row blocks of the CTA-pair schedule (2)."""
     q, kn, kp, v = _qkv(tokens, heads, 128, 64, 128, 100 + tokens)
     want = _reference(q, kn, kp, v)
-    got = ops.attention_prefill(q.cuda(), kn.cuda(), kp.cuda(), v.cuda())
+    prev = ops.attention_prefill_schedule(schedule)
+    try:
+        got = ops.attention_prefill(q.cuda(), kn.cuda(), kp.cuda(), v.cuda())
+    finally:
+        ops.attention_prefill_schedule(prev)
     ops.tc_error_state()
     assert got.shape == want.shape and got.dtype == torch.bfloat16
     assert rel_err(got, want) <= 1e-2, f"relative error {rel_err(got, want)}"
@@ -65,10 +71,23 @@ def test_other_head_shapes(ops, nope, rope, v_dim, shared):
     assert rel_err(got, want) <= 1e-2, f"relative error {rel_err(got, want)}"
 
 
-def test_strided_views_of_projection_outputs(ops):
+@pytest.mark.parametrize("schedule", [1, 2])
+def test_strided_views_of_projection_outputs(ops, schedule):
     """q a view of the q_b output, k_nope / v column slices of one kv_b output [T, H, nope + v]:
-    consumed in place."""
+    consumed in place; a per-head rope key as well."""
     tokens, heads = 333, 4
+    prev = ops.attention_prefill_schedule(schedule)
+    try:
+        _strided_case(ops, tokens, heads)
+        q, kn, kp, v = _qkv(700, 3, 128, 64, 128, 58, shared_pe=False)
+        got = ops.attention_prefill(q.cuda(), kn.cuda(), kp.cuda(), v.cuda())
+        ops.tc_error_state()
+        assert rel_err(got, _reference(q, kn, kp, v)) <= 1e-2
+    finally:
+        ops.attention_prefill_schedule(prev)
+
+
+def _strided_case(ops, tokens, heads):
     q, kn, kp, v = _qkv(tokens, heads, 128, 64, 128, 55)
     kv = torch.cat((kn, v), dim=-1).cuda()                    # [T, H, 256]
     qbuf = torch.zeros(tokens, heads * 192 + 64, dtype=torch.bfloat16, device="cuda")
@@ -79,9 +98,18 @@ def test_strided_views_of_projection_outputs(ops):
     assert rel_err(got, _reference(q, kn, kp, v)) <= 1e-2
 
 
-def test_growing_maxima_and_large_scores(ops):
+@pytest.mark.parametrize("schedule", [1, 2])
+def test_growing_maxima_and_large_scores(ops, schedule):
     """Scores that grow along the sequence (the running maximum is replaced again and again,
     the accumulator rescaled) and a wide score range (exp2 underflow of the early keys)."""
+    prev = ops.attention_prefill_schedule(schedule)
+    try:
+        _growing_case(ops)
+    finally:
+        ops.attention_prefill_schedule(prev)
+
+
+def _growing_case(ops):
     tokens, heads = 640, 2
     q, kn, kp, v = _qkv(tokens, heads, 128, 64, 128, 91, scale=1.0)
     ramp = torch.linspace(0.2, 3.0, tokens).view(tokens, 1, 1)
