@@ -588,7 +588,8 @@ def linear_bf16_batched(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     return out
 
 
-_SPLIT_WEIGHTS: dict[tuple, torch.Tensor] = {}
+_SPLIT_WEIGHTS: dict[tuple, tuple] = {}     # key -> (hi | lo halves, the weight itself)
+_SPLIT_WEIGHTS_MAX = 256
 
 
 def linear_f32_weight(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
@@ -601,13 +602,18 @@ def linear_f32_weight(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
     _require_bf16("linear_f32_weight x", x)
     if weight.dtype != torch.float32 or weight.dim() != 2:
         raise RuntimeError("linear_f32_weight: weight must be a 2-D float32 tensor")
-    key = (weight.data_ptr(), tuple(weight.shape), weight._version)
-    split = _SPLIT_WEIGHTS.get(key)
-    if split is None:
+    # The entry keeps the weight's storage alive, so its address cannot be handed to another
+    # tensor while the entry exists; the version counter catches in-place updates.
+    key = (weight.data_ptr(), tuple(weight.shape), tuple(weight.stride()), weight._version)
+    entry = _SPLIT_WEIGHTS.get(key)
+    if entry is None:
         hi = weight.to(torch.bfloat16)
         lo = (weight - hi.float()).to(torch.bfloat16)
-        split = torch.cat((hi, lo)).contiguous()
-        _SPLIT_WEIGHTS[key] = split
+        entry = (torch.cat((hi, lo)).contiguous(), weight.detach())
+        while len(_SPLIT_WEIGHTS) >= _SPLIT_WEIGHTS_MAX:
+            _SPLIT_WEIGHTS.pop(next(iter(_SPLIT_WEIGHTS)))
+        _SPLIT_WEIGHTS[key] = entry
+    split = entry[0]
     n = weight.shape[0]
     both = linear_bf16(x, split, out_dtype=torch.float32)
     return both[..., :n] + both[..., n:]

@@ -9,11 +9,12 @@ from racetrack_b200 import _lib, ops
 
 BACKEND_AVAILABLE = _lib.available()
 
-_CAT: dict = {}
+_CAT: dict = {}      # key -> ([w1; w3], its scales, w1, w3)
 
 
 def _concat(w1_w, w1_s, w3_w, w3_s):
-    key = (w1_w.data_ptr(), w3_w.data_ptr(), w1_w._version, w3_w._version)
+    key = (w1_w.data_ptr(), w3_w.data_ptr(), tuple(w1_w.shape), tuple(w3_w.shape), w1_w.dtype,
+           w1_w._version, w3_w._version)
     hit = _CAT.get(key)
     if hit is None:
         w13 = torch.cat((w1_w, w3_w)).contiguous()
@@ -22,9 +23,12 @@ def _concat(w1_w, w1_s, w3_w, w3_s):
             if w1_w.shape[0] % 128:
                 raise RuntimeError("fused_mlp_gate_up_proj: FP8 weights need out_features % 128 == 0")
             s13 = torch.cat((w1_s.float(), w3_s.float())).contiguous()
-        hit = (w13, s13)
+        # the entry holds the source weights, so their addresses stay theirs while it exists
+        hit = (w13, s13, w1_w.detach(), w3_w.detach())
+        while len(_CAT) >= 1024:
+            _CAT.pop(next(iter(_CAT)))
         _CAT[key] = hit
-    return hit
+    return hit[0], hit[1]
 
 
 def fused_mlp_gate_up_proj(x, w1_w, w1_s, w3_w, w3_s, *, scale_fmt, fallback):

@@ -20,7 +20,14 @@ from racetrack_b200 import _lib, ops
 
 BACKEND_AVAILABLE = _lib.available()
 
-_CAT: dict = {}
+_CAT: dict = {}          # key -> (derived weight, the tensors it was made from)
+_CAT_MAX = 1024
+
+
+def _remember(key, entry):
+    while len(_CAT) >= _CAT_MAX:
+        _CAT.pop(next(iter(_CAT)))
+    _CAT[key] = entry
 
 
 def _cat_weights(*weights):
@@ -32,9 +39,10 @@ def _cat_weights(*weights):
         for w in weights:
             if w.dtype != torch.bfloat16:
                 raise RuntimeError("the MLA prologue ops take bfloat16 weights")
-        hit = torch.cat(weights, dim=0).contiguous()
-        _CAT[key] = hit
-    return hit
+        # the entry holds the source tensors, so their addresses stay theirs while it exists
+        hit = (torch.cat(weights, dim=0).contiguous(), tuple(w.detach() for w in weights))
+        _remember(key, hit)
+    return hit[0]
 
 
 def _uk_t(wkv_b_weight, n_heads, nope, kv_lora):
@@ -43,9 +51,10 @@ def _uk_t(wkv_b_weight, n_heads, nope, kv_lora):
     key = ("uk_t", wkv_b_weight.data_ptr(), tuple(wkv_b_weight.shape), wkv_b_weight._version)
     hit = _CAT.get(key)
     if hit is None:
-        hit = wkv_b_weight.view(n_heads, -1, kv_lora)[:, :nope].transpose(1, 2).contiguous()
-        _CAT[key] = hit
-    return hit
+        hit = (wkv_b_weight.view(n_heads, -1, kv_lora)[:, :nope].transpose(1, 2).contiguous(),
+               wkv_b_weight.detach())
+        _remember(key, hit)
+    return hit[0]
 
 
 def fused_ar_rms_qkv_proj(x, residual, norm_weight, wq_a_weight, wkv_a_weight, indexer_wk_weight, *,
