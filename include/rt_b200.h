@@ -602,8 +602,9 @@ int rt_mla_sparse_decode(const void* q_abs, const void* q_pe, const void* kv, co
  *      racetrack/models/deepseek.py:780-792 (MHA prefill of MLA.forward).
  */
 /* Selects the schedule of rt_attn_causal_prefill for this process and returns the previous
- * setting: 0 / 1 = one CTA per 256 query rows (default), 2 = CTA pairs (tcgen05 cta_group::2,
- * 512 query rows per pair) wherever the head shape is 128 + 64 / 128. */
+ * setting: 0 = by shape and length (default), 1 = one CTA per 256 query rows with key tiles of
+ * 128, 2 = CTA pairs (tcgen05 cta_group::2, 256 query rows per pair, key tiles of 256) wherever
+ * the head shape is 128 + 64 / 128. */
 int rt_attn_prefill_schedule(int schedule);
 int rt_attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, const void* v,
                            void* out, int64_t tokens, int64_t heads, int64_t nope_dim,

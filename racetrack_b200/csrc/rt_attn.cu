@@ -527,7 +527,7 @@ __device__ long long g_fa_trace[10 * 64];
 #define RT_FTRACE(ev, it) do { } while (0)
 #endif
 
-// 0 / 1: the single-CTA kernel (default), 2: CTA pairs wherever the head shape allows
+// 0: by shape and length, 1: the single-CTA kernel, 2: CTA pairs wherever the head shape allows
 // (rt_attn_prefill_schedule; for A/B measurements and tests).
 static int g_attn_schedule = 0;
 
@@ -564,11 +564,14 @@ __device__ __forceinline__ float ex2_poly(float x) {
 }
 
 // 32 scores of one row -> 32 probabilities as 16 bf16 pairs, and their fp32 sum. One pair in
-// kFPolyEvery takes the polynomial route, the rest the special-function unit.
+// kFPolyEvery takes the polynomial route, the rest the special-function unit (0: none).
 #ifndef RT_FA_POLY_EVERY
 #define RT_FA_POLY_EVERY 0
 #endif
-constexpr int kFPolyEvery = RT_FA_POLY_EVERY;
+#ifndef RT_FA_PAIR_POLY_EVERY
+#define RT_FA_PAIR_POLY_EVERY 0
+#endif
+template <int kFPolyEvery>
 __device__ __forceinline__ void softmax_chunk(const uint32_t (&r)[32], uint32_t (&pk)[16], float scale,
                                               float m, float& sum) {
     float acc0 = 0.f, acc1 = 0.f;
@@ -837,9 +840,9 @@ __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
             // P = exp2(s * scale - m) as bf16 pairs into columns [32 hh, 32 hh + 32) of S_t
             float s0 = 0.f, s1 = 0.f;
             uint32_t pk[16];
-            softmax_chunk(r0, pk, a.scale_log2, m_new, s0);
+            softmax_chunk<RT_FA_POLY_EVERY>(r0, pk, a.scale_log2, m_new, s0);
             tmem_st_32x16(ts + 32u * hh, pk);
-            softmax_chunk(r1, pk, a.scale_log2, m_new, s1);
+            softmax_chunk<RT_FA_POLY_EVERY>(r1, pk, a.scale_log2, m_new, s1);
             tmem_st_32x16(ts + 32u * hh + 16u, pk);
             l += s0 + s1;
             tmem_st_wait();
@@ -893,32 +896,40 @@ __global__ void __launch_bounds__(kFThreads, 1) attn_prefill_kernel(
 
 
 // ---------------------------------------------------------------------------
-// The same attention on CTA PAIRS (tcgen05 cta_group::2) for the MLA head shape
-// (128 nope + 64 rope dims, values of 128)
+// The same attention on CTA PAIRS (tcgen05 cta_group::2) with key tiles of 256 keys, for the
+// MLA head shape (128 nope + 64 rope dims, values of 128)
 // ---------------------------------------------------------------------------
-// A 128 x 128 x 16 MMA with both operands in shared memory reads 8 KB in the 64 cycles its
-// arithmetic nominally takes, all of the 128 B/clk a shared memory delivers. A pair of CTAs
-// issues 256 x 128 x 16 MMAs instead: each CTA supplies ITS OWN 128 query rows (A) and HALF of
-// the key tile (B: 64 keys; for P V half of the value dims), so per MMA a CTA reads 6 KB, loads
-// half of every key / value tile from L2, and has room to double-buffer the values too. It
-// turned out not to be faster (the trace shows the MMA thread busy for the same 3500 - 3700
-// cycles per key tile in both schedules: the tensor pipe itself is the pace), so it is kept as
-// a selectable schedule, not the default.
-// A pair covers 512 query rows of one head: CTA r of the pair owns the row tiles R(r) and R(2 + r)
-// of 128 rows each; MMA 0 spans R0 | R1, MMA 1 spans R2 | R3, processed in ping-pong as above.
-// A row tile's last key tile is its diagonal one; the pair's MMA runs to the diagonal tile of
-// its LATER half, so the earlier half sees one tile that is masked entirely (its softmax
-// threads write zero probabilities without looking at the scores).
-// One thread of the leader CTA (cluster rank 0) issues every MMA and commits to the barriers
-// of both CTAs; the peer's warp 1 relays "my tiles have landed" to the leader; the softmax warps
-// of both CTAs arrive on the leader's p_full. Loads never use multicast.
-constexpr uint32_t kGKOff = 6 * kFChunk;                   // key stages: 2 x (3 chunks of [64 keys][128 B])
-constexpr uint32_t kGKStage = 3 * (kFChunk / 2);
-constexpr uint32_t kGVOff = kGKOff + 2 * kGKStage;         // value stages: 2 x [128 keys][64 dims]
-constexpr uint32_t kGBarOff = kGVOff + 2 * kFChunk;
-constexpr int kGBars = 16;     // q_full[2] k_full[2] k_empty[2] v_full[2] v_empty[2] s_full[2] p_full[2] o_full[2]
-constexpr uint32_t kGXmOff = kGBarOff + kGBars * 8 + 16;
-constexpr uint32_t kGSmemBytes = kGXmOff + 2 * 128 * 2 * 2 + 1024;
+// What paces the kernel above is the thread that issues its MMAs: every tcgen05.mma costs that
+// thread about 65 cycles, every commit as much and every barrier wait about 100, whatever the
+// shape of the MMA, and a 128 x 128 x 16 MMA keeps the tensor core busy for just 64. So this
+// schedule issues larger MMAs: a pair of CTAs covers 256 query rows of one head (128 per CTA)
+// and walks key tiles of 256 keys,
+//   S = Q K^T     12 MMAs of 256 x 256 x 16 (each CTA brings its own 128 query rows as A and 128
+//                 of the tile's keys as B), 128 cycles of tensor core each;
+//   O += P V      16 MMAs of 256 x 128 x 16 (A = P from tensor memory, B = the values MN-major,
+//                 each CTA bringing 64 of the 128 value dims for all 256 keys), 64 cycles each;
+// 28 MMAs, two commits and four waits (about 2400 cycles of the issuing thread) for 2560 cycles
+// of tensor-core work per key tile, where the single-CTA schedule spends 40 MMAs on the same
+// work. Tensor memory per CTA: S 256 columns | P 128 (bf16 pairs) | O 128. P has its own columns,
+// so S(j + 1) is issued as soon as the softmax threads hold the scores of tile j in registers
+// and runs under their exponentials; O += P(j) V(j) follows when P(j) is complete. Softmax: 16
+// warps, four threads per query row with 64 scores each; the four partial maxima of a row meet
+// in shared memory as bf16. A thread writes P(j) only after O += P(j - 1) V(j - 1) has completed
+// (the same barrier tells it that O is at rest for a rescale). Shared memory per CTA: Q 48 KB,
+// two stages of its 128 keys (96 KB), two stages of its 64 value dims of 256 keys (64 KB).
+// One thread of the leader CTA (cluster rank 0) issues every MMA and commits to the barriers of
+// both CTAs; the peer's warp 1 relays "my tiles have landed" to the leader; the softmax warps of
+// both CTAs arrive on the leader's s_free and p_full. Loads never use multicast.
+constexpr uint32_t kGQOff = 0;                              // [3 chunks][128 rows][128 B]
+constexpr uint32_t kGKOff = 3 * kFChunk;                    // key stages: 2 x 3 chunks of this CTA's 128 keys
+constexpr uint32_t kGKStage = 3 * kFChunk;
+constexpr uint32_t kGVOff = kGKOff + 2 * kGKStage;          // value stages: 2 x [256 keys][64 dims]
+constexpr uint32_t kGVStage = 2 * kFChunk;
+constexpr uint32_t kGBarOff = kGVOff + 2 * kGVStage;
+constexpr int kGBars = 15;     // q_full k_full[2] v_full[2] s_done[2] pv_done[2] s_free p_full row_sync[4]
+constexpr uint32_t kGXmOff = kGBarOff + kGBars * 8 + 16;    // row maxima as bf16 [2 steps][128 rows][4]
+constexpr uint32_t kGSmemBytes = kGXmOff + 2 * 128 * 4 * 2 + 1024;
+constexpr uint32_t kGTmemP = 256, kGTmemO = 384;            // first column of P and of O
 static_assert(kGSmemBytes <= 232448, "shared memory budget");
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_prefill_pair_kernel(
@@ -929,14 +940,15 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bars = base + kGBarOff;
-    auto q_full = [&](int t) { return bars + 8u * t; };
-    auto k_full = [&](int st) { return bars + 8u * (2 + st); };
-    auto k_empty = [&](int st) { return bars + 8u * (4 + st); };
-    auto v_full = [&](int st) { return bars + 8u * (6 + st); };
-    auto v_empty = [&](int st) { return bars + 8u * (8 + st); };
-    auto s_full = [&](int t) { return bars + 8u * (10 + t); };
-    auto p_full = [&](int t) { return bars + 8u * (12 + t); };
-    auto o_full = [&](int t) { return bars + 8u * (14 + t); };
+    const uint32_t q_full = bars;
+    auto k_full = [&](int st) { return bars + 8u * (1 + st); };
+    auto v_full = [&](int st) { return bars + 8u * (3 + st); };
+    auto s_done = [&](int st) { return bars + 8u * (5 + st); };     // S of a key tile complete: scores
+                                                                    // readable, its key stage free
+    auto pv_done = [&](int st) { return bars + 8u * (7 + st); };    // O += P V of a key tile complete: its
+                                                                    // value stage and P free, O at rest
+    const uint32_t s_free = bars + 8u * 9, p_full = bars + 8u * 10; // used in the leader only
+    auto row_sync = [&](int quad) { return bars + 8u * (11 + quad); };  // the four warps that share query rows
     const uint32_t slot = bars + 8u * kGBars;
     volatile uint32_t* slot_ptr = reinterpret_cast<volatile uint32_t*>(base_ptr + kGBarOff + 8 * kGBars);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_ptr + 1);
@@ -945,27 +957,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
     const int rank = static_cast<int>(cluster_ctarank());
     const int qb = static_cast<int>(gridDim.x >> 1) - 1 - static_cast<int>(blockIdx.x >> 1);   // heaviest first
     const int h = blockIdx.y;
-    const int q0 = qb * 512;
-    const int n = q0 / 128;
-    const int key_tiles = (a.tokens + 127) / 128;
-    // key tiles MMA t runs over: up to the diagonal tile of its later half (row tile 2 t + 1)
-    const int n0 = min(n + 2, key_tiles);
-    const int n1 = q0 + 256 < a.tokens ? min(n + 4, key_tiles) : 0;
-    const int n_max = max(n0, n1);
+    const int q0 = qb * 256;                 // first query row of the pair
+    const int n = qb + 1;                    // key tiles 0 .. qb of 256 keys; the last one is diagonal
 
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         const uint32_t landed = rank == 0 ? 2 : 1;          // own producer (+ the peer's relay)
+        mbar_init(q_full, landed);
         for (int i = 0; i < 2; ++i) {
-            mbar_init(q_full(i), landed);
             mbar_init(k_full(i), landed);
             mbar_init(v_full(i), landed);
-            mbar_init(k_empty(i), 1);
-            mbar_init(v_empty(i), 1);
-            mbar_init(s_full(i), 1);
-            mbar_init(p_full(i), 16);                       // lane 0 of the tile's softmax warps in both CTAs
-            mbar_init(o_full(i), 1);
+            mbar_init(s_done(i), 1);
+            mbar_init(pv_done(i), 1);
         }
+        mbar_init(s_free, 32);                              // lane 0 of the 16 softmax warps of both CTAs
+        mbar_init(p_full, 32);
+        for (int i = 0; i < 4; ++i) mbar_init(row_sync(i), 4);
         fence_mbar_init();
         tma_prefetch_desc(&tm_qn);
         tma_prefetch_desc(&tm_kn);
@@ -981,172 +988,148 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
     tc_fence_after();
     const uint32_t tmem_base = *slot_ptr;
 
+    // The u-th use of a two-stage barrier (key tile 2 u + st) completes its phase u.
     if (warp == 0) {
         if (lane == 0) {
             const int pe_head = a.pe_shared ? 0 : h;
-            for (int t = 0; t < (n1 > 0 ? 2 : 1); ++t) {
-                const uint32_t dst = base + kFQOff + t * 3 * kFChunk;
-                const int row = q0 + 128 * (2 * t + rank);
-                mbar_arrive_expect_tx(q_full(t), 3 * kFChunk);
-                tma_load_4d(dst, &tm_qn, 0, row, 0, h, q_full(t));
-                tma_load_4d(dst + 2 * kFChunk, &tm_qp, 0, row, 0, h, q_full(t));
-            }
+            const int row_q = q0 + 128 * rank;
+            mbar_arrive_expect_tx(q_full, 3 * kFChunk);
+            tma_load_4d(base + kGQOff, &tm_qn, 0, row_q, 0, h, q_full);
+            tma_load_4d(base + kGQOff + 2 * kFChunk, &tm_qp, 0, row_q, 0, h, q_full);
             bool ok = true;
-            auto load_k = [&](int j) {                         // this CTA's 64 keys of key tile j
+            auto load_k = [&](int j) {                         // this CTA's 128 keys of key tile j
                 const int st = j & 1;
-                if (!(ok = mbar_wait(k_empty(st), ((j >> 1) & 1) ^ 1u, abort_flag, 81))) return;
+                if (j >= 2 && !(ok = mbar_wait(s_done(st), ((j >> 1) & 1) ^ 1u, abort_flag, 81))) return;
                 const uint32_t dst = base + kGKOff + st * kGKStage;
+                const int row = 256 * j + 128 * rank;
                 mbar_arrive_expect_tx(k_full(st), kGKStage);
-                tma_load_4d(dst, &tm_kn, 0, 128 * j + 64 * rank, 0, h, k_full(st));
-                tma_load_4d(dst + kFChunk, &tm_kp, 0, 128 * j + 64 * rank, 0, pe_head, k_full(st));
+                tma_load_4d(dst, &tm_kn, 0, row, 0, h, k_full(st));
+                tma_load_4d(dst + 2 * kFChunk, &tm_kp, 0, row, 0, pe_head, k_full(st));
             };
             auto load_v = [&](int j) {                         // this CTA's 64 value dims of key tile j
                 const int st = j & 1;
-                if (!(ok = mbar_wait(v_empty(st), ((j >> 1) & 1) ^ 1u, abort_flag, 82))) return;
-                mbar_arrive_expect_tx(v_full(st), kFChunk);
-                tma_load_4d(base + kGVOff + st * kFChunk, &tm_v, 0, 128 * j, rank, h, v_full(st));
+                if (j >= 2 && !(ok = mbar_wait(pv_done(st), ((j >> 1) & 1) ^ 1u, abort_flag, 82))) return;
+                mbar_arrive_expect_tx(v_full(st), kGVStage);
+                tma_load_4d(base + kGVOff + st * kGVStage, &tm_v, 0, 256 * j, rank, h, v_full(st));
             };
-            for (int j = 0; ok && j < n_max; ++j) {
-                load_k(j);
-                if (ok) load_v(j);
+            // in the order the stages become free: S(j) completes after O += P(j - 2) V(j - 2)
+            load_k(0);
+            if (n > 1) load_k(1);
+            for (int j = 0; ok && j < n; ++j) {
+                load_v(j);
+                if (ok && j + 2 < n) load_k(j + 2);
             }
         }
         __syncwarp();
     } else if (warp == 1) {
         if (rank == 0 && lane == 0) {
-            // fp32 accumulate, bf16 x bf16, M = 256 over the pair, N = 128; O: B MN-major
-            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (16u << 17) | (16u << 24);
-            const uint32_t idesc_o = idesc_s | (1u << 16);
-            auto t_s = [&](int t) { return tmem_base + static_cast<uint32_t>(128 * t); };
-            auto t_o = [&](int t) { return tmem_base + static_cast<uint32_t>(256 + 128 * t); };
-            auto commit_both = [&](uint32_t bar) {
-                mma_commit_pair(bar);
-                mma_commit_pair(map_to_cta(bar, 1));
-            };
-            auto issue_s = [&](int t, int j) {
-                const uint32_t qa = base + kFQOff + t * 3 * kFChunk, kb = base + kGKOff + (j & 1) * kGKStage;
+            // fp32 accumulate, bf16 x bf16, M = 256 over the pair; S: N = 256, both K-major; O: N = 128, B MN-major
+            const uint32_t idesc_s = (1u << 4) | (1u << 7) | (1u << 10) | (32u << 17) | (16u << 24);
+            const uint32_t idesc_o = (1u << 4) | (1u << 7) | (1u << 10) | (1u << 16) | (16u << 17) | (16u << 24);
+            auto issue_s = [&](int j) {
+                const uint32_t kb = base + kGKOff + (j & 1) * kGKStage;
 #pragma unroll
                 for (int c = 0; c < 3; ++c) {
-                    const uint64_t adesc = smem_desc_sw128(qa + c * kFChunk);
-                    const uint64_t bdesc = smem_desc_sw128(kb + c * (kFChunk / 2));
+                    const uint64_t adesc = smem_desc_sw128(base + kGQOff + c * kFChunk);
+                    const uint64_t bdesc = smem_desc_sw128(kb + c * kFChunk);
 #pragma unroll
                     for (int k = 0; k < 4; ++k)
-                        mma_f16_pair(t_s(t), adesc + 2u * k, bdesc + 2u * k, idesc_s, (c | k) != 0 ? 1u : 0u);
+                        mma_f16_pair(tmem_base, adesc + 2u * k, bdesc + 2u * k, idesc_s, (c | k) != 0 ? 1u : 0u);
                 }
-                commit_both(s_full(t));
+                mma_commit_pair_both(s_done(j & 1));
             };
-            auto issue_pv = [&](int t, int j) {
-                const uint32_t vb = base + kGVOff + (j & 1) * kFChunk;
+            auto issue_pv = [&](int j) {
+                const uint32_t vb = base + kGVOff + (j & 1) * kGVStage;
 #pragma unroll
-                for (int k = 0; k < 8; ++k)
-                    mma_f16_ts_pair(t_o(t), t_s(t) + 8u * k, smem_desc_sw128_mn(vb + k * 2048, kFChunk), idesc_o,
+                for (int k = 0; k < 16; ++k) {
+#if defined(RT_FA_DIAG) && RT_FA_DIAG == 3      // diagnostic build only (wrong results): B read K-major
+                    mma_f16_ts_pair(tmem_base + kGTmemO, tmem_base + kGTmemP + 8u * k,
+                                    smem_desc_sw128(vb + (k >> 2) * 8192) + 2u * (k & 3), idesc_o & ~(1u << 16),
                                     (j | k) != 0 ? 1u : 0u);
+#elif defined(RT_FA_DIAG) && RT_FA_DIAG == 4    // diagnostic build only (wrong results): A read from shared memory
+                    mma_f16_pair(tmem_base + kGTmemO, smem_desc_sw128(base + kGQOff) + 2u * (k & 3),
+                                 smem_desc_sw128_mn(vb + k * 2048, kGVStage), idesc_o, (j | k) != 0 ? 1u : 0u);
+#else
+                    mma_f16_ts_pair(tmem_base + kGTmemO, tmem_base + kGTmemP + 8u * k,
+                                    smem_desc_sw128_mn(vb + k * 2048, kGVStage), idesc_o, (j | k) != 0 ? 1u : 0u);
+#endif
+                }
+                mma_commit_pair_both(pv_done(j & 1));
             };
-            bool ok = mbar_wait(q_full(0), 0, abort_flag, 83) && mbar_wait(k_full(0), 0, abort_flag, 84);
+            bool ok = mbar_wait(q_full, 0, abort_flag, 83) && mbar_wait(k_full(0), 0, abort_flag, 84);
             if (ok) {
                 tc_fence_after();
-                issue_s(0, 0);
-                if (n1 > 0 && (ok = mbar_wait(q_full(1), 0, abort_flag, 83))) {
-                    tc_fence_after();
-                    issue_s(1, 0);
-                }
-                if (ok) commit_both(k_empty(0));
+                issue_s(0);
             }
-            for (int j = 0; ok && j < n_max; ++j) {
-                const uint32_t vpar = (j >> 1) & 1, kpar = ((j + 1) >> 1) & 1;
-                if (j < n0) {
+            for (int j = 0; ok && j < n; ++j) {
+                if (j + 1 < n) {
                     RT_FTRACE(0, j);
-                    if (!(ok = mbar_wait(p_full(0), j & 1, abort_flag, 85))) break;
+                    if (!(ok = mbar_wait(s_free, j & 1, abort_flag, 85))) break;
+                    if (!(ok = mbar_wait(k_full((j + 1) & 1), ((j + 1) >> 1) & 1, abort_flag, 84))) break;
                     RT_FTRACE(1, j);
-                    if (!(ok = mbar_wait(v_full(j & 1), vpar, abort_flag, 86))) break;
+                    tc_fence_after();
+                    issue_s(j + 1);
                     RT_FTRACE(2, j);
-                    tc_fence_after();
-                    issue_pv(0, j);
-                    if (j == n0 - 1) commit_both(o_full(0));
                 }
-                if (j + 1 < n0) {
-                    if (!(ok = mbar_wait(k_full((j + 1) & 1), kpar, abort_flag, 84))) break;
-                    tc_fence_after();
-                    issue_s(0, j + 1);
-                }
-                if (j < n1) {
-                    RT_FTRACE(3, j);
-                    if (!(ok = mbar_wait(p_full(1), j & 1, abort_flag, 85))) break;
-                    RT_FTRACE(4, j);
-                    if (!(ok = mbar_wait(v_full(j & 1), vpar, abort_flag, 86))) break;
-                    tc_fence_after();
-                    issue_pv(1, j);
-                    if (j == n1 - 1) commit_both(o_full(1));
-                }
-                commit_both(v_empty(j & 1));
-                if (j + 1 < n1) {
-                    if (!(ok = mbar_wait(k_full((j + 1) & 1), kpar, abort_flag, 84))) break;
-                    tc_fence_after();
-                    issue_s(1, j + 1);
-                    RT_FTRACE(5, j);
-                }
-                if (j + 1 < n_max) commit_both(k_empty((j + 1) & 1));
+                if (!(ok = mbar_wait(p_full, j & 1, abort_flag, 86))) break;
+                RT_FTRACE(3, j);
+                if (!(ok = mbar_wait(v_full(j & 1), (j >> 1) & 1, abort_flag, 87))) break;
+                RT_FTRACE(4, j);
+                tc_fence_after();
+                issue_pv(j);
+                RT_FTRACE(5, j);
             }
         } else if (rank == 1 && lane == 0) {
             // Relay: tells the leader that this CTA's tiles have landed, in the producer's order.
-            bool ok = mbar_wait(q_full(0), 0, abort_flag, 87);
-            if (ok) mbar_arrive_cluster(map_to_cta(q_full(0), 0));
-            if (ok && n1 > 0 && (ok = mbar_wait(q_full(1), 0, abort_flag, 87)))
-                mbar_arrive_cluster(map_to_cta(q_full(1), 0));
-            for (int j = 0; ok && j < n_max; ++j) {
-                const uint32_t par = (j >> 1) & 1;
-                if (!(ok = mbar_wait(k_full(j & 1), par, abort_flag, 88))) break;
-                mbar_arrive_cluster(map_to_cta(k_full(j & 1), 0));
-                if (!(ok = mbar_wait(v_full(j & 1), par, abort_flag, 89))) break;
-                mbar_arrive_cluster(map_to_cta(v_full(j & 1), 0));
+            bool ok = mbar_wait(q_full, 0, abort_flag, 88);
+            if (ok) mbar_arrive_cluster(map_to_cta(q_full, 0));
+            auto relay = [&](uint32_t bar, int j) {
+                if ((ok = mbar_wait(bar, (j >> 1) & 1, abort_flag, 89))) mbar_arrive_cluster(map_to_cta(bar, 0));
+            };
+            if (ok) relay(k_full(0), 0);
+            if (ok && n > 1) relay(k_full(1), 1);
+            for (int j = 0; ok && j < n; ++j) {
+                relay(v_full(j & 1), j);
+                if (ok && j + 2 < n) relay(k_full(j & 1), j + 2);
             }
         }
         __syncwarp();
     } else {
-        const int t = (warp - 2) >> 3;                        // ping-pong slot of this warp
-        const int hh = ((warp - 2) >> 2) & 1;                 // which 64 key columns of the tile
-        const int quad = warp & 3;
-        const int row = quad * 32 + lane;
-        const int n_t = t == 0 ? n0 : n1;
-        const int diag = n + 2 * t + rank;                    // the diagonal key tile of this CTA's row tile
-        const int pair_bar = 1 + 4 * t + quad;
+        const int quad = warp & 3;                            // the tensor-memory lane quarter it may touch
+        const int cq = (warp - 2) >> 2;                       // which 64 key columns of the tile
+        const int row = quad * 32 + lane;                     // query row within this CTA's tile
+        const int prow = 128 * rank + row;                    // query row within the pair's 256
+        const uint32_t row_bar = row_sync(quad);              // barrier of the four warps of these rows (a
+                                                              // bounded wait, unlike a named barrier)
         const uint32_t lane_base = static_cast<uint32_t>(quad * 32) << 16;
-        const uint32_t ts = tmem_base + lane_base + static_cast<uint32_t>(128 * t);
-        const uint32_t to = tmem_base + lane_base + static_cast<uint32_t>(256 + 128 * t);
-        const uint32_t p_leader = map_to_cta(p_full(t), 0);
+        const uint32_t ts = tmem_base + lane_base + static_cast<uint32_t>(64 * cq);
+        const uint32_t tp = tmem_base + lane_base + kGTmemP + static_cast<uint32_t>(32 * cq);
+        const uint32_t to = tmem_base + lane_base + kGTmemO + static_cast<uint32_t>(32 * cq);
+        const uint32_t s_free_leader = map_to_cta(s_free, 0), p_leader = map_to_cta(p_full, 0);
         const float ninf = __int_as_float(0xff800000);
-        __nv_bfloat16* xm = reinterpret_cast<__nv_bfloat16*>(base_ptr + kGXmOff) + (t * 128 + row) * 2;
+        __nv_bfloat16* xm_base = reinterpret_cast<__nv_bfloat16*>(base_ptr + kGXmOff) + row * 4;
         float m_ref = ninf, l = 0.f;
-        bool ok = n_t > 0;
-        for (int j = 0; ok && j < n_t; ++j) {
-            if (!(ok = mbar_wait(s_full(t), j & 1, abort_flag, 90))) break;
+        bool ok = true;
+        for (int j = 0; ok && j < n; ++j) {
+            if (!(ok = mbar_wait(s_done(j & 1), (j >> 1) & 1, abort_flag, 90))) break;
             if (threadIdx.x == 64) RT_FTRACE(6, j);
             tc_fence_after();
-            if (j > diag) {
-                // the pair's MMA ran one key tile beyond this row tile's diagonal: all masked
-                uint32_t z[16];
-#pragma unroll
-                for (int i = 0; i < 16; ++i) z[i] = 0u;
-                tmem_st_32x16(ts + 32u * hh, z);
-                tmem_st_32x16(ts + 32u * hh + 16u, z);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(p_leader);
-                continue;
-            }
+            // this thread's 64 scores in registers; then the score columns are free for the next tile
             uint32_t r0[32], r1[32];
-            tmem_ld_32x32(ts + 64u * hh, r0);
-            tmem_ld_32x32(ts + 64u * hh + 32u, r1);
+            tmem_ld_32x32(ts, r0);
+            tmem_ld_32x32(ts + 32u, r1);
             tmem_ld_wait(r0);
             tmem_ld_wait(r1);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(s_free_leader);
             if (threadIdx.x == 64) RT_FTRACE(7, j);
-            if (j == diag) {
-                const int c0 = 64 * hh;
+            if (j == n - 1) {                                 // diagonal tile: keys beyond the row's own are masked
+                const int c0 = 64 * cq;
 #pragma unroll
                 for (int i = 0; i < 32; ++i) {
-                    if (c0 + i > row) r0[i] = 0xff800000u;
-                    if (c0 + 32 + i > row) r1[i] = 0xff800000u;
+                    if (c0 + i > prow) r0[i] = 0xff800000u;
+                    if (c0 + 32 + i > prow) r1[i] = 0xff800000u;
                 }
             }
             float mx0 = ninf, mx1 = ninf, mx2 = ninf, mx3 = ninf;
@@ -1157,63 +1140,85 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
                 mx2 = fmaxf(mx2, __uint_as_float(r1[i]));
                 mx3 = fmaxf(mx3, __uint_as_float(r1[16 + i]));
             }
-            const __nv_bfloat16 mine = __float2bfloat16_rn(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2);
-            xm[hh] = mine;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            const float mt = fmaxf(__bfloat162float(mine), __bfloat162float(xm[hh ^ 1]));
+            // the four threads of a row exchange their maxima as bf16, so all use the same value;
+            // the slots alternate with the step, so a fast warp cannot overwrite one still being read
+            __nv_bfloat16* xm = xm_base + (j & 1) * 512;
+            xm[cq] = __float2bfloat16_rn(fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * a.scale_log2);
+            __syncwarp();
+            if (lane == 0) mbar_arrive(row_bar);
+            if (!(ok = mbar_wait(row_bar, j & 1, abort_flag, 93))) break;
+            const uint2 all = *reinterpret_cast<const uint2*>(xm_base + (j & 1) * 512);
+            const __nv_bfloat162 p01 = *reinterpret_cast<const __nv_bfloat162*>(&all.x);
+            const __nv_bfloat162 p23 = *reinterpret_cast<const __nv_bfloat162*>(&all.y);
+            const float mt = fmaxf(fmaxf(__low2float(p01), __high2float(p01)),
+                                   fmaxf(__low2float(p23), __high2float(p23)));
             const bool grow = mt > m_ref + 8.f;
             const float m_new = grow ? mt : m_ref;
-            if (j > 0 && __any_sync(0xffffffffu, grow)) {
-                const float alpha = grow ? ex2_approx(m_ref - m_new) : 1.f;
-                l *= alpha;
-#pragma unroll 1
-                for (int c = 8 * hh; c < 8 * (hh + 1); ++c) {            // 8 columns at a time
-                    uint32_t o[8];
-                    tmem_ld_32x8(to + 8u * c, o);
-                    tmem_ld_wait(o);
+            // the probabilities first, in registers: P(j - 1) still occupies the P columns
+            float s0 = 0.f, s1 = 0.f;
+            uint32_t pk0[16], pk1[16];
+#if defined(RT_FA_DIAG) && RT_FA_DIAG == 1      // diagnostic build only (wrong results): no exponentials
 #pragma unroll
-                    for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-                    tmem_st_32x8(to + 8u * c, o);
+            for (int i = 0; i < 16; ++i) { pk0[i] = r0[i]; pk1[i] = r1[i]; }
+#else
+            softmax_chunk<RT_FA_PAIR_POLY_EVERY>(r0, pk0, a.scale_log2, m_new, s0);
+            softmax_chunk<RT_FA_PAIR_POLY_EVERY>(r1, pk1, a.scale_log2, m_new, s1);
+#endif
+            if (threadIdx.x == 64) RT_FTRACE(8, j);
+            // P(j - 1) has been consumed and O is at rest once O += P(j - 1) V(j - 1) has completed
+            if (j > 0) {
+                if (!(ok = mbar_wait(pv_done((j - 1) & 1), ((j - 1) >> 1) & 1, abort_flag, 91))) break;
+                tc_fence_after();
+                if (__any_sync(0xffffffffu, grow)) {
+                    const float alpha = grow ? ex2_approx(m_ref - m_new) : 1.f;
+                    l *= alpha;
+#pragma unroll 1
+                    for (int c = 0; c < 4; ++c) {             // this thread's 32 output columns, 8 at a time
+                        uint32_t o[8];
+                        tmem_ld_32x8(to + 8u * c, o);
+                        tmem_ld_wait(o);
+#pragma unroll
+                        for (int i = 0; i < 8; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+                        tmem_st_32x8(to + 8u * c, o);
+                    }
                 }
             }
             m_ref = m_new;
-            float s0 = 0.f, s1 = 0.f;
-            uint32_t pk[16];
-            softmax_chunk(r0, pk, a.scale_log2, m_new, s0);
-            tmem_st_32x16(ts + 32u * hh, pk);
-            softmax_chunk(r1, pk, a.scale_log2, m_new, s1);
-            tmem_st_32x16(ts + 32u * hh + 16u, pk);
+            tmem_st_32x16(tp, pk0);
+            tmem_st_32x16(tp + 16u, pk1);
             l += s0 + s1;
             tmem_st_wait();
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(p_leader);
-            if (threadIdx.x == 64) RT_FTRACE(8, j);
-            if (threadIdx.x == 320) RT_FTRACE(9, j);
+            if (threadIdx.x == 64) RT_FTRACE(9, j);
         }
-        if (ok && n_t > 0 && (ok = mbar_wait(o_full(t), 0, abort_flag, 91))) {
+        if (ok && (ok = mbar_wait(pv_done((n - 1) & 1), ((n - 1) >> 1) & 1, abort_flag, 92))) {
             tc_fence_after();
-            float* xl = reinterpret_cast<float*>(base_ptr + kFQOff) + (t * 128 + row) * 2;
-            xl[hh] = l;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");
-            const float inv = 1.f / (l + xl[hh ^ 1]);
-            const int token = q0 + 128 * (2 * t + rank) + row;
-            __nv_bfloat16* orow = a.out + static_cast<int64_t>(token) * a.o_ts + static_cast<int64_t>(h) * a.o_hs;
-#pragma unroll 1
-            for (int c = 2 * hh; c < 2 * (hh + 1); ++c) {
-                uint32_t o[32];
-                tmem_ld_32x32(to + 32u * c, o);
-                tmem_ld_wait(o);
-                if (token < a.tokens) {
+            // the row's denominator is the sum of its four threads' partial sums: exchanged through
+            // the query tile's shared memory, which no MMA reads any more
+            float* xl = reinterpret_cast<float*>(base_ptr + kGQOff) + row * 4;
+            xl[cq] = l;
+            __syncwarp();
+            if (lane == 0) mbar_arrive(row_bar);
+            ok = mbar_wait(row_bar, n & 1, abort_flag, 93);
+            const float4 ls = *reinterpret_cast<const float4*>(xl);
+            const float inv = 1.f / ((ls.x + ls.y) + (ls.z + ls.w));
+            const int token = q0 + prow;
+            uint32_t o[32];
+            tmem_ld_32x32(to, o);
+            tmem_ld_wait(o);
+            if (ok && token < a.tokens) {
+                __nv_bfloat16* orow = a.out + static_cast<int64_t>(token) * a.o_ts +
+                                      static_cast<int64_t>(h) * a.o_hs + 32 * cq;
 #pragma unroll
-                    for (int v = 0; v < 4; ++v) {
-                        uint4 w;
-                        w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
-                        w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
-                        w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
-                        w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
-                        *reinterpret_cast<uint4*>(orow + 32 * c + 8 * v) = w;
-                    }
+                for (int v = 0; v < 4; ++v) {
+                    uint4 w;
+                    w.x = pack_bf16x2(__uint_as_float(o[8 * v + 0]) * inv, __uint_as_float(o[8 * v + 1]) * inv);
+                    w.y = pack_bf16x2(__uint_as_float(o[8 * v + 2]) * inv, __uint_as_float(o[8 * v + 3]) * inv);
+                    w.z = pack_bf16x2(__uint_as_float(o[8 * v + 4]) * inv, __uint_as_float(o[8 * v + 5]) * inv);
+                    w.w = pack_bf16x2(__uint_as_float(o[8 * v + 6]) * inv, __uint_as_float(o[8 * v + 7]) * inv);
+                    *reinterpret_cast<uint4*>(orow + 8 * v) = w;
                 }
             }
         }
@@ -1442,24 +1447,18 @@ extern "C" int rt_attn_causal_prefill(const void* q, const void* k_nope, const v
         tm_kp = tm_kn;
     }
     a.one_op = (one[0] ? 1 : 0) | (one[1] ? 2 : 0) | (one[2] ? 4 : 0) | (one[3] ? 8 : 0) | (one[4] ? 16 : 0);
-    if (tc::g_attn_schedule == 2 && nope_dim == 128 && rope_dim == 64 && v_dim == 128) {
-        // the MLA head shape on CTA pairs: every CTA of a pair brings half of each key / value tile.
-        // Measured at T = 8192 x 128 heads: 2417 us against 2314 us for the single-CTA schedule (the
-        // tensor pipe, not shared memory or L2, paces both), so the default stays single-CTA
+    const bool mla_shape = nope_dim == 128 && rope_dim == 64 && v_dim == 128;
+    if (mla_shape && (tc::g_attn_schedule == 2 || (tc::g_attn_schedule == 0 && tokens >= 1024))) {
+        // the MLA head shape on CTA pairs with key tiles of 256 keys: a CTA brings 128 keys of a
+        // tile (the boxes above) and 64 of the value dims for all of its 256 keys
         bool ignore;
-        if (int rc = tc::make_attn_tmap(&tm_kn, k_nope, nope_dim, tokens, heads, kn_token_stride, kn_head_stride,
-                                        &ignore, 64))
-            return rc;
-        if (int rc = tc::make_attn_tmap(&tm_kp, k_pe, rope_dim, tokens, pe_shared ? 1 : heads, kp_token_stride,
-                                        pe_shared ? kp_token_stride : kp_head_stride, &ignore, 64))
-            return rc;
         if (int rc = tc::make_attn_tmap(&tm_v, v, v_dim, tokens, heads, v_token_stride, v_head_stride, &ignore,
-                                        128, 1))
+                                        256, 1))
             return rc;
         if (int rc = ensure_dynamic_smem(reinterpret_cast<const void*>(&tc::attn_prefill_pair_kernel),
                                          static_cast<int>(tc::kGSmemBytes), "rt_attn_causal_prefill"))
             return rc;
-        dim3 pgrid(static_cast<unsigned>(2 * ((tokens + 511) / 512)), static_cast<unsigned>(heads));
+        dim3 pgrid(static_cast<unsigned>(2 * ((tokens + 255) / 256)), static_cast<unsigned>(heads));
         tc::attn_prefill_pair_kernel<<<pgrid, tc::kFThreads, tc::kGSmemBytes, as_stream(stream)>>>(
             tm_qn, tm_qp, tm_kn, tm_kp, tm_v, a);
         count_launch();

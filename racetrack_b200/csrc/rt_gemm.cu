@@ -763,8 +763,25 @@ struct TokenMaps {
 __device__ long long g_pair_trace[8 * 128];
 #define RT_TRACE(ev, it) \
     do { if (blockIdx.x == 0 && (it) < 128) g_pair_trace[(ev) * 128 + (it)] = clock64(); } while (0)
+// per pair and tile: nanosecond clock when the accumulator became free, when the last MMA of
+// the tile had been issued, and the tile's MMA width
+__device__ long long g_pair_tiles[74 * 128 * 3];
+__device__ __forceinline__ long long global_ns() {
+    long long t;
+    asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+    return t;
+}
+#define RT_TILE_TRACE(pair, i, ev, val) \
+    do { if ((pair) < 74 && (i) < 128) g_pair_tiles[((pair) * 128 + (i)) * 3 + (ev)] = (val); } while (0)
+// MMA thread of pair 0, per K block: before / after the operand wait, after the scale wait,
+// after the four MMAs, after the scale-slot commits, after the stage commits
+__device__ long long g_pair_mma[6 * 128];
+#define RT_MMA_TRACE(ev, it) \
+    do { if (blockIdx.x == 0 && (it) < 128) g_pair_mma[(ev) * 128 + (it)] = clock64(); } while (0)
 #else
+#define RT_MMA_TRACE(ev, it) do { } while (0)
 #define RT_TRACE(ev, it) do { } while (0)
+#define RT_TILE_TRACE(pair, i, ev, val) do { } while (0)
 #endif
 
 // Token rows one CTA of the pair fetches for a wide tile of `valid` rows: the power of two
@@ -879,6 +896,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
             int stage = 0, sf_slot = 0, it = 0;
             uint32_t phase = 0, sf_phase = 0, acc_phase = 0;
             bool ok = true;
+#ifdef RT_PAIR_TRACE
+            int tile_i = 0;
+#endif
             for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
                 const int4 tm = __ldg(wide_map + tile / num_w);
                 const uint32_t nh = static_cast<uint32_t>(pair_half_rows(tm.z));
@@ -887,13 +907,18 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                 const uint32_t idesc = (1u << 7) | (1u << 10) | ((n_mma >> 3) << 17) | (16u << 24);
                 if (!(ok = mbar_wait(tempty_bar, acc_phase ^ 1u, abort_flag, 22))) break;
                 tc_fence_after();
+                RT_TILE_TRACE(pair, tile_i, 0, global_ns());
+                RT_TILE_TRACE(pair, tile_i, 2, static_cast<long long>(n_mma));
                 for (int ds = 0; ok && ds < num_ds; ++ds) {
+                    RT_MMA_TRACE(0, it);
                     if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 23))) break;
+                    RT_MMA_TRACE(1, it);
                     const uint32_t sa = base + stage * kPStageBytes;
                     const int halves = min(2, num_kb - 2 * ds);
                     for (int h = 0; h < halves; ++h, ++it) {
                         if (!(ok = mbar_wait(ready_bar(sf_slot), sf_phase, abort_flag, 29))) break;
                         RT_TRACE(4, it);
+                        RT_MMA_TRACE(2, it);
                         tc_fence_after();
                         const uint32_t t_sfw = tmem_base + kPTmemSf + kPSfCols * sf_slot;
                         const uint32_t t_sfx = t_sfw + 16u;
@@ -905,9 +930,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                                            t_sfw + 4u * j, t_sfx + 8u * j,
                                            (ds | h | j) != 0 ? 1u : 0u);
                         }
+                        RT_MMA_TRACE(3, it);
                         mma_commit_pair(tsfree_bar(sf_slot));
                         mma_commit_pair(peer_tsfree0 + 8u * sf_slot);
                         RT_TRACE(5, it);
+                        RT_MMA_TRACE(4, it);
                         if (++sf_slot == kPSlots) {
                             sf_slot = 0;
                             sf_phase ^= 1u;
@@ -916,6 +943,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                     if (!ok) break;
                     mma_commit_pair(cempty_bar(stage));
                     mma_commit_pair(peer_cempty0 + 8u * stage);
+                    RT_MMA_TRACE(5, it - 1);
                     if (++stage == kPStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -925,6 +953,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                 mma_commit_pair(tfull_bar);
                 mma_commit_pair(peer_tfull);
                 acc_phase ^= 1u;
+#ifdef RT_PAIR_TRACE
+                RT_TILE_TRACE(pair, tile_i, 1, global_ns());
+                ++tile_i;
+#endif
             }
         } else if (rank == 1 && lane == 0) {
             // Relay: tells the leader that this CTA's operands of a stage have landed.
@@ -2126,6 +2158,19 @@ extern "C" int rt_gemm_nvfp4_grouped(const void* a_codes, const void* a_sf, cons
 extern "C" int rt_pair_trace_read(long long* host_out) {
     return cudaMemcpyFromSymbol(host_out, tc::g_pair_trace, sizeof(long long) * 8 * 128) == cudaSuccess
                ? RT_OK : RT_ERR_CUDA;
+}
+extern "C" int rt_pair_mma_read(long long* host_out) {
+    return cudaMemcpyFromSymbol(host_out, tc::g_pair_mma, sizeof(long long) * 6 * 128) == cudaSuccess
+               ? RT_OK : RT_ERR_CUDA;
+}
+extern "C" int rt_pair_tiles_read(long long* host_out, int clear) {
+    if (clear) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, tc::g_pair_tiles) != cudaSuccess) return RT_ERR_CUDA;
+        return cudaMemset(p, 0, sizeof(long long) * 74 * 128 * 3) == cudaSuccess ? RT_OK : RT_ERR_CUDA;
+    }
+    return cudaMemcpyFromSymbol(host_out, tc::g_pair_tiles, sizeof(long long) * 74 * 128 * 3) ==
+                   cudaSuccess ? RT_OK : RT_ERR_CUDA;
 }
 #endif
 

@@ -395,6 +395,25 @@ __device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
                      cluster_addr)
                  : "memory");
 }
+// One commit that arrives on the barrier at this shared-memory offset in BOTH CTAs of the pair
+// (a commit costs the issuing thread about as much as an MMA, so one instead of two matters).
+// The multicast here is of an mbarrier arrival, not of a load.
+#ifndef RT_COMMIT_BOTH_ONE
+#define RT_COMMIT_BOTH_ONE 1
+#endif
+__device__ __forceinline__ void mma_commit_pair_both(uint32_t bar) {
+#if RT_COMMIT_BOTH_ONE
+    const uint16_t both = 3;
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            bar),
+        "h"(both)
+        : "memory");
+#else
+    mma_commit_pair(bar);
+    mma_commit_pair(map_to_cta(bar, 1));
+#endif
+}
 
 }  // namespace tc
 }  // namespace rt

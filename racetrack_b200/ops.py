@@ -934,9 +934,9 @@ def causal_attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor) -> torch
 
 
 def attention_prefill_schedule(schedule: int) -> int:
-    """Selects the schedule of attention_prefill for this process (0 / 1 one CTA per 256 query
-    rows, the default; 2 CTA pairs where the head shape allows) and returns the previous
-    setting."""
+    """Selects the schedule of attention_prefill for this process (0 default = by shape and length,
+    1 one CTA per 256 query rows, 2 CTA pairs with key tiles of 256 where the head shape allows)
+    and returns the previous setting."""
     return int(_lib.load().rt_attn_prefill_schedule(int(schedule)))
 
 
