@@ -243,6 +243,7 @@ class PrefillStackWorkload:
         self.layer_mod, self.moe, self.ops = layer, moe, ops
         self.device, self.rank, self.world = device, rank, world
         layer.ATTENTION_CORE = args.attn_core
+        ops.attention_prefill_schedule({"auto": 0, "single": 1, "pair": 2}[getattr(args, "attn_schedule", "auto")])
         self.tokens, self.layers = args.tokens, args.layers
         if self.default_tokens != 8192 and args.tokens == 8192:
             self.tokens = self.default_tokens         # --tokens was not given
@@ -1150,6 +1151,9 @@ def main() -> None:
     ap.add_argument("--attn-core", default="rt", choices=("rt", "sdpa"),
                     help="attention core of the prefill layer: this backend's causal attention "
                          "kernel, or torch's SDPA as the yardstick it is measured against")
+    ap.add_argument("--attn-schedule", default="auto", choices=("auto", "single", "pair"),
+                    help="schedule of this backend's attention kernel: the library's choice by shape "
+                         "and length, one CTA per 256 query rows, or CTA pairs with key tiles of 256")
     ap.add_argument("--replicated", action="store_true",
                     help="multi-GPU: the reference's schedule (all tokens on every rank, two "
                          "all-reduces per layer) instead of the token-sharded one")

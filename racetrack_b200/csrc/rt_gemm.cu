@@ -719,20 +719,28 @@ __global__ void __launch_bounds__(kFThreads, 1) gemm_nvfp4_kernel(
 // scale factors do not use the TMA unit at all (16-byte cp.async copies by one warp).
 // Shared memory: 3 operand stages of 64 KB (weights [2][128 rows][128 B], tokens
 // [2][N/2 rows][128 B], 128-byte swizzle) and a ring of 5 scale slots of 6 KB.
-// Tensor memory: the accumulator D[weight row, token] takes 256 columns (one buffer), the
-// other 240 hold the scales of 5 K blocks; the epilogue drains the accumulator into
-// registers, releases it, and only then writes: lane = weight row = output column, so one
-// warp store covers 64 contiguous bytes of one token's output row.
+// Tensor memory: the accumulator D[weight row, token] takes 256 columns (one buffer), 192 more
+// hold the scales of two operand stages (per K block 16 columns of weight scales and 32 of
+// token scales); the epilogue drains the accumulator into registers, releases it, and only
+// then writes: lane = weight row = output column, so one warp store covers 64 contiguous bytes
+// of one token's output row.
+// What the issuing thread does per operand stage is the pace of this kernel once the operands
+// arrive in time: a tcgen05.mma costs it about 65 cycles, a commit as much and a barrier wait
+// 100 - 250, whatever the MMA's shape (trace of the first version: two waits, four MMAs and two
+// commits per K block, 800 cycles for 540 cycles of tensor work, the same for 16-token tiles).
+// So a stage is ONE wait, eight MMAs and ONE commit: the scale loaders arrive on the same
+// "stage full" barrier as the operands, and one multicast commit per stage tells both CTAs
+// that the stage's shared memory AND its scale columns are free.
 // Warps (both CTAs): 0 operand producer (one elected thread), 1 tensor-memory owner and MMA
 // issuer (leader CTA, cluster rank 0) or relay (peer: tells the leader that its operands have
 // landed), 2-5 scale loaders (shared -> tensor memory), 6-13 epilogue (lane quarter w % 4,
 // token half (w - 6) / 4), 14 scale producer.
-// Barriers per CTA: cfull[d] (operands of stage d landed; in the leader also the peer's
-// relay), cempty[d] (MMAs of stage d done), sfull[s] / sfree[s] (scale slot s filled in /
-// copied out of shared memory), tsfree[s] (MMAs that read scale slot s of tensor memory
-// done), tfull (accumulator complete); in the leader: ready[s] (scales of both CTAs in tensor
-// memory, 8 warp arrivals) and tempty (accumulator drained by the 16 epilogue warps of the
-// pair). The leader commits cempty, tsfree and tfull to both CTAs.
+// Barriers per CTA: cfull[d] (in the leader: operands of stage d landed in both CTAs and its
+// scales stored in the tensor memory of both, 2 + 8 arrivals; in the peer: its own operands),
+// sdone[d] (MMAs of stage d done: the producer may refill it, the scale loaders may overwrite
+// the scale columns it used), sfull[s] / sfree[s] (scale slot s of shared memory filled /
+// copied out), tfull (accumulator complete); in the leader: tempty (accumulator drained by the
+// 16 epilogue warps of the pair). The leader commits sdone and tfull to both CTAs.
 constexpr int kPStages = 3;                        // operand stages of two K blocks each
 constexpr int kPSlots = 5;                         // scale slots (shared and tensor memory)
 constexpr int kPThreads = 480;
@@ -744,13 +752,14 @@ constexpr uint32_t kPSfxBytes = 2 * 4 * 512;       // scale tiles of up to 256 t
 constexpr uint32_t kPSlotBytes = kPSfwBytes + kPSfxBytes;
 constexpr uint32_t kPSfOffset = kPStages * kPStageBytes;
 constexpr uint32_t kPBarOffset = kPSfOffset + kPSlots * kPSlotBytes;
-constexpr int kPBarriers = 2 * kPStages + 4 * kPSlots + 2;
+constexpr int kPBarriers = 2 * kPStages + 2 * kPSlots + 2;
 constexpr uint32_t kPSmemBytes = kPBarOffset + kPBarriers * 8 + 16 + 1024;
 constexpr uint32_t kPTmemCols = 512;
 constexpr uint32_t kPTmemSf = 256;                 // first scale column
-constexpr uint32_t kPSfCols = 48;                  // per slot: 16 weight + 32 token scale columns
+constexpr uint32_t kPSfCols = 48;                  // per K block: 16 weight + 32 token scale columns
+constexpr uint32_t kPSfStageCols = 2 * kPSfCols;   // per operand stage (two K blocks); two stages resident
 static_assert(kPStageBytes % 1024 == 0, "stages must keep the 1024-byte swizzle alignment");
-static_assert(kPTmemSf + kPSlots * kPSfCols <= kPTmemCols, "tensor memory budget");
+static_assert(kPTmemSf + 2 * kPSfStageCols <= kPTmemCols, "tensor memory budget");
 static_assert(kPSmemBytes <= 232448, "shared memory budget");
 
 struct TokenMaps {
@@ -803,12 +812,10 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
     uint8_t* base_ptr = smem_raw + (base - smem_u32(smem_raw));
     const uint32_t bars = base + kPBarOffset;
     auto cfull_bar = [&](int d) { return bars + 8u * d; };
-    auto cempty_bar = [&](int d) { return bars + 8u * (kPStages + d); };
+    auto sdone_bar = [&](int d) { return bars + 8u * (kPStages + d); };
     auto sfull_bar = [&](int s) { return bars + 8u * (2 * kPStages + s); };
     auto sfree_bar = [&](int s) { return bars + 8u * (2 * kPStages + kPSlots + s); };
-    auto tsfree_bar = [&](int s) { return bars + 8u * (2 * kPStages + 2 * kPSlots + s); };
-    auto ready_bar = [&](int s) { return bars + 8u * (2 * kPStages + 3 * kPSlots + s); };
-    const uint32_t tfull_bar = bars + 8u * (2 * kPStages + 4 * kPSlots);
+    const uint32_t tfull_bar = bars + 8u * (2 * kPStages + 2 * kPSlots);
     const uint32_t tempty_bar = tfull_bar + 8u;
     const uint32_t slot_addr = tfull_bar + 16u;
     volatile uint32_t* slot_ptr =
@@ -828,14 +835,13 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
     if (threadIdx.x == 0) {
         *abort_flag = 0;
         for (int d = 0; d < kPStages; ++d) {
-            mbar_init(cfull_bar(d), rank == 0 ? 2 : 1);   // own producer (+ the peer's relay)
-            mbar_init(cempty_bar(d), 1);
+            // own producer; in the leader also the peer's relay and the 4 scale-loader warps of each CTA
+            mbar_init(cfull_bar(d), rank == 0 ? 10 : 1);
+            mbar_init(sdone_bar(d), 1);
         }
         for (int s = 0; s < kPSlots; ++s) {
             mbar_init(sfull_bar(s), 32);     // 32 scale-copy lanes
             mbar_init(sfree_bar(s), 4);      // 4 scale-loader warps
-            mbar_init(tsfree_bar(s), 1);
-            mbar_init(ready_bar(s), 8);      // 4 scale-loader warps in each CTA of the pair
         }
         mbar_init(tfull_bar, 1);
         mbar_init(tempty_bar, 16);           // 8 epilogue warps in each CTA of the pair
@@ -870,7 +876,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                 const int xb = 31 - __clz(nh) - 3;           // index of the box with nh rows
                 const uint32_t bytes = kPWBytes + static_cast<uint32_t>(nh) * 256u;
                 for (int ds = 0; ds < num_ds; ++ds, ++it) {
-                    if (!(ok = mbar_wait(cempty_bar(stage), phase ^ 1u, abort_flag, 21))) break;
+                    if (!(ok = mbar_wait(sdone_bar(stage), phase ^ 1u, abort_flag, 21))) break;
                     const uint32_t sa = base + stage * kPStageBytes;
                     RT_TRACE(0, it);
                     mbar_arrive_expect_tx(cfull_bar(stage), bytes);
@@ -889,12 +895,8 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
         __syncwarp();
     } else if (warp == 1) {
         if (rank == 0 && lane == 0) {
-            // the peer's barriers sit at the same offsets of its shared-memory window
-            const uint32_t peer_cempty0 = map_to_cta(cempty_bar(0), 1);
-            const uint32_t peer_tsfree0 = map_to_cta(tsfree_bar(0), 1);
-            const uint32_t peer_tfull = map_to_cta(tfull_bar, 1);
-            int stage = 0, sf_slot = 0, it = 0;
-            uint32_t phase = 0, sf_phase = 0, acc_phase = 0;
+            int stage = 0, it = 0;
+            uint32_t phase = 0, acc_phase = 0, sf_par = 0;     // sf_par: which two-stage scale slot
             bool ok = true;
 #ifdef RT_PAIR_TRACE
             int tile_i = 0;
@@ -911,16 +913,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                 RT_TILE_TRACE(pair, tile_i, 2, static_cast<long long>(n_mma));
                 for (int ds = 0; ok && ds < num_ds; ++ds) {
                     RT_MMA_TRACE(0, it);
+                    // operands of both CTAs landed AND the stage's scales stored in tensor memory
                     if (!(ok = mbar_wait(cfull_bar(stage), phase, abort_flag, 23))) break;
                     RT_MMA_TRACE(1, it);
+                    tc_fence_after();
                     const uint32_t sa = base + stage * kPStageBytes;
                     const int halves = min(2, num_kb - 2 * ds);
                     for (int h = 0; h < halves; ++h, ++it) {
-                        if (!(ok = mbar_wait(ready_bar(sf_slot), sf_phase, abort_flag, 29))) break;
                         RT_TRACE(4, it);
                         RT_MMA_TRACE(2, it);
-                        tc_fence_after();
-                        const uint32_t t_sfw = tmem_base + kPTmemSf + kPSfCols * sf_slot;
+                        const uint32_t t_sfw = tmem_base + kPTmemSf + kPSfStageCols * sf_par + kPSfCols * h;
                         const uint32_t t_sfx = t_sfw + 16u;
                         const uint64_t adesc = smem_desc_sw128(sa + h * (kPWBytes / 2));
                         const uint64_t bdesc = smem_desc_sw128(sa + kPWBytes + h * nh * 128u);
@@ -931,27 +933,19 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                                            (ds | h | j) != 0 ? 1u : 0u);
                         }
                         RT_MMA_TRACE(3, it);
-                        mma_commit_pair(tsfree_bar(sf_slot));
-                        mma_commit_pair(peer_tsfree0 + 8u * sf_slot);
                         RT_TRACE(5, it);
                         RT_MMA_TRACE(4, it);
-                        if (++sf_slot == kPSlots) {
-                            sf_slot = 0;
-                            sf_phase ^= 1u;
-                        }
                     }
-                    if (!ok) break;
-                    mma_commit_pair(cempty_bar(stage));
-                    mma_commit_pair(peer_cempty0 + 8u * stage);
+                    mma_commit_pair_both(sdone_bar(stage));
                     RT_MMA_TRACE(5, it - 1);
+                    sf_par ^= 1u;
                     if (++stage == kPStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
                 if (!ok) break;
-                mma_commit_pair(tfull_bar);
-                mma_commit_pair(peer_tfull);
+                mma_commit_pair_both(tfull_bar);
                 acc_phase ^= 1u;
 #ifdef RT_PAIR_TRACE
                 RT_TILE_TRACE(pair, tile_i, 1, global_ns());
@@ -978,17 +972,22 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
         __syncwarp();
     } else if (warp < 6) {
         // Scale loaders: warp w serves the tensor-memory lanes [32 * (w % 4), +32) of its own CTA.
-        // Slot in tensor memory: 16 columns of weight scales (4 per 64-element K step), then 32
-        // columns of token scales (per K step: 4 for token rows 0-127, 4 for 128-255).
+        // Tensor memory holds the scales of two operand stages; per K block 16 columns of weight
+        // scales (4 per 64-element K step), then 32 columns of token scales (per K step: 4 for
+        // token rows 0-127, 4 for 128-255). The columns of stage g are those of stage g - 2, free
+        // once that stage's MMAs are done; a stage's last store is followed by one arrival per warp
+        // on the leader's "stage full" barrier.
         const int quad = warp & 3;
-        const uint32_t ready_leader = map_to_cta(ready_bar(0), 0);
-        int sf_slot = 0, it = 0;
-        uint32_t sf_phase = 0;
+        const uint32_t cfull_leader = map_to_cta(cfull_bar(0), 0);
+        int sf_slot = 0, it = 0, stage = 0, g = 0;       // g: operand stages handled so far
+        int done_stage = 0;                              // stage g - 2 (from g = 2 on): its ring index ...
+        uint32_t sf_phase = 0, done_phase = 0;           // ... and the parity of its completion
         bool ok = true;
         for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
             const int4 tm = __ldg(wide_map + tile / num_w);
             const bool two = tm.z > 128;
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                const int h = kb & 1;
                 if (!(ok = mbar_wait(sfull_bar(sf_slot), sf_phase, abort_flag, 24))) break;
                 if (warp == 2 && lane == 0) RT_TRACE(2, it);
                 const uint8_t* sf_smem = base_ptr + kPSfOffset + sf_slot * kPSlotBytes;
@@ -1008,17 +1007,27 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(sfree_bar(sf_slot));      // the shared slot may refill
-                // the MMAs that read this slot of tensor memory one lap ago are done
-                if (!(ok = mbar_wait(tsfree_bar(sf_slot), sf_phase ^ 1u, abort_flag, 30))) break;
-                tc_fence_after();
-                const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) +
-                                        kPTmemSf + kPSfCols * sf_slot;
+                if (h == 0 && g >= 2) {
+                    // the MMAs of stage g - 2, which read these columns of tensor memory, are done
+                    if (!(ok = mbar_wait(sdone_bar(done_stage), done_phase, abort_flag, 30))) break;
+                    tc_fence_after();
+                }
+                const uint32_t t_slot = tmem_base + (static_cast<uint32_t>(quad * 32) << 16) + kPTmemSf +
+                                        kPSfStageCols * static_cast<uint32_t>(g & 1) +
+                                        kPSfCols * static_cast<uint32_t>(h);
                 tmem_st_32x16(t_slot, rw);
                 tmem_st_32x32(t_slot + 16u, rx);
-                tmem_st_wait();
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) mbar_arrive_cluster(ready_leader + 8u * sf_slot);
+                if (h == 1 || kb == num_kb - 1) {
+                    tmem_st_wait();
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive_cluster(cfull_leader + 8u * stage);
+                    if (++stage == kPStages) stage = 0;
+                    if (++g > 2 && ++done_stage == kPStages) {
+                        done_stage = 0;
+                        done_phase ^= 1u;
+                    }
+                }
                 if (warp == 2 && lane == 0) RT_TRACE(3, it);
                 if (++sf_slot == kPSlots) {
                     sf_slot = 0;
