@@ -237,6 +237,11 @@ class PrefillStackWorkload:
     dominant = "gemm_nvfp4_kernel[experts w13]"
     ffn = "moe"          # "dense": the first-three-layers variant (SwiGLU FFN of width 18432)
     default_tokens = 8192
+    # The stack is replayed from a CUDA graph (racetrack/bench.py:98-111 captures its sweeps the
+    # same way): 61 layers x ~140 launches per step leave one Python thread per rank behind the
+    # GPU once the per-rank work shrinks (4 ranks: 176 ms eager, 165 ms replayed). --no-graph
+    # runs it eagerly.
+    graph_default = True
 
     def __init__(self, device, rank: int, world: int, args):
         from racetrack_b200 import layer, moe, ops
@@ -290,11 +295,10 @@ class PrefillStackWorkload:
 
         def timed(*a, **kw):
             if wl.recording and kw.get("n") == inter2:
-                s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                s, e = wl._event_pair()
                 s.record()
                 out = inner(*a, **kw)
                 e.record()
-                wl.dom_events.append((s, e))
                 return out
             return inner(*a, **kw)
 
@@ -307,11 +311,10 @@ class PrefillStackWorkload:
             def timed_linear(inner_fn, weight_arg):
                 def call(*a, **kw):
                     if wl.recording and a[weight_arg].shape[0] == rows13:
-                        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        s, e = wl._event_pair()
                         s.record()
                         out = inner_fn(*a, **kw)
                         e.record()
-                        wl.dom_events.append((s, e))
                         return out
                     return inner_fn(*a, **kw)
                 return call
@@ -403,6 +406,16 @@ class PrefillStackWorkload:
                              "states stream through the 126 MB L2 every layer)"}
 
     graph = None
+    capturing = False
+
+    def _event_pair(self):
+        """Two timing events around a launch of the dominant kernel. While the stack is being
+        captured they become event-record NODES of the graph (external events), so every replay
+        inside the timed region stamps them."""
+        s = torch.cuda.Event(enable_timing=True, external=self.capturing)
+        e = torch.cuda.Event(enable_timing=True, external=self.capturing)
+        (self.graph_events if self.capturing else self.dom_events).append((s, e))
+        return s, e
 
     def capture_graph(self):
         """Captures one forward of the stack in a CUDA graph (what racetrack/bench.py:98-111
@@ -416,8 +429,13 @@ class PrefillStackWorkload:
         torch.cuda.current_stream().wait_stream(side)
         before = _lib.launch_count()
         self.graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.graph):
-            self.graph_out = self._forward(self.hidden)
+        self.graph_events = []
+        self.capturing = self.recording = True
+        try:
+            with torch.cuda.graph(self.graph):
+                self.graph_out = self._forward(self.hidden)
+        finally:
+            self.capturing = self.recording = False
         self.launches_per_replay = _lib.launch_count() - before
 
     def step(self, record: bool = False):
@@ -1001,13 +1019,20 @@ def run_ours(args) -> None:
         torch.cuda.profiler.stop()
     launches = _lib.launch_count() - launches0
     ms_total = max_over_ranks(start.elapsed_time(end))
+    timed_in = None
     if use_graph:
-        # a replayed graph runs no host code: launches are those recorded at capture, and the
-        # dominant kernel is timed by events in two extra eager steps after the timed region
+        # a replayed graph runs no host code: launches are those recorded at capture. The dominant
+        # kernel is timed by event-record nodes captured around each of its launches, read after
+        # the last timed replay; a workload that captured none times it in two eager steps
         launches = wl.launches_per_replay * args.steps
-        for _ in range(2):
-            wl.step(record=True)
-        barrier()
+        if getattr(wl, "graph_events", None):
+            wl.dom_events = list(wl.graph_events)
+            timed_in = "event-record nodes of the replayed graph (the last timed step)"
+        else:
+            for _ in range(2):
+                wl.step(record=True)
+            barrier()
+            timed_in = "two eager steps after the replayed region"
     dom_us = statistics.mean(s.elapsed_time(e) for s, e in wl.dom_events) * 1e3
     # where the step's time goes between the ranks: one more eager step with CUDA events around
     # every collective (outside the timed region)
@@ -1016,7 +1041,7 @@ def run_ours(args) -> None:
     if distributed and group is not None:
         barrier()
         group.start_timing()
-        wl.step()
+        wl.step(record=True)         # eager even where the timed steps replay a graph
         per = group.stop_timing()
         layers = max(getattr(wl, "layers", 1), 1)
         comm_ms = max_over_ranks(sum(ms for _, ms, _ in per.values())) / layers
@@ -1110,7 +1135,7 @@ def run_ours(args) -> None:
             line["multi_gpu"] = comm_stats
         line["config"]["cuda_graph"] = bool(use_graph)
         if use_graph:
-            line["roofline"]["timed_in"] = "two eager steps after the replayed region"
+            line["roofline"]["timed_in"] = timed_in
         if world == 1 and not args.no_cpu:
             cpu = cpu_line(type(wl), 3, 1)
             cpu.pop("ms_per_step")

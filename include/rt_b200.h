@@ -667,6 +667,19 @@ int rt_peer_reduce_residual_norm(const void* const* partial_ptrs, int64_t world,
                                  int64_t cols, int64_t residual_stride, float eps, void* stream);
 
 /*
+ * All-gather of row-sharded buffers over peer memory: every rank has written its own block
+ * (bytes [rank * slice_bytes[b], (rank + 1) * slice_bytes[b]) of buffer b) into its own copy;
+ * the call copies the other ranks' blocks out of their copies (peer_ptrs[b * world + q] = buffer
+ * b of rank q as mapped into this process) into the local copy, so that afterwards the local
+ * buffer holds all blocks. Up to 4 buffers per call, one launch. Call rt_peer_barrier first.
+ * Peer memory is read with plain loads over NVLink.
+ * ref: the all-gather half of the reference's all-reduce, racetrack/realistic_bench.py:315-316,351,
+ *      moved behind the token-wise kernels (RMSNorm, router, quantisation) that follow it.
+ */
+int rt_peer_gather(const void* const* peer_ptrs, const int64_t* slice_bytes, int64_t n_buffers,
+                   int64_t rank, int64_t world, void* stream);
+
+/*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when
  * one of its bounded waits expired. RT_OK when no kernel gave up since the last call,
  * RT_ERR_TIMEOUT otherwise. Call after synchronising the stream; not graph-capturable.

@@ -15,6 +15,11 @@
 //                              fp32, rounded to bf16 like the all-reduced tensor, then residual
 //                              add + RMSNorm exactly as residual_norm_kernel does. The summed
 //                              tensor never exists in memory.
+//   peer_gather_kernel         the all-gather of row-sharded buffers: every rank has written its
+//                              own block of rows into its own copy of the buffer; the kernel pulls
+//                              the other ranks' blocks out of their copies into the local one, up
+//                              to four buffers per launch (the compact outputs of the token-wise
+//                              kernels: latent projection, NVFP4 codes, block scales, routing).
 #include <string.h>
 
 #include "rt_common.cuh"
@@ -119,6 +124,41 @@ __global__ void __launch_bounds__(512) peer_reduce_norm_kernel(
             for (int k = 0; k < 8; ++k) o[k] = w[k] * (h[i][k] * rs);
             st_stream16(nrow + v, pack_bf16x8(o));
         }
+    }
+}
+
+constexpr int kMaxGather = 4;
+struct GatherArgs {
+    const uint4* src[kMaxGather][kMaxPeers];   // buffer b as mapped from rank q
+    uint4* dst[kMaxGather];                    // the local copy of buffer b
+    int64_t slice_vec[kMaxGather];             // 16-byte vectors per rank's block of buffer b
+};
+
+// grid (CTAs, buffers). A CTA walks the (world - 1) foreign blocks of its buffer in 16-byte
+// vectors, four loads in flight per thread.
+__global__ void __launch_bounds__(256) peer_gather_kernel(GatherArgs a, int rank, int world) {
+    const int b = blockIdx.y;
+    const int64_t slice = a.slice_vec[b];
+    const int64_t total = slice * (world - 1);
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    uint4* dst = a.dst[b];
+    for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+        uint4 v[4];
+        int64_t off[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t i = i0 + u * stride;
+            off[u] = -1;
+            if (i < total) {
+                const int k = static_cast<int>(i / slice);
+                const int q = k + (k >= rank ? 1 : 0);
+                off[u] = static_cast<int64_t>(q) * slice + (i - static_cast<int64_t>(k) * slice);
+                v[u] = ld_once16(a.src[b][q] + off[u]);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (off[u] >= 0) dst[off[u]] = v[u];
     }
 }
 
@@ -264,4 +304,41 @@ extern "C" int rt_peer_reduce_residual_norm(const void* const* partial_ptrs, int
 #undef RT_LAUNCH_PR
     count_launch();
     return check_launch("peer_reduce_norm_kernel");
+}
+
+extern "C" int rt_peer_gather(const void* const* peer_ptrs, const int64_t* slice_bytes, int64_t n_buffers,
+                              int64_t rank, int64_t world, void* stream) {
+    RT_REQUIRE(peer_ptrs && slice_bytes, RT_ERR_BAD_ARG, "rt_peer_gather: null pointer");
+    RT_REQUIRE(n_buffers >= 1 && n_buffers <= kMaxGather, RT_ERR_BAD_ARG, "rt_peer_gather: 1 to %d buffers",
+               kMaxGather);
+    RT_REQUIRE(world >= 1 && world <= kMaxPeers && rank >= 0 && rank < world, RT_ERR_BAD_ARG,
+               "rt_peer_gather: bad rank / world (at most %d ranks)", kMaxPeers);
+    if (world == 1) return RT_OK;
+    GatherArgs a;
+    int64_t most = 0;
+    for (int b = 0; b < kMaxGather; ++b) {
+        a.dst[b] = nullptr;
+        a.slice_vec[b] = 0;
+        for (int q = 0; q < kMaxPeers; ++q) a.src[b][q] = nullptr;
+        if (b >= n_buffers) continue;
+        RT_REQUIRE(slice_bytes[b] >= 0 && slice_bytes[b] % 16 == 0, RT_ERR_BAD_ARG,
+                   "rt_peer_gather: a rank's block must be a multiple of 16 bytes");
+        a.slice_vec[b] = slice_bytes[b] / 16;
+        for (int q = 0; q < world; ++q) {
+            const void* p = peer_ptrs[b * world + q];
+            RT_REQUIRE(p && aligned16(p), RT_ERR_BAD_ARG,
+                       "rt_peer_gather: buffer pointers must be non-null and 16-byte aligned");
+            a.src[b][q] = static_cast<const uint4*>(p);
+        }
+        a.dst[b] = const_cast<uint4*>(a.src[b][rank]);
+        const int64_t total = a.slice_vec[b] * (world - 1);
+        if (total > most) most = total;
+    }
+    if (most == 0) return RT_OK;
+    int64_t ctas = (most + 4 * 256 - 1) / (4 * 256);
+    if (ctas > 4 * 148) ctas = 4 * 148;
+    const dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(n_buffers));
+    peer_gather_kernel<<<grid, 256, 0, as_stream(stream)>>>(a, (int)rank, (int)world);
+    count_launch();
+    return check_launch("peer_gather_kernel");
 }

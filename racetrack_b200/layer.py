@@ -173,6 +173,7 @@ class Projection:
 
     def __init__(self, weight: torch.Tensor, dtype: str):
         k = weight.shape[1]
+        self.out_features = weight.shape[0]
         self.fp8 = k % 128 == 0 and (dtype == "fp8" or (dtype == "mixed" and k >= self.MIXED_FP8_MIN_K))
         if self.fp8:
             self.codes, self.scales = ops.quantize_weight_fp8(weight)
@@ -270,14 +271,14 @@ class RealisticLayer:
             local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
         return self.w_o(local.reshape(tokens, h * s.v_dim), out=out)
 
-    def _route(self, normed: torch.Tensor):
+    def _route(self, normed: torch.Tensor, out: Optional[tuple] = None):
         """Router of racetrack/realistic_bench.py:321-327 for the given rows: fp32 logits of bf16
         operands (tensor cores, fp32 accumulators kept), top-k, softmax over the k logits."""
         logits = ops.linear_bf16(normed, self.w_gate, out_dtype=torch.float32)
         if self.route != "topk_softmax":
             raise ValueError(f"unknown route {self.route!r}")
         return ops.fused_moe_route(logits, None, n_groups=1, topk_groups=1, topk=self.shape.topk,
-                                   route_scale=1.0, score_func="topk_softmax")
+                                   route_scale=1.0, score_func="topk_softmax", out=out)
 
     def ffn_forward(self, normed: torch.Tensor) -> torch.Tensor:
         """racetrack/realistic_bench.py:319-352 (routed experts) or a dense SwiGLU FFN."""
@@ -297,8 +298,8 @@ class RealisticLayer:
                 out = self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]))
         return self._all_reduce(out)
 
-    def ffn_partial_from_rows(self, normed_rows: torch.Tensor,
-                              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    def ffn_partial_from_rows(self, normed_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
+                              px=None) -> torch.Tensor:
         """Token-sharded feed-forward half: `normed_rows` are this rank's T / world rows of the
         normalised hidden states; returns this rank's partial sum [T, H] over ALL tokens (its
         experts' / its FFN columns' share). Routing and quantisation run on the rank's rows, their
@@ -306,12 +307,23 @@ class RealisticLayer:
         scales (dense FFN with FP8 weights) instead of bf16 hidden states."""
         s, c = self.shape, self.comm
         if self.ffn == "moe":
-            weights, indices = self._route(normed_rows)
             # one tensor-wide NVFP4 scale whatever the world size: the maximum over all ranks' rows
             amax = c.all_reduce_max(ops.tensor_absmax(normed_rows))
-            codes, sf, gs = ops.fused_nvfp4_quant(normed_rows, amax=amax)
-            codes, sf = c.all_gather_rows(codes), c.all_gather_rows(sf.view(torch.uint8))
-            weights, indices = c.all_gather_rows(weights), c.all_gather_rows(indices)
+            if px is not None:
+                # routing and quantisation write this rank's rows of the exchange buffers; one
+                # device barrier and one kernel then pull the other ranks' rows over NVLink
+                lo, hi = c.rows_of(px.local["moe_codes"].shape[0])
+                self._route(normed_rows, out=(px.local["moe_w"][lo:hi], px.local["moe_i"][lo:hi]))
+                _, _, gs = ops.fused_nvfp4_quant(normed_rows, amax=amax,
+                                                 out=(px.local["moe_codes"][lo:hi], px.local["moe_sf"][lo:hi]))
+                px.gather("moe_codes", "moe_sf", "moe_w", "moe_i")
+                codes, sf = px.local["moe_codes"], px.local["moe_sf"]
+                weights, indices = px.local["moe_w"], px.local["moe_i"]
+            else:
+                weights, indices = self._route(normed_rows)
+                codes, sf, gs = ops.fused_nvfp4_quant(normed_rows, amax=amax)
+                codes, sf = c.all_gather_rows(codes), c.all_gather_rows(sf.view(torch.uint8))
+                weights, indices = c.all_gather_rows(weights), c.all_gather_rows(indices)
             return moe.fused_moe_experts(None, weights, indices, self.experts, n_experts=s.n_experts,
                                          expert_begin=self.rank * self.local_experts,
                                          x_quant=(codes, sf, gs), out=out)
@@ -355,15 +367,21 @@ class RealisticLayer:
         normed = ops.fused_rms_norm(mine, self.ones_h, eps=s.eps)
         px = self._peer_exchange(tokens) if self.peer_reduce and hidden.is_cuda else None
         for _ in range(layers):
-            qkv = c.all_gather_rows(self.w_qkv_a(normed))              # [T, 2112]: 0.3 of a hidden row
             if px is not None:
-                # the partial sums land in buffers the other ranks have mapped; reduce-scatter,
-                # residual add and RMSNorm are ONE kernel that reads them over NVLink
-                self.attention_partial(qkv, positions, out=px.local["attn"])
+                # every exchange goes through buffers the other ranks have mapped. All-gather: the
+                # latent projection ([T, 2112]: 0.3 of a hidden row) lands in this rank's rows of
+                # its copy and the peers' rows are pulled over NVLink. Reduce-scatter: the partial
+                # sums stay where they are computed; reduce, residual add and RMSNorm are ONE
+                # kernel that reads them from every rank.
+                self.w_qkv_a(normed, out=px.local["qkv"][lo:hi])
+                px.gather("qkv")
+                self.attention_partial(px.local["qkv"], positions, out=px.local["attn"])
                 normed, mine = px.reduce_residual_norm("attn", mine, self.ones_h, eps=s.eps)
-                self.ffn_partial_from_rows(normed, out=px.local["ffn"])
+                self.ffn_partial_from_rows(normed, out=px.local["ffn"],
+                                           px=px if self.ffn == "moe" else None)
                 normed, mine = px.reduce_residual_norm("ffn", mine, self.ones_h, eps=s.eps)
                 continue
+            qkv = c.all_gather_rows(self.w_qkv_a(normed))
             attn = c.reduce_scatter_rows(self.attention_partial(qkv, positions))
             normed, mine = ops.fused_residual_norm(attn, mine, self.ones_h, eps=s.eps)
             ffn = c.reduce_scatter_rows(self.ffn_partial_from_rows(normed))
@@ -375,8 +393,15 @@ class RealisticLayer:
         from . import peer
         px = self._peer.get(tokens)
         if px is None:
-            shape = (tokens, self.shape.hidden)
-            px = peer.PeerExchange(self.comm, self.ones_h.device,
-                                   {"attn": (shape, torch.bfloat16), "ffn": (shape, torch.bfloat16)})
+            s = self.shape
+            shape = (tokens, s.hidden)
+            buffers = {"attn": (shape, torch.bfloat16), "ffn": (shape, torch.bfloat16),
+                       "qkv": ((tokens, self.w_qkv_a.out_features), torch.bfloat16)}
+            if self.ffn == "moe":
+                buffers.update({"moe_codes": ((tokens, s.hidden // 2), torch.uint8),
+                                "moe_sf": ((tokens, s.hidden // 16), torch.uint8),
+                                "moe_w": ((tokens, s.topk), torch.float32),
+                                "moe_i": ((tokens, s.topk), torch.int64)})
+            px = peer.PeerExchange(self.comm, self.ones_h.device, buffers)
             self._peer[tokens] = px
         return px

@@ -352,14 +352,15 @@ def sf_tiled_bytes(rows: int, cols: int) -> int:
 
 def fused_nvfp4_quant(x: torch.Tensor, *, up: Optional[torch.Tensor] = None,
                       amax: Optional[torch.Tensor] = None, tiled_scales: bool = False,
-                      fallback: Optional[Callable] = None):
+                      out: Optional[tuple] = None, fallback: Optional[Callable] = None):
     """NVFP4 quantisation -> (codes uint8 [..., N/2], block_scales float8_e4m3fn, global_scale fp32[1]).
 
     16-element blocks, e2m1 codes (element 2i in the low nibble), e4m3 block scale and
     one fp32 global scale = amax / (448 * 6). ``amax`` (1-element fp32 CUDA tensor) skips the
     abs-max pass when the caller already knows it. With ``up`` the quantised tensor is
     swiglu(x, up). ``tiled_scales`` selects the 128x4-tiled scale layout the block-scaled
-    tensor-core GEMM consumes; otherwise scales are [..., N/16] row-major.
+    tensor-core GEMM consumes; otherwise scales are [..., N/16] row-major. ``out`` = (codes, scales)
+    uint8 tensors of exactly those shapes to write into (e.g. a rank's rows of an exchange buffer).
     racetrack has no NVFP4 arithmetic; the format follows the build's stated configuration.
     """
     del fallback
@@ -375,11 +376,19 @@ def fused_nvfp4_quant(x: torch.Tensor, *, up: Optional[torch.Tensor] = None,
     if amax is None:
         amax = tensor_absmax(x, up)
     rows = x2.shape[0]
-    codes = torch.empty(*x.shape[:-1], n // 2, dtype=torch.uint8, device=x.device)
-    if tiled_scales:
-        sf = torch.empty(sf_tiled_bytes(rows, n), dtype=torch.uint8, device=x.device)
+    if out is not None:
+        codes, sf = out
+        want_sf = (sf_tiled_bytes(rows, n),) if tiled_scales else (*x.shape[:-1], n // 16)
+        if (codes.dtype != torch.uint8 or sf.dtype != torch.uint8 or not codes.is_contiguous()
+                or not sf.is_contiguous() or tuple(codes.shape) != (*x.shape[:-1], n // 2)
+                or tuple(sf.shape) != tuple(want_sf)):
+            raise RuntimeError("fused_nvfp4_quant: out must be contiguous uint8 (codes [..., N/2], scales)")
     else:
-        sf = torch.empty(*x.shape[:-1], n // 16, dtype=torch.uint8, device=x.device)
+        codes = torch.empty(*x.shape[:-1], n // 2, dtype=torch.uint8, device=x.device)
+        if tiled_scales:
+            sf = torch.empty(sf_tiled_bytes(rows, n), dtype=torch.uint8, device=x.device)
+        else:
+            sf = torch.empty(*x.shape[:-1], n // 16, dtype=torch.uint8, device=x.device)
     gs = torch.empty(1, dtype=torch.float32, device=x.device)
     lib = _lib.load()
     _lib.check(lib.rt_nvfp4_quant(x2.data_ptr(), u2.data_ptr() if u2 is not None else None,
@@ -401,9 +410,11 @@ def fused_swiglu_nvfp4_quant(gate: torch.Tensor, up: torch.Tensor, **kw):
 
 def fused_moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], *, n_groups: int,
                     topk_groups: int, topk: int, route_scale: float,
-                    score_func: str = "sigmoid", fallback: Optional[Callable] = None):
+                    score_func: str = "sigmoid", out: Optional[tuple] = None,
+                    fallback: Optional[Callable] = None):
     """(weights fp32 [T, topk], indices int64 [T, topk]) from fp32 router logits [T, E];
-    everything in Gate.forward after the logits GEMM (racetrack/models/deepseek.py:899-920)."""
+    everything in Gate.forward after the logits GEMM (racetrack/models/deepseek.py:899-920).
+    ``out`` = (weights, indices) contiguous tensors of those shapes to write into."""
     del fallback
     _require_cuda(logits)
     if logits.dtype != torch.float32 or logits.dim() != 2:
@@ -413,8 +424,15 @@ def fused_moe_route(logits: torch.Tensor, bias: Optional[torch.Tensor], *, n_gro
     if bias is not None:
         bias = bias.to(torch.float32).contiguous()
     tokens, n_experts = logits.shape
-    weights = torch.empty(tokens, topk, dtype=torch.float32, device=logits.device)
-    indices = torch.empty(tokens, topk, dtype=torch.int64, device=logits.device)
+    if out is not None:
+        weights, indices = out
+        if (weights.dtype != torch.float32 or indices.dtype != torch.int64 or not weights.is_contiguous()
+                or not indices.is_contiguous() or tuple(weights.shape) != (tokens, topk)
+                or tuple(indices.shape) != (tokens, topk)):
+            raise RuntimeError("fused_moe_route: out must be contiguous (fp32 [T, topk], int64 [T, topk])")
+    else:
+        weights = torch.empty(tokens, topk, dtype=torch.float32, device=logits.device)
+        indices = torch.empty(tokens, topk, dtype=torch.int64, device=logits.device)
     func = {"sigmoid": _lib.RT_SCORE_SIGMOID, "softmax": _lib.RT_SCORE_SOFTMAX,
             "topk_softmax": _lib.RT_SCORE_TOPK_SOFTMAX}[score_func]
     lib = _lib.load()

@@ -37,6 +37,20 @@ class _RawCuda:
                                          "version": 3, "strides": None}
 
 
+class _Bytes:
+    """Stands in for a payload tensor where the group's timing wants a byte count."""
+    is_cuda = True
+
+    def __init__(self, nbytes: int):
+        self._n = int(nbytes)
+
+    def numel(self) -> int:
+        return self._n
+
+    def element_size(self) -> int:
+        return 1
+
+
 def _as_tensor(ptr: int, shape: tuple, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
     nbytes = int(torch.empty((), dtype=dtype).element_size())
     for d in shape:
@@ -139,6 +153,27 @@ class PeerExchange:
             ops._weight_tag(w), normed.data_ptr(), hidden.data_ptr(), hi - lo, cols, res.stride(0),
             float(eps), ops._stream()), "rt_peer_reduce_residual_norm")
         return normed, hidden
+
+    def gather(self, *names: str) -> None:
+        """All-gather of the named row-sharded buffers (at most four): every rank has written its
+        own rows [rows_of(T)] of its local copy; after the call the local copies hold all rows.
+        Includes the barrier that makes every rank's rows visible."""
+        lib = _lib.load()
+        ptrs, slices = [], []
+        for name in names:
+            buf = self.local[name]
+            nbytes = buf.numel() * buf.element_size()
+            if buf.shape[0] % self.world or (nbytes // self.world) % 16:
+                raise RuntimeError(f"peer gather: buffer {name!r} does not split into 16-byte aligned blocks")
+            ptrs.extend(self._mapped[name])
+            slices.append(nbytes // self.world)
+        c_ptrs = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        c_slices = (ctypes.c_int64 * len(slices))(*slices)
+        self.group._timed("peer_barrier (wait for the slowest rank)", self.flags, self.barrier)
+        payload = _Bytes(sum(slices) * (self.world - 1))      # what crosses NVLink into this rank
+        self.group._timed("peer_gather", payload, lambda: _lib.check(
+            lib.rt_peer_gather(c_ptrs, c_slices, len(slices), self.rank, self.world, ops._stream()),
+            "rt_peer_gather"))
 
     def check(self) -> None:
         """Synchronises and raises if a barrier gave up waiting for a rank."""

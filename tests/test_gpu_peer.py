@@ -56,9 +56,27 @@ def _two_ranks(rank: int, world: int, port: int, out_dir: str):
         w = torch.ones(hidden, device=dev)
         grp = comm.Group(rank, world)
         px = peer.PeerExchange(grp, dev, {"attn": ((tokens, hidden), torch.bfloat16),
-                                          "ffn": ((tokens, hidden), torch.bfloat16)})
+                                          "ffn": ((tokens, hidden), torch.bfloat16),
+                                          "codes": ((tokens, 3584), torch.uint8),
+                                          "w": ((tokens, 8), torch.float32),
+                                          "i": ((tokens, 8), torch.int64)})
         lo, hi = grp.rows_of(tokens)
         ok = True
+        # all-gather over peer memory: every rank fills its rows, one call pulls the others'
+        full = {"codes": torch.randint(0, 256, (tokens, 3584), generator=g, dtype=torch.uint8),
+                "w": torch.randn(tokens, 8, generator=g),
+                "i": torch.randint(0, 256, (tokens, 8), generator=g)}
+        for rnd in range(2):
+            for name, t in full.items():
+                px.local[name].zero_()
+                px.local[name][lo:hi].copy_((t + rnd).to(dev)[lo:hi])
+            px.gather("codes", "w", "i")
+            px.check()
+            for name, t in full.items():
+                ok = ok and torch.equal(px.local[name].cpu(), t + rnd)
+            # nobody zeroes its buffer for the next round while a peer still reads it: the
+            # reduce below (or, in the layer, the next exchange) brings its own barrier
+            px.barrier()
         for name in ("attn", "ffn", "attn"):
             px.local[name].copy_(parts[rank].to(dev))
             normed, summed = px.reduce_residual_norm(name, res[lo:hi].to(dev), w, eps=1e-6)
