@@ -438,6 +438,16 @@ class PrefillStackWorkload:
             self.capturing = self.recording = False
         self.launches_per_replay = _lib.launch_count() - before
 
+    def capture_timing_graph(self, group):
+        """A second graph of the same forward with the group's timing events captured as nodes;
+        returns the function that replays it."""
+        g = torch.cuda.CUDAGraph()
+        group.start_timing(in_graph=True)
+        with torch.cuda.graph(g):
+            self._timing_out = self._forward(self.hidden)
+        self._timing_graph = g
+        return g.replay
+
     def step(self, record: bool = False):
         if self.graph is not None and not record:
             self.graph.replay()
@@ -1040,8 +1050,16 @@ def run_ours(args) -> None:
     group = getattr(getattr(wl, "model", None), "comm", None)
     if distributed and group is not None:
         barrier()
-        group.start_timing()
-        wl.step(record=True)         # eager even where the timed steps replay a graph
+        if use_graph and hasattr(wl, "capture_timing_graph"):
+            # a second capture of the same stack with event-record nodes around every collective:
+            # replayed like the timed steps, so the intervals carry no host launch skew
+            replay = wl.capture_timing_graph(group)
+            barrier()
+            replay()
+            replay()
+        else:
+            group.start_timing()
+            wl.step(record=True)
         per = group.stop_timing()
         layers = max(getattr(wl, "layers", 1), 1)
         comm_ms = max_over_ranks(sum(ms for _, ms, _ in per.values())) / layers

@@ -34,10 +34,13 @@ class Group:
         self._no_reduce_scatter = world > 1 and dist.get_backend(group) == "gloo"
         self.events = None          # a list while timing: (name, bytes sent by this rank, start, end)
 
-    def start_timing(self) -> None:
+    def start_timing(self, in_graph: bool = False) -> None:
         """From now on every collective is bracketed by CUDA events on the current stream (the
-        interval includes the wait for the collective's input, as the layer experiences it)."""
+        interval includes the wait for the collective's input, as the layer experiences it).
+        `in_graph`: the calls are about to be captured into a CUDA graph; the events become
+        event-record nodes of the graph and are read after a replay."""
         self.events = []
+        self._external = bool(in_graph)
 
     def stop_timing(self) -> dict:
         """{name: (calls, total ms, total payload bytes)} of the collectives since start_timing."""
@@ -47,12 +50,15 @@ class Group:
             calls, ms, total = out.get(name, (0, 0.0, 0))
             out[name] = (calls + 1, ms + start.elapsed_time(end), total + nbytes)
         self.events = None
+        self._external = False
         return out
 
     def _timed(self, name: str, payload: torch.Tensor, fn):
         if self.events is None or not payload.is_cuda:
             return fn()
-        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        ext = getattr(self, "_external", False)
+        start = torch.cuda.Event(enable_timing=True, external=ext)
+        end = torch.cuda.Event(enable_timing=True, external=ext)
         start.record()
         result = fn()
         end.record()
