@@ -184,6 +184,14 @@ def gemm_cases(tokens: int) -> dict[str, tuple[Callable[[], object], int, int, s
         out[f"attention_prefill[{T} tokens x {heads} heads]"] = (
             (lambda q=q, kv=kv, kpe=kpe: ops.attention_prefill(q, kv[..., :128], kpe, kv[..., 128:])),
             flops, nbytes, "bf16")
+
+        def single(q=q, kv=kv, kpe=kpe):      # the single-CTA schedule whatever the length
+            prev = ops.attention_prefill_schedule(1)
+            try:
+                return ops.attention_prefill(q, kv[..., :128], kpe, kv[..., 128:])
+            finally:
+                ops.attention_prefill_schedule(prev)
+        out[f"attention_prefill/single[{T} tokens x {heads} heads]"] = (single, flops, nbytes, "bf16")
         k_full = torch.cat((kv[..., :128], kpe.unsqueeze(1).expand(-1, heads, -1)), dim=-1)
 
         def sdpa(q=q, k=k_full, v=kv[..., 128:]):
