@@ -254,10 +254,14 @@ class PrefillStackWorkload:
             self.tokens = self.default_tokens         # --tokens was not given
         self.shape = layer.DSV32
         self.ffn = args.ffn
+        # several ranks: every rank also holds the whole output projection, so the attention half
+        # exchanges the heads' outputs instead of reducing partial sums (--reduce-w-o: the latter)
+        full_w_o = world > 1 and not args.replicated and not getattr(args, "reduce_w_o", False) \
+            and not args.nccl_reduce
         if self.ffn == "dense":
-            w = layer.make_weights(self.shape, rank, world, device, ffn="dense", std=0.02)
+            w = layer.make_weights(self.shape, rank, world, device, ffn="dense", std=0.02, full_w_o=full_w_o)
         else:
-            w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02)
+            w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02, full_w_o=full_w_o)
             w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
         self.proj = args.proj
         self.schedule = args.nvfp4_schedule
@@ -1067,8 +1071,10 @@ def run_ours(args) -> None:
                       "collectives_per_layer": {k: {"calls": c / layers, "ms": ms / layers,
                                                     "payload_mb": b / layers / 1e6}
                                                 for k, (c, ms, b) in per.items()},
-                      "schedule": "token-sharded: reduce-scatter -> token-wise kernels on T/N rows -> "
-                                  "all-gather of their compact outputs"
+                      "schedule": ("token-sharded: reduce-scatter -> token-wise kernels on T/N rows -> "
+                                   "all-gather of their compact outputs"
+                                   + ("; attention half: heads' outputs exchanged, whole w_o on the rank's rows"
+                                      if getattr(wl.model, "w_o_full", None) is not None else ""))
                       if getattr(wl.model, "token_sharded", False) else "replicated tokens, all-reduce"}
 
     wl.e2e_setup()
@@ -1200,6 +1206,9 @@ def main() -> None:
     ap.add_argument("--replicated", action="store_true",
                     help="multi-GPU: the reference's schedule (all tokens on every rank, two "
                          "all-reduces per layer) instead of the token-sharded one")
+    ap.add_argument("--reduce-w-o", action="store_true",
+                    help="multi-GPU: keep the output projection row-sharded and reduce its partial sums "
+                         "(the reference's arithmetic) instead of exchanging the heads' attention outputs")
     ap.add_argument("--nccl-reduce", action="store_true",
                     help="multi-GPU: NCCL reduce-scatter + the plain residual-norm kernel instead of "
                          "the fused kernel that reads the peers' partial sums over NVLink")

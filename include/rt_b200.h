@@ -680,6 +680,22 @@ int rt_peer_gather(const void* const* peer_ptrs, const int64_t* slice_bytes, int
                    int64_t rank, int64_t world, void* stream);
 
 /*
+ * The transposing exchange in front of a row-sharded consumer: buffer b of rank q
+ * (peer_ptrs[b * world + q], as mapped into this process) holds that rank's column block
+ * [T, src_row_bytes[b]] of a [T, world * src_row_bytes[b]] byte matrix for ALL rows; the call
+ * assembles this rank's rows of the whole matrix:
+ *   dst_b[r, q * src_row_bytes[b] + c] = src_b,q[row0 + r, c]        r < rows
+ * dst_ptrs[b] is local memory of rows * world * src_row_bytes[b] bytes. Up to 4 buffers per call,
+ * one launch; call rt_peer_barrier first.
+ * ref: replaces the all-reduce after the head-sharded output projection,
+ *      racetrack/realistic_bench.py:314-316: every rank gathers all heads' attention outputs (FP8
+ *      codes + scales, or bf16) for ITS rows and applies the whole w_o to them, so the sum over
+ *      heads happens inside one GEMM instead of across ranks.
+ */
+int rt_peer_gather_cols(const void* const* peer_ptrs, void* const* dst_ptrs, const int64_t* src_row_bytes,
+                        int64_t n_buffers, int64_t row0, int64_t rows, int64_t world, void* stream);
+
+/*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when
  * one of its bounded waits expired. RT_OK when no kernel gave up since the last call,
  * RT_ERR_TIMEOUT otherwise. Call after synchronising the stream; not graph-capturable.

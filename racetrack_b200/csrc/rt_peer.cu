@@ -162,6 +162,45 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(GatherArgs a, int rank
     }
 }
 
+// The transposing exchange in front of a row-sharded consumer ("all-to-all"): buffer b of rank q
+// holds that rank's COLUMN block of a [T, world * cols] matrix for ALL rows; this rank wants ITS
+// rows [row0, row0 + rows) of the whole matrix: dst[r, q * cols + c] = src_q[row0 + r, c].
+// grid (CTAs, buffers); 16-byte vectors, four loads in flight per thread.
+struct GatherColsArgs {
+    const uint4* src[kMaxGather][kMaxPeers];
+    uint4* dst[kMaxGather];
+    int64_t row_vec[kMaxGather];               // 16-byte vectors per source row
+};
+
+__global__ void __launch_bounds__(256) peer_gather_cols_kernel(GatherColsArgs a, int world, int64_t row0,
+                                                               int64_t rows) {
+    const int b = blockIdx.y;
+    const int64_t rv = a.row_vec[b];
+    const int64_t per_peer = rows * rv;
+    const int64_t total = per_peer * world;
+    const int64_t stride = static_cast<int64_t>(gridDim.x) * blockDim.x;
+    uint4* dst = a.dst[b];
+    for (int64_t i0 = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i0 < total; i0 += 4 * stride) {
+        uint4 v[4];
+        int64_t off[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int64_t i = i0 + u * stride;
+            off[u] = -1;
+            if (i < total) {
+                const int q = static_cast<int>(i / per_peer);
+                const int64_t rem = i - static_cast<int64_t>(q) * per_peer;
+                const int64_t r = rem / rv, c = rem - r * rv;
+                off[u] = (r * world + q) * rv + c;
+                v[u] = ld_once16(a.src[b][q] + (row0 + r) * rv + c);
+            }
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u)
+            if (off[u] >= 0) dst[off[u]] = v[u];
+    }
+}
+
 }  // namespace rt
 
 using namespace rt;
@@ -341,4 +380,43 @@ extern "C" int rt_peer_gather(const void* const* peer_ptrs, const int64_t* slice
     peer_gather_kernel<<<grid, 256, 0, as_stream(stream)>>>(a, (int)rank, (int)world);
     count_launch();
     return check_launch("peer_gather_kernel");
+}
+
+extern "C" int rt_peer_gather_cols(const void* const* peer_ptrs, void* const* dst_ptrs,
+                                   const int64_t* src_row_bytes, int64_t n_buffers, int64_t row0,
+                                   int64_t rows, int64_t world, void* stream) {
+    RT_REQUIRE(peer_ptrs && dst_ptrs && src_row_bytes, RT_ERR_BAD_ARG, "rt_peer_gather_cols: null pointer");
+    RT_REQUIRE(n_buffers >= 1 && n_buffers <= kMaxGather, RT_ERR_BAD_ARG,
+               "rt_peer_gather_cols: 1 to %d buffers", kMaxGather);
+    RT_REQUIRE(world >= 1 && world <= kMaxPeers && row0 >= 0 && rows >= 0, RT_ERR_BAD_ARG,
+               "rt_peer_gather_cols: bad arguments (at most %d ranks)", kMaxPeers);
+    if (rows == 0) return RT_OK;
+    GatherColsArgs a;
+    int64_t most = 0;
+    for (int b = 0; b < kMaxGather; ++b) {
+        a.dst[b] = nullptr;
+        a.row_vec[b] = 0;
+        for (int q = 0; q < kMaxPeers; ++q) a.src[b][q] = nullptr;
+        if (b >= n_buffers) continue;
+        RT_REQUIRE(src_row_bytes[b] > 0 && src_row_bytes[b] % 16 == 0, RT_ERR_BAD_ARG,
+                   "rt_peer_gather_cols: a source row must be a positive multiple of 16 bytes");
+        a.row_vec[b] = src_row_bytes[b] / 16;
+        for (int q = 0; q < world; ++q) {
+            const void* p = peer_ptrs[b * world + q];
+            RT_REQUIRE(p && aligned16(p), RT_ERR_BAD_ARG,
+                       "rt_peer_gather_cols: buffer pointers must be non-null and 16-byte aligned");
+            a.src[b][q] = static_cast<const uint4*>(p);
+        }
+        RT_REQUIRE(dst_ptrs[b] && aligned16(dst_ptrs[b]), RT_ERR_BAD_ARG,
+                   "rt_peer_gather_cols: destination pointers must be non-null and 16-byte aligned");
+        a.dst[b] = static_cast<uint4*>(dst_ptrs[b]);
+        const int64_t total = a.row_vec[b] * rows * world;
+        if (total > most) most = total;
+    }
+    int64_t ctas = (most + 4 * 256 - 1) / (4 * 256);
+    if (ctas > 4 * 148) ctas = 4 * 148;
+    const dim3 grid(static_cast<unsigned>(ctas), static_cast<unsigned>(n_buffers));
+    peer_gather_cols_kernel<<<grid, 256, 0, as_stream(stream)>>>(a, (int)world, row0, rows);
+    count_launch();
+    return check_launch("peer_gather_cols_kernel");
 }

@@ -13,7 +13,11 @@ tokens and all-reduces the partial sums twice per layer (racetrack/realistic_ben
     and routing of all tokens (0.3 / 0.56 bytes per hidden element instead of 2)
 
 so nothing token-wise is computed world times and less than half the bytes cross NVLink; the sums
-are the same sums (`token_sharded=False` keeps the reference's replicated schedule). Per layer:
+are the same sums (`token_sharded=False` keeps the reference's replicated schedule). When the
+caller also provides the WHOLE output projection (`w_o_full`), the attention half needs no
+reduction at all: the heads' attention outputs change hands (every rank collects all heads for
+its own rows, as FP8 codes + scales when w_o is FP8) and w_o is applied to a rank's rows over all
+heads, which is the single-GPU computation of those rows. Per layer:
 
     rms_norm -> qkv_a GEMM -> fused q_a/kv_a RMSNorm + k_pe RoPE -> q_b GEMM -> q_pe RoPE (in place)
     -> kv_b GEMM -> causal attention over the local heads (tcgen05) -> w_o GEMM -> all-reduce
@@ -88,7 +92,7 @@ def draw_expert(shape: LayerShape, e: int, device, *, std: float = 0.02,
 
 
 def make_weights(shape: LayerShape, rank: int, world: int, device, *, ffn: str = "moe",
-                 std: float = 0.02, dtype: torch.dtype = torch.bfloat16) -> dict:
+                 std: float = 0.02, dtype: torch.dtype = torch.bfloat16, full_w_o: bool = False) -> dict:
     """The weights rank `rank` of `world` owns, drawn unit by unit (see the module docstring).
     Keys: w_qkv_a [q+kv+rope, H]; w_q_b [h_loc*(nope+rope), q]; w_kv_b [h_loc*(nope+v), kv];
     w_o [H, h_loc*v]; w_gate [E, H]; w13 [E_loc, 2I, H], w2 [E_loc, H, I] (ffn == "moe") or
@@ -107,6 +111,11 @@ def make_weights(shape: LayerShape, rank: int, world: int, device, *, ffn: str =
                              for u in units])
     w["w_o"] = torch.cat([_draw((s.hidden, hpu * s.v_dim), seed + 300 + u, std, device, dtype)
                           for u in units], dim=1)
+    if full_w_o and world > 1:
+        # every unit's columns: the whole output projection, for the schedule that applies it to a
+        # rank's own token rows after exchanging the heads' attention outputs (RealisticLayer)
+        w["w_o_full"] = torch.cat([_draw((s.hidden, hpu * s.v_dim), seed + 300 + u, std, device, dtype)
+                                   for u in range(s.units)], dim=1)
     if ffn == "moe":
         e_loc = s.n_experts // world
         experts = [draw_expert(s, e, device, std=std, dtype=dtype)
@@ -220,6 +229,9 @@ class RealisticLayer:
                 torch.cat((wkv[:, :s.nope], gap, wkv[:, s.nope:]), dim=1)
                 .reshape(self.local_heads * (s.nope + s.rope + s.v_dim), s.kv_lora), proj)
         self.w_o = Projection(weights["w_o"], proj)
+        # the whole output projection (all heads' columns), when the caller provides it: the
+        # token-sharded schedule then exchanges attention outputs instead of reducing w_o's
+        self.w_o_full = Projection(weights["w_o_full"], proj) if "w_o_full" in weights and world > 1 else None
         self.w_gate = weights["w_gate"].contiguous()
         self.ones_h = torch.ones(shape.hidden, device=dev, dtype=torch.bfloat16)
         self.q_norm = torch.ones(shape.q_lora, device=dev, dtype=torch.bfloat16)
@@ -255,6 +267,12 @@ class RealisticLayer:
         """From the latent projection qkv [T, q_lora + kv_lora + rope] of ALL tokens to this
         rank's partial sum of the attention output (its heads' share of w_o), written into `out`
         when given (a buffer the other ranks read)."""
+        local = self.attention_heads(qkv, positions)
+        return self.w_o(local, out=out)
+
+    def attention_heads(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+        """From the latent projection of ALL tokens to the attention output of this rank's heads,
+        [T, local_heads * v_dim] (what w_o consumes)."""
         s, h = self.shape, self.local_heads
         tokens = qkv.shape[0]
         q_c, kv_c, k_pe = ops.fused_norm_rope(
@@ -269,7 +287,23 @@ class RealisticLayer:
             kv = self.w_kv_b(kv_c).view(tokens, h, s.qk_dim + s.v_dim)
             ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
             local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
-        return self.w_o(local.reshape(tokens, h * s.v_dim), out=out)
+        return local.reshape(tokens, h * s.v_dim)
+
+    def attention_rows_from_heads(self, px, heads_out: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
+        """The output projection of this rank's token rows [lo, hi) over ALL heads: the heads'
+        attention outputs are exchanged (as FP8 codes + scales when w_o is FP8: a 128-wide
+        quantisation group is one head's v_dim columns and never spans two ranks, so each rank
+        quantises its own columns exactly as the whole row would be) and the whole w_o is applied
+        locally. The sum over heads happens inside one GEMM, as on a single GPU; nothing is
+        reduced across ranks."""
+        if self.w_o_full.fp8:
+            ops.fused_act_quant(heads_out, out=(px.local["ao_codes"], px.local["ao_scales"]))
+            codes, scales = px.gather_cols(("ao_codes", "ao_scales"), lo, hi - lo)
+            return ops.linear_fp8(codes.view(torch.float8_e4m3fn), scales, self.w_o_full.codes,
+                                  self.w_o_full.scales)
+        px.local["ao"].copy_(heads_out)
+        (rows,) = px.gather_cols(("ao",), lo, hi - lo)
+        return ops.linear_bf16(rows, self.w_o_full.weight)
 
     def _route(self, normed: torch.Tensor, out: Optional[tuple] = None):
         """Router of racetrack/realistic_bench.py:321-327 for the given rows: fp32 logits of bf16
@@ -375,8 +409,16 @@ class RealisticLayer:
                 # kernel that reads them from every rank.
                 self.w_qkv_a(normed, out=px.local["qkv"][lo:hi])
                 px.gather("qkv")
-                self.attention_partial(px.local["qkv"], positions, out=px.local["attn"])
-                normed, mine = px.reduce_residual_norm("attn", mine, self.ones_h, eps=s.eps)
+                if self.w_o_full is not None:
+                    # the heads' outputs change hands, not w_o's partial sums: 1 / world of the bytes
+                    # (half of that again in FP8), and this half of the layer equals the single-GPU
+                    # evaluation bit for bit
+                    heads_out = self.attention_heads(px.local["qkv"], positions)
+                    attn = self.attention_rows_from_heads(px, heads_out, lo, hi)
+                    normed, mine = ops.fused_residual_norm(attn, mine, self.ones_h, eps=s.eps)
+                else:
+                    self.attention_partial(px.local["qkv"], positions, out=px.local["attn"])
+                    normed, mine = px.reduce_residual_norm("attn", mine, self.ones_h, eps=s.eps)
                 self.ffn_partial_from_rows(normed, out=px.local["ffn"],
                                            px=px if self.ffn == "moe" else None)
                 normed, mine = px.reduce_residual_norm("ffn", mine, self.ones_h, eps=s.eps)
@@ -395,8 +437,16 @@ class RealisticLayer:
         if px is None:
             s = self.shape
             shape = (tokens, s.hidden)
-            buffers = {"attn": (shape, torch.bfloat16), "ffn": (shape, torch.bfloat16),
+            buffers = {"ffn": (shape, torch.bfloat16),
                        "qkv": ((tokens, self.w_qkv_a.out_features), torch.bfloat16)}
+            cols = self.local_heads * s.v_dim
+            if self.w_o_full is None:
+                buffers["attn"] = (shape, torch.bfloat16)
+            elif self.w_o_full.fp8:
+                buffers["ao_codes"] = ((tokens, cols), torch.uint8)
+                buffers["ao_scales"] = ((tokens, cols // 128), torch.float32)
+            else:
+                buffers["ao"] = ((tokens, cols), torch.bfloat16)
             if self.ffn == "moe":
                 buffers.update({"moe_codes": ((tokens, s.hidden // 2), torch.uint8),
                                 "moe_sf": ((tokens, s.hidden // 16), torch.uint8),

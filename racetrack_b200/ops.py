@@ -290,8 +290,10 @@ def fused_swiglu(gate: torch.Tensor, up: torch.Tensor, *,
     return out
 
 
-def fused_act_quant(x: torch.Tensor, *, fallback: Optional[Callable] = None):
-    """FP8 e4m3 codes [..., N] and fp32 scales [..., N/128]; racetrack/models/deepseek.py:85-107."""
+def fused_act_quant(x: torch.Tensor, *, out: Optional[tuple] = None, fallback: Optional[Callable] = None):
+    """FP8 e4m3 codes [..., N] and fp32 scales [..., N/128]; racetrack/models/deepseek.py:85-107.
+    ``out`` = (codes, scales) contiguous tensors of those shapes to write into (codes as
+    float8_e4m3fn or uint8)."""
     del fallback
     _require_cuda(x)
     _require_bf16("fused_act_quant", x)
@@ -299,8 +301,15 @@ def fused_act_quant(x: torch.Tensor, *, fallback: Optional[Callable] = None):
     if n % 128 != 0:
         raise RuntimeError(f"fused_act_quant: last dim ({n}) must be a multiple of 128")
     x2 = _rows_view(x)
-    codes = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
-    scales = torch.empty(*x.shape[:-1], n // 128, dtype=torch.float32, device=x.device)
+    if out is not None:
+        codes, scales = out
+        if (codes.element_size() != 1 or scales.dtype != torch.float32 or not codes.is_contiguous()
+                or not scales.is_contiguous() or tuple(codes.shape) != tuple(x.shape)
+                or tuple(scales.shape) != (*x.shape[:-1], n // 128)):
+            raise RuntimeError("fused_act_quant: out must be contiguous (1-byte codes [..., N], fp32 scales [..., N/128])")
+    else:
+        codes = torch.empty(x.shape, dtype=torch.float8_e4m3fn, device=x.device)
+        scales = torch.empty(*x.shape[:-1], n // 128, dtype=torch.float32, device=x.device)
     lib = _lib.load()
     _lib.check(lib.rt_act_quant_fp8(x2.data_ptr(), codes.data_ptr(), scales.data_ptr(),
                                     x2.shape[0], n, x2.stride(0), _lib.RT_BF16, _stream()),

@@ -175,6 +175,28 @@ class PeerExchange:
             lib.rt_peer_gather(c_ptrs, c_slices, len(slices), self.rank, self.world, ops._stream()),
             "rt_peer_gather"))
 
+    def gather_cols(self, names: tuple, row0: int, rows: int) -> list:
+        """For each named buffer (every rank's copy holds THAT rank's column block [T, cols] for
+        all rows): this rank's rows [row0, row0 + rows) of the whole [T, world * cols] matrix, as a
+        new local tensor [rows, world * cols]. Includes the barrier."""
+        lib = _lib.load()
+        ptrs, outs, row_bytes = [], [], []
+        for name in names:
+            buf = self.local[name]
+            cols = buf.shape[1]
+            outs.append(torch.empty(rows, self.world * cols, dtype=buf.dtype, device=buf.device))
+            ptrs.extend(self._mapped[name])
+            row_bytes.append(cols * buf.element_size())
+        c_ptrs = (ctypes.c_void_p * len(ptrs))(*ptrs)
+        c_dst = (ctypes.c_void_p * len(outs))(*[o.data_ptr() for o in outs])
+        c_rb = (ctypes.c_int64 * len(row_bytes))(*row_bytes)
+        self.group._timed("peer_barrier (wait for the slowest rank)", self.flags, self.barrier)
+        payload = _Bytes(sum(row_bytes) * rows * (self.world - 1))
+        self.group._timed("peer_gather_cols", payload, lambda: _lib.check(
+            lib.rt_peer_gather_cols(c_ptrs, c_dst, c_rb, len(outs), row0, rows, self.world, ops._stream()),
+            "rt_peer_gather_cols"))
+        return outs
+
     def check(self) -> None:
         """Synchronises and raises if a barrier gave up waiting for a rank."""
         torch.cuda.synchronize()
