@@ -200,7 +200,12 @@ def fused_moe_forward(x: torch.Tensor, gate_weight: torch.Tensor, gate_bias: Opt
                       parts: Optional[dict] = None) -> torch.Tensor:
     """Gate (fp32 logits as in racetrack/models/deepseek.py:898, formed on the tensor cores from
     the bf16 operands with the fp32 accumulators kept) + routing kernel + experts."""
-    logits = ops.linear_bf16(x, gate_weight.to(torch.bfloat16), out_dtype=torch.float32)
+    if gate_weight.dtype == torch.float32:
+        # a gate kept in fp32 (a module built outside the model's bf16 default): both halves of
+        # the weight go through the tensor cores, so near-tied experts are ranked as in fp32
+        logits = ops.linear_f32_weight(x, gate_weight)
+    else:
+        logits = ops.linear_bf16(x, gate_weight.to(torch.bfloat16), out_dtype=torch.float32)
     weights, indices = ops.fused_moe_route(logits, gate_bias, n_groups=n_groups,
                                            topk_groups=topk_groups, topk=topk,
                                            route_scale=route_scale, score_func=score_func)
