@@ -616,6 +616,23 @@ int rt_attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, 
                            int64_t o_token_stride, int64_t o_head_stride,
                            float softmax_scale, void* stream);
 
+/*
+ * The same attention with the epilogue of its consumer fused in: instead of the bf16 output the
+ * kernel writes act_quant(output) (racetrack/models/deepseek.py:85-107), FP8 e4m3 codes
+ * out_codes [tokens, heads * 128] and fp32 scales out_scales [tokens, heads] (a 128-wide
+ * quantisation group is one head's value dims), bit for bit what rt_act_quant_fp8 makes of the
+ * bf16 output of rt_attn_causal_prefill: the input of an FP8 output projection
+ * (racetrack/models/deepseek.py:343-345 applied to w_o) without the [tokens, heads * 128] bf16
+ * round trip. Head shape 128 + 64 / 128 only (the CTA-pair schedule).
+ */
+int rt_attn_causal_prefill_fp8(const void* q, const void* k_nope, const void* k_pe, const void* v,
+                               void* out_codes, float* out_scales, int64_t tokens, int64_t heads,
+                               int64_t nope_dim, int64_t rope_dim, int64_t v_dim,
+                               int64_t q_token_stride, int64_t q_head_stride, int64_t kn_token_stride,
+                               int64_t kn_head_stride, int64_t kp_token_stride, int64_t kp_head_stride,
+                               int64_t v_token_stride, int64_t v_head_stride, float softmax_scale,
+                               void* stream);
+
 /* ------------------------------------------------------------------------ */
 /* Collective steps over NVLink peer memory (one process per GPU)              */
 /* ------------------------------------------------------------------------ */

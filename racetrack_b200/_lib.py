@@ -60,6 +60,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_mla_sparse_decode_splits": (_L, [_L, _L, _L]),
     "rt_mla_sparse_decode": (_I, [_P] * 8 + [_L] * 14 + [_F, _P]),
     "rt_attn_causal_prefill": (_I, [_P] * 5 + [_L] * 15 + [_F, _P]),
+    "rt_attn_causal_prefill_fp8": (_I, [_P] * 6 + [_L] * 13 + [_F, _P]),
     "rt_attn_prefill_schedule": (_I, [_I]),
     "rt_peer_alloc": (_I, [_L, _P, _P]),
     "rt_peer_open": (_I, [_P, _P]),

@@ -540,7 +540,18 @@ struct PrefillArgs {
     int one_op;                  // bit i set: operand i (q_nope, q_pe, k_nope, k_pe, v) arrives as ONE box
     int pe_shared;               // k_pe has one row per token for all heads
     float scale_log2;
+    // optional (pair schedule, v_dim 128): the output as act_quant leaves it, FP8 e4m3 codes
+    // [tokens, heads * 128] and one fp32 scale per token and head (= per 128-wide group)
+    uint8_t* out_codes;
+    float* out_scales;
 };
+
+// Two fp32 -> two e4m3 (RNE, saturating), `lo` in the low byte.
+__device__ __forceinline__ uint32_t attn_cvt_e4m3x2(float lo, float hi) {
+    uint16_t d;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(d) : "f"(hi), "f"(lo));
+    return d;
+}
 
 __device__ __forceinline__ float ex2_approx(float x) {
     float y;
@@ -1208,7 +1219,40 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
             uint32_t o[32];
             tmem_ld_32x32(to, o);
             tmem_ld_wait(o);
-            if (ok && token < a.tokens) {
+            if (a.out_codes != nullptr) {
+                // act_quant of the bf16 output (racetrack/models/deepseek.py:85-107) without writing
+                // it: the 128 values of this row and head are one quantisation group; its amax is
+                // the maximum of the four threads' 32 values, rounded to bf16 as the tensor would be
+                float xb[32];
+                float amax = 0.f;
+#pragma unroll
+                for (int i = 0; i < 32; ++i) {
+                    xb[i] = __bfloat162float(__float2bfloat16_rn(__uint_as_float(o[i]) * inv));
+                    amax = fmaxf(amax, fabsf(xb[i]));
+                }
+                float* xa = xl + 512;                         // [128 rows][4], behind the denominators
+                xa[cq] = amax;
+                __syncwarp();
+                if (lane == 0) mbar_arrive(row_bar);
+                ok = ok && mbar_wait(row_bar, (n + 1) & 1, abort_flag, 93);
+                const float4 am = *reinterpret_cast<const float4*>(xa);
+                amax = fmaxf(fmaxf(fmaxf(am.x, am.y), fmaxf(am.z, am.w)), 1.0e-4f);
+                const float scale = __fdiv_rn(amax, 448.0f);
+                const float rscale = __frcp_rn(scale);
+                if (ok && token < a.tokens) {
+                    uint32_t w[8];
+#pragma unroll
+                    for (int k = 0; k < 8; ++k)
+                        w[k] = attn_cvt_e4m3x2(div_shared(xb[4 * k], scale, rscale),
+                                               div_shared(xb[4 * k + 1], scale, rscale)) |
+                               (attn_cvt_e4m3x2(div_shared(xb[4 * k + 2], scale, rscale),
+                                                div_shared(xb[4 * k + 3], scale, rscale)) << 16);
+                    uint8_t* crow = a.out_codes + (static_cast<int64_t>(token) * a.heads + h) * 128 + 32 * cq;
+                    *reinterpret_cast<uint4*>(crow) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(crow + 16) = make_uint4(w[4], w[5], w[6], w[7]);
+                    if (cq == 0) a.out_scales[static_cast<int64_t>(token) * a.heads + h] = scale;
+                }
+            } else if (ok && token < a.tokens) {
                 __nv_bfloat16* orow = a.out + static_cast<int64_t>(token) * a.o_ts +
                                       static_cast<int64_t>(h) * a.o_hs + 32 * cq;
 #pragma unroll
@@ -1387,6 +1431,14 @@ extern "C" int rt_attn_prefill_schedule(int schedule) {
     return prev;
 }
 
+static int attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, const void* v,
+                               void* out, void* out_codes, float* out_scales, int64_t tokens,
+                               int64_t heads, int64_t nope_dim, int64_t rope_dim, int64_t v_dim,
+                               int64_t q_token_stride, int64_t q_head_stride, int64_t kn_token_stride,
+                               int64_t kn_head_stride, int64_t kp_token_stride, int64_t kp_head_stride,
+                               int64_t v_token_stride, int64_t v_head_stride, int64_t o_token_stride,
+                               int64_t o_head_stride, float softmax_scale, void* stream);
+
 extern "C" int rt_attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, const void* v,
                                       void* out, int64_t tokens, int64_t heads, int64_t nope_dim,
                                       int64_t rope_dim, int64_t v_dim, int64_t q_token_stride,
@@ -1395,9 +1447,42 @@ extern "C" int rt_attn_causal_prefill(const void* q, const void* k_nope, const v
                                       int64_t kp_head_stride, int64_t v_token_stride,
                                       int64_t v_head_stride, int64_t o_token_stride,
                                       int64_t o_head_stride, float softmax_scale, void* stream) {
+    RT_REQUIRE(out, RT_ERR_BAD_ARG, "rt_attn_causal_prefill: null pointer");
+    return attn_causal_prefill(q, k_nope, k_pe, v, out, nullptr, nullptr, tokens, heads, nope_dim, rope_dim,
+                               v_dim, q_token_stride, q_head_stride, kn_token_stride, kn_head_stride,
+                               kp_token_stride, kp_head_stride, v_token_stride, v_head_stride,
+                               o_token_stride, o_head_stride, softmax_scale, stream);
+}
+
+extern "C" int rt_attn_causal_prefill_fp8(const void* q, const void* k_nope, const void* k_pe, const void* v,
+                                          void* out_codes, float* out_scales, int64_t tokens,
+                                          int64_t heads, int64_t nope_dim, int64_t rope_dim,
+                                          int64_t v_dim, int64_t q_token_stride, int64_t q_head_stride,
+                                          int64_t kn_token_stride, int64_t kn_head_stride,
+                                          int64_t kp_token_stride, int64_t kp_head_stride,
+                                          int64_t v_token_stride, int64_t v_head_stride,
+                                          float softmax_scale, void* stream) {
+    RT_REQUIRE(out_codes && out_scales, RT_ERR_BAD_ARG, "rt_attn_causal_prefill_fp8: null pointer");
+    RT_REQUIRE(nope_dim == 128 && rope_dim == 64 && v_dim == 128, RT_ERR_UNSUPPORTED,
+               "rt_attn_causal_prefill_fp8: the FP8 epilogue exists for the 128 + 64 / 128 head shape");
+    RT_REQUIRE(aligned16(out_codes), RT_ERR_BAD_ARG, "rt_attn_causal_prefill_fp8: codes must be 16-byte aligned");
+    return attn_causal_prefill(q, k_nope, k_pe, v, nullptr, out_codes, out_scales, tokens, heads, nope_dim,
+                               rope_dim, v_dim, q_token_stride, q_head_stride, kn_token_stride, kn_head_stride,
+                               kp_token_stride, kp_head_stride, v_token_stride, v_head_stride, 8, 8,
+                               softmax_scale, stream);
+}
+
+static int attn_causal_prefill(const void* q, const void* k_nope, const void* k_pe, const void* v,
+                               void* out, void* out_codes, float* out_scales, int64_t tokens, int64_t heads, int64_t nope_dim,
+                                      int64_t rope_dim, int64_t v_dim, int64_t q_token_stride,
+                                      int64_t q_head_stride, int64_t kn_token_stride,
+                                      int64_t kn_head_stride, int64_t kp_token_stride,
+                                      int64_t kp_head_stride, int64_t v_token_stride,
+                                      int64_t v_head_stride, int64_t o_token_stride,
+                                      int64_t o_head_stride, float softmax_scale, void* stream) {
     RT_REQUIRE(tokens >= 0 && heads > 0, RT_ERR_BAD_ARG, "rt_attn_causal_prefill: bad shape");
     if (tokens == 0) return RT_OK;
-    RT_REQUIRE(q && k_nope && v && out && (k_pe || rope_dim == 0), RT_ERR_BAD_ARG,
+    RT_REQUIRE(q && k_nope && v && (out || out_codes) && (k_pe || rope_dim == 0), RT_ERR_BAD_ARG,
                "rt_attn_causal_prefill: null pointer");
     RT_REQUIRE(nope_dim > 0 && nope_dim <= 128 && rope_dim >= 0 && rope_dim <= 64 && v_dim > 0 && v_dim <= 128 &&
                    nope_dim % 8 == 0 && rope_dim % 8 == 0 && v_dim % 8 == 0,
@@ -1408,7 +1493,7 @@ extern "C" int rt_attn_causal_prefill(const void* q, const void* k_nope, const v
     for (int64_t st : strides)
         RT_REQUIRE(st >= 0 && st % 8 == 0, RT_ERR_BAD_ARG,
                    "rt_attn_causal_prefill: strides must be non-negative multiples of 8 elements");
-    RT_REQUIRE(aligned16(q) && aligned16(k_nope) && aligned16(v) && aligned16(out) && (!k_pe || aligned16(k_pe)),
+    RT_REQUIRE(aligned16(q) && aligned16(k_nope) && aligned16(v) && (!out || aligned16(out)) && (!k_pe || aligned16(k_pe)),
                RT_ERR_BAD_ARG, "rt_attn_causal_prefill: pointers must be 16-byte aligned");
     RT_REQUIRE(tokens < (1ll << 31) - 256 && heads < 65536, RT_ERR_UNSUPPORTED,
                "rt_attn_causal_prefill: dimension too large");
@@ -1425,6 +1510,8 @@ extern "C" int rt_attn_causal_prefill(const void* q, const void* k_nope, const v
     a.v_dim = static_cast<int>(v_dim);
     a.pe_shared = pe_shared ? 1 : 0;
     a.scale_log2 = softmax_scale * 1.4426950408889634f;
+    a.out_codes = static_cast<uint8_t*>(out_codes);
+    a.out_scales = out_scales;
     CUtensorMap tm_qn, tm_qp, tm_kn, tm_kp, tm_v;
     bool one[5] = {false, false, false, false, false};
     const __nv_bfloat16* qb = static_cast<const __nv_bfloat16*>(q);
@@ -1448,7 +1535,7 @@ extern "C" int rt_attn_causal_prefill(const void* q, const void* k_nope, const v
     }
     a.one_op = (one[0] ? 1 : 0) | (one[1] ? 2 : 0) | (one[2] ? 4 : 0) | (one[3] ? 8 : 0) | (one[4] ? 16 : 0);
     const bool mla_shape = nope_dim == 128 && rope_dim == 64 && v_dim == 128;
-    if (mla_shape && (tc::g_attn_schedule == 2 || (tc::g_attn_schedule == 0 && tokens >= 1024))) {
+    if (mla_shape && (out_codes || tc::g_attn_schedule == 2 || (tc::g_attn_schedule == 0 && tokens >= 1024))) {
         // the MLA head shape on CTA pairs with key tiles of 256 keys: a CTA brings 128 keys of a
         // tile (the boxes above) and 64 of the value dims for all of its 256 keys
         bool ignore;

@@ -267,12 +267,18 @@ class RealisticLayer:
         """From the latent projection qkv [T, q_lora + kv_lora + rope] of ALL tokens to this
         rank's partial sum of the attention output (its heads' share of w_o), written into `out`
         when given (a buffer the other ranks read)."""
+        if self.w_o.fp8 and self.attn_core == "rt":
+            # the attention kernel writes the FP8 codes + scales the output projection consumes
+            codes, scales = self.attention_heads(qkv, positions, quantized=True)
+            return ops.linear_fp8(codes, scales, self.w_o.codes, self.w_o.scales, out=out)
         local = self.attention_heads(qkv, positions)
         return self.w_o(local, out=out)
 
-    def attention_heads(self, qkv: torch.Tensor, positions: torch.Tensor) -> torch.Tensor:
+    def attention_heads(self, qkv: torch.Tensor, positions: torch.Tensor, quantized: bool = False,
+                        out: Optional[tuple] = None):
         """From the latent projection of ALL tokens to the attention output of this rank's heads,
-        [T, local_heads * v_dim] (what w_o consumes)."""
+        [T, local_heads * v_dim] (what w_o consumes); quantized=True: as FP8 codes + scales
+        (act_quant of it), written into `out` when given."""
         s, h = self.shape, self.local_heads
         tokens = qkv.shape[0]
         q_c, kv_c, k_pe = ops.fused_norm_rope(
@@ -282,14 +288,17 @@ class RealisticLayer:
         ops.fused_rope_half(q[..., s.nope:], positions, rope_base=s.rope_base, inplace=True)
         if self.attn_core == "rt":
             kv = self.w_kv_b(kv_c).view(tokens, h, s.nope + s.v_dim)
+            if quantized:
+                return ops.attention_prefill(q, kv[..., :s.nope], k_pe, kv[..., s.nope:], quantized=True, out=out)
             local = ops.attention_prefill(q, kv[..., :s.nope], k_pe, kv[..., s.nope:])
         else:
             kv = self.w_kv_b(kv_c).view(tokens, h, s.qk_dim + s.v_dim)
             ops.head_broadcast_(kv[..., s.nope:s.qk_dim], k_pe)       # K = [k_nope | k_pe] in place
             local = attention_core(q, kv[..., :s.qk_dim], kv[..., s.qk_dim:])
-        return local.reshape(tokens, h * s.v_dim)
+        local = local.reshape(tokens, h * s.v_dim)
+        return ops.fused_act_quant(local, out=out) if quantized else local
 
-    def attention_rows_from_heads(self, px, heads_out: torch.Tensor, lo: int, hi: int) -> torch.Tensor:
+    def attention_rows_from_heads(self, px, heads_out: Optional[torch.Tensor], lo: int, hi: int) -> torch.Tensor:
         """The output projection of this rank's token rows [lo, hi) over ALL heads: the heads'
         attention outputs are exchanged (as FP8 codes + scales when w_o is FP8: a 128-wide
         quantisation group is one head's v_dim columns and never spans two ranks, so each rank
@@ -297,7 +306,8 @@ class RealisticLayer:
         locally. The sum over heads happens inside one GEMM, as on a single GPU; nothing is
         reduced across ranks."""
         if self.w_o_full.fp8:
-            ops.fused_act_quant(heads_out, out=(px.local["ao_codes"], px.local["ao_scales"]))
+            if heads_out is not None:      # else the attention kernel wrote the exchange buffers itself
+                ops.fused_act_quant(heads_out, out=(px.local["ao_codes"], px.local["ao_scales"]))
             codes, scales = px.gather_cols(("ao_codes", "ao_scales"), lo, hi - lo)
             return ops.linear_fp8(codes.view(torch.float8_e4m3fn), scales, self.w_o_full.codes,
                                   self.w_o_full.scales)
@@ -413,7 +423,12 @@ class RealisticLayer:
                     # the heads' outputs change hands, not w_o's partial sums: 1 / world of the bytes
                     # (half of that again in FP8), and this half of the layer equals the single-GPU
                     # evaluation bit for bit
-                    heads_out = self.attention_heads(px.local["qkv"], positions)
+                    if self.w_o_full.fp8:
+                        self.attention_heads(px.local["qkv"], positions, quantized=True,
+                                             out=(px.local["ao_codes"], px.local["ao_scales"]))
+                        heads_out = None
+                    else:
+                        heads_out = self.attention_heads(px.local["qkv"], positions)
                     attn = self.attention_rows_from_heads(px, heads_out, lo, hi)
                     normed, mine = ops.fused_residual_norm(attn, mine, self.ones_h, eps=s.eps)
                 else:

@@ -908,13 +908,19 @@ def mla_sparse_decode(q_abs: torch.Tensor, q_pe: torch.Tensor, kv_cache: torch.T
 
 
 def attention_prefill(q: torch.Tensor, k_nope: torch.Tensor, k_pe: Optional[torch.Tensor],
-                      v: torch.Tensor, softmax_scale: Optional[float] = None) -> torch.Tensor:
+                      v: torch.Tensor, softmax_scale: Optional[float] = None, *,
+                      quantized: bool = False, out: Optional[tuple] = None):
     """Causal attention over [tokens, heads, dim] tensors on the tensor cores
     (racetrack/runtime/torch_ops.py:97-110; the attention core of
     racetrack/realistic_bench.py:304-313): q bf16 [T, H, nope + rope]; the key of head h is
     [k_nope[:, h] | k_pe] with k_nope [T, H, nope] and k_pe [T, rope] (one rope key per token for
     all heads, never broadcast in memory) or [T, H, rope], or None; v [T, H, v_dim]. Operands may
-    be strided views (column slices of projection outputs). Returns bf16 [T, H, v_dim]."""
+    be strided views (column slices of projection outputs). Returns bf16 [T, H, v_dim].
+
+    quantized=True returns act_quant of that output instead, (FP8 codes [T, H * v_dim], fp32 scales
+    [T, H]), bit for bit what fused_act_quant makes of it; for the 128 + 64 / 128 head shape the
+    attention kernel writes them from its own epilogue, otherwise the quantiser runs behind it.
+    ``out`` = (codes, scales) to write into (contiguous, 1-byte codes)."""
     _require_cuda(q, k_nope, v)
     tokens, heads, qk = q.shape
     nope = k_nope.shape[-1]
@@ -943,8 +949,28 @@ def attention_prefill(q: torch.Tensor, k_nope: torch.Tensor, k_pe: Optional[torc
             k_pe = k_pe[:, 0]
     if softmax_scale is None:
         softmax_scale = qk ** -0.5
-    out = torch.empty(tokens, heads, v_dim, dtype=torch.bfloat16, device=q.device)
     lib = _lib.load()
+    if quantized:
+        if out is not None:
+            codes, scales = out
+            if (codes.element_size() != 1 or scales.dtype != torch.float32 or not codes.is_contiguous()
+                    or not scales.is_contiguous() or tuple(codes.shape) != (tokens, heads * v_dim)
+                    or tuple(scales.shape) != (tokens, heads * v_dim // 128)):
+                raise RuntimeError("attention_prefill: out must be contiguous (1-byte codes [T, H*v], fp32 scales [T, H*v/128])")
+        if (nope, rope, v_dim) != (128, 64, 128):
+            # no fused epilogue for this head shape: the quantiser runs behind the attention kernel
+            return fused_act_quant(attention_prefill(q, k_nope, k_pe, v, softmax_scale)
+                                   .view(tokens, heads * v_dim), out=out)
+        if out is None:
+            codes = torch.empty(tokens, heads * v_dim, dtype=torch.float8_e4m3fn, device=q.device)
+            scales = torch.empty(tokens, heads, dtype=torch.float32, device=q.device)
+        _lib.check(lib.rt_attn_causal_prefill_fp8(
+            q.data_ptr(), k_nope.data_ptr(), k_pe.data_ptr(), v.data_ptr(), codes.data_ptr(),
+            scales.data_ptr(), tokens, heads, nope, rope, v_dim, q.stride(0), q.stride(1),
+            k_nope.stride(0), k_nope.stride(1), kp_ts, kp_hs, v.stride(0), v.stride(1),
+            float(softmax_scale), _stream()), "rt_attn_causal_prefill_fp8")
+        return codes, scales
+    out = torch.empty(tokens, heads, v_dim, dtype=torch.bfloat16, device=q.device)
     _lib.check(lib.rt_attn_causal_prefill(
         q.data_ptr(), k_nope.data_ptr(), k_pe.data_ptr() if rope else None, v.data_ptr(),
         out.data_ptr(), tokens, heads, nope, rope, v_dim, q.stride(0), q.stride(1),

@@ -148,3 +148,35 @@ def test_longer_sequence_many_heads_against_the_same_math_on_the_gpu(ops):
     scores = scores.masked_fill(~torch.ones(tokens, tokens, dtype=torch.bool, device="cuda").tril(), float("-inf"))
     full = torch.einsum("hts,shd->thd", torch.softmax(scores, dim=-1).to(torch.bfloat16).float(), vc.float())
     assert rel_err(got, full) <= 1e-2
+
+
+@pytest.mark.parametrize("tokens,heads", [(300, 3), (1500, 2)])
+def test_fp8_epilogue_equals_act_quant_of_the_bf16_output(tokens, heads):
+    """attention_prefill(quantized=True): the codes and scales the kernel's own epilogue writes are
+    those fused_act_quant makes of the bf16 output of the same schedule (racetrack/models/
+    deepseek.py:85-107 applied to racetrack/runtime/torch_ops.py:97-110), bit for bit; other head
+    shapes run the quantiser behind the kernel."""
+    from racetrack_b200 import ops
+    g = torch.Generator().manual_seed(tokens)
+    q = (torch.randn(tokens, heads, 192, generator=g) * 0.4).bfloat16().cuda()
+    kv = (torch.randn(tokens, heads, 256, generator=g) * 0.4).bfloat16().cuda()
+    kpe = (torch.randn(tokens, 64, generator=g) * 0.4).bfloat16().cuda()
+    prev = ops.attention_prefill_schedule(2)
+    try:
+        plain = ops.attention_prefill(q, kv[..., :128], kpe, kv[..., 128:])
+    finally:
+        ops.attention_prefill_schedule(prev)
+    want_c, want_s = ops.fused_act_quant(plain.view(tokens, heads * 128))
+    codes, scales = ops.attention_prefill(q, kv[..., :128], kpe, kv[..., 128:], quantized=True)
+    assert torch.equal(codes.view(torch.uint8), want_c.view(torch.uint8))
+    assert torch.equal(scales, want_s)
+    buf = (torch.empty(tokens, heads * 128, dtype=torch.uint8, device="cuda"),
+           torch.empty(tokens, heads, dtype=torch.float32, device="cuda"))
+    ops.attention_prefill(q, kv[..., :128], kpe, kv[..., 128:], quantized=True, out=buf)
+    assert torch.equal(buf[0], want_c.view(torch.uint8)) and torch.equal(buf[1], want_s)
+    # another head shape: same contract through the two-kernel route
+    q2, k2, v2 = q[..., :96].contiguous(), kv[..., :64].contiguous(), kv[..., 128:256].contiguous()
+    c2, s2 = ops.attention_prefill(q2, k2, kpe[:, :32].contiguous(), v2, quantized=True)
+    w2 = ops.fused_act_quant(ops.attention_prefill(q2, k2, kpe[:, :32].contiguous(), v2).view(tokens, heads * 128))
+    assert torch.equal(c2.view(torch.uint8), w2[0].view(torch.uint8)) and torch.equal(s2, w2[1])
+    ops.tc_error_state()
