@@ -9,8 +9,17 @@ of wkv_b and wo follow, and the head-parallel partial sums are all-reduced. The 
 half is the routed NVFP4 expert MLP of racetrack_b200.layer, expert-parallel.
 
 The two absorbed projections are per-head products of a [B, 128] by [128, 512] shape, all heads
-in one launch of the batched bf16 GEMM (ops.linear_bf16_batched). Nothing reads device data back
-to the host, so a step can be captured in a CUDA graph.
+in one launch of the batched bf16 GEMM (ops.linear_bf16_batched), on the raw bf16 halves of
+w_kv_b whatever `proj` says (the reference dequantises wkv_b before its einsums too,
+racetrack/models/deepseek.py:795-798). Nothing reads device data back to the host, so a step can
+be captured in a CUDA graph.
+
+RoPE conventions: the layer's own q_pe / k_pe use the half-split rotation of the synthetic runner
+this layer mirrors (racetrack/realistic_bench.py:297-303, partitions/dsv3_2/model.py:27-81),
+prefill and decode alike, so a cache written by one is read correctly by the other; the indexer
+inside the same step uses the reference model's complex table (non-interleaved pairs,
+racetrack/models/deepseek.py:662-669). The real model's MLA branch rotates interleaved pairs
+(:769-773); `ops.fused_rope` / `ops.fused_norm_rope_interleaved` are that convention.
 """
 from __future__ import annotations
 
@@ -87,6 +96,7 @@ class DecodeLayer(RealisticLayer):
         # per-head operands of the two absorbed projections, K-major for the batched GEMM
         self.w_uk_t = wkv[:, :s.nope].transpose(1, 2).contiguous()    # [h, kv_lora, nope]: q_nope -> latent
         self.w_uv = wkv[:, s.nope:].contiguous()                       # [h, v, kv_lora]: latent -> v
+        self.w_kv_b = None          # the prefill form of this projection is never used by a decode step
         self.index_weights, self.caches, self.index_topk = index_weights, caches, index_topk
         self.softmax_scale = s.qk_dim ** -0.5
         self.freqs = rope_table(s.rope, caches.kv.shape[1], s.rope_base, weights["w_qkv_a"].device)
