@@ -328,6 +328,7 @@ class PrefillStackWorkload:
         # experts that actually receive tokens (their weights are what the GEMM reads)
         inner_permute = ops.fused_moe_permute
         self.touched = []
+        self.rank_rows = []       # per recorded layer: routed rows of every rank's expert block
 
         def permute(indices, n_experts):
             out = inner_permute(indices, n_experts)
@@ -336,6 +337,8 @@ class PrefillStackWorkload:
                 lo = wl.rank * (n_experts // wl.world)
                 hi = lo + n_experts // wl.world
                 wl.touched.append(((off[lo + 1:hi + 1] - off[lo:hi]) > 0).sum())
+                if wl.world > 1:
+                    wl.rank_rows.append((off[1:] - off[:-1]).view(wl.world, -1).sum(-1))
             return out
 
         ops.fused_moe_permute = permute
@@ -1153,6 +1156,14 @@ def run_ours(args) -> None:
             "clocks": clocks,
         }
         line["check"] = check
+        if comm_stats is not None and getattr(wl, "rank_rows", None):
+            rr = torch.stack(wl.rank_rows).float()
+            ratio = rr.max(dim=1).values / rr.mean(dim=1).clamp_min(1.0)
+            comm_stats["expert_rows_busiest_rank_over_mean"] = {
+                "mean": round(float(ratio.mean()), 3), "worst_layer": round(float(ratio.max()), 3),
+                "layers_sampled": int(rr.shape[0]),
+                "note": "routed (token, expert) rows of the busiest rank's expert block over the mean "
+                        "per rank: the feed-forward half runs at that rank's pace"}
         if comm_stats is not None:
             comm_stats["compute_ms_per_layer"] = ms_total / args.steps / max(getattr(wl, "layers", 1), 1) \
                 - comm_stats["comm_ms_per_layer"]

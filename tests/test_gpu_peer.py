@@ -149,7 +149,11 @@ def _two_rank_layer(rank: int, world: int, port: int, out_dir: str):
                 normed = ops.fused_rms_norm(hidden[lo:hi].contiguous(), m.ones_h, eps=shape.eps)
                 m.w_qkv_a(normed, out=px.local["qkv"][lo:hi])
                 px.gather("qkv")
-                if full:
+                if full and m.w_o_full.fp8:      # as the layer does: the attention kernel fills the exchange
+                    m.attention_heads(px.local["qkv"], pos, quantized=True,
+                                      out=(px.local["ao_codes"], px.local["ao_scales"]))
+                    outs["attn_rows"] = m.attention_rows_from_heads(px, None, lo, hi).clone()
+                elif full:
                     rows = m.attention_rows_from_heads(px, m.attention_heads(px.local["qkv"], pos), lo, hi)
                     outs["attn_rows"] = rows.clone()
                 px.barrier()
