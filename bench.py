@@ -804,6 +804,8 @@ class DecodeLayerWorkload(PrefillStackWorkload):
     default_tokens = 64
     default_proj = "bf16"
     graph_default = True      # a decode step is replayed from a CUDA graph, as racetrack/bench.py:98-111 does
+    comm_schedule = ("tokens replicated (a decode step has few rows); the two all-reduces of a layer as "
+                     "one-shot reductions over peer memory fused with residual add + RMSNorm")
 
     def _build_model(self, w, args):
         from racetrack_b200 import decode
@@ -1074,7 +1076,8 @@ def run_ours(args) -> None:
                       "collectives_per_layer": {k: {"calls": c / layers, "ms": ms / layers,
                                                     "payload_mb": b / layers / 1e6}
                                                 for k, (c, ms, b) in per.items()},
-                      "schedule": ("token-sharded: reduce-scatter -> token-wise kernels on T/N rows -> "
+                      "schedule": getattr(wl, "comm_schedule", None) or
+                                  ("token-sharded: reduce-scatter -> token-wise kernels on T/N rows -> "
                                    "all-gather of their compact outputs"
                                    + ("; attention half: heads' outputs exchanged, whole w_o on the rank's rows"
                                       if getattr(wl.model, "w_o_full", None) is not None else ""))

@@ -101,7 +101,10 @@ class DecodeLayer(RealisticLayer):
         self.softmax_scale = s.qk_dim ** -0.5
         self.freqs = rope_table(s.rope, caches.kv.shape[1], s.rope_base, weights["w_qkv_a"].device)
 
-    def decode_attention(self, normed: torch.Tensor, start_pos: int) -> torch.Tensor:
+    def decode_attention(self, normed: torch.Tensor, start_pos: int,
+                         out: torch.Tensor | None = None) -> torch.Tensor:
+        """The attention half of a decode step; with `out` (an exchange buffer the other ranks
+        read) this rank's partial sum is left there and not reduced."""
         s, h, c = self.shape, self.local_heads, self.caches
         batch = normed.shape[0]
         end = start_pos + 1
@@ -121,15 +124,41 @@ class DecodeLayer(RealisticLayer):
         latent = ops.mla_sparse_decode(q_abs, q[..., s.nope:], c.kv[:, :end], c.pe[:, :end], picked,
                                        self.softmax_scale)                                 # [B, h, kv_lora]
         heads_out = ops.linear_bf16_batched(latent, self.w_uv)                          # [B, h, v]
-        out = self.w_o(heads_out.reshape(batch, h * s.v_dim))
-        return self._all_reduce(out)
+        if out is not None:
+            return self.w_o(heads_out.reshape(batch, h * s.v_dim), out=out)
+        return self._all_reduce(self.w_o(heads_out.reshape(batch, h * s.v_dim)))
+
+    def _decode_exchange(self, batch: int):
+        """The two [B, H] partial-sum buffers of this batch size, mapped across the ranks once."""
+        from . import peer
+        key = ("decode", batch)
+        px = self._peer.get(key)
+        if px is None:
+            shape = (batch, self.shape.hidden)
+            px = peer.PeerExchange(self.comm, self.ones_h.device,
+                                   {"attn": (shape, torch.bfloat16), "ffn": (shape, torch.bfloat16)})
+            self._peer[key] = px
+        return px
 
     def decode_stack(self, hidden: torch.Tensor, start_pos: int, layers: int) -> torch.Tensor:
         """hidden [B, H] bf16 (the new token of every sequence) -> hidden after `layers`
         applications of the layer."""
         s = self.shape
         normed = ops.fused_rms_norm(hidden, self.ones_h, eps=s.eps)
+        px = None
+        if self.world > 1 and self.reduce and self.peer_reduce and hidden.is_cuda:
+            # the two all-reduces of a layer (racetrack/realistic_bench.py:315-316,351) for the few
+            # rows of a decode step: every rank leaves its partial sums in a buffer its peers have
+            # mapped, and after one device barrier every rank sums all of them, adds the residual
+            # and normalises in ONE kernel (a one-shot all-reduce fused with its consumer)
+            px = self._decode_exchange(hidden.shape[0])
         for _ in range(layers):
+            if px is not None:
+                self.decode_attention(normed, start_pos, out=px.local["attn"])
+                normed, hidden = px.reduce_residual_norm("attn", hidden, self.ones_h, eps=s.eps, all_rows=True)
+                self.ffn_partial(normed, out=px.local["ffn"])
+                normed, hidden = px.reduce_residual_norm("ffn", hidden, self.ones_h, eps=s.eps, all_rows=True)
+                continue
             attn = self.decode_attention(normed, start_pos)
             normed, hidden = ops.fused_residual_norm(attn, hidden, self.ones_h, eps=s.eps)
             ffn = self.ffn_forward(normed)

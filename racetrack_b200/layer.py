@@ -326,21 +326,23 @@ class RealisticLayer:
 
     def ffn_forward(self, normed: torch.Tensor) -> torch.Tensor:
         """racetrack/realistic_bench.py:319-352 (routed experts) or a dense SwiGLU FFN."""
+        return self._all_reduce(self.ffn_partial(normed))
+
+    def ffn_partial(self, normed: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """The feed-forward half on all tokens, this rank's partial sum (its experts / its FFN
+        columns), written into `out` when given (a buffer the other ranks read)."""
         s = self.shape
         if self.ffn == "moe":
             weights, indices = self._route(normed)
-            out = moe.fused_moe_experts(normed, weights, indices, self.experts,
-                                        n_experts=s.n_experts,
-                                        expert_begin=self.rank * self.local_experts)
-        else:
-            gate_up = self.w13d(normed)
-            inter = gate_up.shape[1] // 2
-            if self.w2d.fp8:     # SwiGLU and the FP8 quantisation of its result in one kernel
-                codes, scales = ops.fused_swiglu_quant(gate_up[:, :inter], gate_up[:, inter:])
-                out = ops.linear_fp8(codes, scales, self.w2d.codes, self.w2d.scales)
-            else:
-                out = self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]))
-        return self._all_reduce(out)
+            return moe.fused_moe_experts(normed, weights, indices, self.experts,
+                                         n_experts=s.n_experts,
+                                         expert_begin=self.rank * self.local_experts, out=out)
+        gate_up = self.w13d(normed)
+        inter = gate_up.shape[1] // 2
+        if self.w2d.fp8:     # SwiGLU and the FP8 quantisation of its result in one kernel
+            codes, scales = ops.fused_swiglu_quant(gate_up[:, :inter], gate_up[:, inter:])
+            return ops.linear_fp8(codes, scales, self.w2d.codes, self.w2d.scales, out=out)
+        return self.w2d(ops.fused_swiglu(gate_up[:, :inter], gate_up[:, inter:]), out=out)
 
     def ffn_partial_from_rows(self, normed_rows: torch.Tensor, out: Optional[torch.Tensor] = None,
                               px=None) -> torch.Tensor:

@@ -129,20 +129,21 @@ class PeerExchange:
                    "rt_peer_barrier")
 
     def reduce_residual_norm(self, name: str, residual_rows: torch.Tensor, weight: torch.Tensor, *,
-                             eps: float):
+                             eps: float, all_rows: bool = False):
         """(normed, hidden) for this rank's rows: hidden = (sum over ranks of buffer `name`)[rows]
         + residual_rows, normed = rms_norm(hidden) * weight. Includes the barrier that makes
-        every rank's partial sums visible."""
+        every rank's partial sums visible. all_rows=True: every rank reduces ALL rows (a one-shot
+        all-reduce fused with the kernel that follows it, for the few rows of a decode step)."""
         part = self.local[name]
         # timed apart: the barrier's interval is the wait for the slowest rank (load imbalance),
         # the kernel's interval is the transfer itself
         self.group._timed("peer_barrier (wait for the slowest rank)", self.flags, self.barrier)
         return self.group._timed("peer_reduce_residual_norm", part,
-                                 lambda: self._reduce_residual_norm(part, name, residual_rows, weight, eps))
+                                 lambda: self._reduce_residual_norm(part, name, residual_rows, weight, eps, all_rows))
 
-    def _reduce_residual_norm(self, part, name, residual_rows, weight, eps):
+    def _reduce_residual_norm(self, part, name, residual_rows, weight, eps, all_rows=False):
         total_rows, cols = part.shape
-        lo, hi = self.group.rows_of(total_rows)
+        lo, hi = (0, total_rows) if all_rows else self.group.rows_of(total_rows)
         res = residual_rows if residual_rows.stride(-1) == 1 else residual_rows.contiguous()
         w = weight.contiguous()
         normed = torch.empty(hi - lo, cols, dtype=torch.bfloat16, device=part.device)
