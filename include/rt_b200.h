@@ -713,6 +713,14 @@ int rt_peer_gather_cols(const void* const* peer_ptrs, void* const* dst_ptrs, con
                         int64_t n_buffers, int64_t row0, int64_t rows, int64_t world, void* stream);
 
 /*
+ * out[0] = max over ranks of the non-negative fp32 value each rank has stored at slot_ptrs[q]
+ * (rank q's slot as mapped into this process). Call rt_peer_barrier first. The tensor-wide amax
+ * behind one NVFP4 global scale for all ranks' rows; no counterpart in the reference (it has
+ * no NVFP4 arithmetic), it stands where a 4-byte all-reduce MAX would.
+ */
+int rt_peer_allmax(const void* const* slot_ptrs, int64_t world, float* out, void* stream);
+
+/*
  * Synchronous: reads (and clears) the device-side flag that a tensor-core kernel sets when
  * one of its bounded waits expired. RT_OK when no kernel gave up since the last call,
  * RT_ERR_TIMEOUT otherwise. Call after synchronising the stream; not graph-capturable.

@@ -71,6 +71,7 @@ SIGNATURES: dict[str, tuple] = {
     "rt_peer_reduce_residual_norm": (_I, [_P, _L, _L, _L, _P, _P, _I, _P, _P, _L, _L, _L, _F, _P]),
     "rt_peer_gather": (_I, [_P, _P, _L, _L, _L, _P]),
     "rt_peer_gather_cols": (_I, [_P, _P, _P, _L, _L, _L, _L, _P]),
+    "rt_peer_allmax": (_I, [_P, _L, _P, _P]),
     "rt_gemm_bf16_schedule": (_I, [_I]),
     "rt_gemm_nvfp4_grouped": (_I, [_P, _P, _P, _P, _P, _P, _P, _P, _P, _L, _L, _L, _L, _L, _L, _P]),
 }

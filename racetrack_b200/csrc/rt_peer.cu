@@ -201,6 +201,20 @@ __global__ void __launch_bounds__(256) peer_gather_cols_kernel(GatherColsArgs a,
     }
 }
 
+// The maximum of one fp32 value per rank (the tensor-wide amax behind an NVFP4 scale): every rank
+// has stored its value in its own slot; after the barrier each rank reads all of them.
+__global__ void peer_allmax_kernel(PeerPtrs slots, int world, float* __restrict__ out) {
+    float v = 0.f;
+    if (static_cast<int>(threadIdx.x) < world) {
+        uint32_t bits;
+        asm volatile("ld.relaxed.sys.global.u32 %0, [%1];" : "=r"(bits) : "l"(slots.p[threadIdx.x]) : "memory");
+        v = __uint_as_float(bits);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    if (threadIdx.x == 0) out[0] = v;
+}
+
 }  // namespace rt
 
 using namespace rt;
@@ -419,4 +433,17 @@ extern "C" int rt_peer_gather_cols(const void* const* peer_ptrs, void* const* ds
     peer_gather_cols_kernel<<<grid, 256, 0, as_stream(stream)>>>(a, (int)world, row0, rows);
     count_launch();
     return check_launch("peer_gather_cols_kernel");
+}
+
+extern "C" int rt_peer_allmax(const void* const* slot_ptrs, int64_t world, float* out, void* stream) {
+    RT_REQUIRE(slot_ptrs && out, RT_ERR_BAD_ARG, "rt_peer_allmax: null pointer");
+    RT_REQUIRE(world >= 1 && world <= kMaxPeers, RT_ERR_BAD_ARG, "rt_peer_allmax: 1 to %d ranks", kMaxPeers);
+    PeerPtrs p;
+    for (int q = 0; q < kMaxPeers; ++q) {
+        p.p[q] = q < world ? slot_ptrs[q] : nullptr;
+        RT_REQUIRE(q >= world || p.p[q], RT_ERR_BAD_ARG, "rt_peer_allmax: null slot pointer");
+    }
+    peer_allmax_kernel<<<1, 32, 0, as_stream(stream)>>>(p, (int)world, out);
+    count_launch();
+    return check_launch("peer_allmax_kernel");
 }

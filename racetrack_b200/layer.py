@@ -354,7 +354,10 @@ class RealisticLayer:
         s, c = self.shape, self.comm
         if self.ffn == "moe":
             # one tensor-wide NVFP4 scale whatever the world size: the maximum over all ranks' rows
-            amax = c.all_reduce_max(ops.tensor_absmax(normed_rows))
+            if px is not None:
+                amax = px.allmax("amax", ops.tensor_absmax(normed_rows))
+            else:
+                amax = c.all_reduce_max(ops.tensor_absmax(normed_rows))
             if px is not None:
                 # routing and quantisation write this rank's rows of the exchange buffers; one
                 # device barrier and one kernel then pull the other ranks' rows over NVLink
@@ -445,6 +448,13 @@ class RealisticLayer:
             normed, mine = ops.fused_residual_norm(attn, mine, self.ones_h, eps=s.eps)
             ffn = c.reduce_scatter_rows(self.ffn_partial_from_rows(normed))
             normed, mine = ops.fused_residual_norm(ffn, mine, self.ones_h, eps=s.eps)
+        if px is not None:
+            # the stack's result for all tokens: the ffn partial-sum buffer carries the final
+            # all-gather (a rank overwrites only ITS rows of ITS copy, which nobody else reads in
+            # the last reduce; the gather's barrier orders the writes before the pulls)
+            px.local["ffn"][lo:hi].copy_(mine)
+            px.gather("ffn")
+            return px.local["ffn"].clone()
         return c.all_gather_rows(mine)
 
     def _peer_exchange(self, tokens: int):
@@ -465,7 +475,8 @@ class RealisticLayer:
             else:
                 buffers["ao"] = ((tokens, cols), torch.bfloat16)
             if self.ffn == "moe":
-                buffers.update({"moe_codes": ((tokens, s.hidden // 2), torch.uint8),
+                buffers.update({"amax": ((4,), torch.float32),
+                                "moe_codes": ((tokens, s.hidden // 2), torch.uint8),
                                 "moe_sf": ((tokens, s.hidden // 16), torch.uint8),
                                 "moe_w": ((tokens, s.topk), torch.float32),
                                 "moe_i": ((tokens, s.topk), torch.int64)})

@@ -198,6 +198,17 @@ class PeerExchange:
             "rt_peer_gather_cols"))
         return outs
 
+    def allmax(self, name: str, value: torch.Tensor) -> torch.Tensor:
+        """The maximum over ranks of a non-negative 1-element fp32 tensor, through the 16-byte
+        buffer `name`: store, barrier, read every rank's slot. Every rank gets the same value."""
+        self.local[name][:1].copy_(value.reshape(1))
+        out = torch.empty(1, dtype=torch.float32, device=value.device)
+        lib = _lib.load()
+        self.group._timed("peer_barrier (wait for the slowest rank)", self.flags, self.barrier)
+        self.group._timed("peer_allmax", out, lambda: _lib.check(
+            lib.rt_peer_allmax(self._ptrs[name], self.world, out.data_ptr(), ops._stream()), "rt_peer_allmax"))
+        return out
+
     def check(self) -> None:
         """Synchronises and raises if a barrier gave up waiting for a rank."""
         torch.cuda.synchronize()
