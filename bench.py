@@ -438,11 +438,15 @@ class PrefillStackWorkload:
         self.graph = torch.cuda.CUDAGraph()
         self.graph_events = []
         self.capturing = self.recording = True
+        group = getattr(getattr(self, "model", None), "comm", None)
+        calls0 = group.nccl_calls if group is not None else 0
         try:
             with torch.cuda.graph(self.graph):
                 self.graph_out = self._forward(self.hidden)
         finally:
             self.capturing = self.recording = False
+        # whether the captured step holds library collectives (the peer-memory schedule has none)
+        self.graph_has_nccl = group is not None and group.nccl_calls > calls0
         self.launches_per_replay = _lib.launch_count() - before
 
     def capture_timing_graph(self, group):
@@ -1179,10 +1183,11 @@ def run_ours(args) -> None:
             cpu.pop("ms_per_step")
             line["cpu_baseline"] = cpu
         print(json.dumps(line), flush=True)
-    if distributed and use_graph:
+    if distributed and use_graph and getattr(wl, "graph_has_nccl", True):
         # A captured graph that holds NCCL kernels kept the interpreter from finishing its
         # teardown here (torch 2.11, NCCL 2.28): drop the graph, meet once more, and leave
-        # without running the communicator's destructors.
+        # without running the communicator's destructors. (A graph of this library's own
+        # peer-memory collectives only is torn down normally, below.)
         wl.graph = None
         wl.graph_out = None
         barrier()
@@ -1190,6 +1195,13 @@ def run_ours(args) -> None:
         sys.stderr.flush()
         os._exit(0)
     if distributed:
+        # graphs first (they reference the exchange buffers), then the peer mappings, then the group
+        for attr in ("graph", "graph_out", "_timing_graph", "_timing_out"):
+            if hasattr(wl, attr):
+                setattr(wl, attr, None)
+        torch.cuda.synchronize()
+        for px in list(getattr(getattr(wl, "model", None), "_peer", {}).values()):
+            px.close()
         dist.destroy_process_group()
 
 

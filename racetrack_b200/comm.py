@@ -33,6 +33,7 @@ class Group:
             raise RuntimeError("a sharded layer needs an initialised torch.distributed process group")
         self._no_reduce_scatter = world > 1 and dist.get_backend(group) == "gloo"
         self.events = None          # a list while timing: (name, bytes sent by this rank, start, end)
+        self.nccl_calls = 0         # collectives handed to torch.distributed so far
 
     def start_timing(self, in_graph: bool = False) -> None:
         """From now on every collective is bracketed by CUDA events on the current stream (the
@@ -54,6 +55,8 @@ class Group:
         return out
 
     def _timed(self, name: str, payload: torch.Tensor, fn):
+        if not name.startswith("peer_"):
+            self.nccl_calls += 1
         if self.events is None or not payload.is_cuda:
             return fn()
         ext = getattr(self, "_external", False)
