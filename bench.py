@@ -1195,6 +1195,10 @@ def run_ours(args) -> None:
         sys.stderr.flush()
         os._exit(0)
     if distributed:
+        # the line is printed; should the teardown of the group ever stall, leave anyway
+        watchdog = threading.Timer(120.0, lambda: os._exit(0))
+        watchdog.daemon = True
+        watchdog.start()
         # graphs first (they reference the exchange buffers), then the peer mappings, then the group
         for attr in ("graph", "graph_out", "_timing_graph", "_timing_out"):
             if hasattr(wl, attr):
