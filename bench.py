@@ -254,6 +254,13 @@ class PrefillStackWorkload:
             self.tokens = self.default_tokens         # --tokens was not given
         self.shape = layer.DSV32
         self.ffn = args.ffn
+        # Experts: expert-parallel up to 4 groups; from 8 ranks on, pairs of ranks share a group's
+        # experts and split their intermediate dimension. Under this runner's router (random gate,
+        # one layer applied 61 times) a few experts attract most rows: the busiest of 8 single-rank
+        # blocks receives 2.2 x the mean rows, the busiest of 4 groups 1.35 x.
+        tp = getattr(args, "moe_tp", "auto")
+        self.moe_tp = (2 if world >= 8 else 1) if tp == "auto" else int(tp)
+        self.ep_world, self.ep_rank = world // self.moe_tp, rank // self.moe_tp
         # several ranks: every rank also holds the whole output projection, so the attention half
         # exchanges the heads' outputs instead of reducing partial sums (--reduce-w-o: the latter)
         full_w_o = world > 1 and not args.replicated and not getattr(args, "reduce_w_o", False) \
@@ -262,13 +269,14 @@ class PrefillStackWorkload:
             w = layer.make_weights(self.shape, rank, world, device, ffn="dense", std=0.02, full_w_o=full_w_o)
         else:
             w = layer.make_weights(self.shape, rank, world, device, ffn="none", std=0.02, full_w_o=full_w_o)
-            w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02)
+            w["experts"] = layer.make_nvfp4_experts(self.shape, rank, world, device, std=0.02,
+                                                    moe_tp=self.moe_tp)
         self.proj = args.proj
         self.schedule = args.nvfp4_schedule
         ops.gemm_nvfp4_schedule({"auto": 0, "single": 1, "pair": 2}[self.schedule])
-        pairs_local = self.tokens * self.shape.topk // world
+        pairs_local = self.tokens * self.shape.topk // self.ep_world
         uses_pairs = self.schedule == "pair" or (
-            self.schedule == "auto" and pairs_local >= 128 * (self.shape.n_experts // world))
+            self.schedule == "auto" and pairs_local >= 128 * (self.shape.n_experts // self.ep_world))
         self.dominant = ("gemm_nvfp4_pair_kernel" if uses_pairs else "gemm_nvfp4_kernel") + \
             "[experts w13]"
         if self.ffn == "dense":
@@ -293,7 +301,7 @@ class PrefillStackWorkload:
 
     def _wrap_dominant(self):
         """CUDA events around every first expert GEMM (w13) of the timed region."""
-        ops, inter2 = self.ops, 2 * self.shape.moe_inter
+        ops, inter2 = self.ops, 2 * self.shape.moe_inter // getattr(self, "moe_tp", 1)
         inner = ops.gemm_nvfp4_grouped
         wl = self
 
@@ -334,11 +342,11 @@ class PrefillStackWorkload:
             out = inner_permute(indices, n_experts)
             if wl.recording and len(wl.touched) < 64:
                 off = out[0]
-                lo = wl.rank * (n_experts // wl.world)
-                hi = lo + n_experts // wl.world
+                lo = wl.ep_rank * (n_experts // wl.ep_world)
+                hi = lo + n_experts // wl.ep_world
                 wl.touched.append(((off[lo + 1:hi + 1] - off[lo:hi]) > 0).sum())
                 if wl.world > 1:
-                    wl.rank_rows.append((off[1:] - off[:-1]).view(wl.world, -1).sum(-1))
+                    wl.rank_rows.append((off[1:] - off[:-1]).view(wl.ep_world, -1).sum(-1))
             return out
 
         ops.fused_moe_permute = permute
@@ -354,8 +362,9 @@ class PrefillStackWorkload:
             n = 2 * s.dense_inter // self.world
             per = 1 if self.proj in ("fp8", "mixed") else 2
             return per * (self.tokens * s.hidden + n * s.hidden) + self.tokens * n * 2
-        e_loc = s.n_experts // self.world
-        pairs_local = self.tokens * s.topk // self.world       # expected rows of this rank
+        e_loc = s.n_experts // self.ep_world
+        inter = s.moe_inter // self.moe_tp
+        pairs_local = self.tokens * s.topk // self.ep_world    # expected rows of this rank's group
         # experts that receive at least one token (all of them at prefill sizes; at decode
         # sizes only the touched experts' weights are read): counted from the routing of the
         # timed layers, else the expectation under uniform routing
@@ -363,25 +372,26 @@ class PrefillStackWorkload:
             touched = float(torch.stack(self.touched).float().mean())
         else:
             touched = e_loc * (1.0 - (1.0 - 1.0 / s.n_experts) ** (self.tokens * s.topk))
-        weights = int(touched * 2 * s.moe_inter * s.hidden * 9 // 16)   # e2m1 codes + e4m3 scales
+        weights = int(touched * 2 * inter * s.hidden * 9 // 16)   # e2m1 codes + e4m3 scales
         acts = pairs_local * s.hidden * 9 // 16
-        out = pairs_local * 2 * s.moe_inter * 2
+        out = pairs_local * 2 * inter * 2
         return weights + acts + out
 
     @property
     def dominant_bytes_all_experts(self) -> int:
         """Algorithmic bytes of a w13 launch in which every local expert receives tokens."""
         s = self.shape
-        pairs_local = self.tokens * s.topk // self.world
-        return ((s.n_experts // self.world) * 2 * s.moe_inter * s.hidden * 9 // 16
-                + pairs_local * s.hidden * 9 // 16 + pairs_local * 2 * s.moe_inter * 2)
+        pairs_local = self.tokens * s.topk // self.ep_world
+        inter = s.moe_inter // self.moe_tp
+        return ((s.n_experts // self.ep_world) * 2 * inter * s.hidden * 9 // 16
+                + pairs_local * s.hidden * 9 // 16 + pairs_local * 2 * inter * 2)
 
     @property
     def dominant_flops(self) -> int:
         s = self.shape
         if self.ffn == "dense":
             return 2 * self.tokens * (2 * s.dense_inter // self.world) * s.hidden
-        return 2 * (self.tokens * s.topk // self.world) * 2 * s.moe_inter * s.hidden
+        return 2 * (self.tokens * s.topk // self.ep_world) * 2 * (s.moe_inter // self.moe_tp) * s.hidden
 
     @property
     def tensor_peak_factor(self) -> float:
@@ -844,9 +854,8 @@ class DecodeLayerWorkload(PrefillStackWorkload):
         wts, idx = ops.fused_moe_route(logits, None, n_groups=1, topk_groups=1, topk=s.topk,
                                        route_scale=1.0, score_func="topk_softmax")
         parts: dict = {}
-        local = s.n_experts // self.world
         ffn = self.moe.fused_moe_experts(n2, wts, idx, m.experts, n_experts=s.n_experts,
-                                         expert_begin=self.rank * local, parts=parts)
+                                         expert_begin=m.expert_begin, parts=parts)
         ffn = m._all_reduce(ffn)
         ops.tc_error_state()
         if self.rank != 0:
@@ -1152,7 +1161,9 @@ def run_ours(args) -> None:
             "ms_per_step": ms_total / args.steps, "higher_is_better": True, "scaling": wl.scaling,
             "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
             "config": {**wl.config(),
-                       "parallelism": f"tp{world}(heads)+ep{world}(experts)" if wl.scaling == "strong"
+                       "parallelism": (f"tp{world}(heads)+ep{getattr(wl, 'ep_world', world)}"
+                                       + (f"xtp{wl.moe_tp}" if getattr(wl, "moe_tp", 1) > 1 else "")
+                                       + "(experts)") if wl.scaling == "strong"
                        else f"replicated-stream x{world}"},
             "roofline": roof,
             "e2e": {"value": wl.units_per_step * e2e_steps / (e2e_ms * 1e-3)
@@ -1236,6 +1247,9 @@ def main() -> None:
     ap.add_argument("--replicated", action="store_true",
                     help="multi-GPU: the reference's schedule (all tokens on every rank, two "
                          "all-reduces per layer) instead of the token-sharded one")
+    ap.add_argument("--moe-tp", default="auto", choices=("auto", "1", "2", "4"),
+                    help="ranks that share one group's experts and split their intermediate dimension "
+                         "(the expert-parallel degree is the world size over this); auto: 2 from 8 ranks on")
     ap.add_argument("--reduce-w-o", action="store_true",
                     help="multi-GPU: keep the output projection row-sharded and reduce its partial sums "
                          "(the reference's arithmetic) instead of exchanging the heads' attention outputs")

@@ -131,19 +131,45 @@ def make_weights(shape: LayerShape, rank: int, world: int, device, *, ffn: str =
 
 
 def make_nvfp4_experts(shape: LayerShape, rank: int, world: int, device, *,
-                       std: float = 0.02) -> "moe.NVFP4Experts":
+                       std: float = 0.02, moe_tp: int = 1) -> "moe.NVFP4Experts":
     """The rank's routed experts drawn and quantised one at a time, so that the bf16 weights of
-    only one expert exist at any moment (all 256 experts in bf16 would take 22.5 GB)."""
+    only one expert exist at any moment (all 256 experts in bf16 would take 22.5 GB).
+
+    moe_tp > 1 makes the expert split a hybrid: the ranks form world / moe_tp expert-parallel
+    groups of moe_tp ranks (rank = group * moe_tp + member); a group owns a contiguous block of
+    experts and member m holds columns [m, m + 1) * inter / moe_tp of every one of them (the
+    matching rows of w1 and w3, the matching K range of w2). The quantised weights are those of
+    the whole expert, cut afterwards (same codes, block scales and global scale at every world
+    size); the members' partial sums add up in the reduction that follows the experts anyway.
+    A group's load is the sum over more experts, so a router that favours a few experts leaves
+    the groups less out of balance than single ranks would be."""
     s = shape
-    e_loc = s.n_experts // world
+    if world % moe_tp or s.n_experts % (world // moe_tp) or s.moe_inter % (256 * moe_tp):
+        raise ValueError("moe_tp must divide the world size and leave inter / moe_tp a multiple of 256")
+    group, member = divmod(rank, moe_tp)
+    e_loc = s.n_experts // (world // moe_tp)
+    inter = s.moe_inter // moe_tp
     parts13, parts2 = [], []
-    for e in range(rank * e_loc, (rank + 1) * e_loc):
+    for e in range(group * e_loc, (group + 1) * e_loc):
         w13, w2 = draw_expert(s, e, device, std=std)
-        parts13.append(ops.fused_nvfp4_quant(w13, tiled_scales=True))
-        parts2.append(ops.fused_nvfp4_quant(w2, tiled_scales=True))
+        c13, sf13, gs13 = ops.fused_nvfp4_quant(w13, tiled_scales=True)
+        c2, sf2, gs2 = ops.fused_nvfp4_quant(w2, tiled_scales=True)
+        if moe_tp > 1:
+            rows = slice(member * inter, (member + 1) * inter)
+            # w13 = [w1; w3]: the member's rows of each; scale tiles are 128 rows x 4 blocks of 16
+            # elements, ordered (row tile, K tile)
+            c13 = c13.view(2, s.moe_inter, -1)[:, rows].reshape(2 * inter, -1).contiguous()
+            t13 = sf13.view(torch.uint8).view(2, s.moe_inter // 128, -1, 512)
+            sf13 = t13[:, member * inter // 128:(member + 1) * inter // 128].reshape(-1).contiguous()
+            # w2 [H, I]: the member's K range (bytes hold two elements, a K tile 64 of them)
+            c2 = c2[:, member * inter // 2:(member + 1) * inter // 2].contiguous()
+            t2 = sf2.view(torch.uint8).view(-1, s.moe_inter // 64, 512)
+            sf2 = t2[:, member * inter // 64:(member + 1) * inter // 64].reshape(-1).contiguous()
+        parts13.append((c13, sf13, gs13))
+        parts2.append((c2, sf2, gs2))
     cat = torch.cat
     return moe.NVFP4Experts(
-        e_loc, s.hidden, s.moe_inter,
+        e_loc, s.hidden, inter,
         cat([p[0] for p in parts13]), cat([p[1].view(torch.uint8) for p in parts13]),
         cat([p[2] for p in parts13]),
         cat([p[0] for p in parts2]), cat([p[1].view(torch.uint8) for p in parts2]),
@@ -237,9 +263,13 @@ class RealisticLayer:
         self.q_norm = torch.ones(shape.q_lora, device=dev, dtype=torch.bfloat16)
         self.kv_norm = torch.ones(shape.kv_lora, device=dev, dtype=torch.bfloat16)
         if ffn == "moe":
-            self.local_experts = shape.n_experts // world
             self.experts = weights["experts"] if "experts" in weights else \
                 moe.quantize_experts(weights["w13"], weights["w2"])
+            # experts cut along their intermediate dimension (make_nvfp4_experts, moe_tp) shrink
+            # the expert-parallel degree: world / moe_tp groups of consecutive ranks
+            self.moe_tp = max(1, shape.moe_inter // self.experts.inter)
+            self.local_experts = shape.n_experts // (world // self.moe_tp)
+            self.expert_begin = (rank // self.moe_tp) * self.local_experts
         else:
             self.w13d = Projection(torch.cat([weights["w1"], weights["w3"]]), proj)
             self.w2d = Projection(weights["w2d"], proj)
@@ -336,7 +366,7 @@ class RealisticLayer:
             weights, indices = self._route(normed)
             return moe.fused_moe_experts(normed, weights, indices, self.experts,
                                          n_experts=s.n_experts,
-                                         expert_begin=self.rank * self.local_experts, out=out)
+                                         expert_begin=self.expert_begin, out=out)
         gate_up = self.w13d(normed)
         inter = gate_up.shape[1] // 2
         if self.w2d.fp8:     # SwiGLU and the FP8 quantisation of its result in one kernel
@@ -374,7 +404,7 @@ class RealisticLayer:
                 codes, sf = c.all_gather_rows(codes), c.all_gather_rows(sf.view(torch.uint8))
                 weights, indices = c.all_gather_rows(weights), c.all_gather_rows(indices)
             return moe.fused_moe_experts(None, weights, indices, self.experts, n_experts=s.n_experts,
-                                         expert_begin=self.rank * self.local_experts,
+                                         expert_begin=self.expert_begin,
                                          x_quant=(codes, sf, gs), out=out)
         if self.w13d.fp8:
             codes, scales = ops.fused_act_quant(normed_rows)

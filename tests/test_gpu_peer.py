@@ -130,7 +130,7 @@ def _two_rank_layer(rank: int, world: int, port: int, out_dir: str):
     dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
     try:
         from racetrack_b200 import layer, ops
-        shape = layer.DSV32.scaled(hidden=1024, heads=16, q_lora=512, kv_lora=512, moe_inter=256,
+        shape = layer.DSV32.scaled(hidden=1024, heads=16, q_lora=512, kv_lora=512, moe_inter=512,
                                    n_experts=16, topk=4, dense_inter=2048, units=8)
         tokens, layers = 512, 2      # 256 rows per rank: above the split-K threshold of few-row GEMMs
         gen = torch.Generator().manual_seed(5)
@@ -158,9 +158,21 @@ def _two_rank_layer(rank: int, world: int, port: int, out_dir: str):
                     outs["attn_rows"] = rows.clone()
                 px.barrier()
                 px.check()
+            # experts cut along their intermediate dimension: one group of two members here
+            wt = layer.make_weights(shape, rank, world, dev, ffn="none", std=0.05, full_w_o=True)
+            wt["experts"] = layer.make_nvfp4_experts(shape, rank, world, dev, std=0.05, moe_tp=2)
+            mt = layer.RealisticLayer(shape, wt, rank, world, proj=proj)
+            assert mt.moe_tp == 2 and mt.local_experts == shape.n_experts and mt.expert_begin == 0
+            outs["moe_tp"] = mt.forward_stack(hidden, pos, layers)
+            normed_all = ops.fused_rms_norm(hidden, mt.ones_h, eps=shape.eps)
+            ffn_tp = mt.ffn_forward(normed_all)                 # all-reduced sum of the two members
+            for px in mt._peer.values():
+                px.check()
             # the same layer on ONE rank (every rank can build it: weights are drawn per unit)
-            w1 = layer.make_weights(shape, 0, 1, dev, std=0.05)
+            w1 = layer.make_weights(shape, 0, 1, dev, ffn="none", std=0.05)
+            w1["experts"] = layer.make_nvfp4_experts(shape, 0, 1, dev, std=0.05)
             m1 = layer.RealisticLayer(shape, w1, 0, 1, proj=proj)
+            ffn_one = m1.ffn_forward(normed_all)
             normed_all = ops.fused_rms_norm(hidden, m1.ones_h, eps=shape.eps)
             lo, hi = rank * tokens // world, (rank + 1) * tokens // world
             attn_all = m1.attention(normed_all, pos)
@@ -171,6 +183,11 @@ def _two_rank_layer(rank: int, world: int, port: int, out_dir: str):
                 "attn_rows_equal_single_rank": bool(torch.equal(outs["attn_rows"], attn_all[lo:hi])),
                 "exchange_vs_single": float((outs["exchange"].float() - one.float()).abs().max()) / scale,
                 "reduce_vs_single": float((outs["reduce"].float() - one.float()).abs().max()) / scale,
+                "moe_tp_vs_single": float((outs["moe_tp"].float() - one.float()).abs().max()) / scale,
+                # one feed-forward half on identical input: same quantised weights, the members'
+                # halves of h carry their own tensor-wide scales, two bf16 partial products per pair
+                "moe_tp_ffn_rel": float((ffn_tp.float() - ffn_one.float()).abs().max()) /
+                                  float(ffn_one.float().abs().max()),
             }
         torch.save(res, f"{out_dir}/layer_rank{rank}.pt")
     finally:
@@ -191,6 +208,7 @@ def test_two_rank_layer_schedules_against_the_single_rank_layer(tmp_path):
         for proj, v in res.items():
             assert v["attn_rows_equal_single_rank"], (r, proj)
             assert v["exchange_vs_single"] <= 0.3 and v["reduce_vs_single"] <= 0.3, (r, proj, v)
+            assert v["moe_tp_vs_single"] <= 0.3 and v["moe_tp_ffn_rel"] <= 0.1, (r, proj, v)
 
 
 def _two_rank_decode(rank: int, world: int, port: int, out_dir: str):
