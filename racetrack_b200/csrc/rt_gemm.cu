@@ -1243,10 +1243,23 @@ __global__ void __launch_bounds__(1024) moe_tile_map_kernel(const int32_t* __res
 // Tile 128 x 256, stage = one K block: 16 KB of A + 32 KB of B, 4 stages.
 // Warps: 0 TMA producer, 1 MMA issuer, 2-9 epilogue (warp w: lane quarter w % 4, column half
 // (w - 2) / 4).
-// A CTA-pair variant (256 x 256 tiles, half the operand bytes and TMA loads per K block, the
-// schedule that speeds the bf16 and NVFP4 GEMMs up) ran at the same 1.6-1.8 PFLOP/s, with the fold
-// waiting four times or twice per K block on tensor-memory loads, and was dropped: neither the
-// operands nor the fold's load latency is what holds this kernel at about 1000 cycles per K block.
+// What holds it at about 975 cycles per K block (1.8-1.9 PFLOP/s; the four MMAs of a K block
+// take 512): the round trip of a buffer. Measured in isolation on this part: an e4m3
+// 128 x 256 x 32 MMA takes 128 cycles back to back (twice the bf16 flops per cycle); tensor-memory
+// loads and MMAs do not slow each other down (the fold alone, eight warps, 386 cycles per
+// 128 x 256 block, with or without MMAs running); one hop through an mbarrier (arrive or commit
+// -> the parked waiter runs again) costs 145-175 cycles; and four MMAs issued into an IDLE
+// tensor pipe are seen complete by a waiter 977 cycles after the first issue (about 260 cycles
+// from issue to execution, 512 of execution, the hop). With two buffers a buffer comes back after
+// issue + execution + hop + loads + hop + the issuing thread's own wait, about 1900 cycles, and
+// two K blocks fit into that. Tried and measured no faster, because none of them shortens that
+// loop: a CTA-pair variant (256 x 256 tiles, two thirds of the operand bytes per K block, one
+// wait and one multicast commit per K block), a second issuing thread (one per buffer), one
+// arrival per warp instead of per thread, polling instead of parked waits, and the issuing thread
+// looking at the next K block's barriers before its last MMA. A third buffer does not fit (512
+// tensor-memory columns), narrower buffers make the issuing thread the limit (eight MMAs per K
+// block), and 16 fold warps or a register copy of the whole buffer before the fold do not fit
+// the register file (128 accumulators per thread).
 constexpr int kQBN = 256;
 constexpr int kQBK = 128;
 constexpr int kQStages = 4;
