@@ -870,9 +870,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kPThreads, 1) gemm_n
             auto weight_row = [&](int tile) {
                 return __ldg(wide_map + tile / num_w).x * N + (tile % num_w) * 256 + static_cast<int>(rank) * 128;
             };
-            // (Requesting the weight boxes into L2 a few stages ahead with cp.async.bulk.prefetch was
-            // measured slower, 1234 - 1295 us against 1195 - 1210 per w13 launch: the prefetches
-            // queue in the same TMA unit as the loads.)
+            // (Requesting the weight boxes into L2 a few stages ahead was measured slower both
+            // ways: with cp.async.bulk.prefetch, 1234 - 1295 us against 1195 - 1210 per w13 launch,
+            // and with one prefetch.global.L2 per 128-byte line from the scale producer's warp, 3, 6
+            // or 12 K blocks ahead, 1250 - 1277 against 1178 - 1186. DRAM latency is not what the
+            // operand stages wait for; the extra requests only compete with the loads.)
             for (int tile = pair; ok && tile < num_tiles; tile += num_pairs) {
                 const int4 tm = __ldg(wide_map + tile / num_w);
                 const int nh = pair_half_rows(tm.z);
