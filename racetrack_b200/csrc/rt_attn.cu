@@ -985,8 +985,20 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
         mbar_init(p_full, 32);
         for (int i = 0; i < 4; ++i) mbar_init(row_sync(i), 4);
         fence_mbar_init();
-        tma_prefetch_desc(&tm_qn);
-        tma_prefetch_desc(&tm_kn);
+        // The queries and the first two key tiles are requested here, by the thread that has just
+        // initialised the barriers they complete on (this CTA's own), so that their latency runs
+        // under the tensor-memory allocation and the cluster-wide synchronisation below instead
+        // of after them: a work item lasts some tens of microseconds and there are thousands.
+        const int pe_head0 = a.pe_shared ? 0 : h;
+        mbar_arrive_expect_tx(q_full, 3 * kFChunk);
+        tma_load_4d(base + kGQOff, &tm_qn, 0, q0 + 128 * rank, 0, h, q_full);
+        tma_load_4d(base + kGQOff + 2 * kFChunk, &tm_qp, 0, q0 + 128 * rank, 0, h, q_full);
+        for (int j = 0; j < 2 && j < n; ++j) {
+            const uint32_t dst = base + kGKOff + j * kGKStage;
+            mbar_arrive_expect_tx(k_full(j), kGKStage);
+            tma_load_4d(dst, &tm_kn, 0, 256 * j + 128 * rank, 0, h, k_full(j));
+            tma_load_4d(dst + 2 * kFChunk, &tm_kp, 0, 256 * j + 128 * rank, 0, pe_head0, k_full(j));
+        }
         tma_prefetch_desc(&tm_v);
     }
     if (warp == 1) {
@@ -1003,10 +1015,6 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
     if (warp == 0) {
         if (lane == 0) {
             const int pe_head = a.pe_shared ? 0 : h;
-            const int row_q = q0 + 128 * rank;
-            mbar_arrive_expect_tx(q_full, 3 * kFChunk);
-            tma_load_4d(base + kGQOff, &tm_qn, 0, row_q, 0, h, q_full);
-            tma_load_4d(base + kGQOff + 2 * kFChunk, &tm_qp, 0, row_q, 0, h, q_full);
             bool ok = true;
             auto load_k = [&](int j) {                         // this CTA's 128 keys of key tile j
                 const int st = j & 1;
@@ -1024,8 +1032,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kFThreads, 1) attn_p
                 tma_load_4d(base + kGVOff + st * kGVStage, &tm_v, 0, 256 * j, rank, h, v_full(st));
             };
             // in the order the stages become free: S(j) completes after O += P(j - 2) V(j - 2)
-            load_k(0);
-            if (n > 1) load_k(1);
+            // (the queries and key tiles 0 and 1 were requested before the cluster-wide set-up)
             for (int j = 0; ok && j < n; ++j) {
                 load_v(j);
                 if (ok && j + 2 < n) load_k(j + 2);
